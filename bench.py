@@ -1,0 +1,308 @@
+"""Benchmark of the MoE layer (router -> permute -> grouped expert GEMMs -> combine), forward and
+backward, on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one forward + backward pass of the layer over one batch of synthetic tokens
+(x ~ N(0,1), weights ~ N(0,0.02), upstream gradient ~ N(0,1), random-init weights).
+N = 1: T=16384, d_model=2048, E=64, d_ff=1408, top-6, bf16 (the headline configuration).
+N > 1: one process per GPU (torchrun); see `_workload` for the per-N workload.
+Prints ONE JSON line on rank 0.  `value` = tokens/s of the whole job with inputs resident in HBM;
+`e2e` = the same through the public nn.Module with host buffers (H2D of x and the upstream
+gradient, D2H of the output and grad_x inside the timed region).
+
+`--impl reference` times the reference's eager algorithm (the CPU oracle port) on the host cores
+on a bounded token sample of the same configuration.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+PKG = "triton-kernel-fused_b200"
+HEADLINE = dict(T=16384, H=2048, E=64, I=1408, k=6)
+# small case for profiler captures: weights (277 MB) exceed L2, about 1.5 GB held on the device
+PROFILE = dict(T=4096, H=2048, E=16, I=1408, k=6)
+METRIC = "moe_layer_fwd_bwd_tokens_per_s"
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], tflops=p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                    source="measured (MEASURED_PEAKS.json, sustained bf16)")
+    return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback (6.65 TB/s, 1.4 PFLOP/s sustained)")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except Exception:
+                continue
+            for name, col in (("hw_slowdown", 4), ("hw_thermal_slowdown", 5), ("sw_thermal_slowdown", 6),
+                              ("sw_power_cap", 7)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    samples=len(sm), reasons=sorted(reasons))
+
+
+def _workload(n_gpus, which="headline"):
+    """Per-rank workload.  N=1: the headline layer.  N>1: every rank holds the same layer and its own
+    T tokens (token-sharded replicas, no data-path collective) until the expert-parallel path replaces it."""
+    w = dict(HEADLINE if which == "headline" else PROFILE)
+    w["name"] = "bf16 MoE layer T={T} H={H} E={E} I={I} top{k} fwd+bwd".format(**w)
+    w["parallelism"] = "single GPU" if n_gpus == 1 else f"token-sharded replicas x{n_gpus} (no collective)"
+    return w
+
+
+def _make_layer(pkg, w, device, seed):
+    torch.manual_seed(seed)
+    layer = pkg.MoELayer(w["H"], w["I"], w["E"], top_k=w["k"])
+    return layer.to(device).to(torch.bfloat16)
+
+
+def run_ours(args):
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    pkg = importlib.import_module(PKG)
+    pkg.lib()
+    ops = pkg.ops
+    w = _workload(world, args.workload)
+    T, H, E, I, k = w["T"], w["H"], w["E"], w["I"], w["k"]
+    layer = _make_layer(pkg, w, dev, seed=0)
+    params = [layer.gate.weight, layer.gate_up_proj, layer.down_proj]
+    g = torch.Generator(device=dev).manual_seed(1 + rank)
+    x_dev = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+    go_dev = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+    x_host = x_dev.cpu().pin_memory()
+    go_host = go_dev.cpu().pin_memory()
+    out_host = torch.empty_like(x_host).pin_memory()
+    gx_host = torch.empty_like(x_host).pin_memory()
+
+    def step_resident():
+        for p in params:
+            p.grad = None
+        x = x_dev.detach().requires_grad_(True)
+        out = layer(x)
+        out.backward(go_dev)
+        return out, x.grad
+
+    def step_e2e():
+        for p in params:
+            p.grad = None
+        x = x_host.to(dev, non_blocking=True).requires_grad_(True)
+        go = go_host.to(dev, non_blocking=True)
+        out = layer(x)
+        out.backward(go)
+        out_host.copy_(out.detach(), non_blocking=True)
+        gx_host.copy_(x.grad, non_blocking=True)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    n_warm = args.warmup if args.workload == "profile" else max(args.warmup, 3)
+    for _ in range(n_warm):
+        step_resident()
+    pkg.check_status()
+
+    # ---- timed region 1: inputs resident in HBM; per-op CUDA events on the launching stream
+    records = []
+    ops.set_hook(lambda name, launches, a, b: records.append((name, launches, a, b)))
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_total = timed(step_resident, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ops.set_hook(None)
+    pkg.check_status()
+    per_op = {}
+    launches = 0
+    for name, n, a, b in records:
+        d = per_op.setdefault(name, [0.0, 0])
+        d[0] += a.elapsed_time(b)
+        d[1] += 1
+        launches += n
+    ms_step = ms_total / args.steps
+
+    # ---- timed region 2: through the module with host buffers
+    for _ in range(min(2, n_warm)):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps) / args.steps
+    pkg.check_status()
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+    peaks = _peaks()
+    M = T * k
+    flops = {  # algorithmic FLOPs per launch (padding rows not counted)
+        "expert_gate_up_swiglu": 2.0 * M * H * 2 * I, "expert_down": 2.0 * M * I * H,
+        "expert_down_dgrad_glu": 2.0 * M * H * I, "expert_gate_up_dgrad": 2.0 * M * 2 * I * H,
+        "expert_wgrad": (2.0 * M * H * I + 2.0 * M * 2 * I * H) / 2.0,   # two launches per step, averaged
+    }
+    kernels = {}
+    for name, (ms, n) in sorted(per_op.items(), key=lambda kv: -kv[1][0]):
+        avg = ms / n
+        entry = dict(launches_per_step=n / args.steps, avg_ms=round(avg, 4), share=round(ms / ms_total, 4))
+        if name in flops:
+            entry["tflops"] = round(flops[name] / (avg * 1e-3) / 1e12, 1)
+        kernels[name] = entry
+    gemm_ms = sum(per_op[n][0] for n in flops if n in per_op) / args.steps
+    top = max((n for n in flops if n in per_op), key=lambda n: per_op[n][0])
+    top_avg_ms = per_op[top][0] / per_op[top][1]
+    achieved = flops[top] / (top_avg_ms * 1e-3) / 1e12
+    layer_flops = 18.0 * H * I * T * k
+    line = {
+        "metric": METRIC, "value": round(T * world / (ms_step * 1e-3), 1), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": n_warm, "ms_per_step": round(ms_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": w["name"], "tokens_per_gpu": T, "d_model": H, "experts": E, "d_ff": I, "top_k": k,
+                   "parallelism": w["parallelism"],
+                   "l2": "working set (1.1 GB of expert weights + 2 GB of activations) exceeds the 126 MB L2"},
+        "layer_tflops_per_gpu": round(layer_flops / (ms_step * 1e-3) / 1e12, 1),
+        "layer_frac_of_peak": round(layer_flops / (ms_step * 1e-3) / 1e12 / peaks["tflops"], 4),
+        "gemm_ms_per_step": round(gemm_ms, 4),
+        "roofline": {"bound": "tensor", "kernel": f"gemm_kernel via {top}", "achieved": round(achieved, 1),
+                     "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": round(achieved / peaks["tflops"], 4),
+                     "traffic": None, "peak_source": peaks["source"]},
+        "kernels": kernels,
+        "e2e": {"value": round(T * world / (ms_e2e * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 4),
+                "h2d_bytes_per_step": 2 * T * H * 2, "d2h_bytes_per_step": 2 * T * H * 2},
+        "gpu_launches": launches,
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(w, steps=1, warmup=0)
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(w, steps, warmup, sample_tokens=512):
+    """The oracle port (plain PyTorch fp32 on the host cores) on a bounded sample: `sample_tokens`
+    tokens through the full-size layer (all E experts, full d_model and d_ff), forward + backward."""
+    from oracle import moe_oracle as O
+    T, H, E, I, k = sample_tokens, w["H"], w["E"], w["I"], w["k"]
+    inp = O.make_inputs(T, H, E, I, k, seed=0)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        O.layer_fwd_bwd(inp["x"], inp["gate_weight"], None, inp["gate_up"], inp["down"], k, inp["grad_out"])
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    return {"value": round(T / sec, 1), "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "ms_per_step": round(sec * 1e3, 2),
+            "sample": f"{T} of {w['T']} tokens through the full-size layer (E={E}, H={H}, I={I}, top{k}), fp32, "
+                      f"oracle/moe_oracle.py layer_fwd_bwd, host cpu_count={os.cpu_count()}"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if rank != 0:
+        return
+    w = _workload(world, args.workload)
+    cb = cpu_baseline(w, steps=max(1, min(args.steps, 3)), warmup=min(args.warmup, 1))
+    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tokens/s", "n_gpus": world,
+            "steps": max(1, min(args.steps, 3)), "warmup": min(args.warmup, 1), "ms_per_step": cb["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": w["name"], "d_model": w["H"], "experts": w["E"], "d_ff": w["I"], "top_k": w["k"],
+                       "parallelism": "host cores, one process"},
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="headline", choices=["headline", "profile"],
+                    help="profile = small case for profiler captures (not a benchmark number)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,152 @@
+/* libb200moe — C ABI of the B200 (sm_100a) MoE hot path.
+ *
+ * The reference (IsNoobgrammer/triton-kernel-fused) has no native interface: its boundary is a set
+ * of Python callables (kernels/sm75/moe.py:838 `moe`, kernels/sm75/router.py:277 `fused_mlp_router`,
+ * :292 `router_bias_update`).  This library sits underneath a Python package that keeps those
+ * signatures; each entry point below replaces one launch site of the reference and cites it.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless it says "host"; the library never allocates or frees
+ *     device memory and never synchronises the device; all work is queued on `stream`;
+ *   - bf16 matrices are row-major and contiguous unless a leading dimension is given;
+ *   - return value: 0 on success, a negative B200MOE_E_* code otherwise (nothing was launched);
+ *     b200moe_last_error_string() describes the last failure on the calling thread;
+ *   - `status` is a caller-owned device int32, zero-initialised once.  Kernels write a non-zero
+ *     code there when a bounded wait ran out or an index was out of range (see
+ *     b200moe_status_string); the word is never cleared by the library;
+ *   - "padded rows": routed rows live in an expert-contiguous layout in which expert e owns rows
+ *     [poffs[e], poffs[e+1]) and every segment is a multiple of B200MOE_TILE_M rows; rows past the
+ *     expert's count are zero rows.  Buffers are sized for the worst case b200moe_padded_rows_cap().
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* b200moe_stream_t; /* == cudaStream_t */
+
+#define B200MOE_TILE_M 128
+#define B200MOE_MAX_EXPERTS 256
+#define B200MOE_MAX_TOPK 32
+
+enum {
+  B200MOE_OK = 0,
+  B200MOE_E_BAD_SHAPE = -1,
+  B200MOE_E_ALIGN = -2,
+  B200MOE_E_UNSUPPORTED = -3,
+  B200MOE_E_WS_TOO_SMALL = -4,
+  B200MOE_E_CUDA = -5,
+  B200MOE_E_NULL = -6
+};
+
+/* kinds of router input accepted by the top-k epilogue */
+enum { B200MOE_LOGITS_BF16 = 0, B200MOE_LOGITS_F32 = 1, B200MOE_SCORES_F32 = 2 };
+
+const char* b200moe_version(void);
+const char* b200moe_last_error_string(void);
+/* host: text for a value read back from a `status` word */
+const char* b200moe_status_string(int status_word);
+/* host: worst-case number of padded rows for M routed rows over E experts */
+int64_t b200moe_padded_rows_cap(int64_t M, int E);
+
+/* ---- router --------------------------------------------------------------------------------- */
+/* Replaces _router_epilogue_fwd_kernel (kernels/sm75/router.py:39-83, launcher :129-148):
+ * sigmoid, +bias for selection only, k rounds of lowest-index argmax with knock-out, unbiased
+ * weights, optional /(sum+1e-20), *scale; counts (nullable) are zeroed then accumulated.
+ * input: (T,E) of `input_kind`; bias: (E) fp32 or NULL; idx: (T,k) int64; w: (T,k) fp32. */
+int b200moe_router_topk_fwd(const void* input, int input_kind, const float* bias, int64_t T, int E,
+                            int k, int norm_topk, float scale, int64_t* idx, float* w,
+                            int32_t* counts, b200moe_stream_t stream);
+
+/* Replaces _router_epilogue_bwd_kernel (kernels/sm75/router.py:86-126): grad_logits (T,E) bf16. */
+int b200moe_router_topk_bwd(const void* logits, int input_kind, const int64_t* idx,
+                            const float* grad_w, int64_t T, int E, int k, int norm_topk, float scale,
+                            void* grad_logits, b200moe_stream_t stream);
+
+/* Replaces router_bias_update (kernels/sm75/router.py:292-301): b += u*sign(mean(c)-c); no-op u<=0. */
+int b200moe_router_bias_update(float* bias, const int32_t* counts, int E, float u,
+                               b200moe_stream_t stream);
+
+/* ---- dense bf16 GEMMs on tcgen05 (router projections) ----------------------------------------
+ * Replace the cuBLAS calls at kernels/sm75/router.py:235 (logits), :258 (dX), :259 (dW).
+ * nt: D(M,N) = A(M,K) * B(N,K)^T      nn: D(M,N) = A(M,K) * B(K,N)
+ * tn_splitk: P[s](M,N) fp32 = A(Kc_s,M)^T * B(Kc_s,N) over K-chunk s of `k_chunk` rows (multiple
+ * of 64); P holds ceil(K/k_chunk) slices; splitk_reduce sums the slices into bf16 D(M,N).
+ * All leading dimensions and N, K must be multiples of 8 elements; base pointers 16-byte aligned. */
+int b200moe_gemm_nt(const void* A, const void* B, void* D, int64_t M, int64_t N, int64_t K,
+                    int32_t* status, b200moe_stream_t stream);
+int b200moe_gemm_nn(const void* A, const void* B, void* D, int64_t M, int64_t N, int64_t K,
+                    int32_t* status, b200moe_stream_t stream);
+int b200moe_gemm_tn_splitk(const void* A, const void* B, float* P, int64_t M, int64_t N, int64_t K,
+                           int64_t k_chunk, int32_t* status, b200moe_stream_t stream);
+int b200moe_splitk_reduce(const float* P, int64_t slices, int64_t elems, void* D,
+                          b200moe_stream_t stream);
+
+/* ---- permutation ---------------------------------------------------------------------------- */
+size_t b200moe_permute_ws_bytes(int64_t M, int E);
+/* Replaces _sort_by_expert + _build_schedule (kernels/sm75/moe.py:564-572, :535-543) with a stable
+ * counting sort done on the device, no host sync.  idx: (T,k) int64.
+ * Outputs: counts (E), offs (E+1) compact end-exclusive scan, poffs (E+1) padded scan,
+ * slot_row (T*k) padded row of slot t*k+j, row_slot (cap) slot of each padded row or -1 (only rows
+ * below poffs[E] are written), tile_expert (cap/128) expert of each row tile,
+ * order (T*k, nullable) = the stable argsort of idx.flatten(). ws: scratch, ws_bytes from above. */
+int b200moe_permute_build(const int64_t* idx, int64_t T, int k, int E, int32_t* counts,
+                          int32_t* offs, int32_t* poffs, int32_t* slot_row, int32_t* row_slot,
+                          int32_t* tile_expert, int64_t* order, void* ws, size_t ws_bytes,
+                          int32_t* status, b200moe_stream_t stream);
+
+/* Replaces hidden.index_select(0, st) (kernels/sm75/moe.py:744, :589): x_s[r] = x[row_slot[r]/k],
+ * zero rows where row_slot[r] < 0.  Only rows below *total_rows (device) are written. */
+int b200moe_gather_rows(const void* x, const int32_t* row_slot, const int32_t* total_rows, int k,
+                        int64_t H, int64_t rows_cap, void* x_s, b200moe_stream_t stream);
+
+/* ---- grouped expert GEMMs (tcgen05, persistent, TMA-fed) -------------------------------------
+ * All take the tables from b200moe_permute_build; `rows_cap` bounds the padded-row buffers. */
+/* Replaces the gate/up GEMM + _glu_fwd (kernels/sm75/moe.py:590-591, :765-767), act code 0:
+ * gate_up (rows,2I) bf16 = x_s * W_gu[e]^T (cols [0,I) gate, [I,2I) up); inter = silu(gate)*up. */
+int b200moe_expert_gate_up_swiglu(const void* x_s, const void* gate_up_proj,
+                                  const int32_t* tile_expert, const int32_t* poffs,
+                                  int64_t rows_cap, int E, int64_t H, int64_t I, void* gate_up,
+                                  void* inter, int32_t* status, b200moe_stream_t stream);
+/* Replaces the down GEMM (kernels/sm75/moe.py:592, :770): eo (rows,H) = inter * W_d[e]^T. */
+int b200moe_expert_down(const void* inter, const void* down_proj, const int32_t* tile_expert,
+                        const int32_t* poffs, int64_t rows_cap, int E, int64_t H, int64_t I,
+                        void* eo, int32_t* status, b200moe_stream_t stream);
+/* Replaces grad_inter = grad_eo @ W_d[e] + _glu_bwd (kernels/sm75/moe.py:609,611, :807,818):
+ * grad_gate_up (rows,2I) = [grad_gate | grad_up] from grad_inter and the saved gate_up. */
+int b200moe_expert_down_dgrad_glu(const void* grad_eo, const void* down_proj, const void* gate_up,
+                                  const int32_t* tile_expert, const int32_t* poffs,
+                                  int64_t rows_cap, int E, int64_t H, int64_t I, void* grad_gate_up,
+                                  int32_t* status, b200moe_stream_t stream);
+/* Replaces grad_x_s = grad_gate_up @ W_gu[e] (kernels/sm75/moe.py:612, :822). */
+int b200moe_expert_gate_up_dgrad(const void* grad_gate_up, const void* gate_up_proj,
+                                 const int32_t* tile_expert, const int32_t* poffs,
+                                 int64_t rows_cap, int E, int64_t H, int64_t I, void* grad_x_s,
+                                 int32_t* status, b200moe_stream_t stream);
+/* Replaces _grouped_wgrad / ge.t() @ it (kernels/sm75/moe.py:556-561, :808, :821):
+ * out[e] (Na,Nb) bf16 = A[rows of e]^T * B[rows of e]; experts with no rows get zeros. */
+int b200moe_expert_wgrad(const void* A, const void* B, const int32_t* poffs, int64_t rows_cap,
+                         int E, int64_t Na, int64_t Nb, void* out, int32_t* status,
+                         b200moe_stream_t stream);
+
+/* ---- combine -------------------------------------------------------------------------------- */
+/* Replaces _combine_scatter_kernel / index_add_ (kernels/sm75/moe.py:673-682, :593-595):
+ * out[t] = sum_j w[t,j] * rows[slot_row[t*k+j]], fp32 accumulate in slot order, bf16 store.
+ * w == NULL means weight 1 (the grad_hidden un-permute, kernels/sm75/moe.py:614-615). */
+int b200moe_combine(const void* rows, const float* w, const int32_t* slot_row, int64_t T, int k,
+                    int64_t H, void* out, b200moe_stream_t stream);
+/* Replaces _combine_bwd_kernel (kernels/sm75/moe.py:688-701): grad_eo[r] = go[tok]*w[slot],
+ * grad_w[slot] = <go[tok], eo[r]> in fp32; zero rows where row_slot[r] < 0. */
+int b200moe_combine_bwd(const void* grad_out, const void* eo, const float* w,
+                        const int32_t* row_slot, const int32_t* total_rows, int k, int64_t H,
+                        int64_t rows_cap, void* grad_eo, float* grad_w, b200moe_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

@@ -191,23 +191,32 @@ def moe_experts(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj):
     order, st, counts, offs = sort_by_expert_stable(top_k_indices, E)
     sw = top_k_weights.flatten()[order]
     out = torch.zeros(N, H, dtype=torch.float32)
+    # unbind once: the backward of a per-expert select would allocate a full (E,.,.) zero tensor per
+    # expert; this only changes how autograd accumulates, not any value
+    w_gu, w_dn = gate_up_proj.unbind(0), down_proj.unbind(0)
     for e in range(E):
         s, en = int(offs[e]), int(offs[e + 1])
         if en == s:
             continue
         rows = st[s:en]
-        gu = hidden[rows] @ gate_up_proj[e].t()
+        gu = hidden[rows] @ w_gu[e].t()
         inter = swiglu(gu, I)
-        eo = inter @ down_proj[e].t()
+        eo = inter @ w_dn[e].t()
         out = out.index_add(0, rows, (eo * sw[s:en].unsqueeze(-1).to(eo.dtype)).float())
     return out.to(hidden.dtype)
 
 
-def moe_layer(x, gate_weight, bias, gate_up_proj, down_proj, top_k, norm_topk=True, scale=1.0):
+def moe_layer(x, gate_weight, bias, gate_up_proj, down_proj, top_k, norm_topk=True, scale=1.0,
+              logits_dtype=None):
     """Whole block, differentiable by autograd w.r.t. x, gate_weight and the expert weights:
-    router (selection is non-differentiable, weights are) -> experts -> combine."""
+    router (selection is non-differentiable, weights are) -> experts -> combine.
+    logits_dtype: round the logits to this dtype before the sigmoid, as the reference does when it
+    runs in bf16 (kernels/sm75/router.py:235 stores logits in x's dtype); gradients pass straight
+    through the rounding."""
     xf = x.reshape(-1, x.shape[-1])
     logits = (xf @ gate_weight.t())
+    if logits_dtype is not None:
+        logits = logits + (logits.detach().to(logits_dtype).to(logits.dtype) - logits.detach())
     with torch.no_grad():
         idx, _, counts = router_epilogue_fwd(logits, bias, top_k, norm_topk, scale)
     s = 1.0 / (1.0 + torch.exp(-logits.float()))
@@ -220,13 +229,13 @@ def moe_layer(x, gate_weight, bias, gate_up_proj, down_proj, top_k, norm_topk=Tr
 
 
 def layer_fwd_bwd(x, gate_weight, bias, gate_up_proj, down_proj, top_k, grad_out,
-                  norm_topk=True, scale=1.0):
+                  norm_topk=True, scale=1.0, logits_dtype=None):
     """Forward + backward of the block under loss = sum(out * grad_out); returns a dict of the
     output and every gradient (fp32 when the inputs are fp32)."""
     leaves = [t.detach().clone().requires_grad_(True)
               for t in (x, gate_weight, gate_up_proj, down_proj)]
     xl, gl, gul, dl = leaves
-    out, idx, w, counts = moe_layer(xl, gl, bias, gul, dl, top_k, norm_topk, scale)
+    out, idx, w, counts = moe_layer(xl, gl, bias, gul, dl, top_k, norm_topk, scale, logits_dtype)
     (out.float() * grad_out.float()).sum().backward()
     return dict(out=out.detach(), idx=idx, w=w.detach(), counts=counts, grad_x=xl.grad,
                 grad_gate_weight=gl.grad, grad_gate_up=gul.grad, grad_down=dl.grad)

@@ -1,0 +1,252 @@
+"""GPU: expert pipeline stage by stage and end to end, against the CPU oracle and the golden
+vectors the reference itself produced."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+from tests.golden.cases import CASES, sub
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TOL_BF16 = 2e-2        # relative L2 vs the fp32 reference, outputs and gradients (stated gate)
+
+
+def _stage_reference(x, idx, w, gu, dn, go):
+    """fp32 CPU values of every intermediate in the padded layout, from bf16-rounded inputs."""
+    E, twoI, H = gu.shape
+    I = twoI // 2
+    tb = O.permutation_tables(idx, E)
+    total = int(tb["poffs"][-1])
+    rs = tb["row_slot"]
+    live = rs >= 0
+    tok = (rs.clamp_min(0) // idx.shape[1]).long()
+    x_s = torch.zeros(total, H)
+    x_s[live] = x.float()[tok[live]]
+    te = torch.repeat_interleave(tb["tile_expert"].long(), 128)
+    gate_up = torch.zeros(total, twoI)
+    eo = torch.zeros(total, H)
+    inter = torch.zeros(total, I)
+    for e in range(E):
+        m = te == e
+        gate_up[m] = x_s[m] @ gu[e].float().t()
+        inter[m] = O.swiglu(gate_up[m], I)
+        eo[m] = inter[m] @ dn[e].float().t()
+    return tb, total, x_s, gate_up, inter, eo, te
+
+
+@pytest.mark.parametrize("T,H,E,I,k", [(1024, 256, 8, 192, 2), (700, 128, 6, 96, 2), (2048, 512, 16, 320, 4)])
+def test_forward_stages(pkg, T, H, E, I, k):
+    inp = O.make_inputs(T, H, E, I, k, seed=21, bias_std=0.01, dtype=torch.bfloat16)
+    idx, w, _ = O.router_epilogue_fwd(inp["x"].float() @ inp["gate_weight"].float().t(), inp["bias"], k)
+    tb, total, x_s, gate_up, inter, eo, te = _stage_reference(inp["x"], idx, w, inp["gate_up"], inp["down"], None)
+    ops = pkg.ops
+    perm = ops.permute_build(idx.to(DEV), E)
+    xs_d = ops.gather_rows(inp["x"].to(DEV), perm)
+    gu_d, it_d = ops.expert_gate_up_swiglu(xs_d, inp["gate_up"].to(DEV), perm)
+    pkg.check_status()
+    assert O.rel_l2(gu_d[:total].float().cpu(), gate_up) < 4e-3
+    assert O.rel_l2(it_d[:total].float().cpu(), inter) < 8e-3
+    eo_d = ops.expert_down(it_d, inp["down"].to(DEV), perm)
+    pkg.check_status()
+    assert O.rel_l2(eo_d[:total].float().cpu(), eo) < 1e-2
+    out = ops.combine(eo_d, w.to(DEV), perm)
+    ref = O.moe_experts(inp["x"].float(), idx, w, inp["gate_up"].float(), inp["down"].float())
+    assert O.rel_l2(out.float().cpu(), ref) < TOL_BF16
+    # pad rows stay zero through the whole forward
+    pad = (tb["row_slot"] < 0)
+    assert (gu_d[:total].cpu()[pad] == 0).all() and (eo_d[:total].cpu()[pad] == 0).all()
+
+
+@pytest.mark.parametrize("T,H,E,I,k", [(1024, 256, 8, 192, 2), (2048, 512, 16, 320, 4)])
+def test_backward_stages(pkg, T, H, E, I, k):
+    inp = O.make_inputs(T, H, E, I, k, seed=22, bias_std=0.01, dtype=torch.bfloat16)
+    idx, w, _ = O.router_epilogue_fwd(inp["x"].float() @ inp["gate_weight"].float().t(), inp["bias"], k)
+    tb, total, x_s, gate_up, inter, eo, te = _stage_reference(inp["x"], idx, w, inp["gate_up"], inp["down"], None)
+    rs = tb["row_slot"]
+    live = rs >= 0
+    tok = (rs.clamp_min(0) // k).long()
+    go = inp["grad_out"].float()
+    grad_eo = torch.zeros(total, H)
+    grad_eo[live] = go[tok[live]] * w.flatten()[rs[live].long()][:, None]
+    grad_w = torch.zeros(T * k)
+    grad_w[rs[live].long()] = (go[tok[live]] * eo[live]).sum(1)
+    ops = pkg.ops
+    perm = ops.permute_build(idx.to(DEV), E)
+    to = lambda t: t.to(torch.bfloat16).to(DEV)
+    cap = perm.cap
+
+    def padded(t):
+        buf = torch.zeros(cap, t.shape[1], dtype=torch.bfloat16, device=DEV)
+        buf[:total] = to(t)
+        return buf
+
+    geo_d, gw_d = ops.combine_bwd(to(go), padded(eo), w.to(DEV), perm)
+    assert O.rel_l2(geo_d[:total].float().cpu(), grad_eo) < 4e-3
+    assert O.rel_l2(gw_d.flatten().cpu(), grad_w) < 1e-2
+
+    # dgrad(down) + GLU backward
+    gu_b = padded(gate_up)
+    ggu_d = ops.expert_down_dgrad_glu(padded(grad_eo), inp["down"].to(DEV), gu_b, perm)
+    pkg.check_status()
+    g = gu_b[:total].float().cpu()
+    gate, up = g[:, :I], g[:, I:]
+    grad_inter = torch.zeros(total, I)
+    for e in range(E):
+        m = te == e
+        grad_inter[m] = padded(grad_eo)[:total].float().cpu()[m] @ inp["down"][e].float()
+    s = torch.sigmoid(gate)
+    ref_ggu = torch.cat([grad_inter * up * s * (1 + gate * (1 - s)), grad_inter * gate * s], 1)
+    assert O.rel_l2(ggu_d[:total].float().cpu(), ref_ggu) < 1.2e-2
+
+    # dgrad(gate_up)
+    gx_d = ops.expert_gate_up_dgrad(padded(ref_ggu), inp["gate_up"].to(DEV), perm)
+    pkg.check_status()
+    ref_gx = torch.zeros(total, H)
+    rg = padded(ref_ggu)[:total].float().cpu()
+    for e in range(E):
+        m = te == e
+        ref_gx[m] = rg[m] @ inp["gate_up"][e].float()
+    assert O.rel_l2(gx_d[:total].float().cpu(), ref_gx) < 4e-3
+
+    # wgrads
+    a, b = padded(grad_eo), padded(inter)
+    gwd_d = ops.expert_wgrad(a, b, perm)
+    pkg.check_status()
+    ref = torch.stack([a[:total].float().cpu()[te == e].t() @ b[:total].float().cpu()[te == e] for e in range(E)])
+    assert O.rel_l2(gwd_d.float().cpu(), ref) < 4e-3
+    a, b = padded(ref_ggu), padded(x_s)
+    gwu_d = ops.expert_wgrad(a, b, perm)
+    pkg.check_status()
+    ref = torch.stack([a[:total].float().cpu()[te == e].t() @ b[:total].float().cpu()[te == e] for e in range(E)])
+    assert O.rel_l2(gwu_d.float().cpu(), ref) < 4e-3
+
+
+def _run_moe(pkg, inp, idx, w):
+    leaves = dict(hidden=inp["x"].to(torch.bfloat16).to(DEV).requires_grad_(True),
+                  wt=w.to(DEV).requires_grad_(True),
+                  gu=inp["gate_up"].to(torch.bfloat16).to(DEV).requires_grad_(True),
+                  dn=inp["down"].to(torch.bfloat16).to(DEV).requires_grad_(True))
+    E = inp["gate_up"].shape[0]
+    codes = torch.zeros(E, dtype=torch.int32, device=DEV)
+    out = pkg.moe(leaves["hidden"], idx.to(DEV), leaves["wt"], leaves["gu"], leaves["dn"], codes)
+    (out.float() * inp["grad_out"].to(DEV).float()).sum().backward()
+    pkg.check_status()
+    return out, leaves
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_moe_against_reference_golden(pkg, golden_dir, name):
+    """bf16 CUDA path vs the fp32 outputs of the reference's own moe_eager (stored fixtures)."""
+    T, H, E, I, k, seed, bstd, cap = CASES[name]
+    g = np.load(os.path.join(golden_dir, f"experts_{name}.npz"))
+    inp = O.make_inputs(T, H, E, I, k, seed=seed, bias_std=bstd)
+    idx, w = torch.from_numpy(g["idx"]), torch.from_numpy(g["w"])
+    out, lv = _run_moe(pkg, inp, idx, w)
+    assert out.dtype == torch.bfloat16 and out.shape == (T, H)
+    assert O.rel_l2(out.float().cpu(), torch.from_numpy(g["out"])) < TOL_BF16
+    assert O.rel_l2(lv["hidden"].grad.float().cpu(), torch.from_numpy(g["grad_hidden"])) < TOL_BF16
+    assert O.rel_l2(lv["wt"].grad.float().cpu(), torch.from_numpy(g["grad_w"])) < TOL_BF16
+    assert O.rel_l2(sub(lv["gu"].grad.float().cpu()), torch.from_numpy(g["grad_gate_up_sub"])) < TOL_BF16
+    assert O.rel_l2(sub(lv["dn"].grad.float().cpu()), torch.from_numpy(g["grad_down_sub"])) < TOL_BF16
+    if cap is not None:     # experts without tokens: exactly zero weight gradients, no NaN
+        assert (lv["gu"].grad[cap:] == 0).all() and (lv["dn"].grad[cap:] == 0).all()
+    for t in lv.values():
+        assert torch.isfinite(t.grad).all()
+
+
+def test_moe_mid_size_vs_oracle_and_determinism(pkg):
+    T, H, E, I, k = 4096, 1024, 16, 704, 4
+    inp = O.make_inputs(T, H, E, I, k, seed=5, dtype=torch.bfloat16)
+    idx, w, _, _ = O.mlp_router_fwd(inp["x"], inp["gate_weight"], None, k)
+    out, lv = _run_moe(pkg, inp, idx, w)
+    out2, lv2 = _run_moe(pkg, inp, idx, w)
+    assert torch.equal(out, out2)
+    for n in lv:
+        assert torch.equal(lv[n].grad, lv2[n].grad), n      # no atomics anywhere: bit-identical reruns
+    hidden = inp["x"].float().requires_grad_(True)
+    wt = w.clone().requires_grad_(True)
+    gu = inp["gate_up"].float().requires_grad_(True)
+    dn = inp["down"].float().requires_grad_(True)
+    ref = O.moe_experts(hidden, idx, wt, gu, dn)
+    (ref * inp["grad_out"].float()).sum().backward()
+    assert O.rel_l2(out.float().cpu(), ref.detach()) < TOL_BF16
+    assert O.rel_l2(lv["hidden"].grad.float().cpu(), hidden.grad) < TOL_BF16
+    assert O.rel_l2(lv["wt"].grad.float().cpu(), wt.grad) < TOL_BF16
+    assert O.rel_l2(lv["gu"].grad.float().cpu(), gu.grad) < TOL_BF16
+    assert O.rel_l2(lv["dn"].grad.float().cpu(), dn.grad) < TOL_BF16
+
+
+def test_layer_module_vs_oracle(pkg):
+    T, H, E, I, k = 2048, 512, 32, 256, 6
+    inp = O.make_inputs(T, H, E, I, k, seed=8, bias_std=0.01, dtype=torch.bfloat16)
+    layer = pkg.MoELayer(H, I, E, top_k=k).to(DEV).to(torch.bfloat16)
+    with torch.no_grad():
+        layer.gate.weight.copy_(inp["gate_weight"])
+        layer.gate_up_proj.copy_(inp["gate_up"])
+        layer.down_proj.copy_(inp["down"])
+        layer.bias.copy_(inp["bias"])
+    assert layer.bias.dtype == torch.float32
+    x = inp["x"].to(DEV).view(4, T // 4, H).requires_grad_(True)
+    out = layer(x)
+    (out.float() * inp["grad_out"].to(DEV).view_as(out).float()).sum().backward()
+    pkg.check_status()
+    r = O.layer_fwd_bwd(inp["x"].float(), inp["gate_weight"].float(), inp["bias"], inp["gate_up"].float(),
+                        inp["down"].float(), k, inp["grad_out"].float(), logits_dtype=torch.bfloat16)
+    # tokens whose routing agrees (a logit on a bf16 rounding boundary can flip a pick): compare those rows
+    idx_d, _, _ = pkg.fused_mlp_router(inp["x"].to(DEV), layer.gate.weight, layer.bias, k, E, return_counts=True)
+    rows = (idx_d.cpu() == r["idx"]).all(1)
+    assert rows.float().mean() > 0.995
+    assert O.rel_l2(out.view(T, H).float().cpu()[rows], r["out"][rows]) < TOL_BF16
+    assert O.rel_l2(x.grad.view(T, H).float().cpu()[rows], r["grad_x"][rows]) < 3e-2
+    assert O.rel_l2(layer.down_proj.grad.float().cpu(), r["grad_down"]) < 6e-2     # includes flipped tokens
+    assert torch.equal(layer.last_counts.cpu().long(), torch.bincount(idx_d.flatten().cpu(), minlength=E))
+    layer.update_bias(0.001)
+    assert (layer.bias != inp["bias"].to(DEV)).any()
+
+
+def test_skewed_routing_with_empty_experts(pkg):
+    """Zipf-skewed logit bias (reduced size of the many-expert skewed config): some experts get no
+    tokens; their weight gradients are exactly zero and nothing is NaN."""
+    T, H, E, I, k = 4096, 256, 128, 128, 8
+    inp = O.make_inputs(T, H, E, I, k, seed=3, zipf_s=1.1, dtype=torch.bfloat16)
+    logits = inp["x"].float() @ inp["gate_weight"].float().t() + 3.0 * inp["logit_bias"][None, :]
+    idx, w, counts = O.router_epilogue_fwd(logits, None, k)
+    assert (counts == 0).any()
+    out, lv = _run_moe(pkg, inp, idx, w)
+    empty = counts == 0
+    assert (lv["gu"].grad.cpu()[empty] == 0).all() and (lv["dn"].grad.cpu()[empty] == 0).all()
+    ref = O.moe_experts(inp["x"].float(), idx, w, inp["gate_up"].float(), inp["down"].float())
+    assert O.rel_l2(out.float().cpu(), ref) < TOL_BF16
+    for t in lv.values():
+        assert torch.isfinite(t.grad).all()
+
+
+def test_full_size_properties(pkg):
+    """Benchmark-size layer (T=16384, H=2048, E=64, I=1408, k=6): size-independent properties.
+    (1) doubling the routing weights doubles the output bit-exactly; (2) permuting the tokens
+    permutes the output rows bit-exactly; (3) the permutation tables invert each other."""
+    T, H, E, I, k = 16384, 2048, 64, 1408, 6
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = torch.randn(T, H, device=DEV, generator=g).to(torch.bfloat16)
+    gu = (torch.randn(E, 2 * I, H, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    dn = (torch.randn(E, H, I, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    wr = (torch.randn(E, H, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    codes = torch.zeros(E, dtype=torch.int32, device=DEV)
+    idx, w = pkg.fused_mlp_router(x, wr, None, k, E)
+    out = pkg.moe(x, idx, w, gu, dn, codes)
+    out2 = pkg.moe(x, idx, w * 2, gu, dn, codes)
+    pkg.check_status()
+    assert torch.isfinite(out).all()
+    assert torch.equal(out2, out * 2)
+    p = torch.randperm(T, device=DEV, generator=g)
+    out3 = pkg.moe(x[p], idx[p], w[p], gu, dn, codes)
+    assert torch.equal(out3, out[p])
+    perm = pkg.ops.permute_build(idx, E)
+    total = int(perm.poffs[-1])
+    rs = perm.row_slot[:total]
+    assert int((rs >= 0).sum()) == T * k
+    assert torch.equal(rs[perm.slot_row.long()].long(), torch.arange(T * k, device=DEV))
+    assert int(perm.counts.sum()) == T * k

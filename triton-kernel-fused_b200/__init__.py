@@ -1,0 +1,12 @@
+"""B200 (sm_100a) implementation of the MoE block of IsNoobgrammer/triton-kernel-fused:
+sigmoid+bias top-k router, device-side expert permutation, grouped tcgen05 expert GEMMs with
+fused SwiGLU, weighted combine — forward and backward — behind the reference's Python callables.
+Requires the in-tree libb200moe.so (see _lib.build); there is no CPU or library fallback."""
+from ._lib import build, check_status, lib, LIB_PATH, EXPORTED
+from .moe import moe, moe_grouped, moe_per_expert, GROUPED_MIN_TOKENS
+from .router import fused_mlp_router, FusedMLPRouter, router_bias_update
+from .layer import MoELayer
+from . import ops
+
+__all__ = ["moe", "moe_grouped", "moe_per_expert", "GROUPED_MIN_TOKENS", "fused_mlp_router",
+           "FusedMLPRouter", "router_bias_update", "MoELayer", "ops", "build", "lib", "check_status"]

@@ -1,0 +1,646 @@
+// Persistent bf16 GEMM for sm_100a: TMA -> 128B-swizzled shared-memory ring -> tcgen05.mma with the
+// fp32 accumulator in TMEM (double buffered) -> epilogue warps read TMEM and store.
+//
+// One kernel serves every contraction of the MoE block:
+//   schedule  DENSE      D(M,N)            = A * B          (router projections)
+//             GROUPED_M  D(rows of e, N)   = A(rows of e) * B[e]   (expert forward + dgrad)
+//             GROUPED_K  D[e](M,N)         = A(rows of e)^T * B(rows of e)   (expert wgrad, split-K)
+//   operand majors: K-major (reduction index contiguous) or MN-major (row/column index contiguous)
+//   epilogues: bf16 store, SwiGLU (gate|up -> gate_up + inter), GLU backward, fp32 store.
+//
+// Warp roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = TMEM owner + MMA issuer (one
+// lane), warps 2-5 = epilogue (TMEM lane quarter = warp_id % 4).
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200moe {
+
+enum : int { SCHED_DENSE = 0, SCHED_GROUPED_M = 1, SCHED_GROUPED_K = 2 };
+enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_GLU_BWD = 2, EPI_STORE_F32 = 3 };
+
+constexpr int BM = 128;  // tile rows = UMMA M = TMEM lanes
+constexpr int BK = 64;   // k-block: 64 bf16 = one 128-byte swizzle row
+constexpr int kThreads = 192;
+
+struct GemmParams {
+  int sched;
+  int a_mn, b_mn;        // 1 = operand is MN-major
+  int M;                 // DENSE: rows of D; GROUPED_K: rows of D[e] (= MN extent of A)
+  int N;                 // columns of D (SwiGLU: I)
+  int K;                 // reduction length (DENSE, GROUPED_M); total rows (GROUPED_K by chunks)
+  int num_groups;        // experts (GROUPED_M/K) or K-chunks
+  int k_chunk;           // GROUPED_K without poffs: rows per chunk (multiple of 64)
+  const int* tile_expert;  // GROUPED_M: expert of each 128-row tile
+  const int* poffs;        // (num_groups+1) padded row offsets, multiples of 128
+  void* D;
+  long long ldd;
+  long long d_group_stride;  // GROUPED_K: elements between D[e] and D[e+1]
+  void* aux;                 // SwiGLU: inter (rows, I); GLU_BWD: saved gate_up (rows, 2I)
+  int I;
+  int* status;
+};
+
+struct Tile {
+  int m0, n0, g, k0, nkb;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int NSTAGE = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = 2 * BN;  // two accumulators; 128, 256 or 512 (power of two >= 32)
+  static constexpr int BAR_BYTES = (2 * NSTAGE + 4) * 8 + 16;
+  static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ int total_tiles(const GemmParams& p, int TN) {
+  const int nt = (p.N + TN - 1) / TN;
+  if (p.sched == SCHED_DENSE) return ((p.M + BM - 1) / BM) * nt;
+  if (p.sched == SCHED_GROUPED_M) return (p.poffs[p.num_groups] / BM) * nt;
+  return ((p.M + BM - 1) / BM) * nt * p.num_groups;
+}
+
+__device__ __forceinline__ Tile get_tile(const GemmParams& p, int tile, int TN) {
+  Tile t;
+  const int nt = (p.N + TN - 1) / TN;
+  if (p.sched == SCHED_GROUPED_K) {
+    const int mt = (p.M + BM - 1) / BM;
+    const int per = mt * nt;
+    t.g = tile / per;
+    const int r = tile - t.g * per;
+    t.m0 = (r / nt) * BM;
+    t.n0 = (r % nt) * TN;
+    int kb, ke;
+    if (p.poffs != nullptr) {
+      kb = p.poffs[t.g];
+      ke = p.poffs[t.g + 1];
+    } else {
+      kb = t.g * p.k_chunk;
+      ke = min(p.K, kb + p.k_chunk);
+    }
+    t.k0 = kb;
+    t.nkb = (ke - kb + BK - 1) / BK;
+  } else {
+    const int mi = tile / nt;
+    t.m0 = mi * BM;
+    t.n0 = (tile - mi * nt) * TN;
+    t.g = (p.sched == SCHED_GROUPED_M) ? p.tile_expert[mi] : 0;
+    t.k0 = 0;
+    t.nkb = (p.K + BK - 1) / BK;
+  }
+  return t;
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const GemmParams p) {
+  using C = Cfg<BN>;
+  constexpr int TN = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  constexpr int NSTAGE = C::NSTAGE;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NSTAGE * C::STAGE_BYTES);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = smem_u32(bars + NSTAGE);
+  const uint32_t bar_tfull = smem_u32(bars + 2 * NSTAGE);
+  const uint32_t bar_tempty = smem_u32(bars + 2 * NSTAGE + 2);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGE + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total = total_tiles(p, TN);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+        const Tile t = get_tile(p, tile, TN);
+        const int gB = (p.sched == SCHED_GROUPED_M) ? t.g : 0;
+        for (int kb = 0; kb < t.nkb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, ST_WAIT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = bar_full + 8 * s;
+          mbar_arrive_expect_tx(full, C::STAGE_BYTES);
+          const uint32_t sa = smem_u32(smem + s * C::STAGE_BYTES);
+          const uint32_t sb = sa + C::A_BYTES;
+          const int kk = t.k0 + kb * BK;
+          if (!p.a_mn) {
+            tma_load_3d(sa, &tmA, full, kk, t.m0, 0);  // box {64 k, 128 rows}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)  // boxes {64 mn, 64 k-rows}
+              tma_load_3d(sa + j * (64 * BK * 2), &tmA, full, t.m0 + 64 * j, kk, 0);
+          }
+          if (EPI == EPI_SWIGLU) {
+            // gate rows [n0, n0+BN/2) of W[e] then up rows of the same range: dims {H, I, 2E}
+            tma_load_3d(sb, &tmB, full, kk, t.n0, 2 * gB);
+            tma_load_3d(sb + (BN / 2) * BK * 2, &tmB, full, kk, t.n0, 2 * gB + 1);
+          } else if (!p.b_mn) {
+            tma_load_3d(sb, &tmB, full, kk, t.n0, gB);  // box {64 k, BN rows}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sb + j * (64 * BK * 2), &tmB, full, t.n0 + 64 * j, kk, gB);
+          }
+          if (++s == NSTAGE) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(BN, p.a_mn, p.b_mn);
+      // K-major: rows are 128 B apart, 8-row groups 1024 B apart, 16 k-elements = 32 B.
+      // MN-major: 64-wide MN blocks are 64*128 B apart (LBO), 8 k-rows 1024 B apart (SBO),
+      //           16 k-rows = 2048 B.
+      const uint32_t a_lbo = p.a_mn ? 64 * BK * 2 : 0, b_lbo = p.b_mn ? 64 * BK * 2 : 0;
+      const uint32_t a_kstep = p.a_mn ? 2048 : 32, b_kstep = p.b_mn ? 2048 : 32;
+      int s = 0, it = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++it) {
+        const Tile t = get_tile(p, tile, TN);
+        const int buf = it & 1;
+        if (!mbar_wait(bar_tempty + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag, ST_WAIT_MMA_TMEM)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < t.nkb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, ST_WAIT_MMA_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * C::STAGE_BYTES);
+          const uint32_t sb = sa + C::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = umma_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
+            const uint64_t db = umma_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
+            umma_bf16(d_tmem, da, db, idesc, (kb | k) != 0);
+          }
+          umma_commit(bar_empty + 8 * s);  // frees the stage when these MMAs have read it
+          if (++s == NSTAGE) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+        if (!ok) break;
+        if (t.nkb > 0) umma_commit(bar_tfull + 8 * buf);
+        else mbar_arrive(bar_tfull + 8 * buf);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps)
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
+      const Tile t = get_tile(p, tile, TN);
+      const int buf = it & 1;
+      if (!mbar_wait(bar_tfull + 8 * buf, (it >> 1) & 1, abort_flag, ST_WAIT_EPILOGUE)) break;
+      __syncwarp();
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      const long long row = static_cast<long long>(t.m0) + q * 32 + lane;
+      const bool have_acc = t.nkb > 0;
+
+      if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32) {
+        const bool row_ok = (p.sched == SCHED_GROUPED_M) || (row < p.M);
+        const long long base = (p.sched == SCHED_GROUPED_K ? t.g * p.d_group_stride : 0) +
+                               row * p.ldd + t.n0;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (t.n0 + c0 >= p.N) break;
+          uint32_t r[32];
+          if (have_acc) {
+            tmem_ld32(taddr + c0, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          if (row_ok) {
+            if constexpr (EPI == EPI_STORE) {
+              __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + base + c0;
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                if (t.n0 + c0 + v * 8 < p.N) {
+                  uint4 o;
+                  o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                  o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                  o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                  o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                  *reinterpret_cast<uint4*>(d + v * 8) = o;
+                }
+              }
+            } else {
+              float* d = reinterpret_cast<float*>(p.D) + base + c0;
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                if (t.n0 + c0 + v * 4 < p.N) {
+                  uint4 o = make_uint4(r[v * 4 + 0], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+                  *reinterpret_cast<uint4*>(d + v * 4) = o;
+                }
+              }
+            }
+          }
+        }
+      } else if constexpr (EPI == EPI_SWIGLU) {
+        // accumulator columns [0,BN/2) = gate, [BN/2,BN) = up for I-columns [n0, n0+BN/2)
+        const int I = p.I;
+        __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(p.D) + row * (2LL * I);
+        __nv_bfloat16* it_out = reinterpret_cast<__nv_bfloat16*>(p.aux) + row * static_cast<long long>(I);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+          if (t.n0 + c0 >= I) break;
+          uint32_t g[32], u[32];
+          tmem_ld32(taddr + c0, g);
+          tmem_ld32(taddr + BN / 2 + c0, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = t.n0 + c0 + v * 8;
+            if (col < I) {
+              uint32_t og[4], ou[4], oh[4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                og[h] = pack_bf16x2(__uint_as_float(g[v * 8 + 2 * h]), __uint_as_float(g[v * 8 + 2 * h + 1]));
+                ou[h] = pack_bf16x2(__uint_as_float(u[v * 8 + 2 * h]), __uint_as_float(u[v * 8 + 2 * h + 1]));
+                // the activation reads the bf16-rounded gate/up, as the reference's separate
+                // activation kernel does (kernels/sm75/moe.py:163-184)
+                const float2 gf = unpack_bf16x2(og[h]);
+                const float2 uf = unpack_bf16x2(ou[h]);
+                const float s0 = 1.0f / (1.0f + __expf(-gf.x));
+                const float s1 = 1.0f / (1.0f + __expf(-gf.y));
+                oh[h] = pack_bf16x2(gf.x * s0 * uf.x, gf.y * s1 * uf.y);
+              }
+              *reinterpret_cast<uint4*>(gu + col) = make_uint4(og[0], og[1], og[2], og[3]);
+              *reinterpret_cast<uint4*>(gu + I + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+              *reinterpret_cast<uint4*>(it_out + col) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+            }
+          }
+        }
+      } else {  // EPI_GLU_BWD: accumulator = grad_inter columns [n0, n0+BN)
+        const int I = p.I;
+        const __nv_bfloat16* gu = reinterpret_cast<const __nv_bfloat16*>(p.aux) + row * (2LL * I);
+        __nv_bfloat16* ggu = reinterpret_cast<__nv_bfloat16*>(p.D) + row * (2LL * I);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (t.n0 + c0 >= I) break;
+          uint32_t r[32];
+          tmem_ld32(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = t.n0 + c0 + v * 8;
+            if (col < I) {
+              const uint4 gv = *reinterpret_cast<const uint4*>(gu + col);
+              const uint4 uv = *reinterpret_cast<const uint4*>(gu + I + col);
+              const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+              const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
+              uint32_t og[4], ou[4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                const float2 gf = unpack_bf16x2(gw[h]);
+                const float2 uf = unpack_bf16x2(uw[h]);
+                // grad_inter is rounded to bf16 first: the reference materialises it in bf16
+                const float go0 = bf16_round(__uint_as_float(r[v * 8 + 2 * h]));
+                const float go1 = bf16_round(__uint_as_float(r[v * 8 + 2 * h + 1]));
+                const float s0 = 1.0f / (1.0f + __expf(-gf.x));
+                const float s1 = 1.0f / (1.0f + __expf(-gf.y));
+                const float d0 = s0 * (1.0f + gf.x * (1.0f - s0));
+                const float d1 = s1 * (1.0f + gf.y * (1.0f - s1));
+                og[h] = pack_bf16x2(go0 * uf.x * d0, go1 * uf.y * d1);
+                ou[h] = pack_bf16x2(go0 * (gf.x * s0), go1 * (gf.y * s1));
+              }
+              *reinterpret_cast<uint4*>(ggu + col) = make_uint4(og[0], og[1], og[2], og[3]);
+              *reinterpret_cast<uint4*>(ggu + I + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+    }
+  }
+
+  // ------------------------------------------------------------------ tear-down
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_flag);
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// bf16 tensor seen as dims {inner, outer, groups}; strides in elements; 128B swizzle; zero OOB fill.
+static int make_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t outer, uint64_t groups,
+                    uint64_t outer_stride, uint64_t group_stride, uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  B200_CHECK_ARG(fn != nullptr, B200MOE_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  B200_CHECK_ARG(aligned16(base), B200MOE_E_ALIGN, "tensor base %p is not 16-byte aligned", base);
+  B200_CHECK_ARG(outer_stride % 8 == 0 && group_stride % 8 == 0, B200MOE_E_ALIGN,
+                 "row/group strides must be multiples of 8 bf16 elements (got %llu, %llu)",
+                 (unsigned long long)outer_stride, (unsigned long long)group_stride);
+  cuuint64_t dims[3] = {inner, outer, groups};
+  cuuint64_t strides[2] = {outer_stride * 2, group_stride * 2};
+  cuuint32_t box[3] = {box_inner, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200_CHECK_ARG(r == CUDA_SUCCESS, B200MOE_E_CUDA,
+                 "cuTensorMapEncodeTiled failed (%d): dims {%llu,%llu,%llu} box {%u,%u}", (int)r,
+                 (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)groups, box_inner,
+                 box_outer);
+  return 0;
+}
+
+template <int BN, int EPI>
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int max_tiles,
+                  cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    C::SMEM_BYTES);
+  });
+  if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(max dynamic smem)");
+  int grid = num_sms();
+  if (max_tiles > 0 && max_tiles < grid) grid = max_tiles;
+  if (grid < 1) grid = 1;
+  gemm_kernel<BN, EPI><<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Operand description used by the host-side dispatcher.
+struct Operand {
+  const void* ptr;
+  int mn_major;         // 0: (rows, K) row-major;  1: (K, rows) row-major
+  long long rows;       // M (for A) or N (for B)
+  long long k;          // reduction extent visible in this tensor
+  long long ld;         // elements between consecutive rows of the stored matrix
+  long long groups;     // stacked matrices (experts), 1 if none
+  long long group_stride;
+};
+
+static int encode_operand(CUtensorMap* tm, const Operand& o, int tile_rows) {
+  if (!o.mn_major)  // dims {K, rows, groups}, box {64, tile_rows}
+    return make_map(tm, o.ptr, o.k, o.rows, o.groups, o.ld, o.group_stride, BK, tile_rows);
+  // dims {rows(mn), K, groups}, box {64 mn, 64 k}
+  return make_map(tm, o.ptr, o.rows, o.k, o.groups, o.ld, o.group_stride, 64, BK);
+}
+
+static int pick_bn(long long n) {
+  if (n <= 64) return 64;
+  if (n % 256 == 0 || n > 1024) {
+    // prefer the wide tile unless it wastes more than 1/8 of the last tile
+    long long waste256 = ((n + 255) / 256) * 256 - n;
+    if (waste256 * 8 <= n) return 256;
+  }
+  return 128;
+}
+
+template <int EPI>
+static int dispatch_bn(int bn, const Operand& A, const Operand& B, GemmParams& p, int max_tiles,
+                       cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  int rc = encode_operand(&tmA, A, BM);
+  if (rc) return rc;
+  const int b_rows = (EPI == EPI_SWIGLU) ? bn / 2 : bn;
+  rc = encode_operand(&tmB, B, b_rows);
+  if (rc) return rc;
+  switch (bn) {
+    case 256: return launch<256, EPI>(tmA, tmB, p, max_tiles, stream);
+    case 128: return launch<128, EPI>(tmA, tmB, p, max_tiles, stream);
+    default:
+      if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32) return launch<64, EPI>(tmA, tmB, p, max_tiles, stream);
+      set_error("tile width %d not built for this epilogue", bn);
+      return B200MOE_E_UNSUPPORTED;
+  }
+}
+
+static long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
+
+}  // namespace b200moe
+
+using namespace b200moe;
+
+#define CHECK_DIM8(v) \
+  B200_CHECK_ARG((v) > 0 && (v) % 8 == 0, B200MOE_E_BAD_SHAPE, #v " = %lld must be a positive multiple of 8", (long long)(v))
+#define CHECK_I32(v) \
+  B200_CHECK_ARG((v) >= 0 && (v) < (1LL << 31), B200MOE_E_BAD_SHAPE, #v " = %lld does not fit int32", (long long)(v))
+
+extern "C" {
+
+int b200moe_gemm_nt(const void* A, const void* B, void* D, int64_t M, int64_t N, int64_t K, int32_t* status,
+                    b200moe_stream_t stream) {
+  B200_CHECK_ARG(A && B && D, B200MOE_E_NULL, "gemm_nt: null pointer");
+  CHECK_DIM8(N); CHECK_DIM8(K); CHECK_I32(M); CHECK_I32(N); CHECK_I32(K);
+  if (M == 0) return 0;
+  B200_CHECK_ARG(aligned16(D), B200MOE_E_ALIGN, "gemm_nt: D not 16-byte aligned");
+  Operand a{A, 0, M, K, K, 1, M * K};
+  Operand b{B, 0, N, K, K, 1, N * K};
+  GemmParams p{};
+  p.sched = SCHED_DENSE; p.M = (int)M; p.N = (int)N; p.K = (int)K; p.num_groups = 1;
+  p.D = D; p.ldd = N; p.status = status;
+  const int bn = pick_bn(N);
+  return dispatch_bn<EPI_STORE>(bn, a, b, p, (int)(ceil_div(M, BM) * ceil_div(N, bn)), (cudaStream_t)stream);
+}
+
+int b200moe_gemm_nn(const void* A, const void* B, void* D, int64_t M, int64_t N, int64_t K, int32_t* status,
+                    b200moe_stream_t stream) {
+  B200_CHECK_ARG(A && B && D, B200MOE_E_NULL, "gemm_nn: null pointer");
+  CHECK_DIM8(N); CHECK_DIM8(K); CHECK_I32(M); CHECK_I32(N); CHECK_I32(K);
+  if (M == 0) return 0;
+  B200_CHECK_ARG(aligned16(D), B200MOE_E_ALIGN, "gemm_nn: D not 16-byte aligned");
+  Operand a{A, 0, M, K, K, 1, M * K};
+  Operand b{B, 1, N, K, N, 1, N * K};   // stored (K, N): MN-major
+  GemmParams p{};
+  p.sched = SCHED_DENSE; p.b_mn = 1; p.M = (int)M; p.N = (int)N; p.K = (int)K; p.num_groups = 1;
+  p.D = D; p.ldd = N; p.status = status;
+  const int bn = pick_bn(N);
+  return dispatch_bn<EPI_STORE>(bn, a, b, p, (int)(ceil_div(M, BM) * ceil_div(N, bn)), (cudaStream_t)stream);
+}
+
+int b200moe_gemm_tn_splitk(const void* A, const void* B, float* P, int64_t M, int64_t N, int64_t K,
+                           int64_t k_chunk, int32_t* status, b200moe_stream_t stream) {
+  B200_CHECK_ARG(A && B && P, B200MOE_E_NULL, "gemm_tn_splitk: null pointer");
+  CHECK_DIM8(M); CHECK_DIM8(N); CHECK_I32(M); CHECK_I32(N); CHECK_I32(K);
+  B200_CHECK_ARG(k_chunk > 0 && k_chunk % 64 == 0, B200MOE_E_BAD_SHAPE,
+                 "gemm_tn_splitk: k_chunk = %lld must be a positive multiple of 64", (long long)k_chunk);
+  B200_CHECK_ARG(K > 0, B200MOE_E_BAD_SHAPE, "gemm_tn_splitk: K must be positive");
+  B200_CHECK_ARG(aligned16(P), B200MOE_E_ALIGN, "gemm_tn_splitk: P not 16-byte aligned");
+  const long long slices = ceil_div(K, k_chunk);
+  Operand a{A, 1, M, K, M, 1, M * K};   // stored (K, M)
+  Operand b{B, 1, N, K, N, 1, N * K};   // stored (K, N)
+  GemmParams p{};
+  p.sched = SCHED_GROUPED_K; p.a_mn = 1; p.b_mn = 1; p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.num_groups = (int)slices; p.k_chunk = (int)k_chunk; p.poffs = nullptr;
+  p.D = P; p.ldd = N; p.d_group_stride = M * N; p.status = status;
+  const int bn = pick_bn(N);
+  return dispatch_bn<EPI_STORE_F32>(bn, a, b, p, (int)(slices * ceil_div(M, BM) * ceil_div(N, bn)),
+                                    (cudaStream_t)stream);
+}
+
+static int check_grouped(const char* who, const void* a, const void* b, const void* c, const int32_t* tile_expert,
+                         const int32_t* poffs, int64_t rows_cap, int E, int64_t H, int64_t I) {
+  B200_CHECK_ARG(a && b && c && poffs, B200MOE_E_NULL, "%s: null pointer", who);
+  (void)tile_expert;
+  B200_CHECK_ARG(E >= 1 && E <= 65535, B200MOE_E_BAD_SHAPE, "%s: E = %d out of range", who, E);
+  B200_CHECK_ARG(rows_cap > 0 && rows_cap % BM == 0 && rows_cap < (1LL << 31), B200MOE_E_BAD_SHAPE,
+                 "%s: rows_cap = %lld must be a positive multiple of %d", who, (long long)rows_cap, BM);
+  B200_CHECK_ARG(H > 0 && H % 8 == 0 && I > 0 && I % 8 == 0, B200MOE_E_BAD_SHAPE,
+                 "%s: H = %lld and I = %lld must be positive multiples of 8", who, (long long)H, (long long)I);
+  B200_CHECK_ARG(2 * E * I < (1LL << 31) && E * H < (1LL << 31), B200MOE_E_BAD_SHAPE, "%s: weight stack too tall", who);
+  return 0;
+}
+
+int b200moe_expert_gate_up_swiglu(const void* x_s, const void* gate_up_proj, const int32_t* tile_expert,
+                                  const int32_t* poffs, int64_t rows_cap, int E, int64_t H, int64_t I,
+                                  void* gate_up, void* inter, int32_t* status, b200moe_stream_t stream) {
+  int rc = check_grouped("expert_gate_up_swiglu", x_s, gate_up_proj, gate_up, tile_expert, poffs, rows_cap, E, H, I);
+  if (rc) return rc;
+  B200_CHECK_ARG(inter && tile_expert, B200MOE_E_NULL, "expert_gate_up_swiglu: null pointer");
+  B200_CHECK_ARG(aligned16(gate_up) && aligned16(inter), B200MOE_E_ALIGN, "expert_gate_up_swiglu: outputs not aligned");
+  Operand a{x_s, 0, rows_cap, H, H, 1, rows_cap * H};
+  // W_gu (E, 2I, H) seen as dims {H, I, 2E}: group 2e = gate rows of expert e, 2e+1 = up rows
+  Operand b{gate_up_proj, 0, I, H, H, 2LL * E, I * H};
+  GemmParams p{};
+  p.sched = SCHED_GROUPED_M; p.N = (int)I; p.K = (int)H; p.num_groups = E;
+  p.tile_expert = tile_expert; p.poffs = poffs; p.D = gate_up; p.aux = inter; p.I = (int)I; p.status = status;
+  const int bn = (I >= 128) ? 256 : 128;   // tile covers bn/2 intermediate columns
+  return dispatch_bn<EPI_SWIGLU>(bn, a, b, p, 0, (cudaStream_t)stream);
+}
+
+int b200moe_expert_down(const void* inter, const void* down_proj, const int32_t* tile_expert, const int32_t* poffs,
+                        int64_t rows_cap, int E, int64_t H, int64_t I, void* eo, int32_t* status,
+                        b200moe_stream_t stream) {
+  int rc = check_grouped("expert_down", inter, down_proj, eo, tile_expert, poffs, rows_cap, E, H, I);
+  if (rc) return rc;
+  B200_CHECK_ARG(tile_expert, B200MOE_E_NULL, "expert_down: null pointer");
+  B200_CHECK_ARG(aligned16(eo), B200MOE_E_ALIGN, "expert_down: output not aligned");
+  Operand a{inter, 0, rows_cap, I, I, 1, rows_cap * I};
+  Operand b{down_proj, 0, H, I, I, E, H * I};   // W_d (E, H, I): rows = H (output cols), K = I
+  GemmParams p{};
+  p.sched = SCHED_GROUPED_M; p.N = (int)H; p.K = (int)I; p.num_groups = E;
+  p.tile_expert = tile_expert; p.poffs = poffs; p.D = eo; p.ldd = H; p.status = status;
+  return dispatch_bn<EPI_STORE>(pick_bn(H) == 64 ? 128 : pick_bn(H), a, b, p, 0, (cudaStream_t)stream);
+}
+
+int b200moe_expert_down_dgrad_glu(const void* grad_eo, const void* down_proj, const void* gate_up,
+                                  const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E,
+                                  int64_t H, int64_t I, void* grad_gate_up, int32_t* status,
+                                  b200moe_stream_t stream) {
+  int rc = check_grouped("expert_down_dgrad_glu", grad_eo, down_proj, grad_gate_up, tile_expert, poffs, rows_cap, E, H, I);
+  if (rc) return rc;
+  B200_CHECK_ARG(gate_up && tile_expert, B200MOE_E_NULL, "expert_down_dgrad_glu: null pointer");
+  B200_CHECK_ARG(aligned16(grad_gate_up) && aligned16(gate_up), B200MOE_E_ALIGN, "expert_down_dgrad_glu: not aligned");
+  Operand a{grad_eo, 0, rows_cap, H, H, 1, rows_cap * H};
+  Operand b{down_proj, 1, I, H, I, E, H * I};   // W_d[e] stored (K=H, N=I): MN-major
+  GemmParams p{};
+  p.sched = SCHED_GROUPED_M; p.b_mn = 1; p.N = (int)I; p.K = (int)H; p.num_groups = E;
+  p.tile_expert = tile_expert; p.poffs = poffs; p.D = grad_gate_up; p.aux = const_cast<void*>(gate_up);
+  p.I = (int)I; p.status = status;
+  const int bn = pick_bn(I) == 64 ? 128 : pick_bn(I);
+  return dispatch_bn<EPI_GLU_BWD>(bn, a, b, p, 0, (cudaStream_t)stream);
+}
+
+int b200moe_expert_gate_up_dgrad(const void* grad_gate_up, const void* gate_up_proj, const int32_t* tile_expert,
+                                 const int32_t* poffs, int64_t rows_cap, int E, int64_t H, int64_t I,
+                                 void* grad_x_s, int32_t* status, b200moe_stream_t stream) {
+  int rc = check_grouped("expert_gate_up_dgrad", grad_gate_up, gate_up_proj, grad_x_s, tile_expert, poffs, rows_cap, E, H, I);
+  if (rc) return rc;
+  B200_CHECK_ARG(tile_expert, B200MOE_E_NULL, "expert_gate_up_dgrad: null pointer");
+  B200_CHECK_ARG(aligned16(grad_x_s), B200MOE_E_ALIGN, "expert_gate_up_dgrad: output not aligned");
+  Operand a{grad_gate_up, 0, rows_cap, 2 * I, 2 * I, 1, rows_cap * 2 * I};
+  Operand b{gate_up_proj, 1, H, 2 * I, H, E, 2 * I * H};   // W_gu[e] stored (K=2I, N=H): MN-major
+  GemmParams p{};
+  p.sched = SCHED_GROUPED_M; p.b_mn = 1; p.N = (int)H; p.K = (int)(2 * I); p.num_groups = E;
+  p.tile_expert = tile_expert; p.poffs = poffs; p.D = grad_x_s; p.ldd = H; p.status = status;
+  return dispatch_bn<EPI_STORE>(pick_bn(H) == 64 ? 128 : pick_bn(H), a, b, p, 0, (cudaStream_t)stream);
+}
+
+int b200moe_expert_wgrad(const void* A, const void* B, const int32_t* poffs, int64_t rows_cap, int E, int64_t Na,
+                         int64_t Nb, void* out, int32_t* status, b200moe_stream_t stream) {
+  B200_CHECK_ARG(A && B && poffs && out, B200MOE_E_NULL, "expert_wgrad: null pointer");
+  B200_CHECK_ARG(E >= 1, B200MOE_E_BAD_SHAPE, "expert_wgrad: E = %d", E);
+  B200_CHECK_ARG(rows_cap > 0 && rows_cap % BM == 0 && rows_cap < (1LL << 31), B200MOE_E_BAD_SHAPE,
+                 "expert_wgrad: rows_cap = %lld must be a positive multiple of %d", (long long)rows_cap, BM);
+  CHECK_DIM8(Na); CHECK_DIM8(Nb); CHECK_I32(Na); CHECK_I32(Nb);
+  B200_CHECK_ARG(aligned16(out), B200MOE_E_ALIGN, "expert_wgrad: output not aligned");
+  Operand a{A, 1, Na, rows_cap, Na, 1, rows_cap * Na};
+  Operand b{B, 1, Nb, rows_cap, Nb, 1, rows_cap * Nb};
+  GemmParams p{};
+  p.sched = SCHED_GROUPED_K; p.a_mn = 1; p.b_mn = 1; p.M = (int)Na; p.N = (int)Nb; p.K = (int)rows_cap;
+  p.num_groups = E; p.poffs = poffs; p.D = out; p.ldd = Nb; p.d_group_stride = Na * Nb; p.status = status;
+  const int bn = pick_bn(Nb);
+  return dispatch_bn<EPI_STORE>(bn, a, b, p, (int)std::min<long long>(1 << 30, E * ceil_div(Na, BM) * ceil_div(Nb, bn)),
+                                (cudaStream_t)stream);
+}
+
+}  // extern "C"

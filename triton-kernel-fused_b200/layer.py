@@ -1,0 +1,51 @@
+"""nn.Module wiring of the block: sigmoid+bias router -> experts, shaped like the reference's
+example module (examples/moe_usage.py:63-77) with the selection-bias buffer of
+.autoresearch/train_grok_moe.py:66-90."""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from .moe import moe
+from .router import fused_mlp_router, router_bias_update
+
+__all__ = ["MoELayer"]
+
+
+class MoELayer(nn.Module):
+    def __init__(self, H, I, E, top_k=2, norm_topk_prob=True, routed_scaling_factor=1.0, init_std=0.02):
+        super().__init__()
+        self.gate = nn.Linear(H, E, bias=False)
+        self.gate_up_proj = nn.Parameter(torch.randn(E, 2 * I, H) * init_std)
+        self.down_proj = nn.Parameter(torch.randn(E, H, I) * init_std)
+        with torch.no_grad():
+            self.gate.weight.normal_(0.0, init_std)
+        self.register_buffer("act_codes", torch.zeros(E, dtype=torch.int32))
+        self.register_buffer("bias", torch.zeros(E, dtype=torch.float32))
+        self.top_k = top_k
+        self.num_experts = E
+        self.norm_topk_prob = norm_topk_prob
+        self.routed_scaling_factor = routed_scaling_factor
+        self.last_counts = None
+
+    def _apply(self, fn, *a, **kw):
+        super()._apply(fn, *a, **kw)
+        self.bias.data = self.bias.data.float()        # the selection bias stays fp32
+        self.act_codes._code_max_cache = 0
+        return self
+
+    def forward(self, x):                               # x: (B,S,H) or (N,H)
+        shape = x.shape
+        flat = x.reshape(-1, shape[-1])
+        idx, w, counts = fused_mlp_router(flat, self.gate.weight, self.bias, self.top_k, self.num_experts,
+                                          self.norm_topk_prob, self.routed_scaling_factor, return_counts=True)
+        self.last_counts = counts
+        out = moe(flat, idx, w, self.gate_up_proj, self.down_proj, self.act_codes)
+        return out.reshape(shape)
+
+    @torch.no_grad()
+    def update_bias(self, u, counts=None):
+        """Load-balance step: pass the all-reduced counts when running on several ranks."""
+        c = self.last_counts if counts is None else counts
+        if c is not None:
+            router_bias_update(self.bias, c, u)

@@ -1,0 +1,254 @@
+"""Thin Python callers of the C ABI, one per entry point; they allocate outputs with torch and
+queue the kernels on the current CUDA stream.  No computation happens in Python."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib as L
+
+LOGITS_BF16, LOGITS_F32, SCORES_F32 = 0, 1, 2
+
+# Optional observer used by the benchmark: hook(name, kernel_launches, start_event, end_event) is
+# called for every op below with CUDA events recorded on the launching stream around it.
+_hook = None
+
+
+def set_hook(hook):
+    global _hook
+    _hook = hook
+
+
+def _op(name, launches=1):
+    def deco(fn):
+        def wrapped(*a, **kw):
+            if _hook is None:
+                return fn(*a, **kw)
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn(*a, **kw)
+            e1.record()
+            _hook(name, launches, e0, e1)
+            return r
+        wrapped.__name__ = fn.__name__
+        wrapped.__doc__ = fn.__doc__
+        return wrapped
+    return deco
+
+
+def _kind(t: torch.Tensor, scores: bool) -> int:
+    if scores:
+        L.require(t.dtype == torch.float32, "scores must be float32")
+        return SCORES_F32
+    if t.dtype == torch.bfloat16:
+        return LOGITS_BF16
+    L.require(t.dtype == torch.float32, f"logits must be bfloat16 or float32, got {t.dtype}")
+    return LOGITS_F32
+
+
+@_op("router_topk_fwd", 1)
+def router_topk_fwd(logits, bias, top_k, norm_topk=True, scale=1.0, want_counts=True, scores=False):
+    """(N,E) logits (or fp32 scores) -> idx int64 (N,k), w fp32 (N,k), counts int32 (E,) or None."""
+    L.require(logits.is_cuda and logits.dim() == 2 and logits.is_contiguous(), "logits must be a contiguous CUDA (N,E) tensor")
+    N, E = logits.shape
+    if bias is not None:
+        L.require(bias.is_cuda and bias.dtype == torch.float32 and bias.numel() == E and bias.is_contiguous(),
+                  "bias must be a contiguous float32 CUDA tensor of E elements")
+    dev = logits.device
+    idx = torch.empty(N, top_k, dtype=torch.int64, device=dev)
+    w = torch.empty(N, top_k, dtype=torch.float32, device=dev)
+    counts = torch.empty(E, dtype=torch.int32, device=dev) if want_counts else None
+    L.check(L.lib().b200moe_router_topk_fwd(L.ptr(logits), _kind(logits, scores), L.ptr(bias), N, E, int(top_k),
+                                            int(bool(norm_topk)), float(scale), L.ptr(idx), L.ptr(w),
+                                            L.ptr(counts), L.stream_of(logits)))
+    return idx, w, counts
+
+
+@_op("router_topk_bwd", 1)
+def router_topk_bwd(logits, idx, grad_w, norm_topk=True, scale=1.0):
+    N, E = logits.shape
+    k = idx.shape[1]
+    gw = grad_w.contiguous().float()
+    gl = torch.empty(N, E, dtype=torch.bfloat16, device=logits.device)
+    L.check(L.lib().b200moe_router_topk_bwd(L.ptr(logits), _kind(logits, False), L.ptr(idx), L.ptr(gw), N, E, k,
+                                            int(bool(norm_topk)), float(scale), L.ptr(gl), L.stream_of(logits)))
+    return gl
+
+
+@_op("router_bias_update", 1)
+def router_bias_update(bias, counts, u):
+    L.require(bias.is_cuda and bias.dtype == torch.float32 and bias.is_contiguous(), "bias must be contiguous float32 CUDA")
+    L.require(counts.is_cuda and counts.dtype == torch.int32 and counts.is_contiguous(), "counts must be contiguous int32 CUDA")
+    L.check(L.lib().b200moe_router_bias_update(L.ptr(bias), L.ptr(counts), bias.numel(), float(u), L.stream_of(bias)))
+
+
+@_op("gemm_nt", 1)
+def gemm_nt(a, b):
+    """a (M,K) @ b (N,K)^T -> (M,N) bf16."""
+    L.require_cuda_bf16("a", a); L.require_cuda_bf16("b", b)
+    L.require(a.is_contiguous() and b.is_contiguous() and a.shape[1] == b.shape[1], "gemm_nt: need contiguous (M,K),(N,K)")
+    M, K = a.shape
+    N = b.shape[0]
+    d = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    L.check(L.lib().b200moe_gemm_nt(L.ptr(a), L.ptr(b), L.ptr(d), M, N, K, L.ptr(L.status_word(a.device)), L.stream_of(a)))
+    return d
+
+
+@_op("gemm_nn", 1)
+def gemm_nn(a, b):
+    """a (M,K) @ b (K,N) -> (M,N) bf16."""
+    L.require_cuda_bf16("a", a); L.require_cuda_bf16("b", b)
+    L.require(a.is_contiguous() and b.is_contiguous() and a.shape[1] == b.shape[0], "gemm_nn: need contiguous (M,K),(K,N)")
+    M, K = a.shape
+    N = b.shape[1]
+    d = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    L.check(L.lib().b200moe_gemm_nn(L.ptr(a), L.ptr(b), L.ptr(d), M, N, K, L.ptr(L.status_word(a.device)), L.stream_of(a)))
+    return d
+
+
+@_op("gemm_tn", 2)
+def gemm_tn(a, b, target_ctas=296):
+    """a (K,M)^T @ b (K,N) -> (M,N) bf16 through fp32 split-K slices."""
+    L.require_cuda_bf16("a", a); L.require_cuda_bf16("b", b)
+    L.require(a.is_contiguous() and b.is_contiguous() and a.shape[0] == b.shape[0], "gemm_tn: need contiguous (K,M),(K,N)")
+    K, M = a.shape
+    N = b.shape[1]
+    tiles = ((M + 127) // 128) * ((N + 255) // 256)
+    slices = max(1, min(target_ctas // max(tiles, 1), (K + 63) // 64))
+    k_chunk = (((K + slices - 1) // slices) + 63) // 64 * 64
+    slices = (K + k_chunk - 1) // k_chunk
+    part = torch.empty(slices, M, N, dtype=torch.float32, device=a.device)
+    d = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    L.check(L.lib().b200moe_gemm_tn_splitk(L.ptr(a), L.ptr(b), L.ptr(part), M, N, K, k_chunk,
+                                           L.ptr(L.status_word(a.device)), L.stream_of(a)))
+    L.check(L.lib().b200moe_splitk_reduce(L.ptr(part), slices, M * N, L.ptr(d), L.stream_of(a)))
+    return d
+
+
+@dataclass
+class Permutation:
+    """Device tables of one routing decision (see include/b200moe.h, b200moe_permute_build)."""
+    T: int
+    k: int
+    E: int
+    cap: int                  # rows of every padded buffer
+    counts: torch.Tensor      # (E,) int32
+    offs: torch.Tensor        # (E+1,) int32 compact offsets
+    poffs: torch.Tensor       # (E+1,) int32 padded offsets
+    slot_row: torch.Tensor    # (T*k,) int32
+    row_slot: torch.Tensor    # (cap,) int32, valid below poffs[E]
+    tile_expert: torch.Tensor # (cap/128,) int32
+    order: torch.Tensor | None
+
+    @property
+    def total_rows(self):     # device scalar view
+        return self.poffs[self.E:]
+
+
+@_op("permute_build", 3)
+def permute_build(idx, E, want_order=False) -> Permutation:
+    L.require(idx.is_cuda and idx.dtype == torch.int64 and idx.dim() == 2, "top_k_indices must be a CUDA int64 (N,k) tensor")
+    idx = idx.contiguous()
+    T, k = idx.shape
+    dev = idx.device
+    M = T * k
+    cap = L.padded_rows_cap(M, E)
+    i32 = dict(dtype=torch.int32, device=dev)
+    counts = torch.empty(E, **i32)
+    offs = torch.empty(E + 1, **i32)
+    poffs = torch.empty(E + 1, **i32)
+    slot_row = torch.empty(M, **i32)
+    row_slot = torch.empty(cap, **i32)
+    tile_expert = torch.empty(cap // 128, **i32)
+    order = torch.empty(M, dtype=torch.int64, device=dev) if want_order else None
+    ws_bytes = int(L.lib().b200moe_permute_ws_bytes(M, E))
+    ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
+    L.check(L.lib().b200moe_permute_build(L.ptr(idx), T, k, E, L.ptr(counts), L.ptr(offs), L.ptr(poffs),
+                                          L.ptr(slot_row), L.ptr(row_slot), L.ptr(tile_expert), L.ptr(order),
+                                          L.ptr(ws), ws_bytes, L.ptr(L.status_word(dev)), L.stream_of(idx)))
+    return Permutation(T, k, E, cap, counts, offs, poffs, slot_row, row_slot, tile_expert, order)
+
+
+@_op("gather_rows", 1)
+def gather_rows(x, perm: Permutation):
+    L.require_cuda_bf16("hidden", x)
+    H = x.shape[1]
+    x_s = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=x.device)
+    L.check(L.lib().b200moe_gather_rows(L.ptr(x), L.ptr(perm.row_slot), L.ptr(perm.total_rows), perm.k, H, perm.cap,
+                                        L.ptr(x_s), L.stream_of(x)))
+    return x_s
+
+
+@_op("expert_gate_up_swiglu", 1)
+def expert_gate_up_swiglu(x_s, gate_up_proj, perm: Permutation):
+    E, twoI, H = gate_up_proj.shape
+    I = twoI // 2
+    gate_up = torch.empty(perm.cap, twoI, dtype=torch.bfloat16, device=x_s.device)
+    inter = torch.empty(perm.cap, I, dtype=torch.bfloat16, device=x_s.device)
+    L.check(L.lib().b200moe_expert_gate_up_swiglu(L.ptr(x_s), L.ptr(gate_up_proj), L.ptr(perm.tile_expert),
+                                                  L.ptr(perm.poffs), perm.cap, E, H, I, L.ptr(gate_up), L.ptr(inter),
+                                                  L.ptr(L.status_word(x_s.device)), L.stream_of(x_s)))
+    return gate_up, inter
+
+
+@_op("expert_down", 1)
+def expert_down(inter, down_proj, perm: Permutation):
+    E, H, I = down_proj.shape
+    eo = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=inter.device)
+    L.check(L.lib().b200moe_expert_down(L.ptr(inter), L.ptr(down_proj), L.ptr(perm.tile_expert), L.ptr(perm.poffs),
+                                        perm.cap, E, H, I, L.ptr(eo), L.ptr(L.status_word(inter.device)),
+                                        L.stream_of(inter)))
+    return eo
+
+
+@_op("expert_down_dgrad_glu", 1)
+def expert_down_dgrad_glu(grad_eo, down_proj, gate_up, perm: Permutation):
+    E, H, I = down_proj.shape
+    ggu = torch.empty(perm.cap, 2 * I, dtype=torch.bfloat16, device=grad_eo.device)
+    L.check(L.lib().b200moe_expert_down_dgrad_glu(L.ptr(grad_eo), L.ptr(down_proj), L.ptr(gate_up),
+                                                  L.ptr(perm.tile_expert), L.ptr(perm.poffs), perm.cap, E, H, I,
+                                                  L.ptr(ggu), L.ptr(L.status_word(grad_eo.device)),
+                                                  L.stream_of(grad_eo)))
+    return ggu
+
+
+@_op("expert_gate_up_dgrad", 1)
+def expert_gate_up_dgrad(grad_gate_up, gate_up_proj, perm: Permutation):
+    E, twoI, H = gate_up_proj.shape
+    gx = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=grad_gate_up.device)
+    L.check(L.lib().b200moe_expert_gate_up_dgrad(L.ptr(grad_gate_up), L.ptr(gate_up_proj), L.ptr(perm.tile_expert),
+                                                 L.ptr(perm.poffs), perm.cap, E, H, twoI // 2, L.ptr(gx),
+                                                 L.ptr(L.status_word(gx.device)), L.stream_of(gx)))
+    return gx
+
+
+@_op("expert_wgrad", 1)
+def expert_wgrad(a, b, perm: Permutation):
+    """out[e] (Na,Nb) = a[rows of e]^T @ b[rows of e]; zero for experts without rows."""
+    Na, Nb = a.shape[1], b.shape[1]
+    out = torch.empty(perm.E, Na, Nb, dtype=torch.bfloat16, device=a.device)
+    L.check(L.lib().b200moe_expert_wgrad(L.ptr(a), L.ptr(b), L.ptr(perm.poffs), perm.cap, perm.E, Na, Nb, L.ptr(out),
+                                         L.ptr(L.status_word(a.device)), L.stream_of(a)))
+    return out
+
+
+@_op("combine", 1)
+def combine(rows, w, perm: Permutation):
+    H = rows.shape[1]
+    out = torch.empty(perm.T, H, dtype=torch.bfloat16, device=rows.device)
+    L.check(L.lib().b200moe_combine(L.ptr(rows), L.ptr(w), L.ptr(perm.slot_row), perm.T, perm.k, H, L.ptr(out),
+                                    L.stream_of(rows)))
+    return out
+
+
+@_op("combine_bwd", 1)
+def combine_bwd(grad_out, eo, w, perm: Permutation):
+    H = eo.shape[1]
+    grad_eo = torch.empty_like(eo)
+    grad_w = torch.empty(perm.T, perm.k, dtype=torch.float32, device=eo.device)
+    L.check(L.lib().b200moe_combine_bwd(L.ptr(grad_out), L.ptr(eo), L.ptr(w), L.ptr(perm.row_slot),
+                                        L.ptr(perm.total_rows), perm.k, H, perm.cap, L.ptr(grad_eo), L.ptr(grad_w),
+                                        L.stream_of(eo)))
+    return grad_eo, grad_w

@@ -1,0 +1,72 @@
+"""Sigmoid-gate linear router behind the reference's callables (kernels/sm75/router.py).
+
+`fused_mlp_router` (:277-289), `FusedMLPRouter` (:221-260) and `router_bias_update` (:292-301) keep
+their signatures.  Logits are a tcgen05 GEMM (fp32 accumulate, stored in x's dtype as the reference
+does), followed by the warp-level top-k epilogue kernel; backward is the epilogue Jacobian kernel
+plus two tcgen05 GEMMs (dX, and dW as a split-K reduction over the tokens).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib as L
+from . import ops
+
+__all__ = ["fused_mlp_router", "FusedMLPRouter", "router_bias_update"]
+
+
+class FusedMLPRouter(torch.autograd.Function):
+    """Returns (idx (N,k) int64, weights (N,k) fp32 final, counts (E,) int32); only `weights` is
+    differentiable (kernels/sm75/router.py:229-242)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, top_k, num_experts, norm_topk=True, scale=1.0):
+        if torch.is_autocast_enabled("cuda"):
+            dt = torch.get_autocast_dtype("cuda")
+            x, weight = x.to(dt), weight.to(dt)
+        L.require_cuda_bf16("x", x)
+        L.require_cuda_bf16("gate_weight", weight)
+        L.require(weight.dim() == 2 and weight.shape[1] == x.shape[-1], "gate_weight must be (E,H)")
+        L.require(num_experts is None or int(num_experts) == weight.shape[0], "num_experts must equal gate_weight.shape[0]")
+        xf = x.reshape(-1, x.shape[-1]).contiguous()
+        weight = weight.contiguous()
+        logits = ops.gemm_nt(xf, weight)
+        bias32 = None
+        if bias is not None:
+            bias32 = bias.detach().float().contiguous()
+        idx, w, counts = ops.router_topk_fwd(logits, bias32, top_k, norm_topk and top_k > 1, scale)
+        ctx.xshape = x.shape
+        ctx.save_for_backward(xf, weight, logits, idx)
+        ctx.norm, ctx.scale = bool(norm_topk and top_k > 1), float(scale)
+        ctx.mark_non_differentiable(idx, counts)
+        return idx, w, counts
+
+    @staticmethod
+    def backward(ctx, grad_idx, grad_weights, grad_counts):
+        xf, weight, logits, idx = ctx.saved_tensors
+        gl = ops.router_topk_bwd(logits, idx, grad_weights, ctx.norm, ctx.scale)
+        grad_x = ops.gemm_nn(gl, weight).view(ctx.xshape) if ctx.needs_input_grad[0] else None
+        grad_w = ops.gemm_tn(gl, xf) if ctx.needs_input_grad[1] else None
+        return grad_x, grad_w, None, None, None, None, None
+
+
+def fused_mlp_router(x, gate_weight, bias, top_k, num_experts, norm_topk_prob=True,
+                     routed_scaling_factor=1.0, return_counts=False):
+    """x (B,S,H) or (N,H), gate_weight (E,H), bias (E,) fp32 or None -> (idx, weights[, counts]);
+    (B,S,k) shapes for 3-D x (kernels/sm75/router.py:277-289)."""
+    idx, w, counts = FusedMLPRouter.apply(x, gate_weight, bias, top_k, num_experts, norm_topk_prob,
+                                          routed_scaling_factor)
+    if x.ndim == 3:
+        B, S, _ = x.shape
+        idx = idx.view(B, S, top_k)
+        w = w.view(B, S, top_k)
+    return (idx, w, counts) if return_counts else (idx, w)
+
+
+@torch.no_grad()
+def router_bias_update(bias, counts, u):
+    """b += u*sign(mean_load - load), in place; `counts` must already be the global load (the caller
+    all-reduces it across ranks first); no-op when u <= 0 (kernels/sm75/router.py:292-301)."""
+    if u <= 0:
+        return
+    ops.router_bias_update(bias, counts.to(torch.int32).contiguous(), u)
