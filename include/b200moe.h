@@ -94,11 +94,12 @@ size_t b200moe_permute_ws_bytes(int64_t M, int E);
  * Outputs: counts (E), offs (E+1) compact end-exclusive scan, poffs (E+1) padded scan,
  * slot_row (T*k) padded row of slot t*k+j, row_slot (cap) slot of each padded row or -1 (only rows
  * below poffs[E] are written), tile_expert (cap/128) expert of each row tile,
- * order (T*k, nullable) = the stable argsort of idx.flatten(). ws: scratch, ws_bytes from above. */
+ * order (T*k, nullable) = the stable argsort of idx.flatten() (compact row -> slot),
+ * slot_pos (T*k, nullable) = its inverse (slot -> compact row). ws: scratch, ws_bytes from above. */
 int b200moe_permute_build(const int64_t* idx, int64_t T, int k, int E, int32_t* counts,
                           int32_t* offs, int32_t* poffs, int32_t* slot_row, int32_t* row_slot,
-                          int32_t* tile_expert, int64_t* order, void* ws, size_t ws_bytes,
-                          int32_t* status, b200moe_stream_t stream);
+                          int32_t* tile_expert, int32_t* order, int32_t* slot_pos, void* ws,
+                          size_t ws_bytes, int32_t* status, b200moe_stream_t stream);
 
 /* Replaces hidden.index_select(0, st) (kernels/sm75/moe.py:744, :589): x_s[r] = x[row_slot[r]/k],
  * zero rows where row_slot[r] < 0.  Only rows below *total_rows (device) are written. */

@@ -31,7 +31,10 @@ def test_tables_bit_exact(pkg, T, E, k, skew, cap):
     assert torch.equal(perm.counts.cpu(), tb["counts"])
     assert torch.equal(perm.offs.cpu(), tb["offs"])
     assert torch.equal(perm.poffs.cpu(), tb["poffs"])
-    assert torch.equal(perm.order.cpu(), tb["order"])            # == torch.sort(stable=True)
+    assert torch.equal(perm.order.cpu().long(), tb["order"])     # == torch.sort(stable=True)
+    inv = torch.empty_like(tb["order"])
+    inv[tb["order"]] = torch.arange(tb["order"].numel())
+    assert torch.equal(perm.slot_pos.cpu().long(), inv)
     assert torch.equal(perm.slot_row.cpu(), tb["slot_row"])
     assert torch.equal(perm.row_slot.cpu()[:total], tb["row_slot"])
     assert torch.equal(perm.tile_expert.cpu()[: total // 128], tb["tile_expert"])

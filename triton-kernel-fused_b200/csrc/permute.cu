@@ -99,7 +99,7 @@ permute_scan_kernel(int* __restrict__ chunk_hist, long long nchunks, int E, int*
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 permute_rank_kernel(const long long* __restrict__ idx, long long M, int E, const int* __restrict__ chunk_hist,
                     const int* __restrict__ offs, const int* __restrict__ poffs, int* __restrict__ slot_row,
-                    int* __restrict__ row_slot, long long* __restrict__ order) {
+                    int* __restrict__ row_slot, int* __restrict__ order, int* __restrict__ slot_pos) {
   extern __shared__ int sh[];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -127,7 +127,8 @@ permute_rank_kernel(const long long* __restrict__ idx, long long M, int E, const
       const int prow = poffs[e] + rank;
       slot_row[s] = prow;
       row_slot[prow] = static_cast<int>(s);
-      if (order != nullptr) order[offs[e] + rank] = s;
+      if (order != nullptr) order[offs[e] + rank] = static_cast<int>(s);
+      if (slot_pos != nullptr) slot_pos[s] = offs[e] + rank;
     }
   }
 }
@@ -168,7 +169,8 @@ size_t b200moe_permute_ws_bytes(int64_t M, int E) {
 
 int b200moe_permute_build(const int64_t* idx, int64_t T, int k, int E, int32_t* counts, int32_t* offs,
                           int32_t* poffs, int32_t* slot_row, int32_t* row_slot, int32_t* tile_expert,
-                          int64_t* order, void* ws, size_t ws_bytes, int32_t* status, b200moe_stream_t stream) {
+                          int32_t* order, int32_t* slot_pos, void* ws, size_t ws_bytes, int32_t* status,
+                          b200moe_stream_t stream) {
   B200_CHECK_ARG(idx && counts && offs && poffs && slot_row && row_slot && tile_expert && ws && status,
                  B200MOE_E_NULL, "permute_build: null pointer");
   B200_CHECK_ARG(E >= 1 && E <= B200MOE_MAX_EXPERTS, B200MOE_E_UNSUPPORTED,
@@ -194,7 +196,7 @@ int b200moe_permute_build(const int64_t* idx, int64_t T, int k, int E, int32_t* 
   B200_CUDA(cudaGetLastError());
   if (blocks > 0) {
     permute_rank_kernel<<<blocks, kWarpsPerBlock * 32, shm, st>>>(idx_ll, M, E, hist, offs, poffs, slot_row, row_slot,
-                                                                   reinterpret_cast<long long*>(order));
+                                                                   order, slot_pos);
     B200_CUDA(cudaGetLastError());
   }
   return 0;

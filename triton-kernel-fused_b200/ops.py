@@ -140,7 +140,8 @@ class Permutation:
     slot_row: torch.Tensor    # (T*k,) int32
     row_slot: torch.Tensor    # (cap,) int32, valid below poffs[E]
     tile_expert: torch.Tensor # (cap/128,) int32
-    order: torch.Tensor | None
+    order: torch.Tensor | None      # (T*k,) int32 compact row -> slot (stable argsort of idx.flatten())
+    slot_pos: torch.Tensor | None   # (T*k,) int32 slot -> compact row
 
     @property
     def total_rows(self):     # device scalar view
@@ -162,23 +163,35 @@ def permute_build(idx, E, want_order=False) -> Permutation:
     slot_row = torch.empty(M, **i32)
     row_slot = torch.empty(cap, **i32)
     tile_expert = torch.empty(cap // 128, **i32)
-    order = torch.empty(M, dtype=torch.int64, device=dev) if want_order else None
+    order = torch.empty(M, **i32) if want_order else None
+    slot_pos = torch.empty(M, **i32) if want_order else None
     ws_bytes = int(L.lib().b200moe_permute_ws_bytes(M, E))
     ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
     L.check(L.lib().b200moe_permute_build(L.ptr(idx), T, k, E, L.ptr(counts), L.ptr(offs), L.ptr(poffs),
                                           L.ptr(slot_row), L.ptr(row_slot), L.ptr(tile_expert), L.ptr(order),
-                                          L.ptr(ws), ws_bytes, L.ptr(L.status_word(dev)), L.stream_of(idx)))
-    return Permutation(T, k, E, cap, counts, offs, poffs, slot_row, row_slot, tile_expert, order)
+                                          L.ptr(slot_pos), L.ptr(ws), ws_bytes, L.ptr(L.status_word(dev)), L.stream_of(idx)))
+    return Permutation(T, k, E, cap, counts, offs, poffs, slot_row, row_slot, tile_expert, order, slot_pos)
 
 
 @_op("gather_rows", 1)
-def gather_rows(x, perm: Permutation):
-    L.require_cuda_bf16("hidden", x)
+def gather_rows_raw(x, row_slot, total_rows, k, rows_cap):
+    """out[r] = x[row_slot[r] // k] for r < *total_rows (device scalar), zero rows where row_slot < 0."""
+    L.require_cuda_bf16("x", x)
     H = x.shape[1]
-    x_s = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=x.device)
-    L.check(L.lib().b200moe_gather_rows(L.ptr(x), L.ptr(perm.row_slot), L.ptr(perm.total_rows), perm.k, H, perm.cap,
-                                        L.ptr(x_s), L.stream_of(x)))
-    return x_s
+    out = torch.empty(max(rows_cap, 1), H, dtype=torch.bfloat16, device=x.device)
+    L.check(L.lib().b200moe_gather_rows(L.ptr(x), L.ptr(row_slot), L.ptr(total_rows), k, H, rows_cap,
+                                        L.ptr(out), L.stream_of(x)))
+    return out
+
+
+def gather_rows(x, perm: Permutation):
+    """Rows of x in the padded expert-contiguous layout of `perm`."""
+    return gather_rows_raw(x, perm.row_slot, perm.total_rows, perm.k, perm.cap)
+
+
+def gather_compact(x, perm: Permutation):
+    """Rows of x in the compact expert-sorted order of `perm` (needs want_order=True)."""
+    return gather_rows_raw(x, perm.order, perm.offs[perm.E:], perm.k, perm.T * perm.k)
 
 
 @_op("expert_gate_up_swiglu", 1)
@@ -235,20 +248,28 @@ def expert_wgrad(a, b, perm: Permutation):
 
 
 @_op("combine", 1)
-def combine(rows, w, perm: Permutation):
+def combine_raw(rows, w, slot_table, T, k):
+    """out[t] = sum_j w[t,j] * rows[slot_table[t*k+j]] (w None = 1), fp32 accumulate, bf16 out."""
     H = rows.shape[1]
-    out = torch.empty(perm.T, H, dtype=torch.bfloat16, device=rows.device)
-    L.check(L.lib().b200moe_combine(L.ptr(rows), L.ptr(w), L.ptr(perm.slot_row), perm.T, perm.k, H, L.ptr(out),
+    out = torch.empty(max(T, 1), H, dtype=torch.bfloat16, device=rows.device)[:T]
+    L.check(L.lib().b200moe_combine(L.ptr(rows), L.ptr(w), L.ptr(slot_table), T, k, H, L.ptr(out),
                                     L.stream_of(rows)))
     return out
 
 
+def combine(rows, w, perm: Permutation):
+    return combine_raw(rows, w, perm.slot_row, perm.T, perm.k)
+
+
 @_op("combine_bwd", 1)
-def combine_bwd(grad_out, eo, w, perm: Permutation):
+def combine_bwd_raw(grad_out, eo, w, row_slot, total_rows, k, rows_cap):
     H = eo.shape[1]
     grad_eo = torch.empty_like(eo)
-    grad_w = torch.empty(perm.T, perm.k, dtype=torch.float32, device=eo.device)
-    L.check(L.lib().b200moe_combine_bwd(L.ptr(grad_out), L.ptr(eo), L.ptr(w), L.ptr(perm.row_slot),
-                                        L.ptr(perm.total_rows), perm.k, H, perm.cap, L.ptr(grad_eo), L.ptr(grad_w),
-                                        L.stream_of(eo)))
+    grad_w = torch.empty(w.shape, dtype=torch.float32, device=eo.device)
+    L.check(L.lib().b200moe_combine_bwd(L.ptr(grad_out), L.ptr(eo), L.ptr(w), L.ptr(row_slot), L.ptr(total_rows), k,
+                                        H, rows_cap, L.ptr(grad_eo), L.ptr(grad_w), L.stream_of(eo)))
     return grad_eo, grad_w
+
+
+def combine_bwd(grad_out, eo, w, perm: Permutation):
+    return combine_bwd_raw(grad_out, eo, w, perm.row_slot, perm.total_rows, perm.k, perm.cap)
