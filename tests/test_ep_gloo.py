@@ -1,0 +1,95 @@
+"""CPU, world_size 2 over gloo: the expert-parallel plumbing (count exchange, uneven all-to-all,
+local re-sort, backward mirror) gives the single-process result on the concatenated batch."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import moe_oracle as O
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, cfg, skew, q):
+    import importlib
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        pkg = importlib.import_module("triton-kernel-fused_b200")
+        from tests.cpu_kernels import CpuKernels
+        T, H, E, I, k = cfg
+        inp = O.make_inputs(T, H, E, I, k, seed=31, bias_std=0.01, zipf_s=1.1 if skew else None)
+        logits = inp["x"] @ inp["gate_weight"].t()
+        if skew:
+            logits = logits + 3.0 * inp["logit_bias"][None, :]
+        idx, w, counts = O.router_epilogue_fwd(logits, inp["bias"], k)
+        Tl, El = T // world, E // world
+        sl = slice(rank * Tl, (rank + 1) * Tl)
+        x = inp["x"][sl].clone().requires_grad_(True)
+        wt = w[sl].clone().requires_grad_(True)
+        gu = inp["gate_up"][rank * El:(rank + 1) * El].clone().requires_grad_(True)
+        dn = inp["down"][rank * El:(rank + 1) * El].clone().requires_grad_(True)
+        out = pkg.ep_moe(x, idx[sl].contiguous(), wt, gu, dn, E, None, _kernels=CpuKernels)
+        (out * inp["grad_out"][sl]).sum().backward()
+        # load-balance plumbing: the all-reduced local counts equal the global histogram
+        local_counts = torch.bincount(idx[sl].flatten(), minlength=E).to(torch.int32)
+        dist.all_reduce(local_counts)
+        assert torch.equal(local_counts, counts)
+        q.put((rank, out.detach(), x.grad, wt.grad, gu.grad, dn.grad))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("cfg,skew", [((256, 64, 8, 48, 2), False), ((384, 32, 16, 40, 4), True)])
+def test_expert_parallel_equals_single_process(cfg, skew):
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, cfg, skew, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(world):
+        r = q.get(timeout=120)
+        res[r[0]] = r[1:]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    T, H, E, I, k = cfg
+    inp = O.make_inputs(T, H, E, I, k, seed=31, bias_std=0.01, zipf_s=1.1 if skew else None)
+    logits = inp["x"] @ inp["gate_weight"].t()
+    if skew:
+        logits = logits + 3.0 * inp["logit_bias"][None, :]
+    idx, w, counts = O.router_epilogue_fwd(logits, inp["bias"], k)
+    if skew:
+        assert (counts == 0).any()          # some experts (and possibly a whole split) are empty
+    x = inp["x"].clone().requires_grad_(True)
+    wt = w.clone().requires_grad_(True)
+    gu = inp["gate_up"].clone().requires_grad_(True)
+    dn = inp["down"].clone().requires_grad_(True)
+    ref = O.moe_experts(x, idx, wt, gu, dn)
+    (ref * inp["grad_out"]).sum().backward()
+    cat = lambda i: torch.cat([res[r][i] for r in range(world)])
+    tol = 1e-5
+    assert O.rel_l2(cat(0), ref.detach()) < tol
+    assert O.rel_l2(cat(1), x.grad) < tol
+    assert O.rel_l2(cat(2), wt.grad) < tol
+    assert O.rel_l2(cat(3), gu.grad) < tol
+    assert O.rel_l2(cat(4), dn.grad) < tol
+
+
+def test_exchange_plan_rejects_indivisible_expert_count():
+    import importlib
+    ep = importlib.import_module("triton-kernel-fused_b200.ep")
+    with pytest.raises(ValueError, match="divisible"):
+        ep.exchange_plan(torch.zeros(7, dtype=torch.int32), 2)
