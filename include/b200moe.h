@@ -101,6 +101,19 @@ int b200moe_permute_build(const int64_t* idx, int64_t T, int k, int E, int32_t* 
                           int32_t* tile_expert, int32_t* order, int32_t* slot_pos, void* ws,
                           size_t ws_bytes, int32_t* status, b200moe_stream_t stream);
 
+/* No counterpart in the reference.  Same outputs as b200moe_permute_build, for callers that cannot
+ * allocate device memory (a plugin inside a framework that owns all free memory, a latency-bound loop
+ * where cudaMalloc's device-wide synchronisation is not allowed): the histogram scratch is a fixed
+ * 1 MiB array inside the library, so ceil(T*k/512)*E*4 bytes must not exceed 1 MiB (e.g. T*k <= 2 097 152
+ * at E = 64, 524 288 at E = 256); larger problems return B200MOE_E_WS_TOO_SMALL.  Allocates nothing.
+ * The first call on each device looks the array's address up (cudaGetSymbolAddress, with that device
+ * current); make that first call before any stream capture begins.  All calls on a device share the
+ * one array: two calls whose kernels can overlap on the GPU (different streams) race on it. */
+int b200moe_permute_build_static(const int64_t* idx, int64_t T, int k, int E, int32_t* counts,
+                                 int32_t* offs, int32_t* poffs, int32_t* slot_row, int32_t* row_slot,
+                                 int32_t* tile_expert, int32_t* order, int32_t* slot_pos,
+                                 int32_t* status, b200moe_stream_t stream);
+
 /* Replaces hidden.index_select(0, st) (kernels/sm75/moe.py:744, :589): x_s[r] = x[row_slot[r]/k],
  * zero rows where row_slot[r] < 0.  Only rows below *total_rows (device) are written. */
 int b200moe_gather_rows(const void* x, const int32_t* row_slot, const int32_t* total_rows, int k,

@@ -41,6 +41,7 @@ _SIGNATURES = {
     "b200moe_permute_ws_bytes": (c_size_t, [c_int64, c_int]),
     "b200moe_permute_build": (c_int, [c_void_p, c_int64, c_int, c_int] + [c_void_p] * 8 +
                               [c_void_p, c_size_t, c_void_p, c_void_p]),
+    "b200moe_permute_build_static": (c_int, [c_void_p, c_int64, c_int, c_int] + [c_void_p] * 8 + [c_void_p, c_void_p]),
     "b200moe_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p]),
     "b200moe_expert_gate_up_swiglu": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 4),
     "b200moe_expert_down": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
