@@ -30,7 +30,7 @@ extern "C" {
 
 typedef struct CUstream_st* b200moe_stream_t; /* == cudaStream_t */
 
-#define B200MOE_TILE_M 128
+#define B200MOE_TILE_M 256
 #define B200MOE_MAX_EXPERTS 256
 #define B200MOE_MAX_TOPK 32
 
@@ -93,7 +93,7 @@ size_t b200moe_permute_ws_bytes(int64_t M, int E);
  * counting sort done on the device, no host sync.  idx: (T,k) int64.
  * Outputs: counts (E), offs (E+1) compact end-exclusive scan, poffs (E+1) padded scan,
  * slot_row (T*k) padded row of slot t*k+j, row_slot (cap) slot of each padded row or -1 (only rows
- * below poffs[E] are written), tile_expert (cap/128) expert of each row tile,
+ * below poffs[E] are written), tile_expert (cap/B200MOE_TILE_M) expert of each row tile,
  * order (T*k, nullable) = the stable argsort of idx.flatten() (compact row -> slot),
  * slot_pos (T*k, nullable) = its inverse (slot -> compact row). ws: scratch, ws_bytes from above. */
 int b200moe_permute_build(const int64_t* idx, int64_t T, int k, int E, int32_t* counts,

@@ -141,7 +141,7 @@ def sort_by_expert_stable(idx: torch.Tensor, E: int):
     return order, st, counts, offs
 
 
-def padded_layout(counts: torch.Tensor, tile: int = 128):
+def padded_layout(counts: torch.Tensor, tile: int = 256):
     """Tile-padded expert segments used by the CUDA path: expert e owns padded rows
     [poffs[e], poffs[e+1]) with poffs[e+1]-poffs[e] = ceil(counts[e]/tile)*tile.  Zero-count
     experts own zero rows (the reference emits zero tiles for them, kernels/sm75/moe.py:535-543)."""
@@ -152,7 +152,7 @@ def padded_layout(counts: torch.Tensor, tile: int = 128):
     return poffs
 
 
-def permutation_tables(idx: torch.Tensor, E: int, tile: int = 128):
+def permutation_tables(idx: torch.Tensor, E: int, tile: int = 256):
     """All tables the CUDA permute kernels emit, computed on the CPU:
     slot_row (M,) padded row of slot t*k+j; row_slot (poffs[E],) slot of each padded row or -1;
     tile_expert (poffs[E]/tile,) expert of each row tile."""

@@ -19,17 +19,17 @@ class CpuKernels:
         T, k = idx.shape
         tb = O.permutation_tables(idx, E) if T > 0 else None
         M = T * k
-        cap = ((M + 127) // 128 + E) * 128
+        cap = ((M + 255) // 256 + E) * 256
         if tb is None:
             z = torch.zeros
             return Permutation(T, k, E, cap, z(E, dtype=torch.int32), z(E + 1, dtype=torch.int32),
                                z(E + 1, dtype=torch.int32), z(0, dtype=torch.int32), z(cap, dtype=torch.int32),
-                               z(cap // 128, dtype=torch.int32), z(0, dtype=torch.int32), z(0, dtype=torch.int32))
+                               z(cap // 256, dtype=torch.int32), z(0, dtype=torch.int32), z(0, dtype=torch.int32))
         total = int(tb["poffs"][-1])
         row_slot = torch.full((cap,), -1, dtype=torch.int32)
         row_slot[:total] = tb["row_slot"]
-        tile_expert = torch.zeros(cap // 128, dtype=torch.int32)
-        tile_expert[: total // 128] = tb["tile_expert"]
+        tile_expert = torch.zeros(cap // 256, dtype=torch.int32)
+        tile_expert[: total // 256] = tb["tile_expert"]
         order = tb["order"].to(torch.int32)
         slot_pos = torch.empty(M, dtype=torch.int32)
         slot_pos[tb["order"]] = torch.arange(M, dtype=torch.int32)

@@ -29,8 +29,8 @@ def test_host_only_entry_points():
     pkg = load_pkg()
     lib = pkg.lib()
     assert b"sm_100a" in lib.b200moe_version()
-    assert lib.b200moe_padded_rows_cap(98304, 64) == (98304 // 128 + 64) * 128
-    assert lib.b200moe_padded_rows_cap(1, 1) == 256
+    assert lib.b200moe_padded_rows_cap(98304, 64) == (98304 // 256 + 64) * 256
+    assert lib.b200moe_padded_rows_cap(1, 1) == 512
     assert lib.b200moe_permute_ws_bytes(98304, 64) >= 98304 // 512 * 64 * 4
     assert b"expert index" in lib.b200moe_status_string(5)
 

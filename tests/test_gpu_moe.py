@@ -25,7 +25,7 @@ def _stage_reference(x, idx, w, gu, dn, go):
     tok = (rs.clamp_min(0) // idx.shape[1]).long()
     x_s = torch.zeros(total, H)
     x_s[live] = x.float()[tok[live]]
-    te = torch.repeat_interleave(tb["tile_expert"].long(), 128)
+    te = torch.repeat_interleave(tb["tile_expert"].long(), 256)
     gate_up = torch.zeros(total, twoI)
     eo = torch.zeros(total, H)
     inter = torch.zeros(total, I)

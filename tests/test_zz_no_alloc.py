@@ -19,7 +19,7 @@ DEV = "cuda"
 def _tables(E, M, cap):
     i32 = dict(dtype=torch.int32, device=DEV)
     names = ("counts", "offs", "poffs", "slot_row", "row_slot", "tile_expert", "order", "slot_pos")
-    sizes = (E, E + 1, E + 1, M, cap, cap // 128, M, M)
+    sizes = (E, E + 1, E + 1, M, cap, cap // 256, M, M)
     return {n: torch.full((s,), -7, **i32) for n, s in zip(names, sizes)}
 
 
@@ -49,7 +49,7 @@ def test_static_scratch_matches_workspace_version_twice_in_a_row(pkg, shapes):
         assert int(status.item()) == 0
         total = int(ref["poffs"][-1])
         for name in ref:                                   # integer tables: bit-exact
-            n = total if name == "row_slot" else (total // 128 if name == "tile_expert" else ref[name].numel())
+            n = total if name == "row_slot" else (total // 256 if name == "tile_expert" else ref[name].numel())
             assert torch.equal(got[name][:n], ref[name][:n]), (call_no, name)
 
 

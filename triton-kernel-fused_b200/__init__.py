@@ -7,6 +7,7 @@ from .moe import moe, moe_grouped, moe_per_expert, GROUPED_MIN_TOKENS
 from .router import fused_mlp_router, FusedMLPRouter, router_bias_update
 from .layer import MoELayer
 from . import ops
+from .ops import TILE_M
 from .ep import ExpertParallelMoELayer, ep_moe
 
 __all__ = ["moe", "moe_grouped", "moe_per_expert", "GROUPED_MIN_TOKENS", "fused_mlp_router",

@@ -7,10 +7,17 @@
 //             GROUPED_K  D[e](M,N)         = A(rows of e)^T * B(rows of e)   (expert wgrad, split-K)
 //   operand majors: K-major (reduction index contiguous) or MN-major (row/column index contiguous)
 //   epilogues: bf16 store, SwiGLU (gate|up -> gate_up + inter), GLU backward, fp32 store.
+//   CTAS = 1: one CTA computes a 128 x BN tile.
+//   CTAS = 2: a CTA pair (cluster of 2) computes a 256 x 256 tile with tcgen05 cta_group::2: each CTA
+//             stages its own 128 rows of A and its own 128 columns of B, the leader CTA issues the
+//             MMAs for both, each CTA's TMEM holds its 128 rows of the accumulator.  This halves
+//             the L2 -> shared-memory traffic per FLOP and leaves room for 6 stages instead of 4.
 //
-// Warp roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = TMEM owner + MMA issuer (one
-// lane), warps 2-5 = epilogue (TMEM lane quarter = warp_id % 4).
+// Warp roles (320 threads): warp 0 = TMA producer (one lane), warp 1 = TMEM owner + MMA issuer (one
+// lane), warps 2-9 = epilogue (TMEM lane quarter = warp_id % 4, two warps per quarter split the
+// columns).
 #include <cuda.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -22,9 +29,10 @@ namespace b200moe {
 enum : int { SCHED_DENSE = 0, SCHED_GROUPED_M = 1, SCHED_GROUPED_K = 2 };
 enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_GLU_BWD = 2, EPI_STORE_F32 = 3 };
 
-constexpr int BM = 128;  // tile rows = UMMA M = TMEM lanes
+constexpr int BM = 128;  // rows per CTA = TMEM lanes
 constexpr int BK = 64;   // k-block: 64 bf16 = one 128-byte swizzle row
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 
 struct GemmParams {
   int sched;
@@ -34,8 +42,8 @@ struct GemmParams {
   int K;                 // reduction length (DENSE, GROUPED_M); total rows (GROUPED_K by chunks)
   int num_groups;        // experts (GROUPED_M/K) or K-chunks
   int k_chunk;           // GROUPED_K without poffs: rows per chunk (multiple of 64)
-  const int* tile_expert;  // GROUPED_M: expert of each 128-row tile
-  const int* poffs;        // (num_groups+1) padded row offsets, multiples of 128
+  const int* tile_expert;  // GROUPED_M: expert of each B200MOE_TILE_M-row tile
+  const int* poffs;        // (num_groups+1) padded row offsets, multiples of B200MOE_TILE_M
   void* D;
   long long ldd;
   long long d_group_stride;  // GROUPED_K: elements between D[e] and D[e+1]
@@ -48,33 +56,34 @@ struct Tile {
   int m0, n0, g, k0, nkb;
 };
 
-template <int BN>
+template <int BN, int CTAS>
 struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_BYTES = (BN / CTAS) * BK * 2;   // per CTA
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int NSTAGE = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int NSTAGE = (192 * 1024) / STAGE_BYTES;  // 4 (48 KB), 6 (32 KB) or 8 (24 KB)
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulators; 128, 256 or 512 (power of two >= 32)
   static constexpr int BAR_BYTES = (2 * NSTAGE + 4) * 8 + 16;
   static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  static constexpr int TILE_ROWS = BM * CTAS;
 };
 
-__device__ __forceinline__ int total_tiles(const GemmParams& p, int TN) {
+__device__ __forceinline__ int total_tiles(const GemmParams& p, int TN, int TM) {
   const int nt = (p.N + TN - 1) / TN;
-  if (p.sched == SCHED_DENSE) return ((p.M + BM - 1) / BM) * nt;
-  if (p.sched == SCHED_GROUPED_M) return (p.poffs[p.num_groups] / BM) * nt;
-  return ((p.M + BM - 1) / BM) * nt * p.num_groups;
+  if (p.sched == SCHED_DENSE) return ((p.M + TM - 1) / TM) * nt;
+  if (p.sched == SCHED_GROUPED_M) return (p.poffs[p.num_groups] / TM) * nt;
+  return ((p.M + TM - 1) / TM) * nt * p.num_groups;
 }
 
-__device__ __forceinline__ Tile get_tile(const GemmParams& p, int tile, int TN) {
+__device__ __forceinline__ Tile get_tile(const GemmParams& p, int tile, int TN, int TM) {
   Tile t;
   const int nt = (p.N + TN - 1) / TN;
   if (p.sched == SCHED_GROUPED_K) {
-    const int mt = (p.M + BM - 1) / BM;
+    const int mt = (p.M + TM - 1) / TM;
     const int per = mt * nt;
     t.g = tile / per;
     const int r = tile - t.g * per;
-    t.m0 = (r / nt) * BM;
+    t.m0 = (r / nt) * TM;
     t.n0 = (r % nt) * TN;
     int kb, ke;
     if (p.poffs != nullptr) {
@@ -88,22 +97,33 @@ __device__ __forceinline__ Tile get_tile(const GemmParams& p, int tile, int TN) 
     t.nkb = (ke - kb + BK - 1) / BK;
   } else {
     const int mi = tile / nt;
-    t.m0 = mi * BM;
+    t.m0 = mi * TM;
     t.n0 = (tile - mi * nt) * TN;
-    t.g = (p.sched == SCHED_GROUPED_M) ? p.tile_expert[mi] : 0;
+    t.g = (p.sched == SCHED_GROUPED_M) ? p.tile_expert[t.m0 / B200MOE_TILE_M] : 0;
     t.k0 = 0;
     t.nkb = (p.K + BK - 1) / BK;
   }
   return t;
 }
 
-template <int BN, int EPI>
+__device__ __forceinline__ uint4 pack8(const uint32_t* r) {
+  uint4 o;
+  o.x = pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1]));
+  o.y = pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3]));
+  o.z = pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5]));
+  o.w = pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7]));
+  return o;
+}
+
+template <int BN, int EPI, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const GemmParams p) {
-  using C = Cfg<BN>;
-  constexpr int TN = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  using C = Cfg<BN, CTAS>;
+  constexpr int TN = (EPI == EPI_SWIGLU) ? BN / 2 : BN;   // output columns one tile covers
+  constexpr int TM = C::TILE_ROWS;
   constexpr int NSTAGE = C::NSTAGE;
+  constexpr int BNC = BN / CTAS;                          // B columns staged by one CTA
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -118,6 +138,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (CTAS == 2) ? cluster_ctarank() : 0u;   // 0 = leader of the pair
+  const int first_tile = (CTAS == 2) ? static_cast<int>(cluster_id_x()) : static_cast<int>(blockIdx.x);
+  const int tile_step = (CTAS == 2) ? static_cast<int>(num_clusters_x()) : static_cast<int>(gridDim.x);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGE; ++s) {
@@ -126,7 +149,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tfull + 8 * b, 1);
-      mbar_init(bar_tempty + 8 * b, 4);
+      mbar_init(bar_tempty + 8 * b, kEpiWarps * CTAS);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -134,51 +157,85 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tma_prefetch_desc(&tmB);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (CTAS == 2) {
+      tmem_alloc_pair(smem_u32(tmem_slot), C::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTAS == 2) {   // peer barriers are initialised before any remote arrive
+    __syncwarp();
+    cluster_sync_all();
+  }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int total = total_tiles(p, TN);
+  const int total = total_tiles(p, TN, TM);
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer (each CTA)
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-        const Tile t = get_tile(p, tile, TN);
+      for (int tile = first_tile; tile < total && ok; tile += tile_step) {
+        const Tile t = get_tile(p, tile, TN, TM);
         const int gB = (p.sched == SCHED_GROUPED_M) ? t.g : 0;
+        const int m0 = t.m0 + BM * static_cast<int>(cta_rank);
         for (int kb = 0; kb < t.nkb; ++kb) {
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, ST_WAIT_PRODUCER)) {
             ok = false;
             break;
           }
-          const uint32_t full = bar_full + 8 * s;
-          mbar_arrive_expect_tx(full, C::STAGE_BYTES);
           const uint32_t sa = smem_u32(smem + s * C::STAGE_BYTES);
           const uint32_t sb = sa + C::A_BYTES;
           const int kk = t.k0 + kb * BK;
-          if (!p.a_mn) {
-            tma_load_3d(sa, &tmA, full, kk, t.m0, 0);  // box {64 k, 128 rows}
-          } else {
+          if constexpr (CTAS == 1) {
+            const uint32_t full = bar_full + 8 * s;
+            mbar_arrive_expect_tx(full, C::STAGE_BYTES);
+            if (!p.a_mn) {
+              tma_load_3d(sa, &tmA, full, kk, m0, 0);  // box {64 k, 128 rows}
+            } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j)  // boxes {64 mn, 64 k-rows}
-              tma_load_3d(sa + j * (64 * BK * 2), &tmA, full, t.m0 + 64 * j, kk, 0);
-          }
-          if (EPI == EPI_SWIGLU) {
-            // gate rows [n0, n0+BN/2) of W[e] then up rows of the same range: dims {H, I, 2E}
-            tma_load_3d(sb, &tmB, full, kk, t.n0, 2 * gB);
-            tma_load_3d(sb + (BN / 2) * BK * 2, &tmB, full, kk, t.n0, 2 * gB + 1);
-          } else if (!p.b_mn) {
-            tma_load_3d(sb, &tmB, full, kk, t.n0, gB);  // box {64 k, BN rows}
-          } else {
+              for (int j = 0; j < BM / 64; ++j)  // boxes {64 mn, 64 k-rows}
+                tma_load_3d(sa + j * (64 * BK * 2), &tmA, full, m0 + 64 * j, kk, 0);
+            }
+            if constexpr (EPI == EPI_SWIGLU) {
+              // gate rows [n0, n0+BN/2) of W[e] then up rows of the same range: dims {H, I, 2E}
+              tma_load_3d(sb, &tmB, full, kk, t.n0, 2 * gB);
+              tma_load_3d(sb + (BN / 2) * BK * 2, &tmB, full, kk, t.n0, 2 * gB + 1);
+            } else if (!p.b_mn) {
+              tma_load_3d(sb, &tmB, full, kk, t.n0, gB);  // box {64 k, BN rows}
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_3d(sb + j * (64 * BK * 2), &tmB, full, t.n0 + 64 * j, kk, gB);
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_3d(sb + j * (64 * BK * 2), &tmB, full, t.n0 + 64 * j, kk, gB);
+            }
+          } else {
+            // the leader's barrier counts the bytes of both CTAs
+            const uint32_t full = mapa_shared(bar_full + 8 * s, 0);
+            if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, 2 * C::STAGE_BYTES);
+            if (!p.a_mn) {
+              tma_load_3d_pair(sa, &tmA, full, kk, m0, 0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j)
+                tma_load_3d_pair(sa + j * (64 * BK * 2), &tmA, full, m0 + 64 * j, kk, 0);
+            }
+            if constexpr (EPI == EPI_SWIGLU) {
+              // leader stages the gate rows, the peer the up rows of I-columns [n0, n0+128)
+              tma_load_3d_pair(sb, &tmB, full, kk, t.n0, 2 * gB + static_cast<int>(cta_rank));
+            } else if (!p.b_mn) {
+              tma_load_3d_pair(sb, &tmB, full, kk, t.n0 + BNC * static_cast<int>(cta_rank), gB);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BNC / 64; ++j)
+                tma_load_3d_pair(sb + j * (64 * BK * 2), &tmB, full,
+                                 t.n0 + BNC * static_cast<int>(cta_rank) + 64 * j, kk, gB);
+            }
           }
           if (++s == NSTAGE) {
             s = 0;
@@ -188,9 +245,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_bf16(BN, p.a_mn, p.b_mn);
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && cta_rank == 0) {
+      const uint32_t idesc = umma_idesc_bf16(BN, p.a_mn, p.b_mn, TM);
       // K-major: rows are 128 B apart, 8-row groups 1024 B apart, 16 k-elements = 32 B.
       // MN-major: 64-wide MN blocks are 64*128 B apart (LBO), 8 k-rows 1024 B apart (SBO),
       //           16 k-rows = 2048 B.
@@ -199,8 +256,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int s = 0, it = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++it) {
-        const Tile t = get_tile(p, tile, TN);
+      for (int tile = first_tile; tile < total && ok; tile += tile_step, ++it) {
+        const Tile t = get_tile(p, tile, TN, TM);
         const int buf = it & 1;
         if (!mbar_wait(bar_tempty + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag, ST_WAIT_MMA_TMEM)) break;
         tc_fence_after();
@@ -217,39 +274,50 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t da = umma_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
             const uint64_t db = umma_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
-            umma_bf16(d_tmem, da, db, idesc, (kb | k) != 0);
+            if constexpr (CTAS == 2) umma_bf16_pair(d_tmem, da, db, idesc, (kb | k) != 0);
+            else umma_bf16(d_tmem, da, db, idesc, (kb | k) != 0);
           }
-          umma_commit(bar_empty + 8 * s);  // frees the stage when these MMAs have read it
+          // frees the stage (in both CTAs) when these MMAs have read it
+          if constexpr (CTAS == 2) umma_commit_pair(bar_empty + 8 * s);
+          else umma_commit(bar_empty + 8 * s);
           if (++s == NSTAGE) {
             s = 0;
             ph ^= 1;
           }
         }
         if (!ok) break;
-        if (t.nkb > 0) umma_commit(bar_tfull + 8 * buf);
-        else mbar_arrive(bar_tfull + 8 * buf);
+        if (t.nkb > 0) {
+          if constexpr (CTAS == 2) umma_commit_pair(bar_tfull + 8 * buf);
+          else umma_commit(bar_tfull + 8 * buf);
+        } else {
+          mbar_arrive(bar_tfull + 8 * buf);
+          if constexpr (CTAS == 2) mbar_arrive_cluster(mapa_shared(bar_tfull + 8 * buf, 1));
+        }
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps)
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // ------------------------------------------------------------------ epilogue (8 warps per CTA)
+    const int q = warp & 3;              // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;    // which half of the tile's columns this warp handles
+    const uint32_t tempty_leader = (CTAS == 2) ? mapa_shared(bar_tempty, 0) : bar_tempty;
     int it = 0;
-    for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
-      const Tile t = get_tile(p, tile, TN);
+    for (int tile = first_tile; tile < total; tile += tile_step, ++it) {
+      const Tile t = get_tile(p, tile, TN, TM);
       const int buf = it & 1;
       if (!mbar_wait(bar_tfull + 8 * buf, (it >> 1) & 1, abort_flag, ST_WAIT_EPILOGUE)) break;
       __syncwarp();
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-      const long long row = static_cast<long long>(t.m0) + q * 32 + lane;
+      const long long row = static_cast<long long>(t.m0) + BM * static_cast<int>(cta_rank) + q * 32 + lane;
       const bool have_acc = t.nkb > 0;
 
       if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32) {
         const bool row_ok = (p.sched == SCHED_GROUPED_M) || (row < p.M);
         const long long base = (p.sched == SCHED_GROUPED_K ? t.g * p.d_group_stride : 0) +
                                row * p.ldd + t.n0;
+        constexpr int W = BN / 2;   // columns per warp
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c0 = half * W; c0 < (half + 1) * W; c0 += 32) {
           if (t.n0 + c0 >= p.N) break;
           uint32_t r[32];
           if (have_acc) {
@@ -263,25 +331,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if constexpr (EPI == EPI_STORE) {
               __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + base + c0;
 #pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                if (t.n0 + c0 + v * 8 < p.N) {
-                  uint4 o;
-                  o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-                  o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-                  o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-                  o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-                  *reinterpret_cast<uint4*>(d + v * 8) = o;
-                }
-              }
+              for (int v = 0; v < 4; ++v)
+                if (t.n0 + c0 + v * 8 < p.N) *reinterpret_cast<uint4*>(d + v * 8) = pack8(r + v * 8);
             } else {
               float* d = reinterpret_cast<float*>(p.D) + base + c0;
 #pragma unroll
-              for (int v = 0; v < 8; ++v) {
-                if (t.n0 + c0 + v * 4 < p.N) {
-                  uint4 o = make_uint4(r[v * 4 + 0], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
-                  *reinterpret_cast<uint4*>(d + v * 4) = o;
-                }
-              }
+              for (int v = 0; v < 8; ++v)
+                if (t.n0 + c0 + v * 4 < p.N)
+                  *reinterpret_cast<uint4*>(d + v * 4) = make_uint4(r[v * 4 + 0], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
             }
           }
         }
@@ -290,8 +347,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int I = p.I;
         __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(p.D) + row * (2LL * I);
         __nv_bfloat16* it_out = reinterpret_cast<__nv_bfloat16*>(p.aux) + row * static_cast<long long>(I);
+        constexpr int W = BN / 4;   // I-columns per warp
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+        for (int c0 = half * W; c0 < (half + 1) * W; c0 += 32) {
           if (t.n0 + c0 >= I) break;
           uint32_t g[32], u[32];
           tmem_ld32(taddr + c0, g);
@@ -324,55 +382,83 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int I = p.I;
         const __nv_bfloat16* gu = reinterpret_cast<const __nv_bfloat16*>(p.aux) + row * (2LL * I);
         __nv_bfloat16* ggu = reinterpret_cast<__nv_bfloat16*>(p.D) + row * (2LL * I);
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          if (t.n0 + c0 >= I) break;
-          uint32_t r[32];
-          tmem_ld32(taddr + c0, r);
-          tmem_ld_wait();
+        constexpr int W = BN / 2;
+        constexpr int NCH = W / 32;
+        // the saved gate/up values of chunk c+1 are fetched while chunk c is computed
+        uint4 gv[2][4], uv[2][4];
+        auto fetch = [&](int c, int slot) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
-            const int col = t.n0 + c0 + v * 8;
+            const int col = t.n0 + half * W + c * 32 + v * 8;
             if (col < I) {
-              const uint4 gv = *reinterpret_cast<const uint4*>(gu + col);
-              const uint4 uv = *reinterpret_cast<const uint4*>(gu + I + col);
-              const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
-              const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
-              uint32_t og[4], ou[4];
+              gv[slot][v] = __ldg(reinterpret_cast<const uint4*>(gu + col));
+              uv[slot][v] = __ldg(reinterpret_cast<const uint4*>(gu + I + col));
+            } else {
+              gv[slot][v] = make_uint4(0u, 0u, 0u, 0u);
+              uv[slot][v] = make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
+        };
+        fetch(0, 0);
 #pragma unroll
-              for (int h = 0; h < 4; ++h) {
-                const float2 gf = unpack_bf16x2(gw[h]);
-                const float2 uf = unpack_bf16x2(uw[h]);
-                // grad_inter is rounded to bf16 first: the reference materialises it in bf16
-                const float go0 = bf16_round(__uint_as_float(r[v * 8 + 2 * h]));
-                const float go1 = bf16_round(__uint_as_float(r[v * 8 + 2 * h + 1]));
-                const float s0 = 1.0f / (1.0f + __expf(-gf.x));
-                const float s1 = 1.0f / (1.0f + __expf(-gf.y));
-                const float d0 = s0 * (1.0f + gf.x * (1.0f - s0));
-                const float d1 = s1 * (1.0f + gf.y * (1.0f - s1));
-                og[h] = pack_bf16x2(go0 * uf.x * d0, go1 * uf.y * d1);
-                ou[h] = pack_bf16x2(go0 * (gf.x * s0), go1 * (gf.y * s1));
+        for (int c = 0; c < NCH; ++c) {
+          const int c0 = half * W + c * 32;
+          if (t.n0 + c0 < I) {          // warp-uniform
+            uint32_t r[32];
+            tmem_ld32(taddr + c0, r);
+            if (c + 1 < NCH) fetch(c + 1, (c + 1) & 1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = t.n0 + c0 + v * 8;
+              if (col < I) {
+                const uint4 g4 = gv[c & 1][v], u4 = uv[c & 1][v];
+                const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
+                const uint32_t uw[4] = {u4.x, u4.y, u4.z, u4.w};
+                uint32_t og[4], ou[4];
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                  const float2 gf = unpack_bf16x2(gw[h]);
+                  const float2 uf = unpack_bf16x2(uw[h]);
+                  // grad_inter is rounded to bf16 first: the reference materialises it in bf16
+                  const float go0 = bf16_round(__uint_as_float(r[v * 8 + 2 * h]));
+                  const float go1 = bf16_round(__uint_as_float(r[v * 8 + 2 * h + 1]));
+                  const float s0 = 1.0f / (1.0f + __expf(-gf.x));
+                  const float s1 = 1.0f / (1.0f + __expf(-gf.y));
+                  const float d0 = s0 * (1.0f + gf.x * (1.0f - s0));
+                  const float d1 = s1 * (1.0f + gf.y * (1.0f - s1));
+                  og[h] = pack_bf16x2(go0 * uf.x * d0, go1 * uf.y * d1);
+                  ou[h] = pack_bf16x2(go0 * (gf.x * s0), go1 * (gf.y * s1));
+                }
+                *reinterpret_cast<uint4*>(ggu + col) = make_uint4(og[0], og[1], og[2], og[3]);
+                *reinterpret_cast<uint4*>(ggu + I + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
               }
-              *reinterpret_cast<uint4*>(ggu + col) = make_uint4(og[0], og[1], og[2], og[3]);
-              *reinterpret_cast<uint4*>(ggu + I + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
             }
           }
         }
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+      if (lane == 0) {
+        if constexpr (CTAS == 2) mbar_arrive_cluster(tempty_leader + 8 * buf);
+        else mbar_arrive(bar_tempty + 8 * buf);
+      }
     }
   }
 
   // ------------------------------------------------------------------ tear-down
   tc_fence_before();
   __syncthreads();
+  if constexpr (CTAS == 2) {   // nobody leaves while the peer may still touch it
+    __syncwarp();
+    cluster_sync_all();
+  }
   if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_flag);
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if constexpr (CTAS == 2) tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+    else tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
 }
 
@@ -418,23 +504,46 @@ static int make_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t 
   return 0;
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, int CTAS>
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int max_tiles,
                   cudaStream_t stream) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, CTAS>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_err = cudaFuncSetAttribute(gemm_kernel<BN, EPI, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     C::SMEM_BYTES);
   });
   if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(max dynamic smem)");
-  int grid = num_sms();
-  if (max_tiles > 0 && max_tiles < grid) grid = max_tiles;
-  if (grid < 1) grid = 1;
-  gemm_kernel<BN, EPI><<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, p);
-  B200_CUDA(cudaGetLastError());
+  int units = num_sms() / CTAS;          // CTAs, or CTA pairs
+  if (max_tiles > 0 && max_tiles < units) units = max_tiles;
+  if (units < 1) units = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(units * CTAS, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (CTAS > 1) ? 1 : 0;
+  B200_CUDA(cudaLaunchKernelEx(&cfg, gemm_kernel<BN, EPI, CTAS>, tmA, tmB, p));
   return 0;
+}
+
+// Pair (2-CTA) tiles are used for the grouped schedules with 256-wide tiles.  Setting the
+// environment variable B200MOE_FORCE_1CTA=1 keeps every launch on single-CTA tiles (A/B measurements).
+static bool pairs_enabled() {
+  static int v = -1;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char* e = getenv("B200MOE_FORCE_1CTA");
+    v = (e != nullptr && e[0] == '1') ? 0 : 1;
+  });
+  return v == 1;
 }
 
 // Operand description used by the host-side dispatcher.
@@ -468,17 +577,20 @@ static int pick_bn(long long n) {
 template <int EPI>
 static int dispatch_bn(int bn, const Operand& A, const Operand& B, GemmParams& p, int max_tiles,
                        cudaStream_t stream) {
+  const bool pair = (bn == 256) && (p.sched != SCHED_DENSE) && pairs_enabled();
   CUtensorMap tmA, tmB;
   int rc = encode_operand(&tmA, A, BM);
   if (rc) return rc;
-  const int b_rows = (EPI == EPI_SWIGLU) ? bn / 2 : bn;
+  // rows of B one TMA box brings in: half a tile for SwiGLU (gate and up halves) and for pairs
+  const int b_rows = (EPI == EPI_SWIGLU || pair) ? bn / 2 : bn;
   rc = encode_operand(&tmB, B, b_rows);
   if (rc) return rc;
+  if (pair) return launch<256, EPI, 2>(tmA, tmB, p, max_tiles > 0 ? (max_tiles + 1) / 2 : 0, stream);
   switch (bn) {
-    case 256: return launch<256, EPI>(tmA, tmB, p, max_tiles, stream);
-    case 128: return launch<128, EPI>(tmA, tmB, p, max_tiles, stream);
+    case 256: return launch<256, EPI, 1>(tmA, tmB, p, max_tiles, stream);
+    case 128: return launch<128, EPI, 1>(tmA, tmB, p, max_tiles, stream);
     default:
-      if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32) return launch<64, EPI>(tmA, tmB, p, max_tiles, stream);
+      if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32) return launch<64, EPI, 1>(tmA, tmB, p, max_tiles, stream);
       set_error("tile width %d not built for this epilogue", bn);
       return B200MOE_E_UNSUPPORTED;
   }
@@ -552,8 +664,8 @@ static int check_grouped(const char* who, const void* a, const void* b, const vo
   B200_CHECK_ARG(a && b && c && poffs, B200MOE_E_NULL, "%s: null pointer", who);
   (void)tile_expert;
   B200_CHECK_ARG(E >= 1 && E <= 65535, B200MOE_E_BAD_SHAPE, "%s: E = %d out of range", who, E);
-  B200_CHECK_ARG(rows_cap > 0 && rows_cap % BM == 0 && rows_cap < (1LL << 31), B200MOE_E_BAD_SHAPE,
-                 "%s: rows_cap = %lld must be a positive multiple of %d", who, (long long)rows_cap, BM);
+  B200_CHECK_ARG(rows_cap > 0 && rows_cap % B200MOE_TILE_M == 0 && rows_cap < (1LL << 31), B200MOE_E_BAD_SHAPE,
+                 "%s: rows_cap = %lld must be a positive multiple of %d", who, (long long)rows_cap, B200MOE_TILE_M);
   B200_CHECK_ARG(H > 0 && H % 8 == 0 && I > 0 && I % 8 == 0, B200MOE_E_BAD_SHAPE,
                  "%s: H = %lld and I = %lld must be positive multiples of 8", who, (long long)H, (long long)I);
   B200_CHECK_ARG(2 * E * I < (1LL << 31) && E * H < (1LL << 31), B200MOE_E_BAD_SHAPE, "%s: weight stack too tall", who);
@@ -629,8 +741,8 @@ int b200moe_expert_wgrad(const void* A, const void* B, const int32_t* poffs, int
                          int64_t Nb, void* out, int32_t* status, b200moe_stream_t stream) {
   B200_CHECK_ARG(A && B && poffs && out, B200MOE_E_NULL, "expert_wgrad: null pointer");
   B200_CHECK_ARG(E >= 1, B200MOE_E_BAD_SHAPE, "expert_wgrad: E = %d", E);
-  B200_CHECK_ARG(rows_cap > 0 && rows_cap % BM == 0 && rows_cap < (1LL << 31), B200MOE_E_BAD_SHAPE,
-                 "expert_wgrad: rows_cap = %lld must be a positive multiple of %d", (long long)rows_cap, BM);
+  B200_CHECK_ARG(rows_cap > 0 && rows_cap % B200MOE_TILE_M == 0 && rows_cap < (1LL << 31), B200MOE_E_BAD_SHAPE,
+                 "expert_wgrad: rows_cap = %lld must be a positive multiple of %d", (long long)rows_cap, B200MOE_TILE_M);
   CHECK_DIM8(Na); CHECK_DIM8(Nb); CHECK_I32(Na); CHECK_I32(Nb);
   B200_CHECK_ARG(aligned16(out), B200MOE_E_ALIGN, "expert_wgrad: output not aligned");
   Operand a{A, 1, Na, rows_cap, Na, 1, rows_cap * Na};

@@ -9,6 +9,7 @@ import torch
 from . import _lib as L
 
 LOGITS_BF16, LOGITS_F32, SCORES_F32 = 0, 1, 2
+TILE_M = 256   # B200MOE_TILE_M: expert segments are padded to this many rows
 
 # Optional observer used by the benchmark: hook(name, kernel_launches, start_event, end_event) is
 # called for every op below with CUDA events recorded on the launching stream around it.
@@ -139,7 +140,7 @@ class Permutation:
     poffs: torch.Tensor       # (E+1,) int32 padded offsets
     slot_row: torch.Tensor    # (T*k,) int32
     row_slot: torch.Tensor    # (cap,) int32, valid below poffs[E]
-    tile_expert: torch.Tensor # (cap/128,) int32
+    tile_expert: torch.Tensor # (cap/TILE_M,) int32
     order: torch.Tensor | None      # (T*k,) int32 compact row -> slot (stable argsort of idx.flatten())
     slot_pos: torch.Tensor | None   # (T*k,) int32 slot -> compact row
 
@@ -162,7 +163,7 @@ def permute_build(idx, E, want_order=False) -> Permutation:
     poffs = torch.empty(E + 1, **i32)
     slot_row = torch.empty(M, **i32)
     row_slot = torch.empty(cap, **i32)
-    tile_expert = torch.empty(cap // 128, **i32)
+    tile_expert = torch.empty(cap // TILE_M, **i32)
     order = torch.empty(M, **i32) if want_order else None
     slot_pos = torch.empty(M, **i32) if want_order else None
     ws_bytes = int(L.lib().b200moe_permute_ws_bytes(M, E))
