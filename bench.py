@@ -36,6 +36,8 @@ PKG = "triton-kernel-fused_b200"
 HEADLINE = dict(T=16384, H=2048, E=64, I=1408, k=6)
 # small case for profiler captures: weights (277 MB) exceed L2, about 1.5 GB held on the device
 PROFILE = dict(T=4096, H=2048, E=16, I=1408, k=6)
+# expert-parallel configuration: 65536 global tokens, 256 experts sharded over the ranks
+EP5 = dict(T=65536, H=7168, E=256, I=2048, k=8)
 METRIC = "moe_layer_fwd_bwd_tokens_per_s"
 
 
@@ -95,18 +97,27 @@ class ClockSampler:
 
 
 def _workload(n_gpus, which="headline"):
-    """Per-rank workload.  N=1: the headline layer.  N>1: every rank holds the same layer and its own
-    T tokens (token-sharded replicas, no data-path collective) until the expert-parallel path replaces it."""
-    w = dict(HEADLINE if which == "headline" else PROFILE)
-    w["name"] = "bf16 MoE layer T={T} H={H} E={E} I={I} top{k} fwd+bwd".format(**w)
-    w["parallelism"] = "single GPU" if n_gpus == 1 else f"token-sharded replicas x{n_gpus} (no collective)"
+    """Per-rank workload.  N=1: the headline layer on one GPU.  N>1: the same layer expert-parallel:
+    every rank keeps T tokens (weak scaling in tokens) and owns E/N of the experts; rows travel by NCCL
+    all-to-all.  `ep5` is the expert-parallel configuration with 65536 global tokens."""
+    if which == "ep5":
+        w = dict(EP5)
+        w["T"] = EP5["T"] // n_gpus
+    else:
+        w = dict(HEADLINE if which == "headline" else PROFILE)
+    w["name"] = "bf16 MoE layer T={T}/GPU H={H} E={E} I={I} top{k} fwd+bwd".format(**w)
+    w["parallelism"] = "single GPU" if n_gpus == 1 else f"expert parallel ep{n_gpus} (E/{n_gpus} experts per GPU, NCCL all-to-all)"
     return w
 
 
-def _make_layer(pkg, w, device, seed):
+def _make_layer(pkg, w, device, seed, world):
     torch.manual_seed(seed)
-    layer = pkg.MoELayer(w["H"], w["I"], w["E"], top_k=w["k"])
-    return layer.to(device).to(torch.bfloat16)
+    with torch.device(device):      # build the (large) expert stacks directly on the GPU
+        if world > 1:
+            layer = pkg.ExpertParallelMoELayer(w["H"], w["I"], w["E"], top_k=w["k"])
+        else:
+            layer = pkg.MoELayer(w["H"], w["I"], w["E"], top_k=w["k"])
+    return layer.to(torch.bfloat16)
 
 
 def run_ours(args):
@@ -124,7 +135,7 @@ def run_ours(args):
     ops = pkg.ops
     w = _workload(world, args.workload)
     T, H, E, I, k = w["T"], w["H"], w["E"], w["I"], w["k"]
-    layer = _make_layer(pkg, w, dev, seed=0)
+    layer = _make_layer(pkg, w, dev, seed=0, world=world)
     params = [layer.gate.weight, layer.gate_up_proj, layer.down_proj]
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     x_dev = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
@@ -231,7 +242,7 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": w["name"], "tokens_per_gpu": T, "d_model": H, "experts": E, "d_ff": I, "top_k": k,
                    "parallelism": w["parallelism"],
-                   "l2": "working set (1.1 GB of expert weights + 2 GB of activations) exceeds the 126 MB L2"},
+                   "l2": "no flush: the working set (expert weights + activations, several GB) exceeds the 126 MB L2"},
         "layer_tflops_per_gpu": round(layer_flops / (ms_step * 1e-3) / 1e12, 1),
         "layer_frac_of_peak": round(layer_flops / (ms_step * 1e-3) / 1e12 / peaks["tflops"], 4),
         "gemm_ms_per_step": round(gemm_ms, 4),
@@ -295,7 +306,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="headline", choices=["headline", "profile"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "profile", "ep5"],
                     help="profile = small case for profiler captures (not a benchmark number)")
     args = ap.parse_args()
     if args.impl == "reference":

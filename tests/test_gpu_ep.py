@@ -1,0 +1,94 @@
+"""GPU, 2 ranks over NCCL: the expert-parallel layer equals the single-GPU layer on the
+concatenated batch (bit-exact routing, values within the bf16 gate).  Needs two GPUs."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, cfg, q):
+    import importlib
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        pkg = importlib.import_module("triton-kernel-fused_b200")
+        from oracle import moe_oracle as O
+        T, H, E, I, k = cfg
+        inp = O.make_inputs(T, H, E, I, k, seed=41, bias_std=0.01, dtype=torch.bfloat16)
+        Tl, El = T // world, E // world
+        sl = slice(rank * Tl, (rank + 1) * Tl)
+        layer = pkg.ExpertParallelMoELayer(H, I, E, top_k=k).to(dev).to(torch.bfloat16)
+        with torch.no_grad():
+            layer.gate.weight.copy_(inp["gate_weight"])
+            layer.gate_up_proj.copy_(inp["gate_up"][rank * El:(rank + 1) * El])
+            layer.down_proj.copy_(inp["down"][rank * El:(rank + 1) * El])
+            layer.bias.copy_(inp["bias"])
+        x = inp["x"][sl].to(dev).requires_grad_(True)
+        out = layer(x)
+        (out.float() * inp["grad_out"][sl].to(dev).float()).sum().backward()
+        torch.cuda.synchronize()
+        pkg.check_status()
+        gw = layer.gate.weight.grad.clone()
+        dist.all_reduce(gw)                      # replicated router weight: sum of the local grads
+        layer.update_bias(0.001)
+        q.put((rank, out.detach().cpu(), x.grad.cpu(), layer.gate_up_proj.grad.cpu(), layer.down_proj.grad.cpu(),
+               gw.cpu(), layer.bias.cpu()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("cfg", [(2048, 512, 16, 256, 4), (1024, 256, 64, 128, 8)])
+def test_expert_parallel_equals_single_gpu(pkg, cfg):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    from oracle import moe_oracle as O
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, cfg, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(world):
+        r = q.get(timeout=300)
+        res[r[0]] = r[1:]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    T, H, E, I, k = cfg
+    inp = O.make_inputs(T, H, E, I, k, seed=41, bias_std=0.01, dtype=torch.bfloat16)
+    dev = "cuda"
+    layer = pkg.MoELayer(H, I, E, top_k=k).to(dev).to(torch.bfloat16)
+    with torch.no_grad():
+        layer.gate.weight.copy_(inp["gate_weight"])
+        layer.gate_up_proj.copy_(inp["gate_up"])
+        layer.down_proj.copy_(inp["down"])
+        layer.bias.copy_(inp["bias"])
+    x = inp["x"].to(dev).requires_grad_(True)
+    out = layer(x)
+    (out.float() * inp["grad_out"].to(dev).float()).sum().backward()
+    layer.update_bias(0.001)
+    cat = lambda i: torch.cat([res[r][i] for r in range(world)])
+    tol = 1e-2      # same bf16 kernels on both sides; only tile composition / summation order differ
+    assert O.rel_l2(cat(0), out.detach().cpu()) < tol
+    assert O.rel_l2(cat(1), x.grad.cpu()) < tol
+    assert O.rel_l2(cat(2), layer.gate_up_proj.grad.cpu()) < tol
+    assert O.rel_l2(cat(3), layer.down_proj.grad.cpu()) < tol
+    assert O.rel_l2(res[0][4], layer.gate.weight.grad.cpu()) < 2e-2
+    assert torch.equal(res[0][5], layer.bias.cpu()) and torch.equal(res[1][5], layer.bias.cpu())

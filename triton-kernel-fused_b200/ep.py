@@ -44,6 +44,7 @@ def exchange_plan(counts, world, group=None):
     return recv_counts, both[0].tolist(), both[1].tolist()
 
 
+@_cuda_ops._op("all_to_all", 0)
 def _a2a(rows, out_rows, out_splits, in_splits, group):
     out = torch.empty(max(out_rows, 1), rows.shape[1], dtype=rows.dtype, device=rows.device)[:out_rows]
     dist.all_to_all_single(out, rows[: sum(in_splits)].contiguous(), out_splits, in_splits, group=group)
