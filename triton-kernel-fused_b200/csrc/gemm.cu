@@ -56,15 +56,31 @@ struct Tile {
   int m0, n0, g, k0, nkb;
 };
 
-template <int BN, int CTAS>
+constexpr int kStageOutBytes = 32 * 128;   // one epilogue warp's staging box: 32 rows x 64 bf16
+
+// BN = 256 kernels with a bf16 result stage it in shared memory and write it with TMA stores
+template <int BN, int EPI>
+__host__ __device__ constexpr bool tma_epilogue() { return BN == 256 && EPI != EPI_STORE_F32; }
+
+// EPI_WARP_BYTES: shared memory each epilogue warp owns (0: none, 4 KB: one output staging box,
+// 8 KB: the GLU-backward gate and up boxes that are loaded by TMA and overwritten in place)
+template <int BN, int EPI>
+__host__ __device__ constexpr int epi_warp_bytes() {
+  return !tma_epilogue<BN, EPI>() ? 0 : (EPI == EPI_GLU_BWD ? 2 * kStageOutBytes : kStageOutBytes);
+}
+
+template <int BN, int CTAS, int EPI_WARP_BYTES = 0>
 struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = (BN / CTAS) * BK * 2;   // per CTA
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int NSTAGE = (192 * 1024) / STAGE_BYTES;  // 4 (48 KB), 6 (32 KB) or 8 (24 KB)
+  static constexpr int EPI_BYTES = kEpiWarps * EPI_WARP_BYTES;
+  static constexpr int kBudget = 232448 - 1024 - 256;       // 227 KB minus alignment slack and barriers
+  static constexpr int kFit = (kBudget - EPI_BYTES) / STAGE_BYTES;
+  static constexpr int NSTAGE = kFit > 8 ? 8 : kFit;
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulators; 128, 256 or 512 (power of two >= 32)
-  static constexpr int BAR_BYTES = (2 * NSTAGE + 4) * 8 + 16;
-  static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  static constexpr int BAR_BYTES = (2 * NSTAGE + 4 + kEpiWarps) * 8 + 16;
+  static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;  // + alignment slack
   static constexpr int TILE_ROWS = BM * CTAS;
 };
 
@@ -115,11 +131,60 @@ __device__ __forceinline__ uint4 pack8(const uint32_t* r) {
   return o;
 }
 
+// grad_gate = gi*up*sig(g)*(1+g*(1-sig(g))), grad_up = gi*g*sig(g) for 32 columns; gi (fp32 accumulator)
+// is rounded to bf16 first because the reference materialises grad_inter in bf16
+__device__ __forceinline__ void glu_bwd32(const uint32_t (&r)[32], const uint4 (&g)[4], const uint4 (&u)[4],
+                                          uint32_t* og, uint32_t* ou) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const uint32_t gw[4] = {g[v].x, g[v].y, g[v].z, g[v].w};
+    const uint32_t uw[4] = {u[v].x, u[v].y, u[v].z, u[v].w};
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      const float2 gf = unpack_bf16x2(gw[h]);
+      const float2 uf = unpack_bf16x2(uw[h]);
+      const float go0 = bf16_round(__uint_as_float(r[v * 8 + 2 * h]));
+      const float go1 = bf16_round(__uint_as_float(r[v * 8 + 2 * h + 1]));
+      const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
+      const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
+      const float d0 = s0 * (1.0f + gf.x * (1.0f - s0));
+      const float d1 = s1 * (1.0f + gf.y * (1.0f - s1));
+      og[4 * v + h] = pack_bf16x2(go0 * uf.x * d0, go1 * uf.y * d1);
+      ou[4 * v + h] = pack_bf16x2(go0 * (gf.x * s0), go1 * (gf.y * s1));
+    }
+  }
+}
+
+// One lane = one row of a 32-row staging box: 64 bf16 (32 packed registers) go to the 128-byte
+// swizzled position the TMA store expects (16-byte chunk j of row r sits at chunk j ^ (r & 7)).
+__device__ __forceinline__ void stage_row(uint8_t* buf, int lane, const uint32_t* pk) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+        make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+}
+// make the staged box visible to the async proxy and let lane 0 issue the store
+__device__ __forceinline__ void store_box(const CUtensorMap* tm, uint8_t* buf, int lane, int c0, int c1, int c2) {
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_3d(tm, smem_u32(buf), c0, c1, c2);
+    bulk_commit_group();
+  }
+}
+// the staging box may be overwritten again
+__device__ __forceinline__ void staging_free(int lane) {
+  if (lane == 0) bulk_wait_read_all();
+  __syncwarp();
+}
+
 template <int BN, int EPI, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmD2,
             const GemmParams p) {
-  using C = Cfg<BN, CTAS>;
+  constexpr bool TMA_EPI = tma_epilogue<BN, EPI>();
+  using C = Cfg<BN, CTAS, epi_warp_bytes<BN, EPI>()>;
   constexpr int TN = (EPI == EPI_SWIGLU) ? BN / 2 : BN;   // output columns one tile covers
   constexpr int TM = C::TILE_ROWS;
   constexpr int NSTAGE = C::NSTAGE;
@@ -128,12 +193,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NSTAGE * C::STAGE_BYTES);
+  uint8_t* epi_smem = smem + NSTAGE * C::STAGE_BYTES;   // 1024-aligned: stages are multiples of 8 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + C::EPI_BYTES);
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = smem_u32(bars + NSTAGE);
   const uint32_t bar_tfull = smem_u32(bars + 2 * NSTAGE);
   const uint32_t bar_tempty = smem_u32(bars + 2 * NSTAGE + 2);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGE + 4);
+  const uint32_t bar_epi = smem_u32(bars + 2 * NSTAGE + 4);   // one per epilogue warp (GLU backward loads)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGE + 4 + kEpiWarps);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -151,6 +218,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       mbar_init(bar_tfull + 8 * b, 1);
       mbar_init(bar_tempty + 8 * b, kEpiWarps * CTAS);
     }
+    for (int w = 0; w < kEpiWarps; ++w) mbar_init(bar_epi + 8 * w, 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
@@ -300,18 +368,143 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int q = warp & 3;              // TMEM lane quarter this warp may read
     const int half = (warp - 2) >> 2;    // which half of the tile's columns this warp handles
     const uint32_t tempty_leader = (CTAS == 2) ? mapa_shared(bar_tempty, 0) : bar_tempty;
+    uint32_t epi_phase = 0;   // parity of this warp's GLU-backward load barrier
     int it = 0;
     for (int tile = first_tile; tile < total; tile += tile_step, ++it) {
       const Tile t = get_tile(p, tile, TN, TM);
       const int buf = it & 1;
+      const int row0 = t.m0 + BM * static_cast<int>(cta_rank) + q * 32;   // first row of this warp
+      const long long row = static_cast<long long>(row0) + lane;
+      // GLU backward: the saved gate/up values do not depend on the accumulator, so the first
+      // 32 columns are fetched before waiting for the MMAs of this tile
+      // GLU backward: the saved gate/up values do not depend on the accumulator, so the TMA loads
+      // of this warp's first 32 x 64 gate and up boxes are issued before waiting for the MMAs
+      const int glu_col0 = t.n0 + half * (BN / 2);
+      uint8_t* bufG = epi_smem + (warp - 2) * C::EPI_BYTES / kEpiWarps;
+      uint8_t* bufU = bufG + kStageOutBytes;
+      const uint32_t ebar = bar_epi + 8 * (warp - 2);
+      auto glu_load = [&](int col) {   // tmD2 = saved gate_up seen as {I, rows, 2}
+        staging_free(lane);            // earlier stores out of these boxes have been read
+        if (lane == 0) {
+          mbar_arrive_expect_tx(ebar, 2 * kStageOutBytes);
+          tma_load_3d(smem_u32(bufG), &tmD2, ebar, col, row0, 0);
+          tma_load_3d(smem_u32(bufU), &tmD2, ebar, col, row0, 1);
+        }
+      };
+      if constexpr (TMA_EPI && EPI == EPI_GLU_BWD) {
+        if (glu_col0 < p.I) glu_load(glu_col0);
+      }
       if (!mbar_wait(bar_tfull + 8 * buf, (it >> 1) & 1, abort_flag, ST_WAIT_EPILOGUE)) break;
       __syncwarp();
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-      const long long row = static_cast<long long>(t.m0) + BM * static_cast<int>(cta_rank) + q * 32 + lane;
       const bool have_acc = t.nkb > 0;
 
-      if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32) {
+      if constexpr (TMA_EPI) {
+        // results are packed to bf16, staged per warp as 32 rows x 64 columns and written by TMA
+        // stores (which clip at the tensor's bounds, so no row or column masks are needed)
+        uint8_t* sbuf = bufG;   // this warp's staging box
+        const int grp = (p.sched == SCHED_GROUPED_K) ? t.g : 0;
+        if constexpr (EPI == EPI_STORE) {
+          constexpr int W = BN / 2;
+#pragma unroll 1
+          for (int c = half * W; c < (half + 1) * W; c += 64) {
+            if (t.n0 + c >= p.N) break;
+            uint32_t pk[32];
+#pragma unroll
+            for (int sub = 0; sub < 2; ++sub) {
+              uint32_t r[32];
+              if (have_acc) {
+                tmem_ld32(taddr + c + 32 * sub, r);
+                tmem_ld_wait();
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = 0u;
+              }
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                pk[16 * sub + i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+            }
+            staging_free(lane);
+            stage_row(sbuf, lane, pk);
+            store_box(&tmD, sbuf, lane, t.n0 + c, row0, grp);
+          }
+        } else if constexpr (EPI == EPI_SWIGLU) {
+          // accumulator columns [0,BN/2) = gate, [BN/2,BN) = up for I-columns [n0, n0+BN/2)
+          const int c = half * (BN / 4);
+          if (t.n0 + c < p.I) {
+            uint32_t og[32], ou[32], oh[32];
+#pragma unroll
+            for (int sub = 0; sub < 2; ++sub) {
+              uint32_t g[32], u[32];
+              tmem_ld32(taddr + c + 32 * sub, g);
+              tmem_ld32(taddr + BN / 2 + c + 32 * sub, u);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const uint32_t pg = pack_bf16x2(__uint_as_float(g[2 * i]), __uint_as_float(g[2 * i + 1]));
+                const uint32_t pu = pack_bf16x2(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]));
+                // the activation reads the bf16-rounded gate/up, as the reference's separate
+                // activation kernel does (kernels/sm75/moe.py:163-184)
+                const float2 gf = unpack_bf16x2(pg);
+                const float2 uf = unpack_bf16x2(pu);
+                const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
+                const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
+                og[16 * sub + i] = pg;
+                ou[16 * sub + i] = pu;
+                oh[16 * sub + i] = pack_bf16x2(gf.x * s0 * uf.x, gf.y * s1 * uf.y);
+              }
+            }
+            staging_free(lane);
+            stage_row(sbuf, lane, og);
+            store_box(&tmD, sbuf, lane, t.n0 + c, row0, 0);    // gate half of gate_up
+            staging_free(lane);
+            stage_row(sbuf, lane, ou);
+            store_box(&tmD, sbuf, lane, t.n0 + c, row0, 1);    // up half
+            staging_free(lane);
+            stage_row(sbuf, lane, oh);
+            store_box(&tmD2, sbuf, lane, t.n0 + c, row0, 0);   // inter
+          }
+        } else {  // EPI_GLU_BWD: accumulator = grad_inter columns [n0, n0+BN); this warp: 128 of them
+          constexpr int W = BN / 2;
+#pragma unroll 1
+          for (int ch = 0; ch < 2; ++ch) {
+            const int col = glu_col0 + 64 * ch;
+            if (col >= p.I) break;                       // warp-uniform
+            if (ch == 1) glu_load(col);
+            if (!mbar_wait(ebar, epi_phase, abort_flag, ST_WAIT_EPILOGUE)) break;
+            epi_phase ^= 1;
+#pragma unroll
+            for (int sb = 0; sb < 2; ++sb) {
+              uint32_t r[32];
+              tmem_ld32(taddr + half * W + 64 * ch + 32 * sb, r);
+              uint4 g4[4], u4[4];
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {              // this lane's row, swizzled 16-byte chunks
+                const int off = lane * 128 + (((4 * sb + v) ^ (lane & 7)) << 4);
+                g4[v] = *reinterpret_cast<const uint4*>(bufG + off);
+                u4[v] = *reinterpret_cast<const uint4*>(bufU + off);
+              }
+              tmem_ld_wait();
+              uint32_t og[16], ou[16];
+              glu_bwd32(r, g4, u4, og, ou);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {              // results replace the inputs in place
+                const int off = lane * 128 + (((4 * sb + v) ^ (lane & 7)) << 4);
+                *reinterpret_cast<uint4*>(bufG + off) = make_uint4(og[4 * v], og[4 * v + 1], og[4 * v + 2], og[4 * v + 3]);
+                *reinterpret_cast<uint4*>(bufU + off) = make_uint4(ou[4 * v], ou[4 * v + 1], ou[4 * v + 2], ou[4 * v + 3]);
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&tmD, smem_u32(bufG), col, row0, 0);   // grad_gate
+              tma_store_3d(&tmD, smem_u32(bufU), col, row0, 1);   // grad_up
+              bulk_commit_group();
+            }
+          }
+        }
+      } else if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32) {
         const bool row_ok = (p.sched == SCHED_GROUPED_M) || (row < p.M);
         const long long base = (p.sched == SCHED_GROUPED_K ? t.g * p.d_group_stride : 0) +
                                row * p.ldd + t.n0;
@@ -368,8 +561,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 // activation kernel does (kernels/sm75/moe.py:163-184)
                 const float2 gf = unpack_bf16x2(og[h]);
                 const float2 uf = unpack_bf16x2(ou[h]);
-                const float s0 = 1.0f / (1.0f + __expf(-gf.x));
-                const float s1 = 1.0f / (1.0f + __expf(-gf.y));
+                const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
+                const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
                 oh[h] = pack_bf16x2(gf.x * s0 * uf.x, gf.y * s1 * uf.y);
               }
               *reinterpret_cast<uint4*>(gu + col) = make_uint4(og[0], og[1], og[2], og[3]);
@@ -423,8 +616,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                   // grad_inter is rounded to bf16 first: the reference materialises it in bf16
                   const float go0 = bf16_round(__uint_as_float(r[v * 8 + 2 * h]));
                   const float go1 = bf16_round(__uint_as_float(r[v * 8 + 2 * h + 1]));
-                  const float s0 = 1.0f / (1.0f + __expf(-gf.x));
-                  const float s1 = 1.0f / (1.0f + __expf(-gf.y));
+                  const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
+                  const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
                   const float d0 = s0 * (1.0f + gf.x * (1.0f - s0));
                   const float d1 = s1 * (1.0f + gf.y * (1.0f - s1));
                   og[h] = pack_bf16x2(go0 * uf.x * d0, go1 * uf.y * d1);
@@ -443,6 +636,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if constexpr (CTAS == 2) mbar_arrive_cluster(tempty_leader + 8 * buf);
         else mbar_arrive(bar_tempty + 8 * buf);
       }
+    }
+    if constexpr (TMA_EPI) {
+      if (lane == 0) bulk_wait_all();   // every TMA store of this warp has completed
     }
   }
 
@@ -505,9 +701,9 @@ static int make_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t 
 }
 
 template <int BN, int EPI, int CTAS>
-static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int max_tiles,
-                  cudaStream_t stream) {
-  using C = Cfg<BN, CTAS>;
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const CUtensorMap& tmD2,
+                  const GemmParams& p, int max_tiles, cudaStream_t stream) {
+  using C = Cfg<BN, CTAS, epi_warp_bytes<BN, EPI>()>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -530,7 +726,7 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmPara
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = (CTAS > 1) ? 1 : 0;
-  B200_CUDA(cudaLaunchKernelEx(&cfg, gemm_kernel<BN, EPI, CTAS>, tmA, tmB, p));
+  B200_CUDA(cudaLaunchKernelEx(&cfg, gemm_kernel<BN, EPI, CTAS>, tmA, tmB, tmD, tmD2, p));
   return 0;
 }
 
@@ -574,23 +770,40 @@ static int pick_bn(long long n) {
   return 128;
 }
 
+// d1 / d2 describe the bf16 outputs as {columns, rows, groups} tensors for the TMA-store epilogue
+// (d2 = the SwiGLU `inter` output); they are ignored by the kernels that store directly.
 template <int EPI>
-static int dispatch_bn(int bn, const Operand& A, const Operand& B, GemmParams& p, int max_tiles,
-                       cudaStream_t stream) {
+static int dispatch_bn(int bn, const Operand& A, const Operand& B, const Operand* d1, const Operand* d2,
+                       GemmParams& p, int max_tiles, cudaStream_t stream) {
   const bool pair = (bn == 256) && (p.sched != SCHED_DENSE) && pairs_enabled();
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmD, tmD2;
   int rc = encode_operand(&tmA, A, BM);
   if (rc) return rc;
   // rows of B one TMA box brings in: half a tile for SwiGLU (gate and up halves) and for pairs
   const int b_rows = (EPI == EPI_SWIGLU || pair) ? bn / 2 : bn;
   rc = encode_operand(&tmB, B, b_rows);
   if (rc) return rc;
-  if (pair) return launch<256, EPI, 2>(tmA, tmB, p, max_tiles > 0 ? (max_tiles + 1) / 2 : 0, stream);
+  tmD = tmA;
+  tmD2 = tmA;
+  if (bn == 256 && EPI != EPI_STORE_F32) {
+    if (d1 == nullptr) {
+      set_error("internal: output description missing");
+      return B200MOE_E_UNSUPPORTED;
+    }
+    rc = encode_operand(&tmD, *d1, 32);   // box {64 columns, 32 rows}
+    if (rc) return rc;
+    if (d2 != nullptr) {
+      rc = encode_operand(&tmD2, *d2, 32);
+      if (rc) return rc;
+    }
+  }
+  if (pair) return launch<256, EPI, 2>(tmA, tmB, tmD, tmD2, p, max_tiles > 0 ? (max_tiles + 1) / 2 : 0, stream);
   switch (bn) {
-    case 256: return launch<256, EPI, 1>(tmA, tmB, p, max_tiles, stream);
-    case 128: return launch<128, EPI, 1>(tmA, tmB, p, max_tiles, stream);
+    case 256: return launch<256, EPI, 1>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
+    case 128: return launch<128, EPI, 1>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
     default:
-      if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32) return launch<64, EPI, 1>(tmA, tmB, p, max_tiles, stream);
+      if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32)
+        return launch<64, EPI, 1>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
       set_error("tile width %d not built for this epilogue", bn);
       return B200MOE_E_UNSUPPORTED;
   }
@@ -621,7 +834,8 @@ int b200moe_gemm_nt(const void* A, const void* B, void* D, int64_t M, int64_t N,
   p.sched = SCHED_DENSE; p.M = (int)M; p.N = (int)N; p.K = (int)K; p.num_groups = 1;
   p.D = D; p.ldd = N; p.status = status;
   const int bn = pick_bn(N);
-  return dispatch_bn<EPI_STORE>(bn, a, b, p, (int)(ceil_div(M, BM) * ceil_div(N, bn)), (cudaStream_t)stream);
+  Operand d{D, 0, M, N, N, 1, M * N};
+  return dispatch_bn<EPI_STORE>(bn, a, b, &d, nullptr, p, (int)(ceil_div(M, BM) * ceil_div(N, bn)), (cudaStream_t)stream);
 }
 
 int b200moe_gemm_nn(const void* A, const void* B, void* D, int64_t M, int64_t N, int64_t K, int32_t* status,
@@ -636,7 +850,8 @@ int b200moe_gemm_nn(const void* A, const void* B, void* D, int64_t M, int64_t N,
   p.sched = SCHED_DENSE; p.b_mn = 1; p.M = (int)M; p.N = (int)N; p.K = (int)K; p.num_groups = 1;
   p.D = D; p.ldd = N; p.status = status;
   const int bn = pick_bn(N);
-  return dispatch_bn<EPI_STORE>(bn, a, b, p, (int)(ceil_div(M, BM) * ceil_div(N, bn)), (cudaStream_t)stream);
+  Operand d{D, 0, M, N, N, 1, M * N};
+  return dispatch_bn<EPI_STORE>(bn, a, b, &d, nullptr, p, (int)(ceil_div(M, BM) * ceil_div(N, bn)), (cudaStream_t)stream);
 }
 
 int b200moe_gemm_tn_splitk(const void* A, const void* B, float* P, int64_t M, int64_t N, int64_t K,
@@ -655,7 +870,7 @@ int b200moe_gemm_tn_splitk(const void* A, const void* B, float* P, int64_t M, in
   p.num_groups = (int)slices; p.k_chunk = (int)k_chunk; p.poffs = nullptr;
   p.D = P; p.ldd = N; p.d_group_stride = M * N; p.status = status;
   const int bn = pick_bn(N);
-  return dispatch_bn<EPI_STORE_F32>(bn, a, b, p, (int)(slices * ceil_div(M, BM) * ceil_div(N, bn)),
+  return dispatch_bn<EPI_STORE_F32>(bn, a, b, nullptr, nullptr, p, (int)(slices * ceil_div(M, BM) * ceil_div(N, bn)),
                                     (cudaStream_t)stream);
 }
 
@@ -686,7 +901,9 @@ int b200moe_expert_gate_up_swiglu(const void* x_s, const void* gate_up_proj, con
   p.sched = SCHED_GROUPED_M; p.N = (int)I; p.K = (int)H; p.num_groups = E;
   p.tile_expert = tile_expert; p.poffs = poffs; p.D = gate_up; p.aux = inter; p.I = (int)I; p.status = status;
   const int bn = (I >= 128) ? 256 : 128;   // tile covers bn/2 intermediate columns
-  return dispatch_bn<EPI_SWIGLU>(bn, a, b, p, 0, (cudaStream_t)stream);
+  Operand d1{gate_up, 0, rows_cap, I, 2 * I, 2, I};       // {I, rows, 2}: group 0 = gate half, 1 = up half
+  Operand d2{inter, 0, rows_cap, I, I, 1, rows_cap * I};
+  return dispatch_bn<EPI_SWIGLU>(bn, a, b, &d1, &d2, p, 0, (cudaStream_t)stream);
 }
 
 int b200moe_expert_down(const void* inter, const void* down_proj, const int32_t* tile_expert, const int32_t* poffs,
@@ -701,7 +918,8 @@ int b200moe_expert_down(const void* inter, const void* down_proj, const int32_t*
   GemmParams p{};
   p.sched = SCHED_GROUPED_M; p.N = (int)H; p.K = (int)I; p.num_groups = E;
   p.tile_expert = tile_expert; p.poffs = poffs; p.D = eo; p.ldd = H; p.status = status;
-  return dispatch_bn<EPI_STORE>(pick_bn(H) == 64 ? 128 : pick_bn(H), a, b, p, 0, (cudaStream_t)stream);
+  Operand d{eo, 0, rows_cap, H, H, 1, rows_cap * H};
+  return dispatch_bn<EPI_STORE>(pick_bn(H) == 64 ? 128 : pick_bn(H), a, b, &d, nullptr, p, 0, (cudaStream_t)stream);
 }
 
 int b200moe_expert_down_dgrad_glu(const void* grad_eo, const void* down_proj, const void* gate_up,
@@ -719,7 +937,9 @@ int b200moe_expert_down_dgrad_glu(const void* grad_eo, const void* down_proj, co
   p.tile_expert = tile_expert; p.poffs = poffs; p.D = grad_gate_up; p.aux = const_cast<void*>(gate_up);
   p.I = (int)I; p.status = status;
   const int bn = pick_bn(I) == 64 ? 128 : pick_bn(I);
-  return dispatch_bn<EPI_GLU_BWD>(bn, a, b, p, 0, (cudaStream_t)stream);
+  Operand d{grad_gate_up, 0, rows_cap, I, 2 * I, 2, I};   // {I, rows, 2}: grad_gate half, grad_up half
+  Operand d2{gate_up, 0, rows_cap, I, 2 * I, 2, I};       // the saved forward gate_up, same view (input)
+  return dispatch_bn<EPI_GLU_BWD>(bn, a, b, &d, &d2, p, 0, (cudaStream_t)stream);
 }
 
 int b200moe_expert_gate_up_dgrad(const void* grad_gate_up, const void* gate_up_proj, const int32_t* tile_expert,
@@ -734,7 +954,8 @@ int b200moe_expert_gate_up_dgrad(const void* grad_gate_up, const void* gate_up_p
   GemmParams p{};
   p.sched = SCHED_GROUPED_M; p.b_mn = 1; p.N = (int)H; p.K = (int)(2 * I); p.num_groups = E;
   p.tile_expert = tile_expert; p.poffs = poffs; p.D = grad_x_s; p.ldd = H; p.status = status;
-  return dispatch_bn<EPI_STORE>(pick_bn(H) == 64 ? 128 : pick_bn(H), a, b, p, 0, (cudaStream_t)stream);
+  Operand d{grad_x_s, 0, rows_cap, H, H, 1, rows_cap * H};
+  return dispatch_bn<EPI_STORE>(pick_bn(H) == 64 ? 128 : pick_bn(H), a, b, &d, nullptr, p, 0, (cudaStream_t)stream);
 }
 
 int b200moe_expert_wgrad(const void* A, const void* B, const int32_t* poffs, int64_t rows_cap, int E, int64_t Na,
@@ -751,7 +972,8 @@ int b200moe_expert_wgrad(const void* A, const void* B, const int32_t* poffs, int
   p.sched = SCHED_GROUPED_K; p.a_mn = 1; p.b_mn = 1; p.M = (int)Na; p.N = (int)Nb; p.K = (int)rows_cap;
   p.num_groups = E; p.poffs = poffs; p.D = out; p.ldd = Nb; p.d_group_stride = Na * Nb; p.status = status;
   const int bn = pick_bn(Nb);
-  return dispatch_bn<EPI_STORE>(bn, a, b, p, (int)std::min<long long>(1 << 30, E * ceil_div(Na, BM) * ceil_div(Nb, bn)),
+  Operand d{out, 0, Na, Nb, Nb, E, Na * Nb};
+  return dispatch_bn<EPI_STORE>(bn, a, b, &d, nullptr, p, (int)std::min<long long>(1 << 30, E * ceil_div(Na, BM) * ceil_div(Nb, bn)),
                                 (cudaStream_t)stream);
 }
 
