@@ -38,16 +38,23 @@ HEADLINE = dict(T=16384, H=2048, E=64, I=1408, k=6)
 PROFILE = dict(T=4096, H=2048, E=16, I=1408, k=6)
 # expert-parallel configuration: 65536 global tokens, 256 experts sharded over the ranks
 EP5 = dict(T=65536, H=7168, E=256, I=2048, k=8)
+# MXFP8 configuration (e4m3 + E8M0 block-32 scales), one GPU
+MXFP8 = dict(T=32768, H=4096, E=8, I=14336, k=2)
 METRIC = "moe_layer_fwd_bwd_tokens_per_s"
 
 
-def _peaks():
+def _peaks(precision="bf16"):
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        return dict(hbm_gbs=p["hbm_gbs"], tflops=p.get("bf16_tflops_sustained", p["bf16_tflops"]),
-                    source="measured (MEASURED_PEAKS.json, sustained bf16)")
-    return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback (6.65 TB/s, 1.4 PFLOP/s sustained)")
+        d = dict(hbm_gbs=p["hbm_gbs"], tflops=p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                 source="measured (MEASURED_PEAKS.json, sustained bf16)")
+    else:
+        d = dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback (6.65 TB/s, 1.4 PFLOP/s sustained)")
+    if precision == "mxfp8":   # no fp8 measurement exists: the fp8 tensor rate is twice the bf16 rate
+        d["tflops"] *= 2.0
+        d["source"] = "2 x " + d["source"] + " (fp8 dense rate = 2 x bf16; no fp8 peak was measured)"
+    return d
 
 
 class ClockSampler:
@@ -62,7 +69,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -103,9 +110,12 @@ def _workload(n_gpus, which="headline"):
     if which == "ep5":
         w = dict(EP5)
         w["T"] = EP5["T"] // n_gpus
+    elif which == "mxfp8":
+        w = dict(MXFP8)
     else:
         w = dict(HEADLINE if which == "headline" else PROFILE)
-    w["name"] = "bf16 MoE layer T={T}/GPU H={H} E={E} I={I} top{k} fwd+bwd".format(**w)
+    w["precision"] = "mxfp8" if which == "mxfp8" else "bf16"
+    w["name"] = (w["precision"] + " MoE layer T={T}/GPU H={H} E={E} I={I} top{k} fwd+bwd").format(**w)
     w["parallelism"] = "single GPU" if n_gpus == 1 else f"expert parallel ep{n_gpus} (E/{n_gpus} experts per GPU, NCCL all-to-all)"
     return w
 
@@ -114,9 +124,11 @@ def _make_layer(pkg, w, device, seed, world):
     torch.manual_seed(seed)
     with torch.device(device):      # build the (large) expert stacks directly on the GPU
         if world > 1:
-            layer = pkg.ExpertParallelMoELayer(w["H"], w["I"], w["E"], top_k=w["k"])
+            layer = pkg.ExpertParallelMoELayer(w["H"], w["I"], w["E"], top_k=w["k"],
+                                               overlap_chunks=int(os.environ.get("B200MOE_EP_CHUNKS", "2")),
+                                               reserved_sms=int(os.environ.get("B200MOE_EP_RESERVED_SMS", "16")))
         else:
-            layer = pkg.MoELayer(w["H"], w["I"], w["E"], top_k=w["k"])
+            layer = pkg.MoELayer(w["H"], w["I"], w["E"], top_k=w["k"], precision=w["precision"])
     return layer.to(torch.bfloat16)
 
 
@@ -217,12 +229,14 @@ def run_ours(args):
         if dist is not None:
             dist.destroy_process_group()
         return
-    peaks = _peaks()
+    peaks = _peaks(w["precision"])
     M = T * k
     flops = {  # algorithmic FLOPs per launch (padding rows not counted)
         "expert_gate_up_swiglu": 2.0 * M * H * 2 * I, "expert_down": 2.0 * M * I * H,
         "expert_down_dgrad_glu": 2.0 * M * H * I, "expert_gate_up_dgrad": 2.0 * M * 2 * I * H,
         "expert_wgrad": (2.0 * M * H * I + 2.0 * M * 2 * I * H) / 2.0,   # two launches per step, averaged
+        "mxfp8_expert_gemm": 12.0 * M * H * I / 4.0,                     # four launches per step, averaged
+        "mxfp8_expert_wgrad": 6.0 * M * H * I / 2.0,
     }
     kernels = {}
     for name, (ms, n) in sorted(per_op.items(), key=lambda kv: -kv[1][0]):
@@ -239,7 +253,7 @@ def run_ours(args):
     line = {
         "metric": METRIC, "value": round(T * world / (ms_step * 1e-3), 1), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": n_warm, "ms_per_step": round(ms_step, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["precision"], "data": "synthetic",
         "config": {"workload": w["name"], "tokens_per_gpu": T, "d_model": H, "experts": E, "d_ff": I, "top_k": k,
                    "parallelism": w["parallelism"],
                    "l2": "no flush: the working set (expert weights + activations, several GB) exceeds the 126 MB L2"},
@@ -302,11 +316,11 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="headline", choices=["headline", "profile", "ep5"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "profile", "ep5", "mxfp8"],
                     help="profile = small case for profiler captures (not a benchmark number)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -54,6 +54,10 @@ const char* b200moe_status_string(int status_word);
 /* host: worst-case number of padded rows for M routed rows over E experts */
 int64_t b200moe_padded_rows_cap(int64_t M, int E);
 
+/* host: keep `n` SMs free of the persistent GEMM kernels (process-wide, default 0) so that
+ * communication kernels queued on another stream can run beside them.  No reference counterpart. */
+int b200moe_set_reserved_sms(int n);
+
 /* ---- router --------------------------------------------------------------------------------- */
 /* Replaces _router_epilogue_fwd_kernel (kernels/sm75/router.py:39-83, launcher :129-148):
  * sigmoid, +bias for selection only, k rounds of lowest-index argmax with knock-out, unbiased
@@ -143,10 +147,40 @@ int b200moe_expert_gate_up_dgrad(const void* grad_gate_up, const void* gate_up_p
                                  int64_t rows_cap, int E, int64_t H, int64_t I, void* grad_x_s,
                                  int32_t* status, b200moe_stream_t stream);
 /* Replaces _grouped_wgrad / ge.t() @ it (kernels/sm75/moe.py:556-561, :808, :821):
- * out[e] (Na,Nb) bf16 = A[rows of e]^T * B[rows of e]; experts with no rows get zeros. */
-int b200moe_expert_wgrad(const void* A, const void* B, const int32_t* poffs, int64_t rows_cap,
-                         int E, int64_t Na, int64_t Nb, void* out, int32_t* status,
+ * out[e] (Na,Nb) bf16 = A[rows of e]^T * B[rows of e]; experts with no rows get zeros.
+ * counts (E, nullable): live rows per expert; when given, the all-zero pad blocks are skipped. */
+int b200moe_expert_wgrad(const void* A, const void* B, const int32_t* poffs, const int32_t* counts,
+                         int64_t rows_cap, int E, int64_t Na, int64_t Nb, void* out, int32_t* status,
                          b200moe_stream_t stream);
+
+/* ---- MXFP8 (e4m3 elements, E8M0 scale per 32 elements along K) ---------------------------------
+ * The reference has no MXFP8 path; these follow the OCP MX convention: scale exponent =
+ * floor(log2(amax)) - 8, elements rounded to nearest even and saturated at +-448.
+ * Scales are stored as 512-byte atoms per (128 rows x 128 k): byte (row%32)*16 + ((row%128)/32)*4 +
+ * (k/32)%4, atoms ordered row-block major, k-chunk minor; b200moe_mxfp8_sf_bytes gives the size. */
+size_t b200moe_mxfp8_sf_bytes(int64_t rows, int64_t K);
+/* x (R,C) bf16 -> q (R,C) e4m3 + scales, blocks along C.  interleave_I > 0: x is a stack of (2I,C)
+ * gate|up matrices and output rows are re-ordered in groups of 64 gate rows then 64 up rows. */
+int b200moe_mxfp8_quant_rows(const void* x, int64_t R, int64_t C, int64_t interleave_I, void* q, void* sf,
+                             b200moe_stream_t stream);
+/* x (G,R,C) bf16 -> q (G,C,R) e4m3 + scales, blocks along R (R % 32 == 0, C % 128 == 0 when G > 1). */
+int b200moe_mxfp8_quant_transpose(const void* x, int64_t G, int64_t R, int64_t C, void* q, void* sf,
+                                  b200moe_stream_t stream);
+/* D (M,N) bf16 = dequant(A)(M,K) * dequant(B)(N,K)^T on tcgen05 block-scaled MMAs; K % 128 == 0. */
+int b200moe_mxfp8_gemm_nt(const void* Aq, const void* Asf, const void* Bq, const void* Bsf, void* D,
+                          int64_t M, int64_t N, int64_t K, int32_t* status, b200moe_stream_t stream);
+/* Grouped expert GEMM over padded rows; B is an (E*N, K) stack (N % 128 == 0).  epilogue: 0 = bf16
+ * store, 1 = SwiGLU (N = 2I, weight rows 64-interleaved, D = gate_up, aux = inter), 2 = GLU backward
+ * (N = I, aux = saved gate_up, D = grad_gate_up).  Same roles as the bf16 entry points above. */
+int b200moe_mxfp8_expert_gemm(int epilogue, const void* Aq, const void* Asf, const void* Bq,
+                              const void* Bsf, const int32_t* tile_expert, const int32_t* poffs,
+                              int64_t rows_cap, int E, int64_t N, int64_t K, int64_t I, void* D, void* aux,
+                              int32_t* status, b200moe_stream_t stream);
+/* Weight gradient: out[e] (Na,Nb) bf16 = At[:, rows of e] * Bt[:, rows of e]^T, At (Na, rows_cap) and
+ * Bt (Nb, rows_cap) quantised along the token rows (b200moe_mxfp8_quant_transpose). */
+int b200moe_mxfp8_expert_wgrad(const void* Atq, const void* Atsf, const void* Btq, const void* Btsf,
+                               const int32_t* poffs, const int32_t* counts, int64_t rows_cap, int E,
+                               int64_t Na, int64_t Nb, void* out, int32_t* status, b200moe_stream_t stream);
 
 /* ---- combine -------------------------------------------------------------------------------- */
 /* Replaces _combine_scatter_kernel / index_add_ (kernels/sm75/moe.py:673-682, :593-595):

@@ -1,0 +1,91 @@
+"""GPU: MXFP8 quantisers (bit-exact against the CPU quantise oracle) and the MXFP8 expert pipeline
+(forward + backward within 5e-2 relative L2 of the quantise->dequantise oracle)."""
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+from oracle import mxfp8_oracle as Q
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TOL_MX = 5e-2       # stated gate for the MXFP8 path
+
+
+def test_quant_rows_bit_exact(pkg):
+    g = torch.Generator().manual_seed(0)
+    x = (torch.randn(333, 384, generator=g) * torch.logspace(-4, 4, 333)[:, None]).to(torch.bfloat16)
+    x[5] = 0                                              # an all-zero row
+    x[7, :32] = torch.tensor(500.0).to(torch.bfloat16)    # saturating block
+    q, sf = pkg.ops.mxfp8_quant_rows(x.to(DEV))
+    cq, cs = Q.quantise(x.float())
+    assert torch.equal(q.cpu(), cq)
+    assert torch.equal(sf.cpu(), Q.sf_atoms(cs))
+
+
+def test_quant_rows_interleave_and_transpose_bit_exact(pkg):
+    g = torch.Generator().manual_seed(1)
+    E, I, H = 3, 128, 256
+    w = (torch.randn(E, 2 * I, H, generator=g) * 0.02).to(torch.bfloat16)
+    q, sf = pkg.ops.mxfp8_quant_rows(w.view(E * 2 * I, H).to(DEV), interleave_I=I)
+    perm = torch.cat([torch.cat([torch.arange(j, j + 64), I + torch.arange(j, j + 64)]) for j in range(0, I, 64)])
+    wi = w[:, perm, :].reshape(E * 2 * I, H)
+    cq, cs = Q.quantise(wi.float())
+    assert torch.equal(q.cpu(), cq) and torch.equal(sf.cpu(), Q.sf_atoms(cs))
+    qt, sft = pkg.ops.mxfp8_quant_transpose(w.to(DEV))
+    wt = w.float().transpose(1, 2).contiguous()
+    cq, cs = Q.quantise(wt)
+    assert torch.equal(qt.cpu(), cq)
+    assert torch.equal(sft.cpu(), Q.sf_atoms(cs.reshape(-1, cs.shape[-1])))
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 264, 1024), (1000, 2048, 512), (64, 72, 256)])
+def test_mxfp8_gemm_matches_dequantised_product(pkg, M, N, K):
+    g = torch.Generator().manual_seed(2)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    b = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    aq, asf = pkg.ops.mxfp8_quant_rows(a.to(DEV))
+    bq, bsf = pkg.ops.mxfp8_quant_rows(b.to(DEV))
+    d = pkg.ops.mxfp8_gemm_nt(aq, asf, bq, bsf)
+    pkg.check_status()
+    ref = Q.qdq(a.float()) @ Q.qdq(b.float()).t()
+    assert O.rel_l2(d.float().cpu(), ref) < 4e-3          # identical operands, bf16 output rounding only
+
+
+@pytest.mark.parametrize("T,H,E,I,k", [(1024, 256, 8, 256, 2), (1536, 384, 6, 128, 3)])
+def test_moe_mxfp8_forward_backward(pkg, T, H, E, I, k):
+    inp = O.make_inputs(T, H, E, I, k, seed=51, bias_std=0.01, dtype=torch.bfloat16)
+    idx, w, _, _ = O.mlp_router_fwd(inp["x"], inp["gate_weight"], inp["bias"], k)
+    lv = dict(hidden=inp["x"].to(DEV).requires_grad_(True), wt=w.to(DEV).requires_grad_(True),
+              gu=inp["gate_up"].to(DEV).requires_grad_(True), dn=inp["down"].to(DEV).requires_grad_(True))
+    codes = torch.zeros(E, dtype=torch.int32, device=DEV)
+    out = pkg.moe_mxfp8(lv["hidden"], idx.to(DEV), lv["wt"], lv["gu"], lv["dn"], codes)
+    (out.float() * inp["grad_out"].to(DEV).float()).sum().backward()
+    pkg.check_status()
+    # the quantise -> dequantise oracle on the same bf16 inputs
+    hid = inp["x"].float().requires_grad_(True)
+    wt = w.clone().requires_grad_(True)
+    gu = inp["gate_up"].float().requires_grad_(True)
+    dn = inp["down"].float().requires_grad_(True)
+    ref = Q.moe_experts_mxfp8(hid, idx, wt, gu, dn)
+    (ref * inp["grad_out"].float()).sum().backward()
+    errs = dict(out=O.rel_l2(out.float().cpu(), ref.detach()),
+                grad_x=O.rel_l2(lv["hidden"].grad.float().cpu(), hid.grad),
+                grad_w=O.rel_l2(lv["wt"].grad.float().cpu(), wt.grad),
+                grad_gate_up=O.rel_l2(lv["gu"].grad.float().cpu(), gu.grad),
+                grad_down=O.rel_l2(lv["dn"].grad.float().cpu(), dn.grad))
+    print("mxfp8 vs quantised oracle:", {k_: f"{v:.3e}" for k_, v in errs.items()})
+    for name, e in errs.items():
+        assert e < TOL_MX, (name, e)
+    # for the record: distance to the unquantised fp32 block
+    full = O.moe_experts(inp["x"].float(), idx, w, inp["gate_up"].float(), inp["down"].float())
+    assert O.rel_l2(out.float().cpu(), full) < 0.1
+
+
+def test_mxfp8_rejects_unaligned_width(pkg):
+    x = torch.zeros(8, 192, dtype=torch.bfloat16, device=DEV)
+    idx = torch.zeros(8, 1, dtype=torch.int64, device=DEV)
+    w = torch.ones(8, 1, device=DEV)
+    gu = torch.zeros(2, 256, 192, dtype=torch.bfloat16, device=DEV)
+    dn = torch.zeros(2, 192, 128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError, match="multiples of 128"):
+        pkg.moe_mxfp8(x, idx, w, gu, dn, torch.zeros(2, dtype=torch.int32, device=DEV))

@@ -6,9 +6,10 @@ from ._lib import build, check_status, lib, LIB_PATH, EXPORTED
 from .moe import moe, moe_grouped, moe_per_expert, GROUPED_MIN_TOKENS
 from .router import fused_mlp_router, FusedMLPRouter, router_bias_update
 from .layer import MoELayer
+from .mxfp8 import moe_mxfp8
 from . import ops
 from .ops import TILE_M
 from .ep import ExpertParallelMoELayer, ep_moe
 
 __all__ = ["moe", "moe_grouped", "moe_per_expert", "GROUPED_MIN_TOKENS", "fused_mlp_router",
-           "FusedMLPRouter", "router_bias_update", "MoELayer", "ExpertParallelMoELayer", "ep_moe", "ops", "build", "lib", "check_status"]
+           "FusedMLPRouter", "router_bias_update", "MoELayer", "moe_mxfp8", "ExpertParallelMoELayer", "ep_moe", "ops", "build", "lib", "check_status"]

@@ -28,6 +28,7 @@ _SIGNATURES = {
     "b200moe_last_error_string": (ctypes.c_char_p, []),
     "b200moe_status_string": (ctypes.c_char_p, [c_int]),
     "b200moe_padded_rows_cap": (c_int64, [c_int64, c_int]),
+    "b200moe_set_reserved_sms": (c_int, [c_int]),
     "b200moe_router_topk_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_float,
                                         c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200moe_router_topk_bwd": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
@@ -47,7 +48,14 @@ _SIGNATURES = {
     "b200moe_expert_down": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
     "b200moe_expert_down_dgrad_glu": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
     "b200moe_expert_gate_up_dgrad": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
-    "b200moe_expert_wgrad": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
+    "b200moe_expert_wgrad": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
+    "b200moe_mxfp8_sf_bytes": (c_size_t, [c_int64, c_int64]),
+    "b200moe_mxfp8_quant_rows": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "b200moe_mxfp8_quant_transpose": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "b200moe_mxfp8_gemm_nt": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_void_p, c_void_p]),
+    "b200moe_mxfp8_expert_gemm": (c_int, [c_int] + [c_void_p] * 6 + [c_int64, c_int, c_int64, c_int64, c_int64] +
+                                  [c_void_p] * 4),
+    "b200moe_mxfp8_expert_wgrad": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
     "b200moe_combine": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64, c_void_p, c_void_p]),
     "b200moe_combine_bwd": (c_int, [c_void_p] * 5 + [c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
 }

@@ -1,6 +1,7 @@
 // Library-wide host helpers: version, thread-local error text, status decoding, device properties.
 #include <stdarg.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -33,9 +34,26 @@ int num_sms() {
   return n;
 }
 
+static std::atomic<int> g_reserved_sms{0};
+
+int gemm_cta_budget() {
+  int n = num_sms() - g_reserved_sms.load(std::memory_order_relaxed);
+  n &= ~1;                      // pair kernels launch clusters of two
+  return n < 2 ? 2 : n;
+}
+
 }  // namespace b200moe
 
 extern "C" {
+
+int b200moe_set_reserved_sms(int n) {
+  if (n < 0 || n >= b200moe::num_sms()) {
+    b200moe::set_error("set_reserved_sms: %d is outside [0, %d)", n, b200moe::num_sms());
+    return B200MOE_E_BAD_SHAPE;
+  }
+  b200moe::g_reserved_sms.store(n, std::memory_order_relaxed);
+  return 0;
+}
 
 const char* b200moe_version(void) { return "b200moe 0.1 (sm_100a)"; }
 

@@ -21,6 +21,7 @@ enum : int {
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
 int num_sms();
+int gemm_cta_budget();   // CTAs a persistent GEMM may occupy (num_sms() minus the reserved SMs)
 
 #define B200_CHECK_ARG(cond, code, ...)  \
   do {                                   \

@@ -1,0 +1,167 @@
+// Pieces shared by the bf16 and the MXFP8 GEMM translation units: schedules, tile decoding,
+// epilogue math, tensor-map encoding.
+#pragma once
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200moe {
+
+enum : int { SCHED_DENSE = 0, SCHED_GROUPED_M = 1, SCHED_GROUPED_K = 2 };
+enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_GLU_BWD = 2, EPI_STORE_F32 = 3 };
+
+constexpr int BM = 128;  // rows per CTA = TMEM lanes
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpiWarps;
+
+struct GemmParams {
+  int sched;
+  int a_mn, b_mn;        // 1 = operand is MN-major
+  int M;                 // DENSE: rows of D; GROUPED_K: rows of D[e] (= MN extent of A)
+  int N;                 // columns of D (SwiGLU: I)
+  int K;                 // reduction length (DENSE, GROUPED_M); total rows (GROUPED_K by chunks)
+  int num_groups;        // experts (GROUPED_M/K) or K-chunks
+  int k_chunk;           // GROUPED_K without poffs: rows per chunk (multiple of 64)
+  const int* tile_expert;  // GROUPED_M: expert of each B200MOE_TILE_M-row tile
+  const int* poffs;        // (num_groups+1) padded row offsets, multiples of B200MOE_TILE_M
+  const int* counts;       // GROUPED_K, optional: live rows per group (pad rows past them are zero)
+  void* D;
+  long long ldd;
+  long long d_group_stride;  // GROUPED_K: elements between D[e] and D[e+1]
+  void* aux;                 // SwiGLU: inter (rows, I); GLU_BWD: saved gate_up (rows, 2I)
+  int I;
+  int* status;
+};
+
+struct Tile {
+  int m0, n0, g, k0, nkb;
+};
+
+__device__ __forceinline__ int total_tiles(const GemmParams& p, int TN, int TM) {
+  const int nt = (p.N + TN - 1) / TN;
+  if (p.sched == SCHED_DENSE) return ((p.M + TM - 1) / TM) * nt;
+  if (p.sched == SCHED_GROUPED_M) return (p.poffs[p.num_groups] / TM) * nt;
+  return ((p.M + TM - 1) / TM) * nt * p.num_groups;
+}
+
+__device__ __forceinline__ Tile get_tile(const GemmParams& p, int tile, int TN, int TM, int BK = 64) {
+  Tile t;
+  const int nt = (p.N + TN - 1) / TN;
+  if (p.sched == SCHED_GROUPED_K) {
+    const int mt = (p.M + TM - 1) / TM;
+    const int per = mt * nt;
+    t.g = tile / per;
+    const int r = tile - t.g * per;
+    t.m0 = (r / nt) * TM;
+    t.n0 = (r % nt) * TN;
+    int kb, ke;
+    if (p.poffs != nullptr) {
+      kb = p.poffs[t.g];
+      ke = (p.counts != nullptr) ? kb + p.counts[t.g] : p.poffs[t.g + 1];   // skip all-zero k-blocks
+    } else {
+      kb = t.g * p.k_chunk;
+      ke = min(p.K, kb + p.k_chunk);
+    }
+    t.k0 = kb;
+    t.nkb = (ke - kb + BK - 1) / BK;
+  } else {
+    const int mi = tile / nt;
+    t.m0 = mi * TM;
+    t.n0 = (tile - mi * nt) * TN;
+    t.g = (p.sched == SCHED_GROUPED_M) ? p.tile_expert[t.m0 / B200MOE_TILE_M] : 0;
+    t.k0 = 0;
+    t.nkb = (p.K + BK - 1) / BK;
+  }
+  return t;
+}
+
+__device__ __forceinline__ uint4 pack8(const uint32_t* r) {
+  uint4 o;
+  o.x = pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1]));
+  o.y = pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3]));
+  o.z = pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5]));
+  o.w = pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7]));
+  return o;
+}
+
+// grad_gate = gi*up*sig(g)*(1+g*(1-sig(g))), grad_up = gi*g*sig(g) for 32 columns; gi (fp32 accumulator)
+// is rounded to bf16 first because the reference materialises grad_inter in bf16
+__device__ __forceinline__ void glu_bwd32(const uint32_t (&r)[32], const uint4 (&g)[4], const uint4 (&u)[4],
+                                          uint32_t* og, uint32_t* ou) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const uint32_t gw[4] = {g[v].x, g[v].y, g[v].z, g[v].w};
+    const uint32_t uw[4] = {u[v].x, u[v].y, u[v].z, u[v].w};
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      const float2 gf = unpack_bf16x2(gw[h]);
+      const float2 uf = unpack_bf16x2(uw[h]);
+      const float go0 = bf16_round(__uint_as_float(r[v * 8 + 2 * h]));
+      const float go1 = bf16_round(__uint_as_float(r[v * 8 + 2 * h + 1]));
+      const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
+      const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
+      const float d0 = s0 * (1.0f + gf.x * (1.0f - s0));
+      const float d1 = s1 * (1.0f + gf.y * (1.0f - s1));
+      og[4 * v + h] = pack_bf16x2(go0 * uf.x * d0, go1 * uf.y * d1);
+      ou[4 * v + h] = pack_bf16x2(go0 * (gf.x * s0), go1 * (gf.y * s1));
+    }
+  }
+}
+
+// One lane = one row of a 32-row staging box: 64 bf16 (32 packed registers) go to the 128-byte
+// swizzled position the TMA store expects (16-byte chunk j of row r sits at chunk j ^ (r & 7)).
+// ---------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// bf16 (or byte) tensor seen as dims {inner, outer, groups}; strides in elements; 128B swizzle; zero OOB fill.
+static int make_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t outer, uint64_t groups,
+                    uint64_t outer_stride, uint64_t group_stride, uint32_t box_inner, uint32_t box_outer,
+                    int elem_bytes = 2) {
+  EncodeTiledFn fn = get_encode_fn();
+  B200_CHECK_ARG(fn != nullptr, B200MOE_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  B200_CHECK_ARG(aligned16(base), B200MOE_E_ALIGN, "tensor base %p is not 16-byte aligned", base);
+  B200_CHECK_ARG((outer_stride * elem_bytes) % 16 == 0 && (group_stride * elem_bytes) % 16 == 0, B200MOE_E_ALIGN,
+                 "row/group strides must be multiples of 16 bytes (got %llu, %llu elements)",
+                 (unsigned long long)outer_stride, (unsigned long long)group_stride);
+  cuuint64_t dims[3] = {inner, outer, groups};
+  cuuint64_t strides[2] = {outer_stride * elem_bytes, group_stride * elem_bytes};
+  cuuint32_t box[3] = {box_inner, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(tm, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200_CHECK_ARG(r == CUDA_SUCCESS, B200MOE_E_CUDA,
+                 "cuTensorMapEncodeTiled failed (%d): dims {%llu,%llu,%llu} box {%u,%u}", (int)r,
+                 (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)groups, box_inner,
+                 box_outer);
+  return 0;
+}
+
+
+static inline long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
+
+}  // namespace b200moe
+
+#define CHECK_DIM8(v) \
+  B200_CHECK_ARG((v) > 0 && (v) % 8 == 0, B200MOE_E_BAD_SHAPE, #v " = %lld must be a positive multiple of 8", (long long)(v))
+#define CHECK_I32(v) \
+  B200_CHECK_ARG((v) >= 0 && (v) < (1LL << 31), B200MOE_E_BAD_SHAPE, #v " = %lld does not fit int32", (long long)(v))

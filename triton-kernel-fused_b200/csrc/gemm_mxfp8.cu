@@ -1,0 +1,397 @@
+// MXFP8 GEMM for sm_100a: e4m3 operands with E8M0 block-32 scales, tcgen05.mma.kind::mxf8f6f4
+// .block_scale, fp32 accumulation in TMEM, bf16 results.
+//
+// Both operands are K-major (the quantisers write transposed copies where a GEMM reduces over the
+// other dimension).  One CTA computes a 128 x 128 tile; a k-block is 128 elements (one 128-byte
+// swizzle row, four MMAs of K = 32).  Per k-block the producer brings in the A and B boxes by TMA
+// plus the two 512-byte scale atoms (bulk copies); the MMA thread copies the atoms into tensor
+// memory (tcgen05.cp 32x128b.warpx4: lane = row % 32, column = row / 32, byte = k-block % 4) and
+// selects the byte with the scale-id fields of the instruction descriptor.
+// Schedules and epilogues are the ones of the bf16 kernel (dense / grouped-M / grouped-K; store,
+// SwiGLU over 64-interleaved gate|up weight rows, GLU backward).
+#include "gemm_common.cuh"
+
+namespace b200moe {
+
+constexpr int FBN = 128;                 // tile columns
+constexpr int FBK = 128;                 // k-block in elements = bytes
+constexpr int kATile = BM * FBK;         // 16 KB
+constexpr int kBTile = FBN * FBK;        // 16 KB
+constexpr int kSfAtom = 512;
+constexpr int kFStage = kATile + kBTile + 2 * kSfAtom;   // 33 KB, a multiple of 1024
+constexpr int kFStages = 6;
+constexpr int kSfTmemBase = 2 * FBN;     // accumulators use columns [0, 256)
+constexpr int kFTmemCols = 512;
+constexpr int kFSmemBytes = kFStages * kFStage + (2 * kFStages + 4) * 8 + 16 + 1024;
+
+struct Fp8Params {
+  GemmParams g;
+  const uint8_t* sfa;       // scale atoms of A: row-block major, k-chunk minor
+  const uint8_t* sfb;
+  int sfa_kc, sfb_kc;       // k-chunks (of 128) per row-block
+  int b_rows_per_group;     // rows of B per expert (GROUPED_M), multiple of 128
+};
+
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// shared-memory descriptor of a 32 x 16-byte scale atom: no swizzle, 8-row groups 128 bytes apart
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;
+  d |= 1ull << 46;
+  return d;
+}
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void umma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// Block-scaled instruction descriptor: e4m3 A/B (format 0), K-major, E8M0 scales.
+//   bits 4-5 B scale id   bits 7-9 A format   bits 10-12 B format   bits 17-22 N >> 3
+//   bit 23 scale format (1 = E8M0)   bits 24-28 M >> 4   bits 29-30 A scale id
+__device__ __forceinline__ uint32_t idesc_mxf8(int n, uint32_t sf_id) {
+  return (sf_id << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (1u << 23) |
+         (static_cast<uint32_t>(BM >> 4) << 24) | (sf_id << 29);
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const Fp8Params fp) {
+  const GemmParams& p = fp.g;
+  constexpr int TN = FBN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kFStages * kFStage);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = smem_u32(bars + kFStages);
+  const uint32_t bar_tfull = smem_u32(bars + 2 * kFStages);
+  const uint32_t bar_tempty = smem_u32(bars + 2 * kFStages + 2);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kFStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kFStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, kEpiWarps);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kFTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total = total_tiles(p, TN, BM);
+
+  if (warp == 0) {
+    if (lane == 0) {   // ---------------------------------------------------------- producer
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+        const Tile t = get_tile(p, tile, TN, BM, FBK);
+        const int gB = (p.sched == SCHED_GROUPED_M) ? t.g : 0;
+        const long long rb_a = t.m0 >> 7;
+        const long long rb_b = (static_cast<long long>(gB) * fp.b_rows_per_group + t.n0) >> 7;
+        for (int kb = 0; kb < t.nkb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, ST_WAIT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = bar_full + 8 * s;
+          mbar_arrive_expect_tx(full, kFStage);
+          const uint32_t sa = smem_u32(smem + s * kFStage);
+          const int kk = t.k0 + kb * FBK;
+          const long long kc = kk >> 7;
+          tma_load_3d(sa, &tmA, full, kk, t.m0, 0);
+          tma_load_3d(sa + kATile, &tmB, full, kk, t.n0, gB);
+          bulk_load_1d(sa + kATile + kBTile, fp.sfa + (rb_a * fp.sfa_kc + kc) * kSfAtom, kSfAtom, full);
+          bulk_load_1d(sa + kATile + kBTile + kSfAtom, fp.sfb + (rb_b * fp.sfb_kc + kc) * kSfAtom, kSfAtom, full);
+          if (++s == kFStages) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {   // ---------------------------------------------------------- MMA issuer
+      int s = 0, it = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++it) {
+        const Tile t = get_tile(p, tile, TN, BM, FBK);
+        const int buf = it & 1;
+        if (!mbar_wait(bar_tempty + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag, ST_WAIT_MMA_TMEM)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * FBN;
+        for (int kb = 0; kb < t.nkb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, ST_WAIT_MMA_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * kFStage);
+          const uint32_t sb = sa + kATile;
+          const uint32_t sfa_t = tmem_base + kSfTmemBase + 8 * s;
+          const uint32_t sfb_t = sfa_t + 4;
+          tmem_cp_sf(sfa_t, sf_desc(sa + kATile + kBTile));
+          tmem_cp_sf(sfb_t, sf_desc(sa + kATile + kBTile + kSfAtom));
+#pragma unroll
+          for (int k = 0; k < FBK / 32; ++k) {
+            const uint64_t da = umma_desc_sw128(sa + k * 32, 0, 1024);
+            const uint64_t db = umma_desc_sw128(sb + k * 32, 0, 1024);
+            umma_mxf8(d_tmem, da, db, idesc_mxf8(FBN, k), sfa_t, sfb_t, (kb | k) != 0);
+          }
+          umma_commit(bar_empty + 8 * s);
+          if (++s == kFStages) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+        if (!ok) break;
+        if (t.nkb > 0) umma_commit(bar_tfull + 8 * buf);
+        else mbar_arrive(bar_tfull + 8 * buf);
+      }
+    }
+  } else {   // ---------------------------------------------------------------------- epilogue
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
+      const Tile t = get_tile(p, tile, TN, BM, FBK);
+      const int buf = it & 1;
+      if (!mbar_wait(bar_tfull + 8 * buf, (it >> 1) & 1, abort_flag, ST_WAIT_EPILOGUE)) break;
+      __syncwarp();
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * FBN;
+      const long long row = static_cast<long long>(t.m0) + q * 32 + lane;
+      const bool have_acc = t.nkb > 0;
+      if constexpr (EPI == EPI_STORE) {
+        const bool row_ok = (p.sched == SCHED_GROUPED_M) || (row < p.M);
+        const long long base = (p.sched == SCHED_GROUPED_K ? t.g * p.d_group_stride : 0) + row * p.ldd + t.n0;
+#pragma unroll 1
+        for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
+          if (t.n0 + c0 >= p.N) break;
+          uint32_t r[32];
+          if (have_acc) {
+            tmem_ld32(taddr + c0, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          if (row_ok) {
+            __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + base + c0;
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              if (t.n0 + c0 + v * 8 < p.N) *reinterpret_cast<uint4*>(d + v * 8) = pack8(r + v * 8);
+          }
+        }
+      } else if constexpr (EPI == EPI_SWIGLU) {
+        // weight rows are 64-interleaved: accumulator columns [0,64) = gate, [64,128) = up of the
+        // intermediate columns [n0/2, n0/2 + 64); this warp handles 32 of them
+        const int I = p.I;
+        const int col0 = t.n0 / 2 + half * 32;
+        if (col0 < I) {
+          __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(p.D) + row * (2LL * I);
+          __nv_bfloat16* it_out = reinterpret_cast<__nv_bfloat16*>(p.aux) + row * static_cast<long long>(I);
+          uint32_t g[32], u[32];
+          tmem_ld32(taddr + half * 32, g);
+          tmem_ld32(taddr + 64 + half * 32, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = col0 + v * 8;
+            if (col < I) {
+              uint32_t og[4], ou[4], oh[4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                og[h] = pack_bf16x2(__uint_as_float(g[v * 8 + 2 * h]), __uint_as_float(g[v * 8 + 2 * h + 1]));
+                ou[h] = pack_bf16x2(__uint_as_float(u[v * 8 + 2 * h]), __uint_as_float(u[v * 8 + 2 * h + 1]));
+                const float2 gf = unpack_bf16x2(og[h]);
+                const float2 uf = unpack_bf16x2(ou[h]);
+                const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
+                const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
+                oh[h] = pack_bf16x2(gf.x * s0 * uf.x, gf.y * s1 * uf.y);
+              }
+              *reinterpret_cast<uint4*>(gu + col) = make_uint4(og[0], og[1], og[2], og[3]);
+              *reinterpret_cast<uint4*>(gu + I + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+              *reinterpret_cast<uint4*>(it_out + col) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+            }
+          }
+        }
+      } else {   // EPI_GLU_BWD: accumulator = grad_inter columns [n0, n0+128), this warp 64 of them
+        const int I = p.I;
+        const __nv_bfloat16* gu = reinterpret_cast<const __nv_bfloat16*>(p.aux) + row * (2LL * I);
+        __nv_bfloat16* ggu = reinterpret_cast<__nv_bfloat16*>(p.D) + row * (2LL * I);
+#pragma unroll 1
+        for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
+          if (t.n0 + c0 >= I) break;
+          uint4 g4[4], u4[4];
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = t.n0 + c0 + v * 8;
+            g4[v] = col < I ? __ldg(reinterpret_cast<const uint4*>(gu + col)) : make_uint4(0u, 0u, 0u, 0u);
+            u4[v] = col < I ? __ldg(reinterpret_cast<const uint4*>(gu + I + col)) : make_uint4(0u, 0u, 0u, 0u);
+          }
+          uint32_t r[32], og[16], ou[16];
+          tmem_ld32(taddr + c0, r);
+          tmem_ld_wait();
+          glu_bwd32(r, g4, u4, og, ou);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = t.n0 + c0 + v * 8;
+            if (col < I) {
+              *reinterpret_cast<uint4*>(ggu + col) = make_uint4(og[4 * v], og[4 * v + 1], og[4 * v + 2], og[4 * v + 3]);
+              *reinterpret_cast<uint4*>(ggu + I + col) = make_uint4(ou[4 * v], ou[4 * v + 1], ou[4 * v + 2], ou[4 * v + 3]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_flag);
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kFTmemCols);
+  }
+}
+
+template <int EPI>
+static int launch_fp8(const CUtensorMap& tmA, const CUtensorMap& tmB, const Fp8Params& fp, int max_tiles,
+                      cudaStream_t stream) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_mxfp8_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(max dynamic smem)");
+  int grid = gemm_cta_budget();
+  if (max_tiles > 0 && max_tiles < grid) grid = max_tiles;
+  if (grid < 1) grid = 1;
+  gemm_mxfp8_kernel<EPI><<<grid, kThreads, kFSmemBytes, stream>>>(tmA, tmB, fp);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// byte tensor {K, rows, groups}, box {128 bytes, 128 rows}
+static int map_fp8(CUtensorMap* tm, const void* q, long long rows, long long K, long long groups) {
+  return make_map(tm, q, K, rows, groups, K, rows * K, FBK, 128, 1);
+}
+
+}  // namespace b200moe
+
+using namespace b200moe;
+
+#define CHECK_K128(v) \
+  B200_CHECK_ARG((v) > 0 && (v) % 128 == 0, B200MOE_E_BAD_SHAPE, #v " = %lld must be a positive multiple of 128", (long long)(v))
+
+extern "C" {
+
+int b200moe_mxfp8_gemm_nt(const void* Aq, const void* Asf, const void* Bq, const void* Bsf, void* D, int64_t M,
+                          int64_t N, int64_t K, int32_t* status, b200moe_stream_t stream) {
+  B200_CHECK_ARG(Aq && Asf && Bq && Bsf && D, B200MOE_E_NULL, "mxfp8_gemm_nt: null pointer");
+  CHECK_K128(K); CHECK_DIM8(N); CHECK_I32(M); CHECK_I32(N); CHECK_I32(K);
+  if (M == 0) return 0;
+  CUtensorMap tmA, tmB;
+  int rc = map_fp8(&tmA, Aq, M, K, 1);
+  if (rc) return rc;
+  rc = map_fp8(&tmB, Bq, N, K, 1);
+  if (rc) return rc;
+  Fp8Params fp{};
+  fp.g.sched = SCHED_DENSE; fp.g.M = (int)M; fp.g.N = (int)N; fp.g.K = (int)K; fp.g.num_groups = 1;
+  fp.g.D = D; fp.g.ldd = N; fp.g.status = status;
+  fp.sfa = (const uint8_t*)Asf; fp.sfb = (const uint8_t*)Bsf; fp.sfa_kc = fp.sfb_kc = (int)(K / 128);
+  return launch_fp8<EPI_STORE>(tmA, tmB, fp, (int)(ceil_div(M, BM) * ceil_div(N, FBN)), (cudaStream_t)stream);
+}
+
+/* grouped-M: D(rows of e, N) = A(rows of e) * B[e]^T; B is an (E*N, K) stack, N %% 128 == 0.
+ * epilogue: 0 store, 1 SwiGLU (B rows 64-interleaved gate|up, N = 2I, D = gate_up, aux = inter),
+ * 2 GLU backward (N = I, aux = saved gate_up, D = grad_gate_up). */
+int b200moe_mxfp8_expert_gemm(int epilogue, const void* Aq, const void* Asf, const void* Bq, const void* Bsf,
+                              const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E, int64_t N,
+                              int64_t K, int64_t I, void* D, void* aux, int32_t* status, b200moe_stream_t stream) {
+  B200_CHECK_ARG(Aq && Asf && Bq && Bsf && D && tile_expert && poffs, B200MOE_E_NULL, "mxfp8_expert_gemm: null pointer");
+  CHECK_K128(K); CHECK_K128(N); CHECK_I32(rows_cap);
+  B200_CHECK_ARG(rows_cap % B200MOE_TILE_M == 0, B200MOE_E_BAD_SHAPE, "mxfp8_expert_gemm: rows_cap %% %d != 0", B200MOE_TILE_M);
+  B200_CHECK_ARG(E >= 1 && E * N < (1LL << 31), B200MOE_E_BAD_SHAPE, "mxfp8_expert_gemm: E = %d", E);
+  CUtensorMap tmA, tmB;
+  int rc = map_fp8(&tmA, Aq, rows_cap, K, 1);
+  if (rc) return rc;
+  rc = map_fp8(&tmB, Bq, N, K, E);
+  if (rc) return rc;
+  Fp8Params fp{};
+  fp.g.sched = SCHED_GROUPED_M; fp.g.N = (int)N; fp.g.K = (int)K; fp.g.num_groups = E;
+  fp.g.tile_expert = tile_expert; fp.g.poffs = poffs; fp.g.D = D; fp.g.ldd = N; fp.g.aux = aux; fp.g.I = (int)I;
+  fp.g.status = status;
+  fp.sfa = (const uint8_t*)Asf; fp.sfb = (const uint8_t*)Bsf; fp.sfa_kc = fp.sfb_kc = (int)(K / 128);
+  fp.b_rows_per_group = (int)N;
+  switch (epilogue) {
+    case EPI_STORE: return launch_fp8<EPI_STORE>(tmA, tmB, fp, 0, (cudaStream_t)stream);
+    case EPI_SWIGLU:
+      B200_CHECK_ARG(aux && N == 2 * I && I % 64 == 0, B200MOE_E_BAD_SHAPE, "mxfp8_expert_gemm: SwiGLU needs N = 2I, I %% 64 == 0");
+      return launch_fp8<EPI_SWIGLU>(tmA, tmB, fp, 0, (cudaStream_t)stream);
+    case EPI_GLU_BWD:
+      B200_CHECK_ARG(aux && N == I, B200MOE_E_BAD_SHAPE, "mxfp8_expert_gemm: GLU backward needs N = I");
+      return launch_fp8<EPI_GLU_BWD>(tmA, tmB, fp, 0, (cudaStream_t)stream);
+    default:
+      set_error("mxfp8_expert_gemm: unknown epilogue %d", epilogue);
+      return B200MOE_E_UNSUPPORTED;
+  }
+}
+
+/* grouped-K (wgrad): out[e] (Na,Nb) = At[:, rows of e] * Bt[:, rows of e]^T with At (Na, rows_cap) and
+ * Bt (Nb, rows_cap) the transposed-quantised operands (K = padded token rows). */
+int b200moe_mxfp8_expert_wgrad(const void* Atq, const void* Atsf, const void* Btq, const void* Btsf,
+                               const int32_t* poffs, const int32_t* counts, int64_t rows_cap, int E, int64_t Na,
+                               int64_t Nb, void* out, int32_t* status, b200moe_stream_t stream) {
+  B200_CHECK_ARG(Atq && Atsf && Btq && Btsf && poffs && out, B200MOE_E_NULL, "mxfp8_expert_wgrad: null pointer");
+  CHECK_K128(rows_cap); CHECK_DIM8(Na); CHECK_DIM8(Nb); CHECK_I32(Na); CHECK_I32(Nb); CHECK_I32(rows_cap);
+  CUtensorMap tmA, tmB;
+  int rc = map_fp8(&tmA, Atq, Na, rows_cap, 1);
+  if (rc) return rc;
+  rc = map_fp8(&tmB, Btq, Nb, rows_cap, 1);
+  if (rc) return rc;
+  Fp8Params fp{};
+  fp.g.sched = SCHED_GROUPED_K; fp.g.M = (int)Na; fp.g.N = (int)Nb; fp.g.K = (int)rows_cap; fp.g.num_groups = E;
+  fp.g.poffs = poffs; fp.g.counts = counts; fp.g.D = out; fp.g.ldd = Nb; fp.g.d_group_stride = Na * Nb;
+  fp.g.status = status;
+  fp.sfa = (const uint8_t*)Atsf; fp.sfb = (const uint8_t*)Btsf; fp.sfa_kc = fp.sfb_kc = (int)(rows_cap / 128);
+  return launch_fp8<EPI_STORE>(tmA, tmB, fp, (int)std::min<long long>(1 << 30, E * ceil_div(Na, BM) * ceil_div(Nb, FBN)),
+                               (cudaStream_t)stream);
+}
+
+}  // extern "C"

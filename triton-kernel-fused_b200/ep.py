@@ -119,8 +119,16 @@ class ExpertParallelMoELayer(nn.Module):
     weight are local sums: all-reduce them (or wrap the module in DDP) as for any replicated
     parameter; expert gradients are complete on the owning rank."""
 
-    def __init__(self, H, I, E, top_k=2, group=None, norm_topk_prob=True, routed_scaling_factor=1.0, init_std=0.02):
+    def __init__(self, H, I, E, top_k=2, group=None, norm_topk_prob=True, routed_scaling_factor=1.0, init_std=0.02,
+                 overlap_chunks=1, reserved_sms=0):
+        """overlap_chunks > 1 splits the local tokens into that many independent pipelines on their own
+        CUDA streams, so the all-to-alls of one chunk run while the expert GEMMs of another do;
+        reserved_sms keeps that many SMs free of the persistent GEMM kernels for the communication
+        kernels (process-wide setting of the library)."""
         super().__init__()
+        self.overlap_chunks = max(1, int(overlap_chunks))
+        self.reserved_sms = int(reserved_sms)
+        self._streams = None
         world = dist.get_world_size(group)
         if E % world != 0:
             raise ValueError(f"num_experts = {E} must be divisible by the group size {world}")
@@ -140,14 +148,35 @@ class ExpertParallelMoELayer(nn.Module):
         self.bias.data = self.bias.data.float()
         return self
 
+    def _pipeline(self, flat):
+        idx, w, counts = fused_mlp_router(flat, self.gate.weight, self.bias, self.top_k, self.num_experts,
+                                          self.norm_topk_prob, self.routed_scaling_factor, return_counts=True)
+        return ep_moe(flat, idx, w, self.gate_up_proj, self.down_proj, self.num_experts, self.group), counts
+
     def forward(self, x):
         shape = x.shape
         flat = x.reshape(-1, shape[-1])
-        idx, w, counts = fused_mlp_router(flat, self.gate.weight, self.bias, self.top_k, self.num_experts,
-                                          self.norm_topk_prob, self.routed_scaling_factor, return_counts=True)
+        n = self.overlap_chunks
+        if n == 1 or flat.shape[0] < n:
+            out, self.last_counts = self._pipeline(flat)
+            return out.reshape(shape)
+        if self._streams is None:
+            self._streams = [torch.cuda.Stream(device=flat.device) for _ in range(n)]
+            L.check(L.lib().b200moe_set_reserved_sms(self.reserved_sms))
+        cur = torch.cuda.current_stream(flat.device)
+        outs, counts = [], None
+        for st, chunk in zip(self._streams, flat.chunk(n)):
+            st.wait_stream(cur)
+            chunk.record_stream(st)
+            with torch.cuda.stream(st):
+                o, c = self._pipeline(chunk)
+                counts = c if counts is None else counts + c
+            o.record_stream(cur)
+            outs.append(o)
+        for st in self._streams:
+            cur.wait_stream(st)
         self.last_counts = counts
-        out = ep_moe(flat, idx, w, self.gate_up_proj, self.down_proj, self.num_experts, self.group)
-        return out.reshape(shape)
+        return torch.cat(outs).reshape(shape)
 
     @torch.no_grad()
     def update_bias(self, u):

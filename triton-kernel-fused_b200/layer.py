@@ -7,14 +7,19 @@ import torch
 import torch.nn as nn
 
 from .moe import moe
+from .mxfp8 import moe_mxfp8
 from .router import fused_mlp_router, router_bias_update
 
 __all__ = ["MoELayer"]
 
 
 class MoELayer(nn.Module):
-    def __init__(self, H, I, E, top_k=2, norm_topk_prob=True, routed_scaling_factor=1.0, init_std=0.02):
+    def __init__(self, H, I, E, top_k=2, norm_topk_prob=True, routed_scaling_factor=1.0, init_std=0.02,
+                 precision="bf16"):
         super().__init__()
+        if precision not in ("bf16", "mxfp8"):
+            raise ValueError("precision must be 'bf16' or 'mxfp8'")
+        self.precision = precision
         self.gate = nn.Linear(H, E, bias=False)
         self.gate_up_proj = nn.Parameter(torch.randn(E, 2 * I, H) * init_std)
         self.down_proj = nn.Parameter(torch.randn(E, H, I) * init_std)
@@ -40,7 +45,8 @@ class MoELayer(nn.Module):
         idx, w, counts = fused_mlp_router(flat, self.gate.weight, self.bias, self.top_k, self.num_experts,
                                           self.norm_topk_prob, self.routed_scaling_factor, return_counts=True)
         self.last_counts = counts
-        out = moe(flat, idx, w, self.gate_up_proj, self.down_proj, self.act_codes)
+        fn = moe_mxfp8 if self.precision == "mxfp8" else moe
+        out = fn(flat, idx, w, self.gate_up_proj, self.down_proj, self.act_codes)
         return out.reshape(shape)
 
     @torch.no_grad()

@@ -1,0 +1,93 @@
+"""MXFP8 expert pipeline: the same block as `moe`, with every expert GEMM (forward, dgrad, wgrad)
+run on tcgen05 block-scaled MMAs over e4m3 operands with E8M0 block-32 scales.
+
+The reference has no MXFP8 path; the signature mirrors `moe` (kernels/sm75/moe.py:838) and the
+numerics follow the OCP MX convention (see include/b200moe.h).  Master weights stay bf16 and are
+quantised on every call; each GEMM quantises its operands along its own reduction dimension
+(row-wise for forward/dgrad activations, transposed copies for weights in dgrad and for both
+operands of the wgrads).  Needs d_model % 128 == 0 and d_ff % 128 == 0.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib as L
+from . import ops
+from .moe import _amp_cast, _check_codes
+
+__all__ = ["moe_mxfp8"]
+
+
+class _MoEMxfp8(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, idx, wt, gate_up_proj, down_proj, act_codes):
+        hidden, gate_up_proj, down_proj = _amp_cast(hidden, gate_up_proj, down_proj)
+        for name, t in (("hidden", hidden), ("gate_up_proj", gate_up_proj), ("down_proj", down_proj)):
+            L.require_cuda_bf16(name, t)
+        N, H = hidden.shape
+        E, twoI, H2 = gate_up_proj.shape
+        I = twoI // 2
+        L.require(H2 == H and tuple(down_proj.shape) == (E, H, I), "weight shapes must be (E,2I,H) and (E,H,I)")
+        L.require(H % 128 == 0 and I % 128 == 0, f"MXFP8 path needs d_model and d_ff multiples of 128 (got {H}, {I})")
+        hidden = hidden.contiguous()
+        gate_up_proj = gate_up_proj.contiguous()
+        down_proj = down_proj.contiguous()
+        w32 = wt.detach().float().contiguous()
+        dev = hidden.device
+
+        perm = ops.permute_build(idx, E)
+        x_s = ops.gather_rows(hidden, perm)
+        xq, xsf = ops.mxfp8_quant_rows(x_s)
+        wq, wsf = ops.mxfp8_quant_rows(gate_up_proj.view(E * twoI, H), interleave_I=I)
+        gate_up = torch.empty(perm.cap, twoI, dtype=torch.bfloat16, device=dev)
+        inter = torch.empty(perm.cap, I, dtype=torch.bfloat16, device=dev)
+        ops.mxfp8_expert_gemm(ops.EPI_SWIGLU, xq, xsf, wq, wsf, perm, twoI, H, I, gate_up, inter)
+        iq, isf = ops.mxfp8_quant_rows(inter)
+        dq, dsf = ops.mxfp8_quant_rows(down_proj.view(E * H, I))
+        eo = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=dev)
+        ops.mxfp8_expert_gemm(ops.EPI_STORE, iq, isf, dq, dsf, perm, H, I, I, eo)
+        out = ops.combine(eo, w32, perm)
+
+        ctx.perm = perm
+        ctx.wt_dtype = wt.dtype
+        ctx.save_for_backward(x_s, gate_up, inter, eo, w32, gate_up_proj, down_proj)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x_s, gate_up, inter, eo, w32, gate_up_proj, down_proj = ctx.saved_tensors
+        perm = ctx.perm
+        E, twoI, H = gate_up_proj.shape
+        I = twoI // 2
+        dev = x_s.device
+        need_x, _, need_w, need_gu, need_dn, _ = ctx.needs_input_grad
+        grad_out = grad_out.contiguous().to(torch.bfloat16)
+        grad_eo, grad_w = ops.combine_bwd(grad_out, eo, w32, perm)
+        grad_hidden = grad_gate_up_proj = grad_down_proj = None
+        if need_x or need_gu:
+            gq, gsf = ops.mxfp8_quant_rows(grad_eo)                       # K = H
+            wtq, wtsf = ops.mxfp8_quant_transpose(down_proj)              # (E, I, H)
+            grad_gu = torch.empty(perm.cap, twoI, dtype=torch.bfloat16, device=dev)
+            ops.mxfp8_expert_gemm(ops.EPI_GLU_BWD, gq, gsf, wtq, wtsf, perm, I, H, I, grad_gu, gate_up)
+            if need_gu:
+                at, atsf = ops.mxfp8_quant_transpose(grad_gu)             # (2I, rows)
+                bt, btsf = ops.mxfp8_quant_transpose(x_s)                 # (H, rows)
+                grad_gate_up_proj = ops.mxfp8_expert_wgrad(at, atsf, bt, btsf, perm)
+            if need_x:
+                ggq, ggsf = ops.mxfp8_quant_rows(grad_gu)                 # K = 2I
+                wgt, wgtsf = ops.mxfp8_quant_transpose(gate_up_proj)      # (E, H, 2I)
+                grad_x_s = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=dev)
+                ops.mxfp8_expert_gemm(ops.EPI_STORE, ggq, ggsf, wgt, wgtsf, perm, H, twoI, I, grad_x_s)
+                grad_hidden = ops.combine(grad_x_s, None, perm)
+        if need_dn:
+            at, atsf = ops.mxfp8_quant_transpose(grad_eo)                 # (H, rows)
+            bt, btsf = ops.mxfp8_quant_transpose(inter)                   # (I, rows)
+            grad_down_proj = ops.mxfp8_expert_wgrad(at, atsf, bt, btsf, perm)
+        grad_wt = grad_w.to(ctx.wt_dtype) if need_w else None
+        return grad_hidden, None, grad_wt, grad_gate_up_proj, grad_down_proj, None
+
+
+def moe_mxfp8(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes, act_params=None):
+    """Same contract as `moe`; expert GEMMs in MXFP8 (e4m3 + E8M0 block-32 scales), bf16 in and out."""
+    _check_codes(act_codes, act_params)
+    return _MoEMxfp8.apply(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes)

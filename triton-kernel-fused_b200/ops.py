@@ -243,7 +243,8 @@ def expert_wgrad(a, b, perm: Permutation):
     """out[e] (Na,Nb) = a[rows of e]^T @ b[rows of e]; zero for experts without rows."""
     Na, Nb = a.shape[1], b.shape[1]
     out = torch.empty(perm.E, Na, Nb, dtype=torch.bfloat16, device=a.device)
-    L.check(L.lib().b200moe_expert_wgrad(L.ptr(a), L.ptr(b), L.ptr(perm.poffs), perm.cap, perm.E, Na, Nb, L.ptr(out),
+    L.check(L.lib().b200moe_expert_wgrad(L.ptr(a), L.ptr(b), L.ptr(perm.poffs), L.ptr(perm.counts), perm.cap, perm.E, Na, Nb,
+                                         L.ptr(out),
                                          L.ptr(L.status_word(a.device)), L.stream_of(a)))
     return out
 
@@ -274,3 +275,66 @@ def combine_bwd_raw(grad_out, eo, w, row_slot, total_rows, k, rows_cap):
 
 def combine_bwd(grad_out, eo, w, perm: Permutation):
     return combine_bwd_raw(grad_out, eo, w, perm.row_slot, perm.total_rows, perm.k, perm.cap)
+
+
+# ----------------------------------------------------------------------------- MXFP8
+EPI_STORE, EPI_SWIGLU, EPI_GLU_BWD = 0, 1, 2
+
+
+def _sf_empty(rows, K, device):
+    return torch.empty(int(L.lib().b200moe_mxfp8_sf_bytes(rows, K)), dtype=torch.uint8, device=device)
+
+
+@_op("mxfp8_quant_rows", 1)
+def mxfp8_quant_rows(x, interleave_I=0):
+    """x (R,C) bf16 -> (q uint8 (R,C) e4m3 codes, scale atoms), one E8M0 scale per 32 elements along C."""
+    L.require_cuda_bf16("x", x)
+    L.require(x.dim() == 2 and x.is_contiguous(), "mxfp8_quant_rows: need a contiguous (R,C) tensor")
+    R, C = x.shape
+    q = torch.empty(R, C, dtype=torch.uint8, device=x.device)
+    sf = _sf_empty(R, C, x.device)
+    L.check(L.lib().b200moe_mxfp8_quant_rows(L.ptr(x), R, C, int(interleave_I), L.ptr(q), L.ptr(sf), L.stream_of(x)))
+    return q, sf
+
+
+@_op("mxfp8_quant_transpose", 1)
+def mxfp8_quant_transpose(x):
+    """x (G,R,C) or (R,C) bf16 -> (q uint8 (G,C,R) / (C,R), scale atoms), scales along R."""
+    L.require_cuda_bf16("x", x)
+    x3 = x if x.dim() == 3 else x.unsqueeze(0)
+    L.require(x3.is_contiguous(), "mxfp8_quant_transpose: need a contiguous tensor")
+    G, R, C = x3.shape
+    q = torch.empty(G, C, R, dtype=torch.uint8, device=x.device)
+    sf = _sf_empty(G * C, R, x.device)
+    L.check(L.lib().b200moe_mxfp8_quant_transpose(L.ptr(x3), G, R, C, L.ptr(q), L.ptr(sf), L.stream_of(x)))
+    return (q if x.dim() == 3 else q[0]), sf
+
+
+@_op("mxfp8_gemm_nt", 1)
+def mxfp8_gemm_nt(aq, asf, bq, bsf):
+    """dequant(aq)(M,K) @ dequant(bq)(N,K)^T -> (M,N) bf16."""
+    M, K = aq.shape
+    N = bq.shape[0]
+    d = torch.empty(M, N, dtype=torch.bfloat16, device=aq.device)
+    L.check(L.lib().b200moe_mxfp8_gemm_nt(L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), L.ptr(d), M, N, K,
+                                          L.ptr(L.status_word(aq.device)), L.stream_of(aq)))
+    return d
+
+
+@_op("mxfp8_expert_gemm", 1)
+def mxfp8_expert_gemm(epilogue, aq, asf, bq, bsf, perm: Permutation, N, K, I, d, aux=None):
+    L.check(L.lib().b200moe_mxfp8_expert_gemm(int(epilogue), L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf),
+                                              L.ptr(perm.tile_expert), L.ptr(perm.poffs), perm.cap, perm.E, N, K, I,
+                                              L.ptr(d), L.ptr(aux), L.ptr(L.status_word(d.device)), L.stream_of(d)))
+    return d
+
+
+@_op("mxfp8_expert_wgrad", 1)
+def mxfp8_expert_wgrad(atq, atsf, btq, btsf, perm: Permutation):
+    """out[e] (Na,Nb) = At[:, rows of e] @ Bt[:, rows of e]^T from transposed-quantised operands."""
+    Na, Nb = atq.shape[0], btq.shape[0]
+    out = torch.empty(perm.E, Na, Nb, dtype=torch.bfloat16, device=atq.device)
+    L.check(L.lib().b200moe_mxfp8_expert_wgrad(L.ptr(atq), L.ptr(atsf), L.ptr(btq), L.ptr(btsf), L.ptr(perm.poffs),
+                                               L.ptr(perm.counts), perm.cap, perm.E, Na, Nb, L.ptr(out),
+                                               L.ptr(L.status_word(out.device)), L.stream_of(out)))
+    return out
