@@ -125,8 +125,8 @@ def _make_layer(pkg, w, device, seed, world):
     with torch.device(device):      # build the (large) expert stacks directly on the GPU
         if world > 1:
             layer = pkg.ExpertParallelMoELayer(w["H"], w["I"], w["E"], top_k=w["k"],
-                                               overlap_chunks=int(os.environ.get("B200MOE_EP_CHUNKS", "2")),
-                                               reserved_sms=int(os.environ.get("B200MOE_EP_RESERVED_SMS", "16")))
+                                               overlap_chunks=int(os.environ.get("B200MOE_EP_CHUNKS", "1")),
+                                               reserved_sms=int(os.environ.get("B200MOE_EP_RESERVED_SMS", "0")))
         else:
             layer = pkg.MoELayer(w["H"], w["I"], w["E"], top_k=w["k"], precision=w["precision"])
     return layer.to(torch.bfloat16)
