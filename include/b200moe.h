@@ -194,6 +194,35 @@ int b200moe_combine_bwd(const void* grad_out, const void* eo, const float* w,
                         const int32_t* row_slot, const int32_t* total_rows, int k, int64_t H,
                         int64_t rows_cap, void* grad_eo, float* grad_w, b200moe_stream_t stream);
 
+/* ---- expert-parallel exchange over peer memory (no reference counterpart: the reference has no
+ * expert parallelism) ------------------------------------------------------------------------------
+ * `*_peers` arguments are HOST arrays of W device pointers, entry r = the same buffer on rank r
+ * (a symmetric allocation mapped into this process).  Kernels only read peer memory and never wait on
+ * a peer; the caller separates the phases with cross-rank barriers.  W <= 16, E % W == 0.
+ * ep_plan: counts_all (W,E) -> this rank's padded segments poffs_l (E/W+1), counts_l (E/W) live rows,
+ * tile_expert_l, src_base (W,E/W) first row of each source rank's block, dest_base (E) first row of
+ * THIS rank's block of expert e inside e's owner. */
+int b200moe_ep_plan(const int32_t* counts_all, int W, int rank, int E, int32_t* poffs_l, int32_t* counts_l,
+                    int32_t* tile_expert_l, int32_t* src_base, int32_t* dest_base, b200moe_stream_t stream);
+/* owner side, forward: x_s[row] = x_peers[src][slot / k] with slot = order_peers[src][offs_peers[src][e] + i];
+ * zero pad rows; records (src, slot) of every row for the backward pass. */
+int b200moe_ep_gather_pull(const void* const* x_peers, const void* const* order_peers,
+                           const void* const* offs_peers, const int32_t* counts_l, const int32_t* poffs_l,
+                           const int32_t* tile_expert_l, const int32_t* src_base, int W, int rank, int E, int k,
+                           int64_t H, int64_t rows_cap, void* x_s, int32_t* row_src, int32_t* row_slot_src,
+                           b200moe_stream_t stream);
+/* home side: out[t] = sum_j w[t,j] * rows_peers[owner][dest_base[e] + slot_pos[s] - offs[e]] (w NULL = 1);
+ * when gw_peers / grad_w are given, grad_w[s] is fetched from the owner's per-row dot products. */
+int b200moe_ep_combine_pull(const void* const* rows_peers, const float* w, const int64_t* idx,
+                            const int32_t* slot_pos, const int32_t* offs, const int32_t* dest_base, int W, int E,
+                            int64_t T, int k, int64_t H, void* out, const void* const* gw_peers, float* grad_w,
+                            b200moe_stream_t stream);
+/* owner side, backward: grad_eo[row] = w_peers[src][slot] * go_peers[src][slot / k]; gw_rows[row] = <go, eo[row]>. */
+int b200moe_ep_combine_bwd_pull(const void* const* go_peers, const void* const* w_peers, const void* eo,
+                                const int32_t* row_src, const int32_t* row_slot_src, const int32_t* total_rows,
+                                int W, int k, int64_t H, int64_t rows_cap, void* grad_eo, float* gw_rows,
+                                b200moe_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

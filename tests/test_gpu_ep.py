@@ -17,7 +17,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, cfg, q):
+def _worker(rank, world, port, cfg, transport, q):
     import importlib
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -31,7 +31,7 @@ def _worker(rank, world, port, cfg, q):
         inp = O.make_inputs(T, H, E, I, k, seed=41, bias_std=0.01, dtype=torch.bfloat16)
         Tl, El = T // world, E // world
         sl = slice(rank * Tl, (rank + 1) * Tl)
-        layer = pkg.ExpertParallelMoELayer(H, I, E, top_k=k).to(dev).to(torch.bfloat16)
+        layer = pkg.ExpertParallelMoELayer(H, I, E, top_k=k, transport=transport).to(dev).to(torch.bfloat16)
         with torch.no_grad():
             layer.gate.weight.copy_(inp["gate_weight"])
             layer.gate_up_proj.copy_(inp["gate_up"][rank * El:(rank + 1) * El])
@@ -51,8 +51,9 @@ def _worker(rank, world, port, cfg, q):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("transport", ["nccl", "p2p"])
 @pytest.mark.parametrize("cfg", [(2048, 512, 16, 256, 4), (1024, 256, 64, 128, 8)])
-def test_expert_parallel_equals_single_gpu(pkg, cfg):
+def test_expert_parallel_equals_single_gpu(pkg, cfg, transport):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
@@ -61,7 +62,7 @@ def test_expert_parallel_equals_single_gpu(pkg, cfg):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, cfg, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, cfg, transport, q)) for r in range(world)]
     for p in procs:
         p.start()
     res = {}

@@ -56,6 +56,10 @@ _SIGNATURES = {
     "b200moe_mxfp8_expert_gemm": (c_int, [c_int] + [c_void_p] * 6 + [c_int64, c_int, c_int64, c_int64, c_int64] +
                                   [c_void_p] * 4),
     "b200moe_mxfp8_expert_wgrad": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
+    "b200moe_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 5 + [c_void_p]),
+    "b200moe_ep_gather_pull": (c_int, [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int64, c_int64] + [c_void_p] * 4),
+    "b200moe_ep_combine_pull": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int64, c_int, c_int64] + [c_void_p] * 4),
+    "b200moe_ep_combine_bwd_pull": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int64, c_int64] + [c_void_p] * 3),
     "b200moe_combine": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64, c_void_p, c_void_p]),
     "b200moe_combine_bwd": (c_int, [c_void_p] * 5 + [c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
 }
@@ -107,6 +111,11 @@ def check(rc: int) -> None:
 
 def ptr(t):
     return None if t is None else t.data_ptr()
+
+
+def ptr_table(addresses):
+    """Host array of device pointers (one per rank) for the `*_peers` arguments of the C ABI."""
+    return (ctypes.c_void_p * len(addresses))(*[int(a) for a in addresses])
 
 
 def stream_of(t: torch.Tensor):

@@ -115,17 +115,23 @@ def ep_moe(hidden, top_k_indices, top_k_weights, gate_up_proj_local, down_proj_l
 
 
 class ExpertParallelMoELayer(nn.Module):
-    """Router replicated on every rank, E/W experts per rank.  Gradients of the replicated router
+    """Router replicated on every rank, E/W experts per rank.  transport = "nccl" moves rows with
+    all_to_all_single; "p2p" uses the peer-memory kernels of csrc/ep.cu (rows are pulled over NVLink
+    inside the gather and combine kernels; needs torch symmetric memory and a fixed token count).  Gradients of the replicated router
     weight are local sums: all-reduce them (or wrap the module in DDP) as for any replicated
     parameter; expert gradients are complete on the owning rank."""
 
     def __init__(self, H, I, E, top_k=2, group=None, norm_topk_prob=True, routed_scaling_factor=1.0, init_std=0.02,
-                 overlap_chunks=1, reserved_sms=0):
+                 overlap_chunks=1, reserved_sms=0, transport="nccl"):
         """overlap_chunks > 1 splits the local tokens into that many independent pipelines on their own
         CUDA streams, so the all-to-alls of one chunk run while the expert GEMMs of another do;
         reserved_sms keeps that many SMs free of the persistent GEMM kernels for the communication
         kernels (process-wide setting of the library)."""
         super().__init__()
+        if transport not in ("nccl", "p2p"):
+            raise ValueError("transport must be 'nccl' (all_to_all_single) or 'p2p' (peer-memory kernels)")
+        self.transport = transport
+        self._workspace = None
         self.overlap_chunks = max(1, int(overlap_chunks))
         self.reserved_sms = int(reserved_sms)
         self._streams = None
@@ -151,6 +157,13 @@ class ExpertParallelMoELayer(nn.Module):
     def _pipeline(self, flat):
         idx, w, counts = fused_mlp_router(flat, self.gate.weight, self.bias, self.top_k, self.num_experts,
                                           self.norm_topk_prob, self.routed_scaling_factor, return_counts=True)
+        if self.transport == "p2p":
+            from .ep_p2p import SymmetricWorkspace, ep_moe_p2p
+            T, H = flat.shape
+            ws = self._workspace
+            if ws is None or (ws.T, ws.H, ws.k) != (T, H, self.top_k):
+                ws = self._workspace = SymmetricWorkspace(T, H, self.top_k, self.num_experts, self.group, flat.device)
+            return ep_moe_p2p(flat, idx, w, self.gate_up_proj, self.down_proj, ws), counts
         return ep_moe(flat, idx, w, self.gate_up_proj, self.down_proj, self.num_experts, self.group), counts
 
     def forward(self, x):

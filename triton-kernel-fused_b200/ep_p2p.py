@@ -1,0 +1,154 @@
+"""Expert-parallel exchange over peer memory: the payload of dispatch and combine never goes through
+a library collective or a staging buffer.  Owners PULL token rows from the home ranks' buffers while
+gathering them into their padded expert layout; home ranks PULL expert outputs while combining.
+Buffers that peers read live in one symmetric allocation per layer (torch symmetric memory gives
+the peer mappings and the cross-rank barrier); the kernels are in csrc/ep.cu.
+
+Per step and direction there is one tiny NCCL all-gather (the (W,E) count matrix, which also orders
+the phases), one host read of that matrix (to size the local buffers) and two device-side barriers.
+Constraint: one forward/backward in flight per workspace, because the symmetric buffers are reused.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+from . import ops
+from .moe import _amp_cast
+
+
+def _align(n, a=256):
+    return (n + a - 1) // a * a
+
+
+class SymmetricWorkspace:
+    """One symmetric allocation carved into the buffers peers read.  Sized for the worst case
+    (every routed row of every rank lands on one rank), so it is allocated once."""
+
+    def __init__(self, T, H, k, E, group, device):
+        import torch.distributed._symmetric_memory as symm
+        self.group = group
+        self.W = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.T, self.H, self.k, self.E = T, H, k, E
+        M = T * k
+        self.cap_w = L.padded_rows_cap(self.W * M, E // self.W)
+        fields = [("x", T * H * 2), ("go", T * H * 2), ("w", M * 4), ("order", M * 4), ("offs", (E + 1) * 4),
+                  ("eo", self.cap_w * H * 2), ("gxs", self.cap_w * H * 2), ("gw", self.cap_w * 4)]
+        self.offsets, total = {}, 0
+        for name, nbytes in fields:
+            self.offsets[name] = total
+            total += _align(nbytes)
+        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+        self.handle = symm.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+        base = [int(p) for p in self.handle.buffer_ptrs]
+        self.peers = {name: L.ptr_table([b + off for b in base]) for name, off in self.offsets.items()}
+        v = lambda name, n, dt: self.buf[self.offsets[name]: self.offsets[name] + n * dt.itemsize].view(dt)
+        self.x = v("x", T * H, torch.bfloat16).view(T, H)
+        self.go = v("go", T * H, torch.bfloat16).view(T, H)
+        self.w = v("w", M, torch.float32).view(T, k)
+        self.order = v("order", M, torch.int32)
+        self.offs = v("offs", E + 1, torch.int32)
+        self.eo = v("eo", self.cap_w * H, torch.bfloat16).view(self.cap_w, H)
+        self.gxs = v("gxs", self.cap_w * H, torch.bfloat16).view(self.cap_w, H)
+        self.gw = v("gw", self.cap_w, torch.float32)
+        self.generation = 0
+
+    def barrier(self):
+        self.handle.barrier(0)
+
+
+class _ExpertParallelP2P(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, idx, wt, gate_up_local, down_local, ws: SymmetricWorkspace):
+        hidden, gate_up_local, down_local = _amp_cast(hidden, gate_up_local, down_local)
+        for name, t in (("hidden", hidden), ("gate_up_proj", gate_up_local), ("down_proj", down_local)):
+            L.require_cuda_bf16(name, t)
+        W, rank, E = ws.W, ws.rank, ws.E
+        El = E // W
+        T, H = hidden.shape
+        k = idx.shape[1]
+        L.require((T, H, k) == (ws.T, ws.H, ws.k), f"workspace was built for T,H,k = {(ws.T, ws.H, ws.k)}, got {(T, H, k)}")
+        L.require(gate_up_local.shape[0] == El and down_local.shape[0] == El, f"this rank must hold {El} experts")
+        dev = hidden.device
+        st = L.stream_of(hidden)
+        lib = L.lib()
+        i32 = dict(dtype=torch.int32, device=dev)
+        idx = idx.contiguous()
+        w32 = wt.detach().float().contiguous()
+        gate_up_local, down_local = gate_up_local.contiguous(), down_local.contiguous()
+
+        perm = ops.permute_build(idx, E, want_order=True)
+        ws.x.copy_(hidden)
+        ws.order.copy_(perm.order)
+        ws.offs.copy_(perm.offs)
+        counts_all = torch.empty(W, E, **i32)
+        dist.all_gather_into_tensor(counts_all, perm.counts, group=ws.group)   # also: peers' x/order/offs are in place
+        R = int(counts_all[:, rank * El:(rank + 1) * El].sum().item())         # the one host sync
+        cap_l = L.padded_rows_cap(R, El)
+        poffs_l = torch.empty(El + 1, **i32)
+        counts_l = torch.empty(El, **i32)
+        tile_expert_l = torch.empty(cap_l // ops.TILE_M, **i32)
+        src_base = torch.empty(W * El, **i32)
+        dest_base = torch.empty(E, **i32)
+        L.check(lib.b200moe_ep_plan(L.ptr(counts_all), W, rank, E, L.ptr(poffs_l), L.ptr(counts_l),
+                                    L.ptr(tile_expert_l), L.ptr(src_base), L.ptr(dest_base), st))
+        x_s = torch.empty(cap_l, H, dtype=torch.bfloat16, device=dev)
+        row_src = torch.empty(cap_l, **i32)
+        row_slot_src = torch.empty(cap_l, **i32)
+        L.check(lib.b200moe_ep_gather_pull(ws.peers["x"], ws.peers["order"], ws.peers["offs"], L.ptr(counts_l),
+                                           L.ptr(poffs_l), L.ptr(tile_expert_l), L.ptr(src_base), W, rank, E, k, H,
+                                           cap_l, L.ptr(x_s), L.ptr(row_src), L.ptr(row_slot_src), st))
+        perm_l = ops.Permutation(R, 1, El, cap_l, counts_l, None, poffs_l, None, None, tile_expert_l, None, None)
+        gate_up, inter = ops.expert_gate_up_swiglu(x_s, gate_up_local, perm_l)
+        ops.expert_down(inter, down_local, perm_l, out=ws.eo[:cap_l])
+        ws.barrier()                                                # every owner's eo is complete
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        L.check(lib.b200moe_ep_combine_pull(ws.peers["eo"], L.ptr(w32), L.ptr(idx), L.ptr(perm.slot_pos),
+                                            L.ptr(perm.offs), L.ptr(dest_base), W, E, T, k, H, L.ptr(out), None, None, st))
+        ws.generation += 1
+        ctx.ws, ctx.perm, ctx.perm_l, ctx.gen = ws, perm, perm_l, ws.generation
+        ctx.tables = (dest_base, row_src, row_slot_src)
+        ctx.wt_dtype = wt.dtype
+        ctx.save_for_backward(idx, x_s, gate_up, inter, w32, gate_up_local, down_local)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        idx, x_s, gate_up, inter, w32, gate_up_local, down_local = ctx.saved_tensors
+        ws, perm, perm_l = ctx.ws, ctx.perm, ctx.perm_l
+        dest_base, row_src, row_slot_src = ctx.tables
+        if ws.generation != ctx.gen:
+            raise RuntimeError("the symmetric workspace was reused by another forward before this backward ran; "
+                               "use one workspace per forward in flight")
+        W, E = ws.W, ws.E
+        T, H, k = ws.T, ws.H, ws.k
+        cap_l = perm_l.cap
+        dev = x_s.device
+        st = L.stream_of(x_s)
+        lib = L.lib()
+        ws.go.copy_(grad_out)
+        ws.w.copy_(w32)
+        ws.barrier()                                                # every home rank's grad_out / w are in place
+        grad_eo = torch.empty(cap_l, H, dtype=torch.bfloat16, device=dev)
+        L.check(lib.b200moe_ep_combine_bwd_pull(ws.peers["go"], ws.peers["w"], L.ptr(ws.eo), L.ptr(row_src),
+                                                L.ptr(row_slot_src), L.ptr(perm_l.poffs[perm_l.E:]), W, k, H, cap_l,
+                                                L.ptr(grad_eo), L.ptr(ws.gw), st))
+        grad_gu = ops.expert_down_dgrad_glu(grad_eo, down_local, gate_up, perm_l)
+        grad_down = ops.expert_wgrad(grad_eo, inter, perm_l)
+        grad_gate_up = ops.expert_wgrad(grad_gu, x_s, perm_l)
+        ops.expert_gate_up_dgrad(grad_gu, gate_up_local, perm_l, out=ws.gxs[:cap_l])
+        ws.barrier()                                                # every owner's grad_x_s / gw are complete
+        grad_hidden = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        grad_w = torch.empty(T, k, dtype=torch.float32, device=dev)
+        L.check(lib.b200moe_ep_combine_pull(ws.peers["gxs"], None, L.ptr(idx), L.ptr(perm.slot_pos), L.ptr(perm.offs),
+                                            L.ptr(dest_base), W, E, T, k, H, L.ptr(grad_hidden), ws.peers["gw"],
+                                            L.ptr(grad_w), st))
+        return grad_hidden, None, grad_w.to(ctx.wt_dtype), grad_gate_up, grad_down, None
+
+
+def ep_moe_p2p(hidden, top_k_indices, top_k_weights, gate_up_proj_local, down_proj_local, workspace):
+    """Expert-parallel `moe` over peer memory; `workspace` is a SymmetricWorkspace of this layer."""
+    return _ExpertParallelP2P.apply(hidden, top_k_indices, top_k_weights, gate_up_proj_local, down_proj_local,
+                                    workspace)

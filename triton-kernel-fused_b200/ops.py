@@ -208,9 +208,9 @@ def expert_gate_up_swiglu(x_s, gate_up_proj, perm: Permutation):
 
 
 @_op("expert_down", 1)
-def expert_down(inter, down_proj, perm: Permutation):
+def expert_down(inter, down_proj, perm: Permutation, out=None):
     E, H, I = down_proj.shape
-    eo = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=inter.device)
+    eo = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=inter.device) if out is None else out
     L.check(L.lib().b200moe_expert_down(L.ptr(inter), L.ptr(down_proj), L.ptr(perm.tile_expert), L.ptr(perm.poffs),
                                         perm.cap, E, H, I, L.ptr(eo), L.ptr(L.status_word(inter.device)),
                                         L.stream_of(inter)))
@@ -229,9 +229,9 @@ def expert_down_dgrad_glu(grad_eo, down_proj, gate_up, perm: Permutation):
 
 
 @_op("expert_gate_up_dgrad", 1)
-def expert_gate_up_dgrad(grad_gate_up, gate_up_proj, perm: Permutation):
+def expert_gate_up_dgrad(grad_gate_up, gate_up_proj, perm: Permutation, out=None):
     E, twoI, H = gate_up_proj.shape
-    gx = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=grad_gate_up.device)
+    gx = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=grad_gate_up.device) if out is None else out
     L.check(L.lib().b200moe_expert_gate_up_dgrad(L.ptr(grad_gate_up), L.ptr(gate_up_proj), L.ptr(perm.tile_expert),
                                                  L.ptr(perm.poffs), perm.cap, E, H, twoI // 2, L.ptr(gx),
                                                  L.ptr(L.status_word(gx.device)), L.stream_of(gx)))
