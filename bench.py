@@ -166,27 +166,69 @@ def run_ours(args):
         out.backward(go_dev)
         return out, x.grad
 
+    # e2e: every step copies its inputs from pinned host memory and its results back.  The copies run
+    # on two copy streams with double-buffered device tensors, so step i+1's H2D and step i-1's D2H
+    # overlap step i's kernels (a user's input pipeline does the same); nothing is skipped.
+    h2d, d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    in_bufs = [(torch.empty_like(x_dev), torch.empty_like(go_dev)) for _ in range(2)]
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+    out_done = [torch.cuda.Event() for _ in range(2)]
+    e2e_state = {"i": 0, "primed": False}
+
+    def _upload(slot):
+        with torch.cuda.stream(h2d):
+            h2d.wait_event(in_free[slot])
+            in_bufs[slot][0].copy_(x_host, non_blocking=True)
+            in_bufs[slot][1].copy_(go_host, non_blocking=True)
+            in_ready[slot].record(h2d)
+
     def step_e2e():
+        cur = torch.cuda.current_stream(dev)
+        i = e2e_state["i"]
+        slot = i & 1
+        if not e2e_state["primed"]:
+            for ev in in_free + out_done:
+                ev.record(cur)
+            _upload(slot)
+            e2e_state["primed"] = True
+        _upload(slot ^ 1)                      # next step's inputs travel while this step computes
         for p in params:
             p.grad = None
-        x = x_host.to(dev, non_blocking=True).requires_grad_(True)
-        go = go_host.to(dev, non_blocking=True)
+        cur.wait_event(in_ready[slot])
+        x = in_bufs[slot][0].detach().requires_grad_(True)
         out = layer(x)
-        out.backward(go)
-        out_host.copy_(out.detach(), non_blocking=True)
-        gx_host.copy_(x.grad, non_blocking=True)
+        out.backward(in_bufs[slot][1])
+        in_free[slot].record(cur)
+        done = torch.cuda.Event()
+        done.record(cur)
+        with torch.cuda.stream(d2h):
+            d2h.wait_event(done)
+            out_host.copy_(out.detach(), non_blocking=True)
+            gx_host.copy_(x.grad, non_blocking=True)
+            out.record_stream(d2h)
+            x.grad.record_stream(d2h)
+            out_done[slot].record(d2h)
+        cur.wait_event(out_done[slot ^ 1])     # at most one result copy in flight behind the compute
+        e2e_state["i"] = i + 1
+
+    def drain_e2e():
+        torch.cuda.current_stream(dev).wait_stream(d2h)
+        torch.cuda.current_stream(dev).wait_stream(h2d)
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, steps, after=None):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
             fn()
+        if after is not None:
+            after()                       # the last copies finish inside the timed region
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
@@ -223,7 +265,7 @@ def run_ours(args):
     # ---- timed region 2: through the module with host buffers
     for _ in range(min(2, n_warm)):
         step_e2e()
-    ms_e2e = timed(step_e2e, args.steps) / args.steps
+    ms_e2e = timed(lambda: step_e2e(), args.steps, after=drain_e2e) / args.steps
     pkg.check_status()
 
     if rank != 0:
