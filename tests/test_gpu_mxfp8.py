@@ -11,6 +11,13 @@ DEV = "cuda"
 TOL_MX = 5e-2       # stated gate for the MXFP8 path
 
 
+def _sf_equal(sf_dev, cs):
+    """Scale atoms agree on every live (row, k-block); the bytes that pad the last 128-row block or
+    the last 4-block chunk are never read by a GEMM and are left unwritten by the quantisers."""
+    live = Q.sf_atoms(torch.ones_like(cs)) == 1
+    return torch.equal(sf_dev.cpu()[live], Q.sf_atoms(cs)[live])
+
+
 def test_quant_rows_bit_exact(pkg):
     g = torch.Generator().manual_seed(0)
     x = (torch.randn(333, 384, generator=g) * torch.logspace(-4, 4, 333)[:, None]).to(torch.bfloat16)
@@ -19,7 +26,7 @@ def test_quant_rows_bit_exact(pkg):
     q, sf = pkg.ops.mxfp8_quant_rows(x.to(DEV))
     cq, cs = Q.quantise(x.float())
     assert torch.equal(q.cpu(), cq)
-    assert torch.equal(sf.cpu(), Q.sf_atoms(cs))
+    assert _sf_equal(sf, cs)
 
 
 def test_quant_rows_interleave_and_transpose_bit_exact(pkg):
@@ -30,12 +37,12 @@ def test_quant_rows_interleave_and_transpose_bit_exact(pkg):
     perm = torch.cat([torch.cat([torch.arange(j, j + 64), I + torch.arange(j, j + 64)]) for j in range(0, I, 64)])
     wi = w[:, perm, :].reshape(E * 2 * I, H)
     cq, cs = Q.quantise(wi.float())
-    assert torch.equal(q.cpu(), cq) and torch.equal(sf.cpu(), Q.sf_atoms(cs))
+    assert torch.equal(q.cpu(), cq) and _sf_equal(sf, cs)
     qt, sft = pkg.ops.mxfp8_quant_transpose(w.to(DEV))
     wt = w.float().transpose(1, 2).contiguous()
     cq, cs = Q.quantise(wt)
     assert torch.equal(qt.cpu(), cq)
-    assert torch.equal(sft.cpu(), Q.sf_atoms(cs.reshape(-1, cs.shape[-1])))
+    assert _sf_equal(sft, cs.reshape(-1, cs.shape[-1]))
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 264, 1024), (1000, 2048, 512), (64, 72, 256)])
