@@ -131,6 +131,15 @@ int b200moe_expert_gate_up_swiglu(const void* x_s, const void* gate_up_proj,
                                   const int32_t* tile_expert, const int32_t* poffs,
                                   int64_t rows_cap, int E, int64_t H, int64_t I, void* gate_up,
                                   void* inter, int32_t* status, b200moe_stream_t stream);
+/* Generic grouped products over the padded rows (the two entry points after them are special cases):
+ * linear:   out (rows,N) = a (rows,K) * W[e]^T, W (E,N,K)   -- kernels/sm75/moe.py:765,770 (x @ W[e].t())
+ * linear_t: out (rows,N) = a (rows,K) * W[e],   W (E,K,N)   -- kernels/sm75/moe.py:807,822 (g @ W[e]) */
+int b200moe_expert_linear(const void* a, const void* w, const int32_t* tile_expert, const int32_t* poffs,
+                          int64_t rows_cap, int E, int64_t N, int64_t K, void* out, int32_t* status,
+                          b200moe_stream_t stream);
+int b200moe_expert_linear_t(const void* a, const void* w, const int32_t* tile_expert, const int32_t* poffs,
+                            int64_t rows_cap, int E, int64_t K, int64_t N, void* out, int32_t* status,
+                            b200moe_stream_t stream);
 /* Replaces the down GEMM (kernels/sm75/moe.py:592, :770): eo (rows,H) = inter * W_d[e]^T. */
 int b200moe_expert_down(const void* inter, const void* down_proj, const int32_t* tile_expert,
                         const int32_t* poffs, int64_t rows_cap, int E, int64_t H, int64_t I,
@@ -152,6 +161,29 @@ int b200moe_expert_gate_up_dgrad(const void* grad_gate_up, const void* gate_up_p
 int b200moe_expert_wgrad(const void* A, const void* B, const int32_t* poffs, const int32_t* counts,
                          int64_t rows_cap, int E, int64_t Na, int64_t Nb, void* out, int32_t* status,
                          b200moe_stream_t stream);
+
+/* ---- PolyGLU activations as row kernels (expert stacks that are not pure SiLU-GLU) -------------
+ * Replace _glu_fwd / _glu_bwd (kernels/sm75/moe.py:363-434, kernels :163-232).  act_codes (E_total)
+ * int32: 0 SiLU, 1 ReLU^2, 2 NormSiLU, 5 SiTU, 6 NormReLU^2, 7 NormSiTU (3 Identity / 4 Zero are expert
+ * kinds, see special_rows); act_params (E_total,2) fp32 [alpha,gamma] for code 5 or NULL.  Rows below
+ * *total_rows are processed; the code of a row is that of its tile's expert. */
+int b200moe_glu_fwd_rows(const void* gate_up, const int32_t* tile_expert, const int32_t* act_codes,
+                         const float* act_params, const int32_t* total_rows, int64_t rows_cap, int64_t I,
+                         void* inter, b200moe_stream_t stream);
+/* grad_gate_up (rows,2I) from grad_inter (rows,I) and the saved gate_up; row_da/row_dg (rows, nullable):
+ * per-row gradient of alpha / gamma for code-5 rows. */
+int b200moe_glu_bwd_rows(const void* grad_inter, const void* gate_up, const int32_t* tile_expert,
+                         const int32_t* act_codes, const float* act_params, const int32_t* total_rows,
+                         int64_t rows_cap, int64_t I, void* grad_gate_up, float* row_da, float* row_dg,
+                         b200moe_stream_t stream);
+/* out (E,2) = per-expert sums of row_da, row_dg (grad of act_params, kernels/sm75/moe.py:814-815). */
+int b200moe_expert_row_sums(const float* row_da, const float* row_dg, const int32_t* poffs, int E, float* out,
+                            b200moe_stream_t stream);
+/* Identity / Zero experts (kernels/sm75/moe.py:761-764, :798-803): for the rows of experts
+ * [first_special, num_experts): dst[row] = src[row] if the expert's code is 3, else 0. */
+int b200moe_special_rows(const void* src, const int32_t* tile_expert, const int32_t* act_codes,
+                         const int32_t* poffs, int first_special, int num_experts, int64_t H, int64_t rows_cap,
+                         void* dst, b200moe_stream_t stream);
 
 /* ---- MXFP8 (e4m3 elements, E8M0 scale per 32 elements along K) ---------------------------------
  * The reference has no MXFP8 path; these follow the OCP MX convention: scale exponent =

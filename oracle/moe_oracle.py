@@ -275,3 +275,51 @@ def make_inputs(T, H, E, I, k, seed=0, bias_std=0.0, zipf_s=None, dtype=torch.fl
     cast = lambda t: t.to(dtype)
     return dict(x=cast(x), gate_weight=cast(wr), gate_up=cast(gu), down=cast(dn),
                 grad_out=cast(go), bias=bias.float(), logit_bias=logit_bias)
+
+
+# ----------------------------------------------------------------------------- PolyGLU
+RMS_EPS = 1e-6      # _NS_EPS, kernels/sm75/moe.py:80
+
+
+def polyglu_act(gate: torch.Tensor, code: int, alpha=1.0, gamma=1.0) -> torch.Tensor:
+    """Activation of the gate half for act code `code`, fp32 (kernels/sm75/moe.py:859-881):
+    0 SiLU, 1 ReLU^2, 2 NormSiLU, 5 SiTU gamma*tanh(alpha g)*sigmoid(g), 6 NormReLU^2, 7 NormSiTU;
+    the Norm codes first divide each row by sqrt(mean(g^2) + 1e-6)."""
+    g = gate.float()
+    if code in (2, 6, 7):
+        g = g * torch.rsqrt(g.square().mean(-1, keepdim=True) + RMS_EPS)
+    if code in (0, 2):
+        return g * torch.sigmoid(g)
+    if code in (1, 6):
+        return torch.relu(g) ** 2
+    if code == 5:
+        return gamma * torch.tanh(alpha * g) * torch.sigmoid(g)
+    if code == 7:
+        return torch.tanh(g) * torch.sigmoid(g)
+    raise ValueError(f"not a GLU act code: {code}")
+
+
+def moe_experts_polyglu(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, codes, act_params=None):
+    """moe_eager with heterogeneous experts (kernels/sm75/moe.py:884-909): GLU experts use weight
+    slot e; Identity (3) passes the weighted input through; Zero (4) contributes nothing."""
+    N, H = hidden.shape
+    I = gate_up_proj.shape[1] // 2
+    E = len(codes)
+    order, st, counts, offs = sort_by_expert_stable(top_k_indices, E)
+    sw = top_k_weights.flatten()[order]
+    out = torch.zeros(N, H, dtype=torch.float32)
+    w_gu, w_dn = gate_up_proj.unbind(0), down_proj.unbind(0)
+    for e in range(E):
+        s, en = int(offs[e]), int(offs[e + 1])
+        if en == s or codes[e] == 4:
+            continue
+        rows = st[s:en]
+        w = sw[s:en].unsqueeze(-1)
+        if codes[e] == 3:
+            out = out.index_add(0, rows, (hidden[rows] * w).float())
+            continue
+        gu = hidden[rows] @ w_gu[e].t()
+        a, g = (act_params[e, 0], act_params[e, 1]) if (codes[e] == 5 and act_params is not None) else (1.0, 1.0)
+        inter = polyglu_act(gu[:, :I], codes[e], a, g).to(gu.dtype) * gu[:, I:]
+        out = out.index_add(0, rows, ((inter @ w_dn[e].t()) * w).float())
+    return out.to(hidden.dtype)

@@ -27,7 +27,7 @@ sys.path.insert(0, REF)
 from kernels.sm75.moe import moe_eager, _sort_by_expert   # noqa: E402  (the reference itself)
 from oracle import moe_oracle as O                        # noqa: E402
 
-from tests.golden.cases import CASES, routing_for, sub  # noqa: E402
+from tests.golden.cases import CASES, POLY_CASES, poly_inputs, routing_for, sub  # noqa: E402
 
 
 def main():
@@ -58,6 +58,27 @@ def main():
             counts=np.asarray(counts, dtype=np.int64), bounds=np.asarray(bounds, dtype=np.int64),
             seg_sorted_tokens=seg_sorted.numpy())
         print(name, "out", tuple(out.shape), "counts", counts)
+    # PolyGLU cases: the reference's moe_eager with heterogeneous act codes, specials and act_params
+    poly = {}
+    for name in POLY_CASES:
+        c = poly_inputs(name)
+        h, wt, gu, dn = (c[k].clone().requires_grad_(True) for k in ("hidden", "w", "gate_up", "down"))
+        ap = c["act_params"].clone().requires_grad_(True) if c["act_params"] is not None else None
+        codes = torch.tensor(c["codes"], dtype=torch.int32)
+        out = moe_eager(h, c["idx"], wt, gu, dn, codes, ap)
+        (out * c["grad_out"]).sum().backward()
+        f16 = lambda t: t.detach().to(torch.float16).numpy()
+        poly[f"{name}.out"] = f16(out)
+        poly[f"{name}.grad_hidden"] = f16(h.grad)
+        poly[f"{name}.grad_w"] = wt.grad.numpy()
+        poly[f"{name}.grad_gate_up_sub"] = f16(gu.grad[:, ::4, ::4])
+        poly[f"{name}.grad_down_sub"] = f16(dn.grad[:, ::4, ::4])
+        poly[f"{name}.grad_gate_up_norm"] = np.float64(gu.grad.double().norm())
+        poly[f"{name}.grad_down_norm"] = np.float64(dn.grad.double().norm())
+        if ap is not None and ap.grad is not None:
+            poly[f"{name}.grad_act_params"] = ap.grad.numpy()
+        print("poly", name, float(out.abs().max()))
+    np.savez_compressed(os.path.join(HERE, "polyglu.npz"), **poly)
 
 
 if __name__ == "__main__":

@@ -73,5 +73,7 @@ def test_cpu_tensors_are_rejected():
     codes = torch.zeros(2, dtype=torch.int32)
     with pytest.raises(ValueError, match="CUDA"):
         pkg.moe(x, idx, w, gu, dn, codes)
-    with pytest.raises(ValueError, match="act code 0"):
-        pkg.moe(x, idx, w, gu, dn, torch.tensor([0, 1], dtype=torch.int32))
+    with pytest.raises(ValueError, match="unknown act code 9"):
+        pkg.moe(x, idx, w, gu, dn, torch.tensor([0, 9], dtype=torch.int32))
+    with pytest.raises(ValueError, match="must precede"):
+        pkg.moe(x, idx, w, gu, dn, torch.tensor([3, 0, 1], dtype=torch.int32))

@@ -757,20 +757,42 @@ int b200moe_expert_gate_up_swiglu(const void* x_s, const void* gate_up_proj, con
   return dispatch_bn<EPI_SWIGLU>(bn, a, b, &d1, &d2, p, 0, (cudaStream_t)stream);
 }
 
+int b200moe_expert_linear(const void* a, const void* w, const int32_t* tile_expert, const int32_t* poffs,
+                          int64_t rows_cap, int E, int64_t N, int64_t K, void* out, int32_t* status,
+                          b200moe_stream_t stream) {
+  int rc = check_grouped("expert_linear", a, w, out, tile_expert, poffs, rows_cap, E, N, K);
+  if (rc) return rc;
+  B200_CHECK_ARG(tile_expert, B200MOE_E_NULL, "expert_linear: null pointer");
+  B200_CHECK_ARG(aligned16(out), B200MOE_E_ALIGN, "expert_linear: output not aligned");
+  Operand oa{a, 0, rows_cap, K, K, 1, rows_cap * K};
+  Operand ob{w, 0, N, K, K, E, N * K};   // W (E, N, K): rows = output columns
+  GemmParams p{};
+  p.sched = SCHED_GROUPED_M; p.N = (int)N; p.K = (int)K; p.num_groups = E;
+  p.tile_expert = tile_expert; p.poffs = poffs; p.D = out; p.ldd = N; p.status = status;
+  Operand d{out, 0, rows_cap, N, N, 1, rows_cap * N};
+  return dispatch_bn<EPI_STORE>(pick_bn(N) == 64 ? 128 : pick_bn(N), oa, ob, &d, nullptr, p, 0, (cudaStream_t)stream);
+}
+
+int b200moe_expert_linear_t(const void* a, const void* w, const int32_t* tile_expert, const int32_t* poffs,
+                            int64_t rows_cap, int E, int64_t K, int64_t N, void* out, int32_t* status,
+                            b200moe_stream_t stream) {
+  int rc = check_grouped("expert_linear_t", a, w, out, tile_expert, poffs, rows_cap, E, N, K);
+  if (rc) return rc;
+  B200_CHECK_ARG(tile_expert, B200MOE_E_NULL, "expert_linear_t: null pointer");
+  B200_CHECK_ARG(aligned16(out), B200MOE_E_ALIGN, "expert_linear_t: output not aligned");
+  Operand oa{a, 0, rows_cap, K, K, 1, rows_cap * K};
+  Operand ob{w, 1, N, K, N, E, K * N};   // W[e] stored (K, N): MN-major
+  GemmParams p{};
+  p.sched = SCHED_GROUPED_M; p.b_mn = 1; p.N = (int)N; p.K = (int)K; p.num_groups = E;
+  p.tile_expert = tile_expert; p.poffs = poffs; p.D = out; p.ldd = N; p.status = status;
+  Operand d{out, 0, rows_cap, N, N, 1, rows_cap * N};
+  return dispatch_bn<EPI_STORE>(pick_bn(N) == 64 ? 128 : pick_bn(N), oa, ob, &d, nullptr, p, 0, (cudaStream_t)stream);
+}
+
 int b200moe_expert_down(const void* inter, const void* down_proj, const int32_t* tile_expert, const int32_t* poffs,
                         int64_t rows_cap, int E, int64_t H, int64_t I, void* eo, int32_t* status,
                         b200moe_stream_t stream) {
-  int rc = check_grouped("expert_down", inter, down_proj, eo, tile_expert, poffs, rows_cap, E, H, I);
-  if (rc) return rc;
-  B200_CHECK_ARG(tile_expert, B200MOE_E_NULL, "expert_down: null pointer");
-  B200_CHECK_ARG(aligned16(eo), B200MOE_E_ALIGN, "expert_down: output not aligned");
-  Operand a{inter, 0, rows_cap, I, I, 1, rows_cap * I};
-  Operand b{down_proj, 0, H, I, I, E, H * I};   // W_d (E, H, I): rows = H (output cols), K = I
-  GemmParams p{};
-  p.sched = SCHED_GROUPED_M; p.N = (int)H; p.K = (int)I; p.num_groups = E;
-  p.tile_expert = tile_expert; p.poffs = poffs; p.D = eo; p.ldd = H; p.status = status;
-  Operand d{eo, 0, rows_cap, H, H, 1, rows_cap * H};
-  return dispatch_bn<EPI_STORE>(pick_bn(H) == 64 ? 128 : pick_bn(H), a, b, &d, nullptr, p, 0, (cudaStream_t)stream);
+  return b200moe_expert_linear(inter, down_proj, tile_expert, poffs, rows_cap, E, H, I, eo, status, stream);
 }
 
 int b200moe_expert_down_dgrad_glu(const void* grad_eo, const void* down_proj, const void* gate_up,
@@ -796,17 +818,8 @@ int b200moe_expert_down_dgrad_glu(const void* grad_eo, const void* down_proj, co
 int b200moe_expert_gate_up_dgrad(const void* grad_gate_up, const void* gate_up_proj, const int32_t* tile_expert,
                                  const int32_t* poffs, int64_t rows_cap, int E, int64_t H, int64_t I,
                                  void* grad_x_s, int32_t* status, b200moe_stream_t stream) {
-  int rc = check_grouped("expert_gate_up_dgrad", grad_gate_up, gate_up_proj, grad_x_s, tile_expert, poffs, rows_cap, E, H, I);
-  if (rc) return rc;
-  B200_CHECK_ARG(tile_expert, B200MOE_E_NULL, "expert_gate_up_dgrad: null pointer");
-  B200_CHECK_ARG(aligned16(grad_x_s), B200MOE_E_ALIGN, "expert_gate_up_dgrad: output not aligned");
-  Operand a{grad_gate_up, 0, rows_cap, 2 * I, 2 * I, 1, rows_cap * 2 * I};
-  Operand b{gate_up_proj, 1, H, 2 * I, H, E, 2 * I * H};   // W_gu[e] stored (K=2I, N=H): MN-major
-  GemmParams p{};
-  p.sched = SCHED_GROUPED_M; p.b_mn = 1; p.N = (int)H; p.K = (int)(2 * I); p.num_groups = E;
-  p.tile_expert = tile_expert; p.poffs = poffs; p.D = grad_x_s; p.ldd = H; p.status = status;
-  Operand d{grad_x_s, 0, rows_cap, H, H, 1, rows_cap * H};
-  return dispatch_bn<EPI_STORE>(pick_bn(H) == 64 ? 128 : pick_bn(H), a, b, &d, nullptr, p, 0, (cudaStream_t)stream);
+  return b200moe_expert_linear_t(grad_gate_up, gate_up_proj, tile_expert, poffs, rows_cap, E, 2 * I, H, grad_x_s,
+                                 status, stream);
 }
 
 int b200moe_expert_wgrad(const void* A, const void* B, const int32_t* poffs, const int32_t* counts, int64_t rows_cap,

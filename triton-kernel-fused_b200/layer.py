@@ -15,17 +15,25 @@ __all__ = ["MoELayer"]
 
 class MoELayer(nn.Module):
     def __init__(self, H, I, E, top_k=2, norm_topk_prob=True, routed_scaling_factor=1.0, init_std=0.02,
-                 precision="bf16"):
+                 precision="bf16", act_codes=None, learnable_situ=False):
+        """act_codes: one activation code per expert (default all 0 = SiLU-GLU); Identity (3) / Zero (4)
+        experts come last and carry no weights.  learnable_situ adds an (E,2) [alpha,gamma] parameter
+        for the code-5 experts."""
         super().__init__()
         if precision not in ("bf16", "mxfp8"):
             raise ValueError("precision must be 'bf16' or 'mxfp8'")
         self.precision = precision
+        codes = [0] * E if act_codes is None else [int(c) for c in act_codes]
+        if len(codes) != E:
+            raise ValueError("act_codes needs one code per expert")
+        n_glu = sum(1 for c in codes if c not in (3, 4))
         self.gate = nn.Linear(H, E, bias=False)
-        self.gate_up_proj = nn.Parameter(torch.randn(E, 2 * I, H) * init_std)
-        self.down_proj = nn.Parameter(torch.randn(E, H, I) * init_std)
+        self.gate_up_proj = nn.Parameter(torch.randn(n_glu, 2 * I, H) * init_std)
+        self.down_proj = nn.Parameter(torch.randn(n_glu, H, I) * init_std)
+        self.act_params = nn.Parameter(torch.ones(E, 2)) if learnable_situ else None
         with torch.no_grad():
             self.gate.weight.normal_(0.0, init_std)
-        self.register_buffer("act_codes", torch.zeros(E, dtype=torch.int32))
+        self.register_buffer("act_codes", torch.tensor(codes, dtype=torch.int32))
         self.register_buffer("bias", torch.zeros(E, dtype=torch.float32))
         self.top_k = top_k
         self.num_experts = E
@@ -36,7 +44,8 @@ class MoELayer(nn.Module):
     def _apply(self, fn, *a, **kw):
         super()._apply(fn, *a, **kw)
         self.bias.data = self.bias.data.float()        # the selection bias stays fp32
-        self.act_codes._code_max_cache = 0
+        if self.act_params is not None:
+            self.act_params.data = self.act_params.data.float()
         return self
 
     def forward(self, x):                               # x: (B,S,H) or (N,H)
@@ -46,7 +55,7 @@ class MoELayer(nn.Module):
                                           self.norm_topk_prob, self.routed_scaling_factor, return_counts=True)
         self.last_counts = counts
         fn = moe_mxfp8 if self.precision == "mxfp8" else moe
-        out = fn(flat, idx, w, self.gate_up_proj, self.down_proj, self.act_codes)
+        out = fn(flat, idx, w, self.gate_up_proj, self.down_proj, self.act_codes, self.act_params)
         return out.reshape(shape)
 
     @torch.no_grad()

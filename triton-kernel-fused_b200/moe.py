@@ -17,19 +17,6 @@ __all__ = ["moe", "moe_grouped", "moe_per_expert", "GROUPED_MIN_TOKENS"]
 GROUPED_MIN_TOKENS = 4096   # kept for API compatibility (kernels/sm75/moe.py:78); one path here
 
 
-def _code_max(act_codes: torch.Tensor) -> int:
-    """Largest activation code (negative codes count as unsupported), one host sync per tensor
-    lifetime: act_codes is static model config (kernels/sm75/moe.py:84-94)."""
-    m = getattr(act_codes, "_code_max_cache", None)
-    if m is None:
-        m = int(act_codes.abs().max()) if act_codes.numel() else 0
-        try:
-            act_codes._code_max_cache = m
-        except Exception:
-            pass
-    return m
-
-
 def _amp_cast(*ts):
     """Under CUDA autocast cast float tensors to the autocast dtype (kernels/sm75/moe.py:97-104)."""
     if torch.is_autocast_enabled("cuda"):
@@ -94,23 +81,116 @@ class _GroupedMoE(torch.autograd.Function):
         return grad_hidden, None, grad_wt, grad_gate_up_proj, grad_down_proj, None
 
 
-def _check_codes(act_codes, act_params):
-    if act_params is not None:
-        raise ValueError("act_params (learnable SiTU, code 5) is not built in this library; only act code 0 (SwiGLU)")
-    if _code_max(act_codes) != 0:
-        raise ValueError("only act code 0 (SiLU-GLU) is built in this library; codes 1-7 are unsupported")
+GLU_CODES = (0, 1, 2, 5, 6, 7)     # weight-carrying experts (kernels/sm75/moe.py:1-31)
+SPECIAL_CODES = (3, 4)             # Identity, Zero: expert kinds without weights, listed after the GLU experts
+
+
+def _code_info(act_codes: torch.Tensor):
+    """(codes tuple, number of GLU experts), read from the device once per tensor lifetime: act_codes
+    is static model config (the reference reads it with .tolist() on every call, moe.py:741)."""
+    info = getattr(act_codes, "_code_info_cache", None)
+    if info is None:
+        codes = tuple(int(c) for c in act_codes.tolist())
+        for c in codes:
+            if c not in GLU_CODES + SPECIAL_CODES:
+                raise ValueError(f"unknown act code {c}; supported: 0 SiLU, 1 ReLU^2, 2 NormSiLU, 3 Identity, "
+                                 "4 Zero, 5 SiTU, 6 NormReLU^2, 7 NormSiTU")
+        n_glu = sum(1 for c in codes if c in GLU_CODES)
+        if any(c in SPECIAL_CODES for c in codes[:n_glu]):
+            raise ValueError("GLU act codes must precede the Identity/Zero experts in act_codes")
+        info = (codes, n_glu)
+        try:
+            act_codes._code_info_cache = info
+        except Exception:
+            pass
+    return info
+
+
+class _PolyGLUMoE(torch.autograd.Function):
+    """Generic path for stacks that are not pure SiLU-GLU: the same sort / GEMMs / combine, with the
+    activation as row kernels between the GEMMs (Norm codes need a row reduction over d_ff) and the
+    Identity / Zero experts handled on their rows.  Mirrors _PerExpertMoE (kernels/sm75/moe.py:724-826)."""
+
+    @staticmethod
+    def forward(ctx, hidden, idx, wt, gate_up_proj, down_proj, act_codes, act_params):
+        hidden, gate_up_proj, down_proj = _amp_cast(hidden, gate_up_proj, down_proj)
+        for name, t in (("hidden", hidden), ("gate_up_proj", gate_up_proj), ("down_proj", down_proj)):
+            L.require_cuda_bf16(name, t)
+        codes, n_glu = _code_info(act_codes)
+        E_total = len(codes)
+        N, H = hidden.shape
+        E, twoI, H2 = gate_up_proj.shape
+        I = twoI // 2
+        L.require(E == n_glu, f"gate_up_proj holds {E} experts but act_codes lists {n_glu} GLU experts")
+        L.require(H2 == H and tuple(down_proj.shape) == (E, H, I), "weight shapes must be (E,2I,H) and (E,H,I)")
+        L.require(tuple(idx.shape) == tuple(wt.shape) and idx.shape[0] == N, "indices/weights must be (N,k)")
+        hidden, gate_up_proj, down_proj = hidden.contiguous(), gate_up_proj.contiguous(), down_proj.contiguous()
+        w32 = wt.detach().float().contiguous()
+        codes_dev = act_codes.to(device=hidden.device, dtype=torch.int32).contiguous()
+        ap32 = None
+        if act_params is not None:
+            L.require(tuple(act_params.shape) == (E_total, 2), "act_params must be (E,2) [alpha, gamma]")
+            ap32 = act_params.detach().float().contiguous()
+
+        import dataclasses
+        perm = ops.permute_build(idx, E_total)
+        perm_glu = dataclasses.replace(perm, E=n_glu)          # GEMMs and row kernels see the GLU rows only
+        x_s = ops.gather_rows(hidden, perm)
+        gate_up = ops.expert_linear(x_s, gate_up_proj, perm_glu)
+        inter = ops.glu_fwd_rows(gate_up, codes_dev, ap32, perm_glu)
+        eo = ops.expert_linear(inter, down_proj, perm_glu)
+        if n_glu < E_total:
+            ops.special_rows(x_s, eo, codes_dev, perm, n_glu)
+        out = ops.combine(eo, w32, perm)
+
+        ctx.perm, ctx.perm_glu, ctx.n_glu, ctx.E_total = perm, perm_glu, n_glu, E_total
+        ctx.wt_dtype = wt.dtype
+        ctx.has_params = ap32 is not None
+        ctx.save_for_backward(x_s, gate_up, inter, eo, w32, gate_up_proj, down_proj, codes_dev,
+                              ap32 if ap32 is not None else torch.empty(0, device=hidden.device))
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x_s, gate_up, inter, eo, w32, gate_up_proj, down_proj, codes_dev, ap32 = ctx.saved_tensors
+        ap32 = ap32 if ctx.has_params else None
+        perm, perm_glu, n_glu = ctx.perm, ctx.perm_glu, ctx.n_glu
+        need_x, _, need_w, need_gu, need_dn, _, need_ap = ctx.needs_input_grad
+        want_ap = bool(ctx.has_params and need_ap)
+        grad_out = grad_out.contiguous().to(torch.bfloat16)
+        grad_eo, grad_w = ops.combine_bwd(grad_out, eo, w32, perm)
+        grad_inter = ops.expert_linear_t(grad_eo, down_proj, perm_glu)
+        grad_gu, row_da, row_dg = ops.glu_bwd_rows(grad_inter, gate_up, codes_dev, ap32, perm_glu, want_ap)
+        grad_down_proj = ops.expert_wgrad(grad_eo, inter, perm_glu) if need_dn else None
+        grad_gate_up_proj = ops.expert_wgrad(grad_gu, x_s, perm_glu) if need_gu else None
+        grad_hidden = None
+        if need_x:
+            grad_x_s = ops.expert_linear_t(grad_gu, gate_up_proj, perm_glu)
+            if n_glu < ctx.E_total:
+                ops.special_rows(grad_eo, grad_x_s, codes_dev, perm, n_glu)
+            grad_hidden = ops.combine(grad_x_s, None, perm)
+        grad_ap = None
+        if want_ap:
+            grad_ap = torch.zeros(ctx.E_total, 2, dtype=torch.float32, device=x_s.device)
+            ops.expert_row_sums(row_da, row_dg, perm_glu, grad_ap)
+        grad_wt = grad_w.to(ctx.wt_dtype) if need_w else None
+        return grad_hidden, None, grad_wt, grad_gate_up_proj, grad_down_proj, None, grad_ap
 
 
 def moe(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes, act_params=None):
-    """hidden (N,H) bf16, indices (N,k) int64, weights (N,k) float, gate_up_proj (E,2I,H),
-    down_proj (E,H,I), act_codes (E,) int32 (all 0) -> (N,H).  Same contract as the reference's
-    `moe` (kernels/sm75/moe.py:838-855); differentiable w.r.t. hidden, weights and both projections."""
-    _check_codes(act_codes, act_params)
-    return _GroupedMoE.apply(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes)
+    """hidden (N,H) bf16, indices (N,k) int64, weights (N,k) float, gate_up_proj (E_glu,2I,H),
+    down_proj (E_glu,H,I), act_codes (E,) int32, act_params (E,2) fp32 [alpha,gamma] for code 5 or None
+    -> (N,H).  Same contract as the reference's `moe` (kernels/sm75/moe.py:838-855); differentiable
+    w.r.t. hidden, weights, both projections and act_params.  A pure SiLU-GLU stack runs with the
+    activation fused into the GEMM epilogues; any other stack runs the PolyGLU row kernels."""
+    codes, n_glu = _code_info(act_codes)
+    if act_params is None and n_glu == len(codes) and all(c == 0 for c in codes):
+        return _GroupedMoE.apply(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes)
+    return _PolyGLUMoE.apply(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes, act_params)
 
 
 def moe_grouped(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes):
-    """Same signature as kernels/sm75/moe.py:621."""
+    """Same signature as kernels/sm75/moe.py:621 (which has no act_params: code 5 runs parameter-free)."""
     return moe(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes)
 
 

@@ -13,7 +13,7 @@ import torch
 
 from . import _lib as L
 from . import ops
-from .moe import _amp_cast, _check_codes
+from .moe import _amp_cast, _code_info
 
 __all__ = ["moe_mxfp8"]
 
@@ -89,5 +89,7 @@ class _MoEMxfp8(torch.autograd.Function):
 
 def moe_mxfp8(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes, act_params=None):
     """Same contract as `moe`; expert GEMMs in MXFP8 (e4m3 + E8M0 block-32 scales), bf16 in and out."""
-    _check_codes(act_codes, act_params)
+    codes, n_glu = _code_info(act_codes)
+    if act_params is not None or n_glu != len(codes) or any(c != 0 for c in codes):
+        raise ValueError("the MXFP8 path is built for pure SiLU-GLU stacks (act code 0) only")
     return _MoEMxfp8.apply(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes)

@@ -338,3 +338,63 @@ def mxfp8_expert_wgrad(atq, atsf, btq, btsf, perm: Permutation):
                                                L.ptr(perm.counts), perm.cap, perm.E, Na, Nb, L.ptr(out),
                                                L.ptr(L.status_word(out.device)), L.stream_of(out)))
     return out
+
+
+# ----------------------------------------------------------------------------- PolyGLU (generic path)
+@_op("expert_linear", 1)
+def expert_linear(a, w, perm: Permutation, out=None):
+    """out (rows,N) = a (rows,K) @ W[e]^T with W (E,N,K), E = perm.E."""
+    E, N, K = w.shape
+    out = torch.empty(perm.cap, N, dtype=torch.bfloat16, device=a.device) if out is None else out
+    L.check(L.lib().b200moe_expert_linear(L.ptr(a), L.ptr(w), L.ptr(perm.tile_expert), L.ptr(perm.poffs), perm.cap,
+                                          perm.E, N, K, L.ptr(out), L.ptr(L.status_word(a.device)), L.stream_of(a)))
+    return out
+
+
+@_op("expert_linear_t", 1)
+def expert_linear_t(a, w, perm: Permutation, out=None):
+    """out (rows,N) = a (rows,K) @ W[e] with W (E,K,N), E = perm.E."""
+    E, K, N = w.shape
+    out = torch.empty(perm.cap, N, dtype=torch.bfloat16, device=a.device) if out is None else out
+    L.check(L.lib().b200moe_expert_linear_t(L.ptr(a), L.ptr(w), L.ptr(perm.tile_expert), L.ptr(perm.poffs), perm.cap,
+                                            perm.E, K, N, L.ptr(out), L.ptr(L.status_word(a.device)), L.stream_of(a)))
+    return out
+
+
+@_op("glu_fwd_rows", 1)
+def glu_fwd_rows(gate_up, act_codes, act_params, perm: Permutation):
+    I = gate_up.shape[1] // 2
+    inter = torch.empty(perm.cap, I, dtype=torch.bfloat16, device=gate_up.device)
+    L.check(L.lib().b200moe_glu_fwd_rows(L.ptr(gate_up), L.ptr(perm.tile_expert), L.ptr(act_codes), L.ptr(act_params),
+                                         L.ptr(perm.total_rows), perm.cap, I, L.ptr(inter), L.stream_of(gate_up)))
+    return inter
+
+
+@_op("glu_bwd_rows", 1)
+def glu_bwd_rows(grad_inter, gate_up, act_codes, act_params, perm: Permutation, want_param_grads=False):
+    I = gate_up.shape[1] // 2
+    dev = gate_up.device
+    ggu = torch.empty_like(gate_up)
+    row_da = torch.empty(perm.cap, dtype=torch.float32, device=dev) if want_param_grads else None
+    row_dg = torch.empty(perm.cap, dtype=torch.float32, device=dev) if want_param_grads else None
+    L.check(L.lib().b200moe_glu_bwd_rows(L.ptr(grad_inter), L.ptr(gate_up), L.ptr(perm.tile_expert), L.ptr(act_codes),
+                                         L.ptr(act_params), L.ptr(perm.total_rows), perm.cap, I, L.ptr(ggu),
+                                         L.ptr(row_da), L.ptr(row_dg), L.stream_of(gate_up)))
+    return ggu, row_da, row_dg
+
+
+@_op("expert_row_sums", 1)
+def expert_row_sums(row_da, row_dg, perm: Permutation, out):
+    """out[:perm.E] (E,2) = per-expert sums of the per-row alpha / gamma gradients."""
+    L.check(L.lib().b200moe_expert_row_sums(L.ptr(row_da), L.ptr(row_dg), L.ptr(perm.poffs), perm.E, L.ptr(out),
+                                            L.stream_of(out)))
+    return out
+
+
+@_op("special_rows", 1)
+def special_rows(src, dst, act_codes, perm: Permutation, first_special):
+    """Rows of the Identity / Zero experts [first_special, perm.E): dst = src or 0."""
+    H = src.shape[1]
+    L.check(L.lib().b200moe_special_rows(L.ptr(src), L.ptr(perm.tile_expert), L.ptr(act_codes), L.ptr(perm.poffs),
+                                         int(first_special), perm.E, H, perm.cap, L.ptr(dst), L.stream_of(src)))
+    return dst
