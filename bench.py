@@ -41,6 +41,12 @@ EP5 = dict(T=65536, H=7168, E=256, I=2048, k=8)
 # MXFP8 configuration (e4m3 + E8M0 block-32 scales), one GPU
 MXFP8 = dict(T=32768, H=4096, E=8, I=14336, k=2)
 METRIC = "moe_layer_fwd_bwd_tokens_per_s"
+# DRAM bytes (read + written) per launch measured with ncu on the profile workload (24 576 routed rows,
+# H=2048, I=1408, 1536 rows per expert), see profiles/dram_traffic_profile_workload.md.  Traffic grows in
+# proportion to the routed rows when H, I and the rows per expert stay the same (the headline workload).
+NCU_TRAFFIC = {"rows": 24576, "H": 2048, "I": 1408, "rows_per_expert": 1536,
+               "bytes": {"expert_gate_up_swiglu": 479.0e6, "expert_down": 242.8e6, "expert_down_dgrad_glu": 482.4e6,
+                         "expert_gate_up_dgrad": 421.5e6, "expert_wgrad": (393.6e6 + 239.3e6) / 2}}
 
 
 def _peaks(precision="bf16"):
@@ -292,6 +298,10 @@ def run_ours(args):
     top = max((n for n in flops if n in per_op), key=lambda n: per_op[n][0])
     top_avg_ms = per_op[top][0] / per_op[top][1]
     achieved = flops[top] / (top_avg_ms * 1e-3) / 1e12
+    traffic = None
+    if (H, I, M // E) == (NCU_TRAFFIC["H"], NCU_TRAFFIC["I"], NCU_TRAFFIC["rows_per_expert"]) and top in NCU_TRAFFIC["bytes"] \
+            and w["precision"] == "bf16" and world == 1:
+        traffic = round(NCU_TRAFFIC["bytes"][top] * M / NCU_TRAFFIC["rows"])
     layer_flops = 18.0 * H * I * T * k
     line = {
         "metric": METRIC, "value": round(T * world / (ms_step * 1e-3), 1), "unit": "tokens/s", "n_gpus": world,
@@ -305,7 +315,8 @@ def run_ours(args):
         "gemm_ms_per_step": round(gemm_ms, 4),
         "roofline": {"bound": "tensor", "kernel": f"gemm_kernel via {top}", "achieved": round(achieved, 1),
                      "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": round(achieved / peaks["tflops"], 4),
-                     "traffic": None, "peak_source": peaks["source"]},
+                     "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write, scaled from the "
+                     "profile workload by routed rows)" if traffic else None, "peak_source": peaks["source"]},
         "kernels": kernels,
         "e2e": {"value": round(T * world / (ms_e2e * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 4),
                 "h2d_bytes_per_step": 2 * T * H * 2, "d2h_bytes_per_step": 2 * T * H * 2},
