@@ -9,6 +9,8 @@
 // selects the byte with the scale-id fields of the instruction descriptor.
 // Schedules and epilogues are the ones of the bf16 kernel (dense / grouped-M / grouped-K; store,
 // SwiGLU over 64-interleaved gate|up weight rows, GLU backward).
+#include <stdlib.h>
+
 #include "gemm_common.cuh"
 
 namespace b200moe {
@@ -290,6 +292,330 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Pair variant: a cluster of two CTAs computes a 256 x 256 tile with cta_group::2 block-scaled MMAs.
+// Each CTA stages its own 128 rows of A, its own 128 rows of B, the scale atom of its A rows and both
+// scale atoms of the tile's B rows (every CTA needs the scales of all 256 columns).  The 256-column
+// accumulator plus the scale columns fill tensor memory, so the accumulator is single-buffered: the
+// epilogue of a tile runs while the producer already refills the stages of the next one.
+constexpr int PBN = 256;
+constexpr int kPStage = 34816;           // A 16 KB + B 16 KB + SFA 512 B + SFB 1 KB, rounded to 1 KB
+constexpr int kPStages = 6;
+constexpr int kPSfCols = 16;             // tensor-memory columns per stage: SFA 4 + SFB 8 (+4 spare)
+constexpr int kPSmemBytes = kPStages * kPStage + (2 * kPStages + 2) * 8 + 16 + 1024;
+
+// pair form of the 3-D load for the scale tensors {128 u32, k-chunks, row-blocks}
+__device__ __forceinline__ void umma_mxf8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_cp_sf_pair(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ uint32_t idesc_mxf8_pair(uint32_t sf_id) {
+  return (sf_id << 4) | (static_cast<uint32_t>(PBN >> 3) << 17) | (1u << 23) |
+         (static_cast<uint32_t>(256 >> 4) << 24) | (sf_id << 29);
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
+                       const Fp8Params fp) {
+  const GemmParams& p = fp.g;
+  constexpr int TN = PBN, TM = 2 * BM;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPStages * kPStage);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = smem_u32(bars + kPStages);
+  const uint32_t bar_tfull = smem_u32(bars + 2 * kPStages);
+  const uint32_t bar_tempty = smem_u32(bars + 2 * kPStages + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPStages + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int cta_rank = static_cast<int>(cluster_ctarank());
+  const int first_tile = static_cast<int>(cluster_id_x());
+  const int tile_step = static_cast<int>(num_clusters_x());
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_tfull, 1);
+    mbar_init(bar_tempty, 2 * kEpiWarps);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmSFA);
+    tma_prefetch_desc(&tmSFB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), kFTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  __syncwarp();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total = total_tiles(p, TN, TM);
+
+  if (warp == 0) {
+    if (lane == 0) {   // ---------------------------------------------------------- producer (each CTA)
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < total && ok; tile += tile_step) {
+        const Tile t = get_tile(p, tile, TN, TM, FBK);
+        const int gB = (p.sched == SCHED_GROUPED_M) ? t.g : 0;
+        const int m0 = t.m0 + BM * cta_rank;
+        const int rb_a = m0 >> 7;
+        const int rb_b = static_cast<int>((static_cast<long long>(gB) * fp.b_rows_per_group + t.n0) >> 7);
+        for (int kb = 0; kb < t.nkb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, ST_WAIT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = mapa_shared(bar_full + 8 * s, 0);   // the leader's barrier counts both CTAs
+          if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, 2 * (kATile + kBTile + 3 * kSfAtom));
+          const uint32_t sa = smem_u32(smem + s * kPStage);
+          const int kk = t.k0 + kb * FBK;
+          const int kc = kk >> 7;
+          tma_load_3d_pair(sa, &tmA, full, kk, m0, 0);
+          tma_load_3d_pair(sa + kATile, &tmB, full, kk, t.n0 + 128 * cta_rank, gB);
+          tma_load_3d_pair(sa + kATile + kBTile, &tmSFA, full, 0, kc, rb_a);              // 1 atom
+          tma_load_3d_pair(sa + kATile + kBTile + kSfAtom, &tmSFB, full, 0, kc, rb_b);    // 2 atoms
+          if (++s == kPStages) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && cta_rank == 0) {   // --------------------------------------------- MMA issuer (leader)
+      int s = 0, it = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < total && ok; tile += tile_step, ++it) {
+        const Tile t = get_tile(p, tile, TN, TM, FBK);
+        if (!mbar_wait(bar_tempty, (it & 1) ^ 1, abort_flag, ST_WAIT_MMA_TMEM)) break;
+        tc_fence_after();
+        for (int kb = 0; kb < t.nkb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, ST_WAIT_MMA_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * kPStage);
+          const uint32_t sb = sa + kATile;
+          const uint32_t sfa_t = tmem_base + PBN + kPSfCols * s;
+          const uint32_t sfb_t = sfa_t + 4;
+          tmem_cp_sf_pair(sfa_t, sf_desc(sa + kATile + kBTile));
+          tmem_cp_sf_pair(sfb_t, sf_desc(sa + kATile + kBTile + kSfAtom));
+          tmem_cp_sf_pair(sfb_t + 4, sf_desc(sa + kATile + kBTile + 2 * kSfAtom));
+#pragma unroll
+          for (int k = 0; k < FBK / 32; ++k) {
+            const uint64_t da = umma_desc_sw128(sa + k * 32, 0, 1024);
+            const uint64_t db = umma_desc_sw128(sb + k * 32, 0, 1024);
+            umma_mxf8_pair(tmem_base, da, db, idesc_mxf8_pair(k), sfa_t, sfb_t, (kb | k) != 0);
+          }
+          umma_commit_pair(bar_empty + 8 * s);
+          if (++s == kPStages) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+        if (!ok) break;
+        if (t.nkb > 0) {
+          umma_commit_pair(bar_tfull);
+        } else {
+          mbar_arrive(bar_tfull);
+          mbar_arrive_cluster(mapa_shared(bar_tfull, 1));
+        }
+      }
+    }
+  } else {   // ---------------------------------------------------------------------- epilogue
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;    // columns [128*half, 128*half + 128) of the tile
+    const uint32_t tempty_leader = mapa_shared(bar_tempty, 0);
+    int it = 0;
+    for (int tile = first_tile; tile < total; tile += tile_step, ++it) {
+      const Tile t = get_tile(p, tile, TN, TM, FBK);
+      if (!mbar_wait(bar_tfull, it & 1, abort_flag, ST_WAIT_EPILOGUE)) break;
+      __syncwarp();
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      const long long row = static_cast<long long>(t.m0) + BM * cta_rank + q * 32 + lane;
+      const bool have_acc = t.nkb > 0;
+      if constexpr (EPI == EPI_STORE) {
+        const bool row_ok = (p.sched == SCHED_GROUPED_M) || (row < p.M);
+        const long long base = (p.sched == SCHED_GROUPED_K ? t.g * p.d_group_stride : 0) + row * p.ldd + t.n0;
+#pragma unroll 1
+        for (int c0 = half * 128; c0 < half * 128 + 128; c0 += 32) {
+          if (t.n0 + c0 >= p.N) break;
+          uint32_t r[32];
+          if (have_acc) {
+            tmem_ld32(taddr + c0, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          if (row_ok) {
+            __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + base + c0;
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              if (t.n0 + c0 + v * 8 < p.N) *reinterpret_cast<uint4*>(d + v * 8) = pack8(r + v * 8);
+          }
+        }
+      } else if constexpr (EPI == EPI_SWIGLU) {
+        // weight rows are 64-interleaved: accumulator columns [128h, 128h+64) = gate and [128h+64, 128h+128) = up
+        // of the intermediate columns [n0/2 + 64h, n0/2 + 64h + 64)
+        const int I = p.I;
+        __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(p.D) + row * (2LL * I);
+        __nv_bfloat16* it_out = reinterpret_cast<__nv_bfloat16*>(p.aux) + row * static_cast<long long>(I);
+#pragma unroll 1
+        for (int c = 0; c < 64; c += 32) {
+          const int col0 = t.n0 / 2 + 64 * half + c;
+          if (col0 >= I) break;
+          uint32_t g[32], u[32];
+          tmem_ld32(taddr + 128 * half + c, g);
+          tmem_ld32(taddr + 128 * half + 64 + c, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = col0 + v * 8;
+            if (col < I) {
+              uint32_t og[4], ou[4], oh[4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                og[h] = pack_bf16x2(__uint_as_float(g[v * 8 + 2 * h]), __uint_as_float(g[v * 8 + 2 * h + 1]));
+                ou[h] = pack_bf16x2(__uint_as_float(u[v * 8 + 2 * h]), __uint_as_float(u[v * 8 + 2 * h + 1]));
+                const float2 gf = unpack_bf16x2(og[h]);
+                const float2 uf = unpack_bf16x2(ou[h]);
+                const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
+                const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
+                oh[h] = pack_bf16x2(gf.x * s0 * uf.x, gf.y * s1 * uf.y);
+              }
+              *reinterpret_cast<uint4*>(gu + col) = make_uint4(og[0], og[1], og[2], og[3]);
+              *reinterpret_cast<uint4*>(gu + I + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+              *reinterpret_cast<uint4*>(it_out + col) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+            }
+          }
+        }
+      } else {   // EPI_GLU_BWD: accumulator = grad_inter columns [n0, n0+256), this warp 128 of them
+        const int I = p.I;
+        const __nv_bfloat16* gu = reinterpret_cast<const __nv_bfloat16*>(p.aux) + row * (2LL * I);
+        __nv_bfloat16* ggu = reinterpret_cast<__nv_bfloat16*>(p.D) + row * (2LL * I);
+#pragma unroll 1
+        for (int c0 = half * 128; c0 < half * 128 + 128; c0 += 32) {
+          if (t.n0 + c0 >= I) break;
+          uint4 g4[4], u4[4];
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = t.n0 + c0 + v * 8;
+            g4[v] = col < I ? __ldg(reinterpret_cast<const uint4*>(gu + col)) : make_uint4(0u, 0u, 0u, 0u);
+            u4[v] = col < I ? __ldg(reinterpret_cast<const uint4*>(gu + I + col)) : make_uint4(0u, 0u, 0u, 0u);
+          }
+          uint32_t r[32], og[16], ou[16];
+          tmem_ld32(taddr + c0, r);
+          tmem_ld_wait();
+          glu_bwd32(r, g4, u4, og, ou);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = t.n0 + c0 + v * 8;
+            if (col < I) {
+              *reinterpret_cast<uint4*>(ggu + col) = make_uint4(og[4 * v], og[4 * v + 1], og[4 * v + 2], og[4 * v + 3]);
+              *reinterpret_cast<uint4*>(ggu + I + col) = make_uint4(ou[4 * v], ou[4 * v + 1], ou[4 * v + 2], ou[4 * v + 3]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_leader);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  __syncwarp();
+  cluster_sync_all();
+  if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_flag);
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kFTmemCols);
+  }
+}
+
+// scale atoms seen as a {128 x u32, k-chunks, row-blocks} tensor, no swizzle; box = `atoms` row-blocks
+static int map_sf(CUtensorMap* tm, const void* sf, long long row_blocks, long long k_chunks, int atoms) {
+  EncodeTiledFn fn = get_encode_fn();
+  B200_CHECK_ARG(fn != nullptr, B200MOE_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  B200_CHECK_ARG(aligned16(sf), B200MOE_E_ALIGN, "scale buffer is not 16-byte aligned");
+  cuuint64_t dims[3] = {128, (cuuint64_t)k_chunks, (cuuint64_t)row_blocks};
+  cuuint64_t strides[2] = {512, (cuuint64_t)k_chunks * 512};
+  cuuint32_t box[3] = {128, 1, (cuuint32_t)atoms};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(sf), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200_CHECK_ARG(r == CUDA_SUCCESS, B200MOE_E_CUDA, "cuTensorMapEncodeTiled(scales) failed (%d)", (int)r);
+  return 0;
+}
+
+template <int EPI>
+static int launch_fp8_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmSFA,
+                           const CUtensorMap& tmSFB, const Fp8Params& fp, int max_tiles, cudaStream_t stream) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(max dynamic smem)");
+  int pairs = gemm_cta_budget() / 2;
+  if (max_tiles > 0 && max_tiles < pairs) pairs = max_tiles;
+  if (pairs < 1) pairs = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(pairs * 2, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kPSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  B200_CUDA(cudaLaunchKernelEx(&cfg, gemm_mxfp8_pair_kernel<EPI>, tmA, tmB, tmSFA, tmSFB, fp));
+  return 0;
+}
+
+// B200MOE_MXFP8_1CTA=1 keeps the single-CTA 128x128 tiles (A/B measurements)
+static bool fp8_pairs_enabled() {
+  static int v = -1;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char* e = getenv("B200MOE_MXFP8_1CTA");
+    v = (e != nullptr && e[0] == '1') ? 0 : 1;
+  });
+  return v == 1;
+}
+
 template <int EPI>
 static int launch_fp8(const CUtensorMap& tmA, const CUtensorMap& tmB, const Fp8Params& fp, int max_tiles,
                       cudaStream_t stream) {
@@ -312,6 +638,26 @@ static int map_fp8(CUtensorMap* tm, const void* q, long long rows, long long K, 
   return make_map(tm, q, K, rows, groups, K, rows * K, FBK, 128, 1);
 }
 
+// Launch with pair tiles when the output is at least one 256-wide tile (and pairs are enabled).
+template <int EPI>
+static int launch_any(const void* Aq, long long a_rows, const void* Bq, long long b_rows, long long b_groups,
+                      long long K, const Fp8Params& fp, int max_tiles_1cta, cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  int rc = map_fp8(&tmA, Aq, a_rows, K, 1);
+  if (rc) return rc;
+  rc = map_fp8(&tmB, Bq, b_rows, K, b_groups);
+  if (rc) return rc;
+  const bool pair = fp8_pairs_enabled() && fp.g.N >= PBN && fp.g.N % 128 == 0 &&
+                    (fp.g.sched != SCHED_DENSE || fp.g.M >= 256);
+  if (!pair) return launch_fp8<EPI>(tmA, tmB, fp, max_tiles_1cta, stream);
+  CUtensorMap tmSFA, tmSFB;
+  rc = map_sf(&tmSFA, fp.sfa, ceil_div(a_rows, 128), fp.sfa_kc, 1);
+  if (rc) return rc;
+  rc = map_sf(&tmSFB, fp.sfb, ceil_div(b_rows * b_groups, 128), fp.sfb_kc, 2);
+  if (rc) return rc;
+  return launch_fp8_pair<EPI>(tmA, tmB, tmSFA, tmSFB, fp, max_tiles_1cta > 0 ? (max_tiles_1cta + 3) / 4 : 0, stream);
+}
+
 }  // namespace b200moe
 
 using namespace b200moe;
@@ -326,16 +672,11 @@ int b200moe_mxfp8_gemm_nt(const void* Aq, const void* Asf, const void* Bq, const
   B200_CHECK_ARG(Aq && Asf && Bq && Bsf && D, B200MOE_E_NULL, "mxfp8_gemm_nt: null pointer");
   CHECK_K128(K); CHECK_DIM8(N); CHECK_I32(M); CHECK_I32(N); CHECK_I32(K);
   if (M == 0) return 0;
-  CUtensorMap tmA, tmB;
-  int rc = map_fp8(&tmA, Aq, M, K, 1);
-  if (rc) return rc;
-  rc = map_fp8(&tmB, Bq, N, K, 1);
-  if (rc) return rc;
   Fp8Params fp{};
   fp.g.sched = SCHED_DENSE; fp.g.M = (int)M; fp.g.N = (int)N; fp.g.K = (int)K; fp.g.num_groups = 1;
   fp.g.D = D; fp.g.ldd = N; fp.g.status = status;
   fp.sfa = (const uint8_t*)Asf; fp.sfb = (const uint8_t*)Bsf; fp.sfa_kc = fp.sfb_kc = (int)(K / 128);
-  return launch_fp8<EPI_STORE>(tmA, tmB, fp, (int)(ceil_div(M, BM) * ceil_div(N, FBN)), (cudaStream_t)stream);
+  return launch_any<EPI_STORE>(Aq, M, Bq, N, 1, K, fp, (int)(ceil_div(M, BM) * ceil_div(N, FBN)), (cudaStream_t)stream);
 }
 
 /* grouped-M: D(rows of e, N) = A(rows of e) * B[e]^T; B is an (E*N, K) stack, N %% 128 == 0.
@@ -348,11 +689,6 @@ int b200moe_mxfp8_expert_gemm(int epilogue, const void* Aq, const void* Asf, con
   CHECK_K128(K); CHECK_K128(N); CHECK_I32(rows_cap);
   B200_CHECK_ARG(rows_cap % B200MOE_TILE_M == 0, B200MOE_E_BAD_SHAPE, "mxfp8_expert_gemm: rows_cap %% %d != 0", B200MOE_TILE_M);
   B200_CHECK_ARG(E >= 1 && E * N < (1LL << 31), B200MOE_E_BAD_SHAPE, "mxfp8_expert_gemm: E = %d", E);
-  CUtensorMap tmA, tmB;
-  int rc = map_fp8(&tmA, Aq, rows_cap, K, 1);
-  if (rc) return rc;
-  rc = map_fp8(&tmB, Bq, N, K, E);
-  if (rc) return rc;
   Fp8Params fp{};
   fp.g.sched = SCHED_GROUPED_M; fp.g.N = (int)N; fp.g.K = (int)K; fp.g.num_groups = E;
   fp.g.tile_expert = tile_expert; fp.g.poffs = poffs; fp.g.D = D; fp.g.ldd = N; fp.g.aux = aux; fp.g.I = (int)I;
@@ -360,13 +696,13 @@ int b200moe_mxfp8_expert_gemm(int epilogue, const void* Aq, const void* Asf, con
   fp.sfa = (const uint8_t*)Asf; fp.sfb = (const uint8_t*)Bsf; fp.sfa_kc = fp.sfb_kc = (int)(K / 128);
   fp.b_rows_per_group = (int)N;
   switch (epilogue) {
-    case EPI_STORE: return launch_fp8<EPI_STORE>(tmA, tmB, fp, 0, (cudaStream_t)stream);
+    case EPI_STORE: return launch_any<EPI_STORE>(Aq, rows_cap, Bq, N, E, K, fp, 0, (cudaStream_t)stream);
     case EPI_SWIGLU:
       B200_CHECK_ARG(aux && N == 2 * I && I % 64 == 0, B200MOE_E_BAD_SHAPE, "mxfp8_expert_gemm: SwiGLU needs N = 2I, I %% 64 == 0");
-      return launch_fp8<EPI_SWIGLU>(tmA, tmB, fp, 0, (cudaStream_t)stream);
+      return launch_any<EPI_SWIGLU>(Aq, rows_cap, Bq, N, E, K, fp, 0, (cudaStream_t)stream);
     case EPI_GLU_BWD:
       B200_CHECK_ARG(aux && N == I, B200MOE_E_BAD_SHAPE, "mxfp8_expert_gemm: GLU backward needs N = I");
-      return launch_fp8<EPI_GLU_BWD>(tmA, tmB, fp, 0, (cudaStream_t)stream);
+      return launch_any<EPI_GLU_BWD>(Aq, rows_cap, Bq, N, E, K, fp, 0, (cudaStream_t)stream);
     default:
       set_error("mxfp8_expert_gemm: unknown epilogue %d", epilogue);
       return B200MOE_E_UNSUPPORTED;
@@ -380,17 +716,13 @@ int b200moe_mxfp8_expert_wgrad(const void* Atq, const void* Atsf, const void* Bt
                                int64_t Nb, void* out, int32_t* status, b200moe_stream_t stream) {
   B200_CHECK_ARG(Atq && Atsf && Btq && Btsf && poffs && out, B200MOE_E_NULL, "mxfp8_expert_wgrad: null pointer");
   CHECK_K128(rows_cap); CHECK_DIM8(Na); CHECK_DIM8(Nb); CHECK_I32(Na); CHECK_I32(Nb); CHECK_I32(rows_cap);
-  CUtensorMap tmA, tmB;
-  int rc = map_fp8(&tmA, Atq, Na, rows_cap, 1);
-  if (rc) return rc;
-  rc = map_fp8(&tmB, Btq, Nb, rows_cap, 1);
-  if (rc) return rc;
   Fp8Params fp{};
   fp.g.sched = SCHED_GROUPED_K; fp.g.M = (int)Na; fp.g.N = (int)Nb; fp.g.K = (int)rows_cap; fp.g.num_groups = E;
   fp.g.poffs = poffs; fp.g.counts = counts; fp.g.D = out; fp.g.ldd = Nb; fp.g.d_group_stride = Na * Nb;
   fp.g.status = status;
   fp.sfa = (const uint8_t*)Atsf; fp.sfb = (const uint8_t*)Btsf; fp.sfa_kc = fp.sfb_kc = (int)(rows_cap / 128);
-  return launch_fp8<EPI_STORE>(tmA, tmB, fp, (int)std::min<long long>(1 << 30, E * ceil_div(Na, BM) * ceil_div(Nb, FBN)),
+  return launch_any<EPI_STORE>(Atq, Na, Btq, Nb, 1, rows_cap, fp,
+                               (int)std::min<long long>(1 << 30, E * ceil_div(Na, BM) * ceil_div(Nb, FBN)),
                                (cudaStream_t)stream);
 }
 
