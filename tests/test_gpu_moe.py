@@ -250,3 +250,70 @@ def test_full_size_properties(pkg):
     assert int((rs >= 0).sum()) == T * k
     assert torch.equal(rs[perm.slot_row.long()].long(), torch.arange(T * k, device=DEV))
     assert int(perm.counts.sum()) == T * k
+
+
+def _torch_gpu_fp32_reference(x, idx, w, gu, dn, go):
+    """Independent fp32 reference on the GPU (plain torch ops, per-expert loop, autograd): used at the
+    benchmark sizes where the CPU oracle would take minutes."""
+    E = gu.shape[0]
+    I = gu.shape[1] // 2
+    xf = x.float().requires_grad_(True)
+    wf = w.float().requires_grad_(True)
+    guf = gu.float().requires_grad_(True)
+    dnf = dn.float().requires_grad_(True)
+    out = torch.zeros_like(xf)
+    flat_e = idx.flatten()
+    tok = torch.arange(idx.shape[0], device=x.device).repeat_interleave(idx.shape[1])
+    order = torch.sort(flat_e, stable=True).indices
+    counts = torch.bincount(flat_e, minlength=E).tolist()
+    pos = 0
+    wu, wd = guf.unbind(0), dnf.unbind(0)
+    for e in range(E):
+        c = counts[e]
+        if c == 0:
+            continue
+        sl = order[pos:pos + c]
+        pos += c
+        rows = tok[sl]
+        g = xf[rows] @ wu[e].t()
+        inter = torch.nn.functional.silu(g[:, :I]) * g[:, I:]
+        out = out.index_add(0, rows, (inter @ wd[e].t()) * wf.flatten()[sl].unsqueeze(-1))
+    (out * go.float()).sum().backward()
+    return out.detach(), xf.grad, wf.grad, guf.grad, dnf.grad, counts
+
+
+@pytest.mark.parametrize("name,T,H,E,I,k,zipf", [("config2", 16384, 2048, 64, 1408, 6, None),
+                                                 ("config3_skewed", 32768, 2048, 128, 768, 8, 1.1)])
+def test_benchmark_size_configs_vs_fp32(pkg, name, T, H, E, I, k, zipf):
+    """The bf16 single-GPU configurations at FULL size: output and every gradient within 2e-2 relative
+    L2 of an fp32 computation; the skewed configuration must leave some experts without tokens and
+    their weight gradients exactly zero."""
+    g = torch.Generator(device=DEV).manual_seed(7)
+    x = torch.randn(T, H, device=DEV, generator=g).to(torch.bfloat16)
+    gu = (torch.randn(E, 2 * I, H, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    dn = (torch.randn(E, H, I, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    wr = (torch.randn(E, H, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    go = torch.randn(T, H, device=DEV, generator=g).to(torch.bfloat16)
+    logits = pkg.ops.gemm_nt(x, wr)
+    if zipf is not None:
+        ranks = torch.randperm(E, device=DEV, generator=g).float() + 1.0
+        p = ranks.pow(-zipf)
+        logits = (logits.float() + 3.0 * torch.log(p / p.sum())[None, :]).to(torch.bfloat16)
+    idx, w, counts = pkg.ops.router_topk_fwd(logits, None, k)
+    lv = dict(x=x.clone().requires_grad_(True), w=w.clone().requires_grad_(True),
+              gu=gu.clone().requires_grad_(True), dn=dn.clone().requires_grad_(True))
+    out = pkg.moe(lv["x"], idx, lv["w"], lv["gu"], lv["dn"], torch.zeros(E, dtype=torch.int32, device=DEV))
+    out.backward(go)
+    pkg.check_status()
+    ref_out, gx, gw, ggu, gdn, cnt = _torch_gpu_fp32_reference(x, idx, w, gu, dn, go)
+    assert cnt == counts.tolist()
+    rel = lambda a, b: float((a.float() - b).norm() / b.norm())
+    errs = dict(out=rel(out, ref_out), grad_x=rel(lv["x"].grad, gx), grad_w=rel(lv["w"].grad, gw),
+                grad_gate_up=rel(lv["gu"].grad, ggu), grad_down=rel(lv["dn"].grad, gdn))
+    print(name, {k_: f"{v:.2e}" for k_, v in errs.items()})
+    for k_, v in errs.items():
+        assert v < TOL_BF16, (name, k_, v)
+    if zipf is not None:
+        empty = counts == 0
+        assert bool(empty.any()), "the skewed routing must leave some experts without tokens"
+        assert (lv["gu"].grad[empty] == 0).all() and (lv["dn"].grad[empty] == 0).all()
