@@ -106,7 +106,16 @@ ep_gather_pull_kernel(PeerPtrs x_peers, PeerPtrs order_peers, PeerPtrs offs_peer
       for (int c = lane; c < vec_per_row; c += 32) dst[c] = make_uint4(0u, 0u, 0u, 0u);
     } else {
       const uint4* srow = reinterpret_cast<const uint4*>(x_peers.p[src]) + static_cast<long long>(slot / k) * vec_per_row;
-      for (int c = lane; c < vec_per_row; c += 32) dst[c] = srow[c];
+      // peer loads have microseconds of latency: keep 8 of them in flight per lane
+      for (int c0 = lane; c0 < vec_per_row; c0 += 32 * 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (c0 + 32 * i < vec_per_row) v[i] = srow[c0 + 32 * i];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (c0 + 32 * i < vec_per_row) dst[c0 + 32 * i] = v[i];
+      }
     }
     if (lane == 0) {
       row_src[r] = src;
@@ -145,9 +154,15 @@ ep_combine_pull_kernel(PeerPtrs rows_peers, const float* __restrict__ w, const l
     __syncthreads();
     for (int c = threadIdx.x; c < vec_per_row; c += blockDim.x) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int j = 0; j < k; ++j) {
-        const uint4 v = reinterpret_cast<const uint4*>(rows_peers.p[s_owner[j]])[static_cast<long long>(s_row[j]) * vec_per_row + c];
-        fma8(acc, v, s_w[j]);
+      for (int j0 = 0; j0 < k; j0 += 8) {      // up to 8 peer loads in flight, summed in slot order
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (j0 + i < k)
+            v[i] = reinterpret_cast<const uint4*>(rows_peers.p[s_owner[j0 + i]])[static_cast<long long>(s_row[j0 + i]) * vec_per_row + c];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (j0 + i < k) fma8(acc, v[i], s_w[j0 + i]);
       }
       uint4 o;
       o.x = pack_bf16x2(acc[0], acc[1]);
@@ -159,21 +174,23 @@ ep_combine_pull_kernel(PeerPtrs rows_peers, const float* __restrict__ w, const l
   }
 }
 
-// One CTA per padded row of this rank: grad_eo[r] = go_peer[src][slot/k] * w_peer[src][slot];
+// One warp per padded row of this rank: grad_eo[r] = go_peer[src][slot/k] * w_peer[src][slot];
 // gw_rows[r] = <go, eo[r]> (fp32); zero rows for pads.
 __global__ void __launch_bounds__(256)
 ep_combine_bwd_pull_kernel(PeerPtrs go_peers, PeerPtrs w_peers, const uint4* __restrict__ eo,
                            const int* __restrict__ row_src, const int* __restrict__ row_slot_src,
                            const int* __restrict__ total_rows, int k, int vec_per_row, uint4* __restrict__ grad_eo,
                            float* __restrict__ gw_rows) {
-  __shared__ float red[8];
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const int total = *total_rows;
-  for (long long r = blockIdx.x; r < total; r += gridDim.x) {
+  for (long long r = warp0; r < total; r += nwarps) {
     const int src = row_src[r];
     uint4* dst = grad_eo + r * vec_per_row;
     if (src < 0) {
-      for (int c = threadIdx.x; c < vec_per_row; c += blockDim.x) dst[c] = make_uint4(0u, 0u, 0u, 0u);
-      if (threadIdx.x == 0) gw_rows[r] = 0.0f;
+      for (int c = lane; c < vec_per_row; c += 32) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+      if (lane == 0) gw_rows[r] = 0.0f;
       continue;
     }
     const int slot = row_slot_src[r];
@@ -181,28 +198,31 @@ ep_combine_bwd_pull_kernel(PeerPtrs go_peers, PeerPtrs w_peers, const uint4* __r
     const uint4* g = reinterpret_cast<const uint4*>(go_peers.p[src]) + static_cast<long long>(slot / k) * vec_per_row;
     const uint4* e = eo + r * vec_per_row;
     float dot = 0.0f;
-    for (int c = threadIdx.x; c < vec_per_row; c += blockDim.x) {
-      const uint4 gv = g[c], ev = e[c];
-      const float2 g0 = unpack_bf16x2(gv.x), g1 = unpack_bf16x2(gv.y), g2 = unpack_bf16x2(gv.z), g3 = unpack_bf16x2(gv.w);
-      const float2 e0 = unpack_bf16x2(ev.x), e1 = unpack_bf16x2(ev.y), e2 = unpack_bf16x2(ev.z), e3 = unpack_bf16x2(ev.w);
-      dot += g0.x * e0.x + g0.y * e0.y + g1.x * e1.x + g1.y * e1.y + g2.x * e2.x + g2.y * e2.y + g3.x * e3.x + g3.y * e3.y;
-      uint4 o;
-      o.x = pack_bf16x2(g0.x * wt, g0.y * wt);
-      o.y = pack_bf16x2(g1.x * wt, g1.y * wt);
-      o.z = pack_bf16x2(g2.x * wt, g2.y * wt);
-      o.w = pack_bf16x2(g3.x * wt, g3.y * wt);
-      dst[c] = o;
+    for (int c0 = lane; c0 < vec_per_row; c0 += 32 * 8) {
+      uint4 gv[8], ev[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (c0 + 32 * i < vec_per_row) {
+          gv[i] = g[c0 + 32 * i];
+          ev[i] = e[c0 + 32 * i];
+        }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (c0 + 32 * i < vec_per_row) {
+          const float2 g0 = unpack_bf16x2(gv[i].x), g1 = unpack_bf16x2(gv[i].y), g2 = unpack_bf16x2(gv[i].z), g3 = unpack_bf16x2(gv[i].w);
+          const float2 e0 = unpack_bf16x2(ev[i].x), e1 = unpack_bf16x2(ev[i].y), e2 = unpack_bf16x2(ev[i].z), e3 = unpack_bf16x2(ev[i].w);
+          dot += g0.x * e0.x + g0.y * e0.y + g1.x * e1.x + g1.y * e1.y + g2.x * e2.x + g2.y * e2.y + g3.x * e3.x + g3.y * e3.y;
+          uint4 o;
+          o.x = pack_bf16x2(g0.x * wt, g0.y * wt);
+          o.y = pack_bf16x2(g1.x * wt, g1.y * wt);
+          o.z = pack_bf16x2(g2.x * wt, g2.y * wt);
+          o.w = pack_bf16x2(g3.x * wt, g3.y * wt);
+          dst[c0 + 32 * i] = o;
+        }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = dot;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float s = 0.0f;
-      for (int i = 0; i < (blockDim.x >> 5); ++i) s += red[i];
-      gw_rows[r] = s;
-    }
+    if (lane == 0) gw_rows[r] = dot;
   }
 }
 
@@ -313,7 +333,7 @@ int b200moe_ep_combine_bwd_pull(const void* const* go_peers, const void* const* 
   rc = load_peers(&wp, w_peers, W, "ep_combine_bwd_pull(weights)");
   if (rc) return rc;
   if (rows_cap <= 0) return 0;
-  ep_combine_bwd_pull_kernel<<<grid_rows(rows_cap, 16), 256, 0, (cudaStream_t)stream>>>(
+  ep_combine_bwd_pull_kernel<<<grid_rows((rows_cap + 7) / 8, 8), 256, 0, (cudaStream_t)stream>>>(
       gp, wp, reinterpret_cast<const uint4*>(eo), row_src, row_slot_src, total_rows, k, static_cast<int>(H / 8),
       reinterpret_cast<uint4*>(grad_eo), gw_rows);
   B200_CUDA(cudaGetLastError());

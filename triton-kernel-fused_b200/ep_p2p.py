@@ -18,6 +18,31 @@ from . import ops
 from .moe import _amp_cast
 
 
+@ops._op("ep_plan", 1)
+def _plan(*a):
+    L.check(L.lib().b200moe_ep_plan(*a))
+
+
+@ops._op("ep_gather_pull", 1)
+def _gather_pull(*a):
+    L.check(L.lib().b200moe_ep_gather_pull(*a))
+
+
+@ops._op("ep_combine_pull", 1)
+def _combine_pull(*a):
+    L.check(L.lib().b200moe_ep_combine_pull(*a))
+
+
+@ops._op("ep_combine_bwd_pull", 1)
+def _combine_bwd_pull(*a):
+    L.check(L.lib().b200moe_ep_combine_bwd_pull(*a))
+
+
+@ops._op("ep_barrier", 0)
+def _barrier(ws):
+    ws.handle.barrier(0)
+
+
 def _align(n, a=256):
     return (n + a - 1) // a * a
 
@@ -56,7 +81,7 @@ class SymmetricWorkspace:
         self.generation = 0
 
     def barrier(self):
-        self.handle.barrier(0)
+        _barrier(self)
 
 
 class _ExpertParallelP2P(torch.autograd.Function):
@@ -73,7 +98,6 @@ class _ExpertParallelP2P(torch.autograd.Function):
         L.require(gate_up_local.shape[0] == El and down_local.shape[0] == El, f"this rank must hold {El} experts")
         dev = hidden.device
         st = L.stream_of(hidden)
-        lib = L.lib()
         i32 = dict(dtype=torch.int32, device=dev)
         idx = idx.contiguous()
         w32 = wt.detach().float().contiguous()
@@ -92,21 +116,21 @@ class _ExpertParallelP2P(torch.autograd.Function):
         tile_expert_l = torch.empty(cap_l // ops.TILE_M, **i32)
         src_base = torch.empty(W * El, **i32)
         dest_base = torch.empty(E, **i32)
-        L.check(lib.b200moe_ep_plan(L.ptr(counts_all), W, rank, E, L.ptr(poffs_l), L.ptr(counts_l),
-                                    L.ptr(tile_expert_l), L.ptr(src_base), L.ptr(dest_base), st))
+        _plan(L.ptr(counts_all), W, rank, E, L.ptr(poffs_l), L.ptr(counts_l),
+                                    L.ptr(tile_expert_l), L.ptr(src_base), L.ptr(dest_base), st)
         x_s = torch.empty(cap_l, H, dtype=torch.bfloat16, device=dev)
         row_src = torch.empty(cap_l, **i32)
         row_slot_src = torch.empty(cap_l, **i32)
-        L.check(lib.b200moe_ep_gather_pull(ws.peers["x"], ws.peers["order"], ws.peers["offs"], L.ptr(counts_l),
+        _gather_pull(ws.peers["x"], ws.peers["order"], ws.peers["offs"], L.ptr(counts_l),
                                            L.ptr(poffs_l), L.ptr(tile_expert_l), L.ptr(src_base), W, rank, E, k, H,
-                                           cap_l, L.ptr(x_s), L.ptr(row_src), L.ptr(row_slot_src), st))
+                                           cap_l, L.ptr(x_s), L.ptr(row_src), L.ptr(row_slot_src), st)
         perm_l = ops.Permutation(R, 1, El, cap_l, counts_l, None, poffs_l, None, None, tile_expert_l, None, None)
         gate_up, inter = ops.expert_gate_up_swiglu(x_s, gate_up_local, perm_l)
         ops.expert_down(inter, down_local, perm_l, out=ws.eo[:cap_l])
         ws.barrier()                                                # every owner's eo is complete
         out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
-        L.check(lib.b200moe_ep_combine_pull(ws.peers["eo"], L.ptr(w32), L.ptr(idx), L.ptr(perm.slot_pos),
-                                            L.ptr(perm.offs), L.ptr(dest_base), W, E, T, k, H, L.ptr(out), None, None, st))
+        _combine_pull(ws.peers["eo"], L.ptr(w32), L.ptr(idx), L.ptr(perm.slot_pos),
+                                            L.ptr(perm.offs), L.ptr(dest_base), W, E, T, k, H, L.ptr(out), None, None, st)
         ws.generation += 1
         ctx.ws, ctx.perm, ctx.perm_l, ctx.gen = ws, perm, perm_l, ws.generation
         ctx.tables = (dest_base, row_src, row_slot_src)
@@ -127,14 +151,13 @@ class _ExpertParallelP2P(torch.autograd.Function):
         cap_l = perm_l.cap
         dev = x_s.device
         st = L.stream_of(x_s)
-        lib = L.lib()
         ws.go.copy_(grad_out)
         ws.w.copy_(w32)
         ws.barrier()                                                # every home rank's grad_out / w are in place
         grad_eo = torch.empty(cap_l, H, dtype=torch.bfloat16, device=dev)
-        L.check(lib.b200moe_ep_combine_bwd_pull(ws.peers["go"], ws.peers["w"], L.ptr(ws.eo), L.ptr(row_src),
+        _combine_bwd_pull(ws.peers["go"], ws.peers["w"], L.ptr(ws.eo), L.ptr(row_src),
                                                 L.ptr(row_slot_src), L.ptr(perm_l.poffs[perm_l.E:]), W, k, H, cap_l,
-                                                L.ptr(grad_eo), L.ptr(ws.gw), st))
+                                                L.ptr(grad_eo), L.ptr(ws.gw), st)
         grad_gu = ops.expert_down_dgrad_glu(grad_eo, down_local, gate_up, perm_l)
         grad_down = ops.expert_wgrad(grad_eo, inter, perm_l)
         grad_gate_up = ops.expert_wgrad(grad_gu, x_s, perm_l)
@@ -142,9 +165,9 @@ class _ExpertParallelP2P(torch.autograd.Function):
         ws.barrier()                                                # every owner's grad_x_s / gw are complete
         grad_hidden = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
         grad_w = torch.empty(T, k, dtype=torch.float32, device=dev)
-        L.check(lib.b200moe_ep_combine_pull(ws.peers["gxs"], None, L.ptr(idx), L.ptr(perm.slot_pos), L.ptr(perm.offs),
+        _combine_pull(ws.peers["gxs"], None, L.ptr(idx), L.ptr(perm.slot_pos), L.ptr(perm.offs),
                                             L.ptr(dest_base), W, E, T, k, H, L.ptr(grad_hidden), ws.peers["gw"],
-                                            L.ptr(grad_w), st))
+                                            L.ptr(grad_w), st)
         return grad_hidden, None, grad_w.to(ctx.wt_dtype), grad_gate_up, grad_down, None
 
 
