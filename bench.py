@@ -42,7 +42,7 @@ EP5 = dict(T=65536, H=7168, E=256, I=2048, k=8)
 MXFP8 = dict(T=32768, H=4096, E=8, I=14336, k=2)
 METRIC = "moe_layer_fwd_bwd_tokens_per_s"
 # DRAM bytes (read + written) per launch measured with ncu on the profile workload (24 576 routed rows,
-# H=2048, I=1408, 1536 rows per expert), see profiles/dram_traffic_profile_workload.md.  Traffic grows in
+# H=2048, I=1408, 1536 rows per expert; the capture is summarised under profiles/).  Traffic grows in
 # proportion to the routed rows when H, I and the rows per expert stay the same (the headline workload).
 NCU_TRAFFIC = {"rows": 24576, "H": 2048, "I": 1408, "rows_per_expert": 1536,
                "bytes": {"expert_gate_up_swiglu": 479.0e6, "expert_down": 242.8e6, "expert_down_dgrad_glu": 482.4e6,

@@ -54,6 +54,11 @@ const char* b200moe_status_string(int status_word);
 /* host: worst-case number of padded rows for M routed rows over E experts */
 int64_t b200moe_padded_rows_cap(int64_t M, int E);
 
+/* Failure-path self-test, no reference counterpart: one CTA waits (at most `limit_cycles` SM clocks,
+ * 1e3..2e9) on a barrier that nothing completes; the wait gives up, `status` receives 6 and the kernel
+ * returns normally.  Shows that a stalled pipeline ends in a status code, not in a hung GPU. */
+int b200moe_selftest_bounded_wait(int32_t* status, int64_t limit_cycles, b200moe_stream_t stream);
+
 /* host: keep `n` SMs free of the persistent GEMM kernels (process-wide, default 0) so that
  * communication kernels queued on another stream can run beside them.  No reference counterpart. */
 int b200moe_set_reserved_sms(int n);

@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this folder by running the REFERENCE's own CPU-runnable code.
 
-Run once in a container that has the reference checkout (default /root/reference, or pass its path
-as argv[1]):   python tests/golden/make_golden.py [/path/to/reference]
+Run once on a machine that has a checkout of the reference; pass its path as argv[1] (or set
+REFERENCE_DIR):   python tests/golden/make_golden.py /path/to/triton-kernel-fused
 
 It imports `moe_eager` and `_sort_by_expert` from the reference's kernels/sm75/moe.py (they run on
 the CPU), feeds them seeded inputs built by oracle.moe_oracle.make_inputs, and stores:
@@ -21,7 +21,9 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_DIR", "")
+if not REF:
+    raise SystemExit("usage: make_golden.py /path/to/reference-checkout")
 sys.path.insert(0, REF)
 
 from kernels.sm75.moe import moe_eager, _sort_by_expert   # noqa: E402  (the reference itself)

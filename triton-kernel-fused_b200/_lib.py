@@ -29,6 +29,7 @@ _SIGNATURES = {
     "b200moe_status_string": (ctypes.c_char_p, [c_int]),
     "b200moe_padded_rows_cap": (c_int64, [c_int64, c_int]),
     "b200moe_set_reserved_sms": (c_int, [c_int]),
+    "b200moe_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_void_p]),
     "b200moe_router_topk_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_float,
                                         c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200moe_router_topk_bwd": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,

@@ -5,6 +5,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace b200moe {
 
@@ -34,6 +35,22 @@ int num_sms() {
   return n;
 }
 
+// One CTA waits on an mbarrier that nothing ever completes, with a limit of `limit_cycles` SM clocks:
+// the wait gives up, the status word receives ST_SELFTEST_TIMEOUT and the kernel returns normally.
+__global__ void selftest_bounded_wait_kernel(int* status, long long limit_cycles) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const bool done = mbar_wait(smem_u32(&bar), 0, &abort_flag, ST_SELFTEST_TIMEOUT, limit_cycles);
+  __syncthreads();
+  if (threadIdx.x == 0 && !done && abort_flag != 0) atomicCAS(status, 0, abort_flag);
+}
+
 static std::atomic<int> g_reserved_sms{0};
 
 int gemm_cta_budget() {
@@ -45,6 +62,17 @@ int gemm_cta_budget() {
 }  // namespace b200moe
 
 extern "C" {
+
+int b200moe_selftest_bounded_wait(int32_t* status, int64_t limit_cycles, b200moe_stream_t stream) {
+  if (status == nullptr || limit_cycles < 1000 || limit_cycles > 2000000000LL) {
+    b200moe::set_error("selftest_bounded_wait: status must be non-null and 1e3 <= limit_cycles <= 2e9");
+    return B200MOE_E_BAD_SHAPE;
+  }
+  b200moe::selftest_bounded_wait_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(status, limit_cycles);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return b200moe::cuda_fail(e, "selftest_bounded_wait launch");
+  return 0;
+}
 
 int b200moe_set_reserved_sms(int n) {
   if (n < 0 || n >= b200moe::num_sms()) {
@@ -67,6 +95,7 @@ const char* b200moe_status_string(int s) {
     case b200moe::ST_WAIT_MMA_TMEM: return "GEMM: MMA issuer gave up waiting for a drained accumulator";
     case b200moe::ST_WAIT_EPILOGUE: return "GEMM: epilogue gave up waiting for a finished accumulator";
     case b200moe::ST_BAD_EXPERT_INDEX: return "permute: expert index outside [0, E)";
+    case b200moe::ST_SELFTEST_TIMEOUT: return "self-test: the bounded wait ran out (expected)";
     default: return "unknown status";
   }
 }

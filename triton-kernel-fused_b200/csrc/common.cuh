@@ -15,7 +15,8 @@ enum : int {
   ST_WAIT_MMA_FULL = 2,   // MMA issuer: a stage never filled
   ST_WAIT_MMA_TMEM = 3,   // MMA issuer: the accumulator was never drained
   ST_WAIT_EPILOGUE = 4,   // epilogue: the accumulator never completed
-  ST_BAD_EXPERT_INDEX = 5 // permute: an expert index outside [0, E)
+  ST_BAD_EXPERT_INDEX = 5,// permute: an expert index outside [0, E)
+  ST_SELFTEST_TIMEOUT = 6 // self-test: a wait that nothing completes ran out, as intended
 };
 
 void set_error(const char* fmt, ...);
