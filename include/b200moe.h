@@ -81,6 +81,13 @@ int b200moe_router_topk_bwd(const void* logits, int input_kind, const int64_t* i
 int b200moe_router_bias_update(float* bias, const int32_t* counts, int E, float u,
                                b200moe_stream_t stream);
 
+/* Conv-router front end (kernels/sm75/router.py:186-190 conv1d with padding K-1, :214-218 backward):
+ * unfold: xu (B*S, K*H) with xu[(b,s), j*H+h] = x[b, s-(K-1)+j, h] or 0, so that the causal K-tap conv is one
+ * GEMM against Wf (E, K*H), Wf[e, j*H+h] = W[e,h,j];  fold: grad_x[b,s,h] = sum_j grad_xu[(b,s+K-1-j), j*H+h]. */
+int b200moe_conv_unfold(const void* x, int64_t B, int64_t S, int64_t H, int K, void* xu, b200moe_stream_t stream);
+int b200moe_conv_fold(const void* grad_xu, int64_t B, int64_t S, int64_t H, int K, void* grad_x,
+                      b200moe_stream_t stream);
+
 /* ---- dense bf16 GEMMs on tcgen05 (router projections) ----------------------------------------
  * Replace the cuBLAS calls at kernels/sm75/router.py:235 (logits), :258 (dX), :259 (dW).
  * nt: D(M,N) = A(M,K) * B(N,K)^T      nn: D(M,N) = A(M,K) * B(K,N)

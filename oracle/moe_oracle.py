@@ -244,8 +244,8 @@ def layer_fwd_bwd(x, gate_weight, bias, gate_up_proj, down_proj, top_k, grad_out
 # ----------------------------------------------------------------------------- comparators
 def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
     """||a-b|| / ||b|| in fp64 (the reference's rel(), .autoresearch/grouped_parity.py:14-15)."""
-    a = a.double().flatten()
-    b = b.double().flatten()
+    a = a.detach().double().flatten()
+    b = b.detach().double().flatten()
     return float((a - b).norm() / b.norm().clamp_min(1e-30))
 
 
@@ -323,3 +323,24 @@ def moe_experts_polyglu(hidden, top_k_indices, top_k_weights, gate_up_proj, down
         inter = polyglu_act(gu[:, :I], codes[e], a, g).to(gu.dtype) * gu[:, I:]
         out = out.index_add(0, rows, ((inter @ w_dn[e].t()) * w).float())
     return out.to(hidden.dtype)
+
+
+# ----------------------------------------------------------------------------- conv router
+def conv_router_logits(x, conv_weight):
+    """Causal K-tap conv logits of the reference's conv router: x (B,S,H), conv_weight (E,H,K) ->
+    (B*S, E); kernels/sm75/router.py:186-190 (conv1d with padding K-1, first S outputs) and the eager
+    statement bench.py:414-416 (left pad K-1)."""
+    B, S, H = x.shape
+    K = conv_weight.shape[2]
+    xp = F.pad(x.transpose(1, 2), (K - 1, 0))
+    return F.conv1d(xp, conv_weight).transpose(1, 2).reshape(B * S, -1)
+
+
+def conv_router_fwd(x, conv_weight, bias, top_k, norm_topk=True, scale=1.0, logits_dtype=None):
+    """Forward of `fused_router`: conv logits (rounded to logits_dtype when given, as the reference
+    stores them in x's dtype), then the shared epilogue.  Returns idx, w, counts, logits."""
+    logits = conv_router_logits(x.float(), conv_weight.float())
+    if logits_dtype is not None:
+        logits = logits.to(logits_dtype)
+    idx, w, counts = router_epilogue_fwd(logits, bias, top_k, norm_topk, scale)
+    return idx, w, counts, logits

@@ -1,0 +1,60 @@
+"""Conv router (`fused_router`): CPU checks of the oracle, GPU parity of the CUDA path."""
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+DEV = "cuda"
+
+
+def test_conv_logits_equal_unfolded_gemm():
+    """The causal conv equals one GEMM over the unfolded input (the formulation the CUDA path uses)."""
+    g = torch.Generator().manual_seed(0)
+    B, S, H, E, K = 3, 17, 16, 5, 4
+    x = torch.randn(B, S, H, generator=g)
+    w = torch.randn(E, H, K, generator=g)
+    ref = O.conv_router_logits(x, w)
+    xu = torch.zeros(B, S, K, H)
+    for j in range(K):
+        sh = K - 1 - j
+        xu[:, sh:, j] = x[:, :S - sh] if sh > 0 else x
+    wf = w.permute(0, 2, 1).reshape(E, K * H)
+    assert torch.allclose(xu.reshape(B * S, K * H) @ wf.t(), ref, atol=1e-5)
+    # causality: changing x[b, s] never changes logits before s
+    x2 = x.clone()
+    x2[:, 10] += 1.0
+    d = (O.conv_router_logits(x2, w) - ref).view(B, S, E).abs().amax(-1)
+    assert (d[:, :10] == 0).all() and (d[:, 10:10 + K] > 0).all() and (d[:, 10 + K:] == 0).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,S,H,E,K,k", [(4, 512, 256, 16, 4, 2), (2, 300, 512, 64, 3, 6)])
+def test_fused_conv_router_forward_backward(pkg, B, S, H, E, K, k):
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(B, S, H, generator=g).to(torch.bfloat16)
+    w = (torch.randn(E, H, K, generator=g) * 0.02).to(torch.bfloat16)
+    bias = torch.randn(E, generator=g) * 0.01
+    G = torch.randn(B, S, k, generator=g)
+    xd = x.to(DEV).requires_grad_(True)
+    wd = w.to(DEV).requires_grad_(True)
+    idx, wt, counts = pkg.fused_router(xd, wd, bias.to(DEV), k, E, return_counts=True)
+    assert idx.shape == (B, S, k) and wt.dtype == torch.float32
+    (wt * G.to(DEV)).sum().backward()
+    pkg.check_status()
+    # oracle: same bf16 inputs, logits rounded to bf16 like the CUDA path
+    xo = x.float().requires_grad_(True)
+    wo = w.float().requires_grad_(True)
+    logits = O.conv_router_logits(xo, wo)
+    logits_r = logits + (logits.detach().to(torch.bfloat16).float() - logits.detach())
+    idx_o, _, counts_o = O.router_epilogue_fwd(logits_r.detach(), bias, k)
+    s = torch.sigmoid(logits_r)
+    ww = s.gather(1, idx_o)
+    ww = ww / (ww.sum(-1, keepdim=True) + 1e-20)
+    (ww * G.view(B * S, k)).sum().backward()
+    rows = (idx.view(B * S, k).cpu() == idx_o).all(1)
+    assert rows.float().mean() > 0.99          # a logit on a bf16 rounding boundary can flip a pick
+    assert O.rel_l2(wt.view(B * S, k).cpu()[rows], ww.detach()[rows]) < 1e-2
+    assert torch.equal(counts.cpu().long(), torch.bincount(idx.flatten().cpu(), minlength=E))
+    gx, gxo = xd.grad.float().cpu().view(B * S, H), xo.grad.view(B * S, H)
+    assert O.rel_l2(gx, gxo) < 6e-2            # includes the few flipped tokens
+    assert O.rel_l2(wd.grad.float().cpu(), wo.grad) < 6e-2

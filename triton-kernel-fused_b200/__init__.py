@@ -4,12 +4,12 @@ fused SwiGLU, weighted combine — forward and backward — behind the reference
 Requires the in-tree libb200moe.so (see _lib.build); there is no CPU or library fallback."""
 from ._lib import build, check_status, lib, LIB_PATH, EXPORTED
 from .moe import moe, moe_grouped, moe_per_expert, GROUPED_MIN_TOKENS
-from .router import fused_mlp_router, FusedMLPRouter, router_bias_update
+from .router import fused_mlp_router, FusedMLPRouter, fused_router, FusedConvRouter, router_bias_update
 from .layer import MoELayer
 from .mxfp8 import moe_mxfp8
 from . import ops
 from .ops import TILE_M
 from .ep import ExpertParallelMoELayer, ep_moe
 
-__all__ = ["moe", "moe_grouped", "moe_per_expert", "GROUPED_MIN_TOKENS", "fused_mlp_router",
+__all__ = ["moe", "moe_grouped", "moe_per_expert", "GROUPED_MIN_TOKENS", "fused_mlp_router", "fused_router", "FusedConvRouter",
            "FusedMLPRouter", "router_bias_update", "MoELayer", "moe_mxfp8", "ExpertParallelMoELayer", "ep_moe", "ops", "build", "lib", "check_status"]

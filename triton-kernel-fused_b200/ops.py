@@ -398,3 +398,21 @@ def special_rows(src, dst, act_codes, perm: Permutation, first_special):
     L.check(L.lib().b200moe_special_rows(L.ptr(src), L.ptr(perm.tile_expert), L.ptr(act_codes), L.ptr(perm.poffs),
                                          int(first_special), perm.E, H, perm.cap, L.ptr(dst), L.stream_of(src)))
     return dst
+
+
+# ----------------------------------------------------------------------------- conv router front end
+@_op("conv_unfold", 1)
+def conv_unfold(x, K):
+    """x (B,S,H) bf16 -> (B*S, K*H): row (b,s) holds x[b, s-(K-1) .. s] (zeros before the sequence start)."""
+    L.require_cuda_bf16("x", x)
+    B, S, H = x.shape
+    xu = torch.empty(B * S, K * H, dtype=torch.bfloat16, device=x.device)
+    L.check(L.lib().b200moe_conv_unfold(L.ptr(x), B, S, H, int(K), L.ptr(xu), L.stream_of(x)))
+    return xu
+
+
+@_op("conv_fold", 1)
+def conv_fold(grad_xu, B, S, H, K):
+    gx = torch.empty(B, S, H, dtype=torch.bfloat16, device=grad_xu.device)
+    L.check(L.lib().b200moe_conv_fold(L.ptr(grad_xu), B, S, H, int(K), L.ptr(gx), L.stream_of(grad_xu)))
+    return gx

@@ -12,7 +12,7 @@ import torch
 from . import _lib as L
 from . import ops
 
-__all__ = ["fused_mlp_router", "FusedMLPRouter", "router_bias_update"]
+__all__ = ["fused_mlp_router", "FusedMLPRouter", "fused_router", "FusedConvRouter", "router_bias_update"]
 
 
 class FusedMLPRouter(torch.autograd.Function):
@@ -60,6 +60,57 @@ def fused_mlp_router(x, gate_weight, bias, top_k, num_experts, norm_topk_prob=Tr
         B, S, _ = x.shape
         idx = idx.view(B, S, top_k)
         w = w.view(B, S, top_k)
+    return (idx, w, counts) if return_counts else (idx, w)
+
+
+class FusedConvRouter(torch.autograd.Function):
+    """Causal-conv router (kernels/sm75/router.py:172-218, FusedConvRouterCuDNN): logits[b,s,e] =
+    sum_{j,h} x[b, s-(K-1)+j, h] * W[e,h,j], then the same sigmoid / bias / top-k epilogue.  The conv is one
+    tcgen05 GEMM over the unfolded input; backward = epilogue Jacobian, dX GEMM + fold, split-K dW GEMM."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, top_k, num_experts, norm_topk=True, scale=1.0):
+        if torch.is_autocast_enabled("cuda"):
+            dt = torch.get_autocast_dtype("cuda")
+            x, weight = x.to(dt), weight.to(dt)
+        L.require_cuda_bf16("x", x)
+        L.require_cuda_bf16("conv_weight", weight)
+        L.require(x.dim() == 3 and weight.dim() == 3 and weight.shape[1] == x.shape[2], "need x (B,S,H) and conv_weight (E,H,K)")
+        B, S, H = x.shape
+        E, _, K = weight.shape
+        L.require(num_experts is None or int(num_experts) == E, "num_experts must equal conv_weight.shape[0]")
+        xu = ops.conv_unfold(x.contiguous(), K)
+        wf = weight.permute(0, 2, 1).reshape(E, K * H).contiguous()      # Wf[e, j*H+h] = W[e,h,j]
+        logits = ops.gemm_nt(xu, wf)
+        bias32 = bias.detach().float().contiguous() if bias is not None else None
+        idx, w, counts = ops.router_topk_fwd(logits, bias32, top_k, norm_topk and top_k > 1, scale)
+        ctx.shape = (B, S, H, E, K)
+        ctx.save_for_backward(xu, wf, logits, idx)
+        ctx.norm, ctx.scale = bool(norm_topk and top_k > 1), float(scale)
+        ctx.mark_non_differentiable(idx, counts)
+        return idx, w, counts
+
+    @staticmethod
+    def backward(ctx, grad_idx, grad_weights, grad_counts):
+        xu, wf, logits, idx = ctx.saved_tensors
+        B, S, H, E, K = ctx.shape
+        gl = ops.router_topk_bwd(logits, idx, grad_weights, ctx.norm, ctx.scale)
+        grad_x = ops.conv_fold(ops.gemm_nn(gl, wf), B, S, H, K) if ctx.needs_input_grad[0] else None
+        grad_w = None
+        if ctx.needs_input_grad[1]:
+            grad_w = ops.gemm_tn(gl, xu).view(E, K, H).permute(0, 2, 1).contiguous()
+        return grad_x, grad_w, None, None, None, None, None
+
+
+def fused_router(x, conv_weight, bias, top_k, num_experts, norm_topk_prob=True, routed_scaling_factor=1.0,
+                 return_counts=False):
+    """Whole conv router: x (B,S,H), conv_weight (E,H,K) from nn.Conv1d(H,E,K), bias (E,) fp32 or None ->
+    (idx (B,S,k) int64, weights (B,S,k) fp32[, counts (E,) int32]); kernels/sm75/router.py:263-274."""
+    B, S, _ = x.shape
+    idx, w, counts = FusedConvRouter.apply(x, conv_weight, bias, top_k, num_experts, norm_topk_prob,
+                                           routed_scaling_factor)
+    idx = idx.view(B, S, top_k)
+    w = w.view(B, S, top_k)
     return (idx, w, counts) if return_counts else (idx, w)
 
 
