@@ -215,11 +215,18 @@ int b200moe_mxfp8_gemm_nt(const void* Aq, const void* Asf, const void* Bq, const
                           int64_t M, int64_t N, int64_t K, int32_t* status, b200moe_stream_t stream);
 /* Grouped expert GEMM over padded rows; B is an (E*N, K) stack (N % 128 == 0).  epilogue: 0 = bf16
  * store, 1 = SwiGLU (N = 2I, weight rows 64-interleaved, D = gate_up, aux = inter), 2 = GLU backward
- * (N = I, aux = saved gate_up, D = grad_gate_up).  Same roles as the bf16 entry points above. */
+ * (N = I, aux = saved gate_up, D = grad_gate_up).  Same roles as the bf16 entry points above.
+ * q_out / q_sf (nullable, epilogues 1 and 2): the epilogue also writes its bf16 result quantised along the
+ * row -- inter as (rows, I) codes, grad_gate_up as (rows, 2I) codes -- i.e. the A operand of the next GEMM,
+ * bit-identical to b200moe_mxfp8_quant_rows on that result. */
 int b200moe_mxfp8_expert_gemm(int epilogue, const void* Aq, const void* Asf, const void* Bq,
                               const void* Bsf, const int32_t* tile_expert, const int32_t* poffs,
                               int64_t rows_cap, int E, int64_t N, int64_t K, int64_t I, void* D, void* aux,
-                              int32_t* status, b200moe_stream_t stream);
+                              void* q_out, void* q_sf, int32_t* status, b200moe_stream_t stream);
+/* Gather fused with the row quantiser: x_s[r] = x[row_slot[r]/k] (bf16, zero pad rows) plus its codes and
+ * scales (H % 32 == 0); replaces b200moe_gather_rows + b200moe_mxfp8_quant_rows. */
+int b200moe_mxfp8_gather_quant(const void* x, const int32_t* row_slot, const int32_t* total_rows, int k, int64_t H,
+                               int64_t rows_cap, void* x_s, void* q, void* sf, b200moe_stream_t stream);
 /* Weight gradient: out[e] (Na,Nb) bf16 = At[:, rows of e] * Bt[:, rows of e]^T, At (Na, rows_cap) and
  * Bt (Nb, rows_cap) quantised along the token rows (b200moe_mxfp8_quant_transpose). */
 int b200moe_mxfp8_expert_wgrad(const void* Atq, const void* Atsf, const void* Btq, const void* Btsf,

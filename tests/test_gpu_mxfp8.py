@@ -96,3 +96,28 @@ def test_mxfp8_rejects_unaligned_width(pkg):
     dn = torch.zeros(2, 192, 128, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(ValueError, match="multiples of 128"):
         pkg.moe_mxfp8(x, idx, w, gu, dn, torch.zeros(2, dtype=torch.int32, device=DEV))
+
+
+def test_producer_epilogues_quantise_bit_identically(pkg):
+    """The quantised copies written by the gather and by the SwiGLU / GLU-backward epilogues equal a
+    separate quant_rows pass over the bf16 results, bit for bit (live rows)."""
+    T, H, E, I, k = 1024, 256, 4, 256, 2
+    ops = pkg.ops
+    inp = O.make_inputs(T, H, E, I, k, seed=61, dtype=torch.bfloat16)
+    idx, w, _, _ = O.mlp_router_fwd(inp["x"], inp["gate_weight"], None, k)
+    perm = ops.permute_build(idx.to(DEV), E)
+    total = int(perm.poffs[-1])
+    x_s, xq, xsf = ops.mxfp8_gather_quant(inp["x"].to(DEV), perm)
+    q_ref, _ = ops.mxfp8_quant_rows(x_s)
+    assert torch.equal(x_s[:total], ops.gather_rows(inp["x"].to(DEV), perm)[:total])
+    assert torch.equal(xq[:total], q_ref[:total])
+    wq, wsf = ops.mxfp8_quant_rows(inp["gate_up"].to(DEV).view(E * 2 * I, H), interleave_I=I)
+    gate_up = torch.empty(perm.cap, 2 * I, dtype=torch.bfloat16, device=DEV)
+    inter = torch.empty(perm.cap, I, dtype=torch.bfloat16, device=DEV)
+    _, iq, isf = ops.mxfp8_expert_gemm(ops.EPI_SWIGLU, xq, xsf, wq, wsf, perm, 2 * I, H, I, gate_up, inter,
+                                       quantise_result=True)
+    iq_ref, isf_ref = ops.mxfp8_quant_rows(inter)
+    pkg.check_status()
+    assert torch.equal(iq[:total], iq_ref[:total])
+    cs = Q.quantise(inter[:total].float().cpu())[1]
+    assert _sf_equal(isf[: Q.sf_atoms(cs).numel()], cs)

@@ -26,7 +26,6 @@
 namespace b200moe {
 
 constexpr int BK = 64;   // k-block: 64 bf16 = one 128-byte swizzle row
-constexpr int kStageOutBytes = 32 * 128;   // one epilogue warp's staging box: 32 rows x 64 bf16
 
 // BN = 256 kernels with a bf16 result stage it in shared memory and write it with TMA stores
 template <int BN, int EPI>
@@ -54,27 +53,6 @@ struct Cfg {
   static constexpr int TILE_ROWS = BM * CTAS;
 };
 
-
-__device__ __forceinline__ void stage_row(uint8_t* buf, int lane, const uint32_t* pk) {
-#pragma unroll
-  for (int j = 0; j < 8; ++j)
-    *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-        make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-}
-// make the staged box visible to the async proxy and let lane 0 issue the store
-__device__ __forceinline__ void store_box(const CUtensorMap* tm, uint8_t* buf, int lane, int c0, int c1, int c2) {
-  fence_proxy_async_smem();
-  __syncwarp();
-  if (lane == 0) {
-    tma_store_3d(tm, smem_u32(buf), c0, c1, c2);
-    bulk_commit_group();
-  }
-}
-// the staging box may be overwritten again
-__device__ __forceinline__ void staging_free(int lane) {
-  if (lane == 0) bulk_wait_read_all();
-  __syncwarp();
-}
 
 template <int BN, int EPI, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)

@@ -12,6 +12,7 @@
 #include <stdlib.h>
 
 #include "gemm_common.cuh"
+#include "mxfp8_quant.cuh"
 
 namespace b200moe {
 
@@ -32,6 +33,10 @@ struct Fp8Params {
   const uint8_t* sfb;
   int sfa_kc, sfb_kc;       // k-chunks (of 128) per row-block
   int b_rows_per_group;     // rows of B per expert (GROUPED_M), multiple of 128
+  // optional: the epilogue also emits its bf16 result quantised along the row (the producer of the
+  // next GEMM's A operand): SwiGLU -> inter (I bytes per row), GLU backward -> grad_gate_up (2I per row)
+  uint8_t* q_out;
+  uint8_t* q_sf;
 };
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -223,7 +228,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (col0 < I) {
           __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(p.D) + row * (2LL * I);
           __nv_bfloat16* it_out = reinterpret_cast<__nv_bfloat16*>(p.aux) + row * static_cast<long long>(I);
-          uint32_t g[32], u[32];
+          uint32_t g[32], u[32], hq[16];
           tmem_ld32(taddr + half * 32, g);
           tmem_ld32(taddr + 64 + half * 32, u);
           tmem_ld_wait();
@@ -245,8 +250,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               *reinterpret_cast<uint4*>(gu + col) = make_uint4(og[0], og[1], og[2], og[3]);
               *reinterpret_cast<uint4*>(gu + I + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
               *reinterpret_cast<uint4*>(it_out + col) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+#pragma unroll
+              for (int h = 0; h < 4; ++h) hq[4 * v + h] = oh[h];
             }
           }
+          if (fp.q_out != nullptr)   // I % 128 == 0: a chunk is one whole 32-element block of the row
+            mx_quant_store32(hq, fp.q_out + row * static_cast<long long>(I) + col0, fp.q_sf, row, col0 >> 5, I >> 7);
         }
       } else {   // EPI_GLU_BWD: accumulator = grad_inter columns [n0, n0+128), this warp 64 of them
         const int I = p.I;
@@ -266,6 +275,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           tmem_ld32(taddr + c0, r);
           tmem_ld_wait();
           glu_bwd32(r, g4, u4, og, ou);
+          if (fp.q_out != nullptr) {   // blocks of the (rows, 2I) grad_gate_up: gate half, then up half
+            const int colq = t.n0 + c0;
+            mx_quant_store32(og, fp.q_out + row * (2LL * I) + colq, fp.q_sf, row, colq >> 5, (2 * I) >> 7);
+            mx_quant_store32(ou, fp.q_out + row * (2LL * I) + I + colq, fp.q_sf, row, (I + colq) >> 5, (2 * I) >> 7);
+          }
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             const int col = t.n0 + c0 + v * 8;
@@ -300,9 +314,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 // epilogue of a tile runs while the producer already refills the stages of the next one.
 constexpr int PBN = 256;
 constexpr int kPStage = 34816;           // A 16 KB + B 16 KB + SFA 512 B + SFB 1 KB, rounded to 1 KB
-constexpr int kPStages = 6;
+constexpr int kPStages = 5;
 constexpr int kPSfCols = 16;             // tensor-memory columns per stage: SFA 4 + SFB 8 (+4 spare)
-constexpr int kPSmemBytes = kPStages * kPStage + (2 * kPStages + 2) * 8 + 16 + 1024;
+constexpr int kPEpiBytes = kEpiWarps * kStageOutBytes;   // one 32 x 64 bf16 staging box per epilogue warp
+constexpr int kPSmemBytes = kPStages * kPStage + kPEpiBytes + (2 * kPStages + 2) * 8 + 16 + 1024;
 
 // pair form of the 3-D load for the scale tensors {128 u32, k-chunks, row-blocks}
 __device__ __forceinline__ void umma_mxf8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -326,13 +341,15 @@ template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
+                       const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmD2,
                        const Fp8Params fp) {
   const GemmParams& p = fp.g;
   constexpr int TN = PBN, TM = 2 * BM;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPStages * kPStage);
+  uint8_t* epi_smem = smem + kPStages * kPStage;          // 1 KB aligned: stages are multiples of 1 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + kPEpiBytes);
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = smem_u32(bars + kPStages);
   const uint32_t bar_tfull = smem_u32(bars + 2 * kPStages);
@@ -457,96 +474,117 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       __syncwarp();
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-      const long long row = static_cast<long long>(t.m0) + BM * cta_rank + q * 32 + lane;
+      const int row0 = t.m0 + BM * cta_rank + q * 32;
+      const long long row = static_cast<long long>(row0) + lane;
       const bool have_acc = t.nkb > 0;
+      uint8_t* sbuf = epi_smem + (warp - 2) * kStageOutBytes;
+      const int grp = (p.sched == SCHED_GROUPED_K) ? t.g : 0;
+      // results are packed to bf16, staged per warp as 32 rows x 64 columns and written by TMA stores
+      // (which clip at the tensor's bounds)
       if constexpr (EPI == EPI_STORE) {
-        const bool row_ok = (p.sched == SCHED_GROUPED_M) || (row < p.M);
-        const long long base = (p.sched == SCHED_GROUPED_K ? t.g * p.d_group_stride : 0) + row * p.ldd + t.n0;
 #pragma unroll 1
-        for (int c0 = half * 128; c0 < half * 128 + 128; c0 += 32) {
-          if (t.n0 + c0 >= p.N) break;
-          uint32_t r[32];
-          if (have_acc) {
-            tmem_ld32(taddr + c0, r);
-            tmem_ld_wait();
-          } else {
+        for (int c = half * 128; c < half * 128 + 128; c += 64) {
+          if (t.n0 + c >= p.N) break;
+          uint32_t pk[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = 0u;
-          }
-          if (row_ok) {
-            __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + base + c0;
+          for (int sub = 0; sub < 2; ++sub) {
+            uint32_t r[32];
+            if (have_acc) {
+              tmem_ld32(taddr + c + 32 * sub, r);
+              tmem_ld_wait();
+            } else {
 #pragma unroll
-            for (int v = 0; v < 4; ++v)
-              if (t.n0 + c0 + v * 8 < p.N) *reinterpret_cast<uint4*>(d + v * 8) = pack8(r + v * 8);
+              for (int i = 0; i < 32; ++i) r[i] = 0u;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              pk[16 * sub + i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
           }
+          staging_free(lane);
+          stage_row(sbuf, lane, pk);
+          store_box(&tmD, sbuf, lane, t.n0 + c, row0, grp);
         }
       } else if constexpr (EPI == EPI_SWIGLU) {
         // weight rows are 64-interleaved: accumulator columns [128h, 128h+64) = gate and [128h+64, 128h+128) = up
         // of the intermediate columns [n0/2 + 64h, n0/2 + 64h + 64)
         const int I = p.I;
-        __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(p.D) + row * (2LL * I);
-        __nv_bfloat16* it_out = reinterpret_cast<__nv_bfloat16*>(p.aux) + row * static_cast<long long>(I);
-#pragma unroll 1
-        for (int c = 0; c < 64; c += 32) {
-          const int col0 = t.n0 / 2 + 64 * half + c;
-          if (col0 >= I) break;
-          uint32_t g[32], u[32];
-          tmem_ld32(taddr + 128 * half + c, g);
-          tmem_ld32(taddr + 128 * half + 64 + c, u);
-          tmem_ld_wait();
+        const int col0 = t.n0 / 2 + 64 * half;
+        if (col0 < I) {
+          uint32_t og[32], ou[32], oh[32];
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int col = col0 + v * 8;
-            if (col < I) {
-              uint32_t og[4], ou[4], oh[4];
+          for (int sub = 0; sub < 2; ++sub) {
+            uint32_t g[32], u[32];
+            tmem_ld32(taddr + 128 * half + 32 * sub, g);
+            tmem_ld32(taddr + 128 * half + 64 + 32 * sub, u);
+            tmem_ld_wait();
 #pragma unroll
-              for (int h = 0; h < 4; ++h) {
-                og[h] = pack_bf16x2(__uint_as_float(g[v * 8 + 2 * h]), __uint_as_float(g[v * 8 + 2 * h + 1]));
-                ou[h] = pack_bf16x2(__uint_as_float(u[v * 8 + 2 * h]), __uint_as_float(u[v * 8 + 2 * h + 1]));
-                const float2 gf = unpack_bf16x2(og[h]);
-                const float2 uf = unpack_bf16x2(ou[h]);
-                const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
-                const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
-                oh[h] = pack_bf16x2(gf.x * s0 * uf.x, gf.y * s1 * uf.y);
-              }
-              *reinterpret_cast<uint4*>(gu + col) = make_uint4(og[0], og[1], og[2], og[3]);
-              *reinterpret_cast<uint4*>(gu + I + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
-              *reinterpret_cast<uint4*>(it_out + col) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+            for (int i = 0; i < 16; ++i) {
+              const uint32_t pg = pack_bf16x2(__uint_as_float(g[2 * i]), __uint_as_float(g[2 * i + 1]));
+              const uint32_t pu = pack_bf16x2(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]));
+              const float2 gf = unpack_bf16x2(pg);
+              const float2 uf = unpack_bf16x2(pu);
+              const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
+              const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
+              og[16 * sub + i] = pg;
+              ou[16 * sub + i] = pu;
+              oh[16 * sub + i] = pack_bf16x2(gf.x * s0 * uf.x, gf.y * s1 * uf.y);
             }
           }
+          if (fp.q_out != nullptr) {   // the quantised `inter` for the down GEMM, two 32-element blocks
+            mx_quant_store32(oh, fp.q_out + row * static_cast<long long>(I) + col0, fp.q_sf, row, col0 >> 5, I >> 7);
+            mx_quant_store32(oh + 16, fp.q_out + row * static_cast<long long>(I) + col0 + 32, fp.q_sf, row,
+                             (col0 + 32) >> 5, I >> 7);
+          }
+          staging_free(lane);
+          stage_row(sbuf, lane, og);
+          store_box(&tmD, sbuf, lane, col0, row0, 0);    // gate half of gate_up
+          staging_free(lane);
+          stage_row(sbuf, lane, ou);
+          store_box(&tmD, sbuf, lane, col0, row0, 1);    // up half
+          staging_free(lane);
+          stage_row(sbuf, lane, oh);
+          store_box(&tmD2, sbuf, lane, col0, row0, 0);   // inter
         }
       } else {   // EPI_GLU_BWD: accumulator = grad_inter columns [n0, n0+256), this warp 128 of them
         const int I = p.I;
         const __nv_bfloat16* gu = reinterpret_cast<const __nv_bfloat16*>(p.aux) + row * (2LL * I);
-        __nv_bfloat16* ggu = reinterpret_cast<__nv_bfloat16*>(p.D) + row * (2LL * I);
 #pragma unroll 1
-        for (int c0 = half * 128; c0 < half * 128 + 128; c0 += 32) {
-          if (t.n0 + c0 >= I) break;
-          uint4 g4[4], u4[4];
+        for (int c = half * 128; c < half * 128 + 128; c += 64) {
+          if (t.n0 + c >= I) break;
+          uint32_t og[32], ou[32];
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int col = t.n0 + c0 + v * 8;
-            g4[v] = col < I ? __ldg(reinterpret_cast<const uint4*>(gu + col)) : make_uint4(0u, 0u, 0u, 0u);
-            u4[v] = col < I ? __ldg(reinterpret_cast<const uint4*>(gu + I + col)) : make_uint4(0u, 0u, 0u, 0u);
-          }
-          uint32_t r[32], og[16], ou[16];
-          tmem_ld32(taddr + c0, r);
-          tmem_ld_wait();
-          glu_bwd32(r, g4, u4, og, ou);
+          for (int sub = 0; sub < 2; ++sub) {
+            const int colq = t.n0 + c + 32 * sub;
+            uint4 g4[4], u4[4];
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int col = t.n0 + c0 + v * 8;
-            if (col < I) {
-              *reinterpret_cast<uint4*>(ggu + col) = make_uint4(og[4 * v], og[4 * v + 1], og[4 * v + 2], og[4 * v + 3]);
-              *reinterpret_cast<uint4*>(ggu + I + col) = make_uint4(ou[4 * v], ou[4 * v + 1], ou[4 * v + 2], ou[4 * v + 3]);
+            for (int v = 0; v < 4; ++v) {
+              const int col = colq + v * 8;
+              g4[v] = col < I ? __ldg(reinterpret_cast<const uint4*>(gu + col)) : make_uint4(0u, 0u, 0u, 0u);
+              u4[v] = col < I ? __ldg(reinterpret_cast<const uint4*>(gu + I + col)) : make_uint4(0u, 0u, 0u, 0u);
+            }
+            uint32_t r[32];
+            tmem_ld32(taddr + c + 32 * sub, r);
+            tmem_ld_wait();
+            glu_bwd32(r, g4, u4, og + 16 * sub, ou + 16 * sub);
+            if (fp.q_out != nullptr) {   // blocks of the (rows, 2I) grad_gate_up: gate half, then up half
+              mx_quant_store32(og + 16 * sub, fp.q_out + row * (2LL * I) + colq, fp.q_sf, row, colq >> 5, (2 * I) >> 7);
+              mx_quant_store32(ou + 16 * sub, fp.q_out + row * (2LL * I) + I + colq, fp.q_sf, row, (I + colq) >> 5,
+                               (2 * I) >> 7);
             }
           }
+          staging_free(lane);
+          stage_row(sbuf, lane, og);
+          store_box(&tmD, sbuf, lane, t.n0 + c, row0, 0);   // grad_gate
+          staging_free(lane);
+          stage_row(sbuf, lane, ou);
+          store_box(&tmD, sbuf, lane, t.n0 + c, row0, 1);   // grad_up
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty_leader);
     }
+    if (lane == 0) bulk_wait_all();   // every TMA store of this warp has completed
   }
 
   tc_fence_before();
@@ -579,7 +617,8 @@ static int map_sf(CUtensorMap* tm, const void* sf, long long row_blocks, long lo
 
 template <int EPI>
 static int launch_fp8_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmSFA,
-                           const CUtensorMap& tmSFB, const Fp8Params& fp, int max_tiles, cudaStream_t stream) {
+                           const CUtensorMap& tmSFB, const CUtensorMap& tmD, const CUtensorMap& tmD2,
+                           const Fp8Params& fp, int max_tiles, cudaStream_t stream) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -601,7 +640,7 @@ static int launch_fp8_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  B200_CUDA(cudaLaunchKernelEx(&cfg, gemm_mxfp8_pair_kernel<EPI>, tmA, tmB, tmSFA, tmSFB, fp));
+  B200_CUDA(cudaLaunchKernelEx(&cfg, gemm_mxfp8_pair_kernel<EPI>, tmA, tmB, tmSFA, tmSFB, tmD, tmD2, fp));
   return 0;
 }
 
@@ -655,7 +694,20 @@ static int launch_any(const void* Aq, long long a_rows, const void* Bq, long lon
   if (rc) return rc;
   rc = map_sf(&tmSFB, fp.sfb, ceil_div(b_rows * b_groups, 128), fp.sfb_kc, 2);
   if (rc) return rc;
-  return launch_fp8_pair<EPI>(tmA, tmB, tmSFA, tmSFB, fp, max_tiles_1cta > 0 ? (max_tiles_1cta + 3) / 4 : 0, stream);
+  // bf16 outputs as {columns, rows, groups} tensors, box {64, 32}, for the TMA-store epilogue
+  CUtensorMap tmD, tmD2 = tmA;
+  const GemmParams& g = fp.g;
+  if (EPI == EPI_STORE) {
+    const long long rows = (g.sched == SCHED_GROUPED_K || g.sched == SCHED_DENSE) ? g.M : a_rows;
+    const long long groups = (g.sched == SCHED_GROUPED_K) ? g.num_groups : 1;
+    rc = make_map(&tmD, g.D, g.N, rows, groups, g.ldd, g.sched == SCHED_GROUPED_K ? g.d_group_stride : rows * g.ldd, 64, 32);
+  } else {
+    rc = make_map(&tmD, g.D, g.I, a_rows, 2, 2LL * g.I, g.I, 64, 32);          // gate_up / grad_gate_up halves
+    if (rc == 0 && EPI == EPI_SWIGLU) rc = make_map(&tmD2, g.aux, g.I, a_rows, 1, g.I, a_rows * g.I, 64, 32);
+  }
+  if (rc) return rc;
+  return launch_fp8_pair<EPI>(tmA, tmB, tmSFA, tmSFB, tmD, tmD2, fp, max_tiles_1cta > 0 ? (max_tiles_1cta + 3) / 4 : 0,
+                              stream);
 }
 
 }  // namespace b200moe
@@ -684,8 +736,12 @@ int b200moe_mxfp8_gemm_nt(const void* Aq, const void* Asf, const void* Bq, const
  * 2 GLU backward (N = I, aux = saved gate_up, D = grad_gate_up). */
 int b200moe_mxfp8_expert_gemm(int epilogue, const void* Aq, const void* Asf, const void* Bq, const void* Bsf,
                               const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E, int64_t N,
-                              int64_t K, int64_t I, void* D, void* aux, int32_t* status, b200moe_stream_t stream) {
+                              int64_t K, int64_t I, void* D, void* aux, void* q_out, void* q_sf, int32_t* status,
+                              b200moe_stream_t stream) {
   B200_CHECK_ARG(Aq && Asf && Bq && Bsf && D && tile_expert && poffs, B200MOE_E_NULL, "mxfp8_expert_gemm: null pointer");
+  B200_CHECK_ARG((q_out == nullptr) == (q_sf == nullptr), B200MOE_E_NULL, "mxfp8_expert_gemm: q_out and q_sf go together");
+  B200_CHECK_ARG(q_out == nullptr || (epilogue != EPI_STORE && I % 128 == 0 && aligned16(q_out)), B200MOE_E_BAD_SHAPE,
+                 "mxfp8_expert_gemm: quantised output needs the SwiGLU / GLU-backward epilogue and I %% 128 == 0");
   CHECK_K128(K); CHECK_K128(N); CHECK_I32(rows_cap);
   B200_CHECK_ARG(rows_cap % B200MOE_TILE_M == 0, B200MOE_E_BAD_SHAPE, "mxfp8_expert_gemm: rows_cap %% %d != 0", B200MOE_TILE_M);
   B200_CHECK_ARG(E >= 1 && E * N < (1LL << 31), B200MOE_E_BAD_SHAPE, "mxfp8_expert_gemm: E = %d", E);
@@ -695,6 +751,7 @@ int b200moe_mxfp8_expert_gemm(int epilogue, const void* Aq, const void* Asf, con
   fp.g.status = status;
   fp.sfa = (const uint8_t*)Asf; fp.sfb = (const uint8_t*)Bsf; fp.sfa_kc = fp.sfb_kc = (int)(K / 128);
   fp.b_rows_per_group = (int)N;
+  fp.q_out = (uint8_t*)q_out; fp.q_sf = (uint8_t*)q_sf;
   switch (epilogue) {
     case EPI_STORE: return launch_any<EPI_STORE>(Aq, rows_cap, Bq, N, E, K, fp, 0, (cudaStream_t)stream);
     case EPI_SWIGLU:

@@ -1,0 +1,52 @@
+// Device helpers of the MXFP8 quantisers, shared with the GEMM epilogues that quantise their own output.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace b200moe {
+
+__device__ __forceinline__ uint32_t e8m0_from_amax(float amax) {
+  const uint32_t e = (__float_as_uint(amax) >> 23) & 0xffu;   // biased exponent = floor(log2) + 127
+  return e > 8u ? (e - 8u > 254u ? 254u : e - 8u) : 0u;        // zero / denormal amax -> smallest scale
+}
+__device__ __forceinline__ float inv_scale_from_e8m0(uint32_t sb) {
+  return __uint_as_float((254u - sb) << 23);                   // 2^(127 - sb), sb <= 247 here
+}
+__device__ __forceinline__ uint32_t cvt4_e4m3(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+__device__ __forceinline__ long long sf_offset(long long row, long long kblock, long long k_chunks) {
+  return ((row >> 7) * k_chunks + (kblock >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kblock & 3);
+}
+
+// 32 consecutive bf16 values of one row (16 packed registers) -> 32 e4m3 bytes at `q32` and the scale
+// byte of (row, kblock); identical to what quant_rows_kernel writes for the same values.
+__device__ __forceinline__ void mx_quant_store32(const uint32_t* pk, uint8_t* q32, uint8_t* sf, long long row,
+                                                 long long kblock, long long k_chunks) {
+  float f[32];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float2 t = unpack_bf16x2(pk[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+    amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y)));
+  }
+  const uint32_t sb = e8m0_from_amax(amax);
+  const float inv = inv_scale_from_e8m0(sb);
+  uint4 o[2];
+  uint32_t* ow = reinterpret_cast<uint32_t*>(o);
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    ow[j] = cvt4_e4m3(f[4 * j] * inv, f[4 * j + 1] * inv, f[4 * j + 2] * inv, f[4 * j + 3] * inv);
+  reinterpret_cast<uint4*>(q32)[0] = o[0];
+  reinterpret_cast<uint4*>(q32)[1] = o[1];
+  sf[sf_offset(row, kblock, k_chunks)] = static_cast<uint8_t>(sb);
+}
+
+}  // namespace b200moe

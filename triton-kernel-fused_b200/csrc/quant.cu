@@ -13,25 +13,9 @@
 #include <cuda_fp8.h>
 
 #include "common.cuh"
-#include "ptx.cuh"
+#include "mxfp8_quant.cuh"
 
 namespace b200moe {
-
-__device__ __forceinline__ uint32_t e8m0_from_amax(float amax) {
-  const uint32_t e = (__float_as_uint(amax) >> 23) & 0xffu;   // biased exponent = floor(log2) + 127
-  return e > 8u ? (e - 8u > 254u ? 254u : e - 8u) : 0u;        // zero / denormal amax -> smallest scale
-}
-__device__ __forceinline__ float inv_scale_from_e8m0(uint32_t sb) {
-  return __uint_as_float((254u - sb) << 23);                   // 2^(127 - sb), sb <= 247 here
-}
-__device__ __forceinline__ uint32_t cvt4_e4m3(float a, float b, float c, float d) {
-  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
-  return lo | (hi << 16);
-}
-__device__ __forceinline__ long long sf_offset(long long row, long long kblock, long long k_chunks) {
-  return ((row >> 7) * k_chunks + (kblock >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kblock & 3);
-}
 
 // One thread quantises one block of 32 consecutive elements of a row.
 // interleave_I > 0: the source is a stack of (2I, C) gate|up matrices; destination rows are
@@ -141,6 +125,36 @@ quant_transpose_kernel(const __nv_bfloat16* __restrict__ x, long long G, long lo
   }
 }
 
+// Gather fused with the row quantiser: x_s[r] = x[row_slot[r] / k] (bf16 copy kept for the backward)
+// and its e4m3 codes + scales; pad rows become zeros with scale byte 0.  One thread per 32-element block.
+__global__ void __launch_bounds__(256)
+gather_quant_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ row_slot,
+                    const int* __restrict__ total_rows, int k, long long C, __nv_bfloat16* __restrict__ x_s,
+                    uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+  const long long blocks_per_row = C >> 5;
+  const long long k_chunks = (C + 127) >> 7;
+  const long long total = static_cast<long long>(*total_rows) * blocks_per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / blocks_per_row;
+    const long long b = i - r * blocks_per_row;
+    const int slot = row_slot[r];
+    uint4 v[4];
+    if (slot >= 0) {
+      const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<long long>(slot / k) * C + b * 32);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = __ldg(src + j);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(x_s + r * C + b * 32);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[j] = v[j];
+    mx_quant_store32(reinterpret_cast<const uint32_t*>(v), q + r * C + b * 32, sf, r, b, k_chunks);
+  }
+}
+
 }  // namespace b200moe
 
 using namespace b200moe;
@@ -169,6 +183,24 @@ int b200moe_mxfp8_quant_rows(const void* x, int64_t R, int64_t C, int64_t interl
   quant_rows_kernel<<<static_cast<int>(grid), 256, 0, (cudaStream_t)stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), R, C, interleave_I, reinterpret_cast<uint8_t*>(q),
       reinterpret_cast<uint8_t*>(sf));
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_mxfp8_gather_quant(const void* x, const int32_t* row_slot, const int32_t* total_rows, int k, int64_t H,
+                               int64_t rows_cap, void* x_s, void* q, void* sf, b200moe_stream_t stream) {
+  B200_CHECK_ARG(x && row_slot && total_rows && x_s && q && sf, B200MOE_E_NULL, "mxfp8_gather_quant: null pointer");
+  B200_CHECK_ARG(H > 0 && H % 32 == 0 && k >= 1, B200MOE_E_BAD_SHAPE, "mxfp8_gather_quant: H = %lld must be a multiple of 32",
+                 (long long)H);
+  B200_CHECK_ARG(aligned16(x) && aligned16(x_s) && aligned16(q), B200MOE_E_ALIGN, "mxfp8_gather_quant: pointers must be aligned");
+  if (rows_cap <= 0) return 0;
+  const long long total = rows_cap * (H / 32);
+  long long grid = (total + 255) / 256;
+  const long long cap = static_cast<long long>(num_sms()) * 32;
+  if (grid > cap) grid = cap;
+  gather_quant_kernel<<<static_cast<int>(grid), 256, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), row_slot, total_rows, k, H, reinterpret_cast<__nv_bfloat16*>(x_s),
+      reinterpret_cast<uint8_t*>(q), reinterpret_cast<uint8_t*>(sf));
   B200_CUDA(cudaGetLastError());
   return 0;
 }

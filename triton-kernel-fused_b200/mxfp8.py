@@ -9,13 +9,19 @@ operands of the wgrads).  Needs d_model % 128 == 0 and d_ff % 128 == 0.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib as L
 from . import ops
 from .moe import _amp_cast, _code_info
 
-__all__ = ["moe_mxfp8"]
+__all__ = ["moe_mxfp8", "FUSE_QUANT_EPILOGUE"]
+
+# When set (B200MOE_MXFP8_FUSE_QUANT=1; off by default, measured 2 % slower), the SwiGLU and GLU-backward epilogues also write their result quantised for the GEMM that
+# consumes it (bit-identical to the separate row quantiser); when clear, a row-quantiser pass does it.
+FUSE_QUANT_EPILOGUE = os.environ.get("B200MOE_MXFP8_FUSE_QUANT", "0") == "1"
 
 
 class _MoEMxfp8(torch.autograd.Function):
@@ -36,13 +42,16 @@ class _MoEMxfp8(torch.autograd.Function):
         dev = hidden.device
 
         perm = ops.permute_build(idx, E)
-        x_s = ops.gather_rows(hidden, perm)
-        xq, xsf = ops.mxfp8_quant_rows(x_s)
+        x_s, xq, xsf = ops.mxfp8_gather_quant(hidden, perm)             # the gather is the quantising producer
         wq, wsf = ops.mxfp8_quant_rows(gate_up_proj.view(E * twoI, H), interleave_I=I)
         gate_up = torch.empty(perm.cap, twoI, dtype=torch.bfloat16, device=dev)
         inter = torch.empty(perm.cap, I, dtype=torch.bfloat16, device=dev)
-        ops.mxfp8_expert_gemm(ops.EPI_SWIGLU, xq, xsf, wq, wsf, perm, twoI, H, I, gate_up, inter)
-        iq, isf = ops.mxfp8_quant_rows(inter)
+        if FUSE_QUANT_EPILOGUE:   # the SwiGLU epilogue also emits `inter` quantised for the down GEMM
+            _, iq, isf = ops.mxfp8_expert_gemm(ops.EPI_SWIGLU, xq, xsf, wq, wsf, perm, twoI, H, I, gate_up, inter,
+                                               quantise_result=True)
+        else:
+            ops.mxfp8_expert_gemm(ops.EPI_SWIGLU, xq, xsf, wq, wsf, perm, twoI, H, I, gate_up, inter)
+            iq, isf = ops.mxfp8_quant_rows(inter)
         dq, dsf = ops.mxfp8_quant_rows(down_proj.view(E * H, I))
         eo = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=dev)
         ops.mxfp8_expert_gemm(ops.EPI_STORE, iq, isf, dq, dsf, perm, H, I, I, eo)
@@ -68,13 +77,18 @@ class _MoEMxfp8(torch.autograd.Function):
             gq, gsf = ops.mxfp8_quant_rows(grad_eo)                       # K = H
             wtq, wtsf = ops.mxfp8_quant_transpose(down_proj)              # (E, I, H)
             grad_gu = torch.empty(perm.cap, twoI, dtype=torch.bfloat16, device=dev)
-            ops.mxfp8_expert_gemm(ops.EPI_GLU_BWD, gq, gsf, wtq, wtsf, perm, I, H, I, grad_gu, gate_up)
+            fuse = FUSE_QUANT_EPILOGUE and need_x   # grad_gate_up quantised along 2I feeds the dgrad below
+            res = ops.mxfp8_expert_gemm(ops.EPI_GLU_BWD, gq, gsf, wtq, wtsf, perm, I, H, I, grad_gu, gate_up,
+                                        quantise_result=fuse)
+            if fuse:
+                _, ggq, ggsf = res
+            elif need_x:
+                ggq, ggsf = ops.mxfp8_quant_rows(grad_gu)
             if need_gu:
                 at, atsf = ops.mxfp8_quant_transpose(grad_gu)             # (2I, rows)
                 bt, btsf = ops.mxfp8_quant_transpose(x_s)                 # (H, rows)
                 grad_gate_up_proj = ops.mxfp8_expert_wgrad(at, atsf, bt, btsf, perm)
             if need_x:
-                ggq, ggsf = ops.mxfp8_quant_rows(grad_gu)                 # K = 2I
                 wgt, wgtsf = ops.mxfp8_quant_transpose(gate_up_proj)      # (E, H, 2I)
                 grad_x_s = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=dev)
                 ops.mxfp8_expert_gemm(ops.EPI_STORE, ggq, ggsf, wgt, wgtsf, perm, H, twoI, I, grad_x_s)

@@ -322,11 +322,32 @@ def mxfp8_gemm_nt(aq, asf, bq, bsf):
 
 
 @_op("mxfp8_expert_gemm", 1)
-def mxfp8_expert_gemm(epilogue, aq, asf, bq, bsf, perm: Permutation, N, K, I, d, aux=None):
+def mxfp8_expert_gemm(epilogue, aq, asf, bq, bsf, perm: Permutation, N, K, I, d, aux=None, quantise_result=False):
+    """quantise_result (SwiGLU / GLU-backward epilogues): also return (codes, scale atoms) of the result
+    quantised along its rows, produced inside the epilogue."""
+    q = qsf = None
+    if quantise_result:
+        width = I if epilogue == EPI_SWIGLU else 2 * I
+        q = torch.empty(perm.cap, width, dtype=torch.uint8, device=d.device)
+        qsf = _sf_empty(perm.cap, width, d.device)
     L.check(L.lib().b200moe_mxfp8_expert_gemm(int(epilogue), L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf),
                                               L.ptr(perm.tile_expert), L.ptr(perm.poffs), perm.cap, perm.E, N, K, I,
-                                              L.ptr(d), L.ptr(aux), L.ptr(L.status_word(d.device)), L.stream_of(d)))
-    return d
+                                              L.ptr(d), L.ptr(aux), L.ptr(q), L.ptr(qsf),
+                                              L.ptr(L.status_word(d.device)), L.stream_of(d)))
+    return (d, q, qsf) if quantise_result else d
+
+
+@_op("mxfp8_gather_quant", 1)
+def mxfp8_gather_quant(x, perm: Permutation):
+    """Gather into the padded layout and quantise along the rows in one pass: (x_s bf16, codes, scale atoms)."""
+    L.require_cuda_bf16("hidden", x)
+    H = x.shape[1]
+    x_s = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=x.device)
+    q = torch.empty(perm.cap, H, dtype=torch.uint8, device=x.device)
+    sf = _sf_empty(perm.cap, H, x.device)
+    L.check(L.lib().b200moe_mxfp8_gather_quant(L.ptr(x), L.ptr(perm.row_slot), L.ptr(perm.total_rows), perm.k, H,
+                                               perm.cap, L.ptr(x_s), L.ptr(q), L.ptr(sf), L.stream_of(x)))
+    return x_s, q, sf
 
 
 @_op("mxfp8_expert_wgrad", 1)
