@@ -207,9 +207,14 @@ size_t b200moe_mxfp8_sf_bytes(int64_t rows, int64_t K);
  * gate|up matrices and output rows are re-ordered in groups of 64 gate rows then 64 up rows. */
 int b200moe_mxfp8_quant_rows(const void* x, int64_t R, int64_t C, int64_t interleave_I, void* q, void* sf,
                              b200moe_stream_t stream);
-/* x (G,R,C) bf16 -> q (G,C,R) e4m3 + scales, blocks along R (R % 32 == 0, C % 128 == 0 when G > 1). */
+/* x (G,R,C) bf16 -> q (G,C,R) e4m3 + scales, blocks along R (R % 32 == 0, C even). */
 int b200moe_mxfp8_quant_transpose(const void* x, int64_t G, int64_t R, int64_t C, void* q, void* sf,
                                   b200moe_stream_t stream);
+/* Both quantisations of x (G,R,C) in one pass over DRAM: q_rows/sf_rows as b200moe_mxfp8_quant_rows gives for
+ * x seen as (G*R, C) (interleave_I as there, with R = 2I), q_t/sf_t as b200moe_mxfp8_quant_transpose gives.
+ * R % 32 == 0, C % 32 == 0. */
+int b200moe_mxfp8_quant_both(const void* x, int64_t G, int64_t R, int64_t C, int64_t interleave_I, void* q_rows,
+                             void* sf_rows, void* q_t, void* sf_t, b200moe_stream_t stream);
 /* D (M,N) bf16 = dequant(A)(M,K) * dequant(B)(N,K)^T on tcgen05 block-scaled MMAs; K % 128 == 0. */
 int b200moe_mxfp8_gemm_nt(const void* Aq, const void* Asf, const void* Bq, const void* Bsf, void* D,
                           int64_t M, int64_t N, int64_t K, int32_t* status, b200moe_stream_t stream);

@@ -45,6 +45,32 @@ def test_quant_rows_interleave_and_transpose_bit_exact(pkg):
     assert _sf_equal(sft, cs.reshape(-1, cs.shape[-1]))
 
 
+@pytest.mark.parametrize("G,R,C", [(1, 32, 2), (1, 160, 200), (2, 96, 130), (3, 256, 384), (1, 4000 * 32, 64)])
+def test_quant_transpose_ragged_tiles_bit_exact(pkg, G, R, C):
+    """Tiles of 128 x 128 with partial row blocks and column tails, several groups, many row tiles."""
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(G, R, C, generator=g) * torch.logspace(-3, 3, C)[None, None, :]).to(torch.bfloat16)
+    x[0, :32, 0] = 0                                      # an all-zero block
+    qt, sft = pkg.ops.mxfp8_quant_transpose(x.to(DEV))
+    cq, cs = Q.quantise(x.float().transpose(1, 2).contiguous())
+    assert torch.equal(qt.cpu(), cq)
+    assert _sf_equal(sft, cs.reshape(-1, cs.shape[-1]))
+
+
+@pytest.mark.parametrize("G,R,C,I", [(1, 160, 224, 0), (3, 256, 384, 128), (2, 128, 96, 64), (1, 2048, 4096, 0)])
+def test_quant_both_equals_the_two_passes(pkg, G, R, C, I):
+    g = torch.Generator().manual_seed(4)
+    x = (torch.randn(G, R, C, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
+    q, sf, qt, sft = pkg.ops.mxfp8_quant_both(x, interleave_I=I)
+    q1, sf1 = pkg.ops.mxfp8_quant_rows(x.view(G * R, C), interleave_I=I)
+    qt1, sft1 = pkg.ops.mxfp8_quant_transpose(x)
+    assert torch.equal(q, q1) and torch.equal(qt, qt1)
+    live = Q.sf_atoms(torch.ones(G * R, C // 32, dtype=torch.uint8)) == 1
+    assert torch.equal(sf.cpu()[live], sf1.cpu()[live])
+    live_t = Q.sf_atoms(torch.ones(G * C, R // 32, dtype=torch.uint8)) == 1
+    assert torch.equal(sft.cpu()[live_t], sft1.cpu()[live_t])
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 264, 1024), (1000, 2048, 512), (64, 72, 256)])
 def test_mxfp8_gemm_matches_dequantised_product(pkg, M, N, K):
     g = torch.Generator().manual_seed(2)

@@ -61,6 +61,7 @@ _SIGNATURES = {
     "b200moe_mxfp8_sf_bytes": (c_size_t, [c_int64, c_int64]),
     "b200moe_mxfp8_quant_rows": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "b200moe_mxfp8_quant_transpose": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "b200moe_mxfp8_quant_both": (c_int, [c_void_p] + [c_int64] * 4 + [c_void_p] * 5),
     "b200moe_mxfp8_gemm_nt": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_void_p, c_void_p]),
     "b200moe_mxfp8_expert_gemm": (c_int, [c_int] + [c_void_p] * 6 + [c_int64, c_int, c_int64, c_int64, c_int64] +
                                   [c_void_p] * 6),

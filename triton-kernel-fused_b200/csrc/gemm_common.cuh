@@ -111,6 +111,28 @@ __device__ __forceinline__ void glu_bwd32(const uint32_t (&r)[32], const uint4 (
   }
 }
 
+// the same with grad_inter already rounded and packed: gi[i] = columns (2i, 2i+1)
+__device__ __forceinline__ void glu_bwd32_packed(const uint32_t* gi, const uint4 (&g)[4], const uint4 (&u)[4],
+                                                 uint32_t* og, uint32_t* ou) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const uint32_t gw[4] = {g[v].x, g[v].y, g[v].z, g[v].w};
+    const uint32_t uw[4] = {u[v].x, u[v].y, u[v].z, u[v].w};
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      const float2 gf = unpack_bf16x2(gw[h]);
+      const float2 uf = unpack_bf16x2(uw[h]);
+      const float2 go = unpack_bf16x2(gi[4 * v + h]);
+      const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
+      const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
+      const float d0 = s0 * (1.0f + gf.x * (1.0f - s0));
+      const float d1 = s1 * (1.0f + gf.y * (1.0f - s1));
+      og[4 * v + h] = pack_bf16x2(go.x * uf.x * d0, go.y * uf.y * d1);
+      ou[4 * v + h] = pack_bf16x2(go.x * (gf.x * s0), go.y * (gf.y * s1));
+    }
+  }
+}
+
 // One lane = one row of a 32-row staging box: 64 bf16 (32 packed registers) go to the 128-byte
 // swizzled position the TMA store expects (16-byte chunk j of row r sits at chunk j ^ (r & 7)).
 constexpr int kStageOutBytes = 32 * 128;   // one epilogue warp's staging box: 32 rows x 64 bf16

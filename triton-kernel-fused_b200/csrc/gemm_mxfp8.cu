@@ -479,30 +479,38 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       const bool have_acc = t.nkb > 0;
       uint8_t* sbuf = epi_smem + (warp - 2) * kStageOutBytes;
       const int grp = (p.sched == SCHED_GROUPED_K) ? t.g : 0;
-      // results are packed to bf16, staged per warp as 32 rows x 64 columns and written by TMA stores
-      // (which clip at the tensor's bounds)
+      // The accumulator is single-buffered, so it is drained first: this warp's 32 rows x 128 columns are
+      // rounded to bf16, packed into 64 registers, and the tensor memory goes back to the MMA warp before any
+      // arithmetic or store; acc[16 s + i] = columns (32 s + 2i, 32 s + 2i + 1) of this warp's column half.
+      uint32_t acc[64];
+#pragma unroll
+      for (int s4 = 0; s4 < 4; ++s4) {
+        uint32_t r[32];
+        if (have_acc) {
+          tmem_ld32(taddr + 128 * half + 32 * s4, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          acc[16 * s4 + i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_leader);
+      // results are staged per warp as 32 rows x 64 columns and written by TMA stores (which clip at the
+      // tensor's bounds)
       if constexpr (EPI == EPI_STORE) {
-#pragma unroll 1
-        for (int c = half * 128; c < half * 128 + 128; c += 64) {
-          if (t.n0 + c >= p.N) break;
-          uint32_t pk[32];
 #pragma unroll
-          for (int sub = 0; sub < 2; ++sub) {
-            uint32_t r[32];
-            if (have_acc) {
-              tmem_ld32(taddr + c + 32 * sub, r);
-              tmem_ld_wait();
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) r[i] = 0u;
-            }
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              pk[16 * sub + i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = half * 128 + 64 * cc;
+          if (t.n0 + c < p.N) {
+            staging_free(lane);
+            stage_row(sbuf, lane, acc + 32 * cc);
+            store_box(&tmD, sbuf, lane, t.n0 + c, row0, grp);
           }
-          staging_free(lane);
-          stage_row(sbuf, lane, pk);
-          store_box(&tmD, sbuf, lane, t.n0 + c, row0, grp);
         }
       } else if constexpr (EPI == EPI_SWIGLU) {
         // weight rows are 64-interleaved: accumulator columns [128h, 128h+64) = gate and [128h+64, 128h+128) = up
@@ -510,25 +518,14 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const int I = p.I;
         const int col0 = t.n0 / 2 + 64 * half;
         if (col0 < I) {
-          uint32_t og[32], ou[32], oh[32];
+          uint32_t oh[32];
 #pragma unroll
-          for (int sub = 0; sub < 2; ++sub) {
-            uint32_t g[32], u[32];
-            tmem_ld32(taddr + 128 * half + 32 * sub, g);
-            tmem_ld32(taddr + 128 * half + 64 + 32 * sub, u);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const uint32_t pg = pack_bf16x2(__uint_as_float(g[2 * i]), __uint_as_float(g[2 * i + 1]));
-              const uint32_t pu = pack_bf16x2(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]));
-              const float2 gf = unpack_bf16x2(pg);
-              const float2 uf = unpack_bf16x2(pu);
-              const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
-              const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
-              og[16 * sub + i] = pg;
-              ou[16 * sub + i] = pu;
-              oh[16 * sub + i] = pack_bf16x2(gf.x * s0 * uf.x, gf.y * s1 * uf.y);
-            }
+          for (int i = 0; i < 32; ++i) {
+            const float2 gf = unpack_bf16x2(acc[i]);
+            const float2 uf = unpack_bf16x2(acc[32 + i]);
+            const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
+            const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
+            oh[i] = pack_bf16x2(gf.x * s0 * uf.x, gf.y * s1 * uf.y);
           }
           if (fp.q_out != nullptr) {   // the quantised `inter` for the down GEMM, two 32-element blocks
             mx_quant_store32(oh, fp.q_out + row * static_cast<long long>(I) + col0, fp.q_sf, row, col0 >> 5, I >> 7);
@@ -536,10 +533,10 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                              (col0 + 32) >> 5, I >> 7);
           }
           staging_free(lane);
-          stage_row(sbuf, lane, og);
+          stage_row(sbuf, lane, acc);
           store_box(&tmD, sbuf, lane, col0, row0, 0);    // gate half of gate_up
           staging_free(lane);
-          stage_row(sbuf, lane, ou);
+          stage_row(sbuf, lane, acc + 32);
           store_box(&tmD, sbuf, lane, col0, row0, 1);    // up half
           staging_free(lane);
           stage_row(sbuf, lane, oh);
@@ -548,41 +545,38 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       } else {   // EPI_GLU_BWD: accumulator = grad_inter columns [n0, n0+256), this warp 128 of them
         const int I = p.I;
         const __nv_bfloat16* gu = reinterpret_cast<const __nv_bfloat16*>(p.aux) + row * (2LL * I);
-#pragma unroll 1
-        for (int c = half * 128; c < half * 128 + 128; c += 64) {
-          if (t.n0 + c >= I) break;
-          uint32_t og[32], ou[32];
 #pragma unroll
-          for (int sub = 0; sub < 2; ++sub) {
-            const int colq = t.n0 + c + 32 * sub;
-            uint4 g4[4], u4[4];
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = half * 128 + 64 * cc;
+          if (t.n0 + c < I) {
+            uint32_t og[32], ou[32];
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const int col = colq + v * 8;
-              g4[v] = col < I ? __ldg(reinterpret_cast<const uint4*>(gu + col)) : make_uint4(0u, 0u, 0u, 0u);
-              u4[v] = col < I ? __ldg(reinterpret_cast<const uint4*>(gu + I + col)) : make_uint4(0u, 0u, 0u, 0u);
+            for (int sub = 0; sub < 2; ++sub) {
+              const int colq = t.n0 + c + 32 * sub;
+              uint4 g4[4], u4[4];
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                const int col = colq + v * 8;
+                g4[v] = col < I ? __ldg(reinterpret_cast<const uint4*>(gu + col)) : make_uint4(0u, 0u, 0u, 0u);
+                u4[v] = col < I ? __ldg(reinterpret_cast<const uint4*>(gu + I + col)) : make_uint4(0u, 0u, 0u, 0u);
+              }
+              glu_bwd32_packed(acc + 32 * cc + 16 * sub, g4, u4, og + 16 * sub, ou + 16 * sub);
+              if (fp.q_out != nullptr) {   // blocks of the (rows, 2I) grad_gate_up: gate half, then up half
+                mx_quant_store32(og + 16 * sub, fp.q_out + row * (2LL * I) + colq, fp.q_sf, row, colq >> 5,
+                                 (2 * I) >> 7);
+                mx_quant_store32(ou + 16 * sub, fp.q_out + row * (2LL * I) + I + colq, fp.q_sf, row, (I + colq) >> 5,
+                                 (2 * I) >> 7);
+              }
             }
-            uint32_t r[32];
-            tmem_ld32(taddr + c + 32 * sub, r);
-            tmem_ld_wait();
-            glu_bwd32(r, g4, u4, og + 16 * sub, ou + 16 * sub);
-            if (fp.q_out != nullptr) {   // blocks of the (rows, 2I) grad_gate_up: gate half, then up half
-              mx_quant_store32(og + 16 * sub, fp.q_out + row * (2LL * I) + colq, fp.q_sf, row, colq >> 5, (2 * I) >> 7);
-              mx_quant_store32(ou + 16 * sub, fp.q_out + row * (2LL * I) + I + colq, fp.q_sf, row, (I + colq) >> 5,
-                               (2 * I) >> 7);
-            }
+            staging_free(lane);
+            stage_row(sbuf, lane, og);
+            store_box(&tmD, sbuf, lane, t.n0 + c, row0, 0);   // grad_gate
+            staging_free(lane);
+            stage_row(sbuf, lane, ou);
+            store_box(&tmD, sbuf, lane, t.n0 + c, row0, 1);   // grad_up
           }
-          staging_free(lane);
-          stage_row(sbuf, lane, og);
-          store_box(&tmD, sbuf, lane, t.n0 + c, row0, 0);   // grad_gate
-          staging_free(lane);
-          stage_row(sbuf, lane, ou);
-          store_box(&tmD, sbuf, lane, t.n0 + c, row0, 1);   // grad_up
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(tempty_leader);
     }
     if (lane == 0) bulk_wait_all();   // every TMA store of this warp has completed
   }

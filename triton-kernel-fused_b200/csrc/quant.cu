@@ -17,6 +17,15 @@
 
 namespace b200moe {
 
+// Destination row of source row r when a stack of (2I, C) gate|up matrices is re-ordered per 64 rows.
+__device__ __forceinline__ long long interleaved_row(long long r, long long I) {
+  const long long e = r / (2 * I);
+  const long long rr = r - e * 2 * I;
+  const long long up = rr >= I ? 1 : 0;
+  const long long j = rr - up * I;
+  return e * 2 * I + (j >> 6) * 128 + up * 64 + (j & 63);
+}
+
 // One thread quantises one block of 32 consecutive elements of a row.
 // interleave_I > 0: the source is a stack of (2I, C) gate|up matrices; destination rows are
 // re-ordered per 64 so that each group of 128 output rows holds gate rows j..j+63 then up rows
@@ -35,93 +44,115 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long R, long long C,
     uint4 v[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) v[j] = __ldg(src + j);
-    float f[32];
-    float amax = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-#pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        const float2 t = unpack_bf16x2(w[h]);
-        f[j * 8 + 2 * h] = t.x;
-        f[j * 8 + 2 * h + 1] = t.y;
-        amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y)));
-      }
-    }
-    const uint32_t sb = e8m0_from_amax(amax);
-    const float inv = inv_scale_from_e8m0(sb);
-    long long dr = r;
-    if (interleave_I > 0) {
-      const long long e = r / (2 * interleave_I);
-      const long long rr = r - e * 2 * interleave_I;
-      const long long up = rr >= interleave_I ? 1 : 0;
-      const long long j = rr - up * interleave_I;
-      dr = e * 2 * interleave_I + (j >> 6) * 128 + up * 64 + (j & 63);
-    }
-    uint4 o[2];
-    uint32_t* ow = reinterpret_cast<uint32_t*>(o);
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-      ow[j] = cvt4_e4m3(f[4 * j] * inv, f[4 * j + 1] * inv, f[4 * j + 2] * inv, f[4 * j + 3] * inv);
-    uint4* dst = reinterpret_cast<uint4*>(q + dr * C + b * 32);
-    dst[0] = o[0];
-    dst[1] = o[1];
-    sf[sf_offset(dr, b, k_chunks)] = static_cast<uint8_t>(sb);
+    const long long dr = interleave_I > 0 ? interleaved_row(r, interleave_I) : r;
+    mx_quant_store32(reinterpret_cast<const uint32_t*>(v), q + dr * C + b * 32, sf, dr, b, k_chunks);
   }
 }
 
-// Transposing quantiser: x (G, R, C) bf16 -> q (G, C, R) e4m3 with blocks of 32 along R (the rows of
-// x become the reduction dimension).  One warp owns 32 rows x 64 columns; lane l owns columns
-// 2l, 2l+1 and writes 32 bytes (one block) for each of them.  R must be a multiple of 32.
-__global__ void __launch_bounds__(256)
-quant_transpose_kernel(const __nv_bfloat16* __restrict__ x, long long G, long long R, long long C,
-                       uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+// Transposing quantiser: x (G, R, C) bf16 -> q_t (G, C, R) e4m3 with blocks of 32 along R (the rows of
+// x become the reduction dimension).  A CTA owns a 128 x 128 tile; warp w quantises row block w & 3
+// (32 rows) of column half w >> 2, lane l owning columns 2l and 2l+1 of that half.  The codes are staged
+// in shared memory as [column][128 bytes along R] (16-byte chunks XOR-swizzled against bank conflicts) and
+// leave as full 128-byte lines; the four scale bytes of a column leave as one word.  R % 32 == 0.
+// ROWS: the same pass also writes the row-wise quantisation of the tile (blocks of 32 along C; rows
+// optionally 64-interleaved), re-reading the tile from cache instead of DRAM.  Needs C % 32 == 0.
+template <bool ROWS>
+__global__ void __launch_bounds__(256, 4)
+quant_tile_kernel(const __nv_bfloat16* __restrict__ x, long long G, long long R, long long C, long long interleave_I,
+                  uint8_t* __restrict__ q_t, uint8_t* __restrict__ sf_t, uint8_t* __restrict__ q_r,
+                  uint8_t* __restrict__ sf_r) {
+  __shared__ __align__(16) uint8_t s_q[128 * 128];
+  __shared__ uint32_t s_sf[128];
   const int lane = threadIdx.x & 31;
-  const long long warps_per_grid = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  const long long cblocks = (C + 63) >> 6;
-  const long long rblocks = R >> 5;
-  const long long k_chunks = (R + 127) >> 7;
-  const long long total = G * rblocks * cblocks;
-  for (long long wi = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; wi < total;
-       wi += warps_per_grid) {
-    const long long g = wi / (rblocks * cblocks);
-    const long long rem = wi - g * rblocks * cblocks;
-    const long long rb = rem / cblocks;
-    const long long cb = rem - rb * cblocks;
-    const long long c = cb * 64 + 2 * lane;
-    if (c >= C) continue;
-    const __nv_bfloat16* src = x + (g * R + rb * 32) * C + c;
-    float a[32], b[32];
-    float amax_a = 0.0f, amax_b = 0.0f;
+  const int warp = threadIdx.x >> 5;
+  const int rbw = warp & 3, ch = warp >> 2;
+  const long long rtiles = (R + 127) >> 7, ctiles = (C + 127) >> 7;
+  const long long kc_t = rtiles;             // 128-wide k chunks of the transposed output (K = R)
+  const long long kc_r = (C + 127) >> 7;     // ... of the row-wise output (K = C)
+  const long long total = G * rtiles * ctiles;
+  for (long long tile = blockIdx.x; tile < total; tile += gridDim.x) {
+    const long long g = tile / (rtiles * ctiles);
+    const long long rem = tile - g * rtiles * ctiles;
+    const long long rt = rem / ctiles;
+    const long long ct = rem - rt * ctiles;
+    if constexpr (ROWS) {   // coalesced first touch of the tile; the strided reads below then hit cache
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float2 t = unpack_bf16x2(__ldg(reinterpret_cast<const uint32_t*>(src + i * C)));
-      a[i] = t.x;
-      b[i] = t.y;
-      amax_a = fmaxf(amax_a, fabsf(t.x));
-      amax_b = fmaxf(amax_b, fabsf(t.y));
-    }
-    const uint32_t sa = e8m0_from_amax(amax_a), sbb = e8m0_from_amax(amax_b);
-    const float ia = inv_scale_from_e8m0(sa), ib = inv_scale_from_e8m0(sbb);
-    uint4 oa[2], ob[2];
-    uint32_t* wa = reinterpret_cast<uint32_t*>(oa);
-    uint32_t* wb = reinterpret_cast<uint32_t*>(ob);
+      for (int i = 0; i < 2; ++i) {
+        const int it = threadIdx.x + 256 * i;
+        const long long r = rt * 128 + (it >> 2);
+        const long long cb = ct * 128 + (it & 3) * 32;
+        if (r < R && cb < C) {
+          const long long gr = g * R + r;
+          const uint4* src = reinterpret_cast<const uint4*>(x + gr * C + cb);
+          uint4 v[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      wa[j] = cvt4_e4m3(a[4 * j] * ia, a[4 * j + 1] * ia, a[4 * j + 2] * ia, a[4 * j + 3] * ia);
-      wb[j] = cvt4_e4m3(b[4 * j] * ib, b[4 * j + 1] * ib, b[4 * j + 2] * ib, b[4 * j + 3] * ib);
+          for (int j = 0; j < 4; ++j) v[j] = __ldg(src + j);
+          const long long dr = interleave_I > 0 ? interleaved_row(gr, interleave_I) : gr;
+          mx_quant_store32(reinterpret_cast<const uint32_t*>(v), q_r + dr * C + cb, sf_r, dr, cb >> 5, kc_r);
+        }
+      }
     }
-    const long long orow = g * C + c;   // output row (a column of x)
-    uint4* da = reinterpret_cast<uint4*>(q + orow * R + rb * 32);
-    da[0] = oa[0];
-    da[1] = oa[1];
-    sf[sf_offset(orow, rb, k_chunks)] = static_cast<uint8_t>(sa);
-    if (c + 1 < C) {
-      uint4* db = reinterpret_cast<uint4*>(q + (orow + 1) * R + rb * 32);
-      db[0] = ob[0];
-      db[1] = ob[1];
-      sf[sf_offset(orow + 1, rb, k_chunks)] = static_cast<uint8_t>(sbb);
+    {
+      const long long r0 = rt * 128 + rbw * 32;
+      const long long c = ct * 128 + ch * 64 + 2 * lane;
+      uint4 oa[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+      uint4 ob[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+      uint32_t sa = 0u, sbb = 0u;
+      if (r0 < R && c < C) {
+        const __nv_bfloat16* src = x + (g * R + r0) * C + c;
+        uint32_t v[32];   // row i of the block: column c in the low half, column c + 1 in the high half
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __ldg(reinterpret_cast<const uint32_t*>(src + i * C));
+        uint32_t m = 0u;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) m = absmax_bf16x2(m, v[i]);
+        sa = e8m0_from_amax(bf16_lo(m));
+        sbb = e8m0_from_amax(bf16_hi(m));
+        const float ia = inv_scale_from_e8m0(sa), ib = inv_scale_from_e8m0(sbb);
+        uint32_t* wa = reinterpret_cast<uint32_t*>(oa);
+        uint32_t* wb = reinterpret_cast<uint32_t*>(ob);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          wa[j] = cvt4_e4m3(bf16_lo(v[4 * j]) * ia, bf16_lo(v[4 * j + 1]) * ia, bf16_lo(v[4 * j + 2]) * ia,
+                            bf16_lo(v[4 * j + 3]) * ia);
+          wb[j] = cvt4_e4m3(bf16_hi(v[4 * j]) * ib, bf16_hi(v[4 * j + 1]) * ib, bf16_hi(v[4 * j + 2]) * ib,
+                            bf16_hi(v[4 * j + 3]) * ib);
+        }
+      }
+      const int cl = ch * 64 + 2 * lane;   // column inside the tile; cl and cl+1 share the swizzle key lane & 7
+      const int j0 = rbw * 2;
+      uint8_t* ra = s_q + cl * 128;
+      *reinterpret_cast<uint4*>(ra + ((j0 ^ (lane & 7)) << 4)) = oa[0];
+      *reinterpret_cast<uint4*>(ra + (((j0 + 1) ^ (lane & 7)) << 4)) = oa[1];
+      *reinterpret_cast<uint4*>(ra + 128 + ((j0 ^ (lane & 7)) << 4)) = ob[0];
+      *reinterpret_cast<uint4*>(ra + 128 + (((j0 + 1) ^ (lane & 7)) << 4)) = ob[1];
+      reinterpret_cast<uint8_t*>(s_sf)[cl * 4 + rbw] = static_cast<uint8_t>(sa);
+      reinterpret_cast<uint8_t*>(s_sf)[cl * 4 + 4 + rbw] = static_cast<uint8_t>(sbb);
     }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = threadIdx.x + 256 * i;
+      const int cl = idx >> 3, j = idx & 7;
+      const long long cg = ct * 128 + cl;
+      const long long rr = rt * 128 + j * 16;
+      if (cg < C && rr < R)
+        *reinterpret_cast<uint4*>(q_t + (g * C + cg) * R + rr) =
+            *reinterpret_cast<const uint4*>(s_q + cl * 128 + ((j ^ ((cl >> 1) & 7)) << 4));
+    }
+    if (threadIdx.x < 128) {
+      const long long cg = ct * 128 + threadIdx.x;
+      if (cg < C) {
+        const long long orow = g * C + cg;   // output row (a column of x)
+        uint8_t* dst = sf_t + sf_offset(orow, rt * 4, kc_t);
+        if (rt * 128 + 128 <= R) {
+          *reinterpret_cast<uint32_t*>(dst) = s_sf[threadIdx.x];
+        } else {
+          for (int b = 0; rt * 128 + b * 32 < R; ++b) dst[b] = reinterpret_cast<const uint8_t*>(s_sf)[threadIdx.x * 4 + b];
+        }
+      }
+    }
+    __syncthreads();   // the staging tile is free again
   }
 }
 
@@ -205,21 +236,45 @@ int b200moe_mxfp8_gather_quant(const void* x, const int32_t* row_slot, const int
   return 0;
 }
 
+static int launch_quant_tile(const void* x, long long G, long long R, long long C, long long interleave_I, void* q_t,
+                             void* sf_t, void* q_r, void* sf_r, cudaStream_t stream) {
+  const long long tiles = G * ((R + 127) / 128) * ((C + 127) / 128);
+  long long grid = tiles;
+  const long long cap = static_cast<long long>(num_sms()) * 8;
+  if (grid > cap) grid = cap;
+  if (q_r != nullptr)
+    quant_tile_kernel<true><<<static_cast<int>(grid), 256, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), G, R, C, interleave_I, reinterpret_cast<uint8_t*>(q_t),
+        reinterpret_cast<uint8_t*>(sf_t), reinterpret_cast<uint8_t*>(q_r), reinterpret_cast<uint8_t*>(sf_r));
+  else
+    quant_tile_kernel<false><<<static_cast<int>(grid), 256, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), G, R, C, 0, reinterpret_cast<uint8_t*>(q_t),
+        reinterpret_cast<uint8_t*>(sf_t), nullptr, nullptr);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
 int b200moe_mxfp8_quant_transpose(const void* x, int64_t G, int64_t R, int64_t C, void* q, void* sf,
                                   b200moe_stream_t stream) {
   B200_CHECK_ARG(x && q && sf, B200MOE_E_NULL, "mxfp8_quant_transpose: null pointer");
   B200_CHECK_ARG(G >= 1 && R > 0 && R % 32 == 0 && C > 0 && C % 2 == 0, B200MOE_E_BAD_SHAPE,
                  "mxfp8_quant_transpose: R = %lld must be a multiple of 32 and C = %lld even", (long long)R, (long long)C);
-  B200_CHECK_ARG(R % 16 == 0 && aligned16(q), B200MOE_E_ALIGN, "mxfp8_quant_transpose: output not 16-byte aligned");
-  const long long warps = G * (R / 32) * ((C + 63) / 64);
-  long long grid = (warps + 7) / 8;
-  const long long cap = static_cast<long long>(num_sms()) * 32;
-  if (grid > cap) grid = cap;
-  quant_transpose_kernel<<<static_cast<int>(grid), 256, 0, (cudaStream_t)stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(x), G, R, C, reinterpret_cast<uint8_t*>(q),
-      reinterpret_cast<uint8_t*>(sf));
-  B200_CUDA(cudaGetLastError());
-  return 0;
+  B200_CHECK_ARG(aligned16(q) && (reinterpret_cast<uintptr_t>(x) & 3) == 0 && (reinterpret_cast<uintptr_t>(sf) & 3) == 0,
+                 B200MOE_E_ALIGN, "mxfp8_quant_transpose: pointers not aligned");
+  return launch_quant_tile(x, G, R, C, 0, q, sf, nullptr, nullptr, (cudaStream_t)stream);
+}
+
+int b200moe_mxfp8_quant_both(const void* x, int64_t G, int64_t R, int64_t C, int64_t interleave_I, void* q_rows,
+                             void* sf_rows, void* q_t, void* sf_t, b200moe_stream_t stream) {
+  B200_CHECK_ARG(x && q_rows && sf_rows && q_t && sf_t, B200MOE_E_NULL, "mxfp8_quant_both: null pointer");
+  B200_CHECK_ARG(G >= 1 && R > 0 && R % 32 == 0 && C > 0 && C % 32 == 0, B200MOE_E_BAD_SHAPE,
+                 "mxfp8_quant_both: R = %lld and C = %lld must be positive multiples of 32", (long long)R, (long long)C);
+  B200_CHECK_ARG(interleave_I == 0 || (interleave_I % 64 == 0 && R % (2 * interleave_I) == 0), B200MOE_E_BAD_SHAPE,
+                 "mxfp8_quant_both: interleave needs I %% 64 == 0 and R a multiple of 2I (I = %lld, R = %lld)",
+                 (long long)interleave_I, (long long)R);
+  B200_CHECK_ARG(aligned16(x) && aligned16(q_rows) && aligned16(q_t) && (reinterpret_cast<uintptr_t>(sf_t) & 3) == 0,
+                 B200MOE_E_ALIGN, "mxfp8_quant_both: pointers must be 16-byte aligned");
+  return launch_quant_tile(x, G, R, C, interleave_I, q_t, sf_t, q_rows, sf_rows, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -19,8 +19,10 @@ from .moe import _amp_cast, _code_info
 
 __all__ = ["moe_mxfp8", "FUSE_QUANT_EPILOGUE"]
 
-# When set (B200MOE_MXFP8_FUSE_QUANT=1; off by default, measured 2 % slower), the SwiGLU and GLU-backward epilogues also write their result quantised for the GEMM that
-# consumes it (bit-identical to the separate row quantiser); when clear, a row-quantiser pass does it.
+# B200MOE_MXFP8_FUSE_QUANT=1: where only the row-wise quantisation of a SwiGLU / GLU-backward result is
+# needed (no weight gradient wants its transposed copy), the GEMM epilogue writes it (bit-identical to the
+# row quantiser) instead of a separate pass.  Off by default: it measured 2 % slower on the full step,
+# because the pair kernel's single-buffered accumulator exposes every cycle added to the epilogue.
 FUSE_QUANT_EPILOGUE = os.environ.get("B200MOE_MXFP8_FUSE_QUANT", "0") == "1"
 
 
@@ -41,62 +43,84 @@ class _MoEMxfp8(torch.autograd.Function):
         w32 = wt.detach().float().contiguous()
         dev = hidden.device
 
+        need_x, _, _, need_gu, need_dn, _ = ctx.needs_input_grad
         perm = ops.permute_build(idx, E)
         x_s, xq, xsf = ops.mxfp8_gather_quant(hidden, perm)             # the gather is the quantising producer
-        wq, wsf = ops.mxfp8_quant_rows(gate_up_proj.view(E * twoI, H), interleave_I=I)
+        # tensors that the backward needs quantised along their other dimension are quantised both ways in
+        # one pass over DRAM, and the transposed copy is what the backward keeps
+        wgt = wgtsf = wtq = wtsf = it = itsf = None
+        if need_x:
+            wq, wsf, wgt, wgtsf = ops.mxfp8_quant_both(gate_up_proj, interleave_I=I)       # + (E, H, 2I)
+        else:
+            wq, wsf = ops.mxfp8_quant_rows(gate_up_proj.view(E * twoI, H), interleave_I=I)
         gate_up = torch.empty(perm.cap, twoI, dtype=torch.bfloat16, device=dev)
         inter = torch.empty(perm.cap, I, dtype=torch.bfloat16, device=dev)
-        if FUSE_QUANT_EPILOGUE:   # the SwiGLU epilogue also emits `inter` quantised for the down GEMM
-            _, iq, isf = ops.mxfp8_expert_gemm(ops.EPI_SWIGLU, xq, xsf, wq, wsf, perm, twoI, H, I, gate_up, inter,
-                                               quantise_result=True)
+        fuse = FUSE_QUANT_EPILOGUE and not need_dn
+        res = ops.mxfp8_expert_gemm(ops.EPI_SWIGLU, xq, xsf, wq, wsf, perm, twoI, H, I, gate_up, inter,
+                                    quantise_result=fuse)
+        if fuse:    # the SwiGLU epilogue also emitted `inter` quantised for the down GEMM
+            _, iq, isf = res
+        elif need_dn:
+            iq, isf, it, itsf = ops.mxfp8_quant_both(inter)                                 # + (I, rows)
         else:
-            ops.mxfp8_expert_gemm(ops.EPI_SWIGLU, xq, xsf, wq, wsf, perm, twoI, H, I, gate_up, inter)
             iq, isf = ops.mxfp8_quant_rows(inter)
-        dq, dsf = ops.mxfp8_quant_rows(down_proj.view(E * H, I))
+        if need_x or need_gu:
+            dq, dsf, wtq, wtsf = ops.mxfp8_quant_both(down_proj)                            # + (E, I, H)
+        else:
+            dq, dsf = ops.mxfp8_quant_rows(down_proj.view(E * H, I))
         eo = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=dev)
         ops.mxfp8_expert_gemm(ops.EPI_STORE, iq, isf, dq, dsf, perm, H, I, I, eo)
         out = ops.combine(eo, w32, perm)
 
         ctx.perm = perm
         ctx.wt_dtype = wt.dtype
-        ctx.save_for_backward(x_s, gate_up, inter, eo, w32, gate_up_proj, down_proj)
+        ctx.dims = (E, H, I)
+        ctx.quantised = (wgt, wgtsf, wtq, wtsf, it, itsf)   # uint8 copies for the backward (not differentiable)
+        ctx.save_for_backward(x_s, gate_up, eo, w32)
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        x_s, gate_up, inter, eo, w32, gate_up_proj, down_proj = ctx.saved_tensors
+        x_s, gate_up, eo, w32 = ctx.saved_tensors
+        wgt, wgtsf, wtq, wtsf, it, itsf = ctx.quantised
         perm = ctx.perm
-        E, twoI, H = gate_up_proj.shape
-        I = twoI // 2
+        E, H, I = ctx.dims
+        twoI = 2 * I
         dev = x_s.device
         need_x, _, need_w, need_gu, need_dn, _ = ctx.needs_input_grad
         grad_out = grad_out.contiguous().to(torch.bfloat16)
         grad_eo, grad_w = ops.combine_bwd(grad_out, eo, w32, perm)
         grad_hidden = grad_gate_up_proj = grad_down_proj = None
+        gq = gsf = gt = gtsf = None
+        if need_dn and (need_x or need_gu):
+            gq, gsf, gt, gtsf = ops.mxfp8_quant_both(grad_eo)             # K = H, and (H, rows)
+        elif need_dn:
+            gt, gtsf = ops.mxfp8_quant_transpose(grad_eo)
+        elif need_x or need_gu:
+            gq, gsf = ops.mxfp8_quant_rows(grad_eo)
         if need_x or need_gu:
-            gq, gsf = ops.mxfp8_quant_rows(grad_eo)                       # K = H
-            wtq, wtsf = ops.mxfp8_quant_transpose(down_proj)              # (E, I, H)
             grad_gu = torch.empty(perm.cap, twoI, dtype=torch.bfloat16, device=dev)
-            fuse = FUSE_QUANT_EPILOGUE and need_x   # grad_gate_up quantised along 2I feeds the dgrad below
+            fuse = FUSE_QUANT_EPILOGUE and need_x and not need_gu
             res = ops.mxfp8_expert_gemm(ops.EPI_GLU_BWD, gq, gsf, wtq, wtsf, perm, I, H, I, grad_gu, gate_up,
                                         quantise_result=fuse)
-            if fuse:
+            ggq = ggsf = at = atsf = None
+            if fuse:   # the GLU-backward epilogue also emitted grad_gate_up quantised along 2I
                 _, ggq, ggsf = res
+            elif need_x and need_gu:
+                ggq, ggsf, at, atsf = ops.mxfp8_quant_both(grad_gu)       # K = 2I, and (2I, rows)
             elif need_x:
                 ggq, ggsf = ops.mxfp8_quant_rows(grad_gu)
+            else:
+                at, atsf = ops.mxfp8_quant_transpose(grad_gu)
             if need_gu:
-                at, atsf = ops.mxfp8_quant_transpose(grad_gu)             # (2I, rows)
                 bt, btsf = ops.mxfp8_quant_transpose(x_s)                 # (H, rows)
                 grad_gate_up_proj = ops.mxfp8_expert_wgrad(at, atsf, bt, btsf, perm)
             if need_x:
-                wgt, wgtsf = ops.mxfp8_quant_transpose(gate_up_proj)      # (E, H, 2I)
                 grad_x_s = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=dev)
                 ops.mxfp8_expert_gemm(ops.EPI_STORE, ggq, ggsf, wgt, wgtsf, perm, H, twoI, I, grad_x_s)
                 grad_hidden = ops.combine(grad_x_s, None, perm)
         if need_dn:
-            at, atsf = ops.mxfp8_quant_transpose(grad_eo)                 # (H, rows)
-            bt, btsf = ops.mxfp8_quant_transpose(inter)                   # (I, rows)
-            grad_down_proj = ops.mxfp8_expert_wgrad(at, atsf, bt, btsf, perm)
+            grad_down_proj = ops.mxfp8_expert_wgrad(gt, gtsf, it, itsf, perm)
         grad_wt = grad_w.to(ctx.wt_dtype) if need_w else None
         return grad_hidden, None, grad_wt, grad_gate_up_proj, grad_down_proj, None
 

@@ -310,6 +310,23 @@ def mxfp8_quant_transpose(x):
     return (q if x.dim() == 3 else q[0]), sf
 
 
+@_op("mxfp8_quant_both", 1)
+def mxfp8_quant_both(x, interleave_I=0):
+    """x (G,R,C) or (R,C) bf16 -> (q_rows (G*R,C), sf_rows, q_t (G,C,R) / (C,R), sf_t): the results of
+    `mxfp8_quant_rows` and `mxfp8_quant_transpose` from one pass over x."""
+    L.require_cuda_bf16("x", x)
+    x3 = x if x.dim() == 3 else x.unsqueeze(0)
+    L.require(x3.is_contiguous(), "mxfp8_quant_both: need a contiguous tensor")
+    G, R, C = x3.shape
+    q = torch.empty(G * R, C, dtype=torch.uint8, device=x.device)
+    sf = _sf_empty(G * R, C, x.device)
+    qt = torch.empty(G, C, R, dtype=torch.uint8, device=x.device)
+    sft = _sf_empty(G * C, R, x.device)
+    L.check(L.lib().b200moe_mxfp8_quant_both(L.ptr(x3), G, R, C, int(interleave_I), L.ptr(q), L.ptr(sf), L.ptr(qt),
+                                             L.ptr(sft), L.stream_of(x)))
+    return q, sf, (qt if x.dim() == 3 else qt[0]), sft
+
+
 @_op("mxfp8_gemm_nt", 1)
 def mxfp8_gemm_nt(aq, asf, bq, bsf):
     """dequant(aq)(M,K) @ dequant(bq)(N,K)^T -> (M,N) bf16."""
