@@ -40,6 +40,10 @@ PROFILE = dict(T=4096, H=2048, E=16, I=1408, k=6)
 EP5 = dict(T=65536, H=7168, E=256, I=2048, k=8)
 # MXFP8 configuration (e4m3 + E8M0 block-32 scales), one GPU
 MXFP8 = dict(T=32768, H=4096, E=8, I=14336, k=2)
+# small MXFP8 case for profiler captures: expert weights 403 MB (above L2), about 2 GB held on the device
+MXFP8_PROFILE = dict(T=8192, H=2048, E=8, I=4096, k=2)
+# skewed routing: per-expert selection bias from Zipf(1.1) frequencies, some experts receive no token
+ZIPF = dict(T=32768, H=2048, E=128, I=768, k=8)
 METRIC = "moe_layer_fwd_bwd_tokens_per_s"
 # DRAM bytes (read + written) per launch measured with ncu on the profile workload (24 576 routed rows,
 # H=2048, I=1408, 1536 rows per expert; the capture is summarised under profiles/).  Traffic grows in
@@ -116,11 +120,13 @@ def _workload(n_gpus, which="headline"):
     if which == "ep5":
         w = dict(EP5)
         w["T"] = EP5["T"] // n_gpus
-    elif which == "mxfp8":
-        w = dict(MXFP8)
+    elif which in ("mxfp8", "mxfp8_profile"):
+        w = dict(MXFP8 if which == "mxfp8" else MXFP8_PROFILE)
+    elif which == "zipf":
+        w = dict(ZIPF)
     else:
         w = dict(HEADLINE if which == "headline" else PROFILE)
-    w["precision"] = "mxfp8" if which == "mxfp8" else "bf16"
+    w["precision"] = "mxfp8" if which.startswith("mxfp8") else "bf16"
     w["name"] = (w["precision"] + " MoE layer T={T}/GPU H={H} E={E} I={I} top{k} fwd+bwd").format(**w)
     w["parallelism"] = "single GPU" if n_gpus == 1 else f"expert parallel ep{n_gpus} (E/{n_gpus} experts per GPU, NCCL all-to-all)"
     return w
@@ -156,6 +162,11 @@ def run_ours(args):
     T, H, E, I, k = w["T"], w["H"], w["E"], w["I"], w["k"]
     layer = _make_layer(pkg, w, dev, seed=0, world=world)
     params = [layer.gate.weight, layer.gate_up_proj, layer.down_proj]
+    if args.workload == "zipf":   # selection bias = 0.15 x log of Zipf(1.1) frequencies over a seeded expert order
+        gz = torch.Generator().manual_seed(7)
+        ranks = (torch.randperm(E, generator=gz) + 1).float()
+        pz = ranks.pow(-1.1)
+        layer.bias.copy_((0.15 * torch.log(pz / pz.sum())).to(dev))
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     x_dev = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
     go_dev = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
@@ -244,7 +255,7 @@ def run_ours(args):
             ms = float(t.item())
         return ms
 
-    n_warm = args.warmup if args.workload == "profile" else max(args.warmup, 3)
+    n_warm = args.warmup if args.workload.endswith("profile") else max(args.warmup, 3)
     for _ in range(n_warm):
         step_resident()
     pkg.check_status()
@@ -310,6 +321,9 @@ def run_ours(args):
         "config": {"workload": w["name"], "tokens_per_gpu": T, "d_model": H, "experts": E, "d_ff": I, "top_k": k,
                    "parallelism": w["parallelism"],
                    "l2": "no flush: the working set (expert weights + activations, several GB) exceeds the 126 MB L2"},
+        "tokens_per_expert": ({"min": int(layer.last_counts.min()), "max": int(layer.last_counts.max()),
+                               "experts_without_tokens": int((layer.last_counts == 0).sum())}
+                              if getattr(layer, "last_counts", None) is not None else None),
         "layer_tflops_per_gpu": round(layer_flops / (ms_step * 1e-3) / 1e12, 1),
         "layer_frac_of_peak": round(layer_flops / (ms_step * 1e-3) / 1e12 / peaks["tflops"], 4),
         "gemm_ms_per_step": round(gemm_ms, 4),
@@ -374,7 +388,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="headline", choices=["headline", "profile", "ep5", "mxfp8"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "profile", "ep5", "mxfp8", "mxfp8_profile", "zipf"],
                     help="profile = small case for profiler captures (not a benchmark number)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -317,7 +317,8 @@ constexpr int kPStage = 34816;           // A 16 KB + B 16 KB + SFA 512 B + SFB 
 constexpr int kPStages = 5;
 constexpr int kPSfCols = 16;             // tensor-memory columns per stage: SFA 4 + SFB 8 (+4 spare)
 constexpr int kPEpiBytes = kEpiWarps * kStageOutBytes;   // one 32 x 64 bf16 staging box per epilogue warp
-constexpr int kPSmemBytes = kPStages * kPStage + kPEpiBytes + (2 * kPStages + 2) * 8 + 16 + 1024;
+constexpr int kPThreads = kThreads + 32;   // one more warp: the scale-copy issuer
+constexpr int kPSmemBytes = kPStages * kPStage + kPEpiBytes + (3 * kPStages + 2) * 8 + 16 + 1024;
 
 // pair form of the 3-D load for the scale tensors {128 u32, k-chunks, row-blocks}
 __device__ __forceinline__ void umma_mxf8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -338,7 +339,7 @@ __device__ __forceinline__ uint32_t idesc_mxf8_pair(uint32_t sf_id) {
 }
 
 template <int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kPThreads, 1)
 gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                        const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmD2,
@@ -352,9 +353,10 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + kPEpiBytes);
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = smem_u32(bars + kPStages);
-  const uint32_t bar_tfull = smem_u32(bars + 2 * kPStages);
-  const uint32_t bar_tempty = smem_u32(bars + 2 * kPStages + 1);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPStages + 2);
+  const uint32_t bar_sf = smem_u32(bars + 2 * kPStages);   // scales of the stage are in tensor memory
+  const uint32_t bar_tfull = smem_u32(bars + 3 * kPStages);
+  const uint32_t bar_tempty = smem_u32(bars + 3 * kPStages + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kPStages + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -366,6 +368,7 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     for (int s = 0; s < kPStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
+      mbar_init(bar_sf + 8 * s, 1);
     }
     mbar_init(bar_tfull, 1);
     mbar_init(bar_tempty, 2 * kEpiWarps);
@@ -430,7 +433,9 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         if (!mbar_wait(bar_tempty, (it & 1) ^ 1, abort_flag, ST_WAIT_MMA_TMEM)) break;
         tc_fence_after();
         for (int kb = 0; kb < t.nkb; ++kb) {
-          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, ST_WAIT_MMA_FULL)) {
+          // operands landed in shared memory (full) and the scale-copy warp moved the scales to tensor memory (sf)
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, ST_WAIT_MMA_FULL) ||
+              !mbar_wait(bar_sf + 8 * s, ph, abort_flag, ST_WAIT_MMA_FULL)) {
             ok = false;
             break;
           }
@@ -439,9 +444,6 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           const uint32_t sb = sa + kATile;
           const uint32_t sfa_t = tmem_base + PBN + kPSfCols * s;
           const uint32_t sfb_t = sfa_t + 4;
-          tmem_cp_sf_pair(sfa_t, sf_desc(sa + kATile + kBTile));
-          tmem_cp_sf_pair(sfb_t, sf_desc(sa + kATile + kBTile + kSfAtom));
-          tmem_cp_sf_pair(sfb_t + 4, sf_desc(sa + kATile + kBTile + 2 * kSfAtom));
 #pragma unroll
           for (int k = 0; k < FBK / 32; ++k) {
             const uint64_t da = umma_desc_sw128(sa + k * 32, 0, 1024);
@@ -460,6 +462,37 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         } else {
           mbar_arrive(bar_tfull);
           mbar_arrive_cluster(mapa_shared(bar_tfull, 1));
+        }
+      }
+    }
+  } else if (warp == 2 + kEpiWarps) {
+    // ------------------------------------------------------------------------- scale-copy issuer (leader)
+    // The three scale atoms of a stage go from shared to tensor memory (tcgen05.cp) from a thread of their
+    // own, stages ahead of the MMAs, instead of in the MMA thread's instruction stream directly before the
+    // MMAs that read them.  A stage's scale columns are free again once the stage itself was refilled: the
+    // producer waited for the commit that followed the MMAs reading them.
+    if (lane == 0 && cta_rank == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < total && ok; tile += tile_step) {
+        const int nkb = get_tile(p, tile, TN, TM, FBK).nkb;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, ST_WAIT_MMA_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sf_s = smem_u32(smem + s * kPStage) + kATile + kBTile;
+          const uint32_t sfa_t = tmem_base + PBN + kPSfCols * s;
+          tmem_cp_sf_pair(sfa_t, sf_desc(sf_s));
+          tmem_cp_sf_pair(sfa_t + 4, sf_desc(sf_s + kSfAtom));
+          tmem_cp_sf_pair(sfa_t + 8, sf_desc(sf_s + 2 * kSfAtom));
+          umma_commit_pair_local(bar_sf + 8 * s);
+          if (++s == kPStages) {
+            s = 0;
+            ph ^= 1;
+          }
         }
       }
     }
@@ -624,7 +657,7 @@ static int launch_fp8_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const
   if (pairs < 1) pairs = 1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(pairs * 2, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(kPThreads, 1, 1);
   cfg.dynamicSmemBytes = kPSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

@@ -199,6 +199,12 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
       ::"r"(bar), "h"(mask)
       : "memory");
 }
+// arrive (count 1) on this CTA's barrier only once all cta_group::2 operations issued so far by this thread
+// have completed
+__device__ __forceinline__ void umma_commit_pair_local(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
 // 32 lanes x 32 consecutive fp32 columns: thread t of the warp receives lane (base_lane + t).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
