@@ -109,6 +109,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tmem_relinquish();
     }
   }
+  __shared__ int s_order[B200MOE_MAX_EXPERTS];
+  const int* order = build_group_order(p, s_order);
   tc_fence_before();
   __syncthreads();
   if constexpr (CTAS == 2) {   // peer barriers are initialised before any remote arrive
@@ -126,9 +128,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t ph = 0;
       bool ok = true;
       for (int tile = first_tile; tile < total && ok; tile += tile_step) {
-        const Tile t = get_tile(p, tile, TN, TM);
+        const Tile t = get_tile(p, tile, TN, TM, 64, order);
         const int gB = (p.sched == SCHED_GROUPED_M) ? t.g : 0;
         const int m0 = t.m0 + BM * static_cast<int>(cta_rank);
+        // a last pair tile with at most BN/2 live columns runs as a 256 x BN/2 MMA: each CTA then
+        // supplies BN/4 columns of B, the first ones of its (still BN/2 wide) staging tile
+        const int bstep = (CTAS == 2 && EPI != EPI_SWIGLU && p.N - t.n0 <= BN / 2) ? BNC / 2 : BNC;
         for (int kb = 0; kb < t.nkb; ++kb) {
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, ST_WAIT_PRODUCER)) {
             ok = false;
@@ -173,12 +178,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               // leader stages the gate rows, the peer the up rows of I-columns [n0, n0+128)
               tma_load_3d_pair(sb, &tmB, full, kk, t.n0, 2 * gB + static_cast<int>(cta_rank));
             } else if (!p.b_mn) {
-              tma_load_3d_pair(sb, &tmB, full, kk, t.n0 + BNC * static_cast<int>(cta_rank), gB);
+              tma_load_3d_pair(sb, &tmB, full, kk, t.n0 + bstep * static_cast<int>(cta_rank), gB);
             } else {
 #pragma unroll
               for (int j = 0; j < BNC / 64; ++j)
                 tma_load_3d_pair(sb + j * (64 * BK * 2), &tmB, full,
-                                 t.n0 + BNC * static_cast<int>(cta_rank) + 64 * j, kk, gB);
+                                 t.n0 + bstep * static_cast<int>(cta_rank) + 64 * j, kk, gB);
             }
           }
           if (++s == NSTAGE) {
@@ -191,7 +196,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && cta_rank == 0) {
-      const uint32_t idesc = umma_idesc_bf16(BN, p.a_mn, p.b_mn, TM);
+      const uint32_t idesc_full = umma_idesc_bf16(BN, p.a_mn, p.b_mn, TM);
+      const uint32_t idesc_half = umma_idesc_bf16(BN / 2, p.a_mn, p.b_mn, TM);   // narrow last pair tile
       // K-major: rows are 128 B apart, 8-row groups 1024 B apart, 16 k-elements = 32 B.
       // MN-major: 64-wide MN blocks are 64*128 B apart (LBO), 8 k-rows 1024 B apart (SBO),
       //           16 k-rows = 2048 B.
@@ -201,11 +207,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t ph = 0;
       bool ok = true;
       for (int tile = first_tile; tile < total && ok; tile += tile_step, ++it) {
-        const Tile t = get_tile(p, tile, TN, TM);
+        const Tile t = get_tile(p, tile, TN, TM, 64, order);
         const int buf = it & 1;
         if (!mbar_wait(bar_tempty + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag, ST_WAIT_MMA_TMEM)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
+        const uint32_t idesc =
+            (CTAS == 2 && EPI != EPI_SWIGLU && p.N - t.n0 <= BN / 2) ? idesc_half : idesc_full;
         for (int kb = 0; kb < t.nkb; ++kb) {
           if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, ST_WAIT_MMA_FULL)) {
             ok = false;
@@ -247,7 +255,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     uint32_t epi_phase = 0;   // parity of this warp's GLU-backward load barrier
     int it = 0;
     for (int tile = first_tile; tile < total; tile += tile_step, ++it) {
-      const Tile t = get_tile(p, tile, TN, TM);
+      const Tile t = get_tile(p, tile, TN, TM, 64, order);
       const int buf = it & 1;
       const int row0 = t.m0 + BM * static_cast<int>(cta_rank) + q * 32;   // first row of this warp
       const long long row = static_cast<long long>(row0) + lane;

@@ -47,14 +47,35 @@ __device__ __forceinline__ int total_tiles(const GemmParams& p, int TN, int TM) 
   return ((p.M + TM - 1) / TM) * nt * p.num_groups;
 }
 
-__device__ __forceinline__ Tile get_tile(const GemmParams& p, int tile, int TN, int TM, int BK = 64) {
+// GROUPED_K with live-row counts: the groups in descending order of their reduction length, so that the
+// static round-robin of tiles over the persistent CTAs deals the long tiles out evenly (an expert with many
+// rows next to experts with few would otherwise leave most CTAs idle at the end).  Every thread of the CTA
+// calls this before the barrier that precedes the role dispatch; `order` is a shared array of
+// B200MOE_MAX_EXPERTS ints.  Returns nullptr when the plain order is used.
+__device__ __forceinline__ const int* build_group_order(const GemmParams& p, int* order) {
+  if (p.sched != SCHED_GROUPED_K || p.counts == nullptr || p.num_groups > B200MOE_MAX_EXPERTS) return nullptr;
+  for (int i = threadIdx.x; i < p.num_groups; i += blockDim.x) {
+    const int ci = p.counts[i];
+    int rank = 0;
+    for (int j = 0; j < p.num_groups; ++j) {
+      const int cj = p.counts[j];
+      rank += (cj > ci || (cj == ci && j < i)) ? 1 : 0;
+    }
+    order[rank] = i;
+  }
+  return order;
+}
+
+__device__ __forceinline__ Tile get_tile(const GemmParams& p, int tile, int TN, int TM, int BK = 64,
+                                         const int* order = nullptr) {
   Tile t;
   const int nt = (p.N + TN - 1) / TN;
   if (p.sched == SCHED_GROUPED_K) {
     const int mt = (p.M + TM - 1) / TM;
     const int per = mt * nt;
-    t.g = tile / per;
-    const int r = tile - t.g * per;
+    const int gi = tile / per;
+    t.g = order != nullptr ? order[gi] : gi;
+    const int r = tile - gi * per;
     t.m0 = (r / nt) * TM;
     t.n0 = (r % nt) * TN;
     int kb, ke;

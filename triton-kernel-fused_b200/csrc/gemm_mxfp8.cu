@@ -109,6 +109,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     tmem_alloc(smem_u32(tmem_slot), kFTmemCols);
     tmem_relinquish();
   }
+  __shared__ int s_order[B200MOE_MAX_EXPERTS];
+  const int* order = build_group_order(p, s_order);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -121,7 +123,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t ph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-        const Tile t = get_tile(p, tile, TN, BM, FBK);
+        const Tile t = get_tile(p, tile, TN, BM, FBK, order);
         const int gB = (p.sched == SCHED_GROUPED_M) ? t.g : 0;
         const long long rb_a = t.m0 >> 7;
         const long long rb_b = (static_cast<long long>(gB) * fp.b_rows_per_group + t.n0) >> 7;
@@ -152,7 +154,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t ph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++it) {
-        const Tile t = get_tile(p, tile, TN, BM, FBK);
+        const Tile t = get_tile(p, tile, TN, BM, FBK, order);
         const int buf = it & 1;
         if (!mbar_wait(bar_tempty + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag, ST_WAIT_MMA_TMEM)) break;
         tc_fence_after();
@@ -191,7 +193,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int half = (warp - 2) >> 2;
     int it = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
-      const Tile t = get_tile(p, tile, TN, BM, FBK);
+      const Tile t = get_tile(p, tile, TN, BM, FBK, order);
       const int buf = it & 1;
       if (!mbar_wait(bar_tfull + 8 * buf, (it >> 1) & 1, abort_flag, ST_WAIT_EPILOGUE)) break;
       __syncwarp();
@@ -383,6 +385,8 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     tmem_alloc_pair(smem_u32(tmem_slot), kFTmemCols);
     tmem_relinquish_pair();
   }
+  __shared__ int s_order[B200MOE_MAX_EXPERTS];
+  const int* order = build_group_order(p, s_order);
   tc_fence_before();
   __syncthreads();
   __syncwarp();
@@ -397,7 +401,7 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       uint32_t ph = 0;
       bool ok = true;
       for (int tile = first_tile; tile < total && ok; tile += tile_step) {
-        const Tile t = get_tile(p, tile, TN, TM, FBK);
+        const Tile t = get_tile(p, tile, TN, TM, FBK, order);
         const int gB = (p.sched == SCHED_GROUPED_M) ? t.g : 0;
         const int m0 = t.m0 + BM * cta_rank;
         const int rb_a = m0 >> 7;
@@ -429,7 +433,7 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       uint32_t ph = 0;
       bool ok = true;
       for (int tile = first_tile; tile < total && ok; tile += tile_step, ++it) {
-        const Tile t = get_tile(p, tile, TN, TM, FBK);
+        const Tile t = get_tile(p, tile, TN, TM, FBK, order);
         if (!mbar_wait(bar_tempty, (it & 1) ^ 1, abort_flag, ST_WAIT_MMA_TMEM)) break;
         tc_fence_after();
         for (int kb = 0; kb < t.nkb; ++kb) {
@@ -476,7 +480,7 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       uint32_t ph = 0;
       bool ok = true;
       for (int tile = first_tile; tile < total && ok; tile += tile_step) {
-        const int nkb = get_tile(p, tile, TN, TM, FBK).nkb;
+        const int nkb = get_tile(p, tile, TN, TM, FBK, order).nkb;
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, ST_WAIT_MMA_FULL)) {
             ok = false;
@@ -502,7 +506,7 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     const uint32_t tempty_leader = mapa_shared(bar_tempty, 0);
     int it = 0;
     for (int tile = first_tile; tile < total; tile += tile_step, ++it) {
-      const Tile t = get_tile(p, tile, TN, TM, FBK);
+      const Tile t = get_tile(p, tile, TN, TM, FBK, order);
       if (!mbar_wait(bar_tfull, it & 1, abort_flag, ST_WAIT_EPILOGUE)) break;
       __syncwarp();
       tc_fence_after();
