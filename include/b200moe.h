@@ -62,6 +62,9 @@ int b200moe_selftest_bounded_wait(int32_t* status, int64_t limit_cycles, b200moe
 /* host: keep `n` SMs free of the persistent GEMM kernels (process-wide, default 0) so that
  * communication kernels queued on another stream can run beside them.  No reference counterpart. */
 int b200moe_set_reserved_sms(int n);
+/* host: let b200moe_ep_combine_pull occupy at most `n` SMs (one 1024-thread CTA each; 0 = all SMs), the
+ * counterpart of b200moe_set_reserved_sms when a pull runs beside a GEMM.  No reference counterpart. */
+int b200moe_set_exchange_sms(int n);
 
 /* ---- router --------------------------------------------------------------------------------- */
 /* Replaces _router_epilogue_fwd_kernel (kernels/sm75/router.py:39-83, launcher :129-148):
@@ -260,24 +263,30 @@ int b200moe_combine_bwd(const void* grad_out, const void* eo, const float* w,
  * THIS rank's block of expert e inside e's owner. */
 int b200moe_ep_plan(const int32_t* counts_all, int W, int rank, int E, int32_t* poffs_l, int32_t* counts_l,
                     int32_t* tile_expert_l, int32_t* src_base, int32_t* dest_base, b200moe_stream_t stream);
-/* owner side, forward: x_s[row] = x_peers[src][slot / k] with slot = order_peers[src][offs_peers[src][e] + i];
- * zero pad rows; records (src, slot) of every row for the backward pass. */
-int b200moe_ep_gather_pull(const void* const* x_peers, const void* const* order_peers,
+/* owner side, forward.  For every source rank s and token t the kernel reads slot j of the token from the
+ * source's routing tables (idx_peers int64 (T,k), spos_peers = slot_pos int32 (T,k), offs_peers int32 (E+1)) and,
+ * for each expert that lives on this rank, writes x_peers[s][t] to row
+ * src_base[s][e_local] + slot_pos - offs[e]; the token row is read from the peer ONCE however many of its
+ * experts live here.  Pad rows are zeroed.  T is the token count of every rank. */
+int b200moe_ep_gather_pull(const void* const* x_peers, const void* const* idx_peers, const void* const* spos_peers,
                            const void* const* offs_peers, const int32_t* counts_l, const int32_t* poffs_l,
-                           const int32_t* tile_expert_l, const int32_t* src_base, int W, int rank, int E, int k,
-                           int64_t H, int64_t rows_cap, void* x_s, int32_t* row_src, int32_t* row_slot_src,
+                           const int32_t* src_base, int W, int rank, int E, int64_t T, int k, int64_t H, void* x_s,
                            b200moe_stream_t stream);
-/* home side: out[t] = sum_j w[t,j] * rows_peers[owner][dest_base[e] + slot_pos[s] - offs[e]] (w NULL = 1);
- * when gw_peers / grad_w are given, grad_w[s] is fetched from the owner's per-row dot products. */
+/* home side: out[t] = sum_j w[t,j] * rows_peers[owner][dest_base[e] + slot_pos[s] - offs[e]] (w NULL = 1),
+ * summed in slot order; the rows arrive by bulk copies into a shared-memory ring (one CTA per SM, on at most
+ * the SMs b200moe_set_exchange_sms allows).  When gw_peers / grad_w are given, grad_w[s] is fetched from the
+ * owner's per-row dot products.  `status` (nullable) receives a wait code if a bounded wait gives up. */
 int b200moe_ep_combine_pull(const void* const* rows_peers, const float* w, const int64_t* idx,
                             const int32_t* slot_pos, const int32_t* offs, const int32_t* dest_base, int W, int E,
                             int64_t T, int k, int64_t H, void* out, const void* const* gw_peers, float* grad_w,
-                            b200moe_stream_t stream);
-/* owner side, backward: grad_eo[row] = w_peers[src][slot] * go_peers[src][slot / k]; gw_rows[row] = <go, eo[row]>. */
-int b200moe_ep_combine_bwd_pull(const void* const* go_peers, const void* const* w_peers, const void* eo,
-                                const int32_t* row_src, const int32_t* row_slot_src, const int32_t* total_rows,
-                                int W, int k, int64_t H, int64_t rows_cap, void* grad_eo, float* gw_rows,
-                                b200moe_stream_t stream);
+                            int32_t* status, b200moe_stream_t stream);
+/* owner side, backward, same traversal: grad_eo[row] = w_peers[s][t,j] * go_peers[s][t] (grad_out read once per
+ * token and owner); gw_rows[row] = <go, eo[row]>; pad rows zero. */
+int b200moe_ep_combine_bwd_pull(const void* const* go_peers, const void* const* w_peers,
+                                const void* const* idx_peers, const void* const* spos_peers,
+                                const void* const* offs_peers, const void* eo, const int32_t* counts_l,
+                                const int32_t* poffs_l, const int32_t* src_base, int W, int rank, int E, int64_t T,
+                                int k, int64_t H, void* grad_eo, float* gw_rows, b200moe_stream_t stream);
 
 #ifdef __cplusplus
 }

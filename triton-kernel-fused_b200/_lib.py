@@ -29,6 +29,7 @@ _SIGNATURES = {
     "b200moe_status_string": (ctypes.c_char_p, [c_int]),
     "b200moe_padded_rows_cap": (c_int64, [c_int64, c_int]),
     "b200moe_set_reserved_sms": (c_int, [c_int]),
+    "b200moe_set_exchange_sms": (c_int, [c_int]),
     "b200moe_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_void_p]),
     "b200moe_router_topk_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_float,
                                         c_void_p, c_void_p, c_void_p, c_void_p]),
@@ -68,9 +69,9 @@ _SIGNATURES = {
     "b200moe_mxfp8_gather_quant": (c_int, [c_void_p] * 3 + [c_int, c_int64, c_int64] + [c_void_p] * 4),
     "b200moe_mxfp8_expert_wgrad": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
     "b200moe_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 5 + [c_void_p]),
-    "b200moe_ep_gather_pull": (c_int, [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int64, c_int64] + [c_void_p] * 4),
-    "b200moe_ep_combine_pull": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int64, c_int, c_int64] + [c_void_p] * 4),
-    "b200moe_ep_combine_bwd_pull": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int64, c_int64] + [c_void_p] * 3),
+    "b200moe_ep_gather_pull": (c_int, [c_void_p] * 7 + [c_int, c_int, c_int, c_int64, c_int, c_int64] + [c_void_p] * 2),
+    "b200moe_ep_combine_pull": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int64, c_int, c_int64] + [c_void_p] * 5),
+    "b200moe_ep_combine_bwd_pull": (c_int, [c_void_p] * 9 + [c_int, c_int, c_int, c_int64, c_int, c_int64] + [c_void_p] * 3),
     "b200moe_combine": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64, c_void_p, c_void_p]),
     "b200moe_combine_bwd": (c_int, [c_void_p] * 5 + [c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
 }

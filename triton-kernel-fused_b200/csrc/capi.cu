@@ -59,6 +59,13 @@ int gemm_cta_budget() {
   return n < 2 ? 2 : n;
 }
 
+static std::atomic<int> g_exchange_sms{0};
+
+int exchange_sm_budget() {
+  const int n = g_exchange_sms.load(std::memory_order_relaxed);
+  return n > 0 ? n : num_sms();
+}
+
 }  // namespace b200moe
 
 extern "C" {
@@ -80,6 +87,15 @@ int b200moe_set_reserved_sms(int n) {
     return B200MOE_E_BAD_SHAPE;
   }
   b200moe::g_reserved_sms.store(n, std::memory_order_relaxed);
+  return 0;
+}
+
+int b200moe_set_exchange_sms(int n) {
+  if (n < 0 || n > b200moe::num_sms()) {
+    b200moe::set_error("set_exchange_sms: %d is outside [0, %d]", n, b200moe::num_sms());
+    return B200MOE_E_BAD_SHAPE;
+  }
+  b200moe::g_exchange_sms.store(n, std::memory_order_relaxed);
   return 0;
 }
 

@@ -23,6 +23,7 @@ void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
 int num_sms();
 int gemm_cta_budget();   // CTAs a persistent GEMM may occupy (num_sms() minus the reserved SMs)
+int exchange_sm_budget();   // SMs (= fat CTAs) the home-side pull kernel of the expert-parallel exchange may occupy
 
 #define B200_CHECK_ARG(cond, code, ...)  \
   do {                                   \

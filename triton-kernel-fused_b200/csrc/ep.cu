@@ -5,13 +5,18 @@
 //   ep_plan             from the all-gathered (W,E) count matrix: this rank's padded expert segments,
 //                       where each source rank's block starts inside them, and where this rank's own
 //                       blocks start on their owners
-//   ep_gather_pull      owner side, forward: x_s[row] = x of the source rank's token, zero pad rows
+//   ep_gather_pull      owner side, forward: x_s[row] = x of the source rank's token, zero pad rows; a token
+//                       routed to several experts of this rank crosses NVLink once and is written to all
+//                       of its rows
 //   ep_combine_pull     home side: out[t] = sum_j w * rows of the owners (forward combine, and the
 //                       grad_hidden un-permute with w = 1, plus the grad of the routing weights)
-//   ep_combine_bwd_pull owner side, backward: grad_eo[row] = w * grad_out of the source's token
+//   ep_combine_bwd_pull owner side, backward: grad_eo[row] = w * grad_out of the source's token (again one
+//                       transfer per token and owner), gw[row] = <grad_out, eo[row]>
 // Kernels only READ peer memory; each phase is separated from the next by a cross-rank barrier
 // that the host side issues (the kernels themselves never wait on a peer).
 #include <cuda_bf16.h>
+
+#include <mutex>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -72,56 +77,77 @@ ep_plan_kernel(const int* __restrict__ counts_all, int W, int rank, int E, int* 
   }
 }
 
-// One warp per padded row of this rank.
+// The rows of this rank that a (source rank, token) pair feeds: lane j < k looks at slot j of the token in
+// the source's routing tables (peer reads) and, when that expert lives here, computes the padded row
+//   src_base[source][local expert] + (position of the slot inside its expert segment at the source).
+// Returns the ballot of lanes with a local slot; `row` is valid on those lanes.
+__device__ __forceinline__ unsigned local_rows_of_token(const long long* __restrict__ idx_s,
+                                                        const int* __restrict__ spos_s,
+                                                        const int* __restrict__ offs_s,
+                                                        const int* __restrict__ src_base, int s, long long t, int k,
+                                                        int rank, int El, int lane, int& row) {
+  bool local = false;
+  row = 0;
+  if (lane < k) {
+    const int e = static_cast<int>(idx_s[t * k + lane]);
+    if (e / El == rank) {
+      local = true;
+      row = src_base[s * El + (e - rank * El)] + spos_s[t * k + lane] - offs_s[e];
+    }
+  }
+  return __ballot_sync(0xffffffffu, local);
+}
+
+// pad rows [poffs[j] + counts[j], poffs[j+1]) of every local expert, one warp per row
+template <typename F>
+__device__ __forceinline__ void for_each_pad_row(const int* __restrict__ counts_l, const int* __restrict__ poffs_l,
+                                                 int El, long long warp0, long long nwarps, F f) {
+  for (int j = 0; j < El; ++j) {
+    const int p0 = poffs_l[j] + counts_l[j], p1 = poffs_l[j + 1];
+    for (long long r = p0 + warp0; r < p1; r += nwarps) f(r);
+  }
+}
+
+// One warp per (source rank, token): the token row is loaded once (from the peer's x) and stored to each of
+// its rows here.  Tasks are numbered token-major so that neighbouring warps read from different peers.
 __global__ void __launch_bounds__(256)
-ep_gather_pull_kernel(PeerPtrs x_peers, PeerPtrs order_peers, PeerPtrs offs_peers, const int* __restrict__ counts_l,
-                      const int* __restrict__ poffs_l, const int* __restrict__ tile_expert_l,
-                      const int* __restrict__ src_base, int W, int rank, int El, int k, int vec_per_row,
-                      uint4* __restrict__ x_s, int* __restrict__ row_src, int* __restrict__ row_slot_src) {
+ep_gather_pull_kernel(const __grid_constant__ PeerPtrs x_peers, const __grid_constant__ PeerPtrs idx_peers,
+                      const __grid_constant__ PeerPtrs spos_peers, const __grid_constant__ PeerPtrs offs_peers,
+                      const int* __restrict__ counts_l, const int* __restrict__ poffs_l,
+                      const int* __restrict__ src_base, int W, int rank, int El, long long T, int k, int vec_per_row,
+                      uint4* __restrict__ x_s) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  const int total = poffs_l[El];
-  for (long long r = warp0; r < total; r += nwarps) {
-    int src = -1, slot = 0;
-    if (lane == 0) {
-      const int j = tile_expert_l[r / B200MOE_TILE_M];
-      const int i = static_cast<int>(r) - poffs_l[j];
-      if (i < counts_l[j]) {
-        int s = 0;
-        while (s + 1 < W && src_base[(s + 1) * El + j] <= static_cast<int>(r)) ++s;
-        // skip sources whose block is empty: the largest s with src_base <= r is the owner of r
-        const int within = static_cast<int>(r) - src_base[s * El + j];
-        const int* offs_s = reinterpret_cast<const int*>(offs_peers.p[s]);
-        const int* order_s = reinterpret_cast<const int*>(order_peers.p[s]);
-        const int e = rank * El + j;
-        slot = order_s[offs_s[e] + within];
-        src = s;
-      }
-    }
-    src = __shfl_sync(0xffffffffu, src, 0);
-    slot = __shfl_sync(0xffffffffu, slot, 0);
-    uint4* dst = x_s + r * vec_per_row;
-    if (src < 0) {
-      for (int c = lane; c < vec_per_row; c += 32) dst[c] = make_uint4(0u, 0u, 0u, 0u);
-    } else {
-      const uint4* srow = reinterpret_cast<const uint4*>(x_peers.p[src]) + static_cast<long long>(slot / k) * vec_per_row;
-      // peer loads have microseconds of latency: keep 8 of them in flight per lane
-      for (int c0 = lane; c0 < vec_per_row; c0 += 32 * 8) {
-        uint4 v[8];
+  for (long long task = warp0; task < T * W; task += nwarps) {
+    const int s = static_cast<int>(task % W);
+    const long long t = task / W;
+    int row;
+    const unsigned mask = local_rows_of_token(reinterpret_cast<const long long*>(idx_peers.p[s]),
+                                              reinterpret_cast<const int*>(spos_peers.p[s]),
+                                              reinterpret_cast<const int*>(offs_peers.p[s]), src_base, s, t, k, rank,
+                                              El, lane, row);
+    if (mask == 0u) continue;
+    const uint4* srow = reinterpret_cast<const uint4*>(x_peers.p[s]) + t * vec_per_row;
+    // peer loads have microseconds of latency: keep 8 of them in flight per lane
+    for (int c0 = lane; c0 < vec_per_row; c0 += 32 * 8) {
+      uint4 v[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (c0 + 32 * i < vec_per_row) v[i] = srow[c0 + 32 * i];
+      for (int i = 0; i < 8; ++i)
+        if (c0 + 32 * i < vec_per_row) v[i] = srow[c0 + 32 * i];
+      for (unsigned m = mask; m != 0u; m &= m - 1) {
+        const int r = __shfl_sync(0xffffffffu, row, __ffs(m) - 1);
+        uint4* dst = x_s + static_cast<long long>(r) * vec_per_row;
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           if (c0 + 32 * i < vec_per_row) dst[c0 + 32 * i] = v[i];
       }
     }
-    if (lane == 0) {
-      row_src[r] = src;
-      row_slot_src[r] = slot;
-    }
   }
+  for_each_pad_row(counts_l, poffs_l, El, warp0, nwarps, [&](long long r) {
+    uint4* dst = x_s + r * vec_per_row;
+    for (int c = lane; c < vec_per_row; c += 32) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+  });
 }
 
 __device__ __forceinline__ void fma8(float (&acc)[8], const uint4& v, float w) {
@@ -130,100 +156,241 @@ __device__ __forceinline__ void fma8(float (&acc)[8], const uint4& v, float w) {
   acc[4] += w * c.x; acc[5] += w * c.y; acc[6] += w * d.x; acc[7] += w * d.y;
 }
 
-// One CTA per token: out[t] = sum_j w[t,j] * rows_peer[owner(e_j)][dest_base[e_j] + slot_pos - offs[e_j]]
-__global__ void __launch_bounds__(256)
-ep_combine_pull_kernel(PeerPtrs rows_peers, const float* __restrict__ w, const long long* __restrict__ idx,
-                       const int* __restrict__ slot_pos, const int* __restrict__ offs,
-                       const int* __restrict__ dest_base, int El, long long T, int k, int vec_per_row,
-                       uint4* __restrict__ out, PeerPtrs gw_peers, float* __restrict__ grad_w) {
-  __shared__ int s_row[B200MOE_MAX_TOPK];
-  __shared__ int s_owner[B200MOE_MAX_TOPK];
-  __shared__ float s_w[B200MOE_MAX_TOPK];
-  for (long long t = blockIdx.x; t < T; t += gridDim.x) {
-    __syncthreads();
-    if (threadIdx.x < k) {
-      const long long s = t * k + threadIdx.x;
-      const int e = static_cast<int>(idx[s]);
-      const int row = dest_base[e] + slot_pos[s] - offs[e];
-      const int owner = e / El;
-      s_row[threadIdx.x] = row;
-      s_owner[threadIdx.x] = owner;
-      s_w[threadIdx.x] = (w != nullptr) ? w[s] : 1.0f;
-      if (grad_w != nullptr) grad_w[s] = reinterpret_cast<const float*>(gw_peers.p[owner])[row];
+// out[t] = sum_j w[t,j] * rows_peer[owner(e_j)][dest_base[e_j] + slot_pos - offs[e_j]]
+//
+// A bulk-copy pipeline, so that a few SMs keep enough bytes in flight to fill NVLink and the kernel can run
+// beside a persistent GEMM that leaves those SMs free.  One CTA per SM (its shared-memory ring fills the SM),
+// 288 threads: warp 0 is the producer, warps 1-8 sum and store.  A work item is (token, 4 KB column chunk);
+// its k source pieces are fetched with one cp.async.bulk each into a ring slot, counted on the slot's `full`
+// barrier; the consumers add them in slot order j = 0..k-1 with the weights the producer left beside the data
+// and release the slot.  The producer resolves the routing tables for 32/k items at a time (lane = item, slot)
+// and one batch ahead, so those dependent loads are off the copy path.  Every wait is bounded.
+constexpr int kPullChunk = 4096;          // bytes of one row piece
+constexpr int kPullConsumers = 256;       // one 16-byte vector of the chunk per consumer thread
+constexpr int kPullThreads = 32 + kPullConsumers;
+
+__global__ void __launch_bounds__(kPullThreads, 1)
+ep_combine_pull_kernel(const __grid_constant__ PeerPtrs rows_peers, const float* __restrict__ w,
+                       const long long* __restrict__ idx, const int* __restrict__ slot_pos,
+                       const int* __restrict__ offs, const int* __restrict__ dest_base, int El, long long T, int k,
+                       long long row_bytes, int nslots, uint8_t* __restrict__ out, int* __restrict__ status) {
+  extern __shared__ uint8_t pull_smem_raw[];
+  uint8_t* data = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pull_smem_raw) + 127) & ~static_cast<uintptr_t>(127));
+  float* sw = reinterpret_cast<float*>(data + static_cast<size_t>(nslots) * k * kPullChunk);   // [nslots][32]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sw + nslots * 32);
+  const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + nslots);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * nslots);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < nslots; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, kPullConsumers / 32);
     }
-    __syncthreads();
-    for (int c = threadIdx.x; c < vec_per_row; c += blockDim.x) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int j0 = 0; j0 < k; j0 += 8) {      // up to 8 peer loads in flight, summed in slot order
-        uint4 v[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (j0 + i < k)
-            v[i] = reinterpret_cast<const uint4*>(rows_peers.p[s_owner[j0 + i]])[static_cast<long long>(s_row[j0 + i]) * vec_per_row + c];
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (j0 + i < k) fma8(acc, v[i], s_w[j0 + i]);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const int nchunk = static_cast<int>((row_bytes + kPullChunk - 1) / kPullChunk);
+  const long long items = T * nchunk;
+  if (warp == 0) {
+    const int per = 32 / k;                  // items resolved per batch
+    const int sub = lane / k, j = lane - sub * k;
+    const bool active = sub < per;
+    int slot = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    // metadata of a batch: source address and weight of (item = first + sub * gridDim.x, slot j)
+    auto resolve = [&](long long first, const uint8_t*& src, float& wj, uint32_t& bytes) {
+      src = nullptr;
+      wj = 0.0f;
+      bytes = 0;
+      const long long item = first + static_cast<long long>(sub) * gridDim.x;
+      if (active && item < items) {
+        const long long t = item / nchunk;
+        const int ch = static_cast<int>(item - t * nchunk);
+        const long long s = t * k + j;
+        const int e = static_cast<int>(idx[s]);
+        const long long row = dest_base[e] + slot_pos[s] - offs[e];
+        const long long off = static_cast<long long>(ch) * kPullChunk;
+        bytes = static_cast<uint32_t>(row_bytes - off < kPullChunk ? row_bytes - off : kPullChunk);
+        src = reinterpret_cast<const uint8_t*>(rows_peers.p[e / El]) + row * row_bytes + off;
+        wj = (w != nullptr) ? w[s] : 1.0f;
       }
-      uint4 o;
-      o.x = pack_bf16x2(acc[0], acc[1]);
-      o.y = pack_bf16x2(acc[2], acc[3]);
-      o.z = pack_bf16x2(acc[4], acc[5]);
-      o.w = pack_bf16x2(acc[6], acc[7]);
-      out[t * vec_per_row + c] = o;
+    };
+    const long long stride = static_cast<long long>(per) * gridDim.x;
+    const uint8_t* src;
+    float wj;
+    uint32_t bytes;
+    resolve(blockIdx.x, src, wj, bytes);
+    for (long long first = blockIdx.x; first < items && ok; first += stride) {
+      const uint8_t* src_n;
+      float wj_n;
+      uint32_t bytes_n;
+      resolve(first + stride, src_n, wj_n, bytes_n);   // next batch's tables are read during this batch's copies
+      for (int b = 0; b < per; ++b) {
+        if (first + static_cast<long long>(b) * gridDim.x >= items) break;
+        int good = 1;
+        if (lane == 0) good = mbar_wait(bar_empty + 8 * slot, ph ^ 1, abort_flag, ST_WAIT_PRODUCER) ? 1 : 0;
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) {
+          ok = false;
+          break;
+        }
+        const uint32_t bytes_b = __shfl_sync(0xffffffffu, bytes, b * k);
+        if (sub == b && active) sw[slot * 32 + j] = wj;
+        __syncwarp();
+        if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * slot, static_cast<uint32_t>(k) * bytes_b);
+        __syncwarp();
+        if (sub == b && active)
+          bulk_load_1d(smem_u32(data + (static_cast<size_t>(slot) * k + j) * kPullChunk), src, bytes, bar_full + 8 * slot);
+        if (++slot == nslots) {
+          slot = 0;
+          ph ^= 1;
+        }
+      }
+      src = src_n;
+      wj = wj_n;
+      bytes = bytes_n;
     }
+  } else {
+    const int tid = threadIdx.x - 32;
+    int slot = 0;
+    uint32_t ph = 0;
+    // items of this CTA in the producer's order: batches of `per`, item = first + b * gridDim.x
+    const int per = 32 / k;
+    const long long stride = static_cast<long long>(per) * gridDim.x;
+    bool ok = true;
+    for (long long first = blockIdx.x; first < items && ok; first += stride) {
+      for (int b = 0; b < per; ++b) {
+        const long long item = first + static_cast<long long>(b) * gridDim.x;
+        if (item >= items) break;
+        if (!mbar_wait(bar_full + 8 * slot, ph, abort_flag, ST_WAIT_EPILOGUE)) {
+          ok = false;
+          break;
+        }
+        const long long t = item / nchunk;
+        const long long off = (item - t * nchunk) * kPullChunk;
+        const int nvec = static_cast<int>((row_bytes - off < kPullChunk ? row_bytes - off : kPullChunk) >> 4);
+        if (tid < nvec) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          const uint8_t* base = data + static_cast<size_t>(slot) * k * kPullChunk + tid * 16;
+          for (int jj = 0; jj < k; ++jj)
+            fma8(acc, *reinterpret_cast<const uint4*>(base + static_cast<size_t>(jj) * kPullChunk), sw[slot * 32 + jj]);
+          uint4 o;
+          o.x = pack_bf16x2(acc[0], acc[1]);
+          o.y = pack_bf16x2(acc[2], acc[3]);
+          o.z = pack_bf16x2(acc[4], acc[5]);
+          o.w = pack_bf16x2(acc[6], acc[7]);
+          *reinterpret_cast<uint4*>(out + t * row_bytes + off + tid * 16) = o;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
+        if (++slot == nslots) {
+          slot = 0;
+          ph ^= 1;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0 && status != nullptr) atomicCAS(status, 0, *abort_flag);
+}
+
+// grad of the routing weights: grad_w[t,j] = the owner's row dot product of that slot (a 4-byte peer read each)
+__global__ void __launch_bounds__(256)
+ep_pull_row_scalars_kernel(const __grid_constant__ PeerPtrs gw_peers, const long long* __restrict__ idx,
+                           const int* __restrict__ slot_pos, const int* __restrict__ offs,
+                           const int* __restrict__ dest_base, int El, long long slots, float* __restrict__ grad_w) {
+  for (long long s = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; s < slots;
+       s += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int e = static_cast<int>(idx[s]);
+    grad_w[s] = reinterpret_cast<const float*>(gw_peers.p[e / El])[dest_base[e] + slot_pos[s] - offs[e]];
   }
 }
 
-// One warp per padded row of this rank: grad_eo[r] = go_peer[src][slot/k] * w_peer[src][slot];
-// gw_rows[r] = <go, eo[r]> (fp32); zero rows for pads.
-__global__ void __launch_bounds__(256)
-ep_combine_bwd_pull_kernel(PeerPtrs go_peers, PeerPtrs w_peers, const uint4* __restrict__ eo,
-                           const int* __restrict__ row_src, const int* __restrict__ row_slot_src,
-                           const int* __restrict__ total_rows, int k, int vec_per_row, uint4* __restrict__ grad_eo,
+// One warp per (source rank, token): grad_out of the token is loaded once from the peer; for each of its
+// rows r here grad_eo[r] = grad_out * w_peer[slot] and gw_rows[r] = <grad_out, eo[r]> (fp32); pad rows zero.
+__global__ void __launch_bounds__(256, 3)
+ep_combine_bwd_pull_kernel(const __grid_constant__ PeerPtrs go_peers, const __grid_constant__ PeerPtrs w_peers,
+                           const __grid_constant__ PeerPtrs idx_peers, const __grid_constant__ PeerPtrs spos_peers,
+                           const __grid_constant__ PeerPtrs offs_peers, const uint4* __restrict__ eo, const int* __restrict__ counts_l,
+                           const int* __restrict__ poffs_l, const int* __restrict__ src_base, int W, int rank, int El,
+                           long long T, int k, int vec_per_row, uint4* __restrict__ grad_eo,
                            float* __restrict__ gw_rows) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  const int total = *total_rows;
-  for (long long r = warp0; r < total; r += nwarps) {
-    const int src = row_src[r];
-    uint4* dst = grad_eo + r * vec_per_row;
-    if (src < 0) {
-      for (int c = lane; c < vec_per_row; c += 32) dst[c] = make_uint4(0u, 0u, 0u, 0u);
-      if (lane == 0) gw_rows[r] = 0.0f;
-      continue;
-    }
-    const int slot = row_slot_src[r];
-    const float wt = reinterpret_cast<const float*>(w_peers.p[src])[slot];
-    const uint4* g = reinterpret_cast<const uint4*>(go_peers.p[src]) + static_cast<long long>(slot / k) * vec_per_row;
-    const uint4* e = eo + r * vec_per_row;
-    float dot = 0.0f;
-    for (int c0 = lane; c0 < vec_per_row; c0 += 32 * 8) {
-      uint4 gv[8], ev[8];
+  for (long long task = warp0; task < T * W; task += nwarps) {
+    const int s = static_cast<int>(task % W);
+    const long long t = task / W;
+    int row;
+    const unsigned mask = local_rows_of_token(reinterpret_cast<const long long*>(idx_peers.p[s]),
+                                              reinterpret_cast<const int*>(spos_peers.p[s]),
+                                              reinterpret_cast<const int*>(offs_peers.p[s]), src_base, s, t, k, rank,
+                                              El, lane, row);
+    if (mask == 0u) continue;
+    float wt_lane = 0.0f;
+    if ((mask >> lane) & 1u) wt_lane = reinterpret_cast<const float*>(w_peers.p[s])[t * k + lane];
+    const uint4* g = reinterpret_cast<const uint4*>(go_peers.p[s]) + t * vec_per_row;
+    float dot_lane = 0.0f;   // lane j keeps the row dot of slot j
+    constexpr int kB = 4;   // 16-byte vectors per lane and row in flight
+    for (int c0 = lane; c0 < vec_per_row; c0 += 32 * kB) {
+      uint4 gv[kB], ev[kB], ev_next[kB];
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (c0 + 32 * i < vec_per_row) {
-          gv[i] = g[c0 + 32 * i];
-          ev[i] = e[c0 + 32 * i];
+      for (int i = 0; i < kB; ++i)
+        if (c0 + 32 * i < vec_per_row) gv[i] = g[c0 + 32 * i];
+      unsigned m = mask;
+      int j = __ffs(m) - 1;
+      int r = __shfl_sync(0xffffffffu, row, j);
+      {
+        const uint4* e = eo + static_cast<long long>(r) * vec_per_row;
+#pragma unroll
+        for (int i = 0; i < kB; ++i)
+          if (c0 + 32 * i < vec_per_row) ev[i] = e[c0 + 32 * i];
+      }
+      while (m != 0u) {
+        m &= m - 1;
+        // the next slot's eo row is requested before this slot's arithmetic
+        const int jn = m != 0u ? __ffs(m) - 1 : j;
+        const int rn = __shfl_sync(0xffffffffu, row, jn);
+        if (m != 0u) {
+          const uint4* e = eo + static_cast<long long>(rn) * vec_per_row;
+#pragma unroll
+          for (int i = 0; i < kB; ++i)
+            if (c0 + 32 * i < vec_per_row) ev_next[i] = e[c0 + 32 * i];
         }
+        const float wt = __shfl_sync(0xffffffffu, wt_lane, j);
+        uint4* dst = grad_eo + static_cast<long long>(r) * vec_per_row;
+        float dot = 0.0f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (c0 + 32 * i < vec_per_row) {
-          const float2 g0 = unpack_bf16x2(gv[i].x), g1 = unpack_bf16x2(gv[i].y), g2 = unpack_bf16x2(gv[i].z), g3 = unpack_bf16x2(gv[i].w);
-          const float2 e0 = unpack_bf16x2(ev[i].x), e1 = unpack_bf16x2(ev[i].y), e2 = unpack_bf16x2(ev[i].z), e3 = unpack_bf16x2(ev[i].w);
-          dot += g0.x * e0.x + g0.y * e0.y + g1.x * e1.x + g1.y * e1.y + g2.x * e2.x + g2.y * e2.y + g3.x * e3.x + g3.y * e3.y;
-          uint4 o;
-          o.x = pack_bf16x2(g0.x * wt, g0.y * wt);
-          o.y = pack_bf16x2(g1.x * wt, g1.y * wt);
-          o.z = pack_bf16x2(g2.x * wt, g2.y * wt);
-          o.w = pack_bf16x2(g3.x * wt, g3.y * wt);
-          dst[c0 + 32 * i] = o;
-        }
+        for (int i = 0; i < kB; ++i)
+          if (c0 + 32 * i < vec_per_row) {
+            const float2 g0 = unpack_bf16x2(gv[i].x), g1 = unpack_bf16x2(gv[i].y), g2 = unpack_bf16x2(gv[i].z), g3 = unpack_bf16x2(gv[i].w);
+            const float2 e0 = unpack_bf16x2(ev[i].x), e1 = unpack_bf16x2(ev[i].y), e2 = unpack_bf16x2(ev[i].z), e3 = unpack_bf16x2(ev[i].w);
+            dot += g0.x * e0.x + g0.y * e0.y + g1.x * e1.x + g1.y * e1.y + g2.x * e2.x + g2.y * e2.y + g3.x * e3.x + g3.y * e3.y;
+            uint4 o;
+            o.x = pack_bf16x2(g0.x * wt, g0.y * wt);
+            o.y = pack_bf16x2(g1.x * wt, g1.y * wt);
+            o.z = pack_bf16x2(g2.x * wt, g2.y * wt);
+            o.w = pack_bf16x2(g3.x * wt, g3.y * wt);
+            dst[c0 + 32 * i] = o;
+          }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+        if (lane == j) dot_lane += dot;   // chunks of the row in ascending order: a fixed summation order
+#pragma unroll
+        for (int i = 0; i < kB; ++i) ev[i] = ev_next[i];
+        j = jn;
+        r = rn;
+      }
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-    if (lane == 0) gw_rows[r] = dot;
+    if ((mask >> lane) & 1u) gw_rows[row] = dot_lane;
   }
+  for_each_pad_row(counts_l, poffs_l, El, warp0, nwarps, [&](long long r) {
+    uint4* dst = grad_eo + r * vec_per_row;
+    for (int c = lane; c < vec_per_row; c += 32) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+    if (lane == 0) gw_rows[r] = 0.0f;
+  });
 }
 
 static int load_peers(PeerPtrs* out, const void* const* host_ptrs, int W, const char* who) {
@@ -267,33 +434,36 @@ int b200moe_ep_plan(const int32_t* counts_all, int W, int rank, int E, int32_t* 
   return 0;
 }
 
-int b200moe_ep_gather_pull(const void* const* x_peers, const void* const* order_peers, const void* const* offs_peers,
-                           const int32_t* counts_l, const int32_t* poffs_l, const int32_t* tile_expert_l,
-                           const int32_t* src_base, int W, int rank, int E, int k, int64_t H, int64_t rows_cap,
-                           void* x_s, int32_t* row_src, int32_t* row_slot_src, b200moe_stream_t stream) {
-  B200_CHECK_ARG(counts_l && poffs_l && tile_expert_l && src_base && x_s && row_src && row_slot_src, B200MOE_E_NULL,
-                 "ep_gather_pull: null pointer");
+#define LOAD_PEERS(var, table, who)                 \
+  PeerPtrs var;                                     \
+  {                                                 \
+    const int rc__ = load_peers(&var, table, W, who); \
+    if (rc__) return rc__;                          \
+  }
+
+int b200moe_ep_gather_pull(const void* const* x_peers, const void* const* idx_peers, const void* const* spos_peers,
+                           const void* const* offs_peers, const int32_t* counts_l, const int32_t* poffs_l,
+                           const int32_t* src_base, int W, int rank, int E, int64_t T, int k, int64_t H, void* x_s,
+                           b200moe_stream_t stream) {
+  B200_CHECK_ARG(counts_l && poffs_l && src_base && x_s, B200MOE_E_NULL, "ep_gather_pull: null pointer");
   CHECK_WORLD("ep_gather_pull");
-  B200_CHECK_ARG(H > 0 && H % 8 == 0 && k >= 1 && E % W == 0, B200MOE_E_BAD_SHAPE, "ep_gather_pull: H = %lld, k = %d",
-                 (long long)H, k);
-  PeerPtrs xp, op, fp;
-  int rc = load_peers(&xp, x_peers, W, "ep_gather_pull(x)");
-  if (rc) return rc;
-  rc = load_peers(&op, order_peers, W, "ep_gather_pull(order)");
-  if (rc) return rc;
-  rc = load_peers(&fp, offs_peers, W, "ep_gather_pull(offs)");
-  if (rc) return rc;
-  if (rows_cap <= 0) return 0;
-  ep_gather_pull_kernel<<<grid_rows((rows_cap + 7) / 8, 8), 256, 0, (cudaStream_t)stream>>>(
-      xp, op, fp, counts_l, poffs_l, tile_expert_l, src_base, W, rank, E / W, k, static_cast<int>(H / 8),
-      reinterpret_cast<uint4*>(x_s), row_src, row_slot_src);
+  B200_CHECK_ARG(H > 0 && H % 8 == 0 && k >= 1 && k <= B200MOE_MAX_TOPK && E % W == 0 && T >= 0, B200MOE_E_BAD_SHAPE,
+                 "ep_gather_pull: H = %lld, k = %d, T = %lld", (long long)H, k, (long long)T);
+  LOAD_PEERS(xp, x_peers, "ep_gather_pull(x)");
+  LOAD_PEERS(ip, idx_peers, "ep_gather_pull(idx)");
+  LOAD_PEERS(sp, spos_peers, "ep_gather_pull(slot_pos)");
+  LOAD_PEERS(fp, offs_peers, "ep_gather_pull(offs)");
+  ep_gather_pull_kernel<<<grid_rows((T * W + 7) / 8, 8), 256, 0, (cudaStream_t)stream>>>(
+      xp, ip, sp, fp, counts_l, poffs_l, src_base, W, rank, E / W, T, k, static_cast<int>(H / 8),
+      reinterpret_cast<uint4*>(x_s));
   B200_CUDA(cudaGetLastError());
   return 0;
 }
 
 int b200moe_ep_combine_pull(const void* const* rows_peers, const float* w, const int64_t* idx, const int32_t* slot_pos,
                             const int32_t* offs, const int32_t* dest_base, int W, int E, int64_t T, int k, int64_t H,
-                            void* out, const void* const* gw_peers, float* grad_w, b200moe_stream_t stream) {
+                            void* out, const void* const* gw_peers, float* grad_w, int32_t* status,
+                            b200moe_stream_t stream) {
   B200_CHECK_ARG(idx && slot_pos && offs && dest_base && out, B200MOE_E_NULL, "ep_combine_pull: null pointer");
   const int rank = 0;
   CHECK_WORLD("ep_combine_pull");
@@ -301,41 +471,56 @@ int b200moe_ep_combine_pull(const void* const* rows_peers, const float* w, const
                  "ep_combine_pull: H = %lld, k = %d", (long long)H, k);
   B200_CHECK_ARG((gw_peers == nullptr) == (grad_w == nullptr), B200MOE_E_NULL,
                  "ep_combine_pull: gw_peers and grad_w go together");
-  PeerPtrs rp, gp;
-  int rc = load_peers(&rp, rows_peers, W, "ep_combine_pull(rows)");
-  if (rc) return rc;
-  for (int i = 0; i < kMaxRanks; ++i) gp.p[i] = nullptr;
-  if (gw_peers != nullptr) {
-    rc = load_peers(&gp, gw_peers, W, "ep_combine_pull(grad_w rows)");
-    if (rc) return rc;
-  }
+  B200_CHECK_ARG(aligned16(out), B200MOE_E_ALIGN, "ep_combine_pull: out must be 16-byte aligned");
+  LOAD_PEERS(rp, rows_peers, "ep_combine_pull(rows)");
   if (T <= 0) return 0;
-  ep_combine_pull_kernel<<<grid_rows(T, 16), 256, 0, (cudaStream_t)stream>>>(
-      rp, w, reinterpret_cast<const long long*>(idx), slot_pos, offs, dest_base, E / W, T, k, static_cast<int>(H / 8),
-      reinterpret_cast<uint4*>(out), gp, grad_w);
+  if (gw_peers != nullptr) {
+    LOAD_PEERS(gp, gw_peers, "ep_combine_pull(grad_w rows)");
+    ep_pull_row_scalars_kernel<<<grid_rows((T * k + 255) / 256, 8), 256, 0, (cudaStream_t)stream>>>(
+        gp, reinterpret_cast<const long long*>(idx), slot_pos, offs, dest_base, E / W, T * k, grad_w);
+    B200_CUDA(cudaGetLastError());
+  }
+  // ring slots: as many (k pieces of 4 KB + 32 weights + 2 barriers) as fit in 227 KB, at most 16
+  const size_t per_slot = static_cast<size_t>(k) * kPullChunk + 32 * sizeof(float) + 16;
+  int nslots = static_cast<int>((232448 - 256) / per_slot);
+  if (nslots > 16) nslots = 16;
+  B200_CHECK_ARG(nslots >= 2, B200MOE_E_UNSUPPORTED, "ep_combine_pull: k = %d rows of 4 KB do not fit twice in shared memory", k);
+  const size_t smem = nslots * per_slot + 128 + 16;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(ep_combine_pull_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+  });
+  if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(max dynamic smem)");
+  const long long row_bytes = H * 2;
+  const long long items = T * ((row_bytes + kPullChunk - 1) / kPullChunk);
+  long long grid = exchange_sm_budget();
+  if (grid > items) grid = items;
+  ep_combine_pull_kernel<<<static_cast<int>(grid), kPullThreads, smem, (cudaStream_t)stream>>>(
+      rp, w, reinterpret_cast<const long long*>(idx), slot_pos, offs, dest_base, E / W, T, k, row_bytes, nslots,
+      reinterpret_cast<uint8_t*>(out), status);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
 
-int b200moe_ep_combine_bwd_pull(const void* const* go_peers, const void* const* w_peers, const void* eo,
-                                const int32_t* row_src, const int32_t* row_slot_src, const int32_t* total_rows, int W,
-                                int k, int64_t H, int64_t rows_cap, void* grad_eo, float* gw_rows,
-                                b200moe_stream_t stream) {
-  B200_CHECK_ARG(eo && row_src && row_slot_src && total_rows && grad_eo && gw_rows, B200MOE_E_NULL,
+int b200moe_ep_combine_bwd_pull(const void* const* go_peers, const void* const* w_peers,
+                                const void* const* idx_peers, const void* const* spos_peers,
+                                const void* const* offs_peers, const void* eo, const int32_t* counts_l,
+                                const int32_t* poffs_l, const int32_t* src_base, int W, int rank, int E, int64_t T,
+                                int k, int64_t H, void* grad_eo, float* gw_rows, b200moe_stream_t stream) {
+  B200_CHECK_ARG(eo && counts_l && poffs_l && src_base && grad_eo && gw_rows, B200MOE_E_NULL,
                  "ep_combine_bwd_pull: null pointer");
-  const int rank = 0;
   CHECK_WORLD("ep_combine_bwd_pull");
-  B200_CHECK_ARG(H > 0 && H % 8 == 0 && k >= 1, B200MOE_E_BAD_SHAPE, "ep_combine_bwd_pull: H = %lld, k = %d",
-                 (long long)H, k);
-  PeerPtrs gp, wp;
-  int rc = load_peers(&gp, go_peers, W, "ep_combine_bwd_pull(grad_out)");
-  if (rc) return rc;
-  rc = load_peers(&wp, w_peers, W, "ep_combine_bwd_pull(weights)");
-  if (rc) return rc;
-  if (rows_cap <= 0) return 0;
-  ep_combine_bwd_pull_kernel<<<grid_rows((rows_cap + 7) / 8, 8), 256, 0, (cudaStream_t)stream>>>(
-      gp, wp, reinterpret_cast<const uint4*>(eo), row_src, row_slot_src, total_rows, k, static_cast<int>(H / 8),
-      reinterpret_cast<uint4*>(grad_eo), gw_rows);
+  B200_CHECK_ARG(H > 0 && H % 8 == 0 && k >= 1 && k <= B200MOE_MAX_TOPK && E % W == 0 && T >= 0, B200MOE_E_BAD_SHAPE,
+                 "ep_combine_bwd_pull: H = %lld, k = %d, T = %lld", (long long)H, k, (long long)T);
+  LOAD_PEERS(gp, go_peers, "ep_combine_bwd_pull(grad_out)");
+  LOAD_PEERS(wp, w_peers, "ep_combine_bwd_pull(weights)");
+  LOAD_PEERS(ip, idx_peers, "ep_combine_bwd_pull(idx)");
+  LOAD_PEERS(sp, spos_peers, "ep_combine_bwd_pull(slot_pos)");
+  LOAD_PEERS(fp, offs_peers, "ep_combine_bwd_pull(offs)");
+  ep_combine_bwd_pull_kernel<<<grid_rows((T * W + 7) / 8, 8), 256, 0, (cudaStream_t)stream>>>(
+      gp, wp, ip, sp, fp, reinterpret_cast<const uint4*>(eo), counts_l, poffs_l, src_base, W, rank, E / W, T, k,
+      static_cast<int>(H / 8), reinterpret_cast<uint4*>(grad_eo), gw_rows);
   B200_CUDA(cudaGetLastError());
   return 0;
 }

@@ -39,11 +39,6 @@ struct Fp8Params {
   uint8_t* q_sf;
 };
 
-__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
-               : "memory");
-}
 // shared-memory descriptor of a 32 x 16-byte scale atom: no swizzle, 8-row groups 128 bytes apart
 __device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
   uint64_t d = 0;

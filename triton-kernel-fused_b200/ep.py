@@ -126,7 +126,8 @@ class ExpertParallelMoELayer(nn.Module):
         """overlap_chunks > 1 splits the local tokens into that many independent pipelines on their own
         CUDA streams, so the all-to-alls of one chunk run while the expert GEMMs of another do;
         reserved_sms keeps that many SMs free of the persistent GEMM kernels for the communication
-        kernels (process-wide setting of the library)."""
+        kernels (process-wide setting of the library); with transport="p2p" it is the number of SMs on which
+        the backward's last pull runs beside the weight-gradient GEMMs (0 = no overlap)."""
         super().__init__()
         if transport not in ("nccl", "p2p"):
             raise ValueError("transport must be 'nccl' (all_to_all_single) or 'p2p' (peer-memory kernels)")
@@ -162,7 +163,8 @@ class ExpertParallelMoELayer(nn.Module):
             T, H = flat.shape
             ws = self._workspace
             if ws is None or (ws.T, ws.H, ws.k) != (T, H, self.top_k):
-                ws = self._workspace = SymmetricWorkspace(T, H, self.top_k, self.num_experts, self.group, flat.device)
+                ws = self._workspace = SymmetricWorkspace(T, H, self.top_k, self.num_experts, self.group, flat.device,
+                                                          overlap_sms=self.reserved_sms)
             return ep_moe_p2p(flat, idx, w, self.gate_up_proj, self.down_proj, ws), counts
         return ep_moe(flat, idx, w, self.gate_up_proj, self.down_proj, self.num_experts, self.group), counts
 

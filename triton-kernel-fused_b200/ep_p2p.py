@@ -51,15 +51,19 @@ class SymmetricWorkspace:
     """One symmetric allocation carved into the buffers peers read.  Sized for the worst case
     (every routed row of every rank lands on one rank), so it is allocated once."""
 
-    def __init__(self, T, H, k, E, group, device):
+    def __init__(self, T, H, k, E, group, device, overlap_sms=0):
+        """overlap_sms > 0: in the backward pass the last pull (grad_hidden) runs on that many SMs beside the
+        weight-gradient GEMMs, which leave them free and run on a high-priority stream of their own."""
         import torch.distributed._symmetric_memory as symm
+        self.overlap_sms = int(overlap_sms)
+        self.gemm_stream = torch.cuda.Stream(device=device, priority=-1) if self.overlap_sms > 0 else None
         self.group = group
         self.W = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.T, self.H, self.k, self.E = T, H, k, E
         M = T * k
         self.cap_w = L.padded_rows_cap(self.W * M, E // self.W)
-        fields = [("x", T * H * 2), ("go", T * H * 2), ("w", M * 4), ("order", M * 4), ("offs", (E + 1) * 4),
+        fields = [("x", T * H * 2), ("go", T * H * 2), ("w", M * 4), ("idx", M * 8), ("spos", M * 4), ("offs", (E + 1) * 4),
                   ("eo", self.cap_w * H * 2), ("gxs", self.cap_w * H * 2), ("gw", self.cap_w * 4)]
         self.offsets, total = {}, 0
         for name, nbytes in fields:
@@ -73,7 +77,8 @@ class SymmetricWorkspace:
         self.x = v("x", T * H, torch.bfloat16).view(T, H)
         self.go = v("go", T * H, torch.bfloat16).view(T, H)
         self.w = v("w", M, torch.float32).view(T, k)
-        self.order = v("order", M, torch.int32)
+        self.idx = v("idx", M, torch.int64).view(T, k)
+        self.spos = v("spos", M, torch.int32)
         self.offs = v("offs", E + 1, torch.int32)
         self.eo = v("eo", self.cap_w * H, torch.bfloat16).view(self.cap_w, H)
         self.gxs = v("gxs", self.cap_w * H, torch.bfloat16).view(self.cap_w, H)
@@ -103,12 +108,13 @@ class _ExpertParallelP2P(torch.autograd.Function):
         w32 = wt.detach().float().contiguous()
         gate_up_local, down_local = gate_up_local.contiguous(), down_local.contiguous()
 
-        perm = ops.permute_build(idx, E, want_order=True)
+        perm = ops.permute_build(idx, E, want_order=True)   # slot_pos comes with the order tables
         ws.x.copy_(hidden)
-        ws.order.copy_(perm.order)
+        ws.idx.copy_(idx)
+        ws.spos.copy_(perm.slot_pos)
         ws.offs.copy_(perm.offs)
         counts_all = torch.empty(W, E, **i32)
-        dist.all_gather_into_tensor(counts_all, perm.counts, group=ws.group)   # also: peers' x/order/offs are in place
+        dist.all_gather_into_tensor(counts_all, perm.counts, group=ws.group)   # also: peers' x/idx/spos/offs are in place
         R = int(counts_all[:, rank * El:(rank + 1) * El].sum().item())         # the one host sync
         cap_l = L.padded_rows_cap(R, El)
         poffs_l = torch.empty(El + 1, **i32)
@@ -119,21 +125,19 @@ class _ExpertParallelP2P(torch.autograd.Function):
         _plan(L.ptr(counts_all), W, rank, E, L.ptr(poffs_l), L.ptr(counts_l),
                                     L.ptr(tile_expert_l), L.ptr(src_base), L.ptr(dest_base), st)
         x_s = torch.empty(cap_l, H, dtype=torch.bfloat16, device=dev)
-        row_src = torch.empty(cap_l, **i32)
-        row_slot_src = torch.empty(cap_l, **i32)
-        _gather_pull(ws.peers["x"], ws.peers["order"], ws.peers["offs"], L.ptr(counts_l),
-                                           L.ptr(poffs_l), L.ptr(tile_expert_l), L.ptr(src_base), W, rank, E, k, H,
-                                           cap_l, L.ptr(x_s), L.ptr(row_src), L.ptr(row_slot_src), st)
+        _gather_pull(ws.peers["x"], ws.peers["idx"], ws.peers["spos"], ws.peers["offs"], L.ptr(counts_l),
+                     L.ptr(poffs_l), L.ptr(src_base), W, rank, E, T, k, H, L.ptr(x_s), st)
         perm_l = ops.Permutation(R, 1, El, cap_l, counts_l, None, poffs_l, None, None, tile_expert_l, None, None)
         gate_up, inter = ops.expert_gate_up_swiglu(x_s, gate_up_local, perm_l)
         ops.expert_down(inter, down_local, perm_l, out=ws.eo[:cap_l])
         ws.barrier()                                                # every owner's eo is complete
         out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
         _combine_pull(ws.peers["eo"], L.ptr(w32), L.ptr(idx), L.ptr(perm.slot_pos),
-                                            L.ptr(perm.offs), L.ptr(dest_base), W, E, T, k, H, L.ptr(out), None, None, st)
+                                            L.ptr(perm.offs), L.ptr(dest_base), W, E, T, k, H, L.ptr(out), None, None,
+                                            L.ptr(L.status_word(dev)), st)
         ws.generation += 1
         ctx.ws, ctx.perm, ctx.perm_l, ctx.gen = ws, perm, perm_l, ws.generation
-        ctx.tables = (dest_base, row_src, row_slot_src)
+        ctx.tables = (dest_base, src_base)
         ctx.wt_dtype = wt.dtype
         ctx.save_for_backward(idx, x_s, gate_up, inter, w32, gate_up_local, down_local)
         return out
@@ -142,7 +146,7 @@ class _ExpertParallelP2P(torch.autograd.Function):
     def backward(ctx, grad_out):
         idx, x_s, gate_up, inter, w32, gate_up_local, down_local = ctx.saved_tensors
         ws, perm, perm_l = ctx.ws, ctx.perm, ctx.perm_l
-        dest_base, row_src, row_slot_src = ctx.tables
+        dest_base, src_base = ctx.tables
         if ws.generation != ctx.gen:
             raise RuntimeError("the symmetric workspace was reused by another forward before this backward ran; "
                                "use one workspace per forward in flight")
@@ -155,19 +159,47 @@ class _ExpertParallelP2P(torch.autograd.Function):
         ws.w.copy_(w32)
         ws.barrier()                                                # every home rank's grad_out / w are in place
         grad_eo = torch.empty(cap_l, H, dtype=torch.bfloat16, device=dev)
-        _combine_bwd_pull(ws.peers["go"], ws.peers["w"], L.ptr(ws.eo), L.ptr(row_src),
-                                                L.ptr(row_slot_src), L.ptr(perm_l.poffs[perm_l.E:]), W, k, H, cap_l,
-                                                L.ptr(grad_eo), L.ptr(ws.gw), st)
+        _combine_bwd_pull(ws.peers["go"], ws.peers["w"], ws.peers["idx"], ws.peers["spos"], ws.peers["offs"],
+                          L.ptr(ws.eo), L.ptr(perm_l.counts), L.ptr(perm_l.poffs), L.ptr(src_base), W, ws.rank, E, T, k,
+                          H, L.ptr(grad_eo), L.ptr(ws.gw), st)
         grad_gu = ops.expert_down_dgrad_glu(grad_eo, down_local, gate_up, perm_l)
-        grad_down = ops.expert_wgrad(grad_eo, inter, perm_l)
-        grad_gate_up = ops.expert_wgrad(grad_gu, x_s, perm_l)
-        ops.expert_gate_up_dgrad(grad_gu, gate_up_local, perm_l, out=ws.gxs[:cap_l])
-        ws.barrier()                                                # every owner's grad_x_s / gw are complete
         grad_hidden = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
         grad_w = torch.empty(T, k, dtype=torch.float32, device=dev)
-        _combine_pull(ws.peers["gxs"], None, L.ptr(idx), L.ptr(perm.slot_pos), L.ptr(perm.offs),
-                                            L.ptr(dest_base), W, E, T, k, H, L.ptr(grad_hidden), ws.peers["gw"],
-                                            L.ptr(grad_w), st)
+
+        def pull_grad_hidden():
+            _combine_pull(ws.peers["gxs"], None, L.ptr(idx), L.ptr(perm.slot_pos), L.ptr(perm.offs),
+                          L.ptr(dest_base), W, E, T, k, H, L.ptr(grad_hidden), ws.peers["gw"], L.ptr(grad_w),
+                          L.ptr(L.status_word(dev)), st)
+
+        if ws.overlap_sms <= 0:
+            grad_down = ops.expert_wgrad(grad_eo, inter, perm_l)
+            grad_gate_up = ops.expert_wgrad(grad_gu, x_s, perm_l)
+            ops.expert_gate_up_dgrad(grad_gu, gate_up_local, perm_l, out=ws.gxs[:cap_l])
+            ws.barrier()                                            # every owner's grad_x_s / gw are complete
+            pull_grad_hidden()
+        else:
+            # the dgrad that peers wait for goes first; the pull of grad_hidden then runs on overlap_sms SMs
+            # while the two weight-gradient GEMMs run on the others (the pull's CTAs each fill an SM, the GEMMs'
+            # persistent grids leave that many SMs out, so neither kernel waits for the other's SMs)
+            ops.expert_gate_up_dgrad(grad_gu, gate_up_local, perm_l, out=ws.gxs[:cap_l])
+            ws.barrier()
+            main, side = torch.cuda.current_stream(dev), ws.gemm_stream
+            side.wait_stream(main)
+            L.check(L.lib().b200moe_set_reserved_sms(ws.overlap_sms))
+            L.check(L.lib().b200moe_set_exchange_sms(ws.overlap_sms))
+            try:
+                with torch.cuda.stream(side):
+                    grad_gate_up = ops.expert_wgrad(grad_gu, x_s, perm_l)
+                    grad_down = ops.expert_wgrad(grad_eo, inter, perm_l)
+                pull_grad_hidden()
+            finally:
+                L.check(L.lib().b200moe_set_reserved_sms(0))
+                L.check(L.lib().b200moe_set_exchange_sms(0))
+            for t_ in (grad_gu, x_s, grad_eo, inter):
+                t_.record_stream(side)
+            main.wait_stream(side)
+            grad_gate_up.record_stream(main)
+            grad_down.record_stream(main)
         return grad_hidden, None, grad_w.to(ctx.wt_dtype), grad_gate_up, grad_down, None
 
 
