@@ -33,6 +33,8 @@ __host__ __device__ constexpr bool tma_epilogue() { return BN == 256 && EPI != E
 
 // EPI_WARP_BYTES: shared memory each epilogue warp owns (0: none, 4 KB: one output staging box,
 // 8 KB: the GLU-backward gate and up boxes that are loaded by TMA and overwritten in place)
+constexpr int kGluBoxBytes = 32 * 64;   // GLU backward: one 32 rows x 32 columns bf16 box
+
 template <int BN, int EPI>
 __host__ __device__ constexpr int epi_warp_bytes() {
   return !tma_epilogue<BN, EPI>() ? 0 : (EPI == EPI_GLU_BWD ? 2 * kStageOutBytes : kStageOutBytes);
@@ -48,7 +50,7 @@ struct Cfg {
   static constexpr int kFit = (kBudget - EPI_BYTES) / STAGE_BYTES;
   static constexpr int NSTAGE = kFit > 8 ? 8 : kFit;
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulators; 128, 256 or 512 (power of two >= 32)
-  static constexpr int BAR_BYTES = (2 * NSTAGE + 4 + kEpiWarps) * 8 + 16;
+  static constexpr int BAR_BYTES = (2 * NSTAGE + 4 + 2 * kEpiWarps) * 8 + 16;
   static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;  // + alignment slack
   static constexpr int TILE_ROWS = BM * CTAS;
 };
@@ -75,8 +77,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const uint32_t bar_empty = smem_u32(bars + NSTAGE);
   const uint32_t bar_tfull = smem_u32(bars + 2 * NSTAGE);
   const uint32_t bar_tempty = smem_u32(bars + 2 * NSTAGE + 2);
-  const uint32_t bar_epi = smem_u32(bars + 2 * NSTAGE + 4);   // one per epilogue warp (GLU backward loads)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGE + 4 + kEpiWarps);
+  const uint32_t bar_epi = smem_u32(bars + 2 * NSTAGE + 4);   // two per epilogue warp (GLU backward load sets)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGE + 4 + 2 * kEpiWarps);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -94,7 +96,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       mbar_init(bar_tfull + 8 * b, 1);
       mbar_init(bar_tempty + 8 * b, kEpiWarps * CTAS);
     }
-    for (int w = 0; w < kEpiWarps; ++w) mbar_init(bar_epi + 8 * w, 1);
+    for (int w = 0; w < 2 * kEpiWarps; ++w) mbar_init(bar_epi + 8 * w, 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
@@ -259,24 +261,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int buf = it & 1;
       const int row0 = t.m0 + BM * static_cast<int>(cta_rank) + q * 32;   // first row of this warp
       const long long row = static_cast<long long>(row0) + lane;
-      // GLU backward: the saved gate/up values do not depend on the accumulator, so the first
-      // 32 columns are fetched before waiting for the MMAs of this tile
-      // GLU backward: the saved gate/up values do not depend on the accumulator, so the TMA loads
-      // of this warp's first 32 x 64 gate and up boxes are issued before waiting for the MMAs
+      // GLU backward works on four 32-column sub-chunks per warp with two sets of (gate, up) boxes of
+      // 32 rows x 32 columns (2 KB, 64-byte swizzle): a set is loaded by TMA, overwritten in place with
+      // grad_gate / grad_up and stored by TMA while the other set is loading or being computed on.  The saved
+      // gate/up values do not depend on the accumulator, so the first two loads go out before the MMAs of
+      // the tile are waited for.
       const int glu_col0 = t.n0 + half * (BN / 2);
-      uint8_t* bufG = epi_smem + (warp - 2) * C::EPI_BYTES / kEpiWarps;
-      uint8_t* bufU = bufG + kStageOutBytes;
-      const uint32_t ebar = bar_epi + 8 * (warp - 2);
-      auto glu_load = [&](int col) {   // tmD2 = saved gate_up seen as {I, rows, 2}
-        staging_free(lane);            // earlier stores out of these boxes have been read
+      uint8_t* ebuf = epi_smem + (warp - 2) * C::EPI_BYTES / kEpiWarps;   // [set][gate | up] boxes of 2 KB
+      const uint32_t ebar = bar_epi + 16 * (warp - 2);                     // + 8 * set
+      auto glu_load = [&](int sub) {   // tmD2 = saved gate_up seen as {I, rows, 2}, box {32, 32}
+        const int set = sub & 1;
         if (lane == 0) {
-          mbar_arrive_expect_tx(ebar, 2 * kStageOutBytes);
-          tma_load_3d(smem_u32(bufG), &tmD2, ebar, col, row0, 0);
-          tma_load_3d(smem_u32(bufU), &tmD2, ebar, col, row0, 1);
+          mbar_arrive_expect_tx(ebar + 8 * set, 2 * kGluBoxBytes);
+          tma_load_3d(smem_u32(ebuf + set * 2 * kGluBoxBytes), &tmD2, ebar + 8 * set, glu_col0 + 32 * sub, row0, 0);
+          tma_load_3d(smem_u32(ebuf + set * 2 * kGluBoxBytes + kGluBoxBytes), &tmD2, ebar + 8 * set,
+                      glu_col0 + 32 * sub, row0, 1);
         }
       };
+      uint8_t* bufG = ebuf;   // staging box of the other TMA-store epilogues
       if constexpr (TMA_EPI && EPI == EPI_GLU_BWD) {
-        if (glu_col0 < p.I) glu_load(glu_col0);
+        staging_free(lane);   // the previous tile's stores out of these boxes have been read
+        if (glu_col0 < p.I) glu_load(0);
+        if (glu_col0 + 32 < p.I) glu_load(1);
       }
       if (!mbar_wait(bar_tfull + 8 * buf, (it >> 1) & 1, abort_flag, ST_WAIT_EPILOGUE)) break;
       __syncwarp();
@@ -352,39 +358,44 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         } else {  // EPI_GLU_BWD: accumulator = grad_inter columns [n0, n0+BN); this warp: 128 of them
           constexpr int W = BN / 2;
 #pragma unroll 1
-          for (int ch = 0; ch < 2; ++ch) {
-            const int col = glu_col0 + 64 * ch;
+          for (int sub = 0; sub < W / 32; ++sub) {
+            const int col = glu_col0 + 32 * sub;
             if (col >= p.I) break;                       // warp-uniform
-            if (ch == 1) glu_load(col);
-            if (!mbar_wait(ebar, epi_phase, abort_flag, ST_WAIT_EPILOGUE)) break;
-            epi_phase ^= 1;
+            const int set = sub & 1;
+            uint8_t* bG = ebuf + set * 2 * kGluBoxBytes;
+            uint8_t* bU = bG + kGluBoxBytes;
+            uint32_t r[32];
+            tmem_ld32(taddr + half * W + 32 * sub, r);
+            if (!mbar_wait(ebar + 8 * set, (epi_phase >> set) & 1u, abort_flag, ST_WAIT_EPILOGUE)) break;
+            epi_phase ^= 1u << set;
+            uint4 g4[4], u4[4];
 #pragma unroll
-            for (int sb = 0; sb < 2; ++sb) {
-              uint32_t r[32];
-              tmem_ld32(taddr + half * W + 64 * ch + 32 * sb, r);
-              uint4 g4[4], u4[4];
+            for (int v = 0; v < 4; ++v) {              // this lane's row: 64 bytes, 64-byte swizzle
+              const int off = lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4);
+              g4[v] = *reinterpret_cast<const uint4*>(bG + off);
+              u4[v] = *reinterpret_cast<const uint4*>(bU + off);
+            }
+            tmem_ld_wait();
+            uint32_t og[16], ou[16];
+            glu_bwd32(r, g4, u4, og, ou);
 #pragma unroll
-              for (int v = 0; v < 4; ++v) {              // this lane's row, swizzled 16-byte chunks
-                const int off = lane * 128 + (((4 * sb + v) ^ (lane & 7)) << 4);
-                g4[v] = *reinterpret_cast<const uint4*>(bufG + off);
-                u4[v] = *reinterpret_cast<const uint4*>(bufU + off);
-              }
-              tmem_ld_wait();
-              uint32_t og[16], ou[16];
-              glu_bwd32(r, g4, u4, og, ou);
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {              // results replace the inputs in place
-                const int off = lane * 128 + (((4 * sb + v) ^ (lane & 7)) << 4);
-                *reinterpret_cast<uint4*>(bufG + off) = make_uint4(og[4 * v], og[4 * v + 1], og[4 * v + 2], og[4 * v + 3]);
-                *reinterpret_cast<uint4*>(bufU + off) = make_uint4(ou[4 * v], ou[4 * v + 1], ou[4 * v + 2], ou[4 * v + 3]);
-              }
+            for (int v = 0; v < 4; ++v) {              // results replace the inputs in place
+              const int off = lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4);
+              *reinterpret_cast<uint4*>(bG + off) = make_uint4(og[4 * v], og[4 * v + 1], og[4 * v + 2], og[4 * v + 3]);
+              *reinterpret_cast<uint4*>(bU + off) = make_uint4(ou[4 * v], ou[4 * v + 1], ou[4 * v + 2], ou[4 * v + 3]);
             }
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tma_store_3d(&tmD, smem_u32(bufG), col, row0, 0);   // grad_gate
-              tma_store_3d(&tmD, smem_u32(bufU), col, row0, 1);   // grad_up
+              tma_store_3d(&tmD, smem_u32(bG), col, row0, 0);   // grad_gate
+              tma_store_3d(&tmD, smem_u32(bU), col, row0, 1);   // grad_up
               bulk_commit_group();
+            }
+            // as soon as that store has read its boxes (a few hundred ns), they are reloaded with the sub-chunk
+            // after the next one, which then has a whole sub-chunk of arithmetic to arrive
+            if (sub + 2 < W / 32 && glu_col0 + 32 * (sub + 2) < p.I) {
+              staging_free(lane);
+              glu_load(sub + 2);
             }
           }
         }
@@ -633,11 +644,22 @@ static int dispatch_bn(int bn, const Operand& A, const Operand& B, const Operand
       set_error("internal: output description missing");
       return B200MOE_E_UNSUPPORTED;
     }
-    rc = encode_operand(&tmD, *d1, 32);   // box {64 columns, 32 rows}
-    if (rc) return rc;
-    if (d2 != nullptr) {
-      rc = encode_operand(&tmD2, *d2, 32);
+    if (EPI == EPI_GLU_BWD) {   // boxes {32 columns, 32 rows}, 64-byte swizzle, for the in-place epilogue
+      if (d2 == nullptr) {
+        set_error("internal: saved gate_up description missing");
+        return B200MOE_E_UNSUPPORTED;
+      }
+      rc = make_map(&tmD, d1->ptr, d1->k, d1->rows, d1->groups, d1->ld, d1->group_stride, 32, 32, 2, 64);
       if (rc) return rc;
+      rc = make_map(&tmD2, d2->ptr, d2->k, d2->rows, d2->groups, d2->ld, d2->group_stride, 32, 32, 2, 64);
+      if (rc) return rc;
+    } else {
+      rc = encode_operand(&tmD, *d1, 32);   // box {64 columns, 32 rows}
+      if (rc) return rc;
+      if (d2 != nullptr) {
+        rc = encode_operand(&tmD2, *d2, 32);
+        if (rc) return rc;
+      }
     }
   }
   if (pair) return launch<256, EPI, 2>(tmA, tmB, tmD, tmD2, p, max_tiles > 0 ? (max_tiles + 1) / 2 : 0, stream);

@@ -200,10 +200,10 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// bf16 (or byte) tensor seen as dims {inner, outer, groups}; strides in elements; 128B swizzle; zero OOB fill.
+// bf16 (or byte) tensor seen as dims {inner, outer, groups}; strides in elements; 128B (or 64B) swizzle; zero OOB fill.
 static int make_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t outer, uint64_t groups,
                     uint64_t outer_stride, uint64_t group_stride, uint32_t box_inner, uint32_t box_outer,
-                    int elem_bytes = 2) {
+                    int elem_bytes = 2, int swizzle_bytes = 128) {
   EncodeTiledFn fn = get_encode_fn();
   B200_CHECK_ARG(fn != nullptr, B200MOE_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
   B200_CHECK_ARG(aligned16(base), B200MOE_E_ALIGN, "tensor base %p is not 16-byte aligned", base);
@@ -215,7 +215,7 @@ static int make_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t 
   cuuint32_t box[3] = {box_inner, box_outer, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(tm, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   B200_CHECK_ARG(r == CUDA_SUCCESS, B200MOE_E_CUDA,
                  "cuTensorMapEncodeTiled failed (%d): dims {%llu,%llu,%llu} box {%u,%u}", (int)r,

@@ -311,11 +311,17 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 // epilogue of a tile runs while the producer already refills the stages of the next one.
 constexpr int PBN = 256;
 constexpr int kPStage = 34816;           // A 16 KB + B 16 KB + SFA 512 B + SFB 1 KB, rounded to 1 KB
-constexpr int kPStages = 5;
+// GLU backward keeps two boxes per epilogue warp (gate and up: loaded by TMA, overwritten in place, stored by
+// TMA) and therefore one stage less
+template <int EPI> struct PairCfg {
+  static constexpr int kStages = (EPI == EPI_GLU_BWD) ? 4 : 5;
+  static constexpr int kEpiBytes = kEpiWarps * kStageOutBytes * ((EPI == EPI_GLU_BWD) ? 2 : 1);
+  // barriers: full, empty, sf per stage; tfull, tempty; two per epilogue warp (GLU-backward load sets)
+  static constexpr int kSmemBytes = kStages * kPStage + kEpiBytes +
+                                    (3 * kStages + 2 + 2 * kEpiWarps) * 8 + 16 + 1024;
+};
 constexpr int kPSfCols = 16;             // tensor-memory columns per stage: SFA 4 + SFB 8 (+4 spare)
-constexpr int kPEpiBytes = kEpiWarps * kStageOutBytes;   // one 32 x 64 bf16 staging box per epilogue warp
 constexpr int kPThreads = kThreads + 32;   // one more warp: the scale-copy issuer
-constexpr int kPSmemBytes = kPStages * kPStage + kPEpiBytes + (3 * kPStages + 2) * 8 + 16 + 1024;
 
 // pair form of the 3-D load for the scale tensors {128 u32, k-chunks, row-blocks}
 __device__ __forceinline__ void umma_mxf8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -346,6 +352,8 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
+  constexpr int kPStages = PairCfg<EPI>::kStages;
+  constexpr int kPEpiBytes = PairCfg<EPI>::kEpiBytes;
   uint8_t* epi_smem = smem + kPStages * kPStage;          // 1 KB aligned: stages are multiples of 1 KB
   uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + kPEpiBytes);
   const uint32_t bar_full = smem_u32(bars);
@@ -353,7 +361,8 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const uint32_t bar_sf = smem_u32(bars + 2 * kPStages);   // scales of the stage are in tensor memory
   const uint32_t bar_tfull = smem_u32(bars + 3 * kPStages);
   const uint32_t bar_tempty = smem_u32(bars + 3 * kPStages + 1);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kPStages + 2);
+  const uint32_t bar_epi = smem_u32(bars + 3 * kPStages + 2);   // two per epilogue warp: GLU-backward loads landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kPStages + 2 + 2 * kEpiWarps);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -369,6 +378,7 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     }
     mbar_init(bar_tfull, 1);
     mbar_init(bar_tempty, 2 * kEpiWarps);
+    for (int i = 0; i < 2 * kEpiWarps; ++i) mbar_init(bar_epi + 8 * i, 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
@@ -499,17 +509,40 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;    // columns [128*half, 128*half + 128) of the tile
     const uint32_t tempty_leader = mapa_shared(bar_tempty, 0);
+    uint32_t epi_phase = 0;   // parity of this warp's GLU-backward load barrier
     int it = 0;
     for (int tile = first_tile; tile < total; tile += tile_step, ++it) {
       const Tile t = get_tile(p, tile, TN, TM, FBK, order);
+      const int row0 = t.m0 + BM * cta_rank + q * 32;
+      const long long row = static_cast<long long>(row0) + lane;
+      // GLU backward works on four 32-column sub-chunks per warp with two sets of (gate, up) boxes of 32 rows x
+      // 32 columns (2 KB, 64-byte swizzle): a set is loaded by TMA, overwritten in place with grad_gate /
+      // grad_up and stored by TMA while the other set is loading or being computed on.  The saved gate/up
+      // values do not depend on the accumulator, so the first two loads go out before the MMAs are waited for.
+      constexpr int kGluBox = 32 * 64;
+      const int glu_col0 = t.n0 + half * 128;
+      uint8_t* ebuf = epi_smem + (warp - 2) * (kPEpiBytes / kEpiWarps);
+      const uint32_t ebar = bar_epi + 16 * (warp - 2);   // + 8 * set
+      auto glu_load = [&](int sub) {   // tmD2 = saved gate_up seen as {I, rows, 2}, box {32, 32}
+        const int set = sub & 1;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(ebar + 8 * set, 2 * kGluBox);
+          tma_load_3d(smem_u32(ebuf + set * 2 * kGluBox), &tmD2, ebar + 8 * set, glu_col0 + 32 * sub, row0, 0);
+          tma_load_3d(smem_u32(ebuf + set * 2 * kGluBox + kGluBox), &tmD2, ebar + 8 * set, glu_col0 + 32 * sub, row0, 1);
+        }
+      };
+      uint8_t* bufG = ebuf;   // staging box of the other epilogues
+      if constexpr (EPI == EPI_GLU_BWD) {
+        staging_free(lane);   // the previous tile's stores out of these boxes have been read
+        if (glu_col0 < p.I) glu_load(0);
+        if (glu_col0 + 32 < p.I) glu_load(1);
+      }
       if (!mbar_wait(bar_tfull, it & 1, abort_flag, ST_WAIT_EPILOGUE)) break;
       __syncwarp();
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-      const int row0 = t.m0 + BM * cta_rank + q * 32;
-      const long long row = static_cast<long long>(row0) + lane;
       const bool have_acc = t.nkb > 0;
-      uint8_t* sbuf = epi_smem + (warp - 2) * kStageOutBytes;
+      uint8_t* sbuf = bufG;   // this warp's staging box
       const int grp = (p.sched == SCHED_GROUPED_K) ? t.g : 0;
       // The accumulator is single-buffered, so it is drained first: this warp's 32 rows x 128 columns are
       // rounded to bf16, packed into 64 registers, and the tensor memory goes back to the MMA warp before any
@@ -576,36 +609,50 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         }
       } else {   // EPI_GLU_BWD: accumulator = grad_inter columns [n0, n0+256), this warp 128 of them
         const int I = p.I;
-        const __nv_bfloat16* gu = reinterpret_cast<const __nv_bfloat16*>(p.aux) + row * (2LL * I);
+        bool live = true;
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = half * 128 + 64 * cc;
-          if (t.n0 + c < I) {
-            uint32_t og[32], ou[32];
+        for (int sub = 0; sub < 4; ++sub) {
+          const int col = glu_col0 + 32 * sub;
+          live = live && col < I;                      // warp-uniform
+          if (!live) continue;
+          const int set = sub & 1;
+          uint8_t* bG = ebuf + set * 2 * kGluBox;
+          uint8_t* bU = bG + kGluBox;
+          if (!mbar_wait(ebar + 8 * set, (epi_phase >> set) & 1u, abort_flag, ST_WAIT_EPILOGUE)) {
+            live = false;
+            continue;
+          }
+          epi_phase ^= 1u << set;
+          uint4 g4[4], u4[4];
 #pragma unroll
-            for (int sub = 0; sub < 2; ++sub) {
-              const int colq = t.n0 + c + 32 * sub;
-              uint4 g4[4], u4[4];
+          for (int v = 0; v < 4; ++v) {              // this lane's row: 64 bytes, 64-byte swizzle
+            const int off = lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4);
+            g4[v] = *reinterpret_cast<const uint4*>(bG + off);
+            u4[v] = *reinterpret_cast<const uint4*>(bU + off);
+          }
+          uint32_t og[16], ou[16];
+          glu_bwd32_packed(acc + 16 * sub, g4, u4, og, ou);
+          if (fp.q_out != nullptr) {   // blocks of the (rows, 2I) grad_gate_up: gate half, then up half
+            mx_quant_store32(og, fp.q_out + row * (2LL * I) + col, fp.q_sf, row, col >> 5, (2 * I) >> 7);
+            mx_quant_store32(ou, fp.q_out + row * (2LL * I) + I + col, fp.q_sf, row, (I + col) >> 5, (2 * I) >> 7);
+          }
 #pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                const int col = colq + v * 8;
-                g4[v] = col < I ? __ldg(reinterpret_cast<const uint4*>(gu + col)) : make_uint4(0u, 0u, 0u, 0u);
-                u4[v] = col < I ? __ldg(reinterpret_cast<const uint4*>(gu + I + col)) : make_uint4(0u, 0u, 0u, 0u);
-              }
-              glu_bwd32_packed(acc + 32 * cc + 16 * sub, g4, u4, og + 16 * sub, ou + 16 * sub);
-              if (fp.q_out != nullptr) {   // blocks of the (rows, 2I) grad_gate_up: gate half, then up half
-                mx_quant_store32(og + 16 * sub, fp.q_out + row * (2LL * I) + colq, fp.q_sf, row, colq >> 5,
-                                 (2 * I) >> 7);
-                mx_quant_store32(ou + 16 * sub, fp.q_out + row * (2LL * I) + I + colq, fp.q_sf, row, (I + colq) >> 5,
-                                 (2 * I) >> 7);
-              }
-            }
+          for (int v = 0; v < 4; ++v) {              // results replace the inputs in place
+            const int off = lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4);
+            *reinterpret_cast<uint4*>(bG + off) = make_uint4(og[4 * v], og[4 * v + 1], og[4 * v + 2], og[4 * v + 3]);
+            *reinterpret_cast<uint4*>(bU + off) = make_uint4(ou[4 * v], ou[4 * v + 1], ou[4 * v + 2], ou[4 * v + 3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tmD, smem_u32(bG), col, row0, 0);   // grad_gate
+            tma_store_3d(&tmD, smem_u32(bU), col, row0, 1);   // grad_up
+            bulk_commit_group();
+          }
+          // once that store has read its boxes they are reloaded with the sub-chunk after the next one
+          if (sub + 2 < 4 && glu_col0 + 32 * (sub + 2) < I) {
             staging_free(lane);
-            stage_row(sbuf, lane, og);
-            store_box(&tmD, sbuf, lane, t.n0 + c, row0, 0);   // grad_gate
-            staging_free(lane);
-            stage_row(sbuf, lane, ou);
-            store_box(&tmD, sbuf, lane, t.n0 + c, row0, 1);   // grad_up
+            glu_load(sub + 2);
           }
         }
       }
@@ -648,7 +695,7 @@ static int launch_fp8_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPSmemBytes);
+    attr_err = cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<EPI>::kSmemBytes);
   });
   if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(max dynamic smem)");
   int pairs = gemm_cta_budget() / 2;
@@ -657,7 +704,7 @@ static int launch_fp8_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(pairs * 2, 1, 1);
   cfg.blockDim = dim3(kPThreads, 1, 1);
-  cfg.dynamicSmemBytes = kPSmemBytes;
+  cfg.dynamicSmemBytes = PairCfg<EPI>::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -728,8 +775,13 @@ static int launch_any(const void* Aq, long long a_rows, const void* Bq, long lon
     const long long groups = (g.sched == SCHED_GROUPED_K) ? g.num_groups : 1;
     rc = make_map(&tmD, g.D, g.N, rows, groups, g.ldd, g.sched == SCHED_GROUPED_K ? g.d_group_stride : rows * g.ldd, 64, 32);
   } else {
-    rc = make_map(&tmD, g.D, g.I, a_rows, 2, 2LL * g.I, g.I, 64, 32);          // gate_up / grad_gate_up halves
-    if (rc == 0 && EPI == EPI_SWIGLU) rc = make_map(&tmD2, g.aux, g.I, a_rows, 1, g.I, a_rows * g.I, 64, 32);
+    if (EPI == EPI_SWIGLU) {
+      rc = make_map(&tmD, g.D, g.I, a_rows, 2, 2LL * g.I, g.I, 64, 32);          // gate and up halves of gate_up
+      if (rc == 0) rc = make_map(&tmD2, g.aux, g.I, a_rows, 1, g.I, a_rows * g.I, 64, 32);
+    } else {   // GLU backward: boxes {32 columns, 32 rows}, 64-byte swizzle, for the in-place epilogue
+      rc = make_map(&tmD, g.D, g.I, a_rows, 2, 2LL * g.I, g.I, 32, 32, 2, 64);   // grad_gate_up halves
+      if (rc == 0) rc = make_map(&tmD2, g.aux, g.I, a_rows, 2, 2LL * g.I, g.I, 32, 32, 2, 64);   // saved gate_up
+    }
   }
   if (rc) return rc;
   return launch_fp8_pair<EPI>(tmA, tmB, tmSFA, tmSFB, tmD, tmD2, fp, max_tiles_1cta > 0 ? (max_tiles_1cta + 3) / 4 : 0,
