@@ -549,18 +549,21 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       // arithmetic or store; acc[16 s + i] = columns (32 s + 2i, 32 s + 2i + 1) of this warp's column half.
       uint32_t acc[64];
 #pragma unroll
-      for (int s4 = 0; s4 < 4; ++s4) {
-        uint32_t r[32];
+      for (int s2 = 0; s2 < 2; ++s2) {   // two tensor-memory loads in flight per wait
+        uint32_t r0[32], r1[32];
         if (have_acc) {
-          tmem_ld32(taddr + 128 * half + 32 * s4, r);
+          tmem_ld32(taddr + 128 * half + 64 * s2, r0);
+          tmem_ld32(taddr + 128 * half + 64 * s2 + 32, r1);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
+          for (int i = 0; i < 32; ++i) r0[i] = r1[i] = 0u;
         }
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          acc[16 * s4 + i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        for (int i = 0; i < 16; ++i) {
+          acc[32 * s2 + i] = pack_bf16x2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+          acc[32 * s2 + 16 + i] = pack_bf16x2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+        }
       }
       tc_fence_before();
       __syncwarp();
