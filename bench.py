@@ -139,7 +139,8 @@ def _make_layer(pkg, w, device, seed, world):
             layer = pkg.ExpertParallelMoELayer(w["H"], w["I"], w["E"], top_k=w["k"],
                                                overlap_chunks=int(os.environ.get("B200MOE_EP_CHUNKS", "1")),
                                                reserved_sms=int(os.environ.get("B200MOE_EP_RESERVED_SMS", "12")),
-                                               transport=os.environ.get("B200MOE_EP_TRANSPORT", "p2p"))
+                                               transport=os.environ.get("B200MOE_EP_TRANSPORT", "p2p"),
+                                               exchange=os.environ.get("B200MOE_EP_EXCHANGE", "push"))
         else:
             layer = pkg.MoELayer(w["H"], w["I"], w["E"], top_k=w["k"], precision=w["precision"])
     return layer.to(torch.bfloat16)

@@ -155,6 +155,15 @@ int b200moe_expert_linear(const void* a, const void* w, const int32_t* tile_expe
 int b200moe_expert_linear_t(const void* a, const void* w, const int32_t* tile_expert, const int32_t* poffs,
                             int64_t rows_cap, int E, int64_t K, int64_t N, void* out, int32_t* status,
                             b200moe_stream_t stream);
+/* Fused GEMM + dispatch over peer memory: out row r = a[r] * W[e(r)] as b200moe_expert_linear (w_kn = 0,
+ * W (E,N,K)) or b200moe_expert_linear_t (w_kn = 1, W (E,K,N)) computes it, but the row is not stored locally:
+ * the epilogue sends it to peer_base[row_rank[r]] + row_slot[r] * N elements with one bulk copy per 128-byte
+ * piece, tile by tile while the GEMM runs (rows with row_rank < 0 are dropped).  peer_base is a DEVICE array of
+ * W buffer addresses (this GPU's own among them); N % 64 == 0.  No reference counterpart. */
+int b200moe_expert_linear_push(const void* a, const void* w, int w_kn, const int32_t* tile_expert, const int32_t* poffs,
+                               int64_t rows_cap, int E, int64_t N, int64_t K, const int32_t* row_rank,
+                               const int32_t* row_slot, const int64_t* peer_base, int32_t* status,
+                               b200moe_stream_t stream);
 /* Replaces the down GEMM (kernels/sm75/moe.py:592, :770): eo (rows,H) = inter * W_d[e]^T. */
 int b200moe_expert_down(const void* inter, const void* down_proj, const int32_t* tile_expert,
                         const int32_t* poffs, int64_t rows_cap, int E, int64_t H, int64_t I,
@@ -267,11 +276,13 @@ int b200moe_ep_plan(const int32_t* counts_all, int W, int rank, int E, int32_t* 
  * source's routing tables (idx_peers int64 (T,k), spos_peers = slot_pos int32 (T,k), offs_peers int32 (E+1)) and,
  * for each expert that lives on this rank, writes x_peers[s][t] to row
  * src_base[s][e_local] + slot_pos - offs[e]; the token row is read from the peer ONCE however many of its
- * experts live here.  Pad rows are zeroed.  T is the token count of every rank. */
+ * experts live here.  Pad rows are zeroed.  T is the token count of every rank.  row_rank / row_slot (nullable,
+ * both or none): for every row the home rank and the slot t*k+j it came from (-1 / 0 for pad rows), i.e. where
+ * b200moe_expert_linear_push sends that row's result. */
 int b200moe_ep_gather_pull(const void* const* x_peers, const void* const* idx_peers, const void* const* spos_peers,
                            const void* const* offs_peers, const int32_t* counts_l, const int32_t* poffs_l,
                            const int32_t* src_base, int W, int rank, int E, int64_t T, int k, int64_t H, void* x_s,
-                           b200moe_stream_t stream);
+                           int32_t* row_rank, int32_t* row_slot, b200moe_stream_t stream);
 /* home side: out[t] = sum_j w[t,j] * rows_peers[owner][dest_base[e] + slot_pos[s] - offs[e]] (w NULL = 1),
  * summed in slot order; the rows arrive by bulk copies into a shared-memory ring (one CTA per SM, on at most
  * the SMs b200moe_set_exchange_sms allows).  When gw_peers / grad_w are given, grad_w[s] is fetched from the
@@ -281,12 +292,18 @@ int b200moe_ep_combine_pull(const void* const* rows_peers, const float* w, const
                             int64_t T, int k, int64_t H, void* out, const void* const* gw_peers, float* grad_w,
                             int32_t* status, b200moe_stream_t stream);
 /* owner side, backward, same traversal: grad_eo[row] = w_peers[s][t,j] * go_peers[s][t] (grad_out read once per
- * token and owner); gw_rows[row] = <go, eo[row]>; pad rows zero. */
+ * token and owner); gw_rows[row] = <go, eo[row]> (eo and gw_rows both NULL: no dot products); pad rows zero. */
 int b200moe_ep_combine_bwd_pull(const void* const* go_peers, const void* const* w_peers,
                                 const void* const* idx_peers, const void* const* spos_peers,
                                 const void* const* offs_peers, const void* eo, const int32_t* counts_l,
                                 const int32_t* poffs_l, const int32_t* src_base, int W, int rank, int E, int64_t T,
                                 int k, int64_t H, void* grad_eo, float* gw_rows, b200moe_stream_t stream);
+
+/* out[t*k+j] = <grad_out[t], rows[t*k+j]> (fp32): the gradient of the routing weights at the home rank when the
+ * expert outputs of its tokens were pushed to it in slot order.  No reference counterpart as a kernel (the
+ * reference computes this inside _combine_bwd_kernel, kernels/sm75/moe.py:688-701). */
+int b200moe_slot_dots(const void* grad_out, const void* rows, int64_t T, int k, int64_t H, float* out,
+                      b200moe_stream_t stream);
 
 #ifdef __cplusplus
 }

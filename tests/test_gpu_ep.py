@@ -31,9 +31,12 @@ def _worker(rank, world, port, cfg, transport, q):
         inp = O.make_inputs(T, H, E, I, k, seed=41, bias_std=0.01, dtype=torch.bfloat16)
         Tl, El = T // world, E // world
         sl = slice(rank * Tl, (rank + 1) * Tl)
-        transport, _, sms = transport.partition("+")   # "p2p+24": the overlapped backward with 24 exchange SMs
-        layer = pkg.ExpertParallelMoELayer(H, I, E, top_k=k, transport=transport,
-                                           reserved_sms=int(sms or 0)).to(dev).to(torch.bfloat16)
+        # "p2p" = push exchange, "p2p-pull" = pull exchange, "p2p-pull+24" = pull with the last backward pull
+        # overlapped on 24 SMs
+        transport, _, sms = transport.partition("+")
+        transport, _, exch = transport.partition("-")
+        layer = pkg.ExpertParallelMoELayer(H, I, E, top_k=k, transport=transport, reserved_sms=int(sms or 0),
+                                           exchange=exch or "push").to(dev).to(torch.bfloat16)
         with torch.no_grad():
             layer.gate.weight.copy_(inp["gate_weight"])
             layer.gate_up_proj.copy_(inp["gate_up"][rank * El:(rank + 1) * El])
@@ -53,7 +56,7 @@ def _worker(rank, world, port, cfg, transport, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport", ["nccl", "p2p", "p2p+24"])
+@pytest.mark.parametrize("transport", ["nccl", "p2p", "p2p-pull", "p2p-pull+24"])
 @pytest.mark.parametrize("cfg", [(2048, 512, 16, 256, 4), (1024, 256, 64, 128, 8)])
 def test_expert_parallel_equals_single_gpu(pkg, cfg, transport):
     if torch.cuda.device_count() < 2:

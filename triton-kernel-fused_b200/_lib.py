@@ -69,7 +69,10 @@ _SIGNATURES = {
     "b200moe_mxfp8_gather_quant": (c_int, [c_void_p] * 3 + [c_int, c_int64, c_int64] + [c_void_p] * 4),
     "b200moe_mxfp8_expert_wgrad": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
     "b200moe_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 5 + [c_void_p]),
-    "b200moe_ep_gather_pull": (c_int, [c_void_p] * 7 + [c_int, c_int, c_int, c_int64, c_int, c_int64] + [c_void_p] * 2),
+    "b200moe_ep_gather_pull": (c_int, [c_void_p] * 7 + [c_int, c_int, c_int, c_int64, c_int, c_int64] + [c_void_p] * 4),
+    "b200moe_slot_dots": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_void_p, c_void_p]),
+    "b200moe_expert_linear_push": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64] +
+                                   [c_void_p] * 5),
     "b200moe_ep_combine_pull": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int64, c_int, c_int64] + [c_void_p] * 5),
     "b200moe_ep_combine_bwd_pull": (c_int, [c_void_p] * 9 + [c_int, c_int, c_int, c_int64, c_int, c_int64] + [c_void_p] * 3),
     "b200moe_combine": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64, c_void_p, c_void_p]),

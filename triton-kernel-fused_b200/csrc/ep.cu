@@ -115,7 +115,7 @@ ep_gather_pull_kernel(const __grid_constant__ PeerPtrs x_peers, const __grid_con
                       const __grid_constant__ PeerPtrs spos_peers, const __grid_constant__ PeerPtrs offs_peers,
                       const int* __restrict__ counts_l, const int* __restrict__ poffs_l,
                       const int* __restrict__ src_base, int W, int rank, int El, long long T, int k, int vec_per_row,
-                      uint4* __restrict__ x_s) {
+                      uint4* __restrict__ x_s, int* __restrict__ row_rank, int* __restrict__ row_slot) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
@@ -128,6 +128,10 @@ ep_gather_pull_kernel(const __grid_constant__ PeerPtrs x_peers, const __grid_con
                                               reinterpret_cast<const int*>(offs_peers.p[s]), src_base, s, t, k, rank,
                                               El, lane, row);
     if (mask == 0u) continue;
+    if (row_rank != nullptr && ((mask >> lane) & 1u)) {   // where the result rows of this row go back to
+      row_rank[row] = s;
+      row_slot[row] = static_cast<int>(t * k + lane);
+    }
     const uint4* srow = reinterpret_cast<const uint4*>(x_peers.p[s]) + t * vec_per_row;
     // peer loads have microseconds of latency: keep 8 of them in flight per lane
     for (int c0 = lane; c0 < vec_per_row; c0 += 32 * 8) {
@@ -147,6 +151,10 @@ ep_gather_pull_kernel(const __grid_constant__ PeerPtrs x_peers, const __grid_con
   for_each_pad_row(counts_l, poffs_l, El, warp0, nwarps, [&](long long r) {
     uint4* dst = x_s + r * vec_per_row;
     for (int c = lane; c < vec_per_row; c += 32) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+    if (row_rank != nullptr && lane == 0) {
+      row_rank[r] = -1;
+      row_slot[r] = 0;
+    }
   });
 }
 
@@ -342,7 +350,7 @@ ep_combine_bwd_pull_kernel(const __grid_constant__ PeerPtrs go_peers, const __gr
       unsigned m = mask;
       int j = __ffs(m) - 1;
       int r = __shfl_sync(0xffffffffu, row, j);
-      {
+      if (eo != nullptr) {
         const uint4* e = eo + static_cast<long long>(r) * vec_per_row;
 #pragma unroll
         for (int i = 0; i < kB; ++i)
@@ -353,7 +361,7 @@ ep_combine_bwd_pull_kernel(const __grid_constant__ PeerPtrs go_peers, const __gr
         // the next slot's eo row is requested before this slot's arithmetic
         const int jn = m != 0u ? __ffs(m) - 1 : j;
         const int rn = __shfl_sync(0xffffffffu, row, jn);
-        if (m != 0u) {
+        if (m != 0u && eo != nullptr) {
           const uint4* e = eo + static_cast<long long>(rn) * vec_per_row;
 #pragma unroll
           for (int i = 0; i < kB; ++i)
@@ -366,8 +374,10 @@ ep_combine_bwd_pull_kernel(const __grid_constant__ PeerPtrs go_peers, const __gr
         for (int i = 0; i < kB; ++i)
           if (c0 + 32 * i < vec_per_row) {
             const float2 g0 = unpack_bf16x2(gv[i].x), g1 = unpack_bf16x2(gv[i].y), g2 = unpack_bf16x2(gv[i].z), g3 = unpack_bf16x2(gv[i].w);
-            const float2 e0 = unpack_bf16x2(ev[i].x), e1 = unpack_bf16x2(ev[i].y), e2 = unpack_bf16x2(ev[i].z), e3 = unpack_bf16x2(ev[i].w);
-            dot += g0.x * e0.x + g0.y * e0.y + g1.x * e1.x + g1.y * e1.y + g2.x * e2.x + g2.y * e2.y + g3.x * e3.x + g3.y * e3.y;
+            if (eo != nullptr) {
+              const float2 e0 = unpack_bf16x2(ev[i].x), e1 = unpack_bf16x2(ev[i].y), e2 = unpack_bf16x2(ev[i].z), e3 = unpack_bf16x2(ev[i].w);
+              dot += g0.x * e0.x + g0.y * e0.y + g1.x * e1.x + g1.y * e1.y + g2.x * e2.x + g2.y * e2.y + g3.x * e3.x + g3.y * e3.y;
+            }
             uint4 o;
             o.x = pack_bf16x2(g0.x * wt, g0.y * wt);
             o.y = pack_bf16x2(g1.x * wt, g1.y * wt);
@@ -384,13 +394,45 @@ ep_combine_bwd_pull_kernel(const __grid_constant__ PeerPtrs go_peers, const __gr
         r = rn;
       }
     }
-    if ((mask >> lane) & 1u) gw_rows[row] = dot_lane;
+    if (gw_rows != nullptr && ((mask >> lane) & 1u)) gw_rows[row] = dot_lane;
   }
   for_each_pad_row(counts_l, poffs_l, El, warp0, nwarps, [&](long long r) {
     uint4* dst = grad_eo + r * vec_per_row;
     for (int c = lane; c < vec_per_row; c += 32) dst[c] = make_uint4(0u, 0u, 0u, 0u);
-    if (lane == 0) gw_rows[r] = 0.0f;
+    if (gw_rows != nullptr && lane == 0) gw_rows[r] = 0.0f;
   });
+}
+
+// out[s] = <go[s / k], rows[s]> in fp32, one warp per slot (the routing-weight gradient where the expert
+// outputs of a token sit in slot order at its home rank)
+__global__ void __launch_bounds__(256)
+slot_dots_kernel(const uint4* __restrict__ go, const uint4* __restrict__ rows, long long slots, int k, int vec_per_row,
+                 float* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long s = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; s < slots; s += nwarps) {
+    const uint4* g = go + (s / k) * vec_per_row;
+    const uint4* e = rows + s * vec_per_row;
+    float dot = 0.0f;
+    for (int c0 = lane; c0 < vec_per_row; c0 += 32 * 4) {
+      uint4 gv[4], ev[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bool in = c0 + 32 * i < vec_per_row;
+        gv[i] = in ? g[c0 + 32 * i] : make_uint4(0u, 0u, 0u, 0u);
+        ev[i] = in ? e[c0 + 32 * i] : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 g0 = unpack_bf16x2(gv[i].x), g1 = unpack_bf16x2(gv[i].y), g2 = unpack_bf16x2(gv[i].z), g3 = unpack_bf16x2(gv[i].w);
+        const float2 e0 = unpack_bf16x2(ev[i].x), e1 = unpack_bf16x2(ev[i].y), e2 = unpack_bf16x2(ev[i].z), e3 = unpack_bf16x2(ev[i].w);
+        dot += g0.x * e0.x + g0.y * e0.y + g1.x * e1.x + g1.y * e1.y + g2.x * e2.x + g2.y * e2.y + g3.x * e3.x + g3.y * e3.y;
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+    if (lane == 0) out[s] = dot;
+  }
 }
 
 static int load_peers(PeerPtrs* out, const void* const* host_ptrs, int W, const char* who) {
@@ -444,8 +486,10 @@ int b200moe_ep_plan(const int32_t* counts_all, int W, int rank, int E, int32_t* 
 int b200moe_ep_gather_pull(const void* const* x_peers, const void* const* idx_peers, const void* const* spos_peers,
                            const void* const* offs_peers, const int32_t* counts_l, const int32_t* poffs_l,
                            const int32_t* src_base, int W, int rank, int E, int64_t T, int k, int64_t H, void* x_s,
-                           b200moe_stream_t stream) {
+                           int32_t* row_rank, int32_t* row_slot, b200moe_stream_t stream) {
   B200_CHECK_ARG(counts_l && poffs_l && src_base && x_s, B200MOE_E_NULL, "ep_gather_pull: null pointer");
+  B200_CHECK_ARG((row_rank == nullptr) == (row_slot == nullptr), B200MOE_E_NULL,
+                 "ep_gather_pull: row_rank and row_slot go together");
   CHECK_WORLD("ep_gather_pull");
   B200_CHECK_ARG(H > 0 && H % 8 == 0 && k >= 1 && k <= B200MOE_MAX_TOPK && E % W == 0 && T >= 0, B200MOE_E_BAD_SHAPE,
                  "ep_gather_pull: H = %lld, k = %d, T = %lld", (long long)H, k, (long long)T);
@@ -455,7 +499,7 @@ int b200moe_ep_gather_pull(const void* const* x_peers, const void* const* idx_pe
   LOAD_PEERS(fp, offs_peers, "ep_gather_pull(offs)");
   ep_gather_pull_kernel<<<grid_rows((T * W + 7) / 8, 8), 256, 0, (cudaStream_t)stream>>>(
       xp, ip, sp, fp, counts_l, poffs_l, src_base, W, rank, E / W, T, k, static_cast<int>(H / 8),
-      reinterpret_cast<uint4*>(x_s));
+      reinterpret_cast<uint4*>(x_s), row_rank, row_slot);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -508,8 +552,9 @@ int b200moe_ep_combine_bwd_pull(const void* const* go_peers, const void* const* 
                                 const void* const* offs_peers, const void* eo, const int32_t* counts_l,
                                 const int32_t* poffs_l, const int32_t* src_base, int W, int rank, int E, int64_t T,
                                 int k, int64_t H, void* grad_eo, float* gw_rows, b200moe_stream_t stream) {
-  B200_CHECK_ARG(eo && counts_l && poffs_l && src_base && grad_eo && gw_rows, B200MOE_E_NULL,
-                 "ep_combine_bwd_pull: null pointer");
+  B200_CHECK_ARG(counts_l && poffs_l && src_base && grad_eo, B200MOE_E_NULL, "ep_combine_bwd_pull: null pointer");
+  B200_CHECK_ARG((eo == nullptr) == (gw_rows == nullptr), B200MOE_E_NULL,
+                 "ep_combine_bwd_pull: eo and gw_rows go together (both NULL: no row dot products)");
   CHECK_WORLD("ep_combine_bwd_pull");
   B200_CHECK_ARG(H > 0 && H % 8 == 0 && k >= 1 && k <= B200MOE_MAX_TOPK && E % W == 0 && T >= 0, B200MOE_E_BAD_SHAPE,
                  "ep_combine_bwd_pull: H = %lld, k = %d, T = %lld", (long long)H, k, (long long)T);
@@ -521,6 +566,18 @@ int b200moe_ep_combine_bwd_pull(const void* const* go_peers, const void* const* 
   ep_combine_bwd_pull_kernel<<<grid_rows((T * W + 7) / 8, 8), 256, 0, (cudaStream_t)stream>>>(
       gp, wp, ip, sp, fp, reinterpret_cast<const uint4*>(eo), counts_l, poffs_l, src_base, W, rank, E / W, T, k,
       static_cast<int>(H / 8), reinterpret_cast<uint4*>(grad_eo), gw_rows);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_slot_dots(const void* grad_out, const void* rows, int64_t T, int k, int64_t H, float* out,
+                      b200moe_stream_t stream) {
+  B200_CHECK_ARG(grad_out && rows && out, B200MOE_E_NULL, "slot_dots: null pointer");
+  B200_CHECK_ARG(H > 0 && H % 8 == 0 && k >= 1 && T >= 0, B200MOE_E_BAD_SHAPE, "slot_dots: H = %lld, k = %d", (long long)H, k);
+  B200_CHECK_ARG(aligned16(grad_out) && aligned16(rows), B200MOE_E_ALIGN, "slot_dots: pointers must be 16-byte aligned");
+  if (T == 0) return 0;
+  slot_dots_kernel<<<grid_rows((T * k + 7) / 8, 8), 256, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const uint4*>(grad_out), reinterpret_cast<const uint4*>(rows), T * k, k, static_cast<int>(H / 8), out);
   B200_CUDA(cudaGetLastError());
   return 0;
 }

@@ -297,6 +297,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int grp = (p.sched == SCHED_GROUPED_K) ? t.g : 0;
         if constexpr (EPI == EPI_STORE) {
           constexpr int W = BN / 2;
+          // push mode: this lane's output row goes to a slot of another GPU's (or this GPU's) receive buffer
+          uint8_t* push_dst = nullptr;
+          if (p.push_rank != nullptr) {
+            const int rk = p.push_rank[row];
+            if (rk >= 0)
+              push_dst = reinterpret_cast<uint8_t*>(p.push_base[rk]) + static_cast<long long>(p.push_slot[row]) * p.N * 2;
+          }
 #pragma unroll 1
           for (int c = half * W; c < (half + 1) * W; c += 64) {
             if (t.n0 + c >= p.N) break;
@@ -315,9 +322,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               for (int i = 0; i < 16; ++i)
                 pk[16 * sub + i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
             }
-            staging_free(lane);
-            stage_row(sbuf, lane, pk);
-            store_box(&tmD, sbuf, lane, t.n0 + c, row0, grp);
+            if (p.push_rank != nullptr) {
+              // each lane stages its own 128-byte row piece (unswizzled) and sends it with one bulk copy
+              bulk_wait_read_all();   // this lane's previous copy has read the piece
+              uint8_t* mine = sbuf + lane * 128;
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4*>(mine + 16 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+              fence_proxy_async_smem();
+              if (push_dst != nullptr) {
+                const int left = (p.N - (t.n0 + c)) * 2;
+                bulk_store_1d(push_dst + static_cast<long long>(t.n0 + c) * 2, smem_u32(mine), left < 128 ? left : 128);
+              }
+              bulk_commit_group();
+            } else {
+              staging_free(lane);
+              stage_row(sbuf, lane, pk);
+              store_box(&tmD, sbuf, lane, t.n0 + c, row0, grp);
+            }
           }
         } else if constexpr (EPI == EPI_SWIGLU) {
           // accumulator columns [0,BN/2) = gate, [BN/2,BN) = up for I-columns [n0, n0+BN/2)
@@ -533,7 +555,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
     }
     if constexpr (TMA_EPI) {
-      if (lane == 0) bulk_wait_all();   // every TMA store of this warp has completed
+      if (lane == 0 || p.push_rank != nullptr) bulk_wait_all();   // every bulk store of this warp (push mode: of this lane) has completed
     }
   }
 
@@ -639,7 +661,7 @@ static int dispatch_bn(int bn, const Operand& A, const Operand& B, const Operand
   if (rc) return rc;
   tmD = tmA;
   tmD2 = tmA;
-  if (bn == 256 && EPI != EPI_STORE_F32) {
+  if (bn == 256 && EPI != EPI_STORE_F32 && p.push_rank == nullptr) {
     if (d1 == nullptr) {
       set_error("internal: output description missing");
       return B200MOE_E_UNSUPPORTED;
@@ -795,6 +817,24 @@ int b200moe_expert_linear_t(const void* a, const void* w, const int32_t* tile_ex
   p.tile_expert = tile_expert; p.poffs = poffs; p.D = out; p.ldd = N; p.status = status;
   Operand d{out, 0, rows_cap, N, N, 1, rows_cap * N};
   return dispatch_bn<EPI_STORE>(pick_bn(N) == 64 ? 128 : pick_bn(N), oa, ob, &d, nullptr, p, 0, (cudaStream_t)stream);
+}
+
+int b200moe_expert_linear_push(const void* a, const void* w, int w_kn, const int32_t* tile_expert, const int32_t* poffs,
+                               int64_t rows_cap, int E, int64_t N, int64_t K, const int32_t* row_rank,
+                               const int32_t* row_slot, const int64_t* peer_base, int32_t* status,
+                               b200moe_stream_t stream) {
+  int rc = check_grouped("expert_linear_push", a, w, peer_base, tile_expert, poffs, rows_cap, E, N, K);
+  if (rc) return rc;
+  B200_CHECK_ARG(tile_expert && row_rank && row_slot && peer_base, B200MOE_E_NULL, "expert_linear_push: null pointer");
+  B200_CHECK_ARG(N % 64 == 0, B200MOE_E_BAD_SHAPE, "expert_linear_push: N = %lld must be a multiple of 64", (long long)N);
+  Operand oa{a, 0, rows_cap, K, K, 1, rows_cap * K};
+  Operand ob_nk{w, 0, N, K, K, E, N * K};   // W (E, N, K): rows = output columns
+  Operand ob_kn{w, 1, N, K, N, E, K * N};   // W[e] stored (K, N): MN-major
+  GemmParams p{};
+  p.sched = SCHED_GROUPED_M; p.b_mn = w_kn ? 1 : 0; p.N = (int)N; p.K = (int)K; p.num_groups = E;
+  p.tile_expert = tile_expert; p.poffs = poffs; p.D = nullptr; p.ldd = N; p.status = status;
+  p.push_rank = row_rank; p.push_slot = row_slot; p.push_base = reinterpret_cast<const long long*>(peer_base);
+  return dispatch_bn<EPI_STORE>(256, oa, w_kn ? ob_kn : ob_nk, nullptr, nullptr, p, 0, (cudaStream_t)stream);
 }
 
 int b200moe_expert_down(const void* inter, const void* down_proj, const int32_t* tile_expert, const int32_t* poffs,

@@ -34,6 +34,11 @@ struct GemmParams {
   void* aux;                 // SwiGLU: inter (rows, I); GLU_BWD: saved gate_up (rows, 2I)
   int I;
   int* status;
+  // optional, EPI_STORE with 256-wide tiles: output row r is not stored to D but sent to
+  // push_base[push_rank[r]] + push_slot[r] * N elements (a peer GPU's buffer); rows with push_rank < 0 are dropped
+  const int* push_rank;
+  const int* push_slot;
+  const long long* push_base;
 };
 
 struct Tile {

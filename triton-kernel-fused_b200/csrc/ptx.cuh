@@ -72,6 +72,13 @@ __device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* tm, int c0
 __device__ __forceinline__ void prefetch_l2(const void* p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<uint64_t>(p)));
 }
+// untiled bulk copy this CTA's shared memory -> global (both 16-byte aligned, size a multiple of 16 bytes),
+// tracked by the issuing thread's bulk groups
+__device__ __forceinline__ void bulk_store_1d(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(reinterpret_cast<uint64_t>(dst)), "r"(src), "r"(bytes)
+               : "memory");
+}
 // untiled bulk copy global -> this CTA's shared memory (both 16-byte aligned, size a multiple of 16 bytes);
 // completion is counted in bytes on `bar`
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {

@@ -4,6 +4,11 @@ gathering them into their padded expert layout; home ranks PULL expert outputs w
 Buffers that peers read live in one symmetric allocation per layer (torch symmetric memory gives
 the peer mappings and the cross-rank barrier); the kernels are in csrc/ep.cu.
 
+Two ways to bring results home: `exchange="push"` (default) fuses the transfer into the producing GEMM -- the
+epilogue of the down projection (forward) and of the gate/up dgrad (backward) sends every output row to its
+slot of the home rank's receive buffer, tile by tile while the GEMM runs, and the home rank combines locally;
+`exchange="pull"` keeps the rows on the owner and lets the home ranks pull them while combining.
+
 Per step and direction there is one tiny NCCL all-gather (the (W,E) count matrix, which also orders
 the phases), one host read of that matrix (to size the local buffers) and two device-side barriers.
 Constraint: one forward/backward in flight per workspace, because the symmetric buffers are reused.
@@ -38,6 +43,16 @@ def _combine_bwd_pull(*a):
     L.check(L.lib().b200moe_ep_combine_bwd_pull(*a))
 
 
+@ops._op("expert_linear_push", 1)
+def _linear_push(*a):
+    L.check(L.lib().b200moe_expert_linear_push(*a))
+
+
+@ops._op("slot_dots", 1)
+def _slot_dots(*a):
+    L.check(L.lib().b200moe_slot_dots(*a))
+
+
 @ops._op("ep_barrier", 0)
 def _barrier(ws):
     ws.handle.barrier(0)
@@ -51,11 +66,14 @@ class SymmetricWorkspace:
     """One symmetric allocation carved into the buffers peers read.  Sized for the worst case
     (every routed row of every rank lands on one rank), so it is allocated once."""
 
-    def __init__(self, T, H, k, E, group, device, overlap_sms=0):
+    def __init__(self, T, H, k, E, group, device, overlap_sms=0, exchange="push"):
         """overlap_sms > 0: in the backward pass the last pull (grad_hidden) runs on that many SMs beside the
         weight-gradient GEMMs, which leave them free and run on a high-priority stream of their own."""
         import torch.distributed._symmetric_memory as symm
-        self.overlap_sms = int(overlap_sms)
+        if exchange not in ("push", "pull"):
+            raise ValueError("exchange must be 'push' or 'pull'")
+        self.exchange = exchange
+        self.overlap_sms = int(overlap_sms) if exchange == "pull" else 0
         self.gemm_stream = torch.cuda.Stream(device=device, priority=-1) if self.overlap_sms > 0 else None
         self.group = group
         self.W = dist.get_world_size(group)
@@ -63,8 +81,11 @@ class SymmetricWorkspace:
         self.T, self.H, self.k, self.E = T, H, k, E
         M = T * k
         self.cap_w = L.padded_rows_cap(self.W * M, E // self.W)
-        fields = [("x", T * H * 2), ("go", T * H * 2), ("w", M * 4), ("idx", M * 8), ("spos", M * 4), ("offs", (E + 1) * 4),
-                  ("eo", self.cap_w * H * 2), ("gxs", self.cap_w * H * 2), ("gw", self.cap_w * 4)]
+        fields = [("x", T * H * 2), ("go", T * H * 2), ("w", M * 4), ("idx", M * 8), ("spos", M * 4), ("offs", (E + 1) * 4)]
+        if exchange == "pull":     # owners keep their result rows; sized for every routed row landing on one rank
+            fields += [("eo", self.cap_w * H * 2), ("gxs", self.cap_w * H * 2), ("gw", self.cap_w * 4)]
+        else:                      # home ranks receive the result rows of their own slots
+            fields += [("recv", M * H * 2), ("recvg", M * H * 2)]
         self.offsets, total = {}, 0
         for name, nbytes in fields:
             self.offsets[name] = total
@@ -80,13 +101,49 @@ class SymmetricWorkspace:
         self.idx = v("idx", M, torch.int64).view(T, k)
         self.spos = v("spos", M, torch.int32)
         self.offs = v("offs", E + 1, torch.int32)
-        self.eo = v("eo", self.cap_w * H, torch.bfloat16).view(self.cap_w, H)
-        self.gxs = v("gxs", self.cap_w * H, torch.bfloat16).view(self.cap_w, H)
-        self.gw = v("gw", self.cap_w, torch.float32)
+        if exchange == "pull":
+            self.eo = v("eo", self.cap_w * H, torch.bfloat16).view(self.cap_w, H)
+            self.gxs = v("gxs", self.cap_w * H, torch.bfloat16).view(self.cap_w, H)
+            self.gw = v("gw", self.cap_w, torch.float32)
+        else:
+            self.recv = v("recv", M * H, torch.bfloat16).view(M, H)
+            self.recvg = v("recvg", M * H, torch.bfloat16).view(M, H)
+            # device arrays of the peers' receive-buffer addresses, read by the pushing GEMM epilogues
+            self.recv_base = torch.tensor([b + self.offsets["recv"] for b in base], dtype=torch.int64, device=device)
+            self.recvg_base = torch.tensor([b + self.offsets["recvg"] for b in base], dtype=torch.int64, device=device)
+            self.ident = torch.arange(M, dtype=torch.int32, device=device)   # slot -> row of the receive buffers
         self.generation = 0
 
     def barrier(self):
         _barrier(self)
+
+
+def _backward_push(ctx, grad_out, grad_eo):
+    """Backward of the push exchange (the barrier that put grad_out / w in place has been issued)."""
+    idx, x_s, gate_up, inter, w32, gate_up_local, down_local = ctx.saved_tensors
+    ws, perm_l = ctx.ws, ctx.perm_l
+    _, src_base, row_rank, row_slot = ctx.tables
+    W, E, T, H, k = ws.W, ws.E, ws.T, ws.H, ws.k
+    El, cap_l = E // W, perm_l.cap
+    dev = x_s.device
+    st = L.stream_of(x_s)
+    status = L.ptr(L.status_word(dev))
+    # the expert outputs of this rank's tokens are still in its receive buffer: grad of the routing weights
+    grad_w = torch.empty(T, k, dtype=torch.float32, device=dev)
+    _slot_dots(L.ptr(ws.go), L.ptr(ws.recv), T, k, H, L.ptr(grad_w), st)
+    _combine_bwd_pull(ws.peers["go"], ws.peers["w"], ws.peers["idx"], ws.peers["spos"], ws.peers["offs"], None,
+                      L.ptr(perm_l.counts), L.ptr(perm_l.poffs), L.ptr(src_base), W, ws.rank, E, T, k, H,
+                      L.ptr(grad_eo), None, st)
+    grad_gu = ops.expert_down_dgrad_glu(grad_eo, down_local, gate_up, perm_l)
+    # gate/up dgrad whose epilogue sends each grad_x row to its slot at the token's home rank
+    twoI = gate_up_local.shape[1]
+    _linear_push(L.ptr(grad_gu), L.ptr(gate_up_local), 1, L.ptr(perm_l.tile_expert), L.ptr(perm_l.poffs), cap_l, El, H,
+                 twoI, L.ptr(row_rank), L.ptr(row_slot), L.ptr(ws.recvg_base), status, st)
+    grad_down = ops.expert_wgrad(grad_eo, inter, perm_l)
+    grad_gate_up = ops.expert_wgrad(grad_gu, x_s, perm_l)
+    ws.barrier()                                                    # every owner's grad_x rows have arrived
+    grad_hidden = ops.combine_raw(ws.recvg, None, ws.ident, T, k)
+    return grad_hidden, None, grad_w.to(ctx.wt_dtype), grad_gate_up, grad_down, None
 
 
 class _ExpertParallelP2P(torch.autograd.Function):
@@ -125,19 +182,31 @@ class _ExpertParallelP2P(torch.autograd.Function):
         _plan(L.ptr(counts_all), W, rank, E, L.ptr(poffs_l), L.ptr(counts_l),
                                     L.ptr(tile_expert_l), L.ptr(src_base), L.ptr(dest_base), st)
         x_s = torch.empty(cap_l, H, dtype=torch.bfloat16, device=dev)
+        push = ws.exchange == "push"
+        row_rank = torch.empty(cap_l, **i32) if push else None
+        row_slot = torch.empty(cap_l, **i32) if push else None
         _gather_pull(ws.peers["x"], ws.peers["idx"], ws.peers["spos"], ws.peers["offs"], L.ptr(counts_l),
-                     L.ptr(poffs_l), L.ptr(src_base), W, rank, E, T, k, H, L.ptr(x_s), st)
+                     L.ptr(poffs_l), L.ptr(src_base), W, rank, E, T, k, H, L.ptr(x_s), L.ptr(row_rank),
+                     L.ptr(row_slot), st)
         perm_l = ops.Permutation(R, 1, El, cap_l, counts_l, None, poffs_l, None, None, tile_expert_l, None, None)
         gate_up, inter = ops.expert_gate_up_swiglu(x_s, gate_up_local, perm_l)
-        ops.expert_down(inter, down_local, perm_l, out=ws.eo[:cap_l])
-        ws.barrier()                                                # every owner's eo is complete
-        out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
-        _combine_pull(ws.peers["eo"], L.ptr(w32), L.ptr(idx), L.ptr(perm.slot_pos),
-                                            L.ptr(perm.offs), L.ptr(dest_base), W, E, T, k, H, L.ptr(out), None, None,
-                                            L.ptr(L.status_word(dev)), st)
+        status = L.ptr(L.status_word(dev))
+        if push:
+            # down projection whose epilogue sends each output row to its slot at the token's home rank
+            I = down_local.shape[2]
+            _linear_push(L.ptr(inter), L.ptr(down_local), 0, L.ptr(tile_expert_l), L.ptr(poffs_l), cap_l, El, H, I,
+                         L.ptr(row_rank), L.ptr(row_slot), L.ptr(ws.recv_base), status, st)
+            ws.barrier()                                            # every owner's rows have arrived
+            out = ops.combine_raw(ws.recv, w32, ws.ident, T, k)
+        else:
+            ops.expert_down(inter, down_local, perm_l, out=ws.eo[:cap_l])
+            ws.barrier()                                            # every owner's eo is complete
+            out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+            _combine_pull(ws.peers["eo"], L.ptr(w32), L.ptr(idx), L.ptr(perm.slot_pos),
+                          L.ptr(perm.offs), L.ptr(dest_base), W, E, T, k, H, L.ptr(out), None, None, status, st)
         ws.generation += 1
         ctx.ws, ctx.perm, ctx.perm_l, ctx.gen = ws, perm, perm_l, ws.generation
-        ctx.tables = (dest_base, src_base)
+        ctx.tables = (dest_base, src_base, row_rank, row_slot)
         ctx.wt_dtype = wt.dtype
         ctx.save_for_backward(idx, x_s, gate_up, inter, w32, gate_up_local, down_local)
         return out
@@ -146,7 +215,7 @@ class _ExpertParallelP2P(torch.autograd.Function):
     def backward(ctx, grad_out):
         idx, x_s, gate_up, inter, w32, gate_up_local, down_local = ctx.saved_tensors
         ws, perm, perm_l = ctx.ws, ctx.perm, ctx.perm_l
-        dest_base, src_base = ctx.tables
+        dest_base, src_base, row_rank, row_slot = ctx.tables
         if ws.generation != ctx.gen:
             raise RuntimeError("the symmetric workspace was reused by another forward before this backward ran; "
                                "use one workspace per forward in flight")
@@ -159,6 +228,8 @@ class _ExpertParallelP2P(torch.autograd.Function):
         ws.w.copy_(w32)
         ws.barrier()                                                # every home rank's grad_out / w are in place
         grad_eo = torch.empty(cap_l, H, dtype=torch.bfloat16, device=dev)
+        if ws.exchange == "push":
+            return _backward_push(ctx, grad_out, grad_eo)
         _combine_bwd_pull(ws.peers["go"], ws.peers["w"], ws.peers["idx"], ws.peers["spos"], ws.peers["offs"],
                           L.ptr(ws.eo), L.ptr(perm_l.counts), L.ptr(perm_l.poffs), L.ptr(src_base), W, ws.rank, E, T, k,
                           H, L.ptr(grad_eo), L.ptr(ws.gw), st)
