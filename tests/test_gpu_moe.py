@@ -317,3 +317,27 @@ def test_benchmark_size_configs_vs_fp32(pkg, name, T, H, E, I, k, zipf):
         empty = counts == 0
         assert bool(empty.any()), "the skewed routing must leave some experts without tokens"
         assert (lv["gu"].grad[empty] == 0).all() and (lv["dn"].grad[empty] == 0).all()
+
+
+def test_empty_input_gives_empty_output_and_zero_grads(pkg):
+    """No tokens at all (an empty micro-batch): nothing is launched, shapes and zero gradients come back."""
+    H, I, E, k = 256, 128, 8, 2
+    gu = (torch.randn(E, 2 * I, H, device=DEV) * 0.02).to(torch.bfloat16).requires_grad_(True)
+    dn = (torch.randn(E, H, I, device=DEV) * 0.02).to(torch.bfloat16).requires_grad_(True)
+    codes = torch.zeros(E, dtype=torch.int32, device=DEV)
+    for fn in (pkg.moe, pkg.moe_mxfp8):
+        x = torch.zeros(0, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        w = torch.zeros(0, k, device=DEV, dtype=torch.float32, requires_grad=True)
+        out = fn(x, torch.zeros(0, k, device=DEV, dtype=torch.int64), w, gu, dn, codes)
+        assert out.shape == (0, H) and out.dtype == torch.bfloat16
+        gu.grad = dn.grad = None
+        out.sum().backward()
+        assert x.grad.shape == (0, H) and w.grad.shape == (0, k)
+        assert float(gu.grad.abs().sum()) == 0.0 and float(dn.grad.abs().sum()) == 0.0
+    layer = pkg.MoELayer(H, I, E, top_k=k).to(DEV).to(torch.bfloat16)
+    x = torch.zeros(2, 0, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    out = layer(x)
+    assert out.shape == (2, 0, H)
+    out.sum().backward()
+    assert float(layer.gate.weight.grad.abs().sum()) == 0.0
+    pkg.check_status()

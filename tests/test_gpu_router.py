@@ -17,7 +17,7 @@ def _scores(N, E, seed, bf16_grid):
 
 
 @pytest.mark.parametrize("N,E,k", [(1000, 8, 2), (4099, 64, 6), (2048, 128, 8), (1024, 256, 8), (257, 40, 1),
-                                   (512, 16, 16)])
+                                   (512, 16, 16), (300, 64, 32), (64, 256, 32)])
 @pytest.mark.parametrize("bf16_grid", [False, True])
 @pytest.mark.parametrize("with_bias", [False, True])
 def test_topk_from_identical_scores_is_bit_exact(pkg, N, E, k, bf16_grid, with_bias):

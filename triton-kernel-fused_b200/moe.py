@@ -177,6 +177,17 @@ class _PolyGLUMoE(torch.autograd.Function):
         return grad_hidden, None, grad_wt, grad_gate_up_proj, grad_down_proj, None, grad_ap
 
 
+def _empty_result(hidden, top_k_weights, *params):
+    """No tokens: an empty (0,H) result that still hangs on every differentiable input, so that a backward pass
+    gives zero gradients of the right shapes (what the reference's eager loop does with zero rows)."""
+    out = _amp_cast(hidden)[0]
+    out = out + top_k_weights.to(out.dtype).sum(dim=-1, keepdim=True)
+    for p in params:
+        if p is not None:
+            out = out + 0.0 * p.sum().to(out.dtype)
+    return out
+
+
 def moe(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes, act_params=None):
     """hidden (N,H) bf16, indices (N,k) int64, weights (N,k) float, gate_up_proj (E_glu,2I,H),
     down_proj (E_glu,H,I), act_codes (E,) int32, act_params (E,2) fp32 [alpha,gamma] for code 5 or None
@@ -184,6 +195,8 @@ def moe(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes
     w.r.t. hidden, weights, both projections and act_params.  A pure SiLU-GLU stack runs with the
     activation fused into the GEMM epilogues; any other stack runs the PolyGLU row kernels."""
     codes, n_glu = _code_info(act_codes)
+    if hidden.shape[0] == 0:
+        return _empty_result(hidden, top_k_weights, gate_up_proj, down_proj, act_params)
     if act_params is None and n_glu == len(codes) and all(c == 0 for c in codes):
         return _GroupedMoE.apply(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes)
     return _PolyGLUMoE.apply(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes, act_params)

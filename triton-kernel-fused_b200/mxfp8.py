@@ -15,7 +15,7 @@ import torch
 
 from . import _lib as L
 from . import ops
-from .moe import _amp_cast, _code_info
+from .moe import _amp_cast, _code_info, _empty_result
 
 __all__ = ["moe_mxfp8", "FUSE_QUANT_EPILOGUE"]
 
@@ -130,4 +130,6 @@ def moe_mxfp8(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act
     codes, n_glu = _code_info(act_codes)
     if act_params is not None or n_glu != len(codes) or any(c != 0 for c in codes):
         raise ValueError("the MXFP8 path is built for pure SiLU-GLU stacks (act code 0) only")
+    if hidden.shape[0] == 0:
+        return _empty_result(hidden, top_k_weights, gate_up_proj, down_proj)
     return _MoEMxfp8.apply(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes)

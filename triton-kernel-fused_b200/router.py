@@ -50,12 +50,24 @@ class FusedMLPRouter(torch.autograd.Function):
         return grad_x, grad_w, None, None, None, None, None
 
 
+def _empty_routing(x, weight, top_k):
+    """No tokens: empty picks and weights (the weights still hang on x and the gate weight), zero counts."""
+    n = x.numel() // max(x.shape[-1], 1)
+    idx = torch.zeros(n, top_k, dtype=torch.int64, device=x.device)
+    w = (x.reshape(n, x.shape[-1])[:, :1].float() + 0.0 * weight.float().sum()).expand(n, top_k)
+    counts = torch.zeros(weight.shape[0], dtype=torch.int32, device=x.device)
+    return idx, w, counts
+
+
 def fused_mlp_router(x, gate_weight, bias, top_k, num_experts, norm_topk_prob=True,
                      routed_scaling_factor=1.0, return_counts=False):
     """x (B,S,H) or (N,H), gate_weight (E,H), bias (E,) fp32 or None -> (idx, weights[, counts]);
     (B,S,k) shapes for 3-D x (kernels/sm75/router.py:277-289)."""
-    idx, w, counts = FusedMLPRouter.apply(x, gate_weight, bias, top_k, num_experts, norm_topk_prob,
-                                          routed_scaling_factor)
+    if x.numel() == 0:
+        idx, w, counts = _empty_routing(x, gate_weight, top_k)
+    else:
+        idx, w, counts = FusedMLPRouter.apply(x, gate_weight, bias, top_k, num_experts, norm_topk_prob,
+                                              routed_scaling_factor)
     if x.ndim == 3:
         B, S, _ = x.shape
         idx = idx.view(B, S, top_k)
@@ -107,8 +119,11 @@ def fused_router(x, conv_weight, bias, top_k, num_experts, norm_topk_prob=True, 
     """Whole conv router: x (B,S,H), conv_weight (E,H,K) from nn.Conv1d(H,E,K), bias (E,) fp32 or None ->
     (idx (B,S,k) int64, weights (B,S,k) fp32[, counts (E,) int32]); kernels/sm75/router.py:263-274."""
     B, S, _ = x.shape
-    idx, w, counts = FusedConvRouter.apply(x, conv_weight, bias, top_k, num_experts, norm_topk_prob,
-                                           routed_scaling_factor)
+    if x.numel() == 0:
+        idx, w, counts = _empty_routing(x, conv_weight, top_k)
+    else:
+        idx, w, counts = FusedConvRouter.apply(x, conv_weight, bias, top_k, num_experts, norm_topk_prob,
+                                               routed_scaling_factor)
     idx = idx.view(B, S, top_k)
     w = w.view(B, S, top_k)
     return (idx, w, counts) if return_counts else (idx, w)
