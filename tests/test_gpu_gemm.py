@@ -40,3 +40,37 @@ def test_gemm_tn_splitk(pkg, M, N, K):
     pkg.check_status()
     ref = a.float().t() @ b.float()
     assert O.rel_l2(d.float().cpu(), ref) < TOL
+
+
+@pytest.mark.parametrize("T,E,k,N,K,w_kn", [(1500, 8, 2, 2048, 1408, False), (900, 6, 3, 320, 256, False),
+                                            (1200, 4, 2, 512, 704, True), (700, 16, 4, 64, 128, True)])
+def test_expert_linear_push_equals_store_then_scatter(pkg, T, E, k, N, K, w_kn):
+    """The pushing epilogue (one bulk copy per 128-byte row piece to base[rank] + slot * N) against the storing
+    GEMM followed by a scatter; the receive buffer is local here (one rank), some rows are dropped (rank -1)."""
+    ops = pkg.ops
+    g = torch.Generator().manual_seed(11)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)])
+    perm = ops.permute_build(idx.to(DEV), E)
+    a = _rand(T, K, seed=12).to(DEV)
+    a_s = ops.gather_rows(a, perm)
+    w = (_rand(E, K, N, seed=13) if w_kn else _rand(E, N, K, seed=13)).to(DEV) * 0.05
+    w = w.contiguous()
+    ref_rows = (ops.expert_linear_t if w_kn else ops.expert_linear)(a_s, w, perm)
+    # every live row gets a distinct slot; every seventh one is dropped
+    row_slot_src = perm.row_slot.clone()
+    total = int(perm.poffs[-1])                 # rows past the padded total are not part of the permutation
+    live = (row_slot_src >= 0) & (torch.arange(row_slot_src.numel(), device=DEV) < total)
+    slots = torch.full_like(row_slot_src, 0)
+    slots[live] = torch.randperm(int(live.sum()), generator=g).to(torch.int32).to(DEV)
+    rank = torch.where(live, torch.zeros_like(slots), torch.full_like(slots, -1))
+    drop = (torch.arange(rank.numel(), device=DEV) % 7 == 3) & live
+    rank[drop] = -1
+    recv = torch.full((int(live.sum()), N), 7.0, dtype=torch.bfloat16, device=DEV)
+    base = torch.tensor([recv.data_ptr()], dtype=torch.int64, device=DEV)
+    ops.expert_linear_push(a_s, w, perm, rank, slots, base, w_kn=w_kn)
+    torch.cuda.synchronize()
+    pkg.check_status()
+    expect = torch.full_like(recv, 7.0)
+    keep = live & ~drop
+    expect[slots[keep].long()] = ref_rows[keep]
+    assert torch.equal(recv, expect)

@@ -389,6 +389,18 @@ def expert_linear(a, w, perm: Permutation, out=None):
     return out
 
 
+@_op("expert_linear_push", 1)
+def expert_linear_push(a, w, perm: Permutation, row_rank, row_slot, peer_base, w_kn=False):
+    """Row r of a (rows,K) @ W[e(r)]^T (W (E,N,K); w_kn: a @ W[e(r)], W (E,K,N)) is sent to
+    peer_base[row_rank[r]] + row_slot[r] * N elements instead of being stored; rows with row_rank < 0 are dropped.
+    peer_base: int64 device tensor of buffer addresses."""
+    E = w.shape[0]
+    K, N = (w.shape[1], w.shape[2]) if w_kn else (w.shape[2], w.shape[1])
+    L.check(L.lib().b200moe_expert_linear_push(L.ptr(a), L.ptr(w), 1 if w_kn else 0, L.ptr(perm.tile_expert),
+                                               L.ptr(perm.poffs), perm.cap, E, N, K, L.ptr(row_rank), L.ptr(row_slot),
+                                               L.ptr(peer_base), L.ptr(L.status_word(a.device)), L.stream_of(a)))
+
+
 @_op("expert_linear_t", 1)
 def expert_linear_t(a, w, perm: Permutation, out=None):
     """out (rows,N) = a (rows,K) @ W[e] with W (E,K,N), E = perm.E."""
