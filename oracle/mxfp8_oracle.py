@@ -82,7 +82,7 @@ def moe_experts_mxfp8(hidden, top_k_indices, top_k_weights, gate_up_proj, down_p
     I = twoI // 2
     order, st, counts, offs = O.sort_by_expert_stable(top_k_indices, E)
     sw = top_k_weights.flatten()[order]
-    out = torch.zeros(N, H, dtype=torch.float32)
+    out = torch.zeros(N, H, dtype=torch.float32, device=hidden.device)   # runs on whichever device holds the inputs
     w_gu, w_dn = gate_up_proj.unbind(0), down_proj.unbind(0)
     for e in range(E):
         s, en = int(offs[e]), int(offs[e + 1])

@@ -147,3 +147,33 @@ def test_producer_epilogues_quantise_bit_identically(pkg):
     assert torch.equal(iq[:total], iq_ref[:total])
     cs = Q.quantise(inter[:total].float().cpu())[1]
     assert _sf_equal(isf[: Q.sf_atoms(cs).numel()], cs)
+
+
+def test_mxfp8_configuration_at_full_size(pkg):
+    """T=32768, H=4096, E=8, I=14336, top-2 (the MXFP8 configuration of the benchmark) at FULL size: output and
+    every gradient within 5e-2 relative L2 of the quantise -> dequantise restatement, evaluated in fp32 on the
+    GPU (the same oracle code, run on CUDA tensors; the CPU would need an hour for its 69 TFLOP)."""
+    T, H, E, I, k = 32768, 4096, 8, 14336, 2
+    g = torch.Generator(device=DEV).manual_seed(9)
+    x = torch.randn(T, H, device=DEV, generator=g).to(torch.bfloat16)
+    gu = (torch.randn(E, 2 * I, H, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    dn = (torch.randn(E, H, I, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    go = torch.randn(T, H, device=DEV, generator=g).to(torch.bfloat16)
+    idx, w, _ = pkg.ops.router_topk_fwd(torch.randn(T, E, device=DEV, generator=g), None, k)
+    lv = dict(x=x.clone().requires_grad_(True), w=w.clone().requires_grad_(True),
+              gu=gu.clone().requires_grad_(True), dn=dn.clone().requires_grad_(True))
+    out = pkg.moe_mxfp8(lv["x"], idx, lv["w"], lv["gu"], lv["dn"], torch.zeros(E, dtype=torch.int32, device=DEV))
+    out.backward(go)
+    pkg.check_status()
+    got = dict(out=out.detach().float(), grad_x=lv["x"].grad.float(), grad_w=lv["w"].grad.float(),
+               grad_gate_up=lv["gu"].grad.float(), grad_down=lv["dn"].grad.float())
+    del out, lv
+    rx, rw = x.float().requires_grad_(True), w.clone().requires_grad_(True)
+    rgu, rdn = gu.float().requires_grad_(True), dn.float().requires_grad_(True)
+    ref = Q.moe_experts_mxfp8(rx, idx, rw, rgu, rdn)
+    ref.backward(go.float())
+    want = dict(out=ref.detach(), grad_x=rx.grad, grad_w=rw.grad, grad_gate_up=rgu.grad, grad_down=rdn.grad)
+    errs = {n: float((got[n] - want[n]).norm() / want[n].norm()) for n in got}
+    print("config 4 at full size vs quantised fp32 reference:", {n: f"{v:.3e}" for n, v in errs.items()})
+    for n, v in errs.items():
+        assert v < TOL_MX, (n, v)
