@@ -244,6 +244,12 @@ int b200moe_mxfp8_expert_gemm(int epilogue, const void* Aq, const void* Asf, con
  * scales (H % 32 == 0); replaces b200moe_gather_rows + b200moe_mxfp8_quant_rows. */
 int b200moe_mxfp8_gather_quant(const void* x, const int32_t* row_slot, const int32_t* total_rows, int k, int64_t H,
                                int64_t rows_cap, void* x_s, void* q, void* sf, b200moe_stream_t stream);
+/* The gather fused with both quantisers: what b200moe_mxfp8_gather_quant's codes/scales and
+ * b200moe_mxfp8_quant_transpose of its x_s would be, without writing x_s (rows_cap % 32 == 0, H % 32 == 0;
+ * q_t is (H, rows_cap)). */
+int b200moe_mxfp8_gather_quant_both(const void* x, const int32_t* row_slot, const int32_t* total_rows, int k, int64_t H,
+                                    int64_t rows_cap, void* q_rows, void* sf_rows, void* q_t, void* sf_t,
+                                    b200moe_stream_t stream);
 /* Weight gradient: out[e] (Na,Nb) bf16 = At[:, rows of e] * Bt[:, rows of e]^T, At (Na, rows_cap) and
  * Bt (Nb, rows_cap) quantised along the token rows (b200moe_mxfp8_quant_transpose). */
 int b200moe_mxfp8_expert_wgrad(const void* Atq, const void* Atsf, const void* Btq, const void* Btsf,

@@ -71,6 +71,27 @@ def test_quant_both_equals_the_two_passes(pkg, G, R, C, I):
     assert torch.equal(sft.cpu()[live_t], sft1.cpu()[live_t])
 
 
+@pytest.mark.parametrize("T,E,k,H", [(700, 6, 2, 256), (1500, 8, 3, 384), (33, 4, 1, 64)])
+def test_gather_quant_both_equals_gather_then_quantise(pkg, T, E, k, H):
+    """The fused gather + dual quantiser against gather_quant followed by the transposing quantiser of x_s."""
+    g = torch.Generator().manual_seed(6)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)])
+    perm = pkg.ops.permute_build(idx.to(DEV), E)
+    x = (torch.randn(T, H, generator=g) * torch.logspace(-2, 2, T)[:, None]).to(torch.bfloat16).to(DEV)
+    q, sf, qt, sft = pkg.ops.mxfp8_gather_quant_both(x, perm)
+    x_s, q1, sf1 = pkg.ops.mxfp8_gather_quant(x, perm)
+    total = int(perm.poffs[-1])
+    x_s[total:] = 0                                  # rows past the padded total are not written by the plain gather
+    qt1, sft1 = pkg.ops.mxfp8_quant_transpose(x_s)
+    assert torch.equal(q[:total], q1[:total]) and torch.equal(qt, qt1)
+    ones = torch.zeros(perm.cap, H // 32, dtype=torch.uint8)
+    ones[:total] = 1
+    live = Q.sf_atoms(ones) == 1
+    assert torch.equal(sf.cpu()[live], sf1.cpu()[live])
+    live_t = Q.sf_atoms(torch.ones(H, perm.cap // 32, dtype=torch.uint8)) == 1
+    assert torch.equal(sft.cpu()[live_t], sft1.cpu()[live_t])
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 264, 1024), (1000, 2048, 512), (64, 72, 256)])
 def test_mxfp8_gemm_matches_dequantised_product(pkg, M, N, K):
     g = torch.Generator().manual_seed(2)

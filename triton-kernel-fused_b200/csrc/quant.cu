@@ -56,11 +56,24 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long R, long long C,
 // leave as full 128-byte lines; the four scale bytes of a column leave as one word.  R % 32 == 0.
 // ROWS: the same pass also writes the row-wise quantisation of the tile (blocks of 32 along C; rows
 // optionally 64-interleaved), re-reading the tile from cache instead of DRAM.  Needs C % 32 == 0.
-template <bool ROWS>
+// GATHER (G = 1): row r of the quantised matrix is x[row_slot[r] / k] (a token row) when r < *total_rows and
+// row_slot[r] >= 0, and a zero row otherwise: the gathered matrix itself is never written.
+template <bool ROWS, bool GATHER = false>
 __global__ void __launch_bounds__(256, 4)
 quant_tile_kernel(const __nv_bfloat16* __restrict__ x, long long G, long long R, long long C, long long interleave_I,
                   uint8_t* __restrict__ q_t, uint8_t* __restrict__ sf_t, uint8_t* __restrict__ q_r,
-                  uint8_t* __restrict__ sf_r) {
+                  uint8_t* __restrict__ sf_r, const int* __restrict__ row_slot = nullptr,
+                  const int* __restrict__ total_rows = nullptr, int k = 1) {
+  // source row of matrix row r (nullptr = zero row)
+  auto src_row = [&](long long g, long long r) -> const __nv_bfloat16* {
+    if constexpr (GATHER) {
+      if (r >= *total_rows) return nullptr;
+      const int slot = row_slot[r];
+      return slot < 0 ? nullptr : x + static_cast<long long>(slot / k) * C;
+    } else {
+      return x + (g * R + r) * C;
+    }
+  };
   __shared__ __align__(16) uint8_t s_q[128 * 128];
   __shared__ uint32_t s_sf[128];
   const int lane = threadIdx.x & 31;
@@ -83,10 +96,11 @@ quant_tile_kernel(const __nv_bfloat16* __restrict__ x, long long G, long long R,
         const long long cb = ct * 128 + (it & 3) * 32;
         if (r < R && cb < C) {
           const long long gr = g * R + r;
-          const uint4* src = reinterpret_cast<const uint4*>(x + gr * C + cb);
+          const __nv_bfloat16* srow = src_row(g, r);
           uint4 v[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) v[j] = __ldg(src + j);
+          for (int j = 0; j < 4; ++j)
+            v[j] = srow != nullptr ? __ldg(reinterpret_cast<const uint4*>(srow + cb) + j) : make_uint4(0u, 0u, 0u, 0u);
           const long long dr = interleave_I > 0 ? interleaved_row(gr, interleave_I) : gr;
           mx_quant_store32(reinterpret_cast<const uint32_t*>(v), q_r + dr * C + cb, sf_r, dr, cb >> 5, kc_r);
         }
@@ -95,14 +109,32 @@ quant_tile_kernel(const __nv_bfloat16* __restrict__ x, long long G, long long R,
     {
       const long long r0 = rt * 128 + rbw * 32;
       const long long c = ct * 128 + ch * 64 + 2 * lane;
+      int my_tok = -1;   // GATHER: lane i looks up the token of row r0 + i once, the warp shares it by shuffle
+      if constexpr (GATHER) {
+        const long long r = r0 + lane;
+        if (r < R && r < *total_rows) {
+          const int slot = row_slot[r];
+          if (slot >= 0) my_tok = slot / k;
+        }
+      }
       uint4 oa[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
       uint4 ob[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
       uint32_t sa = 0u, sbb = 0u;
-      if (r0 < R && c < C) {
-        const __nv_bfloat16* src = x + (g * R + r0) * C + c;
-        uint32_t v[32];   // row i of the block: column c in the low half, column c + 1 in the high half
+      uint32_t v[32];   // row i of the block: column c in the low half, column c + 1 in the high half
+      if constexpr (GATHER) {   // every lane takes part in the shuffles, also those past the last column
+        const bool in = r0 < R && c < C;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __ldg(reinterpret_cast<const uint32_t*>(src + i * C));
+        for (int i = 0; i < 32; ++i) {
+          const int t = __shfl_sync(0xffffffffu, my_tok, i);
+          v[i] = (in && t >= 0) ? __ldg(reinterpret_cast<const uint32_t*>(x + static_cast<long long>(t) * C + c)) : 0u;
+        }
+      }
+      if (r0 < R && c < C) {
+        if constexpr (!GATHER) {
+          const __nv_bfloat16* src = x + (g * R + r0) * C + c;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __ldg(reinterpret_cast<const uint32_t*>(src + i * C));
+        }
         uint32_t m = 0u;
 #pragma unroll
         for (int i = 0; i < 32; ++i) m = absmax_bf16x2(m, v[i]);
@@ -250,6 +282,29 @@ static int launch_quant_tile(const void* x, long long G, long long R, long long 
     quant_tile_kernel<false><<<static_cast<int>(grid), 256, 0, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(x), G, R, C, 0, reinterpret_cast<uint8_t*>(q_t),
         reinterpret_cast<uint8_t*>(sf_t), nullptr, nullptr);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_mxfp8_gather_quant_both(const void* x, const int32_t* row_slot, const int32_t* total_rows, int k, int64_t H,
+                                    int64_t rows_cap, void* q_rows, void* sf_rows, void* q_t, void* sf_t,
+                                    b200moe_stream_t stream) {
+  B200_CHECK_ARG(x && row_slot && total_rows && q_rows && sf_rows && q_t && sf_t, B200MOE_E_NULL,
+                 "mxfp8_gather_quant_both: null pointer");
+  B200_CHECK_ARG(H > 0 && H % 32 == 0 && k >= 1 && rows_cap >= 0 && rows_cap % 32 == 0, B200MOE_E_BAD_SHAPE,
+                 "mxfp8_gather_quant_both: H = %lld and rows_cap = %lld must be multiples of 32", (long long)H,
+                 (long long)rows_cap);
+  B200_CHECK_ARG(aligned16(x) && aligned16(q_rows) && aligned16(q_t) && (reinterpret_cast<uintptr_t>(sf_t) & 3) == 0,
+                 B200MOE_E_ALIGN, "mxfp8_gather_quant_both: pointers must be 16-byte aligned");
+  if (rows_cap == 0) return 0;
+  const long long tiles = ((rows_cap + 127) / 128) * ((H + 127) / 128);
+  long long grid = tiles;
+  const long long cap = static_cast<long long>(num_sms()) * 8;
+  if (grid > cap) grid = cap;
+  quant_tile_kernel<true, true><<<static_cast<int>(grid), 256, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), 1, rows_cap, H, 0, reinterpret_cast<uint8_t*>(q_t),
+      reinterpret_cast<uint8_t*>(sf_t), reinterpret_cast<uint8_t*>(q_rows), reinterpret_cast<uint8_t*>(sf_rows), row_slot,
+      total_rows, k);
   B200_CUDA(cudaGetLastError());
   return 0;
 }

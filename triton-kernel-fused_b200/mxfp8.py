@@ -45,7 +45,13 @@ class _MoEMxfp8(torch.autograd.Function):
 
         need_x, _, _, need_gu, need_dn, _ = ctx.needs_input_grad
         perm = ops.permute_build(idx, E)
-        x_s, xq, xsf = ops.mxfp8_gather_quant(hidden, perm)             # the gather is the quantising producer
+        # the gather is the quantising producer; when the gate/up weight gradient is wanted it also writes the
+        # copy quantised along the token rows, and the gathered bf16 rows are never materialised
+        xt = xtsf = None
+        if need_gu:
+            xq, xsf, xt, xtsf = ops.mxfp8_gather_quant_both(hidden, perm)
+        else:
+            _, xq, xsf = ops.mxfp8_gather_quant(hidden, perm)
         # tensors that the backward needs quantised along their other dimension are quantised both ways in
         # one pass over DRAM, and the transposed copy is what the backward keeps
         wgt = wgtsf = wtq = wtsf = it = itsf = None
@@ -75,18 +81,18 @@ class _MoEMxfp8(torch.autograd.Function):
         ctx.perm = perm
         ctx.wt_dtype = wt.dtype
         ctx.dims = (E, H, I)
-        ctx.quantised = (wgt, wgtsf, wtq, wtsf, it, itsf)   # uint8 copies for the backward (not differentiable)
-        ctx.save_for_backward(x_s, gate_up, eo, w32)
+        ctx.quantised = (wgt, wgtsf, wtq, wtsf, it, itsf, xt, xtsf)   # uint8 copies for the backward (not differentiable)
+        ctx.save_for_backward(gate_up, eo, w32)
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        x_s, gate_up, eo, w32 = ctx.saved_tensors
-        wgt, wgtsf, wtq, wtsf, it, itsf = ctx.quantised
+        gate_up, eo, w32 = ctx.saved_tensors
+        wgt, wgtsf, wtq, wtsf, it, itsf, xt, xtsf = ctx.quantised
         perm = ctx.perm
         E, H, I = ctx.dims
         twoI = 2 * I
-        dev = x_s.device
+        dev = eo.device
         need_x, _, need_w, need_gu, need_dn, _ = ctx.needs_input_grad
         grad_out = grad_out.contiguous().to(torch.bfloat16)
         grad_eo, grad_w = ops.combine_bwd(grad_out, eo, w32, perm)
@@ -113,8 +119,7 @@ class _MoEMxfp8(torch.autograd.Function):
             else:
                 at, atsf = ops.mxfp8_quant_transpose(grad_gu)
             if need_gu:
-                bt, btsf = ops.mxfp8_quant_transpose(x_s)                 # (H, rows)
-                grad_gate_up_proj = ops.mxfp8_expert_wgrad(at, atsf, bt, btsf, perm)
+                grad_gate_up_proj = ops.mxfp8_expert_wgrad(at, atsf, xt, xtsf, perm)   # xt: (H, rows) from the forward
             if need_x:
                 grad_x_s = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=dev)
                 ops.mxfp8_expert_gemm(ops.EPI_STORE, ggq, ggsf, wgt, wgtsf, perm, H, twoI, I, grad_x_s)

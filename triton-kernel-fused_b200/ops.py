@@ -354,6 +354,21 @@ def mxfp8_expert_gemm(epilogue, aq, asf, bq, bsf, perm: Permutation, N, K, I, d,
     return (d, q, qsf) if quantise_result else d
 
 
+@_op("mxfp8_gather_quant_both", 1)
+def mxfp8_gather_quant_both(x, perm: Permutation):
+    """Codes + scales of the gathered rows x[row_slot/k] quantised along H (rows, H) and along the rows (H, rows),
+    pad rows as zeros; the gathered bf16 matrix is not materialised."""
+    L.require_cuda_bf16("x", x)
+    H = x.shape[1]
+    q = torch.empty(perm.cap, H, dtype=torch.uint8, device=x.device)
+    sf = _sf_empty(perm.cap, H, x.device)
+    qt = torch.empty(H, perm.cap, dtype=torch.uint8, device=x.device)
+    sft = _sf_empty(H, perm.cap, x.device)
+    L.check(L.lib().b200moe_mxfp8_gather_quant_both(L.ptr(x), L.ptr(perm.row_slot), L.ptr(perm.total_rows), perm.k, H,
+                                                    perm.cap, L.ptr(q), L.ptr(sf), L.ptr(qt), L.ptr(sft), L.stream_of(x)))
+    return q, sf, qt, sft
+
+
 @_op("mxfp8_gather_quant", 1)
 def mxfp8_gather_quant(x, perm: Permutation):
     """Gather into the padded layout and quantise along the rows in one pass: (x_s bf16, codes, scale atoms)."""
