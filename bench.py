@@ -345,6 +345,112 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_muon(args):
+    """--workload muon: one optimizer step (FusedMuon, the reference's default scale mode) over the two expert stacks of
+    the headline layer, (E,2I,H) and (E,H,I) in bf16 with bf16 gradients.  Not the headline metric: a line of its own
+    for the optimizer row, same timing rules (CUDA events on the launching stream, warm-up, working set above L2)."""
+    if int(os.environ.get("WORLD_SIZE", 1)) > 1:
+        if int(os.environ.get("RANK", 0)) == 0:
+            print(json.dumps({"workload": "muon", "unavailable": "single-GPU workload (stacks are not sharded)"}), flush=True)
+        return
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    pkg = importlib.import_module(PKG)
+    pkg.lib()
+    ops = pkg.ops
+    H, E, I = HEADLINE["H"], HEADLINE["E"], HEADLINE["I"]
+    shapes = [(E, 2 * I, H), (E, H, I)]
+    g = torch.Generator(device=dev).manual_seed(3)
+    params = [torch.nn.Parameter((torch.randn(*sh, device=dev, generator=g) * 0.02).to(torch.bfloat16)) for sh in shapes]
+    grads_host = [torch.randn(*sh, generator=torch.Generator().manual_seed(4 + i)).to(torch.bfloat16).pin_memory()
+                  for i, sh in enumerate(shapes)]
+    grads_dev = [t.to(dev) for t in grads_host]
+    params_host = [torch.empty_like(t).pin_memory() for t in grads_host]
+    opt = pkg.FusedMuon(params, lr=3e-4, weight_decay=0.1)
+
+    def step_resident():
+        for p, gr in zip(params, grads_dev):
+            p.grad = gr
+        opt.step()
+
+    def step_e2e():
+        for p, gh in zip(params, grads_host):
+            p.grad = gh.to(dev, non_blocking=True)
+        opt.step()
+        for p, ph in zip(params, params_host):
+            ph.copy_(p.detach(), non_blocking=True)
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    n_warm = max(args.warmup, 3)
+    for _ in range(n_warm):
+        step_resident()
+    pkg.check_status()
+    records = []
+    ops.set_hook(lambda name, launches, a, b: records.append((name, launches, a, b)))
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms_total = timed(step_resident, args.steps)
+    clocks = sampler.stop()
+    ops.set_hook(None)
+    pkg.check_status()
+    ms_e2e = timed(step_e2e, args.steps) / args.steps
+    per_op, launches = {}, 0
+    for name, n, a, b in records:
+        d = per_op.setdefault(name, [0.0, 0])
+        d[0] += a.elapsed_time(b)
+        d[1] += 1
+        launches += n
+    ms_step = ms_total / args.steps
+    iters = len(pkg.muon.DSV4_COEFFS)
+    flops = 0.0                      # algorithmic: per matrix and iteration 2 s^2 w (X X^T) + 2 s^3 (A A) + 2 s^2 w (B X)
+    for (n, r, c) in shapes:
+        s_, w_ = min(r, c), max(r, c)
+        flops += n * iters * (4.0 * s_ * s_ * w_ + 2.0 * s_ ** 3)
+    gemm_names = [n for n in ("expert_linear", "expert_linear_t") if n in per_op]
+    gemm_ms = sum(per_op[n][0] for n in gemm_names) / args.steps
+    peaks = _peaks("bf16")
+    kernels = {name: dict(launches_per_step=n / args.steps, avg_ms=round(ms / n, 4), share=round(ms / ms_total, 4))
+               for name, (ms, n) in sorted(per_op.items(), key=lambda kv: -kv[1][0])}
+    achieved = flops / (gemm_ms * 1e-3) / 1e12
+    nbytes = sum(2 * n * r * c for n, r, c in shapes)
+    line = {
+        "metric": "expert_stack_muon_step_ms", "value": round(ms_step, 3), "unit": "ms", "n_gpus": 1, "steps": args.steps,
+        "warmup": n_warm, "ms_per_step": round(ms_step, 3), "higher_is_better": False, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"FusedMuon step (aurora, {iters} Newton-Schulz iterations) over expert stacks "
+                               f"{shapes[0]} and {shapes[1]}, bf16 parameters and gradients",
+                   "l2": "no flush: every stack (0.4-0.7 GB) exceeds the 126 MB L2"},
+        "step_tflops": round(flops / (ms_step * 1e-3) / 1e12, 1),
+        "gemm_ms_per_step": round(gemm_ms, 3),
+        "roofline": {"bound": "tensor", "kernel": "gemm_kernel via expert_linear / expert_linear_t (Newton-Schulz products)",
+                     "achieved": round(achieved, 1), "peak": peaks["tflops"], "unit": "TFLOP/s",
+                     "frac": round(achieved / peaks["tflops"], 4), "traffic": None, "peak_source": peaks["source"]},
+        "kernels": kernels,
+        "e2e": {"value": round(ms_e2e, 3), "unit": "ms", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes},
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    if not args.no_cpu_baseline:
+        from oracle import muon_oracle as MO
+        t0 = time.perf_counter()
+        for (n, r, c) in shapes:       # one matrix of each stack, fp32, the oracle's step
+            p1 = torch.randn(1, r, c) * 0.02
+            MO.muon_step(p1, torch.randn(1, r, c), torch.zeros(1, r, c), 3e-4, weight_decay=0.1)
+        sec = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": round(sec * 1e3 * E, 1), "unit": "ms", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": f"1 of {E} matrices of each stack, fp32, oracle/muon_oracle.py muon_step "
+                                          f"({round(sec, 2)} s), scaled by {E}; host cpu_count={os.cpu_count()}"}
+    print(json.dumps(line), flush=True)
+
+
 def cpu_baseline(w, steps, warmup, sample_tokens=512):
     """The oracle port (plain PyTorch fp32 on the host cores) on a bounded sample: `sample_tokens`
     tokens through the full-size layer (all E experts, full d_model and d_ff), forward + backward."""
@@ -389,11 +495,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="headline", choices=["headline", "profile", "ep5", "mxfp8", "mxfp8_profile", "zipf"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "profile", "ep5", "mxfp8", "mxfp8_profile", "zipf", "muon"],
                     help="profile = small case for profiler captures (not a benchmark number)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "muon":
+        run_muon(args)
     else:
         run_ours(args)
 

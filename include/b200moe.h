@@ -311,6 +311,45 @@ int b200moe_ep_combine_bwd_pull(const void* const* go_peers, const void* const* 
 int b200moe_slot_dots(const void* grad_out, const void* rows, int64_t T, int k, int64_t H, float* out,
                       b200moe_stream_t stream);
 
+/* ---- Expert-stack optimizer step (Muon), the consumer of the layer's weight gradients.
+ * Replaces the body of FusedMuon.step for stacks (E, r, c) of matrices (kernels/sm75/muon.py:366-434, the
+ * capturable form :300-315) and newton_schulz (:62-89).  The three matrix products of each Newton-Schulz iteration
+ * are b200moe_expert_linear / b200moe_expert_linear_t calls on a stack whose E row segments have `Rp` rows each
+ * (a multiple of B200MOE_TILE_M, rows past the matrix are zero); these entry points are everything around them.
+ * r and c are multiples of 8; bf16 unless stated. */
+
+/* buf = mu*buf + g; u = nesterov ? g + mu*buf : buf (kernels/sm75/muon.py:389-390).  grad: n elements, fp32 if
+ * grad_f32 else bf16, rounded to bf16 first as the reference's staging copy does (:386-388); mom (in/out), u: bf16. */
+int b200moe_muon_momentum(const void* grad, int grad_f32, void* mom, void* u, int64_t n, float mu, int nesterov,
+                          b200moe_stream_t stream);
+
+/* rowss[row] = sum_j x[row,j]^2, fp32 accumulation (torch.linalg.vector_norm(..., dtype=float32),
+ * kernels/sm75/muon.py:78, kernels/muon/muon_scaling.py:110). */
+int b200moe_muon_row_sumsq(const void* x, int64_t rows, int64_t cols, float* rowss, b200moe_stream_t stream);
+
+/* out[row,:] = bf16(x[row,:] * (tgt / max(sqrt(rowss[row]), eps))); rowss_out[row] = sum of squares of the rounded
+ * row.  The row prescale of scale_mode "aurora" with K = 1, beta = 0 (kernels/muon/muon_scaling.py:107-111). */
+int b200moe_muon_prescale_rows(const void* x, const float* rowss, int64_t rows, int64_t cols, float tgt, float eps,
+                               void* out, float* rowss_out, b200moe_stream_t stream);
+
+/* Frobenius normalisation into the iteration's layout (kernels/sm75/muon.py:78-82): norms[e] =
+ * bf16(max(sqrt(sum_i rowss[e*r+i]), eps)); transposed == 0: xp (E, Rp, c), xp[e,i,:] = x[e,i,:] / norms[e];
+ * transposed != 0 (use it when r > c): xp (E, Rp, r), xp[e,j,i] = x[e,i,j] / norms[e].  Rows of xp past the matrix
+ * are written as zeros.  norms: E floats of caller-owned scratch. */
+int b200moe_muon_normalise_pack(const void* x, const float* rowss, int E, int64_t r, int64_t c, int64_t Rp,
+                                int transposed, float eps, float* norms, void* xp, b200moe_stream_t stream);
+
+/* out = bf16(alpha*x + beta*y), n elements; out may alias x or y.  The axpy halves of the reference's baddbmm calls
+ * (kernels/sm75/muon.py:85-86). */
+int b200moe_axpby_bf16(const void* x, float alpha, const void* y, float beta, void* out, int64_t n,
+                       b200moe_stream_t stream);
+
+/* p = round(round(p*decay) + alpha * bf16(gain*o)), o[e,i,j] = xp[e,i,j] (xp (E,Rp,c)) or xp[e,j,i] (transposed,
+ * xp (E,Rp,r)); p (E,r,c) fp32 if p_f32 else bf16.  Decoupled weight decay + update (kernels/sm75/muon.py:381,
+ * 431-434); gain is the aurora gain (kernels/muon/muon_scaling.py:112), 1 for scale_mode "polar". */
+int b200moe_muon_apply(const void* xp, int E, int64_t r, int64_t c, int64_t Rp, int transposed, float gain, float decay,
+                       float alpha, void* p, int p_f32, b200moe_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

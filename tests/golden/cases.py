@@ -64,3 +64,36 @@ def poly_inputs(name):
     ap = torch.stack([torch.rand(E, generator=g) + 0.5, torch.rand(E, generator=g) + 0.5], dim=1) if use_ap else None
     gsig = torch.randn(POLY_N, POLY_H, generator=g) * 0.1
     return dict(codes=codes, hidden=hid, gate_up=gup, down=dwn, idx=idx, w=wt, act_params=ap, grad_out=gsig, I=I)
+
+
+# ---- expert-stack optimizer (Muon) cases: name -> (shape, seed).  Wide, tall, square stacks and one plain matrix.
+MUON_NS_CASES = {
+    "wide": ((3, 64, 96), 11),
+    "tall": ((3, 96, 64), 12),
+    "square": ((2, 64, 64), 13),
+    "matrix": ((48, 80), 14),
+}
+# name -> (shape, seed, scale_mode, nesterov, weight_decay, steps)
+MUON_STEP_CASES = {
+    "polar_tall": ((4, 96, 64), 21, "polar", True, 0.1, 3),
+    "polar_wide_plain_momentum": ((4, 64, 96), 22, "polar", False, 0.0, 3),
+    "aurora_tall": ((4, 96, 64), 23, "aurora", True, 0.1, 3),
+    "aurora_wide": ((4, 64, 96), 24, "aurora", True, 0.0, 3),
+}
+MUON_LR, MUON_MOMENTUM = 0.02, 0.95
+
+
+def muon_ns_input(name):
+    import torch
+    shape, seed = MUON_NS_CASES[name]
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed))
+
+
+def muon_step_inputs(name):
+    """(initial parameters, list of per-step gradients), fp32, seeded."""
+    import torch
+    shape, seed, _mode, _nest, _wd, steps = MUON_STEP_CASES[name]
+    g = torch.Generator().manual_seed(seed)
+    p0 = torch.randn(*shape, generator=g) * 0.02
+    grads = [torch.randn(*shape, generator=g) for _ in range(steps)]
+    return p0, grads

@@ -1,0 +1,118 @@
+"""GPU: the expert-stack optimizer step (`newton_schulz`, `FusedMuon`) against the CPU oracle and against results
+of the reference's own code (tests/golden/muon.npz).
+
+The iteration runs in bf16 on the GPU.  Ten quintic steps with the default coefficients amplify rounding noise of
+the small singular directions, so a bf16 run is compared (a) with the fp32 result at 1e-1 relative L2, (b) by the
+reference's own stability gate for its low-precision iteration (bench.py:1054-1058: no NaN, mean singular value in
+[0.8, 1.2]), and (c) exactly where the arithmetic is exact or rounds at the same places: momentum buffers, pad
+rows, reruns."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import muon_oracle as MO
+from tests.golden.cases import (MUON_LR, MUON_MOMENTUM, MUON_NS_CASES, MUON_STEP_CASES, muon_ns_input,
+                                muon_step_inputs)
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+NS_TOL = 1e-1       # bf16 iteration against the fp32 iteration, relative L2
+STEP_TOL = 1e-1     # the same for the update p_new - p_old of a step
+
+
+@pytest.fixture(scope="module")
+def gold(golden_dir):
+    return np.load(os.path.join(golden_dir, "muon.npz"))
+
+
+def _sv_gate(Y):
+    Y = Y.float()
+    sv = torch.linalg.svdvals(Y if Y.dim() == 3 else Y[None])
+    assert not Y.isnan().any()
+    assert 0.8 <= sv.mean().item() <= 1.2, sv.mean().item()
+
+
+@pytest.mark.parametrize("name", list(MUON_NS_CASES))
+def test_newton_schulz_against_reference_golden(pkg, gold, name):
+    G = muon_ns_input(name)
+    got = pkg.newton_schulz(G.to(DEV)).cpu()
+    torch.cuda.synchronize(); pkg.check_status()
+    assert got.shape == G.shape and got.dtype == G.dtype
+    assert MO.rel_l2(got, torch.from_numpy(gold[f"ns_{name}_f32"])) < NS_TOL
+    assert MO.rel_l2(got, torch.from_numpy(gold[f"ns_{name}_bf16"])) < NS_TOL
+    _sv_gate(got)
+
+
+# the reference's stability shapes (bench.py:1054) and the layer's own expert stacks (headline: (E,2I,H), (E,H,I))
+@pytest.mark.parametrize("shape", [(512, 512), (256, 512), (1536, 512), (9, 1536, 512), (9, 512, 768),
+                                   (4, 2816, 2048), (4, 2048, 1408), (2, 1536, 2048)])
+def test_newton_schulz_against_oracle(pkg, shape):
+    G = torch.randn(*shape, generator=torch.Generator().manual_seed(sum(shape)))
+    got = pkg.newton_schulz(G.to(DEV).to(torch.bfloat16)).float()
+    torch.cuda.synchronize(); pkg.check_status()
+    ref = MO.newton_schulz(G.to(torch.bfloat16).float().to(DEV), ns_dtype=torch.float32)   # oracle code, fp32
+    assert MO.rel_l2(got, ref) < NS_TOL
+    _sv_gate(got)
+    again = pkg.newton_schulz(G.to(DEV).to(torch.bfloat16)).float()
+    assert torch.equal(got, again)                      # no atomics anywhere: reruns are bit-identical
+
+
+def test_zero_matrix_stays_zero_and_finite(pkg):
+    G = torch.zeros(2, 64, 128, device=DEV, dtype=torch.bfloat16)
+    out = pkg.newton_schulz(G)
+    assert torch.equal(out, G)                          # norm clamps at eps (kernels/sm75/muon.py:78): 0 / eps = 0
+
+
+@pytest.mark.parametrize("name", list(MUON_STEP_CASES))
+@pytest.mark.parametrize("pdtype", [torch.float32, torch.bfloat16])
+def test_step_against_reference_golden_and_oracle(pkg, gold, name, pdtype):
+    _shape, _seed, mode, nesterov, wd, steps = MUON_STEP_CASES[name]
+    p0, grads = muon_step_inputs(name)
+    p = torch.nn.Parameter(p0.to(DEV).to(pdtype))
+    opt = pkg.FusedMuon([p], lr=MUON_LR, momentum=MUON_MOMENTUM, nesterov=nesterov, weight_decay=wd, scale_mode=mode)
+    po, mo = p0.to(pdtype).clone(), torch.zeros_like(p0, dtype=torch.bfloat16)
+    for i in range(steps):
+        p.grad = grads[i].to(DEV).to(pdtype)         # torch wants a gradient of the parameter's dtype
+        opt.step()
+        MO.muon_step(po, grads[i].to(pdtype), mo, MUON_LR, MUON_MOMENTUM, nesterov, wd, ns_dtype=torch.bfloat16, scale_mode=mode)
+    torch.cuda.synchronize(); pkg.check_status()
+    # momentum: the same bf16 roundings in the same order (a product that lands on a rounding tie may differ by one
+    # unit in the last place between the host's and the GPU's multiply)
+    mom = opt.state[p]["muon_mom"].cpu().view_as(mo).float()
+    assert (mom != mo.float()).float().mean().item() < 1e-3 and MO.rel_l2(mom, mo.float()) < 1e-3
+    start = p0.to(pdtype).float()
+    moved = p.detach().float().cpu() - start
+    ref_moved = torch.from_numpy(gold[f"step_{name}_p"]) - p0           # the reference, fp32 throughout
+    tol = STEP_TOL if pdtype == torch.float32 else 2 * STEP_TOL         # bf16 parameters round every update
+    assert MO.rel_l2(moved, ref_moved) < tol
+    assert MO.rel_l2(moved, po.float() - start) < tol                   # oracle with a bf16 iteration
+
+
+def test_layer_sized_stack_step_and_padding(pkg):
+    # d_ff = 1408 is not a multiple of the 256-row tile: the iteration runs on 1536 padded rows
+    E, H, I = 3, 512, 1408
+    g = torch.Generator().manual_seed(5)
+    p0 = torch.randn(E, H, I, generator=g) * 0.02
+    grad = torch.randn(E, H, I, generator=g)
+    p = torch.nn.Parameter(p0.to(DEV).to(torch.bfloat16))
+    p.grad = grad.to(DEV).to(torch.bfloat16)
+    opt = pkg.FusedMuon([p], lr=0.01, weight_decay=0.0, scale_mode="polar")
+    opt.step()
+    torch.cuda.synchronize(); pkg.check_status()
+    po, mo = p0.to(torch.bfloat16).float(), torch.zeros(E, H, I)
+    MO.muon_step(po, grad.to(torch.bfloat16).float(), mo, 0.01, weight_decay=0.0, ns_dtype=torch.float32,
+                 scale_mode="polar")
+    start = p0.to(torch.bfloat16).float()
+    assert MO.rel_l2(p.detach().float().cpu() - start, po - start) < 2 * STEP_TOL
+
+
+def test_rejected_options(pkg):
+    p = torch.nn.Parameter(torch.zeros(2, 64, 64, device=DEV))
+    for kw in (dict(scale_mode="normuon"), dict(aurora_k=2), dict(ns_dtype=torch.float16), dict(use_graph=True),
+               dict(xorth_post=0.1), dict(spectral_wd=0.1)):
+        with pytest.raises(ValueError):
+            pkg.FusedMuon([p], **kw)
+    with pytest.raises(ValueError):
+        pkg.newton_schulz(torch.zeros(4, 12, 64, device=DEV))          # 12 is not a multiple of 8

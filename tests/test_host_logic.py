@@ -43,3 +43,32 @@ def test_unknown_activation_codes_raise_value_error():
     except ValueError:
         return
     raise AssertionError("act code 9 must be rejected")
+
+
+def test_muon_rejects_what_is_not_built_and_cpu_tensors():
+    """Constructor checks of the optimizer and the device check of newton_schulz run before any launch."""
+    import pytest
+    pkg = importlib.import_module(PKG)
+    p = torch.nn.Parameter(torch.zeros(2, 64, 64))
+    for kw in (dict(scale_mode="normuon"), dict(scale_mode="aurora_ema"), dict(aurora_k=2), dict(ns_dtype=torch.float32),
+               dict(use_graph=True), dict(xorth_post=0.1), dict(spectral_wd=0.1)):
+        with pytest.raises(ValueError):
+            pkg.FusedMuon([p], **kw)
+    opt = pkg.FusedMuon([p], lr=0.1, scale_mode="polar")
+    opt.step()                                   # no gradient: nothing is stepped, nothing is launched
+    assert float(p.detach().abs().sum()) == 0.0 and not opt.state[p]
+    p.grad = torch.ones_like(p)
+    with pytest.raises(ValueError):              # a CPU parameter never reaches the library
+        opt.step()
+    with pytest.raises(ValueError):
+        pkg.newton_schulz(torch.zeros(8, 8))
+
+
+def test_muon_uniform_segment_tables():
+    """The row tables that stand in for a routing decision when the grouped GEMMs run over a stack."""
+    pkg = importlib.import_module(PKG)
+    seg = pkg.muon._uniform_segments(3, 512, "cpu")
+    assert seg.cap == 1536 and seg.E == 3
+    assert seg.poffs.tolist() == [0, 512, 1024, 1536]
+    assert seg.tile_expert.tolist() == [0, 0, 1, 1, 2, 2]
+    assert seg.tile_expert.dtype == torch.int32 and seg.poffs.dtype == torch.int32

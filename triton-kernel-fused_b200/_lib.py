@@ -78,6 +78,15 @@ _SIGNATURES = {
     "b200moe_ep_combine_bwd_pull": (c_int, [c_void_p] * 9 + [c_int, c_int, c_int, c_int64, c_int, c_int64] + [c_void_p] * 3),
     "b200moe_combine": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64, c_void_p, c_void_p]),
     "b200moe_combine_bwd": (c_int, [c_void_p] * 5 + [c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "b200moe_muon_momentum": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_float, c_int, c_void_p]),
+    "b200moe_muon_row_sumsq": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "b200moe_muon_prescale_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_float, c_float, c_void_p, c_void_p,
+                                           c_void_p]),
+    "b200moe_muon_normalise_pack": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_float,
+                                            c_void_p, c_void_p, c_void_p]),
+    "b200moe_axpby_bf16": (c_int, [c_void_p, c_float, c_void_p, c_float, c_void_p, c_int64, c_void_p]),
+    "b200moe_muon_apply": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_float, c_float, c_float,
+                                   c_void_p, c_int, c_void_p]),
 }
 
 EXPORTED = tuple(_SIGNATURES)

@@ -1,0 +1,366 @@
+// Expert-stack optimizer step (Muon): the element-wise and reduction kernels around the Newton-Schulz GEMMs.
+//
+// The reference's step (kernels/sm75/muon.py:300-315 `_compute`, :366-434 `step`) is, per stack of E matrices
+// (E, r, c): decoupled weight decay, momentum (+ Nesterov), orthogonalisation of the momentum by a Newton-Schulz
+// iteration (:62-89 `newton_schulz`: Frobenius normalisation, then X <- a X + (b A + c A A) X with A = X X^T on
+// the smaller Gram side), a scale, and the update of the parameters.  The three matrix products per iteration run on
+// the grouped tcgen05 GEMMs of gemm.cu over a stack whose row segments are padded to the GEMM's 256-row tiles; the
+// kernels here produce that padded (and, for tall matrices, transposed) stack, fold the axpy steps, and apply the
+// result.  All of them are HBM-bound streaming kernels: 16-byte accesses, one pass over their operands.
+//
+// Rounding follows the reference run with a bf16 iteration dtype (its setting for Blackwell,
+// kernels/sm120/muon.py): every tensor the reference materialises in bf16 is rounded at the same place here;
+// norms are accumulated in fp32 (kernels/sm75/muon.py:78).
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200moe {
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+  o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+  return o;
+}
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// buf = mu * buf + g;  u = nesterov ? g + mu * buf : buf   (kernels/sm75/muon.py:389-390), 8 elements per thread.
+// g is first rounded to bf16 (the reference gathers the gradients into a bf16 staging buffer, :386-388).
+template <bool kGradF32>
+__global__ void __launch_bounds__(256) muon_momentum_kernel(const void* __restrict__ grad, uint4* __restrict__ mom,
+                                                            uint4* __restrict__ u, long long nvec, float mu,
+                                                            int nesterov) {
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < nvec; i += gridDim.x * 256LL) {
+    float g[8], m[8], o[8];
+    if (kGradF32) {
+      const float4 g0 = reinterpret_cast<const float4*>(grad)[2 * i], g1 = reinterpret_cast<const float4*>(grad)[2 * i + 1];
+      g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[j] = round_bf16(g[j]);
+    } else {
+      unpack8(reinterpret_cast<const uint4*>(grad)[i], g);
+    }
+    unpack8(mom[i], m);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      m[j] = round_bf16(round_bf16(m[j] * mu) + g[j]);
+      o[j] = nesterov ? g[j] + mu * m[j] : m[j];
+    }
+    mom[i] = pack8(m);
+    u[i] = pack8(o);
+  }
+}
+
+// rowss[row] = sum_j x[row, j]^2 in fp32; one warp per row.
+__global__ void __launch_bounds__(256) muon_row_sumsq_kernel(const uint4* __restrict__ x, long long rows, int vec_per_row,
+                                                             float* __restrict__ rowss) {
+  const int lane = threadIdx.x & 31;
+  for (long long row = blockIdx.x * 8LL + (threadIdx.x >> 5); row < rows; row += gridDim.x * 8LL) {
+    const uint4* src = x + row * vec_per_row;
+    float ss = 0.0f;
+    for (int c = lane; c < vec_per_row; c += 32) {
+      float f[8];
+      unpack8(src[c], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if (lane == 0) rowss[row] = ss;
+  }
+}
+
+// out[row, :] = bf16(x[row, :] * (tgt / max(sqrt(rowss[row]), eps))) and the sum of squares of the rounded row:
+// the row prescale of the reference's default `aurora` mode (kernels/muon/muon_scaling.py:107-112).
+__global__ void __launch_bounds__(256) muon_prescale_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ rowss,
+                                                                 long long rows, int vec_per_row, float tgt, float eps,
+                                                                 uint4* __restrict__ out, float* __restrict__ rowss_out) {
+  const int lane = threadIdx.x & 31;
+  for (long long row = blockIdx.x * 8LL + (threadIdx.x >> 5); row < rows; row += gridDim.x * 8LL) {
+    const float s = tgt / fmaxf(sqrtf(rowss[row]), eps);
+    const uint4* src = x + row * vec_per_row;
+    uint4* dst = out + row * vec_per_row;
+    float ss = 0.0f;
+    for (int c = lane; c < vec_per_row; c += 32) {
+      float f[8];
+      unpack8(src[c], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        f[j] = round_bf16(f[j] * s);
+        ss += f[j] * f[j];
+      }
+      dst[c] = pack8(f);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if (lane == 0) rowss_out[row] = ss;
+  }
+}
+
+// norms[e] = bf16(max(sqrt(sum_i rowss[e, i]), eps)) as a float: the per-matrix Frobenius norm the iteration divides
+// by (kernels/sm75/muon.py:78,82).  One CTA per matrix, fixed summation order (reruns are bit-identical).
+__global__ void __launch_bounds__(256) muon_stack_norms_kernel(const float* __restrict__ rowss, int r, float eps,
+                                                               float* __restrict__ norms) {
+  __shared__ float part[256];
+  const float* src = rowss + static_cast<long long>(blockIdx.x) * r;
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < r; i += 256) s += src[i];
+  part[threadIdx.x] = s;
+  __syncthreads();
+  for (int w = 128; w > 0; w >>= 1) {
+    if (threadIdx.x < w) part[threadIdx.x] += part[threadIdx.x + w];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) norms[blockIdx.x] = round_bf16(fmaxf(sqrtf(part[0]), eps));
+}
+
+// Stack in the layout of the iteration, rows kept: xp (E, Rp, c), xp[e, i, :] = bf16(x[e, i, :] / norms[e]) for
+// i < r and zero rows up to Rp (kernels/sm75/muon.py:82).  One warp per output row.
+__global__ void __launch_bounds__(256) muon_pack_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ norms,
+                                                             int E, int r, int Rp, int vec_per_row,
+                                                             uint4* __restrict__ xp) {
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(E) * Rp;
+  for (long long orow = blockIdx.x * 8LL + (threadIdx.x >> 5); orow < total; orow += gridDim.x * 8LL) {
+    const int e = static_cast<int>(orow / Rp), i = static_cast<int>(orow % Rp);
+    uint4* dst = xp + orow * vec_per_row;
+    if (i >= r) {
+      for (int c = lane; c < vec_per_row; c += 32) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
+    const float nrm = norms[e];
+    const uint4* src = x + (static_cast<long long>(e) * r + i) * vec_per_row;
+    for (int c = lane; c < vec_per_row; c += 32) {
+      float f[8];
+      unpack8(src[c], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = f[j] / nrm;
+      dst[c] = pack8(f);
+    }
+  }
+}
+
+// Tall matrices (r > c) iterate on the transpose (kernels/sm75/muon.py:79-81): xp (E, Rp, r),
+// xp[e, j, i] = bf16(x[e, i, j] / norms[e]) for j < c, zero rows for c <= j < Rp.  64 x 64 tiles through shared
+// memory, 4-byte accesses on both sides.  grid = (ceil(r/64), Rp/64, E).
+__global__ void __launch_bounds__(256) muon_pack_transpose_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                  const float* __restrict__ norms, int r, int c, int Rp,
+                                                                  __nv_bfloat16* __restrict__ xp) {
+  __shared__ float tile[64][65];
+  const int e = blockIdx.z, i0 = blockIdx.x * 64, j0 = blockIdx.y * 64;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const float nrm = norms[e];
+  const __nv_bfloat16* src = x + static_cast<long long>(e) * r * c;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int i = i0 + ty + 8 * k, j = j0 + 2 * tx;
+    float2 v = make_float2(0.0f, 0.0f);
+    if (i < r && j < c) v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + static_cast<long long>(i) * c + j));
+    tile[ty + 8 * k][2 * tx] = v.x / nrm;
+    tile[ty + 8 * k][2 * tx + 1] = v.y / nrm;
+  }
+  __syncthreads();
+  __nv_bfloat16* dst = xp + static_cast<long long>(e) * Rp * r;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int j = j0 + ty + 8 * k, i = i0 + 2 * tx;
+    if (i < r)
+      *reinterpret_cast<__nv_bfloat162*>(dst + static_cast<long long>(j) * r + i) =
+          __floats2bfloat162_rn(tile[2 * tx][ty + 8 * k], tile[2 * tx + 1][ty + 8 * k]);
+  }
+}
+
+// out = bf16(alpha * x + beta * y): the two axpy steps of one iteration (b A + c A A; a X + B X), which the
+// reference folds into its library GEMM calls (kernels/sm75/muon.py:85-86).  out may alias x or y.
+__global__ void __launch_bounds__(256) axpby_bf16_kernel(const uint4* x, float alpha, const uint4* y, float beta,
+                                                         uint4* out, long long nvec) {
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < nvec; i += gridDim.x * 256LL) {
+    float a[8], b[8];
+    unpack8(x[i], a);
+    unpack8(y[i], b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = alpha * a[j] + beta * b[j];
+    out[i] = pack8(a);
+  }
+}
+
+template <bool kPF32>
+__device__ __forceinline__ float load_param(const void* p, long long i) {
+  return kPF32 ? reinterpret_cast<const float*>(p)[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+template <bool kPF32>
+__device__ __forceinline__ float round_param(float v) { return kPF32 ? v : round_bf16(v); }
+template <bool kPF32>
+__device__ __forceinline__ void store_param(void* p, long long i, float v) {
+  if (kPF32) reinterpret_cast<float*>(p)[i] = v;
+  else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+
+// p = round(round(p * decay) + alpha * bf16(gain * o)), o = the orthogonalised stack read back from the iteration's
+// layout (kernels/sm75/muon.py:381,431-434; gain: kernels/muon/muon_scaling.py:112).  Rows kept: o = xp[e, i, j].
+template <bool kPF32>
+__global__ void __launch_bounds__(256) muon_apply_rows_kernel(const __nv_bfloat16* __restrict__ xp, int E, int r, int c,
+                                                              int Rp, float gain, float decay, float alpha, void* p) {
+  const long long total = static_cast<long long>(E) * r * (c / 2);
+  for (long long t = blockIdx.x * 256LL + threadIdx.x; t < total; t += gridDim.x * 256LL) {
+    const int j = static_cast<int>(t % (c / 2)) * 2;
+    const long long row = t / (c / 2);
+    const int e = static_cast<int>(row / r), i = static_cast<int>(row % r);
+    const float2 o = __bfloat1622float2(
+        *reinterpret_cast<const __nv_bfloat162*>(xp + (static_cast<long long>(e) * Rp + i) * c + j));
+    const long long pi = row * c + j;
+    store_param<kPF32>(p, pi, round_param<kPF32>(load_param<kPF32>(p, pi) * decay) + alpha * round_bf16(gain * o.x));
+    store_param<kPF32>(p, pi + 1,
+                       round_param<kPF32>(load_param<kPF32>(p, pi + 1) * decay) + alpha * round_bf16(gain * o.y));
+  }
+}
+
+// Transposed stack: o[e, i, j] = xp[e, j, i] with xp (E, Rp, r).  grid = (ceil(r/64), ceil(c/64), E).
+template <bool kPF32>
+__global__ void __launch_bounds__(256) muon_apply_transpose_kernel(const __nv_bfloat16* __restrict__ xp, int r, int c,
+                                                                   int Rp, float gain, float decay, float alpha,
+                                                                   void* p) {
+  __shared__ float tile[64][65];
+  const int e = blockIdx.z, i0 = blockIdx.x * 64, j0 = blockIdx.y * 64;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const __nv_bfloat16* src = xp + static_cast<long long>(e) * Rp * r;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int j = j0 + ty + 8 * k, i = i0 + 2 * tx;
+    float2 v = make_float2(0.0f, 0.0f);
+    if (j < c && i < r) v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + static_cast<long long>(j) * r + i));
+    tile[ty + 8 * k][2 * tx] = v.x;
+    tile[ty + 8 * k][2 * tx + 1] = v.y;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int i = i0 + ty + 8 * k, j = j0 + 2 * tx;
+    if (i < r && j < c) {
+      const long long pi = (static_cast<long long>(e) * r + i) * c + j;
+      const float o0 = tile[2 * tx][ty + 8 * k], o1 = tile[2 * tx + 1][ty + 8 * k];
+      store_param<kPF32>(p, pi, round_param<kPF32>(load_param<kPF32>(p, pi) * decay) + alpha * round_bf16(gain * o0));
+      store_param<kPF32>(p, pi + 1, round_param<kPF32>(load_param<kPF32>(p, pi + 1) * decay) + alpha * round_bf16(gain * o1));
+    }
+  }
+}
+
+static int stream_grid(long long work_items, int per_cta) {
+  long long grid = (work_items + per_cta - 1) / per_cta;
+  const long long cap = static_cast<long long>(num_sms()) * 16;
+  if (grid > cap) grid = cap;
+  return static_cast<int>(grid < 1 ? 1 : grid);
+}
+
+}  // namespace b200moe
+
+using namespace b200moe;
+
+#define MUON_CHECK_DIMS(who, E, r, c, Rp)                                                                          \
+  B200_CHECK_ARG((E) >= 1 && (E) <= 65535 && (r) > 0 && (c) > 0 && (r) % 8 == 0 && (c) % 8 == 0 &&                 \
+                     (r) < (1LL << 24) && (c) < (1LL << 24),                                                       \
+                 B200MOE_E_BAD_SHAPE, who ": a stack of %d matrices of %lld x %lld (both must be multiples of 8)",  \
+                 (int)(E), (long long)(r), (long long)(c));                                                        \
+  B200_CHECK_ARG((Rp) % B200MOE_TILE_M == 0 && (Rp) >= ((transposed) ? (c) : (r)) && (Rp) < (1LL << 24),           \
+                 B200MOE_E_BAD_SHAPE, who ": padded rows %lld must be a multiple of %d covering the smaller side", \
+                 (long long)(Rp), B200MOE_TILE_M)
+
+extern "C" {
+
+int b200moe_muon_momentum(const void* grad, int grad_f32, void* mom, void* u, int64_t n, float mu, int nesterov,
+                          b200moe_stream_t stream) {
+  B200_CHECK_ARG(grad && mom && u, B200MOE_E_NULL, "muon_momentum: null pointer");
+  B200_CHECK_ARG(n >= 0 && n % 8 == 0, B200MOE_E_BAD_SHAPE, "muon_momentum: n = %lld must be a multiple of 8", (long long)n);
+  B200_CHECK_ARG(aligned16(grad) && aligned16(mom) && aligned16(u), B200MOE_E_ALIGN, "muon_momentum: pointers must be 16-byte aligned");
+  if (n == 0) return 0;
+  const long long nvec = n / 8;
+  const int grid = stream_grid(nvec, 256);
+  if (grad_f32)
+    muon_momentum_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(grad, (uint4*)mom, (uint4*)u, nvec, mu, nesterov);
+  else
+    muon_momentum_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(grad, (uint4*)mom, (uint4*)u, nvec, mu, nesterov);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_muon_row_sumsq(const void* x, int64_t rows, int64_t cols, float* rowss, b200moe_stream_t stream) {
+  B200_CHECK_ARG(x && rowss, B200MOE_E_NULL, "muon_row_sumsq: null pointer");
+  B200_CHECK_ARG(rows >= 0 && cols > 0 && cols % 8 == 0 && cols < (1LL << 24), B200MOE_E_BAD_SHAPE,
+                 "muon_row_sumsq: cols = %lld must be a multiple of 8", (long long)cols);
+  B200_CHECK_ARG(aligned16(x), B200MOE_E_ALIGN, "muon_row_sumsq: x must be 16-byte aligned");
+  if (rows == 0) return 0;
+  muon_row_sumsq_kernel<<<stream_grid(rows, 8), 256, 0, (cudaStream_t)stream>>>((const uint4*)x, rows, (int)(cols / 8), rowss);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_muon_prescale_rows(const void* x, const float* rowss, int64_t rows, int64_t cols, float tgt, float eps,
+                               void* out, float* rowss_out, b200moe_stream_t stream) {
+  B200_CHECK_ARG(x && rowss && out && rowss_out, B200MOE_E_NULL, "muon_prescale_rows: null pointer");
+  B200_CHECK_ARG(rows >= 0 && cols > 0 && cols % 8 == 0 && cols < (1LL << 24), B200MOE_E_BAD_SHAPE,
+                 "muon_prescale_rows: cols = %lld must be a multiple of 8", (long long)cols);
+  B200_CHECK_ARG(aligned16(x) && aligned16(out), B200MOE_E_ALIGN, "muon_prescale_rows: pointers must be 16-byte aligned");
+  if (rows == 0) return 0;
+  muon_prescale_rows_kernel<<<stream_grid(rows, 8), 256, 0, (cudaStream_t)stream>>>(
+      (const uint4*)x, rowss, rows, (int)(cols / 8), tgt, eps, (uint4*)out, rowss_out);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_muon_normalise_pack(const void* x, const float* rowss, int E, int64_t r, int64_t c, int64_t Rp,
+                                int transposed, float eps, float* norms, void* xp, b200moe_stream_t stream) {
+  B200_CHECK_ARG(x && rowss && norms && xp, B200MOE_E_NULL, "muon_normalise_pack: null pointer");
+  MUON_CHECK_DIMS("muon_normalise_pack", E, r, c, Rp);
+  B200_CHECK_ARG(aligned16(x) && aligned16(xp), B200MOE_E_ALIGN, "muon_normalise_pack: pointers must be 16-byte aligned");
+  muon_stack_norms_kernel<<<E, 256, 0, (cudaStream_t)stream>>>(rowss, (int)r, eps, norms);
+  if (transposed) {
+    dim3 grid((unsigned)((r + 63) / 64), (unsigned)(Rp / 64), (unsigned)E);
+    muon_pack_transpose_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, norms, (int)r, (int)c,
+                                                                       (int)Rp, (__nv_bfloat16*)xp);
+  } else {
+    muon_pack_rows_kernel<<<stream_grid((long long)E * Rp, 8), 256, 0, (cudaStream_t)stream>>>(
+        (const uint4*)x, norms, E, (int)r, (int)Rp, (int)(c / 8), (uint4*)xp);
+  }
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_axpby_bf16(const void* x, float alpha, const void* y, float beta, void* out, int64_t n,
+                       b200moe_stream_t stream) {
+  B200_CHECK_ARG(x && y && out, B200MOE_E_NULL, "axpby_bf16: null pointer");
+  B200_CHECK_ARG(n >= 0 && n % 8 == 0, B200MOE_E_BAD_SHAPE, "axpby_bf16: n = %lld must be a multiple of 8", (long long)n);
+  B200_CHECK_ARG(aligned16(x) && aligned16(y) && aligned16(out), B200MOE_E_ALIGN, "axpby_bf16: pointers must be 16-byte aligned");
+  if (n == 0) return 0;
+  axpby_bf16_kernel<<<stream_grid(n / 8, 256), 256, 0, (cudaStream_t)stream>>>((const uint4*)x, alpha, (const uint4*)y, beta,
+                                                                               (uint4*)out, n / 8);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_muon_apply(const void* xp, int E, int64_t r, int64_t c, int64_t Rp, int transposed, float gain, float decay,
+                       float alpha, void* p, int p_f32, b200moe_stream_t stream) {
+  B200_CHECK_ARG(xp && p, B200MOE_E_NULL, "muon_apply: null pointer");
+  MUON_CHECK_DIMS("muon_apply", E, r, c, Rp);
+  B200_CHECK_ARG(aligned16(xp) && aligned16(p), B200MOE_E_ALIGN, "muon_apply: pointers must be 16-byte aligned");
+  const cudaStream_t s = (cudaStream_t)stream;
+  const __nv_bfloat16* o = (const __nv_bfloat16*)xp;
+  if (transposed) {
+    dim3 grid((unsigned)((r + 63) / 64), (unsigned)((c + 63) / 64), (unsigned)E);
+    if (p_f32) muon_apply_transpose_kernel<true><<<grid, 256, 0, s>>>(o, (int)r, (int)c, (int)Rp, gain, decay, alpha, p);
+    else muon_apply_transpose_kernel<false><<<grid, 256, 0, s>>>(o, (int)r, (int)c, (int)Rp, gain, decay, alpha, p);
+  } else {
+    const int grid = stream_grid((long long)E * r * (c / 2), 256);
+    if (p_f32) muon_apply_rows_kernel<true><<<grid, 256, 0, s>>>(o, E, (int)r, (int)c, (int)Rp, gain, decay, alpha, p);
+    else muon_apply_rows_kernel<false><<<grid, 256, 0, s>>>(o, E, (int)r, (int)c, (int)Rp, gain, decay, alpha, p);
+  }
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

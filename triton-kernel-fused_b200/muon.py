@@ -1,0 +1,199 @@
+"""Expert-stack optimizer step (Muon) on the grouped tcgen05 GEMMs: the consumer of the MoE layer's weight gradients.
+
+Mirrors kernels/sm75/muon.py of the reference: `newton_schulz(G, coeffs, ns_dtype, eps)` (:62-89) and the
+optimizer class `FusedMuon` (:91) with its `step` (:366-434), for the scale modes "polar" and "aurora" (the
+reference's default, K = 1) and a bf16 iteration dtype (the reference's setting for Blackwell,
+kernels/sm120/muon.py).  A stack (E, r, c) is orthogonalised as E independent matrices; the three products of each
+Newton-Schulz iteration run as grouped GEMMs over a stack whose E row segments are padded to the 256-row GEMM tile,
+everything around them (momentum, norms, row prescale, packing/transposing, axpy, weight update) as streaming
+kernels.  The step's arithmetic all goes through the C ABI; torch only allocates.
+
+Not carried over (ValueError): scale modes "normuon" / "aurora_ema*", aurora_k != 1, cross-expert whitening
+(xorth_post), spectral weight decay, fp16 / fp32 iteration dtypes, `use_graph`, `DistributedMuon`.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib as L
+from . import ops
+
+__all__ = ["newton_schulz", "FusedMuon", "DSV4_COEFFS"]
+
+# the reference's default coefficient schedule (kernels/sm75/muon.py:50)
+DSV4_COEFFS = ((3.4445, -4.7750, 2.0315),) * 8 + ((2.0, -1.5, 0.5),) * 2
+RMS_TARGET = 0.2      # kernels/muon/muon_scaling.py:33
+ROW_EPS = 1e-8        # kernels/muon/muon_scaling.py:36
+TILE = ops.TILE_M
+
+_segments = {}
+
+
+def _uniform_segments(E: int, Rp: int, device) -> ops.Permutation:
+    """Row tables of a stack of E equal segments of Rp rows (Rp a multiple of the GEMM tile): what the grouped
+    GEMMs read instead of a routing decision."""
+    key = (E, Rp, torch.device(device).index)
+    seg = _segments.get(key)
+    if seg is None:
+        i32 = dict(dtype=torch.int32, device=device)
+        poffs = torch.arange(E + 1, **i32) * Rp
+        tile_expert = torch.arange(E, **i32).repeat_interleave(Rp // TILE)
+        counts = torch.full((E,), Rp, **i32)
+        seg = ops.Permutation(T=0, k=1, E=E, cap=E * Rp, counts=counts, offs=poffs, poffs=poffs, slot_row=None,
+                              row_slot=None, tile_expert=tile_expert, order=None, slot_pos=None)
+        _segments[key] = seg
+    return seg
+
+
+def _check_stack(name: str, t: torch.Tensor):
+    L.require(t.is_cuda, f"{name} must be a CUDA tensor (this package has no CPU path)")
+    L.require(t.dim() in (2, 3), f"{name} must be a matrix or a stack of matrices, got {t.dim()} dimensions")
+    r, c = t.shape[-2], t.shape[-1]
+    L.require(r % 8 == 0 and c % 8 == 0, f"{name}: both matrix dimensions must be multiples of 8, got {r} x {c}")
+    return (t.shape[0] if t.dim() == 3 else 1), r, c
+
+
+@ops._op("muon_momentum", 1)
+def _momentum(grad, mom, mu, nesterov):
+    u = torch.empty_like(mom)
+    L.check(L.lib().b200moe_muon_momentum(L.ptr(grad), 1 if grad.dtype == torch.float32 else 0, L.ptr(mom), L.ptr(u),
+                                          mom.numel(), float(mu), 1 if nesterov else 0, L.stream_of(mom)))
+    return u
+
+
+@ops._op("muon_row_sumsq", 1)
+def _row_sumsq(x, rows, cols):
+    out = torch.empty(rows, dtype=torch.float32, device=x.device)
+    L.check(L.lib().b200moe_muon_row_sumsq(L.ptr(x), rows, cols, L.ptr(out), L.stream_of(x)))
+    return out
+
+
+@ops._op("muon_prescale_rows", 1)
+def _prescale_rows(x, rowss, rows, cols, tgt):
+    out = torch.empty_like(x)
+    ss = torch.empty_like(rowss)
+    L.check(L.lib().b200moe_muon_prescale_rows(L.ptr(x), L.ptr(rowss), rows, cols, float(tgt), ROW_EPS, L.ptr(out),
+                                               L.ptr(ss), L.stream_of(x)))
+    return out, ss
+
+
+@ops._op("muon_normalise_pack", 2)
+def _normalise_pack(x, rowss, E, r, c, Rp, tall, eps):
+    xp = torch.empty(E, Rp, r if tall else c, dtype=torch.bfloat16, device=x.device)
+    norms = torch.empty(E, dtype=torch.float32, device=x.device)
+    L.check(L.lib().b200moe_muon_normalise_pack(L.ptr(x), L.ptr(rowss), E, r, c, Rp, 1 if tall else 0, float(eps),
+                                                L.ptr(norms), L.ptr(xp), L.stream_of(x)))
+    return xp
+
+
+@ops._op("axpby", 1)
+def _axpby(x, alpha, y, beta, out):
+    L.check(L.lib().b200moe_axpby_bf16(L.ptr(x), float(alpha), L.ptr(y), float(beta), L.ptr(out), x.numel(),
+                                       L.stream_of(x)))
+    return out
+
+
+@ops._op("muon_apply", 1)
+def _apply(xp, E, r, c, Rp, tall, gain, decay, alpha, p):
+    L.check(L.lib().b200moe_muon_apply(L.ptr(xp), E, r, c, Rp, 1 if tall else 0, float(gain), float(decay),
+                                       float(alpha), L.ptr(p), 1 if p.dtype == torch.float32 else 0, L.stream_of(p)))
+
+
+def _orthogonalise_packed(u, E, r, c, coeffs, eps, rowss=None):
+    """u (E, r, c) bf16 (rowss: its per-row sums of squares, if already known) -> the iterated stack in the
+    iteration's layout (E, Rp, max(r,c)), its row padding Rp and whether it is transposed.
+    kernels/sm75/muon.py:78-86."""
+    tall = r > c
+    small, wide = (c, r) if tall else (r, c)
+    Rp = -(-small // TILE) * TILE
+    if rowss is None:
+        rowss = _row_sumsq(u, E * r, c)
+    X = _normalise_pack(u, rowss, E, r, c, Rp, tall, eps)
+    return _iterate(X, E, Rp, wide, coeffs), Rp, tall
+
+
+def _iterate(X, E, Rp, wide, coeffs):
+    seg = _uniform_segments(E, Rp, X.device)
+    rows = E * Rp
+    A = torch.empty(rows, Rp, dtype=torch.bfloat16, device=X.device)
+    A2 = torch.empty_like(A)
+    BX = torch.empty(rows, wide, dtype=torch.bfloat16, device=X.device)
+    Xr = X.view(rows, wide)
+    for a, b, c in coeffs:
+        ops.expert_linear(Xr, X, seg, out=A)                      # A = X X^T
+        ops.expert_linear(A, A.view(E, Rp, Rp), seg, out=A2)      # A A^T = A A (A is symmetric)
+        _axpby(A, b, A2, c, A2)                                   # B = b A + c A A
+        ops.expert_linear_t(A2, X, seg, out=BX)                   # B X
+        _axpby(Xr, a, BX, 1.0, Xr)                                # X = a X + B X
+    return X
+
+
+def newton_schulz(G: torch.Tensor, coeffs=DSV4_COEFFS, ns_dtype=torch.bfloat16, eps: float = 1e-7) -> torch.Tensor:
+    """Orthogonalise every matrix of G ((r,c) or (E,r,c), CUDA, bf16 or fp32); same call as the reference's
+    `newton_schulz` (kernels/sm75/muon.py:62).  Returns G's dtype and shape."""
+    L.require(ns_dtype == torch.bfloat16, f"the iteration runs in bfloat16 only, got ns_dtype={ns_dtype}")
+    E, r, c = _check_stack("G", G)
+    L.require(G.dtype in (torch.bfloat16, torch.float32), f"G must be bfloat16 or float32, got {G.dtype}")
+    u = G.detach().to(torch.bfloat16).contiguous().view(E, r, c)
+    X, Rp, tall = _orthogonalise_packed(u, E, r, c, coeffs, eps)
+    out = torch.zeros(E, r, c, dtype=G.dtype, device=G.device)
+    _apply(X, E, r, c, Rp, tall, 1.0, 1.0, 1.0, out)              # out = 0 + 1 * X, laid back out as (E, r, c)
+    return out.view(G.shape)
+
+
+class FusedMuon(torch.optim.Optimizer):
+    """Muon for matrices and stacks of matrices; constructor and state follow the reference's `FusedMuon`
+    (kernels/sm75/muon.py:91-137).  Parameters are CUDA tensors, bf16 or fp32 (fp32 master weights), 2-D or 3-D,
+    with gradients in bf16 or fp32; the momentum buffer `muon_mom` is bf16 (the iteration dtype) and is kept per
+    parameter, shaped (E, r, c)."""
+
+    DEFAULT_NS_DTYPE = torch.bfloat16
+
+    def __init__(self, params, lr=3e-4, momentum=0.95, nesterov=True, weight_decay=0.0, coeffs=DSV4_COEFFS,
+                 ns_dtype=None, scale_mode="aurora", use_graph=False, aurora_k=None, spectral_wd=0.0, xorth_post=0.0):
+        if scale_mode not in ("polar", "aurora"):
+            raise ValueError(f"scale_mode {scale_mode!r} is not built here; use 'polar' or 'aurora'")
+        if aurora_k not in (None, 1):
+            raise ValueError("only aurora_k = 1 (the reference's default) is built here")
+        if spectral_wd != 0 or xorth_post != 0 or use_graph:
+            raise ValueError("spectral_wd, xorth_post and use_graph are not built here")
+        ns_dtype = self.DEFAULT_NS_DTYPE if ns_dtype is None else ns_dtype
+        if ns_dtype != torch.bfloat16:
+            raise ValueError(f"the iteration runs in bfloat16 only, got ns_dtype={ns_dtype}")
+        super().__init__(params, dict(lr=lr, momentum=momentum, nesterov=nesterov, weight_decay=weight_decay))
+        self.coeffs, self.ns_dtype, self.scale_mode = coeffs, ns_dtype, scale_mode
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            lr, mu, wd, nesterov = group["lr"], group["momentum"], group["weight_decay"], group["nesterov"]
+            for p in group["params"]:
+                if p.grad is None or p.dim() not in (2, 3):      # as the reference: other shapes are not stepped
+                    continue
+                self._step_one(p, lr, mu, wd, nesterov)
+        return loss
+
+    def _step_one(self, p, lr, mu, wd, nesterov):
+        E, r, c = _check_stack("parameter", p)
+        g = p.grad
+        L.require(p.is_contiguous(), "parameters must be contiguous")
+        L.require(p.dtype in (torch.bfloat16, torch.float32) and g.dtype in (torch.bfloat16, torch.float32),
+                  f"parameters and gradients must be bfloat16 or float32, got {p.dtype} / {g.dtype}")
+        g = g.contiguous()
+        st = self.state[p]
+        if "muon_mom" not in st:
+            st["muon_mom"] = torch.zeros(E, r, c, dtype=torch.bfloat16, device=p.device)
+        u = _momentum(g, st["muon_mom"], mu, nesterov)
+        if self.scale_mode == "aurora":                           # kernels/muon/muon_scaling.py:101-112
+            tgt = (min(r, c) / r) ** 0.5
+            u, rowss = _prescale_rows(u, _row_sumsq(u, E * r, c), E * r, c, tgt)
+            gain, alpha = RMS_TARGET * max(r, c) ** 0.5, -lr
+        else:                                                     # kernels/muon/muon_scaling.py:79-83
+            rowss = None
+            gain, alpha = 1.0, -lr * RMS_TARGET * max(r, c) ** 0.5
+        X, Rp, tall = _orthogonalise_packed(u, E, r, c, self.coeffs, 1e-7, rowss)
+        _apply(X, E, r, c, Rp, tall, gain, 1.0 - lr * wd, alpha, p)
