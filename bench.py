@@ -359,6 +359,8 @@ def run_muon(args):
     pkg.lib()
     ops = pkg.ops
     H, E, I = HEADLINE["H"], HEADLINE["E"], HEADLINE["I"]
+    if args.workload == "muon_profile":     # small case for profiler captures: 8 experts, under 1 GB on the device
+        E = 8
     shapes = [(E, 2 * I, H), (E, H, I)]
     g = torch.Generator(device=dev).manual_seed(3)
     params = [torch.nn.Parameter((torch.randn(*sh, device=dev, generator=g) * 0.02).to(torch.bfloat16)) for sh in shapes]
@@ -390,7 +392,7 @@ def run_muon(args):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1)
 
-    n_warm = max(args.warmup, 3)
+    n_warm = args.warmup if args.workload.endswith("profile") else max(args.warmup, 3)
     for _ in range(n_warm):
         step_resident()
     pkg.check_status()
@@ -415,7 +417,7 @@ def run_muon(args):
     for (n, r, c) in shapes:
         s_, w_ = min(r, c), max(r, c)
         flops += n * iters * (4.0 * s_ * s_ * w_ + 2.0 * s_ ** 3)
-    gemm_names = [n for n in ("expert_linear", "expert_linear_t") if n in per_op]
+    gemm_names = [n for n in ("expert_linear", "expert_linear_axpby", "expert_linear_t") if n in per_op]
     gemm_ms = sum(per_op[n][0] for n in gemm_names) / args.steps
     peaks = _peaks("bf16")
     kernels = {name: dict(launches_per_step=n / args.steps, avg_ms=round(ms / n, 4), share=round(ms / ms_total, 4))
@@ -431,7 +433,7 @@ def run_muon(args):
                    "l2": "no flush: every stack (0.4-0.7 GB) exceeds the 126 MB L2"},
         "step_tflops": round(flops / (ms_step * 1e-3) / 1e12, 1),
         "gemm_ms_per_step": round(gemm_ms, 3),
-        "roofline": {"bound": "tensor", "kernel": "gemm_kernel via expert_linear / expert_linear_t (Newton-Schulz products)",
+        "roofline": {"bound": "tensor", "kernel": "gemm_kernel via expert_linear / expert_linear_axpby / expert_linear_t (Newton-Schulz products)",
                      "achieved": round(achieved, 1), "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": round(achieved / peaks["tflops"], 4), "traffic": None, "peak_source": peaks["source"]},
         "kernels": kernels,
@@ -495,12 +497,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="headline", choices=["headline", "profile", "ep5", "mxfp8", "mxfp8_profile", "zipf", "muon"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "profile", "ep5", "mxfp8", "mxfp8_profile", "zipf", "muon", "muon_profile"],
                     help="profile = small case for profiler captures (not a benchmark number)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload == "muon":
+    elif args.workload.startswith("muon"):
         run_muon(args)
     else:
         run_ours(args)

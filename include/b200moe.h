@@ -339,10 +339,20 @@ int b200moe_muon_prescale_rows(const void* x, const float* rowss, int64_t rows, 
 int b200moe_muon_normalise_pack(const void* x, const float* rowss, int E, int64_t r, int64_t c, int64_t Rp,
                                 int transposed, float eps, float* norms, void* xp, b200moe_stream_t stream);
 
-/* out = bf16(alpha*x + beta*y), n elements; out may alias x or y.  The axpy halves of the reference's baddbmm calls
- * (kernels/sm75/muon.py:85-86). */
-int b200moe_axpby_bf16(const void* x, float alpha, const void* y, float beta, void* out, int64_t n,
-                       b200moe_stream_t stream);
+/* out (rows,N) = bf16(alpha * (a (rows,K) @ W[e]^T) + beta * c + diag * I_e): b200moe_expert_linear with the
+ * reference's baddbmm epilogue (kernels/sm75/muon.py:85: b*A + c*(A@A)) and an identity term on each group's own
+ * diagonal (column == row - poffs[e]) folded into the GEMM's store.  c: (rows,N) bf16, read-only, must not alias out.
+ * N a multiple of 256.  With a = c = the Gram matrices A, W = A, alpha = c, beta = b, diag = a it produces the whole
+ * left factor (b A + c A A + a I) of one Newton-Schulz iteration. */
+int b200moe_expert_linear_axpby(const void* a, const void* w, const void* c, float alpha, float beta, float diag,
+                                const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E, int64_t N,
+                                int64_t K, void* out, int32_t* status, b200moe_stream_t stream);
+
+/* out = bf16(alpha*x + beta*y + diag*I), n elements seen as a stack of ld x ld matrices (ld = 0: no identity term);
+ * out may alias x or y.  The axpy halves of the reference's baddbmm calls (kernels/sm75/muon.py:85-86): with
+ * alpha = b, beta = c, diag = a it builds (b A + c A A) + a I, whose product with X is a X + (b A + c A A) X. */
+int b200moe_axpby_bf16(const void* x, float alpha, const void* y, float beta, float diag, int64_t ld, void* out,
+                       int64_t n, b200moe_stream_t stream);
 
 /* p = round(round(p*decay) + alpha * bf16(gain*o)), o[e,i,j] = xp[e,i,j] (xp (E,Rp,c)) or xp[e,j,i] (transposed,
  * xp (E,Rp,r)); p (E,r,c) fp32 if p_f32 else bf16.  Decoupled weight decay + update (kernels/sm75/muon.py:381,

@@ -74,3 +74,23 @@ def test_expert_linear_push_equals_store_then_scatter(pkg, T, E, k, N, K, w_kn):
     keep = live & ~drop
     expect[slots[keep].long()] = ref_rows[keep]
     assert torch.equal(recv, expect)
+
+
+@pytest.mark.parametrize("E,R,K", [(3, 256, 96), (2, 512, 512), (5, 1536, 264)])
+def test_expert_linear_axpby_epilogue(pkg, E, R, K):
+    """alpha * (a @ W[e]^T) + beta * c + diag * I on uniform row segments against the plain grouped GEMM followed
+    by the same arithmetic in fp32 (the fused epilogue rounds once, so it is compared with the fp32 result)."""
+    seg = pkg.muon._uniform_segments(E, R, DEV)
+    a = _rand(E * R, K, seed=21).to(DEV) * 0.1
+    w = _rand(E, R, K, seed=22).to(DEV) * 0.1
+    c = _rand(E * R, R, seed=23).to(DEV)
+    alpha, beta, diag = 2.0315, -4.775, 3.4445
+    out = torch.full((E * R, R), 9.0, dtype=torch.bfloat16, device=DEV)
+    pkg.ops.expert_linear_axpby(a, w, c, alpha, beta, diag, seg, out)
+    torch.cuda.synchronize()
+    pkg.check_status()
+    prod = torch.bmm(a.float().view(E, R, K), w.float().transpose(1, 2))
+    ref = alpha * prod + beta * c.float().view(E, R, R) + diag * torch.eye(R, device=DEV)
+    assert O.rel_l2(out.float().view(E, R, R).cpu(), ref.cpu()) < TOL
+    plain = pkg.ops.expert_linear(a, w, seg).float().view(E, R, R)      # and the unfused product is what it scales
+    assert O.rel_l2(plain.cpu(), prod.cpu()) < TOL

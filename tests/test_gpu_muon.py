@@ -2,7 +2,7 @@
 of the reference's own code (tests/golden/muon.npz).
 
 The iteration runs in bf16 on the GPU.  Ten quintic steps with the default coefficients amplify rounding noise of
-the small singular directions, so a bf16 run is compared (a) with the fp32 result at 1e-1 relative L2, (b) by the
+the small singular directions, so a bf16 run is compared (a) with the fp32 result at 3e-2 relative L2, (b) by the
 reference's own stability gate for its low-precision iteration (bench.py:1054-1058: no NaN, mean singular value in
 [0.8, 1.2]), and (c) exactly where the arithmetic is exact or rounds at the same places: momentum buffers, pad
 rows, reruns."""
@@ -18,7 +18,7 @@ from tests.golden.cases import (MUON_LR, MUON_MOMENTUM, MUON_NS_CASES, MUON_STEP
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
-NS_TOL = 1e-1       # bf16 iteration against the fp32 iteration, relative L2
+NS_TOL = 3e-2       # bf16 iteration against the fp32 iteration, relative L2 (measured 6e-3 ... 7e-3)
 STEP_TOL = 1e-1     # the same for the update p_new - p_old of a step
 
 

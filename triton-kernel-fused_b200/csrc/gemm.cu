@@ -295,7 +295,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // stores (which clip at the tensor's bounds, so no row or column masks are needed)
         uint8_t* sbuf = bufG;   // this warp's staging box
         const int grp = (p.sched == SCHED_GROUPED_K) ? t.g : 0;
-        if constexpr (EPI == EPI_STORE) {
+        if constexpr (EPI == EPI_STORE || EPI == EPI_AXPBY) {
           constexpr int W = BN / 2;
           // push mode: this lane's output row goes to a slot of another GPU's (or this GPU's) receive buffer
           uint8_t* push_dst = nullptr;
@@ -304,6 +304,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (rk >= 0)
               push_dst = reinterpret_cast<uint8_t*>(p.push_base[rk]) + static_cast<long long>(p.push_slot[row]) * p.N * 2;
           }
+          const int ax_drow = (EPI == EPI_AXPBY) ? static_cast<int>(row) - p.poffs[t.g] : 0;   // row inside its group
 #pragma unroll 1
           for (int c = half * W; c < (half + 1) * W; c += 64) {
             if (t.n0 + c >= p.N) break;
@@ -317,6 +318,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               } else {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) r[i] = 0u;
+              }
+              if constexpr (EPI == EPI_AXPBY) {
+                // r = alpha * acc + beta * C[row, columns] (+ diag on the group's own diagonal); the lane reads the
+                // 64 bytes of its row of C that lie under this sub-chunk
+                const int col0 = t.n0 + c + 32 * sub;
+                const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.aux) +
+                                                                  row * p.N + col0);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                  const uint4 cv = src[v];
+                  const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+                  for (int h = 0; h < 4; ++h) {
+                    const float2 cf = unpack_bf16x2(cw[h]);
+                    const int i = 8 * v + 2 * h;
+                    float v0 = p.ax_alpha * __uint_as_float(r[i]) + p.ax_beta * cf.x;
+                    float v1 = p.ax_alpha * __uint_as_float(r[i + 1]) + p.ax_beta * cf.y;
+                    if (col0 + i == ax_drow) v0 += p.ax_diag;
+                    if (col0 + i + 1 == ax_drow) v1 += p.ax_diag;
+                    r[i] = __float_as_uint(v0);
+                    r[i + 1] = __float_as_uint(v1);
+                  }
+                }
               }
 #pragma unroll
               for (int i = 0; i < 16; ++i)
@@ -685,6 +709,11 @@ static int dispatch_bn(int bn, const Operand& A, const Operand& B, const Operand
     }
   }
   if (pair) return launch<256, EPI, 2>(tmA, tmB, tmD, tmD2, p, max_tiles > 0 ? (max_tiles + 1) / 2 : 0, stream);
+  if constexpr (EPI == EPI_AXPBY) {   // built for the 256-wide TMA-store epilogue only
+    if (bn == 256) return launch<256, EPI, 1>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
+    set_error("tile width %d not built for this epilogue", bn);
+    return B200MOE_E_UNSUPPORTED;
+  } else
   switch (bn) {
     case 256: return launch<256, EPI, 1>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
     case 128: return launch<128, EPI, 1>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
@@ -801,6 +830,24 @@ int b200moe_expert_linear(const void* a, const void* w, const int32_t* tile_expe
   p.tile_expert = tile_expert; p.poffs = poffs; p.D = out; p.ldd = N; p.status = status;
   Operand d{out, 0, rows_cap, N, N, 1, rows_cap * N};
   return dispatch_bn<EPI_STORE>(pick_bn(N) == 64 ? 128 : pick_bn(N), oa, ob, &d, nullptr, p, 0, (cudaStream_t)stream);
+}
+
+int b200moe_expert_linear_axpby(const void* a, const void* w, const void* c, float alpha, float beta, float diag,
+                                const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E, int64_t N,
+                                int64_t K, void* out, int32_t* status, b200moe_stream_t stream) {
+  int rc = check_grouped("expert_linear_axpby", a, w, out, tile_expert, poffs, rows_cap, E, N, K);
+  if (rc) return rc;
+  B200_CHECK_ARG(tile_expert && c, B200MOE_E_NULL, "expert_linear_axpby: null pointer");
+  B200_CHECK_ARG(N % 256 == 0, B200MOE_E_BAD_SHAPE, "expert_linear_axpby: N = %lld must be a multiple of 256", (long long)N);
+  B200_CHECK_ARG(aligned16(out) && aligned16(c), B200MOE_E_ALIGN, "expert_linear_axpby: pointers must be 16-byte aligned");
+  Operand oa{a, 0, rows_cap, K, K, 1, rows_cap * K};
+  Operand ob{w, 0, N, K, K, E, N * K};   // W (E, N, K): rows = output columns
+  GemmParams p{};
+  p.sched = SCHED_GROUPED_M; p.N = (int)N; p.K = (int)K; p.num_groups = E;
+  p.tile_expert = tile_expert; p.poffs = poffs; p.D = out; p.ldd = N; p.status = status;
+  p.aux = const_cast<void*>(c); p.ax_alpha = alpha; p.ax_beta = beta; p.ax_diag = diag;
+  Operand d{out, 0, rows_cap, N, N, 1, rows_cap * N};
+  return dispatch_bn<EPI_AXPBY>(256, oa, ob, &d, nullptr, p, 0, (cudaStream_t)stream);
 }
 
 int b200moe_expert_linear_t(const void* a, const void* w, const int32_t* tile_expert, const int32_t* poffs,

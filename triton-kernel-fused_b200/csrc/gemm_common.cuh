@@ -11,7 +11,7 @@
 namespace b200moe {
 
 enum : int { SCHED_DENSE = 0, SCHED_GROUPED_M = 1, SCHED_GROUPED_K = 2 };
-enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_GLU_BWD = 2, EPI_STORE_F32 = 3 };
+enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_GLU_BWD = 2, EPI_STORE_F32 = 3, EPI_AXPBY = 4 };
 
 constexpr int BM = 128;  // rows per CTA = TMEM lanes
 constexpr int kEpiWarps = 8;
@@ -31,8 +31,10 @@ struct GemmParams {
   void* D;
   long long ldd;
   long long d_group_stride;  // GROUPED_K: elements between D[e] and D[e+1]
-  void* aux;                 // SwiGLU: inter (rows, I); GLU_BWD: saved gate_up (rows, 2I)
+  void* aux;                 // SwiGLU: inter (rows, I); GLU_BWD: saved gate_up (rows, 2I); AXPBY: C (rows, N)
   int I;
+  // EPI_AXPBY (256-wide tiles): D = ax_alpha * (A B) + ax_beta * C + ax_diag * [column == row - poffs[group]]
+  float ax_alpha, ax_beta, ax_diag;
   int* status;
   // optional, EPI_STORE with 256-wide tiles: output row r is not stored to D but sent to
   // push_base[push_rank[r]] + push_slot[r] * N elements (a peer GPU's buffer); rows with push_rank < 0 are dropped

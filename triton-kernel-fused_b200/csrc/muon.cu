@@ -176,16 +176,27 @@ __global__ void __launch_bounds__(256) muon_pack_transpose_kernel(const __nv_bfl
   }
 }
 
-// out = bf16(alpha * x + beta * y): the two axpy steps of one iteration (b A + c A A; a X + B X), which the
-// reference folds into its library GEMM calls (kernels/sm75/muon.py:85-86).  out may alias x or y.
+// out = bf16(alpha * x + beta * y + diag * I) over a stack of ld x ld matrices (ld = 0: plain vectors, no identity
+// term).  One pass builds the whole left factor of an iteration: the reference's X <- a X + (b A + c A A) X
+// (kernels/sm75/muon.py:85-86) is evaluated as ((b A + c A A) + a I) X, so the a X term rides on the GEMM and costs no
+// pass over X.  out may alias x or y.
 __global__ void __launch_bounds__(256) axpby_bf16_kernel(const uint4* x, float alpha, const uint4* y, float beta,
-                                                         uint4* out, long long nvec) {
+                                                         float diag, int ld, uint4* out, long long nvec) {
   for (long long i = blockIdx.x * 256LL + threadIdx.x; i < nvec; i += gridDim.x * 256LL) {
     float a[8], b[8];
     unpack8(x[i], a);
     unpack8(y[i], b);
 #pragma unroll
     for (int j = 0; j < 8; ++j) a[j] = alpha * a[j] + beta * b[j];
+    if (ld > 0) {
+      const long long e0 = i * 8;                       // ld is a multiple of 8: the 8 elements share a row
+      const int col0 = static_cast<int>(e0 % ld), row = static_cast<int>((e0 / ld) % ld);
+      if (row >= col0 && row < col0 + 8) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (col0 + j == row) a[j] += diag;
+      }
+    }
     out[i] = pack8(a);
   }
 }
@@ -331,14 +342,16 @@ int b200moe_muon_normalise_pack(const void* x, const float* rowss, int E, int64_
   return 0;
 }
 
-int b200moe_axpby_bf16(const void* x, float alpha, const void* y, float beta, void* out, int64_t n,
-                       b200moe_stream_t stream) {
+int b200moe_axpby_bf16(const void* x, float alpha, const void* y, float beta, float diag, int64_t ld, void* out,
+                       int64_t n, b200moe_stream_t stream) {
   B200_CHECK_ARG(x && y && out, B200MOE_E_NULL, "axpby_bf16: null pointer");
   B200_CHECK_ARG(n >= 0 && n % 8 == 0, B200MOE_E_BAD_SHAPE, "axpby_bf16: n = %lld must be a multiple of 8", (long long)n);
+  B200_CHECK_ARG(ld >= 0 && ld % 8 == 0 && ld < (1LL << 24) && (ld == 0 || n % (ld * ld) == 0), B200MOE_E_BAD_SHAPE,
+                 "axpby_bf16: ld = %lld must be a multiple of 8 and n a whole number of ld x ld matrices", (long long)ld);
   B200_CHECK_ARG(aligned16(x) && aligned16(y) && aligned16(out), B200MOE_E_ALIGN, "axpby_bf16: pointers must be 16-byte aligned");
   if (n == 0) return 0;
   axpby_bf16_kernel<<<stream_grid(n / 8, 256), 256, 0, (cudaStream_t)stream>>>((const uint4*)x, alpha, (const uint4*)y, beta,
-                                                                               (uint4*)out, n / 8);
+                                                                               diag, (int)ld, (uint4*)out, n / 8);
   B200_CUDA(cudaGetLastError());
   return 0;
 }

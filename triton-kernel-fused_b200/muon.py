@@ -87,9 +87,9 @@ def _normalise_pack(x, rowss, E, r, c, Rp, tall, eps):
 
 
 @ops._op("axpby", 1)
-def _axpby(x, alpha, y, beta, out):
-    L.check(L.lib().b200moe_axpby_bf16(L.ptr(x), float(alpha), L.ptr(y), float(beta), L.ptr(out), x.numel(),
-                                       L.stream_of(x)))
+def _axpby(x, alpha, y, beta, out, diag=0.0, ld=0):
+    L.check(L.lib().b200moe_axpby_bf16(L.ptr(x), float(alpha), L.ptr(y), float(beta), float(diag), ld, L.ptr(out),
+                                       x.numel(), L.stream_of(x)))
     return out
 
 
@@ -113,18 +113,19 @@ def _orthogonalise_packed(u, E, r, c, coeffs, eps, rowss=None):
 
 
 def _iterate(X, E, Rp, wide, coeffs):
+    """X <- a X + (b A + c A A) X with A = X X^T (kernels/sm75/muon.py:83-86), evaluated as ((b A + c A A) + a I) X:
+    three grouped GEMMs per iteration and no element-wise pass, X ping-pongs between two buffers."""
     seg = _uniform_segments(E, Rp, X.device)
     rows = E * Rp
     A = torch.empty(rows, Rp, dtype=torch.bfloat16, device=X.device)
     A2 = torch.empty_like(A)
-    BX = torch.empty(rows, wide, dtype=torch.bfloat16, device=X.device)
-    Xr = X.view(rows, wide)
+    Xn = torch.empty_like(X)
     for a, b, c in coeffs:
-        ops.expert_linear(Xr, X, seg, out=A)                      # A = X X^T
-        ops.expert_linear(A, A.view(E, Rp, Rp), seg, out=A2)      # A A^T = A A (A is symmetric)
-        _axpby(A, b, A2, c, A2)                                   # B = b A + c A A
-        ops.expert_linear_t(A2, X, seg, out=BX)                   # B X
-        _axpby(Xr, a, BX, 1.0, Xr)                                # X = a X + B X
+        ops.expert_linear(X.view(rows, wide), X, seg, out=A)          # A = X X^T
+        # B = c A A + b A + a I in one GEMM (A A^T = A A: A is symmetric), axpy and identity in its epilogue
+        ops.expert_linear_axpby(A, A.view(E, Rp, Rp), A, c, b, a, seg, out=A2)
+        ops.expert_linear_t(A2, X, seg, out=Xn.view(rows, wide))      # X = B X
+        X, Xn = Xn, X
     return X
 
 

@@ -404,6 +404,16 @@ def expert_linear(a, w, perm: Permutation, out=None):
     return out
 
 
+@_op("expert_linear_axpby", 1)
+def expert_linear_axpby(a, w, c, alpha, beta, diag, perm: Permutation, out):
+    """out (rows,N) = alpha * (a (rows,K) @ W[e]^T) + beta * c + diag on each group's own diagonal; W (E,N,K)."""
+    E, N, K = w.shape
+    L.check(L.lib().b200moe_expert_linear_axpby(L.ptr(a), L.ptr(w), L.ptr(c), float(alpha), float(beta), float(diag),
+                                                L.ptr(perm.tile_expert), L.ptr(perm.poffs), perm.cap, perm.E, N, K,
+                                                L.ptr(out), L.ptr(L.status_word(a.device)), L.stream_of(a)))
+    return out
+
+
 @_op("expert_linear_push", 1)
 def expert_linear_push(a, w, perm: Permutation, row_rank, row_slot, peer_base, w_kn=False):
     """Row r of a (rows,K) @ W[e(r)]^T (W (E,N,K); w_kn: a @ W[e(r)], W (E,K,N)) is sent to
