@@ -339,13 +339,26 @@ int b200moe_muon_prescale_rows(const void* x, const float* rowss, int64_t rows, 
 int b200moe_muon_normalise_pack(const void* x, const float* rowss, int E, int64_t r, int64_t c, int64_t Rp,
                                 int transposed, float eps, float* norms, void* xp, b200moe_stream_t stream);
 
+/* Gram matrices of a stack: out[e] (R,R) = x[e] x[e]^T for E equal groups of R = rows_cap / E rows (R a multiple of
+ * 256), x (rows_cap,K).  The result is symmetric, so only the tiles that reach the upper triangle of each group are
+ * computed and stored; b200moe_mirror_upper completes the rest.  torch.bmm(X, X.transpose(1, 2)),
+ * kernels/sm75/muon.py:84 (the reference's sm_120 fork has a symmetric-product kernel for the same purpose,
+ * kernels/sm120/newton_schulz_symmul.py:50). */
+int b200moe_expert_gram(const void* x, const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E,
+                        int64_t K, void* out, int32_t* status, b200moe_stream_t stream);
+
+/* a[e,i,j] = a[e,j,i] for every 64 x 64 block strictly below the block diagonal of E matrices of order n (a multiple
+ * of 64), in place: the second half of a symmetric product.  No reference counterpart as a kernel. */
+int b200moe_mirror_upper(void* a, int E, int64_t n, b200moe_stream_t stream);
+
 /* out (rows,N) = bf16(alpha * (a (rows,K) @ W[e]^T) + beta * c + diag * I_e): b200moe_expert_linear with the
  * reference's baddbmm epilogue (kernels/sm75/muon.py:85: b*A + c*(A@A)) and an identity term on each group's own
  * diagonal (column == row - poffs[e]) folded into the GEMM's store.  c: (rows,N) bf16, read-only, must not alias out.
  * N a multiple of 256.  With a = c = the Gram matrices A, W = A, alpha = c, beta = b, diag = a it produces the whole
- * left factor (b A + c A A + a I) of one Newton-Schulz iteration. */
+ * left factor (b A + c A A + a I) of one Newton-Schulz iteration.  symmetric != 0 (E equal groups of N rows, a
+ * result known to be symmetric): only the tiles reaching the upper triangle are computed, as in b200moe_expert_gram. */
 int b200moe_expert_linear_axpby(const void* a, const void* w, const void* c, float alpha, float beta, float diag,
-                                const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E, int64_t N,
+                                int symmetric, const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E, int64_t N,
                                 int64_t K, void* out, int32_t* status, b200moe_stream_t stream);
 
 /* out = bf16(alpha*x + beta*y + diag*I), n elements seen as a stack of ld x ld matrices (ld = 0: no identity term);

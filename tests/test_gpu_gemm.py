@@ -94,3 +94,26 @@ def test_expert_linear_axpby_epilogue(pkg, E, R, K):
     assert O.rel_l2(out.float().view(E, R, R).cpu(), ref.cpu()) < TOL
     plain = pkg.ops.expert_linear(a, w, seg).float().view(E, R, R)      # and the unfused product is what it scales
     assert O.rel_l2(plain.cpu(), prod.cpu()) < TOL
+
+
+@pytest.mark.parametrize("E,R,K", [(3, 256, 96), (2, 768, 512), (4, 1536, 264), (1, 2048, 128)])
+def test_symmetric_products_equal_the_full_ones_bit_for_bit(pkg, E, R, K):
+    """x x^T and alpha * (A A^T) + beta * A + diag * I computed over the upper tiles and mirrored against the same
+    products computed in full: element (i,j) and (j,i) sum the same products in the same order, so the bits agree."""
+    ops = pkg.ops
+    seg = pkg.muon._uniform_segments(E, R, DEV)
+    x = _rand(E * R, K, seed=31).to(DEV) * 0.1
+    full = ops.expert_linear(x, x.view(E, R, K), seg)
+    sym = torch.full((E * R, R), 9.0, dtype=torch.bfloat16, device=DEV)
+    ops.mirror_upper(ops.expert_gram(x, seg, sym), E, R)
+    torch.cuda.synchronize(); pkg.check_status()
+    assert torch.equal(sym, full)
+    assert torch.equal(full.view(E, R, R), full.view(E, R, R).transpose(1, 2))
+    A = full
+    out_full = torch.empty_like(A)
+    ops.expert_linear_axpby(A, A.view(E, R, R), A, 2.0315, -4.775, 3.4445, seg, out_full)
+    out_sym = torch.full_like(A, 9.0)
+    ops.mirror_upper(ops.expert_linear_axpby(A, A.view(E, R, R), A, 2.0315, -4.775, 3.4445, seg, out_sym,
+                                             symmetric=True), E, R)
+    torch.cuda.synchronize(); pkg.check_status()
+    assert torch.equal(out_sym, out_full)

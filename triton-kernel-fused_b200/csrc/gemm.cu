@@ -832,9 +832,28 @@ int b200moe_expert_linear(const void* a, const void* w, const int32_t* tile_expe
   return dispatch_bn<EPI_STORE>(pick_bn(N) == 64 ? 128 : pick_bn(N), oa, ob, &d, nullptr, p, 0, (cudaStream_t)stream);
 }
 
+int b200moe_expert_gram(const void* x, const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E,
+                        int64_t K, void* out, int32_t* status, b200moe_stream_t stream) {
+  B200_CHECK_ARG(E >= 1 && rows_cap % E == 0, B200MOE_E_BAD_SHAPE, "expert_gram: %lld rows do not split into %d equal groups",
+                 (long long)rows_cap, E);
+  const int64_t R = rows_cap / E;
+  int rc = check_grouped("expert_gram", x, x, out, tile_expert, poffs, rows_cap, E, R, K);
+  if (rc) return rc;
+  B200_CHECK_ARG(tile_expert, B200MOE_E_NULL, "expert_gram: null pointer");
+  B200_CHECK_ARG(R % 256 == 0, B200MOE_E_BAD_SHAPE, "expert_gram: %lld rows per group must be a multiple of 256", (long long)R);
+  B200_CHECK_ARG(aligned16(out), B200MOE_E_ALIGN, "expert_gram: output not aligned");
+  Operand oa{x, 0, rows_cap, K, K, 1, rows_cap * K};
+  Operand ob{x, 0, R, K, K, E, R * K};
+  GemmParams p{};
+  p.sched = SCHED_GROUPED_M; p.N = (int)R; p.K = (int)K; p.num_groups = E; p.sym_rows = (int)R;
+  p.tile_expert = tile_expert; p.poffs = poffs; p.D = out; p.ldd = R; p.status = status;
+  Operand d{out, 0, rows_cap, R, R, 1, rows_cap * R};
+  return dispatch_bn<EPI_STORE>(256, oa, ob, &d, nullptr, p, 0, (cudaStream_t)stream);
+}
+
 int b200moe_expert_linear_axpby(const void* a, const void* w, const void* c, float alpha, float beta, float diag,
-                                const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E, int64_t N,
-                                int64_t K, void* out, int32_t* status, b200moe_stream_t stream) {
+                                int symmetric, const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E,
+                                int64_t N, int64_t K, void* out, int32_t* status, b200moe_stream_t stream) {
   int rc = check_grouped("expert_linear_axpby", a, w, out, tile_expert, poffs, rows_cap, E, N, K);
   if (rc) return rc;
   B200_CHECK_ARG(tile_expert && c, B200MOE_E_NULL, "expert_linear_axpby: null pointer");
@@ -846,6 +865,11 @@ int b200moe_expert_linear_axpby(const void* a, const void* w, const void* c, flo
   p.sched = SCHED_GROUPED_M; p.N = (int)N; p.K = (int)K; p.num_groups = E;
   p.tile_expert = tile_expert; p.poffs = poffs; p.D = out; p.ldd = N; p.status = status;
   p.aux = const_cast<void*>(c); p.ax_alpha = alpha; p.ax_beta = beta; p.ax_diag = diag;
+  if (symmetric) {
+    B200_CHECK_ARG(rows_cap == (int64_t)E * N, B200MOE_E_BAD_SHAPE,
+                   "expert_linear_axpby: a symmetric result needs %d equal groups of N = %lld rows", E, (long long)N);
+    p.sym_rows = (int)N;
+  }
   Operand d{out, 0, rows_cap, N, N, 1, rows_cap * N};
   return dispatch_bn<EPI_AXPBY>(256, oa, ob, &d, nullptr, p, 0, (cudaStream_t)stream);
 }

@@ -33,6 +33,9 @@ struct GemmParams {
   long long d_group_stride;  // GROUPED_K: elements between D[e] and D[e+1]
   void* aux;                 // SwiGLU: inter (rows, I); GLU_BWD: saved gate_up (rows, 2I); AXPBY: C (rows, N)
   int I;
+  // GROUPED_M with equal square groups (sym_rows rows and N = sym_rows columns each) whose result is symmetric:
+  // only the tiles that reach the upper triangle of each group are computed (0 = all tiles)
+  int sym_rows;
   // EPI_AXPBY (256-wide tiles): D = ax_alpha * (A B) + ax_beta * C + ax_diag * [column == row - poffs[group]]
   float ax_alpha, ax_beta, ax_diag;
   int* status;
@@ -47,8 +50,17 @@ struct Tile {
   int m0, n0, g, k0, nkb;
 };
 
+// tiles of one symmetric group that reach its upper triangle: row tile mi covers columns from (mi*TM/TN)*TN on
+__device__ __forceinline__ int sym_tiles_per_group(const GemmParams& p, int TN, int TM) {
+  const int nt = (p.N + TN - 1) / TN;
+  int n = 0;
+  for (int mi = 0; mi * TM < p.sym_rows; ++mi) n += nt - (mi * TM) / TN;
+  return n;
+}
+
 __device__ __forceinline__ int total_tiles(const GemmParams& p, int TN, int TM) {
   const int nt = (p.N + TN - 1) / TN;
+  if (p.sched == SCHED_GROUPED_M && p.sym_rows > 0) return p.num_groups * sym_tiles_per_group(p, TN, TM);
   if (p.sched == SCHED_DENSE) return ((p.M + TM - 1) / TM) * nt;
   if (p.sched == SCHED_GROUPED_M) return (p.poffs[p.num_groups] / TM) * nt;
   return ((p.M + TM - 1) / TM) * nt * p.num_groups;
@@ -95,6 +107,20 @@ __device__ __forceinline__ Tile get_tile(const GemmParams& p, int tile, int TN, 
     }
     t.k0 = kb;
     t.nkb = (ke - kb + BK - 1) / BK;
+  } else if (p.sched == SCHED_GROUPED_M && p.sym_rows > 0) {
+    const int per = sym_tiles_per_group(p, TN, TM);
+    const int g = tile / per;
+    int r = tile - g * per, mi = 0;
+    for (;; ++mi) {                       // row tile mi owns nt - first(mi) consecutive indices
+      const int len = nt - (mi * TM) / TN;
+      if (r < len) break;
+      r -= len;
+    }
+    t.m0 = g * p.sym_rows + mi * TM;
+    t.n0 = ((mi * TM) / TN + r) * TN;
+    t.g = g;
+    t.k0 = 0;
+    t.nkb = (p.K + BK - 1) / BK;
   } else {
     const int mi = tile / nt;
     t.m0 = mi * TM;

@@ -262,6 +262,31 @@ __global__ void __launch_bounds__(256) muon_apply_transpose_kernel(const __nv_bf
   }
 }
 
+// a[e, i, j] = a[e, j, i] for every 64 x 64 block strictly below the block diagonal of each n x n matrix: completes a
+// symmetric product of which only the tiles reaching the upper triangle were computed.  grid = (n/64, n/64, E).
+__global__ void __launch_bounds__(256) mirror_upper_kernel(__nv_bfloat16* __restrict__ a, int n) {
+  const int bi = blockIdx.y, bj = blockIdx.x;           // destination block (row bi, column bj)
+  if (bi <= bj) return;
+  __shared__ uint32_t tile[64][33];                      // source block (bj, bi) as bf16 pairs, 66 values per row
+  __nv_bfloat16* m = a + static_cast<long long>(blockIdx.z) * n * n;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int r = ty + 8 * k;
+    tile[r][tx] = *reinterpret_cast<const uint32_t*>(m + static_cast<long long>(bj * 64 + r) * n + bi * 64 + 2 * tx);
+  }
+  __syncthreads();
+  const __nv_bfloat16* th = reinterpret_cast<const __nv_bfloat16*>(&tile[0][0]);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int r = ty + 8 * k;                            // destination row inside the block = source column
+    __nv_bfloat162 v;
+    v.x = th[(2 * tx) * 66 + r];
+    v.y = th[(2 * tx + 1) * 66 + r];
+    *reinterpret_cast<__nv_bfloat162*>(m + static_cast<long long>(bi * 64 + r) * n + bj * 64 + 2 * tx) = v;
+  }
+}
+
 static int stream_grid(long long work_items, int per_cta) {
   long long grid = (work_items + per_cta - 1) / per_cta;
   const long long cap = static_cast<long long>(num_sms()) * 16;
@@ -352,6 +377,17 @@ int b200moe_axpby_bf16(const void* x, float alpha, const void* y, float beta, fl
   if (n == 0) return 0;
   axpby_bf16_kernel<<<stream_grid(n / 8, 256), 256, 0, (cudaStream_t)stream>>>((const uint4*)x, alpha, (const uint4*)y, beta,
                                                                                diag, (int)ld, (uint4*)out, n / 8);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_mirror_upper(void* a, int E, int64_t n, b200moe_stream_t stream) {
+  B200_CHECK_ARG(a, B200MOE_E_NULL, "mirror_upper: null pointer");
+  B200_CHECK_ARG(E >= 1 && E <= 65535 && n > 0 && n % 64 == 0 && n < (1LL << 22), B200MOE_E_BAD_SHAPE,
+                 "mirror_upper: %d matrices of order %lld (must be a multiple of 64)", E, (long long)n);
+  B200_CHECK_ARG(aligned16(a), B200MOE_E_ALIGN, "mirror_upper: pointer must be 16-byte aligned");
+  dim3 grid((unsigned)(n / 64), (unsigned)(n / 64), (unsigned)E);
+  mirror_upper_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)a, (int)n);
   B200_CUDA(cudaGetLastError());
   return 0;
 }

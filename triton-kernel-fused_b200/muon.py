@@ -114,16 +114,17 @@ def _orthogonalise_packed(u, E, r, c, coeffs, eps, rowss=None):
 
 def _iterate(X, E, Rp, wide, coeffs):
     """X <- a X + (b A + c A A) X with A = X X^T (kernels/sm75/muon.py:83-86), evaluated as ((b A + c A A) + a I) X:
-    three grouped GEMMs per iteration and no element-wise pass, X ping-pongs between two buffers."""
+    three grouped GEMMs per iteration (two of them over the upper triangle only), X ping-pongs between two buffers."""
     seg = _uniform_segments(E, Rp, X.device)
     rows = E * Rp
     A = torch.empty(rows, Rp, dtype=torch.bfloat16, device=X.device)
     A2 = torch.empty_like(A)
     Xn = torch.empty_like(X)
     for a, b, c in coeffs:
-        ops.expert_linear(X.view(rows, wide), X, seg, out=A)          # A = X X^T
-        # B = c A A + b A + a I in one GEMM (A A^T = A A: A is symmetric), axpy and identity in its epilogue
-        ops.expert_linear_axpby(A, A.view(E, Rp, Rp), A, c, b, a, seg, out=A2)
+        # A = X X^T and B = c A A + b A + a I are symmetric: their GEMMs compute the upper tiles, a copy mirrors them
+        ops.mirror_upper(ops.expert_gram(X.view(rows, wide), seg, out=A), E, Rp)
+        # (A A^T = A A; axpy and identity in the GEMM's epilogue)
+        ops.mirror_upper(ops.expert_linear_axpby(A, A.view(E, Rp, Rp), A, c, b, a, seg, out=A2, symmetric=True), E, Rp)
         ops.expert_linear_t(A2, X, seg, out=Xn.view(rows, wide))      # X = B X
         X, Xn = Xn, X
     return X

@@ -405,13 +405,31 @@ def expert_linear(a, w, perm: Permutation, out=None):
 
 
 @_op("expert_linear_axpby", 1)
-def expert_linear_axpby(a, w, c, alpha, beta, diag, perm: Permutation, out):
-    """out (rows,N) = alpha * (a (rows,K) @ W[e]^T) + beta * c + diag on each group's own diagonal; W (E,N,K)."""
+def expert_linear_axpby(a, w, c, alpha, beta, diag, perm: Permutation, out, symmetric=False):
+    """out (rows,N) = alpha * (a (rows,K) @ W[e]^T) + beta * c + diag on each group's own diagonal; W (E,N,K).
+    symmetric: the result is known to be symmetric per group; only its upper tiles are computed (see mirror_upper)."""
     E, N, K = w.shape
     L.check(L.lib().b200moe_expert_linear_axpby(L.ptr(a), L.ptr(w), L.ptr(c), float(alpha), float(beta), float(diag),
-                                                L.ptr(perm.tile_expert), L.ptr(perm.poffs), perm.cap, perm.E, N, K,
-                                                L.ptr(out), L.ptr(L.status_word(a.device)), L.stream_of(a)))
+                                                1 if symmetric else 0, L.ptr(perm.tile_expert), L.ptr(perm.poffs),
+                                                perm.cap, perm.E, N, K, L.ptr(out), L.ptr(L.status_word(a.device)),
+                                                L.stream_of(a)))
     return out
+
+
+@_op("expert_gram", 1)
+def expert_gram(x, perm: Permutation, out):
+    """out[e] = x[e] x[e]^T for equal groups of rows; only the tiles reaching the upper triangle are written."""
+    K = x.shape[-1]
+    L.check(L.lib().b200moe_expert_gram(L.ptr(x), L.ptr(perm.tile_expert), L.ptr(perm.poffs), perm.cap, perm.E, K,
+                                        L.ptr(out), L.ptr(L.status_word(x.device)), L.stream_of(x)))
+    return out
+
+
+@_op("mirror_upper", 1)
+def mirror_upper(a, E, n):
+    """In place a[e,i,j] = a[e,j,i] below the 64-block diagonal of E matrices of order n."""
+    L.check(L.lib().b200moe_mirror_upper(L.ptr(a), E, n, L.stream_of(a)))
+    return a
 
 
 @_op("expert_linear_push", 1)
