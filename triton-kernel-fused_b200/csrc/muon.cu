@@ -267,23 +267,28 @@ __global__ void __launch_bounds__(256) muon_apply_transpose_kernel(const __nv_bf
 __global__ void __launch_bounds__(256) mirror_upper_kernel(__nv_bfloat16* __restrict__ a, int n) {
   const int bi = blockIdx.y, bj = blockIdx.x;           // destination block (row bi, column bj)
   if (bi <= bj) return;
-  __shared__ uint32_t tile[64][33];                      // source block (bj, bi) as bf16 pairs, 66 values per row
+  // source block (bj, bi) as 64 rows of 32 words (bf16 pairs); word w of row r sits at w ^ ((r >> 3) << 2), which
+  // keeps 16-byte vectors whole and makes the column-wise reads below conflict-free
+  __shared__ __align__(16) uint32_t tile[64 * 32];
   __nv_bfloat16* m = a + static_cast<long long>(blockIdx.z) * n * n;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const int r = ty + 8 * k;
-    tile[r][tx] = *reinterpret_cast<const uint32_t*>(m + static_cast<long long>(bj * 64 + r) * n + bi * 64 + 2 * tx);
+  for (int k = 0; k < 2; ++k) {                          // 64 rows x 8 vectors of 8 values, two per thread
+    const int v = threadIdx.x + 256 * k, r = v >> 3, w4 = (v & 7) * 4;
+    *reinterpret_cast<uint4*>(&tile[r * 32 + (w4 ^ ((r >> 3) << 2))]) =
+        *reinterpret_cast<const uint4*>(m + static_cast<long long>(bj * 64 + r) * n + bi * 64 + 2 * w4);
   }
   __syncthreads();
-  const __nv_bfloat16* th = reinterpret_cast<const __nv_bfloat16*>(&tile[0][0]);
+  const __nv_bfloat16* th = reinterpret_cast<const __nv_bfloat16*>(tile);
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const int r = ty + 8 * k;                            // destination row inside the block = source column
-    __nv_bfloat162 v;
-    v.x = th[(2 * tx) * 66 + r];
-    v.y = th[(2 * tx + 1) * 66 + r];
-    *reinterpret_cast<__nv_bfloat162*>(m + static_cast<long long>(bi * 64 + r) * n + bj * 64 + 2 * tx) = v;
+  for (int k = 0; k < 2; ++k) {
+    const int v = threadIdx.x + 256 * k, r = v >> 3, c8 = (v & 7) * 8;   // destination row r, columns c8 .. c8+7
+    __align__(16) __nv_bfloat16 o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {                        // destination (r, c8+j) = source (c8+j, r)
+      const int sr = c8 + j;
+      o[j] = th[2 * (sr * 32 + ((r >> 1) ^ ((sr >> 3) << 2))) + (r & 1)];
+    }
+    *reinterpret_cast<uint4*>(m + static_cast<long long>(bi * 64 + r) * n + bj * 64 + c8) = *reinterpret_cast<const uint4*>(o);
   }
 }
 
