@@ -116,3 +116,25 @@ def test_rejected_options(pkg):
             pkg.FusedMuon([p], **kw)
     with pytest.raises(ValueError):
         pkg.newton_schulz(torch.zeros(4, 12, 64, device=DEV))          # 12 is not a multiple of 8
+
+
+def test_a_shard_of_a_stack_steps_like_the_whole_stack(pkg):
+    """Matrices of a stack are orthogonalised independently, so an expert-parallel rank that owns experts [e0, e1)
+    steps its shard with no exchange: the shard's result equals the same matrices inside the full stack, bit for bit."""
+    E, r, c = 8, 512, 320
+    g = torch.Generator().manual_seed(9)
+    p0 = (torch.randn(E, r, c, generator=g) * 0.02).to(torch.bfloat16)
+    grad = torch.randn(E, r, c, generator=g).to(torch.bfloat16)
+
+    def step(lo, hi):
+        p = torch.nn.Parameter(p0[lo:hi].clone().to(DEV))
+        p.grad = grad[lo:hi].clone().to(DEV)
+        opt = pkg.FusedMuon([p], lr=0.01, weight_decay=0.1)
+        opt.step(); opt.step()
+        return p.detach().clone(), opt.state[p]["muon_mom"].clone()
+
+    full_p, full_m = step(0, E)
+    for lo, hi in ((0, 4), (4, 8), (2, 3)):
+        sp, sm = step(lo, hi)
+        assert torch.equal(sp, full_p[lo:hi]) and torch.equal(sm, full_m[lo:hi])
+    torch.cuda.synchronize(); pkg.check_status()

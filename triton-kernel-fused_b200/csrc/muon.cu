@@ -146,33 +146,58 @@ __global__ void __launch_bounds__(256) muon_pack_rows_kernel(const uint4* __rest
   }
 }
 
+// A 64 x 64 bf16 tile in shared memory for transposing with 16-byte accesses on both sides: 64 rows of 32 words
+// (bf16 pairs); word w of row r sits at w ^ ((r >> 3) << 2), which keeps 8-value vectors whole and makes the
+// column-wise reads of the second phase conflict-free.  Thread v (0..511, two per thread) owns the vector of row
+// v >> 3 that starts at column 8 * (v & 7), in the source for the first phase and in the destination for the second.
+struct TransposeTile {
+  uint32_t w[64 * 32];
+  __device__ __forceinline__ void put(int r, int c8, const uint4& v) {
+    *reinterpret_cast<uint4*>(&w[r * 32 + ((c8 >> 1) ^ ((r >> 3) << 2))]) = v;
+  }
+  // the 8 values of destination row r, columns c8 .. c8+7 = source column r, rows c8 .. c8+7
+  __device__ __forceinline__ void get_transposed(int r, int c8, float (&f)[8]) const {
+    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(w);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int sr = c8 + j;
+      f[j] = __bfloat162float(h[2 * (sr * 32 + ((r >> 1) ^ ((sr >> 3) << 2))) + (r & 1)]);
+    }
+  }
+};
+
 // Tall matrices (r > c) iterate on the transpose (kernels/sm75/muon.py:79-81): xp (E, Rp, r),
-// xp[e, j, i] = bf16(x[e, i, j] / norms[e]) for j < c, zero rows for c <= j < Rp.  64 x 64 tiles through shared
-// memory, 4-byte accesses on both sides.  grid = (ceil(r/64), Rp/64, E).
+// xp[e, j, i] = bf16(x[e, i, j] / norms[e]) for j < c, zero rows for c <= j < Rp.  grid = (ceil(r/64), Rp/64, E).
 __global__ void __launch_bounds__(256) muon_pack_transpose_kernel(const __nv_bfloat16* __restrict__ x,
                                                                   const float* __restrict__ norms, int r, int c, int Rp,
                                                                   __nv_bfloat16* __restrict__ xp) {
-  __shared__ float tile[64][65];
+  __shared__ __align__(16) TransposeTile tile;
   const int e = blockIdx.z, i0 = blockIdx.x * 64, j0 = blockIdx.y * 64;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const float nrm = norms[e];
   const __nv_bfloat16* src = x + static_cast<long long>(e) * r * c;
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const int i = i0 + ty + 8 * k, j = j0 + 2 * tx;
-    float2 v = make_float2(0.0f, 0.0f);
-    if (i < r && j < c) v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + static_cast<long long>(i) * c + j));
-    tile[ty + 8 * k][2 * tx] = v.x / nrm;
-    tile[ty + 8 * k][2 * tx + 1] = v.y / nrm;
+  for (int k = 0; k < 2; ++k) {
+    const int v = threadIdx.x + 256 * k, i = i0 + (v >> 3), j = j0 + (v & 7) * 8;
+    uint4 q = make_uint4(0u, 0u, 0u, 0u);
+    if (i < r && j < c) {                                  // c is a multiple of 8: the vector is inside or outside
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(src + static_cast<long long>(i) * c + j), f);
+#pragma unroll
+      for (int t = 0; t < 8; ++t) f[t] = f[t] / nrm;
+      q = pack8(f);
+    }
+    tile.put(v >> 3, (v & 7) * 8, q);
   }
   __syncthreads();
   __nv_bfloat16* dst = xp + static_cast<long long>(e) * Rp * r;
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const int j = j0 + ty + 8 * k, i = i0 + 2 * tx;
-    if (i < r)
-      *reinterpret_cast<__nv_bfloat162*>(dst + static_cast<long long>(j) * r + i) =
-          __floats2bfloat162_rn(tile[2 * tx][ty + 8 * k], tile[2 * tx + 1][ty + 8 * k]);
+  for (int k = 0; k < 2; ++k) {
+    const int v = threadIdx.x + 256 * k, j = j0 + (v >> 3), i = i0 + (v & 7) * 8;
+    if (i < r) {
+      float f[8];
+      tile.get_transposed(v >> 3, (v & 7) * 8, f);
+      *reinterpret_cast<uint4*>(dst + static_cast<long long>(j) * r + i) = pack8(f);
+    }
   }
 }
 
@@ -237,27 +262,39 @@ template <bool kPF32>
 __global__ void __launch_bounds__(256) muon_apply_transpose_kernel(const __nv_bfloat16* __restrict__ xp, int r, int c,
                                                                    int Rp, float gain, float decay, float alpha,
                                                                    void* p) {
-  __shared__ float tile[64][65];
+  __shared__ __align__(16) TransposeTile tile;
   const int e = blockIdx.z, i0 = blockIdx.x * 64, j0 = blockIdx.y * 64;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const __nv_bfloat16* src = xp + static_cast<long long>(e) * Rp * r;
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const int j = j0 + ty + 8 * k, i = i0 + 2 * tx;
-    float2 v = make_float2(0.0f, 0.0f);
-    if (j < c && i < r) v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + static_cast<long long>(j) * r + i));
-    tile[ty + 8 * k][2 * tx] = v.x;
-    tile[ty + 8 * k][2 * tx + 1] = v.y;
+  for (int k = 0; k < 2; ++k) {
+    const int v = threadIdx.x + 256 * k, j = j0 + (v >> 3), i = i0 + (v & 7) * 8;
+    uint4 q = make_uint4(0u, 0u, 0u, 0u);
+    if (j < c && i < r) q = *reinterpret_cast<const uint4*>(src + static_cast<long long>(j) * r + i);
+    tile.put(v >> 3, (v & 7) * 8, q);
   }
   __syncthreads();
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const int i = i0 + ty + 8 * k, j = j0 + 2 * tx;
+  for (int k = 0; k < 2; ++k) {
+    const int v = threadIdx.x + 256 * k, i = i0 + (v >> 3), j = j0 + (v & 7) * 8;
     if (i < r && j < c) {
+      float o[8], w[8];
+      tile.get_transposed(v >> 3, (v & 7) * 8, o);
       const long long pi = (static_cast<long long>(e) * r + i) * c + j;
-      const float o0 = tile[2 * tx][ty + 8 * k], o1 = tile[2 * tx + 1][ty + 8 * k];
-      store_param<kPF32>(p, pi, round_param<kPF32>(load_param<kPF32>(p, pi) * decay) + alpha * round_bf16(gain * o0));
-      store_param<kPF32>(p, pi + 1, round_param<kPF32>(load_param<kPF32>(p, pi + 1) * decay) + alpha * round_bf16(gain * o1));
+      if (kPF32) {
+        float4* pp = reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + pi);
+        const float4 a = pp[0], b = pp[1];
+        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+#pragma unroll
+        for (int t = 0; t < 8; ++t) w[t] = w[t] * decay + alpha * round_bf16(gain * o[t]);
+        pp[0] = make_float4(w[0], w[1], w[2], w[3]);
+        pp[1] = make_float4(w[4], w[5], w[6], w[7]);
+      } else {
+        uint4* pp = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p) + pi);
+        unpack8(*pp, w);
+#pragma unroll
+        for (int t = 0; t < 8; ++t) w[t] = round_bf16(w[t] * decay) + alpha * round_bf16(gain * o[t]);
+        *pp = pack8(w);
+      }
     }
   }
 }
@@ -267,28 +304,20 @@ __global__ void __launch_bounds__(256) muon_apply_transpose_kernel(const __nv_bf
 __global__ void __launch_bounds__(256) mirror_upper_kernel(__nv_bfloat16* __restrict__ a, int n) {
   const int bi = blockIdx.y, bj = blockIdx.x;           // destination block (row bi, column bj)
   if (bi <= bj) return;
-  // source block (bj, bi) as 64 rows of 32 words (bf16 pairs); word w of row r sits at w ^ ((r >> 3) << 2), which
-  // keeps 16-byte vectors whole and makes the column-wise reads below conflict-free
-  __shared__ __align__(16) uint32_t tile[64 * 32];
+  __shared__ __align__(16) TransposeTile tile;          // source block (bj, bi)
   __nv_bfloat16* m = a + static_cast<long long>(blockIdx.z) * n * n;
 #pragma unroll
-  for (int k = 0; k < 2; ++k) {                          // 64 rows x 8 vectors of 8 values, two per thread
-    const int v = threadIdx.x + 256 * k, r = v >> 3, w4 = (v & 7) * 4;
-    *reinterpret_cast<uint4*>(&tile[r * 32 + (w4 ^ ((r >> 3) << 2))]) =
-        *reinterpret_cast<const uint4*>(m + static_cast<long long>(bj * 64 + r) * n + bi * 64 + 2 * w4);
+  for (int k = 0; k < 2; ++k) {
+    const int v = threadIdx.x + 256 * k, r = v >> 3, c8 = (v & 7) * 8;
+    tile.put(r, c8, *reinterpret_cast<const uint4*>(m + static_cast<long long>(bj * 64 + r) * n + bi * 64 + c8));
   }
   __syncthreads();
-  const __nv_bfloat16* th = reinterpret_cast<const __nv_bfloat16*>(tile);
 #pragma unroll
   for (int k = 0; k < 2; ++k) {
-    const int v = threadIdx.x + 256 * k, r = v >> 3, c8 = (v & 7) * 8;   // destination row r, columns c8 .. c8+7
-    __align__(16) __nv_bfloat16 o[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {                        // destination (r, c8+j) = source (c8+j, r)
-      const int sr = c8 + j;
-      o[j] = th[2 * (sr * 32 + ((r >> 1) ^ ((sr >> 3) << 2))) + (r & 1)];
-    }
-    *reinterpret_cast<uint4*>(m + static_cast<long long>(bi * 64 + r) * n + bj * 64 + c8) = *reinterpret_cast<const uint4*>(o);
+    const int v = threadIdx.x + 256 * k, r = v >> 3, c8 = (v & 7) * 8;
+    float f[8];
+    tile.get_transposed(r, c8, f);                       // bf16 -> float -> bf16 is exact
+    *reinterpret_cast<uint4*>(m + static_cast<long long>(bi * 64 + r) * n + bj * 64 + c8) = pack8(f);
   }
 }
 
