@@ -341,11 +341,12 @@ int b200moe_muon_normalise_pack(const void* x, const float* rowss, int E, int64_
 
 /* Gram matrices of a stack: out[e] (R,R) = x[e] x[e]^T for E equal groups of R = rows_cap / E rows (R a multiple of
  * 256), x (rows_cap,K).  The result is symmetric, so only the tiles that reach the upper triangle of each group are
- * computed and stored; b200moe_mirror_upper completes the rest.  torch.bmm(X, X.transpose(1, 2)),
+ * computed; with mirror != 0 the epilogue stores every chunk right of the diagonal tile a second time, transposed,
+ * so the whole matrix is written, with mirror == 0 b200moe_mirror_upper completes it.  torch.bmm(X, X.transpose(1, 2)),
  * kernels/sm75/muon.py:84 (the reference's sm_120 fork has a symmetric-product kernel for the same purpose,
  * kernels/sm120/newton_schulz_symmul.py:50). */
 int b200moe_expert_gram(const void* x, const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E,
-                        int64_t K, void* out, int32_t* status, b200moe_stream_t stream);
+                        int64_t K, int mirror, void* out, int32_t* status, b200moe_stream_t stream);
 
 /* a[e,i,j] = a[e,j,i] for every 64 x 64 block strictly below the block diagonal of E matrices of order n (a multiple
  * of 64), in place: the second half of a symmetric product.  No reference counterpart as a kernel. */
@@ -356,7 +357,8 @@ int b200moe_mirror_upper(void* a, int E, int64_t n, b200moe_stream_t stream);
  * diagonal (column == row - poffs[e]) folded into the GEMM's store.  c: (rows,N) bf16, read-only, must not alias out.
  * N a multiple of 256.  With a = c = the Gram matrices A, W = A, alpha = c, beta = b, diag = a it produces the whole
  * left factor (b A + c A A + a I) of one Newton-Schulz iteration.  symmetric != 0 (E equal groups of N rows, a
- * result known to be symmetric): only the tiles reaching the upper triangle are computed, as in b200moe_expert_gram. */
+ * result known to be symmetric): only the tiles reaching the upper triangle are computed, as in b200moe_expert_gram;
+ * symmetric == 2 also stores the transposed chunks from the epilogue (the whole matrix is written). */
 int b200moe_expert_linear_axpby(const void* a, const void* w, const void* c, float alpha, float beta, float diag,
                                 int symmetric, const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E, int64_t N,
                                 int64_t K, void* out, int32_t* status, b200moe_stream_t stream);

@@ -105,15 +105,19 @@ def test_symmetric_products_equal_the_full_ones_bit_for_bit(pkg, E, R, K):
     x = _rand(E * R, K, seed=31).to(DEV) * 0.1
     full = ops.expert_linear(x, x.view(E, R, K), seg)
     sym = torch.full((E * R, R), 9.0, dtype=torch.bfloat16, device=DEV)
-    ops.mirror_upper(ops.expert_gram(x, seg, sym), E, R)
+    ops.mirror_upper(ops.expert_gram(x, seg, sym, mirror=False), E, R)      # upper tiles, then the mirroring copy
+    sym2 = torch.full((E * R, R), 9.0, dtype=torch.bfloat16, device=DEV)
+    ops.expert_gram(x, seg, sym2)                                            # transposed chunks from the epilogue
     torch.cuda.synchronize(); pkg.check_status()
-    assert torch.equal(sym, full)
+    assert torch.equal(sym, full) and torch.equal(sym2, full)
     assert torch.equal(full.view(E, R, R), full.view(E, R, R).transpose(1, 2))
     A = full
     out_full = torch.empty_like(A)
     ops.expert_linear_axpby(A, A.view(E, R, R), A, 2.0315, -4.775, 3.4445, seg, out_full)
     out_sym = torch.full_like(A, 9.0)
     ops.mirror_upper(ops.expert_linear_axpby(A, A.view(E, R, R), A, 2.0315, -4.775, 3.4445, seg, out_sym,
-                                             symmetric=True), E, R)
+                                             symmetric=1), E, R)
+    out_sym2 = torch.full_like(A, 9.0)
+    ops.expert_linear_axpby(A, A.view(E, R, R), A, 2.0315, -4.775, 3.4445, seg, out_sym2, symmetric=2)
     torch.cuda.synchronize(); pkg.check_status()
-    assert torch.equal(out_sym, out_full)
+    assert torch.equal(out_sym, out_full) and torch.equal(out_sym2, out_full)

@@ -86,7 +86,7 @@ _SIGNATURES = {
                                             c_void_p, c_void_p, c_void_p]),
     "b200moe_expert_linear_axpby": (c_int, [c_void_p] * 3 + [c_float] * 3 + [c_int] + [c_void_p] * 2 +
                                     [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
-    "b200moe_expert_gram": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64] + [c_void_p] * 3),
+    "b200moe_expert_gram": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64, c_int] + [c_void_p] * 3),
     "b200moe_mirror_upper": (c_int, [c_void_p, c_int, c_int64, c_void_p]),
     "b200moe_axpby_bf16": (c_int, [c_void_p, c_float, c_void_p, c_float, c_float, c_int64, c_void_p, c_int64, c_void_p]),
     "b200moe_muon_apply": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_float, c_float, c_float,

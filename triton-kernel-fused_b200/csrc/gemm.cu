@@ -295,7 +295,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // stores (which clip at the tensor's bounds, so no row or column masks are needed)
         uint8_t* sbuf = bufG;   // this warp's staging box
         const int grp = (p.sched == SCHED_GROUPED_K) ? t.g : 0;
-        if constexpr (EPI == EPI_STORE || EPI == EPI_AXPBY) {
+        if constexpr (EPI == EPI_STORE || EPI == EPI_AXPBY || EPI == EPI_STORE_SYM) {
           constexpr int W = BN / 2;
           // push mode: this lane's output row goes to a slot of another GPU's (or this GPU's) receive buffer
           uint8_t* push_dst = nullptr;
@@ -363,6 +363,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               staging_free(lane);
               stage_row(sbuf, lane, pk);
               store_box(&tmD, sbuf, lane, t.n0 + c, row0, grp);
+              if constexpr (EPI == EPI_AXPBY || EPI == EPI_STORE_SYM) if (p.sym_mirror) {
+                // symmetric result: the chunk (32 rows x 64 columns) of a tile right of the diagonal tile is also
+                // the transpose of a chunk nobody computes.  Stage it as 64 rows x 32 columns (unswizzled rows of
+                // 64 bytes; lane l owns column l) and store it through the second map.
+                const int lrow0 = row0 - t.g * p.sym_rows;          // this warp's first row inside its group
+                if ((t.n0 + c) / B200MOE_TILE_M > lrow0 / B200MOE_TILE_M) {
+                  staging_free(lane);                               // the store above has read the box
+#pragma unroll
+                  for (int m = 0; m < 32; ++m) {
+                    *reinterpret_cast<uint16_t*>(sbuf + (2 * m) * 64 + lane * 2) = static_cast<uint16_t>(pk[m] & 0xffffu);
+                    *reinterpret_cast<uint16_t*>(sbuf + (2 * m + 1) * 64 + lane * 2) = static_cast<uint16_t>(pk[m] >> 16);
+                  }
+                  store_box(&tmD2, sbuf, lane, lrow0, t.g * p.sym_rows + t.n0 + c, 0);
+                }
+              }
             }
           }
         } else if constexpr (EPI == EPI_SWIGLU) {
@@ -705,11 +720,14 @@ static int dispatch_bn(int bn, const Operand& A, const Operand& B, const Operand
       if (d2 != nullptr) {
         rc = encode_operand(&tmD2, *d2, 32);
         if (rc) return rc;
+      } else if (p.sym_mirror) {            // the same output through boxes {32 columns, 64 rows}, no swizzle
+        rc = make_map(&tmD2, d1->ptr, d1->k, d1->rows, d1->groups, d1->ld, d1->group_stride, 32, 64, 2, 0);
+        if (rc) return rc;
       }
     }
   }
   if (pair) return launch<256, EPI, 2>(tmA, tmB, tmD, tmD2, p, max_tiles > 0 ? (max_tiles + 1) / 2 : 0, stream);
-  if constexpr (EPI == EPI_AXPBY) {   // built for the 256-wide TMA-store epilogue only
+  if constexpr (EPI == EPI_AXPBY || EPI == EPI_STORE_SYM) {   // built for the 256-wide TMA-store epilogue only
     if (bn == 256) return launch<256, EPI, 1>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
     set_error("tile width %d not built for this epilogue", bn);
     return B200MOE_E_UNSUPPORTED;
@@ -833,7 +851,7 @@ int b200moe_expert_linear(const void* a, const void* w, const int32_t* tile_expe
 }
 
 int b200moe_expert_gram(const void* x, const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E,
-                        int64_t K, void* out, int32_t* status, b200moe_stream_t stream) {
+                        int64_t K, int mirror, void* out, int32_t* status, b200moe_stream_t stream) {
   B200_CHECK_ARG(E >= 1 && rows_cap % E == 0, B200MOE_E_BAD_SHAPE, "expert_gram: %lld rows do not split into %d equal groups",
                  (long long)rows_cap, E);
   const int64_t R = rows_cap / E;
@@ -845,10 +863,10 @@ int b200moe_expert_gram(const void* x, const int32_t* tile_expert, const int32_t
   Operand oa{x, 0, rows_cap, K, K, 1, rows_cap * K};
   Operand ob{x, 0, R, K, K, E, R * K};
   GemmParams p{};
-  p.sched = SCHED_GROUPED_M; p.N = (int)R; p.K = (int)K; p.num_groups = E; p.sym_rows = (int)R;
+  p.sched = SCHED_GROUPED_M; p.N = (int)R; p.K = (int)K; p.num_groups = E; p.sym_rows = (int)R; p.sym_mirror = mirror ? 1 : 0;
   p.tile_expert = tile_expert; p.poffs = poffs; p.D = out; p.ldd = R; p.status = status;
   Operand d{out, 0, rows_cap, R, R, 1, rows_cap * R};
-  return dispatch_bn<EPI_STORE>(256, oa, ob, &d, nullptr, p, 0, (cudaStream_t)stream);
+  return dispatch_bn<EPI_STORE_SYM>(256, oa, ob, &d, nullptr, p, 0, (cudaStream_t)stream);
 }
 
 int b200moe_expert_linear_axpby(const void* a, const void* w, const void* c, float alpha, float beta, float diag,
@@ -869,6 +887,7 @@ int b200moe_expert_linear_axpby(const void* a, const void* w, const void* c, flo
     B200_CHECK_ARG(rows_cap == (int64_t)E * N, B200MOE_E_BAD_SHAPE,
                    "expert_linear_axpby: a symmetric result needs %d equal groups of N = %lld rows", E, (long long)N);
     p.sym_rows = (int)N;
+    p.sym_mirror = symmetric > 1 ? 1 : 0;
   }
   Operand d{out, 0, rows_cap, N, N, 1, rows_cap * N};
   return dispatch_bn<EPI_AXPBY>(256, oa, ob, &d, nullptr, p, 0, (cudaStream_t)stream);

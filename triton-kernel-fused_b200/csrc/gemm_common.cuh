@@ -11,7 +11,8 @@
 namespace b200moe {
 
 enum : int { SCHED_DENSE = 0, SCHED_GROUPED_M = 1, SCHED_GROUPED_K = 2 };
-enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_GLU_BWD = 2, EPI_STORE_F32 = 3, EPI_AXPBY = 4 };
+// EPI_STORE_SYM: EPI_STORE for symmetric results (256-wide tiles), able to store the transposed chunks as well
+enum : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_GLU_BWD = 2, EPI_STORE_F32 = 3, EPI_AXPBY = 4, EPI_STORE_SYM = 5 };
 
 constexpr int BM = 128;  // rows per CTA = TMEM lanes
 constexpr int kEpiWarps = 8;
@@ -34,8 +35,11 @@ struct GemmParams {
   void* aux;                 // SwiGLU: inter (rows, I); GLU_BWD: saved gate_up (rows, 2I); AXPBY: C (rows, N)
   int I;
   // GROUPED_M with equal square groups (sym_rows rows and N = sym_rows columns each) whose result is symmetric:
-  // only the tiles that reach the upper triangle of each group are computed (0 = all tiles)
+  // only the tiles that reach the upper triangle of each group are computed (0 = all tiles); with sym_mirror the
+  // epilogue also stores every chunk of a tile right of the diagonal tile a second time, transposed, so the
+  // result arrives complete
   int sym_rows;
+  int sym_mirror;
   // EPI_AXPBY (256-wide tiles): D = ax_alpha * (A B) + ax_beta * C + ax_diag * [column == row - poffs[group]]
   float ax_alpha, ax_beta, ax_diag;
   int* status;
@@ -248,7 +252,8 @@ static int make_map(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t 
   cuuint32_t box[3] = {box_inner, box_outer, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(tm, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle_bytes == 0 ? CU_TENSOR_MAP_SWIZZLE_NONE : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   B200_CHECK_ARG(r == CUDA_SUCCESS, B200MOE_E_CUDA,
                  "cuTensorMapEncodeTiled failed (%d): dims {%llu,%llu,%llu} box {%u,%u}", (int)r,

@@ -121,10 +121,10 @@ def _iterate(X, E, Rp, wide, coeffs):
     A2 = torch.empty_like(A)
     Xn = torch.empty_like(X)
     for a, b, c in coeffs:
-        # A = X X^T and B = c A A + b A + a I are symmetric: their GEMMs compute the upper tiles, a copy mirrors them
-        ops.mirror_upper(ops.expert_gram(X.view(rows, wide), seg, out=A), E, Rp)
-        # (A A^T = A A; axpy and identity in the GEMM's epilogue)
-        ops.mirror_upper(ops.expert_linear_axpby(A, A.view(E, Rp, Rp), A, c, b, a, seg, out=A2, symmetric=True), E, Rp)
+        # A = X X^T and B = c A A + b A + a I are symmetric: their GEMMs compute the upper tiles and store each chunk
+        # right of the diagonal tile twice, the second time transposed (A A^T = A A; axpy and identity in the epilogue)
+        ops.expert_gram(X.view(rows, wide), seg, out=A)
+        ops.expert_linear_axpby(A, A.view(E, Rp, Rp), A, c, b, a, seg, out=A2, symmetric=2)
         ops.expert_linear_t(A2, X, seg, out=Xn.view(rows, wide))      # X = B X
         X, Xn = Xn, X
     return X

@@ -405,23 +405,25 @@ def expert_linear(a, w, perm: Permutation, out=None):
 
 
 @_op("expert_linear_axpby", 1)
-def expert_linear_axpby(a, w, c, alpha, beta, diag, perm: Permutation, out, symmetric=False):
+def expert_linear_axpby(a, w, c, alpha, beta, diag, perm: Permutation, out, symmetric=0):
     """out (rows,N) = alpha * (a (rows,K) @ W[e]^T) + beta * c + diag on each group's own diagonal; W (E,N,K).
-    symmetric: the result is known to be symmetric per group; only its upper tiles are computed (see mirror_upper)."""
+    symmetric: 1 = the result is known to be symmetric per group and only its upper tiles are computed and written
+    (mirror_upper completes it), 2 = the epilogue also writes the transposed chunks (complete result)."""
     E, N, K = w.shape
     L.check(L.lib().b200moe_expert_linear_axpby(L.ptr(a), L.ptr(w), L.ptr(c), float(alpha), float(beta), float(diag),
-                                                1 if symmetric else 0, L.ptr(perm.tile_expert), L.ptr(perm.poffs),
+                                                int(symmetric), L.ptr(perm.tile_expert), L.ptr(perm.poffs),
                                                 perm.cap, perm.E, N, K, L.ptr(out), L.ptr(L.status_word(a.device)),
                                                 L.stream_of(a)))
     return out
 
 
 @_op("expert_gram", 1)
-def expert_gram(x, perm: Permutation, out):
-    """out[e] = x[e] x[e]^T for equal groups of rows; only the tiles reaching the upper triangle are written."""
+def expert_gram(x, perm: Permutation, out, mirror=True):
+    """out[e] = x[e] x[e]^T for equal groups of rows, computed over the tiles that reach the upper triangle; the
+    epilogue writes the transposed chunks too (mirror=False: only the computed tiles are written)."""
     K = x.shape[-1]
     L.check(L.lib().b200moe_expert_gram(L.ptr(x), L.ptr(perm.tile_expert), L.ptr(perm.poffs), perm.cap, perm.E, K,
-                                        L.ptr(out), L.ptr(L.status_word(x.device)), L.stream_of(x)))
+                                        1 if mirror else 0, L.ptr(out), L.ptr(L.status_word(x.device)), L.stream_of(x)))
     return out
 
 
