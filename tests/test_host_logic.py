@@ -72,3 +72,19 @@ def test_muon_uniform_segment_tables():
     assert seg.poffs.tolist() == [0, 512, 1024, 1536]
     assert seg.tile_expert.tolist() == [0, 0, 1, 1, 2, 2]
     assert seg.tile_expert.dtype == torch.int32 and seg.poffs.dtype == torch.int32
+
+
+def test_muon_accepts_the_reference_argument_list():
+    """Every keyword of the reference's FusedMuon constructor is accepted; the ones that act only together with
+    rejected options are ignored, a group that switches whitening on is rejected at step time."""
+    import pytest
+    pkg = importlib.import_module(PKG)
+    p = torch.nn.Parameter(torch.zeros(2, 64, 64))
+    opt = pkg.FusedMuon([{"params": [p], "xorth_post": 0.01}], lr=3e-4, momentum=0.95, nesterov=True, weight_decay=0.0,
+                        ns_dtype=None, scale_mode="aurora", ns_batch_elems=4 * 1024 * 1024, use_graph=False,
+                        graph_warmup=3, aurora_k=None, spectral_wd=0.0, swd_beta=0.99, xorth_post=0.0,
+                        xorth_backend="ns", xorth_ns_iters=18, xorth_ema=0.95, xorth_gate_ref=0.3,
+                        xorth_warmup_steps=0, xorth_where="post")
+    p.grad = torch.zeros_like(p)
+    with pytest.raises(ValueError):
+        opt.step()

@@ -332,7 +332,7 @@ static int stream_grid(long long work_items, int per_cta) {
 
 using namespace b200moe;
 
-#define MUON_CHECK_DIMS(who, E, r, c, Rp)                                                                          \
+#define MUON_CHECK_DIMS(who, E, r, c, Rp, transposed)                                                             \
   B200_CHECK_ARG((E) >= 1 && (E) <= 65535 && (r) > 0 && (c) > 0 && (r) % 8 == 0 && (c) % 8 == 0 &&                 \
                      (r) < (1LL << 24) && (c) < (1LL << 24),                                                       \
                  B200MOE_E_BAD_SHAPE, who ": a stack of %d matrices of %lld x %lld (both must be multiples of 8)",  \
@@ -386,7 +386,7 @@ int b200moe_muon_prescale_rows(const void* x, const float* rowss, int64_t rows, 
 int b200moe_muon_normalise_pack(const void* x, const float* rowss, int E, int64_t r, int64_t c, int64_t Rp,
                                 int transposed, float eps, float* norms, void* xp, b200moe_stream_t stream) {
   B200_CHECK_ARG(x && rowss && norms && xp, B200MOE_E_NULL, "muon_normalise_pack: null pointer");
-  MUON_CHECK_DIMS("muon_normalise_pack", E, r, c, Rp);
+  MUON_CHECK_DIMS("muon_normalise_pack", E, r, c, Rp, transposed);
   B200_CHECK_ARG(aligned16(x) && aligned16(xp), B200MOE_E_ALIGN, "muon_normalise_pack: pointers must be 16-byte aligned");
   muon_stack_norms_kernel<<<E, 256, 0, (cudaStream_t)stream>>>(rowss, (int)r, eps, norms);
   if (transposed) {
@@ -429,7 +429,7 @@ int b200moe_mirror_upper(void* a, int E, int64_t n, b200moe_stream_t stream) {
 int b200moe_muon_apply(const void* xp, int E, int64_t r, int64_t c, int64_t Rp, int transposed, float gain, float decay,
                        float alpha, void* p, int p_f32, b200moe_stream_t stream) {
   B200_CHECK_ARG(xp && p, B200MOE_E_NULL, "muon_apply: null pointer");
-  MUON_CHECK_DIMS("muon_apply", E, r, c, Rp);
+  MUON_CHECK_DIMS("muon_apply", E, r, c, Rp, transposed);
   B200_CHECK_ARG(aligned16(xp) && aligned16(p), B200MOE_E_ALIGN, "muon_apply: pointers must be 16-byte aligned");
   const cudaStream_t s = (cudaStream_t)stream;
   const __nv_bfloat16* o = (const __nv_bfloat16*)xp;

@@ -152,7 +152,12 @@ class FusedMuon(torch.optim.Optimizer):
     DEFAULT_NS_DTYPE = torch.bfloat16
 
     def __init__(self, params, lr=3e-4, momentum=0.95, nesterov=True, weight_decay=0.0, coeffs=DSV4_COEFFS,
-                 ns_dtype=None, scale_mode="aurora", use_graph=False, aurora_k=None, spectral_wd=0.0, xorth_post=0.0):
+                 ns_dtype=None, scale_mode="aurora", ns_batch_elems=None, use_graph=False, graph_warmup=3,
+                 aurora_k=None, spectral_wd=0.0, swd_beta=0.99, xorth_post=0.0, xorth_backend="ns", xorth_ns_iters=18,
+                 xorth_ema=0.95, xorth_gate_ref=0.3, xorth_warmup_steps=0, xorth_where="post"):
+        # the reference's argument list (kernels/sm75/muon.py:112-118).  ns_batch_elems (its cap on the rows of one
+        # batched call, a memory knob), graph_warmup, swd_beta and the xorth_* details are accepted and unused:
+        # they only act together with options that are rejected below.
         if scale_mode not in ("polar", "aurora"):
             raise ValueError(f"scale_mode {scale_mode!r} is not built here; use 'polar' or 'aurora'")
         if aurora_k not in (None, 1):
@@ -162,7 +167,8 @@ class FusedMuon(torch.optim.Optimizer):
         ns_dtype = self.DEFAULT_NS_DTYPE if ns_dtype is None else ns_dtype
         if ns_dtype != torch.bfloat16:
             raise ValueError(f"the iteration runs in bfloat16 only, got ns_dtype={ns_dtype}")
-        super().__init__(params, dict(lr=lr, momentum=momentum, nesterov=nesterov, weight_decay=weight_decay))
+        super().__init__(params, dict(lr=lr, momentum=momentum, nesterov=nesterov, weight_decay=weight_decay,
+                                      xorth_post=0.0))
         self.coeffs, self.ns_dtype, self.scale_mode = coeffs, ns_dtype, scale_mode
 
     @torch.no_grad()
@@ -173,6 +179,8 @@ class FusedMuon(torch.optim.Optimizer):
                 loss = closure()
         for group in self.param_groups:
             lr, mu, wd, nesterov = group["lr"], group["momentum"], group["weight_decay"], group["nesterov"]
+            if group.get("xorth_post", 0.0) != 0:               # a group-level option in the reference (:119-124)
+                raise ValueError("xorth_post (cross-expert whitening) is not built here")
             for p in group["params"]:
                 if p.grad is None or p.dim() not in (2, 3):      # as the reference: other shapes are not stepped
                     continue
