@@ -157,6 +157,28 @@ def test_moe_against_reference_golden(pkg, golden_dir, name):
         assert torch.isfinite(t.grad).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_moe_takes_fp32_and_fp16_tensors(pkg, golden_dir, dtype):
+    """Benchmark config 1 is stated in fp32: fp32 / fp16 callers get the bf16 computation with results and
+    gradients in their own dtypes, within the bf16 tolerance of the reference's fp32 outputs."""
+    T, H, E, I, k, seed, bstd, cap = CASES["cfg1"]
+    g = np.load(os.path.join(golden_dir, "experts_cfg1.npz"))
+    inp = O.make_inputs(T, H, E, I, k, seed=seed, bias_std=bstd)
+    idx, w = torch.from_numpy(g["idx"]).to(DEV), torch.from_numpy(g["w"]).to(DEV).requires_grad_(True)
+    hidden = inp["x"].to(dtype).to(DEV).requires_grad_(True)
+    gu = inp["gate_up"].to(dtype).to(DEV).requires_grad_(True)
+    dn = inp["down"].to(dtype).to(DEV).requires_grad_(True)
+    out = pkg.moe(hidden, idx, w, gu, dn, torch.zeros(E, dtype=torch.int32, device=DEV))
+    (out.float() * inp["grad_out"].to(DEV).float()).sum().backward()
+    pkg.check_status()
+    assert out.dtype == dtype and hidden.grad.dtype == dtype and gu.grad.dtype == dtype and dn.grad.dtype == dtype
+    assert O.rel_l2(out.float().cpu(), torch.from_numpy(g["out"])) < TOL_BF16
+    assert O.rel_l2(hidden.grad.float().cpu(), torch.from_numpy(g["grad_hidden"])) < TOL_BF16
+    assert O.rel_l2(w.grad.float().cpu(), torch.from_numpy(g["grad_w"])) < TOL_BF16
+    assert O.rel_l2(sub(gu.grad.float().cpu()), torch.from_numpy(g["grad_gate_up_sub"])) < TOL_BF16
+    assert O.rel_l2(sub(dn.grad.float().cpu()), torch.from_numpy(g["grad_down_sub"])) < TOL_BF16
+
+
 def test_moe_mid_size_vs_oracle_and_determinism(pkg):
     T, H, E, I, k = 4096, 1024, 16, 704, 4
     inp = O.make_inputs(T, H, E, I, k, seed=5, dtype=torch.bfloat16)

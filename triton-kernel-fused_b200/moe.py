@@ -189,7 +189,7 @@ def _empty_result(hidden, top_k_weights, *params):
 
 
 def moe(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes, act_params=None):
-    """hidden (N,H) bf16, indices (N,k) int64, weights (N,k) float, gate_up_proj (E_glu,2I,H),
+    """hidden (N,H) bf16 (fp16 / fp32: computed in bf16), indices (N,k) int64, weights (N,k) float, gate_up_proj (E_glu,2I,H),
     down_proj (E_glu,H,I), act_codes (E,) int32, act_params (E,2) fp32 [alpha,gamma] for code 5 or None
     -> (N,H).  Same contract as the reference's `moe` (kernels/sm75/moe.py:838-855); differentiable
     w.r.t. hidden, weights, both projections and act_params.  A pure SiLU-GLU stack runs with the
@@ -197,6 +197,14 @@ def moe(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes
     codes, n_glu = _code_info(act_codes)
     if hidden.shape[0] == 0:
         return _empty_result(hidden, top_k_weights, gate_up_proj, down_proj, act_params)
+    if hidden.dtype in (torch.float16, torch.float32) and not torch.is_autocast_enabled("cuda"):
+        # The reference computes in hidden's dtype.  The kernels here are bf16 (fp32 accumulation): fp16 / fp32 callers
+        # get the bf16 computation, the result in their dtype and, through the casts, gradients in the dtypes of
+        # their tensors.  Accuracy is that of the bf16 path (2e-2 relative L2 against fp32).
+        bf = torch.bfloat16
+        out = moe(hidden.to(bf), top_k_indices, top_k_weights, gate_up_proj.to(bf), down_proj.to(bf), act_codes,
+                  act_params)
+        return out.to(hidden.dtype)
     if act_params is None and n_glu == len(codes) and all(c == 0 for c in codes):
         return _GroupedMoE.apply(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes)
     return _PolyGLUMoE.apply(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes, act_params)
