@@ -138,3 +138,30 @@ def test_a_shard_of_a_stack_steps_like_the_whole_stack(pkg):
         sp, sm = step(lo, hi)
         assert torch.equal(sp, full_p[lo:hi]) and torch.equal(sm, full_m[lo:hi])
     torch.cuda.synchronize(); pkg.check_status()
+
+
+def test_same_shape_parameters_step_as_one_stack(pkg):
+    """2-D and 3-D parameters with the same matrix shape are orthogonalised in one batched stack (the reference's
+    batched-state design); every parameter ends up exactly where it would stepping alone, also when the cap on the
+    batch splits the stack into chunks."""
+    g = torch.Generator().manual_seed(17)
+    shapes = [(128, 192), (128, 192), (3, 128, 192), (192, 128), (128, 192)]
+    init = [(torch.randn(*s, generator=g) * 0.02) for s in shapes]
+    grads = [torch.randn(*s, generator=g) for s in shapes]
+
+    def run(split, cap):
+        ps = [torch.nn.Parameter(t.clone().to(DEV)) for t in init]
+        opts = ([pkg.FusedMuon([p], lr=0.01, weight_decay=0.1) for p in ps] if split
+                else [pkg.FusedMuon(ps, lr=0.01, weight_decay=0.1, ns_batch_elems=cap)])
+        for _ in range(2):
+            for p, gr in zip(ps, grads):
+                p.grad = gr.to(DEV)
+            for o in opts:
+                o.step()
+        torch.cuda.synchronize(); pkg.check_status()
+        return [p.detach().clone() for p in ps]
+
+    alone = run(True, None)
+    for cap in (64 * 1024 * 1024, 2 * 128 * 192, 1):        # one stack of 6; chunks of at most 2 matrices; one by one
+        for a, b in zip(alone, run(False, cap)):
+            assert torch.equal(a, b)

@@ -54,8 +54,8 @@ def _check_stack(name: str, t: torch.Tensor):
 
 
 @ops._op("muon_momentum", 1)
-def _momentum(grad, mom, mu, nesterov):
-    u = torch.empty_like(mom)
+def _momentum(grad, mom, mu, nesterov, out=None):
+    u = torch.empty_like(mom) if out is None else out
     L.check(L.lib().b200moe_muon_momentum(L.ptr(grad), 1 if grad.dtype == torch.float32 else 0, L.ptr(mom), L.ptr(u),
                                           mom.numel(), float(mu), 1 if nesterov else 0, L.stream_of(mom)))
     return u
@@ -147,17 +147,18 @@ class FusedMuon(torch.optim.Optimizer):
     """Muon for matrices and stacks of matrices; constructor and state follow the reference's `FusedMuon`
     (kernels/sm75/muon.py:91-137).  Parameters are CUDA tensors, bf16 or fp32 (fp32 master weights), 2-D or 3-D,
     with gradients in bf16 or fp32; the momentum buffer `muon_mom` is bf16 (the iteration dtype) and is kept per
-    parameter, shaped (E, r, c)."""
+    parameter, shaped (E, r, c).  Same-shape parameters of a group are orthogonalised together as one stack."""
 
     DEFAULT_NS_DTYPE = torch.bfloat16
 
     def __init__(self, params, lr=3e-4, momentum=0.95, nesterov=True, weight_decay=0.0, coeffs=DSV4_COEFFS,
-                 ns_dtype=None, scale_mode="aurora", ns_batch_elems=None, use_graph=False, graph_warmup=3,
+                 ns_dtype=None, scale_mode="aurora", ns_batch_elems=64 * 1024 * 1024, use_graph=False, graph_warmup=3,
                  aurora_k=None, spectral_wd=0.0, swd_beta=0.99, xorth_post=0.0, xorth_backend="ns", xorth_ns_iters=18,
                  xorth_ema=0.95, xorth_gate_ref=0.3, xorth_warmup_steps=0, xorth_where="post"):
-        # the reference's argument list (kernels/sm75/muon.py:112-118).  ns_batch_elems (its cap on the rows of one
-        # batched call, a memory knob), graph_warmup, swd_beta and the xorth_* details are accepted and unused:
-        # they only act together with options that are rejected below.
+        # the reference's argument list (kernels/sm75/muon.py:112-118).  ns_batch_elems caps the elements of one
+        # batched stack of same-shape parameters (the reference defaults to 4M for a 16 GB T4; 64M here = 128 MB of
+        # bf16 per buffer); graph_warmup, swd_beta and the xorth_* details are accepted and unused: they only act
+        # together with options that are rejected below.
         if scale_mode not in ("polar", "aurora"):
             raise ValueError(f"scale_mode {scale_mode!r} is not built here; use 'polar' or 'aurora'")
         if aurora_k not in (None, 1):
@@ -170,6 +171,7 @@ class FusedMuon(torch.optim.Optimizer):
         super().__init__(params, dict(lr=lr, momentum=momentum, nesterov=nesterov, weight_decay=weight_decay,
                                       xorth_post=0.0))
         self.coeffs, self.ns_dtype, self.scale_mode = coeffs, ns_dtype, scale_mode
+        self.ns_batch_elems = int(ns_batch_elems)
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -181,29 +183,52 @@ class FusedMuon(torch.optim.Optimizer):
             lr, mu, wd, nesterov = group["lr"], group["momentum"], group["weight_decay"], group["nesterov"]
             if group.get("xorth_post", 0.0) != 0:               # a group-level option in the reference (:119-124)
                 raise ValueError("xorth_post (cross-expert whitening) is not built here")
+            # Same-shape parameters are orthogonalised as ONE stack (the reference's batched-state design,
+            # kernels/sm75/muon.py:215-248): a 2-D parameter contributes one matrix, a 3-D one its E matrices.  Chunks
+            # are capped at ns_batch_elems elements with parameters kept whole, as in the reference (:239-247).
+            buckets = {}
             for p in group["params"]:
                 if p.grad is None or p.dim() not in (2, 3):      # as the reference: other shapes are not stepped
                     continue
-                self._step_one(p, lr, mu, wd, nesterov)
+                buckets.setdefault((p.shape[-2], p.shape[-1], p.device), []).append(p)
+            for (r, c, _dev), ps in buckets.items():
+                cap = max(1, self.ns_batch_elems // (r * c))
+                chunk, n = [], 0
+                for p in ps:
+                    n_p = p.numel() // (r * c)
+                    if chunk and n + n_p > cap:
+                        self._step_chunk(chunk, n, r, c, lr, mu, wd, nesterov)
+                        chunk, n = [], 0
+                    chunk.append(p)
+                    n += n_p
+                if chunk:
+                    self._step_chunk(chunk, n, r, c, lr, mu, wd, nesterov)
         return loss
 
-    def _step_one(self, p, lr, mu, wd, nesterov):
-        E, r, c = _check_stack("parameter", p)
-        g = p.grad
-        L.require(p.is_contiguous(), "parameters must be contiguous")
-        L.require(p.dtype in (torch.bfloat16, torch.float32) and g.dtype in (torch.bfloat16, torch.float32),
-                  f"parameters and gradients must be bfloat16 or float32, got {p.dtype} / {g.dtype}")
-        g = g.contiguous()
-        st = self.state[p]
-        if "muon_mom" not in st:
-            st["muon_mom"] = torch.zeros(E, r, c, dtype=torch.bfloat16, device=p.device)
-        u = _momentum(g, st["muon_mom"], mu, nesterov)
+    def _step_chunk(self, ps, n, r, c, lr, mu, wd, nesterov):
+        """One stack of n matrices (r, c) gathered from the parameters `ps`."""
+        dev = ps[0].device
+        u = torch.empty(n, r, c, dtype=torch.bfloat16, device=dev)
+        off, spans = 0, []
+        for p in ps:
+            E, _, _ = _check_stack("parameter", p)
+            g = p.grad
+            L.require(p.is_contiguous(), "parameters must be contiguous")
+            L.require(p.dtype in (torch.bfloat16, torch.float32) and g.dtype in (torch.bfloat16, torch.float32),
+                      f"parameters and gradients must be bfloat16 or float32, got {p.dtype} / {g.dtype}")
+            st = self.state[p]
+            if "muon_mom" not in st:
+                st["muon_mom"] = torch.zeros(E, r, c, dtype=torch.bfloat16, device=dev)
+            _momentum(g.contiguous(), st["muon_mom"], mu, nesterov, out=u[off:off + E])
+            spans.append((p, off, E))
+            off += E
         if self.scale_mode == "aurora":                           # kernels/muon/muon_scaling.py:101-112
             tgt = (min(r, c) / r) ** 0.5
-            u, rowss = _prescale_rows(u, _row_sumsq(u, E * r, c), E * r, c, tgt)
+            u, rowss = _prescale_rows(u, _row_sumsq(u, n * r, c), n * r, c, tgt)
             gain, alpha = RMS_TARGET * max(r, c) ** 0.5, -lr
         else:                                                     # kernels/muon/muon_scaling.py:79-83
             rowss = None
             gain, alpha = 1.0, -lr * RMS_TARGET * max(r, c) ** 0.5
-        X, Rp, tall = _orthogonalise_packed(u, E, r, c, self.coeffs, 1e-7, rowss)
-        _apply(X, E, r, c, Rp, tall, gain, 1.0 - lr * wd, alpha, p)
+        X, Rp, tall = _orthogonalise_packed(u, n, r, c, self.coeffs, 1e-7, rowss)
+        for p, o, E in spans:
+            _apply(X[o:o + E], E, r, c, Rp, tall, gain, 1.0 - lr * wd, alpha, p)
