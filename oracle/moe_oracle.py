@@ -7,10 +7,13 @@ Every function restates, in plain PyTorch on the CPU, what one piece of the refe
 (IsNoobgrammer/triton-kernel-fused) computes, and cites the reference lines it follows.
 Parity pin: `tests/golden/make_golden.py` runs the reference's own `moe_eager` and
 `_sort_by_expert` (they import and run on CPU) and stores their outputs; `tests/test_oracle.py`
-checks this module against those stored outputs.  The fused router epilogue of the reference is a
-Triton kernel that cannot run without a GPU, so `router_epilogue_fwd/bwd` are pinned against the
-two eager statements of the same router in the reference tree (bench.py:414-422 and
-.autoresearch/train_grok_moe.py:72-77) on tie-free inputs, and against autograd for the backward.
+checks this module against those stored outputs.  The router functions are pinned on the
+reference's own fused kernels: `tests/golden/make_golden_router.py` runs `_epilogue_fwd`,
+`_router_epilogue_bwd_kernel`, `_count_experts`, `FusedMLPRouter`, `FusedConvRouterCuDNN` and
+`router_bias_update` of kernels/sm75/router.py under the Triton interpreter on CPU tensors
+(tie-free logits and logits full of exact ties), and `tests/test_router_golden.py` holds
+`router_epilogue_fwd/bwd`, `mlp_router_fwd/bwd`, `conv_router_logits` and `router_bias_update`
+to those outputs (picks and counts bit-exact, weights 1e-6, gradients 1e-5).
 """
 from __future__ import annotations
 

@@ -97,3 +97,62 @@ def muon_step_inputs(name):
     p0 = torch.randn(*shape, generator=g) * 0.02
     grads = [torch.randn(*shape, generator=g) for _ in range(steps)]
     return p0, grads
+
+
+# ---- router cases pinned on the reference's own Triton kernels run under the Triton interpreter on CPU tensors.
+# Epilogue cases: name -> (N, E, k, norm_topk, scale, use_bias, kind, seed)
+#   kind "f32"  : tie-free fp32 logits ~ N(0,1)
+#   kind "grid" : fp32 logits on a coarse grid (multiples of 1/4 in [-1, 1]): every row is full of exact ties
+#   kind "bf16" : bf16 tensor of grid logits (ties survive the dtype)
+ROUTER_EPI_CASES = {
+    "f32_e8_k2": (300, 8, 2, True, 1.0, True, "f32", 31),
+    "f32_e64_k6": (300, 64, 6, True, 1.0, False, "f32", 32),
+    "f32_e64_k6_bias_scale": (300, 64, 6, True, 2.5, True, "f32", 33),
+    "f32_e128_k8_nonorm": (260, 128, 8, False, 1.0, True, "f32", 34),
+    "f32_e256_k8": (200, 256, 8, True, 0.5, True, "f32", 35),
+    "f32_e11_k1": (140, 11, 1, True, 1.0, True, "f32", 36),
+    "grid_e8_k2": (300, 8, 2, True, 1.0, False, "grid", 37),
+    "grid_e64_k6_bias": (300, 64, 6, True, 1.0, True, "grid", 38),
+    "grid_e256_k8": (150, 256, 8, True, 1.0, False, "grid", 39),
+    "bf16_e64_k6": (300, 64, 6, True, 1.0, False, "bf16", 40),
+    "bf16_e128_k8_bias": (200, 128, 8, True, 1.5, True, "bf16", 41),
+}
+# Whole linear / conv router cases: name -> (B, S, H, E, k, K (0 = linear router), norm, scale, use_bias, seed)
+ROUTER_FULL_CASES = {
+    "mlp_e8_k2": (2, 96, 64, 8, 2, 0, True, 1.0, True, 51),
+    "mlp_e64_k6": (1, 200, 96, 64, 6, 0, True, 2.0, False, 52),
+    "mlp_e16_k4_nonorm": (3, 50, 64, 16, 4, 0, False, 1.0, True, 53),
+    "conv_e11_k2_K4": (2, 80, 64, 11, 2, 4, True, 1.0, True, 54),
+    "conv_e16_k4_K3": (3, 40, 32, 16, 4, 3, True, 1.5, False, 55),
+}
+
+
+def router_epi_inputs(name):
+    """(logits, bias or None, upstream gradient of the weights) of an epilogue case, seeded."""
+    import torch
+    N, E, k, _norm, _scale, use_bias, kind, seed = ROUTER_EPI_CASES[name]
+    g = torch.Generator().manual_seed(seed)
+    if kind == "f32":
+        logits = torch.randn(N, E, generator=g)
+    else:
+        logits = torch.randint(-4, 5, (N, E), generator=g).float() * 0.25
+        if kind == "bf16":
+            logits = logits.to(torch.bfloat16)
+    # a bias on the same coarse grid keeps sel = score + bias full of ties in the grid cases
+    bias = None
+    if use_bias:
+        bias = (torch.randint(-2, 3, (E,), generator=g).float() * 0.125) if kind != "f32" else torch.randn(E, generator=g) * 0.01
+    grad_w = torch.randn(N, k, generator=g)
+    return logits, bias, grad_w
+
+
+def router_full_inputs(name):
+    """(x (B,S,H), weight (E,H) or (E,H,K), bias or None, upstream gradient of the weights (B*S,k)), fp32, seeded."""
+    import torch
+    B, S, H, E, k, K, _norm, _scale, use_bias, seed = ROUTER_FULL_CASES[name]
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, S, H, generator=g)
+    w = torch.randn(*((E, H, K) if K else (E, H)), generator=g) * (0.1 if K else 0.2)
+    bias = torch.randn(E, generator=g) * 0.01 if use_bias else None
+    grad_w = torch.randn(B * S, k, generator=g)
+    return x, w, bias, grad_w
