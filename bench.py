@@ -1,7 +1,7 @@
 """Benchmark of the MoE layer (router -> permute -> grouped expert GEMMs -> combine), forward and
 backward, on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|torch_grouped]
 
 One step = one forward + backward pass of the layer over one batch of synthetic tokens
 (x ~ N(0,1), weights ~ N(0,0.02), upstream gradient ~ N(0,1), random-init weights).
@@ -12,7 +12,15 @@ Prints ONE JSON line on rank 0.  `value` = tokens/s of the whole job with inputs
 gradient, D2H of the output and grad_x inside the timed region).
 
 `--impl reference` times the reference's eager algorithm (the CPU oracle port) on the host cores
-on a bounded token sample of the same configuration.
+on a bounded token sample of the same configuration (rank 0, all host threads).
+`--impl torch_grouped` times a plain-PyTorch composition of the reference's library path (sort ->
+torch._grouped_mm x2 with SiLU-GLU between -> index_add_, autograd backward) on the same GPU: a same-box
+library yardstick reported beside the number, not a target and not part of this package.
+
+Beside the headline, the line carries `secondary` (the skewed-routing and the MXFP8 configurations at N = 1,
+the 65536-token expert-parallel configuration at N > 1, a few steps each) and, at N > 1, `ep_parity`: one
+forward + backward of a small expert-parallel layer checked against the single-GPU layer on the concatenated
+batch; the process exits non-zero when that check fails.
 """
 from __future__ import annotations
 
@@ -54,17 +62,38 @@ NCU_TRAFFIC = {"rows": 24576, "H": 2048, "I": 1408, "rows_per_expert": 1536,
 
 
 def _peaks(precision="bf16"):
+    """Measured denominators (MEASURED_PEAKS.json): the cuBLAS bf16 rate as a burst and sustained under the
+    power cap.  Which of the two a measurement is divided by follows the SM clock sampled during it
+    (`_pick_peak`)."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        d = dict(hbm_gbs=p["hbm_gbs"], tflops=p.get("bf16_tflops_sustained", p["bf16_tflops"]),
-                 source="measured (MEASURED_PEAKS.json, sustained bf16)")
+        d = dict(hbm_gbs=p["hbm_gbs"], burst=p["bf16_tflops"], sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                 source="measured (MEASURED_PEAKS.json)")
     else:
-        d = dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback (6.65 TB/s, 1.4 PFLOP/s sustained)")
+        d = dict(hbm_gbs=6650.0, burst=1590.0, sustained=1400.0, source="fallback (6.65 TB/s, 1.59 / 1.4 PFLOP/s)")
     if precision == "mxfp8":   # no fp8 measurement exists: the fp8 tensor rate is twice the bf16 rate
-        d["tflops"] *= 2.0
+        d["burst"] *= 2.0
+        d["sustained"] *= 2.0
         d["source"] = "2 x " + d["source"] + " (fp8 dense rate = 2 x bf16; no fp8 peak was measured)"
     return d
+
+
+def _pick_peak(peaks, clocks):
+    """Like for like: a timed region whose median SM clock stayed at >= 90 % of the maximum ran in the regime the
+    burst figure was taken in; below that (power cap) it is compared with the sustained figure."""
+    sm, mx = (clocks or {}).get("sm_mhz"), (clocks or {}).get("sm_max_mhz")
+    if sm and mx and sm >= 0.9 * mx:
+        return "burst", peaks["burst"]
+    if sm and mx:
+        return "sustained", peaks["sustained"]
+    return "sustained (no clock sample)", peaks["sustained"]
+
+
+def _fractions(tflops, peaks, clocks):
+    rule, peak = _pick_peak(peaks, clocks)
+    return dict(frac=round(tflops / peak, 4), peak=peak, rule=rule,
+                frac_of_burst=round(tflops / peaks["burst"], 4), frac_of_sustained=round(tflops / peaks["sustained"], 4))
 
 
 class ClockSampler:
@@ -113,10 +142,31 @@ class ClockSampler:
                     samples=len(sm), reasons=sorted(reasons))
 
 
+def _ep_settings():
+    """Transport and exchange of the expert-parallel layer in this run (environment overrides for A/B runs)."""
+    return dict(transport=os.environ.get("B200MOE_EP_TRANSPORT", "p2p"), exchange=os.environ.get("B200MOE_EP_EXCHANGE", "push"),
+                overlap_chunks=int(os.environ.get("B200MOE_EP_CHUNKS", "1")),
+                reserved_sms=int(os.environ.get("B200MOE_EP_RESERVED_SMS", "12")))
+
+
+def _parallelism_label(n_gpus):
+    if n_gpus == 1:
+        return "single GPU"
+    ep = _ep_settings()
+    if ep["transport"] == "nccl":
+        plane = "rows by NCCL all_to_all_single, four payload exchanges per step"
+    elif ep["exchange"] == "push":
+        plane = ("peer memory over NVLink: token rows pulled by the experts' owners, result rows pushed home by the "
+                 "GEMM epilogues; NCCL carries only the count all-gather")
+    else:
+        plane = "peer memory over NVLink: rows pulled in both directions; NCCL carries only the count all-gather"
+    return f"expert parallel ep{n_gpus} (E/{n_gpus} experts per GPU; transport={ep['transport']}, exchange={ep['exchange']}: {plane})"
+
+
 def _workload(n_gpus, which="headline"):
     """Per-rank workload.  N=1: the headline layer on one GPU.  N>1: the same layer expert-parallel:
-    every rank keeps T tokens (weak scaling in tokens) and owns E/N of the experts; rows travel by NCCL
-    all-to-all.  `ep5` is the expert-parallel configuration with 65536 global tokens."""
+    every rank keeps T tokens (weak scaling in tokens) and owns E/N of the experts.  `ep5` is the
+    expert-parallel configuration with 65536 global tokens."""
     if which == "ep5":
         w = dict(EP5)
         w["T"] = EP5["T"] // n_gpus
@@ -126,9 +176,10 @@ def _workload(n_gpus, which="headline"):
         w = dict(ZIPF)
     else:
         w = dict(HEADLINE if which == "headline" else PROFILE)
+    w["which"] = which
     w["precision"] = "mxfp8" if which.startswith("mxfp8") else "bf16"
     w["name"] = (w["precision"] + " MoE layer T={T}/GPU H={H} E={E} I={I} top{k} fwd+bwd").format(**w)
-    w["parallelism"] = "single GPU" if n_gpus == 1 else f"expert parallel ep{n_gpus} (E/{n_gpus} experts per GPU, NCCL all-to-all)"
+    w["parallelism"] = _parallelism_label(n_gpus)
     return w
 
 
@@ -136,45 +187,86 @@ def _make_layer(pkg, w, device, seed, world):
     torch.manual_seed(seed)
     with torch.device(device):      # build the (large) expert stacks directly on the GPU
         if world > 1:
-            layer = pkg.ExpertParallelMoELayer(w["H"], w["I"], w["E"], top_k=w["k"],
-                                               overlap_chunks=int(os.environ.get("B200MOE_EP_CHUNKS", "1")),
-                                               reserved_sms=int(os.environ.get("B200MOE_EP_RESERVED_SMS", "12")),
-                                               transport=os.environ.get("B200MOE_EP_TRANSPORT", "p2p"),
-                                               exchange=os.environ.get("B200MOE_EP_EXCHANGE", "push"))
+            layer = pkg.ExpertParallelMoELayer(w["H"], w["I"], w["E"], top_k=w["k"], **_ep_settings())
         else:
             layer = pkg.MoELayer(w["H"], w["I"], w["E"], top_k=w["k"], precision=w["precision"])
-    return layer.to(torch.bfloat16)
+    layer = layer.to(torch.bfloat16)
+    if w["which"] == "zipf":   # selection bias = 0.15 x log of Zipf(1.1) frequencies over a seeded expert order
+        gz = torch.Generator().manual_seed(7)
+        ranks = (torch.randperm(w["E"], generator=gz) + 1).float()
+        pz = ranks.pow(-1.1)
+        layer.bias.copy_((0.15 * torch.log(pz / pz.sum())).to(device))
+    return layer
 
 
-def run_ours(args):
-    rank = int(os.environ.get("RANK", 0))
-    world = int(os.environ.get("WORLD_SIZE", 1))
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
-    pkg = importlib.import_module(PKG)
-    pkg.lib()
+GEMM_OPS = ("expert_gate_up_swiglu", "expert_down", "expert_down_dgrad_glu", "expert_gate_up_dgrad", "expert_wgrad",
+            "expert_linear_push", "mxfp8_expert_gemm", "mxfp8_expert_wgrad")
+
+
+def _gemm_flops(w):
+    """Algorithmic FLOPs per launch of each expert GEMM op (padding rows not counted)."""
+    M, H, I = w["T"] * w["k"], w["H"], w["I"]
+    return {"expert_gate_up_swiglu": 2.0 * M * H * 2 * I, "expert_down": 2.0 * M * I * H,
+            "expert_down_dgrad_glu": 2.0 * M * H * I, "expert_gate_up_dgrad": 2.0 * M * 2 * I * H,
+            "expert_wgrad": (2.0 * M * H * I + 2.0 * M * 2 * I * H) / 2.0,   # two launches per step, averaged
+            "expert_linear_push": (2.0 * M * I * H + 2.0 * M * 2 * I * H) / 2.0,   # down + gate/up dgrad, averaged
+            "mxfp8_expert_gemm": 12.0 * M * H * I / 4.0,                     # four launches per step, averaged
+            "mxfp8_expert_wgrad": 6.0 * M * H * I / 2.0}
+
+
+class Ctx:
+    """Process-wide pieces of one benchmark run."""
+
+    def __init__(self):
+        self.rank = int(os.environ.get("RANK", 0))
+        self.world = int(os.environ.get("WORLD_SIZE", 1))
+        self.local = int(os.environ.get("LOCAL_RANK", 0))
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=self.dev)
+            self.dist = dist
+        self.pkg = importlib.import_module(PKG)
+        self.pkg.lib()
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(self, fn, steps, after=None):
+        """CUDA events on the launching stream around exactly `steps` calls, barrier + synchronize on both
+        sides, maximum over the ranks."""
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        if after is not None:
+            after()                       # the last copies finish inside the timed region
+        e1.record()
+        self.barrier()
+        ms = e0.elapsed_time(e1)
+        if self.dist is not None:
+            t = torch.tensor([ms], device=self.dev)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+
+def measure_layer(cx, w, steps, n_warm, e2e=True):
+    """Build the layer of workload `w`, warm up, time `steps` steps with inputs resident in HBM (per-op CUDA
+    events on the launching stream) and, if asked, the same through host buffers.  Returns a dict of raw figures."""
+    pkg, dev, rank, world = cx.pkg, cx.dev, cx.rank, cx.world
     ops = pkg.ops
-    w = _workload(world, args.workload)
-    T, H, E, I, k = w["T"], w["H"], w["E"], w["I"], w["k"]
+    T, H = w["T"], w["H"]
     layer = _make_layer(pkg, w, dev, seed=0, world=world)
     params = [layer.gate.weight, layer.gate_up_proj, layer.down_proj]
-    if args.workload == "zipf":   # selection bias = 0.15 x log of Zipf(1.1) frequencies over a seeded expert order
-        gz = torch.Generator().manual_seed(7)
-        ranks = (torch.randperm(E, generator=gz) + 1).float()
-        pz = ranks.pow(-1.1)
-        layer.bias.copy_((0.15 * torch.log(pz / pz.sum())).to(dev))
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     x_dev = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
     go_dev = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
-    x_host = x_dev.cpu().pin_memory()
-    go_host = go_dev.cpu().pin_memory()
-    out_host = torch.empty_like(x_host).pin_memory()
-    gx_host = torch.empty_like(x_host).pin_memory()
 
     def step_resident():
         for p in params:
@@ -184,15 +276,44 @@ def run_ours(args):
         out.backward(go_dev)
         return out, x.grad
 
-    # e2e: every step copies its inputs from pinned host memory and its results back.  The copies run
-    # on two copy streams with double-buffered device tensors, so step i+1's H2D and step i-1's D2H
-    # overlap step i's kernels (a user's input pipeline does the same); nothing is skipped.
+    for _ in range(n_warm):
+        step_resident()
+    pkg.check_status()
+
+    # ---- timed region 1: inputs resident in HBM; per-op CUDA events on the launching stream
+    records = []
+    ops.set_hook(lambda name, launches, a, b: records.append((name, launches, a, b)))
+    sampler = ClockSampler(cx.local)
+    if rank == 0:
+        sampler.start()
+    ms_total = cx.timed(step_resident, steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ops.set_hook(None)
+    pkg.check_status()
+    per_op, launches = {}, 0
+    for name, n, a, b in records:
+        d = per_op.setdefault(name, [0.0, 0])
+        d[0] += a.elapsed_time(b)
+        d[1] += 1
+        launches += n
+    res = dict(ms_step=ms_total / steps, ms_total=ms_total, per_op=per_op, launches=launches, clocks=clocks,
+               counts=getattr(layer, "last_counts", None))
+    if not e2e:
+        return res
+
+    # ---- timed region 2: through the module with host buffers.  Every step copies its inputs from pinned host
+    # memory and its results back.  The copies run on two copy streams with double-buffered device tensors, so step
+    # i+1's H2D and step i-1's D2H overlap step i's kernels (a user's input pipeline does the same); nothing is skipped.
+    x_host = x_dev.cpu().pin_memory()
+    go_host = go_dev.cpu().pin_memory()
+    out_host = torch.empty_like(x_host).pin_memory()
+    gx_host = torch.empty_like(x_host).pin_memory()
     h2d, d2h = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     in_bufs = [(torch.empty_like(x_dev), torch.empty_like(go_dev)) for _ in range(2)]
     in_ready = [torch.cuda.Event() for _ in range(2)]
     in_free = [torch.cuda.Event() for _ in range(2)]
     out_done = [torch.cuda.Event() for _ in range(2)]
-    e2e_state = {"i": 0, "primed": False}
+    state = {"i": 0, "primed": False}
 
     def _upload(slot):
         with torch.cuda.stream(h2d):
@@ -201,120 +322,261 @@ def run_ours(args):
             in_bufs[slot][1].copy_(go_host, non_blocking=True)
             in_ready[slot].record(h2d)
 
-    def step_e2e():
+    def step_e2e(compute=True):
         cur = torch.cuda.current_stream(dev)
-        i = e2e_state["i"]
+        i = state["i"]
         slot = i & 1
-        if not e2e_state["primed"]:
+        if not state["primed"]:
             for ev in in_free + out_done:
                 ev.record(cur)
             _upload(slot)
-            e2e_state["primed"] = True
+            state["primed"] = True
         _upload(slot ^ 1)                      # next step's inputs travel while this step computes
-        for p in params:
-            p.grad = None
         cur.wait_event(in_ready[slot])
-        x = in_bufs[slot][0].detach().requires_grad_(True)
-        out = layer(x)
-        out.backward(in_bufs[slot][1])
-        in_free[slot].record(cur)
+        if compute:
+            for p in params:
+                p.grad = None
+            x = in_bufs[slot][0].detach().requires_grad_(True)
+            out = layer(x)
+            out.backward(in_bufs[slot][1])
+            out_t, gx_t = out.detach(), x.grad
+        else:                                  # copies only: the device tensors stand in for the results
+            out_t, gx_t = in_bufs[slot][0], in_bufs[slot][1]
         done = torch.cuda.Event()
         done.record(cur)
+        in_free[slot].record(cur)
         with torch.cuda.stream(d2h):
             d2h.wait_event(done)
-            out_host.copy_(out.detach(), non_blocking=True)
-            gx_host.copy_(x.grad, non_blocking=True)
-            out.record_stream(d2h)
-            x.grad.record_stream(d2h)
+            out_host.copy_(out_t, non_blocking=True)
+            gx_host.copy_(gx_t, non_blocking=True)
+            out_t.record_stream(d2h)
+            gx_t.record_stream(d2h)
             out_done[slot].record(d2h)
         cur.wait_event(out_done[slot ^ 1])     # at most one result copy in flight behind the compute
-        e2e_state["i"] = i + 1
+        state["i"] = i + 1
 
-    def drain_e2e():
+    def drain():
         torch.cuda.current_stream(dev).wait_stream(d2h)
         torch.cuda.current_stream(dev).wait_stream(h2d)
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps, after=None):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        if after is not None:
-            after()                       # the last copies finish inside the timed region
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if dist is not None:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
-
-    n_warm = args.warmup if args.workload.endswith("profile") else max(args.warmup, 3)
-    for _ in range(n_warm):
-        step_resident()
-    pkg.check_status()
-
-    # ---- timed region 1: inputs resident in HBM; per-op CUDA events on the launching stream
-    records = []
-    ops.set_hook(lambda name, launches, a, b: records.append((name, launches, a, b)))
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    ms_total = timed(step_resident, args.steps)
-    clocks = sampler.stop() if rank == 0 else None
-    ops.set_hook(None)
-    pkg.check_status()
-    per_op = {}
-    launches = 0
-    for name, n, a, b in records:
-        d = per_op.setdefault(name, [0.0, 0])
-        d[0] += a.elapsed_time(b)
-        d[1] += 1
-        launches += n
-    ms_step = ms_total / args.steps
-
-    # ---- timed region 2: through the module with host buffers
     for _ in range(min(2, n_warm)):
         step_e2e()
-    ms_e2e = timed(lambda: step_e2e(), args.steps, after=drain_e2e) / args.steps
+    res["ms_e2e"] = cx.timed(step_e2e, steps, after=drain) / steps
     pkg.check_status()
+    # what the host side alone allows: the same copies (2 x T x H bf16 each way per step and rank) with no kernels
+    # between them, all ranks at once; an e2e step cannot be faster than this on this host
+    for _ in range(2):
+        step_e2e(False)
+    res["ms_copy_only"] = cx.timed(lambda: step_e2e(False), steps, after=drain) / steps
+    return res
+
+
+def _kernel_table(res, w, steps):
+    flops = _gemm_flops(w)
+    kernels = {}
+    for name, (ms, n) in sorted(res["per_op"].items(), key=lambda kv: -kv[1][0]):
+        avg = ms / n
+        entry = dict(launches_per_step=n / steps, avg_ms=round(avg, 4), share=round(ms / res["ms_total"], 4))
+        if name in flops:
+            entry["tflops"] = round(flops[name] / (avg * 1e-3) / 1e12, 1)
+        kernels[name] = entry
+    return kernels
+
+
+def _secondary(cx, which, steps, n_warm):
+    """A few steps of another configuration after the headline, resident inputs only."""
+    torch.cuda.empty_cache()
+    w = _workload(cx.world, which)
+    res = measure_layer(cx, w, steps, n_warm, e2e=False)
+    if cx.rank != 0:
+        return None
+    peaks = _peaks(w["precision"])
+    tf = 18.0 * w["H"] * w["I"] * w["T"] * w["k"] / (res["ms_step"] * 1e-3) / 1e12
+    fr = _fractions(tf, peaks, res["clocks"])
+    out = {"workload": w["name"], "steps": steps, "warmup": n_warm, "ms_per_step": round(res["ms_step"], 4),
+           "tokens_per_s": round(w["T"] * cx.world / (res["ms_step"] * 1e-3), 1), "layer_tflops_per_gpu": round(tf, 1),
+           "layer_frac": fr["frac"], "layer_frac_rule": fr["rule"], "layer_frac_of_burst": fr["frac_of_burst"],
+           "layer_frac_of_sustained": fr["frac_of_sustained"], "peak_source": peaks["source"], "clocks": res["clocks"],
+           "kernels": _kernel_table(res, w, steps)}
+    if res["counts"] is not None:
+        c = res["counts"]
+        out["tokens_per_expert"] = {"min": int(c.min()), "max": int(c.max()), "experts_without_tokens": int((c == 0).sum())}
+    return out
+
+
+def _library_mxfp8_tflops(dev):
+    """cuBLAS's own MXFP8 GEMM (torch._scaled_mm with E8M0 block-32 scales) on this GPU in this run: the library
+    yardstick for the block-scaled kernels.  Returns TFLOP/s or the error text."""
+    try:
+        M, N, K = 16384, 8192, 8192
+        a = torch.randn(M, K, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(N, K, device=dev).to(torch.float8_e4m3fn)
+        blocks = lambda r, k: ((r + 127) // 128) * ((k // 32 + 3) // 4) * 512
+        sa = torch.full((blocks(M, K),), 127, dtype=torch.uint8, device=dev).view(torch.float8_e8m0fnu)
+        sb = torch.full((blocks(N, K),), 127, dtype=torch.uint8, device=dev).view(torch.float8_e8m0fnu)
+        fn = lambda: torch._scaled_mm(a, b.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return round(2.0 * M * N * K * 20 / (e0.elapsed_time(e1) * 1e-3) / 1e12, 1)
+    except Exception as exc:   # the box's torch may not expose MX scales
+        return f"unavailable: {repr(exc)[:160]}"
+
+
+EP_PARITY_TOL = 1e-2
+
+
+def ep_parity(cx):
+    """One forward + backward of a small expert-parallel layer (the transport and exchange of this run) against
+    the single-GPU layer holding all experts on the concatenated batch, plus one load-balance step.  Every rank
+    takes part; rank 0 compares.  Returns the report (rank 0) or None."""
+    pkg, dist, dev, rank, W = cx.pkg, cx.dist, cx.dev, cx.rank, cx.world
+    T, H, I, k = 1024, 512, 256, 4
+    E = 8 * W
+    El = E // W
+    gen = torch.Generator().manual_seed(1234)                       # the same full model on every rank
+    gate_w = (torch.randn(E, H, generator=gen) * 0.02).to(torch.bfloat16)
+    gu = (torch.randn(E, 2 * I, H, generator=gen) * 0.02).to(torch.bfloat16)
+    dn = (torch.randn(E, H, I, generator=gen) * 0.02).to(torch.bfloat16)
+    bias = torch.randn(E, generator=gen) * 0.01
+    x_all = torch.randn(W * T, H, generator=gen).to(torch.bfloat16)
+    go_all = torch.randn(W * T, H, generator=gen).to(torch.bfloat16)
+    ep = _ep_settings()
+    with torch.device(dev):
+        layer = pkg.ExpertParallelMoELayer(H, I, E, top_k=k, **ep).to(torch.bfloat16)
+    with torch.no_grad():
+        layer.gate.weight.copy_(gate_w)
+        layer.gate_up_proj.copy_(gu[rank * El:(rank + 1) * El])
+        layer.down_proj.copy_(dn[rank * El:(rank + 1) * El])
+        layer.bias.copy_(bias)
+    x = x_all[rank * T:(rank + 1) * T].to(dev).requires_grad_(True)
+    out = layer(x)
+    out.backward(go_all[rank * T:(rank + 1) * T].to(dev))
+    idx, _ = pkg.fused_mlp_router(x.detach(), layer.gate.weight, layer.bias, k, E)
+    layer.update_bias(0.001)
+    torch.cuda.synchronize()
+    pkg.check_status()
+
+    def gather(t):          # equal shapes on every rank -> list on every rank
+        parts = [torch.empty_like(t) for _ in range(W)]
+        dist.all_gather(parts, t.contiguous())
+        return parts
+
+    outs, gxs, idxs = gather(out.detach()), gather(x.grad), gather(idx)
+    ggu, gdn = gather(layer.gate_up_proj.grad), gather(layer.down_proj.grad)
+    biases = gather(layer.bias)
+    grw = layer.gate.weight.grad.float()
+    dist.all_reduce(grw)                                            # the replicated router weight holds local sums
+    if rank != 0:
+        return None
+    with torch.device(dev):
+        ref = pkg.MoELayer(H, I, E, top_k=k).to(torch.bfloat16)
+    with torch.no_grad():
+        ref.gate.weight.copy_(gate_w)
+        ref.gate_up_proj.copy_(gu)
+        ref.down_proj.copy_(dn)
+        ref.bias.copy_(bias)
+    xr = x_all.to(dev).requires_grad_(True)
+    out_r = ref(xr)
+    out_r.backward(go_all.to(dev))
+    idx_r, _ = pkg.fused_mlp_router(xr.detach(), ref.gate.weight, ref.bias, k, E)
+    ref.update_bias(0.001)
+    torch.cuda.synchronize()
+    pkg.check_status()
+
+    def rel(a, b):
+        a, b = a.double().flatten(), b.double().flatten()
+        return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+    errs = {"out": rel(torch.cat(outs), out_r.detach()), "grad_x": rel(torch.cat(gxs), xr.grad),
+            "grad_gate_up": rel(torch.cat(ggu), ref.gate_up_proj.grad), "grad_down": rel(torch.cat(gdn), ref.down_proj.grad),
+            "grad_router_w": rel(grw, ref.gate.weight.grad.float())}
+    routing_equal = bool(torch.equal(torch.cat(idxs), idx_r))
+    bias_same_on_all_ranks = all(bool(torch.equal(b, biases[0])) for b in biases)
+    bias_equals_single = bool(torch.equal(biases[0], ref.bias))
+    ok = routing_equal and bias_same_on_all_ranks and bias_equals_single and all(e < EP_PARITY_TOL for e in errs.values())
+    return {"passed": ok, "routing_equal": routing_equal, "rel_l2": {n: float(f"{e:.3e}") for n, e in errs.items()},
+            "tol": EP_PARITY_TOL, "bias_update": {"identical_on_all_ranks": bias_same_on_all_ranks,
+                                                  "equals_single_gpu": bias_equals_single},
+            "case": f"T={T}/rank H={H} E={E} I={I} top{k}, transport={ep['transport']}, exchange={ep['exchange']}, "
+                    f"against MoELayer with all {E} experts on the concatenated {W * T} tokens"}
+
+
+def _nvlink_bytes(index):
+    """Cumulative NVLink payload counters of one GPU (NVML field values, a read-only query): (tx, rx) bytes or None."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        ids = [pynvml.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_TX, pynvml.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_RX]
+        vals = pynvml.nvmlDeviceGetFieldValues(h, ids)
+        out = []
+        for v in vals:
+            if v.nvmlReturn != 0:
+                return None
+            out.append(int(v.value.ullVal) * 1024)     # the counters are in KiB
+        return tuple(out)
+    except Exception:
+        return None
+
+
+def run_ours(args):
+    cx = Ctx()
+    rank, world, dev, dist, pkg = cx.rank, cx.world, cx.dev, cx.dist, cx.pkg
+    parity = ep_parity(cx) if (world > 1 and not args.no_parity) else None
+    torch.cuda.empty_cache()
+    w = _workload(world, args.workload)
+    T, H, E, I, k = w["T"], w["H"], w["E"], w["I"], w["k"]
+    n_warm = args.warmup if args.workload.endswith("profile") else max(args.warmup, 3)
+    nv0 = _nvlink_bytes(cx.local) if (rank == 0 and world > 1) else None
+    res = measure_layer(cx, w, args.steps, n_warm, e2e=True)
+    nv1 = _nvlink_bytes(cx.local) if (rank == 0 and world > 1) else None
+    ms_step = res["ms_step"]
+
+    secondary = {}
+    if not args.no_secondary and args.workload == "headline":
+        sec_steps, sec_warm = max(3, min(args.steps, 10)), 3
+        names = ("zipf", "mxfp8") if world == 1 else ("ep5",)
+        for name in names:
+            try:
+                secondary[name] = _secondary(cx, name, sec_steps if name != "ep5" else max(3, min(args.steps, 5)), sec_warm)
+            except Exception as exc:            # the headline line is still printed
+                secondary[name] = {"failed": repr(exc)[:300]}
+        if world == 1:
+            torch.cuda.empty_cache()
+            lib = _library_mxfp8_tflops(dev)
+            if isinstance(secondary.get("mxfp8"), dict):
+                secondary["mxfp8"]["library_mxfp8_tflops"] = lib
+                secondary["mxfp8"]["library_mxfp8_what"] = ("torch._scaled_mm, e4m3 x e4m3 with E8M0 block-32 scales, "
+                                                             "16384 x 8192 x 8192, 20 calls, same GPU and run")
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
     peaks = _peaks(w["precision"])
+    clocks = res["clocks"]
     M = T * k
-    flops = {  # algorithmic FLOPs per launch (padding rows not counted)
-        "expert_gate_up_swiglu": 2.0 * M * H * 2 * I, "expert_down": 2.0 * M * I * H,
-        "expert_down_dgrad_glu": 2.0 * M * H * I, "expert_gate_up_dgrad": 2.0 * M * 2 * I * H,
-        "expert_wgrad": (2.0 * M * H * I + 2.0 * M * 2 * I * H) / 2.0,   # two launches per step, averaged
-        "mxfp8_expert_gemm": 12.0 * M * H * I / 4.0,                     # four launches per step, averaged
-        "mxfp8_expert_wgrad": 6.0 * M * H * I / 2.0,
-    }
-    kernels = {}
-    for name, (ms, n) in sorted(per_op.items(), key=lambda kv: -kv[1][0]):
-        avg = ms / n
-        entry = dict(launches_per_step=n / args.steps, avg_ms=round(avg, 4), share=round(ms / ms_total, 4))
-        if name in flops:
-            entry["tflops"] = round(flops[name] / (avg * 1e-3) / 1e12, 1)
-        kernels[name] = entry
-    gemm_ms = sum(per_op[n][0] for n in flops if n in per_op) / args.steps
-    top = max((n for n in flops if n in per_op), key=lambda n: per_op[n][0])
+    flops = _gemm_flops(w)
+    per_op = res["per_op"]
+    kernels = _kernel_table(res, w, args.steps)
+    gemm_ms = sum(per_op[n][0] for n in GEMM_OPS if n in per_op) / args.steps
+    top = max((n for n in GEMM_OPS if n in per_op), key=lambda n: per_op[n][0])
     top_avg_ms = per_op[top][0] / per_op[top][1]
     achieved = flops[top] / (top_avg_ms * 1e-3) / 1e12
     traffic = None
     if (H, I, M // E) == (NCU_TRAFFIC["H"], NCU_TRAFFIC["I"], NCU_TRAFFIC["rows_per_expert"]) and top in NCU_TRAFFIC["bytes"] \
             and w["precision"] == "bf16" and world == 1:
         traffic = round(NCU_TRAFFIC["bytes"][top] * M / NCU_TRAFFIC["rows"])
-    layer_flops = 18.0 * H * I * T * k
+    layer_tf = 18.0 * H * I * T * k / (ms_step * 1e-3) / 1e12
+    lf, kf = _fractions(layer_tf, peaks, clocks), _fractions(achieved, peaks, clocks)
+    counts = res["counts"]
     line = {
         "metric": METRIC, "value": round(T * world / (ms_step * 1e-3), 1), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": n_warm, "ms_per_step": round(ms_step, 4),
@@ -322,27 +584,52 @@ def run_ours(args):
         "config": {"workload": w["name"], "tokens_per_gpu": T, "d_model": H, "experts": E, "d_ff": I, "top_k": k,
                    "parallelism": w["parallelism"],
                    "l2": "no flush: the working set (expert weights + activations, several GB) exceeds the 126 MB L2"},
-        "tokens_per_expert": ({"min": int(layer.last_counts.min()), "max": int(layer.last_counts.max()),
-                               "experts_without_tokens": int((layer.last_counts == 0).sum())}
-                              if getattr(layer, "last_counts", None) is not None else None),
-        "layer_tflops_per_gpu": round(layer_flops / (ms_step * 1e-3) / 1e12, 1),
-        "layer_frac_of_peak": round(layer_flops / (ms_step * 1e-3) / 1e12 / peaks["tflops"], 4),
+        "tokens_per_expert": ({"min": int(counts.min()), "max": int(counts.max()),
+                               "experts_without_tokens": int((counts == 0).sum())} if counts is not None else None),
+        "layer_tflops_per_gpu": round(layer_tf, 1),
+        "layer_frac_of_peak": lf["frac"], "layer_frac_of_burst": lf["frac_of_burst"],
+        "layer_frac_of_sustained": lf["frac_of_sustained"],
         "gemm_ms_per_step": round(gemm_ms, 4),
         "roofline": {"bound": "tensor", "kernel": f"gemm_kernel via {top}", "achieved": round(achieved, 1),
-                     "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": round(achieved / peaks["tflops"], 4),
+                     "peak": kf["peak"], "unit": "TFLOP/s", "frac": kf["frac"],
+                     "peak_rule": f"{kf['rule']}: median SM clock {clocks.get('sm_mhz')} of {clocks.get('sm_max_mhz')} MHz "
+                                  "(>= 90 % of max -> burst cuBLAS figure, else the sustained one)",
+                     "frac_of_burst": kf["frac_of_burst"], "frac_of_sustained": kf["frac_of_sustained"],
+                     "peaks": {"bf16_tflops_burst": peaks["burst"], "bf16_tflops_sustained": peaks["sustained"]},
                      "traffic": traffic, "traffic_unit": "bytes per launch (ncu dram read+write, scaled from the "
                      "profile workload by routed rows)" if traffic else None, "peak_source": peaks["source"]},
         "kernels": kernels,
-        "e2e": {"value": round(T * world / (ms_e2e * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 4),
-                "h2d_bytes_per_step": 2 * T * H * 2, "d2h_bytes_per_step": 2 * T * H * 2},
-        "gpu_launches": launches,
+        "e2e": {"value": round(T * world / (res["ms_e2e"] * 1e-3), 1), "unit": "tokens/s",
+                "ms_per_step": round(res["ms_e2e"], 4),
+                "h2d_bytes_per_step": 2 * T * H * 2, "d2h_bytes_per_step": 2 * T * H * 2,
+                "host_copy_ceiling_ms": round(res["ms_copy_only"], 4),
+                "host_copy_ceiling_what": "the same pinned-memory copies on all ranks at once with no kernels between "
+                                          "them: the floor the host side sets for an e2e step"},
+        "gpu_launches": res["launches"],
         "clocks": clocks,
     }
+    if secondary:
+        line["secondary"] = secondary
+    if parity is not None:
+        line["ep_parity"] = parity
+    if nv0 is not None and nv1 is not None:
+        steps_all = n_warm + args.steps + min(2, n_warm) + args.steps          # resident + host-buffer steps
+        sent = (nv1[0] - nv0[0]) / steps_all
+        # what the design sends: a token row leaves once per remote owner GPU (dispatch, twice: x and grad_out),
+        # a result row once per remote routed row (forward and backward)
+        line["nvlink"] = {"tx_bytes_per_step_counted": round(sent), "rx_bytes_per_step_counted": round((nv1[1] - nv0[1]) / steps_all),
+                          "source": "NVML NVLINK_THROUGHPUT_DATA_TX/RX of GPU 0 before and after the timed regions "
+                                    f"(a query), divided by the {steps_all} layer steps between the two reads "
+                                    "(copy-only steps move nothing over NVLink)",
+                          "result_rows_bytes_per_step_algorithmic": round(2.0 * M * H * 2 * (world - 1) / world)}
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(w, steps=1, warmup=0)
     print(json.dumps(line), flush=True)
+    failed = parity is not None and not parity["passed"]
     if dist is not None:
         dist.destroy_process_group()
+    if failed:
+        sys.exit(3)
 
 
 def run_muon(args):
@@ -427,6 +714,7 @@ def run_muon(args):
     kernels = {name: dict(launches_per_step=n / args.steps, avg_ms=round(ms / n, 4), share=round(ms / ms_total, 4))
                for name, (ms, n) in sorted(per_op.items(), key=lambda kv: -kv[1][0])}
     achieved = flops / (gemm_ms * 1e-3) / 1e12
+    fr = _fractions(achieved, peaks, clocks)
     nbytes = sum(2 * n * r * c for n, r, c in shapes)
     line = {
         "metric": "expert_stack_muon_step_ms", "value": round(ms_step, 3), "unit": "ms", "n_gpus": 1, "steps": args.steps,
@@ -439,8 +727,9 @@ def run_muon(args):
         "step_tflops_reference_count": round(flops_ref / (ms_step * 1e-3) / 1e12, 1),
         "gemm_ms_per_step": round(gemm_ms, 3),
         "roofline": {"bound": "tensor", "kernel": "gemm_kernel via expert_gram / expert_linear_axpby / expert_linear_t (Newton-Schulz products)",
-                     "achieved": round(achieved, 1), "peak": peaks["tflops"], "unit": "TFLOP/s",
-                     "frac": round(achieved / peaks["tflops"], 4), "traffic": None, "peak_source": peaks["source"]},
+                     "achieved": round(achieved, 1), "peak": fr["peak"], "unit": "TFLOP/s", "frac": fr["frac"],
+                     "peak_rule": fr["rule"], "frac_of_burst": fr["frac_of_burst"],
+                     "frac_of_sustained": fr["frac_of_sustained"], "traffic": None, "peak_source": peaks["source"]},
         "kernels": kernels,
         "e2e": {"value": round(ms_e2e, 3), "unit": "ms", "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes},
         "gpu_launches": launches, "clocks": clocks,
@@ -482,16 +771,84 @@ def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", 1))
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm runs on rank 0 alone and uses every host core
+    torch.set_num_threads(os.cpu_count() or 1)
     w = _workload(world, args.workload)
     cb = cpu_baseline(w, steps=max(1, min(args.steps, 3)), warmup=min(args.warmup, 1))
     line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tokens/s", "n_gpus": world,
             "steps": max(1, min(args.steps, 3)), "warmup": min(args.warmup, 1), "ms_per_step": cb["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": w["name"], "d_model": w["H"], "experts": w["E"], "d_ff": w["I"], "top_k": w["k"],
-                       "parallelism": "host cores, one process"},
+                       "parallelism": f"host cores, one process, {torch.get_num_threads()} threads"},
             "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_torch_grouped(args):
+    """Same-box library yardstick: the reference's library-GEMM formulation of the expert pipeline written out in
+    plain PyTorch (sort by expert -> torch._grouped_mm -> SiLU-GLU -> torch._grouped_mm -> weighted index_add_,
+    backward by autograd; the formulation of kernels/sm120/moe_grouped.py:93-121), fed by this package's router so
+    that only the expert pipeline differs.  Not part of the product; printed with "impl": "torch_grouped"."""
+    if int(os.environ.get("RANK", 0)) != 0:
+        return
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    pkg = importlib.import_module(PKG)
+    w = _workload(1, args.workload)
+    T, H, E, I, k = w["T"], w["H"], w["E"], w["I"], w["k"]
+    line = {"impl": "torch_grouped", "metric": METRIC, "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True,
+            "dtype": "bf16", "data": "synthetic", "config": {"workload": w["name"], "parallelism": "single GPU",
+                                                             "what": "torch.sort + torch._grouped_mm x2 + index_add_, autograd backward"}}
+    if not hasattr(torch, "_grouped_mm"):
+        line["unavailable"] = "this torch has no torch._grouped_mm"
+        print(json.dumps(line), flush=True)
+        return
+    layer = _make_layer(pkg, w, dev, seed=0, world=1)
+    g = torch.Generator(device=dev).manual_seed(1)
+    x_dev = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+    go_dev = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+    params = [layer.gate.weight, layer.gate_up_proj, layer.down_proj]
+
+    def experts(flat, idx, wt):
+        order = torch.sort(idx.flatten(), stable=True).indices
+        tok = order // k
+        offs = torch.cumsum(torch.bincount(idx.flatten(), minlength=E), 0).to(torch.int32)
+        xs = flat[tok]
+        gu = torch._grouped_mm(xs, layer.gate_up_proj.transpose(-2, -1), offs=offs)
+        inter = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+        eo = torch._grouped_mm(inter, layer.down_proj.transpose(-2, -1), offs=offs)
+        out = torch.zeros(T, H, dtype=torch.float32, device=dev)
+        out.index_add_(0, tok, eo.float() * wt.flatten()[order].unsqueeze(-1))
+        return out.to(flat.dtype)
+
+    def step():
+        for p in params:
+            p.grad = None
+        x = x_dev.detach().requires_grad_(True)
+        idx, wt = pkg.fused_mlp_router(x, layer.gate.weight, layer.bias, k, E)
+        experts(x, idx, wt).backward(go_dev)
+
+    try:
+        for _ in range(max(args.warmup, 3)):
+            step()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+        ms = e0.elapsed_time(e1) / args.steps
+        line.update(value=round(T / (ms * 1e-3), 1), steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=round(ms, 4),
+                    layer_tflops_per_gpu=round(18.0 * H * I * T * k / (ms * 1e-3) / 1e12, 1), clocks=clocks,
+                    peak_memory_gb=round(torch.cuda.max_memory_allocated() / 1e9, 2))
+    except Exception as exc:
+        line["unavailable"] = repr(exc)[:300]
     print(json.dumps(line), flush=True)
 
 
@@ -500,13 +857,17 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch_grouped"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary configurations after the headline")
+    ap.add_argument("--no-parity", action="store_true", help="N > 1: skip the expert-parallel parity check")
     ap.add_argument("--workload", default="headline", choices=["headline", "profile", "ep5", "mxfp8", "mxfp8_profile", "zipf", "muon", "muon_profile"],
                     help="profile = small case for profiler captures (not a benchmark number)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "torch_grouped":
+        run_torch_grouped(args)
     elif args.workload.startswith("muon"):
         run_muon(args)
     else:

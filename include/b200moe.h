@@ -278,6 +278,16 @@ int b200moe_combine_bwd(const void* grad_out, const void* eo, const float* w,
  * THIS rank's block of expert e inside e's owner. */
 int b200moe_ep_plan(const int32_t* counts_all, int W, int rank, int E, int32_t* poffs_l, int32_t* counts_l,
                     int32_t* tile_expert_l, int32_t* src_base, int32_t* dest_base, b200moe_stream_t stream);
+/* Cross-rank barrier of the exchange (no reference counterpart).  flags_peers: HOST array of W device pointers,
+ * entry r = rank r's flag array of W uint32 words (symmetric memory, zero before the first barrier).  The kernel
+ * stores `generation` into word `rank` of every peer's array (release) and waits until all W words of its own
+ * array have reached `generation` (acquire); the caller passes 1, 2, 3, ... on successive barriers, the same
+ * sequence on every rank.  The wait gives up after `limit_cycles` SM clocks (1e3..4e10): `status` then receives 7
+ * and the kernel returns normally -- a peer that never arrives costs a status code, not a hung GPU.  Writes
+ * queued on `stream` before the barrier (peer stores included) are visible to every rank's kernels queued
+ * after it. */
+int b200moe_ep_barrier(const void* const* flags_peers, int W, int rank, uint32_t generation, int64_t limit_cycles,
+                       int32_t* status, b200moe_stream_t stream);
 /* owner side, forward.  For every source rank s and token t the kernel reads slot j of the token from the
  * source's routing tables (idx_peers int64 (T,k), spos_peers = slot_pos int32 (T,k), offs_peers int32 (E+1)) and,
  * for each expert that lives on this rank, writes x_peers[s][t] to row

@@ -210,7 +210,7 @@ def moe_experts(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj):
 
 
 def moe_layer(x, gate_weight, bias, gate_up_proj, down_proj, top_k, norm_topk=True, scale=1.0,
-              logits_dtype=None):
+              logits_dtype=None, idx_override=None):
     """Whole block, differentiable by autograd w.r.t. x, gate_weight and the expert weights:
     router (selection is non-differentiable, weights are) -> experts -> combine.
     logits_dtype: round the logits to this dtype before the sigmoid, as the reference does when it
@@ -222,6 +222,12 @@ def moe_layer(x, gate_weight, bias, gate_up_proj, down_proj, top_k, norm_topk=Tr
         logits = logits + (logits.detach().to(logits_dtype).to(logits.dtype) - logits.detach())
     with torch.no_grad():
         idx, _, counts = router_epilogue_fwd(logits, bias, top_k, norm_topk, scale)
+    if idx_override is not None:
+        # the picks of another implementation of the same router (a logit that sits on a rounding boundary of
+        # logits_dtype can land on either side and flip a pick): everything downstream of the selection is then
+        # compared on identical routing
+        idx = idx_override
+        counts = torch.bincount(idx.flatten(), minlength=gate_weight.shape[0]).to(torch.int32)
     s = 1.0 / (1.0 + torch.exp(-logits.float()))
     w = s.gather(1, idx)
     if norm_topk and top_k > 1:
@@ -232,13 +238,13 @@ def moe_layer(x, gate_weight, bias, gate_up_proj, down_proj, top_k, norm_topk=Tr
 
 
 def layer_fwd_bwd(x, gate_weight, bias, gate_up_proj, down_proj, top_k, grad_out,
-                  norm_topk=True, scale=1.0, logits_dtype=None):
+                  norm_topk=True, scale=1.0, logits_dtype=None, idx_override=None):
     """Forward + backward of the block under loss = sum(out * grad_out); returns a dict of the
     output and every gradient (fp32 when the inputs are fp32)."""
     leaves = [t.detach().clone().requires_grad_(True)
               for t in (x, gate_weight, gate_up_proj, down_proj)]
     xl, gl, gul, dl = leaves
-    out, idx, w, counts = moe_layer(xl, gl, bias, gul, dl, top_k, norm_topk, scale, logits_dtype)
+    out, idx, w, counts = moe_layer(xl, gl, bias, gul, dl, top_k, norm_topk, scale, logits_dtype, idx_override)
     (out.float() * grad_out.float()).sum().backward()
     return dict(out=out.detach(), idx=idx, w=w.detach(), counts=counts, grad_x=xl.grad,
                 grad_gate_weight=gl.grad, grad_gate_up=gul.grad, grad_down=dl.grad)

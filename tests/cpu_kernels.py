@@ -99,7 +99,9 @@ class CpuKernels:
 
     @staticmethod
     def combine_raw(rows, w, slot_table, T, k):
-        r = rows[slot_table.long()].view(T, k, -1)
+        st = slot_table.long()
+        live = (st >= 0).view(T, k, 1).to(rows.dtype)          # a slot without a row (-1) adds nothing
+        r = rows[st.clamp_min(0)].view(T, k, -1) * live
         if w is None:
             return r.sum(1)
         return (r * w.view(T, k, 1).to(rows.dtype)).sum(1)

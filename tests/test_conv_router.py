@@ -47,14 +47,16 @@ def test_fused_conv_router_forward_backward(pkg, B, S, H, E, K, k):
     logits = O.conv_router_logits(xo, wo)
     logits_r = logits + (logits.detach().to(torch.bfloat16).float() - logits.detach())
     idx_o, _, counts_o = O.router_epilogue_fwd(logits_r.detach(), bias, k)
+    idx_dev = idx.view(B * S, k).cpu()
+    # a logit on a bf16 rounding boundary can flip a pick: the flip rate is asserted on its own, the values are
+    # compared on the device's picks at the 2e-2 gate
+    assert (idx_dev != idx_o).any(1).float().mean() < 0.005
     s = torch.sigmoid(logits_r)
-    ww = s.gather(1, idx_o)
+    ww = s.gather(1, idx_dev)
     ww = ww / (ww.sum(-1, keepdim=True) + 1e-20)
     (ww * G.view(B * S, k)).sum().backward()
-    rows = (idx.view(B * S, k).cpu() == idx_o).all(1)
-    assert rows.float().mean() > 0.99          # a logit on a bf16 rounding boundary can flip a pick
-    assert O.rel_l2(wt.view(B * S, k).cpu()[rows], ww.detach()[rows]) < 1e-2
+    assert O.rel_l2(wt.view(B * S, k).cpu(), ww.detach()) < 1e-2
     assert torch.equal(counts.cpu().long(), torch.bincount(idx.flatten().cpu(), minlength=E))
     gx, gxo = xd.grad.float().cpu().view(B * S, H), xo.grad.view(B * S, H)
-    assert O.rel_l2(gx, gxo) < 6e-2            # includes the few flipped tokens
-    assert O.rel_l2(wd.grad.float().cpu(), wo.grad) < 6e-2
+    assert O.rel_l2(gx, gxo) < 2e-2
+    assert O.rel_l2(wd.grad.float().cpu(), wo.grad) < 2e-2

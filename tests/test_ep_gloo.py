@@ -93,3 +93,13 @@ def test_exchange_plan_rejects_indivisible_expert_count():
     ep = importlib.import_module("triton-kernel-fused_b200.ep")
     with pytest.raises(ValueError, match="divisible"):
         ep.exchange_plan(torch.zeros(7, dtype=torch.int32), 2)
+
+
+def test_layer_rejects_chunked_overlap_on_the_peer_memory_transport():
+    """One symmetric workspace per layer, one forward in flight on it: chunk pipelines would share it."""
+    import importlib
+    pkg = importlib.import_module("triton-kernel-fused_b200")
+    with pytest.raises(ValueError, match="overlap_chunks"):
+        pkg.ExpertParallelMoELayer(64, 32, 8, top_k=2, transport="p2p", overlap_chunks=2)
+    with pytest.raises(ValueError, match="exchange"):
+        pkg.ExpertParallelMoELayer(64, 32, 8, top_k=2, transport="p2p", exchange="both")

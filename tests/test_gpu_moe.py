@@ -215,15 +215,21 @@ def test_layer_module_vs_oracle(pkg):
     out = layer(x)
     (out.float() * inp["grad_out"].to(DEV).view_as(out).float()).sum().backward()
     pkg.check_status()
-    r = O.layer_fwd_bwd(inp["x"].float(), inp["gate_weight"].float(), inp["bias"], inp["gate_up"].float(),
-                        inp["down"].float(), k, inp["grad_out"].float(), logits_dtype=torch.bfloat16)
-    # tokens whose routing agrees (a logit on a bf16 rounding boundary can flip a pick): compare those rows
+    # A logit on a bf16 rounding boundary can land on either side and flip a pick.  The flip rate is asserted on
+    # its own; the values are then compared on IDENTICAL routing (the oracle's experts and backward run on the
+    # device's picks), every tensor at the 2e-2 gate.
     idx_d, _, _ = pkg.fused_mlp_router(inp["x"].to(DEV), layer.gate.weight, layer.bias, k, E, return_counts=True)
-    rows = (idx_d.cpu() == r["idx"]).all(1)
-    assert rows.float().mean() > 0.995
-    assert O.rel_l2(out.view(T, H).float().cpu()[rows], r["out"][rows]) < TOL_BF16
-    assert O.rel_l2(x.grad.view(T, H).float().cpu()[rows], r["grad_x"][rows]) < 3e-2
-    assert O.rel_l2(layer.down_proj.grad.float().cpu(), r["grad_down"]) < 6e-2     # includes flipped tokens
+    own = O.layer_fwd_bwd(inp["x"].float(), inp["gate_weight"].float(), inp["bias"], inp["gate_up"].float(),
+                          inp["down"].float(), k, inp["grad_out"].float(), logits_dtype=torch.bfloat16)
+    assert (idx_d.cpu() != own["idx"]).any(1).float().mean() < 0.005
+    r = O.layer_fwd_bwd(inp["x"].float(), inp["gate_weight"].float(), inp["bias"], inp["gate_up"].float(),
+                        inp["down"].float(), k, inp["grad_out"].float(), logits_dtype=torch.bfloat16,
+                        idx_override=idx_d.cpu())
+    assert O.rel_l2(out.view(T, H).float().cpu(), r["out"]) < TOL_BF16
+    assert O.rel_l2(x.grad.view(T, H).float().cpu(), r["grad_x"]) < TOL_BF16
+    assert O.rel_l2(layer.gate_up_proj.grad.float().cpu(), r["grad_gate_up"]) < TOL_BF16
+    assert O.rel_l2(layer.down_proj.grad.float().cpu(), r["grad_down"]) < TOL_BF16
+    assert O.rel_l2(layer.gate.weight.grad.float().cpu(), r["grad_gate_weight"]) < TOL_BF16
     assert torch.equal(layer.last_counts.cpu().long(), torch.bincount(idx_d.flatten().cpu(), minlength=E))
     layer.update_bias(0.001)
     assert (layer.bias != inp["bias"].to(DEV)).any()

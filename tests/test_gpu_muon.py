@@ -165,3 +165,41 @@ def test_same_shape_parameters_step_as_one_stack(pkg):
     for cap in (64 * 1024 * 1024, 2 * 128 * 192, 1):        # one stack of 6; chunks of at most 2 matrices; one by one
         for a, b in zip(alone, run(False, cap)):
             assert torch.equal(a, b)
+
+
+def test_state_dict_round_trip_with_fp32_master_weights(pkg):
+    """`load_state_dict` casts the bf16 momentum buffer to the parameter's dtype (fp32 masters).  The resumed
+    optimizer must bring it back to bf16 instead of letting the kernel reinterpret fp32 memory: a run interrupted
+    by state_dict / load_state_dict ends bit-identically to an uninterrupted one."""
+    g = torch.Generator().manual_seed(23)
+    p0 = torch.randn(3, 128, 192, generator=g) * 0.02
+    grads = [torch.randn(3, 128, 192, generator=g) for _ in range(3)]
+
+    def make():
+        p = torch.nn.Parameter(p0.clone().to(DEV))           # fp32 master weights
+        return p, pkg.FusedMuon([p], lr=0.01, weight_decay=0.1)
+
+    p_a, opt_a = make()
+    for gr in grads:
+        p_a.grad = gr.to(DEV)
+        opt_a.step()
+    p_b, opt_b = make()
+    for gr in grads[:2]:
+        p_b.grad = gr.to(DEV)
+        opt_b.step()
+    saved = opt_b.state_dict()
+    p_c = torch.nn.Parameter(p_b.detach().clone())
+    opt_c = pkg.FusedMuon([p_c], lr=0.01, weight_decay=0.1)
+    opt_c.load_state_dict(saved)
+    assert opt_c.state[p_c]["muon_mom"].dtype == torch.float32      # what torch's loader did to it
+    p_c.grad = grads[2].to(DEV)
+    opt_c.step()
+    torch.cuda.synchronize(); pkg.check_status()
+    assert opt_c.state[p_c]["muon_mom"].dtype == torch.bfloat16
+    assert torch.equal(p_c.detach(), p_a.detach())
+    assert torch.equal(opt_c.state[p_c]["muon_mom"], opt_a.state[p_a]["muon_mom"])
+    # a buffer of the wrong size is refused, not read out of bounds
+    opt_c.state[p_c]["muon_mom"] = torch.zeros(2, 128, 192, dtype=torch.bfloat16, device=DEV)
+    p_c.grad = grads[0].to(DEV)
+    with pytest.raises(ValueError):
+        opt_c.step()

@@ -87,12 +87,13 @@ def test_fused_mlp_router_forward_backward(pkg):
     pkg.check_status()
     # oracle on the same bf16 inputs
     idx_o, w_o, c_o, logits_o = O.mlp_router_fwd(inp["x"], inp["gate_weight"], inp["bias"], k)
-    agree = (idx.view(T, k).cpu() == idx_o).all(1).float().mean().item()
-    assert agree > 0.995            # logits may differ by one bf16 ulp at a rounding boundary
+    idx_dev = idx.view(T, k).cpu()
+    # logits may differ by one bf16 ulp at a rounding boundary and flip a pick: the flip rate is gated on its own,
+    # the gradients are compared on the device's picks
+    assert (idx_dev != idx_o).any(1).float().mean().item() < 0.005
     G = torch.randn(T, k, generator=torch.Generator().manual_seed(1))
     (w.view(T, k) * G.to(DEV)).sum().backward()
-    rows = (idx.view(T, k).cpu() == idx_o).all(1)
-    gx_o, gw_o, _ = O.mlp_router_bwd(inp["x"], inp["gate_weight"], logits_o, idx_o, G)
-    assert O.rel_l2(x.grad.float().cpu()[rows], gx_o.float()[rows]) < 2e-2
-    assert O.rel_l2(W.grad.float().cpu(), gw_o.float()) < 3e-2
+    gx_o, gw_o, _ = O.mlp_router_bwd(inp["x"], inp["gate_weight"], logits_o, idx_dev, G)
+    assert O.rel_l2(x.grad.float().cpu(), gx_o.float()) < 2e-2
+    assert O.rel_l2(W.grad.float().cpu(), gw_o.float()) < 2e-2
     pkg.check_status()

@@ -88,3 +88,37 @@ def test_muon_accepts_the_reference_argument_list():
     p.grad = torch.zeros_like(p)
     with pytest.raises(ValueError):
         opt.step()
+
+
+def test_muon_momentum_buffer_is_checked_before_the_kernel_sees_it():
+    """A momentum buffer that `load_state_dict` cast to fp32 comes back as bf16 with the same values; a buffer of
+    another size is refused (the kernel would otherwise read and write out of bounds)."""
+    import pytest
+    pkg = importlib.import_module(PKG)
+    check = pkg.muon._checked_momentum
+    cpu = torch.device("cpu")
+    m = (torch.randn(2, 8, 16) * 0.1).to(torch.bfloat16)
+    assert check(m, 2, 8, 16, cpu) is m                       # already right: passed through untouched
+    back = check(m.float(), 2, 8, 16, cpu)
+    assert back.dtype == torch.bfloat16 and torch.equal(back, m)
+    flat = check(m.float().view(-1), 2, 8, 16, cpu)
+    assert flat.shape == (2, 8, 16) and torch.equal(flat, m)
+    for bad in (torch.zeros(1, 8, 16), torch.zeros(2, 8, 8), None):
+        with pytest.raises(ValueError):
+            check(bad, 2, 8, 16, cpu)
+
+
+def test_status_codes_become_runtime_errors():
+    """What a kernel leaves in the status word reaches the caller as a RuntimeError naming the cause; 7 is the
+    cross-rank barrier that gave up waiting for a peer."""
+    import pytest
+    L = importlib.import_module(PKG + "._lib")
+    L.raise_for_status(0)
+    with pytest.raises(RuntimeError, match="peer rank did not arrive"):
+        L.raise_for_status(7)
+    with pytest.raises(RuntimeError, match="expert index"):
+        L.raise_for_status(5)
+    # argument errors of the barrier never reach the GPU
+    lib = L.lib()
+    assert lib.b200moe_ep_barrier(None, 2, 0, 1, 10**6, None, None) < 0
+    assert b"status" in lib.b200moe_last_error_string()

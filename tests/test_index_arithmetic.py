@@ -63,3 +63,18 @@ def test_swizzled_transpose_tile():
     for r in range(64):
         for j in range(8):
             assert len({((c8 + j) * 32 + ((r >> 1) ^ (((c8 + j) >> 3) << 2))) % 32 for c8 in range(0, 64, 8)}) == 8
+
+
+def test_slots_without_a_row_are_skipped_by_the_combine_model():
+    """An expert index outside [0, E) leaves its slot without a row: the rank pass writes -1 into slot_row /
+    slot_pos and every consumer skips such entries (csrc/permute.cu, csrc/combine.cu, csrc/ep.cu).  The CPU model
+    of the combine follows the same rule."""
+    import torch
+    from tests.cpu_kernels import CpuKernels
+    rows = torch.arange(12, dtype=torch.float32).view(6, 2)
+    table = torch.tensor([0, -1, 5, 2], dtype=torch.int32)          # T = 2, k = 2; token 0's second slot has no row
+    w = torch.tensor([[0.5, 100.0], [1.0, 2.0]])
+    out = CpuKernels.combine_raw(rows, w, table, 2, 2)
+    assert torch.equal(out[0], 0.5 * rows[0])
+    assert torch.equal(out[1], rows[5] + 2.0 * rows[2])
+    assert torch.equal(CpuKernels.combine_raw(rows, None, table, 2, 2)[0], rows[0])

@@ -5,7 +5,9 @@ that owns all free device memory, a latency-bound serving loop), so this entry p
 histogram scratch in a fixed 1 MiB array inside the library.  The test calls it through the C ABI
 twice in a row on different routings (the array keeps the previous call's contents) and checks every
 output table bit for bit against b200moe_permute_build, which takes a caller-allocated workspace.
-This file is collected last on purpose, and it passes on its own in a fresh process as well.
+The file name sorts last so that pytest collects it after every other test: a run that stops at the
+first failure (-x) has then already exercised the whole main path before this side entry point can end
+it.  Nothing here depends on the other tests; it passes on its own in a fresh process as well.
 """
 import importlib
 

@@ -70,6 +70,7 @@ _SIGNATURES = {
     "b200moe_mxfp8_gather_quant": (c_int, [c_void_p] * 3 + [c_int, c_int64, c_int64] + [c_void_p] * 4),
     "b200moe_mxfp8_expert_wgrad": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
     "b200moe_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 5 + [c_void_p]),
+    "b200moe_ep_barrier": (c_int, [c_void_p, c_int, c_int, ctypes.c_uint32, c_int64, c_void_p, c_void_p]),
     "b200moe_ep_gather_pull": (c_int, [c_void_p] * 7 + [c_int, c_int, c_int, c_int64, c_int, c_int64] + [c_void_p] * 4),
     "b200moe_slot_dots": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_void_p, c_void_p]),
     "b200moe_expert_linear_push": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64] +
@@ -171,6 +172,13 @@ def check_status(device=None) -> None:
     v = int(w.item())
     if v != 0:
         w.zero_()
+    raise_for_status(v)
+
+
+def raise_for_status(v: int) -> None:
+    """RuntimeError for a non-zero value read from a status word (a bounded wait that ran out: a stalled GEMM
+    pipeline, a peer rank missing at a barrier; an expert index out of range), with the library's text for it."""
+    if v != 0:
         raise RuntimeError(f"b200moe kernel status {v}: {lib().b200moe_status_string(v).decode()}")
 
 

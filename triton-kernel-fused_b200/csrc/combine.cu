@@ -31,6 +31,7 @@ combine_kernel(const uint4* __restrict__ rows, const float* __restrict__ w, cons
     for (int c = threadIdx.x; c < vec_per_row; c += blockDim.x) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       for (int j = 0; j < k; ++j) {
+        if (s_row[j] < 0) continue;   // a slot without a row (its expert index was out of range) adds nothing
         const uint4 v = rows[static_cast<long long>(s_row[j]) * vec_per_row + c];
         fma8(acc, v, s_w[j]);
       }

@@ -89,10 +89,14 @@ __device__ __forceinline__ unsigned local_rows_of_token(const long long* __restr
   bool local = false;
   row = 0;
   if (lane < k) {
-    const int e = static_cast<int>(idx_s[t * k + lane]);
-    if (e / El == rank) {
-      local = true;
-      row = src_base[s * El + (e - rank * El)] + spos_s[t * k + lane] - offs_s[e];
+    const long long ev = idx_s[t * k + lane];
+    if (ev >= 0 && ev / El == rank) {   // an index below 0 or past the last expert belongs to no rank
+      const int e = static_cast<int>(ev);
+      const int sp = spos_s[t * k + lane];
+      if (sp >= 0) {                    // -1: the source's permutation gave the slot no row
+        local = true;
+        row = src_base[s * El + (e - rank * El)] + sp - offs_s[e];
+      }
     }
   }
   return __ballot_sync(0xffffffffu, local);
@@ -180,7 +184,7 @@ constexpr int kPullThreads = 32 + kPullConsumers;
 __global__ void __launch_bounds__(kPullThreads, 1)
 ep_combine_pull_kernel(const __grid_constant__ PeerPtrs rows_peers, const float* __restrict__ w,
                        const long long* __restrict__ idx, const int* __restrict__ slot_pos,
-                       const int* __restrict__ offs, const int* __restrict__ dest_base, int El, long long T, int k,
+                       const int* __restrict__ offs, const int* __restrict__ dest_base, int El, int E, long long T, int k,
                        long long row_bytes, int nslots, uint8_t* __restrict__ out, int* __restrict__ status) {
   extern __shared__ uint8_t pull_smem_raw[];
   uint8_t* data = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pull_smem_raw) + 127) & ~static_cast<uintptr_t>(127));
@@ -217,12 +221,20 @@ ep_combine_pull_kernel(const __grid_constant__ PeerPtrs rows_peers, const float*
         const long long t = item / nchunk;
         const int ch = static_cast<int>(item - t * nchunk);
         const long long s = t * k + j;
-        const int e = static_cast<int>(idx[s]);
-        const long long row = dest_base[e] + slot_pos[s] - offs[e];
+        const long long ev = idx[s];
+        const int e = static_cast<int>(ev);
         const long long off = static_cast<long long>(ch) * kPullChunk;
         bytes = static_cast<uint32_t>(row_bytes - off < kPullChunk ? row_bytes - off : kPullChunk);
-        src = reinterpret_cast<const uint8_t*>(rows_peers.p[e / El]) + row * row_bytes + off;
-        wj = (w != nullptr) ? w[s] : 1.0f;
+        if (ev >= 0 && ev < E && slot_pos[s] >= 0) {
+          const long long row = dest_base[e] + slot_pos[s] - offs[e];
+          src = reinterpret_cast<const uint8_t*>(rows_peers.p[e / El]) + row * row_bytes + off;
+          wj = (w != nullptr) ? w[s] : 1.0f;
+        } else {
+          // expert index out of range (the permutation raised the status word): the copy still has to deliver its
+          // bytes to the barrier, so it reads row 0 of the first buffer; weight 0 makes the consumers skip the piece
+          src = reinterpret_cast<const uint8_t*>(rows_peers.p[0]) + off;
+          wj = 0.0f;
+        }
       }
     };
     const long long stride = static_cast<long long>(per) * gridDim.x;
@@ -282,8 +294,10 @@ ep_combine_pull_kernel(const __grid_constant__ PeerPtrs rows_peers, const float*
         if (tid < nvec) {
           float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
           const uint8_t* base = data + static_cast<size_t>(slot) * k * kPullChunk + tid * 16;
-          for (int jj = 0; jj < k; ++jj)
-            fma8(acc, *reinterpret_cast<const uint4*>(base + static_cast<size_t>(jj) * kPullChunk), sw[slot * 32 + jj]);
+          for (int jj = 0; jj < k; ++jj) {
+            const float wjj = sw[slot * 32 + jj];
+            if (wjj != 0.0f) fma8(acc, *reinterpret_cast<const uint4*>(base + static_cast<size_t>(jj) * kPullChunk), wjj);
+          }
           uint4 o;
           o.x = pack_bf16x2(acc[0], acc[1]);
           o.y = pack_bf16x2(acc[2], acc[3]);
@@ -308,11 +322,14 @@ ep_combine_pull_kernel(const __grid_constant__ PeerPtrs rows_peers, const float*
 __global__ void __launch_bounds__(256)
 ep_pull_row_scalars_kernel(const __grid_constant__ PeerPtrs gw_peers, const long long* __restrict__ idx,
                            const int* __restrict__ slot_pos, const int* __restrict__ offs,
-                           const int* __restrict__ dest_base, int El, long long slots, float* __restrict__ grad_w) {
+                           const int* __restrict__ dest_base, int El, int E, long long slots, float* __restrict__ grad_w) {
   for (long long s = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; s < slots;
        s += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int e = static_cast<int>(idx[s]);
-    grad_w[s] = reinterpret_cast<const float*>(gw_peers.p[e / El])[dest_base[e] + slot_pos[s] - offs[e]];
+    const long long ev = idx[s];
+    const int e = static_cast<int>(ev);
+    grad_w[s] = (ev >= 0 && ev < E && slot_pos[s] >= 0)
+                    ? reinterpret_cast<const float*>(gw_peers.p[e / El])[dest_base[e] + slot_pos[s] - offs[e]]
+                    : 0.0f;   // a slot whose expert index is out of range owns no row
   }
 }
 
@@ -435,6 +452,35 @@ slot_dots_kernel(const uint4* __restrict__ go, const uint4* __restrict__ rows, l
   }
 }
 
+// Cross-rank barrier on a symmetric flag array (W unsigned words per rank, zero before the first use).
+// Thread p of the one CTA announces this rank at peer p: a release store of `generation` into word `rank` of
+// p's array (a plain peer store over NVLink); then it waits, with an acquire load of its OWN array's word p,
+// until peer p's announcement of the same (or a later) generation shows up.  Every rank writes only its own
+// word of every array, so no atomics are needed and generations only grow.  The wait is bounded by
+// `limit_cycles` SM clocks: when it runs out the kernel raises ST_WAIT_PEER in `status` and returns normally,
+// so a missing peer ends in a status code and a usable context, never in a hung GPU or a trap.
+// Stream order makes the writes of earlier kernels of this stream (peer stores included) complete before the
+// release store; the acquire load orders the kernels queued after the barrier behind the peers' writes.
+__global__ void __launch_bounds__(kMaxRanks)
+ep_barrier_kernel(const __grid_constant__ PeerPtrs flags_peers, int W, int rank, unsigned generation,
+                  long long limit_cycles, int* __restrict__ status) {
+  const int p = threadIdx.x;
+  if (p >= W) return;
+  unsigned* theirs = reinterpret_cast<unsigned*>(const_cast<void*>(flags_peers.p[p])) + rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(generation) : "memory");
+  const unsigned* mine = reinterpret_cast<const unsigned*>(flags_peers.p[rank]) + p;
+  const long long t0 = clock64();
+  for (unsigned it = 0;; ++it) {
+    unsigned seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+    if (static_cast<int>(seen - generation) >= 0) return;       // wrap-safe "seen >= generation"
+    if ((it & 0x3f) == 0x3f && clock64() - t0 > limit_cycles) {
+      atomicCAS(status, 0, ST_WAIT_PEER);
+      return;
+    }
+  }
+}
+
 static int load_peers(PeerPtrs* out, const void* const* host_ptrs, int W, const char* who) {
   B200_CHECK_ARG(host_ptrs != nullptr, B200MOE_E_NULL, "%s: null peer pointer table", who);
   for (int i = 0; i < kMaxRanks; ++i) out->p[i] = nullptr;
@@ -521,7 +567,7 @@ int b200moe_ep_combine_pull(const void* const* rows_peers, const float* w, const
   if (gw_peers != nullptr) {
     LOAD_PEERS(gp, gw_peers, "ep_combine_pull(grad_w rows)");
     ep_pull_row_scalars_kernel<<<grid_rows((T * k + 255) / 256, 8), 256, 0, (cudaStream_t)stream>>>(
-        gp, reinterpret_cast<const long long*>(idx), slot_pos, offs, dest_base, E / W, T * k, grad_w);
+        gp, reinterpret_cast<const long long*>(idx), slot_pos, offs, dest_base, E / W, E, T * k, grad_w);
     B200_CUDA(cudaGetLastError());
   }
   // ring slots: as many (k pieces of 4 KB + 32 weights + 2 barriers) as fit in 227 KB, at most 16
@@ -541,7 +587,7 @@ int b200moe_ep_combine_pull(const void* const* rows_peers, const float* w, const
   long long grid = exchange_sm_budget();
   if (grid > items) grid = items;
   ep_combine_pull_kernel<<<static_cast<int>(grid), kPullThreads, smem, (cudaStream_t)stream>>>(
-      rp, w, reinterpret_cast<const long long*>(idx), slot_pos, offs, dest_base, E / W, T, k, row_bytes, nslots,
+      rp, w, reinterpret_cast<const long long*>(idx), slot_pos, offs, dest_base, E / W, E, T, k, row_bytes, nslots,
       reinterpret_cast<uint8_t*>(out), status);
   B200_CUDA(cudaGetLastError());
   return 0;
@@ -566,6 +612,25 @@ int b200moe_ep_combine_bwd_pull(const void* const* go_peers, const void* const* 
   ep_combine_bwd_pull_kernel<<<grid_rows((T * W + 7) / 8, 8), 256, 0, (cudaStream_t)stream>>>(
       gp, wp, ip, sp, fp, reinterpret_cast<const uint4*>(eo), counts_l, poffs_l, src_base, W, rank, E / W, T, k,
       static_cast<int>(H / 8), reinterpret_cast<uint4*>(grad_eo), gw_rows);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_ep_barrier(const void* const* flags_peers, int W, int rank, uint32_t generation, int64_t limit_cycles,
+                       int32_t* status, b200moe_stream_t stream) {
+  B200_CHECK_ARG(status != nullptr, B200MOE_E_NULL, "ep_barrier: null status word");
+  CHECK_WORLD("ep_barrier");
+  B200_CHECK_ARG(limit_cycles >= 1000 && limit_cycles <= 40000000000LL, B200MOE_E_BAD_SHAPE,
+                 "ep_barrier: limit_cycles = %lld outside [1e3, 4e10]", (long long)limit_cycles);
+  B200_CHECK_ARG(flags_peers != nullptr, B200MOE_E_NULL, "ep_barrier: null peer pointer table");
+  PeerPtrs fp;
+  for (int i = 0; i < kMaxRanks; ++i) fp.p[i] = nullptr;
+  for (int i = 0; i < W; ++i) {
+    B200_CHECK_ARG(flags_peers[i] != nullptr && (reinterpret_cast<uintptr_t>(flags_peers[i]) & 3) == 0, B200MOE_E_ALIGN,
+                   "ep_barrier: flag array %d is null or not 4-byte aligned", i);
+    fp.p[i] = flags_peers[i];
+  }
+  ep_barrier_kernel<<<1, kMaxRanks, 0, (cudaStream_t)stream>>>(fp, W, rank, generation, limit_cycles, status);
   B200_CUDA(cudaGetLastError());
   return 0;
 }

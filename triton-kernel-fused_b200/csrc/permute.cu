@@ -129,6 +129,11 @@ permute_rank_kernel(const long long* __restrict__ idx, long long M, int E, const
       row_slot[prow] = static_cast<int>(s);
       if (order != nullptr) order[offs[e] + rank] = static_cast<int>(s);
       if (slot_pos != nullptr) slot_pos[s] = offs[e] + rank;
+    } else if (s < M) {
+      // an expert index outside [0, E) (the hist pass raised the status word): the slot owns no row.  -1 makes the
+      // consumers of these tables skip it instead of following whatever the buffer held.
+      slot_row[s] = -1;
+      if (slot_pos != nullptr) slot_pos[s] = -1;
     }
   }
 }

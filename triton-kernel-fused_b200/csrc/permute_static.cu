@@ -20,7 +20,9 @@ static __device__ __align__(256) unsigned char g_permute_scratch[kStaticScratchB
 constexpr int kMaxDevices = 64;
 
 // The array's name is only a host-side handle for the symbol: the address kernels can use has to be
-// asked for, once per device and with that device current.
+// asked for, once per device and with that device current.  The address is cached per device ordinal for
+// the life of the process; a cudaDeviceReset() destroys the context the address belongs to, so a process
+// that resets a device must not call this entry point on it afterwards.
 static int static_scratch(void** out) {
   static std::mutex mu;
   static void* ptrs[kMaxDevices] = {nullptr};
@@ -45,8 +47,10 @@ extern "C" int b200moe_permute_build_static(const int64_t* idx, int64_t T, int k
                                             int32_t* offs, int32_t* poffs, int32_t* slot_row, int32_t* row_slot,
                                             int32_t* tile_expert, int32_t* order, int32_t* slot_pos,
                                             int32_t* status, b200moe_stream_t stream) {
-  B200_CHECK_ARG(T >= 0 && k >= 1 && E >= 1, B200MOE_E_BAD_SHAPE, "permute_build_static: T = %lld, k = %d, E = %d",
-                 (long long)T, k, E);
+  // the ranges are checked before T * k is formed, so the product below cannot overflow
+  B200_CHECK_ARG(T >= 0 && T < (1LL << 31) && k >= 1 && k <= B200MOE_MAX_TOPK && E >= 1 && E <= B200MOE_MAX_EXPERTS,
+                 B200MOE_E_BAD_SHAPE, "permute_build_static: T = %lld, k = %d (1..%d), E = %d (1..%d)", (long long)T, k,
+                 B200MOE_MAX_TOPK, E, B200MOE_MAX_EXPERTS);
   const size_t need = b200moe_permute_ws_bytes(T * k, E);
   B200_CHECK_ARG(need <= kStaticScratchBytes, B200MOE_E_WS_TOO_SMALL,
                  "permute_build_static: T*k = %lld slots over E = %d experts need %zu bytes of scratch, the built-in "

@@ -133,6 +133,14 @@ class ExpertParallelMoELayer(nn.Module):
         super().__init__()
         if transport not in ("nccl", "p2p"):
             raise ValueError("transport must be 'nccl' (all_to_all_single) or 'p2p' (peer-memory kernels)")
+        if exchange not in ("push", "pull"):
+            raise ValueError("exchange must be 'push' or 'pull'")
+        if transport == "p2p" and int(overlap_chunks) > 1:
+            # the peer-memory transport keeps ONE symmetric workspace per layer (inputs, routing tables and receive
+            # buffers that peers read and write) and allows one forward in flight on it; chunk pipelines on their own
+            # streams would overwrite each other's buffers while peers still use them
+            raise ValueError("overlap_chunks > 1 needs transport='nccl': the p2p transport has one workspace per "
+                             "layer and one forward in flight")
         self.transport = transport
         self.exchange = exchange
         self._workspace = None

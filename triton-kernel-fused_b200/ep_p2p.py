@@ -10,10 +10,13 @@ slot of the home rank's receive buffer, tile by tile while the GEMM runs, and th
 `exchange="pull"` keeps the rows on the owner and lets the home ranks pull them while combining.
 
 Per step and direction there is one tiny NCCL all-gather (the (W,E) count matrix, which also orders
-the phases), one host read of that matrix (to size the local buffers) and two device-side barriers.
+the phases), one host read of that matrix (to size the local buffers) and two device-side barriers
+(`b200moe_ep_barrier`: flag words in the symmetric buffer, plain peer stores and bounded local waits).
 Constraint: one forward/backward in flight per workspace, because the symmetric buffers are reused.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 import torch.distributed as dist
@@ -53,9 +56,19 @@ def _slot_dots(*a):
     L.check(L.lib().b200moe_slot_dots(*a))
 
 
-@ops._op("ep_barrier", 0)
+# SM clocks a rank waits for its peers at a barrier before it gives up with status 7 (about 10 s; ranks reach a
+# barrier within microseconds of each other once a step is under way, the margin is for a peer delayed on its host)
+BARRIER_LIMIT_CYCLES = int(float(os.environ.get("B200MOE_EP_BARRIER_LIMIT_S", "10")) * 1.9e9)
+
+
+@ops._op("ep_barrier", 1)
 def _barrier(ws):
-    ws.handle.barrier(0)
+    """Bounded cross-rank barrier on the workspace's flag words (csrc/ep.cu ep_barrier_kernel): a peer that never
+    arrives raises the status word (read by `check_status`) instead of hanging the GPU."""
+    ws.barrier_generation += 1
+    L.check(L.lib().b200moe_ep_barrier(ws.peers["flags"], ws.W, ws.rank, ws.barrier_generation & 0xFFFFFFFF,
+                                       BARRIER_LIMIT_CYCLES, L.ptr(L.status_word(ws.buf.device)),
+                                       torch.cuda.current_stream(ws.buf.device).cuda_stream))
 
 
 def _align(n, a=256):
@@ -81,7 +94,7 @@ class SymmetricWorkspace:
         self.T, self.H, self.k, self.E = T, H, k, E
         M = T * k
         self.cap_w = L.padded_rows_cap(self.W * M, E // self.W)
-        fields = [("x", T * H * 2), ("go", T * H * 2), ("w", M * 4), ("idx", M * 8), ("spos", M * 4), ("offs", (E + 1) * 4)]
+        fields = [("flags", 16 * 4), ("x", T * H * 2), ("go", T * H * 2), ("w", M * 4), ("idx", M * 8), ("spos", M * 4), ("offs", (E + 1) * 4)]
         if exchange == "pull":     # owners keep their result rows; sized for every routed row landing on one rank
             fields += [("eo", self.cap_w * H * 2), ("gxs", self.cap_w * H * 2), ("gw", self.cap_w * 4)]
         else:                      # home ranks receive the result rows of their own slots
@@ -113,6 +126,13 @@ class SymmetricWorkspace:
             self.recvg_base = torch.tensor([b + self.offsets["recvg"] for b in base], dtype=torch.int64, device=device)
             self.ident = torch.arange(M, dtype=torch.int32, device=device)   # slot -> row of the receive buffers
         self.generation = 0
+        # barrier flags: one word per peer, zero before the first barrier on every rank (the rendezvous below is the
+        # one library barrier of the workspace's life: nobody announces itself into an array that is still being zeroed)
+        self.flags = v("flags", 16, torch.int32)
+        self.flags.zero_()
+        self.barrier_generation = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
 
     def barrier(self):
         _barrier(self)

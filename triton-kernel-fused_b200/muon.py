@@ -130,6 +130,19 @@ def _iterate(X, E, Rp, wide, coeffs):
     return X
 
 
+def _checked_momentum(mom, E, r, c, dev):
+    """The momentum kernel reads and writes the buffer as E*r*c contiguous bf16 values on the parameter's device.
+    `Optimizer.load_state_dict` casts floating-point state to the parameter's dtype (fp32 master weights turn a
+    restored buffer into fp32) and may leave it on another device: such a buffer is brought back to bf16 (exact: it
+    held bf16 values before the cast); a buffer of another size is refused rather than read out of bounds."""
+    if not torch.is_tensor(mom) or mom.numel() != E * r * c:
+        raise ValueError(f"optimizer state 'muon_mom' has {tuple(getattr(mom, 'shape', ()))}, the parameter needs "
+                         f"({E}, {r}, {c})")
+    if mom.dtype != torch.bfloat16 or mom.device != dev or not mom.is_contiguous() or mom.dim() != 3:
+        mom = mom.to(device=dev, dtype=torch.bfloat16).contiguous().view(E, r, c)
+    return mom
+
+
 def newton_schulz(G: torch.Tensor, coeffs=DSV4_COEFFS, ns_dtype=torch.bfloat16, eps: float = 1e-7) -> torch.Tensor:
     """Orthogonalise every matrix of G ((r,c) or (E,r,c), CUDA, bf16 or fp32); same call as the reference's
     `newton_schulz` (kernels/sm75/muon.py:62).  Returns G's dtype and shape."""
@@ -219,6 +232,7 @@ class FusedMuon(torch.optim.Optimizer):
             st = self.state[p]
             if "muon_mom" not in st:
                 st["muon_mom"] = torch.zeros(E, r, c, dtype=torch.bfloat16, device=dev)
+            st["muon_mom"] = _checked_momentum(st["muon_mom"], E, r, c, dev)
             _momentum(g.contiguous(), st["muon_mom"], mu, nesterov, out=u[off:off + E])
             spans.append((p, off, E))
             off += E
