@@ -509,21 +509,23 @@ def ep_parity(cx):
 
 
 def _nvlink_bytes(index):
-    """Cumulative NVLink payload counters of one GPU (NVML field values, a read-only query): (tx, rx) bytes or None."""
+    """Cumulative NVLink payload counters of one GPU (NVML field values, a read-only query): (tx, rx) bytes, or the
+    reason why the counters cannot be read."""
     try:
         import pynvml
         pynvml.nvmlInit()
         h = pynvml.nvmlDeviceGetHandleByIndex(index)
-        ids = [pynvml.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_TX, pynvml.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_RX]
+        # scope 0xFFFFFFFF = the sum over all links of the GPU
+        ids = [(pynvml.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_TX, 0xFFFFFFFF), (pynvml.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_RX, 0xFFFFFFFF)]
         vals = pynvml.nvmlDeviceGetFieldValues(h, ids)
         out = []
         for v in vals:
             if v.nvmlReturn != 0:
-                return None
+                return f"NVML field {v.fieldId} (NVLink data throughput) returned code {v.nvmlReturn} (3 = not supported on this GPU / driver)"
             out.append(int(v.value.ullVal) * 1024)     # the counters are in KiB
         return tuple(out)
-    except Exception:
-        return None
+    except Exception as exc:
+        return f"NVML query failed: {repr(exc)[:120]}"
 
 
 def run_ours(args):
@@ -612,16 +614,21 @@ def run_ours(args):
         line["secondary"] = secondary
     if parity is not None:
         line["ep_parity"] = parity
-    if nv0 is not None and nv1 is not None:
-        steps_all = n_warm + args.steps + min(2, n_warm) + args.steps          # resident + host-buffer steps
-        sent = (nv1[0] - nv0[0]) / steps_all
-        # what the design sends: a token row leaves once per remote owner GPU (dispatch, twice: x and grad_out),
-        # a result row once per remote routed row (forward and backward)
-        line["nvlink"] = {"tx_bytes_per_step_counted": round(sent), "rx_bytes_per_step_counted": round((nv1[1] - nv0[1]) / steps_all),
-                          "source": "NVML NVLINK_THROUGHPUT_DATA_TX/RX of GPU 0 before and after the timed regions "
-                                    f"(a query), divided by the {steps_all} layer steps between the two reads "
-                                    "(copy-only steps move nothing over NVLink)",
-                          "result_rows_bytes_per_step_algorithmic": round(2.0 * M * H * 2 * (world - 1) / world)}
+    if world > 1:
+        # what the push exchange sends per step and GPU: a result row leaves once per routed row whose token lives on
+        # another GPU, forward (down projection) and backward (gate/up dgrad)
+        nvl = {"result_rows_bytes_per_step_algorithmic": round(2.0 * M * H * 2 * (world - 1) / world)}
+        if isinstance(nv0, tuple) and isinstance(nv1, tuple):
+            steps_all = n_warm + args.steps + min(2, n_warm) + args.steps          # resident + host-buffer steps
+            nvl.update(tx_bytes_per_step_counted=round((nv1[0] - nv0[0]) / steps_all),
+                       rx_bytes_per_step_counted=round((nv1[1] - nv0[1]) / steps_all),
+                       source="NVML NVLINK_THROUGHPUT_DATA_TX/RX of GPU 0 before and after the timed regions (a query), "
+                              f"divided by the {steps_all} layer steps between the two reads (copy-only steps move "
+                              "nothing over NVLink)")
+        else:
+            nvl["counted"] = None
+            nvl["counters_unavailable"] = nv0 if isinstance(nv0, str) else nv1
+        line["nvlink"] = nvl
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(w, steps=1, warmup=0)
     print(json.dumps(line), flush=True)

@@ -278,6 +278,13 @@ int b200moe_combine_bwd(const void* grad_out, const void* eo, const float* w,
  * THIS rank's block of expert e inside e's owner. */
 int b200moe_ep_plan(const int32_t* counts_all, int W, int rank, int E, int32_t* poffs_l, int32_t* counts_l,
                     int32_t* tile_expert_l, int32_t* src_base, int32_t* dest_base, b200moe_stream_t stream);
+/* ep_local_rows: the number of routed rows that arrive on this rank (sum over the sources of counts_all (W,E) for
+ * the local experts), written to `host_word`, a word of PINNED HOST memory (cudaHostAlloc / cudaHostRegister; the
+ * call fails with B200MOE_E_CUDA and launches nothing otherwise).  The host sizes its buffers from it after waiting
+ * for an event recorded behind this call; no device-to-host copy is involved, so the read does not queue behind
+ * transfers that occupy the copy engines.  No reference counterpart. */
+int b200moe_ep_local_rows(const int32_t* counts_all, int W, int rank, int E, int32_t* host_word,
+                          b200moe_stream_t stream);
 /* Cross-rank barrier of the exchange (no reference counterpart).  flags_peers: HOST array of W device pointers,
  * entry r = rank r's flag array of W uint32 words (symmetric memory, zero before the first barrier).  The kernel
  * stores `generation` into word `rank` of every peer's array (release) and waits until all W words of its own

@@ -122,3 +122,25 @@ def test_status_codes_become_runtime_errors():
     lib = L.lib()
     assert lib.b200moe_ep_barrier(None, 2, 0, 1, 10**6, None, None) < 0
     assert b"status" in lib.b200moe_last_error_string()
+
+
+def test_bf16_copies_of_frozen_stacks_are_reused_until_the_stack_changes():
+    """fp32 / fp16 callers: the bf16 copy of an expert stack that needs no gradient is made once and reused until the
+    stack is updated in place or freed; stacks that need a gradient are cast afresh (autograd needs the cast)."""
+    moe_mod = importlib.import_module(PKG + ".moe")
+    w = torch.randn(2, 8, 4)
+    a = moe_mod._bf16_copy(w)
+    assert a.dtype == torch.bfloat16 and moe_mod._bf16_copy(w) is a
+    w.mul_(2.0)                                           # an optimizer step moves the version counter
+    b = moe_mod._bf16_copy(w)
+    assert b is not a and torch.equal(b, w.to(torch.bfloat16))
+    p = torch.nn.Parameter(torch.randn(2, 8, 4))
+    c = moe_mod._bf16_copy(p)
+    assert c.requires_grad and moe_mod._bf16_copy(p) is not c
+    with torch.no_grad():
+        assert moe_mod._bf16_copy(p) is moe_mod._bf16_copy(p)
+    n = len(moe_mod._BF16_COPIES)
+    del w, a, b
+    import gc
+    gc.collect()
+    assert len(moe_mod._BF16_COPIES) == n - 1             # freed with its tensor

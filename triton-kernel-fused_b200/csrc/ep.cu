@@ -77,6 +77,28 @@ ep_plan_kernel(const int* __restrict__ counts_all, int W, int rank, int E, int* 
   }
 }
 
+// Rows that arrive on this rank (the sum of every source's counts for the local experts), stored straight into a
+// word of pinned host memory: the host learns how large its buffers must be by waiting for this kernel, without a
+// device-to-host copy that would queue behind whatever transfer the copy engines are busy with.
+__global__ void __launch_bounds__(B200MOE_MAX_EXPERTS)
+ep_local_rows_kernel(const int* __restrict__ counts_all, int W, int rank, int E, volatile int* __restrict__ host_word) {
+  __shared__ int s_sum[B200MOE_MAX_EXPERTS / 32];
+  const int El = E / W;
+  int v = 0;
+  if (static_cast<int>(threadIdx.x) < El)
+    for (int s = 0; s < W; ++s) v += counts_all[s * E + rank * El + threadIdx.x];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  if ((threadIdx.x & 31) == 0) s_sum[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tot = 0;
+    for (int i = 0; i < B200MOE_MAX_EXPERTS / 32; ++i) tot += s_sum[i];
+    *host_word = tot;
+    __threadfence_system();
+  }
+}
+
 // The rows of this rank that a (source rank, token) pair feeds: lane j < k looks at slot j of the token in
 // the source's routing tables (peer reads) and, when that expert lives here, computes the padded row
 //   src_base[source][local expert] + (position of the slot inside its expert segment at the source).
@@ -518,6 +540,20 @@ int b200moe_ep_plan(const int32_t* counts_all, int W, int rank, int E, int32_t* 
                  "ep_plan: E = %d must be a multiple of W = %d and at most %d", E, W, B200MOE_MAX_EXPERTS);
   ep_plan_kernel<<<1, B200MOE_MAX_EXPERTS, 0, (cudaStream_t)stream>>>(counts_all, W, rank, E, poffs_l, counts_l,
                                                                        tile_expert_l, src_base, dest_base);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_ep_local_rows(const int32_t* counts_all, int W, int rank, int E, int32_t* host_word,
+                          b200moe_stream_t stream) {
+  B200_CHECK_ARG(counts_all && host_word, B200MOE_E_NULL, "ep_local_rows: null pointer");
+  CHECK_WORLD("ep_local_rows");
+  B200_CHECK_ARG(E >= W && E <= B200MOE_MAX_EXPERTS && E % W == 0, B200MOE_E_BAD_SHAPE,
+                 "ep_local_rows: E = %d must be a multiple of W = %d and at most %d", E, W, B200MOE_MAX_EXPERTS);
+  void* dev_view = nullptr;   // the device's address of the pinned host word; fails (nothing launched) if it is not pinned
+  B200_CUDA(cudaHostGetDevicePointer(&dev_view, host_word, 0));
+  ep_local_rows_kernel<<<1, B200MOE_MAX_EXPERTS, 0, (cudaStream_t)stream>>>(counts_all, W, rank, E,
+                                                                             reinterpret_cast<volatile int*>(dev_view));
   B200_CUDA(cudaGetLastError());
   return 0;
 }

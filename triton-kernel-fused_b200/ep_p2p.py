@@ -126,6 +126,8 @@ class SymmetricWorkspace:
             self.recvg_base = torch.tensor([b + self.offsets["recvg"] for b in base], dtype=torch.int64, device=device)
             self.ident = torch.arange(M, dtype=torch.int32, device=device)   # slot -> row of the receive buffers
         self.generation = 0
+        self.rows_host = torch.zeros(1, dtype=torch.int32).pin_memory()   # written by ep_local_rows_kernel
+        self.rows_event = torch.cuda.Event()
         # barrier flags: one word per peer, zero before the first barrier on every rank (the rendezvous below is the
         # one library barrier of the workspace's life: nobody announces itself into an array that is still being zeroed)
         self.flags = v("flags", 16, torch.int32)
@@ -192,7 +194,13 @@ class _ExpertParallelP2P(torch.autograd.Function):
         ws.offs.copy_(perm.offs)
         counts_all = torch.empty(W, E, **i32)
         dist.all_gather_into_tensor(counts_all, perm.counts, group=ws.group)   # also: peers' x/idx/spos/offs are in place
-        R = int(counts_all[:, rank * El:(rank + 1) * El].sum().item())         # the one host sync
+        # the one host wait of the step: a kernel stores the row count into pinned host memory and the host waits
+        # for an event behind it (a .item() would be a device-to-host copy, and that copy queues behind any large
+        # transfer the caller's input pipeline has on the copy engines)
+        L.check(L.lib().b200moe_ep_local_rows(L.ptr(counts_all), W, rank, E, ws.rows_host.data_ptr(), st))
+        ws.rows_event.record(torch.cuda.current_stream(dev))
+        ws.rows_event.synchronize()
+        R = int(ws.rows_host[0])
         cap_l = L.padded_rows_cap(R, El)
         poffs_l = torch.empty(El + 1, **i32)
         counts_l = torch.empty(El, **i32)

@@ -188,6 +188,26 @@ def _empty_result(hidden, top_k_weights, *params):
     return out
 
 
+_BF16_COPIES = {}     # id(parameter) -> (weak reference, version, bf16 copy)
+
+
+def _bf16_copy(t):
+    """bf16 copy of an fp16 / fp32 expert stack, kept until the tensor changes (its autograd version counter moves
+    on every in-place update, e.g. an optimizer step) or is freed.  Callers with fp32 master weights would otherwise
+    pay a full copy of both stacks on every call.  Tensors that need a gradient are cast afresh, so that autograd
+    carries the gradient back through the cast."""
+    if t.requires_grad and torch.is_grad_enabled():
+        return t.to(torch.bfloat16)
+    import weakref
+    key = id(t)
+    hit = _BF16_COPIES.get(key)
+    if hit is not None and hit[0]() is t and hit[1] == t._version:
+        return hit[2]
+    c = t.detach().to(torch.bfloat16)
+    _BF16_COPIES[key] = (weakref.ref(t, lambda _r, k=key: _BF16_COPIES.pop(k, None)), t._version, c)
+    return c
+
+
 def moe(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes, act_params=None):
     """hidden (N,H) bf16 (fp16 / fp32: computed in bf16), indices (N,k) int64, weights (N,k) float, gate_up_proj (E_glu,2I,H),
     down_proj (E_glu,H,I), act_codes (E,) int32, act_params (E,2) fp32 [alpha,gamma] for code 5 or None
@@ -202,8 +222,8 @@ def moe(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes
         # get the bf16 computation, the result in their dtype and, through the casts, gradients in the dtypes of
         # their tensors.  Accuracy is that of the bf16 path (2e-2 relative L2 against fp32).
         bf = torch.bfloat16
-        out = moe(hidden.to(bf), top_k_indices, top_k_weights, gate_up_proj.to(bf), down_proj.to(bf), act_codes,
-                  act_params)
+        out = moe(hidden.to(bf), top_k_indices, top_k_weights, _bf16_copy(gate_up_proj), _bf16_copy(down_proj),
+                  act_codes, act_params)
         return out.to(hidden.dtype)
     if act_params is None and n_glu == len(codes) and all(c == 0 for c in codes):
         return _GroupedMoE.apply(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes)
