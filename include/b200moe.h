@@ -285,6 +285,16 @@ int b200moe_ep_plan(const int32_t* counts_all, int W, int rank, int E, int32_t* 
  * transfers that occupy the copy engines.  No reference counterpart. */
 int b200moe_ep_local_rows(const int32_t* counts_all, int W, int rank, int E, int32_t* host_word,
                           b200moe_stream_t stream);
+/* ep_publish: this rank's routing tables -- idx (M) int64, slot_pos (M) int32, w (M) fp32 routing weights, offs
+ * (E+1) int32 -- stored into slot `rank` of the replica arrays of EVERY rank (tab_*_peers[r] = base of rank r's
+ * replica array, laid out [W][slot_stride] resp. [W][offs_stride] elements, both strides multiples of 4 so that
+ * every replica starts 16-byte aligned; plain peer stores, the local rank included).  After the next
+ * cross-rank ordering point every rank holds all W tables locally, and b200moe_ep_gather_pull /
+ * b200moe_ep_combine_bwd_pull are given pointers into these replicas as their idx / slot_pos / offs / w tables, so
+ * that only payload rows are read from peers.  No reference counterpart. */
+int b200moe_ep_publish(const int64_t* idx, const int32_t* slot_pos, const float* w, const int32_t* offs, int64_t M, int E,
+                       int W, int rank, int64_t slot_stride, int offs_stride, const void* const* tab_idx_peers, const void* const* tab_spos_peers,
+                       const void* const* tab_w_peers, const void* const* tab_offs_peers, b200moe_stream_t stream);
 /* Cross-rank barrier of the exchange (no reference counterpart).  flags_peers: HOST array of W device pointers,
  * entry r = rank r's flag array of W uint32 words (symmetric memory, zero before the first barrier).  The kernel
  * stores `generation` into word `rank` of every peer's array (release) and waits until all W words of its own

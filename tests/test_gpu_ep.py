@@ -52,6 +52,9 @@ def _worker(rank, world, port, cfg, transport, q):
         layer.update_bias(0.001)
         q.put((rank, out.detach().cpu(), x.grad.cpu(), layer.gate_up_proj.grad.cpu(), layer.down_proj.grad.cpu(),
                gw.cpu(), layer.bias.cpu()))
+    except BaseException as exc:                 # reported at once: the parent must not sit out its queue timeout
+        q.put((rank, "error", repr(exc)[:500]))
+        raise
     finally:
         dist.destroy_process_group()
 
@@ -71,9 +74,17 @@ def test_expert_parallel_equals_single_gpu(pkg, cfg, transport):
     for p in procs:
         p.start()
     res = {}
-    for _ in range(world):
-        r = q.get(timeout=300)
-        res[r[0]] = r[1:]
+    try:
+        for _ in range(world):
+            r = q.get(timeout=300)
+            assert r[1] != "error" if isinstance(r[1], str) else True, f"rank {r[0]} failed: {r[2]}"
+            res[r[0]] = r[1:]
+    except BaseException:
+        for p in procs:                          # a rank that failed leaves its peer waiting: end both
+            p.join(timeout=5)
+            if p.is_alive():
+                p.kill()
+        raise
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0

@@ -99,6 +99,31 @@ ep_local_rows_kernel(const int* __restrict__ counts_all, int W, int rank, int E,
   }
 }
 
+// Every rank sends its routing tables (expert index, position inside the expert segment and routing weight of each
+// slot; the segment offsets) to all ranks, itself included, with plain stores into slot `rank` of the replica arrays
+// in the receivers' symmetric buffers.  The pull kernels then resolve (source rank, token) -> local row from LOCAL
+// memory: the only peer reads left on their path are the payload rows.  1.5 MB per peer at 98 304 slots.
+__global__ void __launch_bounds__(256)
+ep_publish_kernel(const long long* __restrict__ idx, const int* __restrict__ spos, const float* __restrict__ w,
+                  const int* __restrict__ offs, long long M, int E, int rank, long long slot_stride, int offs_stride,
+                  const __grid_constant__ PeerPtrs tab_idx,
+                  const __grid_constant__ PeerPtrs tab_spos, const __grid_constant__ PeerPtrs tab_w,
+                  const __grid_constant__ PeerPtrs tab_offs) {
+  const int p = blockIdx.y;    // receiving rank
+  long long* d_idx = reinterpret_cast<long long*>(const_cast<void*>(tab_idx.p[p])) + rank * slot_stride;
+  int* d_spos = reinterpret_cast<int*>(const_cast<void*>(tab_spos.p[p])) + rank * slot_stride;
+  float* d_w = reinterpret_cast<float*>(const_cast<void*>(tab_w.p[p])) + rank * slot_stride;
+  int* d_offs = reinterpret_cast<int*>(const_cast<void*>(tab_offs.p[p])) + rank * offs_stride;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < M; i += stride) {
+    d_idx[i] = idx[i];
+    d_spos[i] = spos[i];
+    d_w[i] = w[i];
+  }
+  if (blockIdx.x == 0)
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) d_offs[e] = offs[e];
+}
+
 // The rows of this rank that a (source rank, token) pair feeds: lane j < k looks at slot j of the token in
 // the source's routing tables (peer reads) and, when that expert lives here, computes the padded row
 //   src_base[source][local expert] + (position of the slot inside its expert segment at the source).
@@ -564,6 +589,28 @@ int b200moe_ep_local_rows(const int32_t* counts_all, int W, int rank, int E, int
     const int rc__ = load_peers(&var, table, W, who); \
     if (rc__) return rc__;                          \
   }
+
+int b200moe_ep_publish(const int64_t* idx, const int32_t* slot_pos, const float* w, const int32_t* offs, int64_t M, int E,
+                       int W, int rank, int64_t slot_stride, int offs_stride, const void* const* tab_idx_peers, const void* const* tab_spos_peers,
+                       const void* const* tab_w_peers, const void* const* tab_offs_peers, b200moe_stream_t stream) {
+  B200_CHECK_ARG(idx && slot_pos && w && offs, B200MOE_E_NULL, "ep_publish: null pointer");
+  CHECK_WORLD("ep_publish");
+  B200_CHECK_ARG(M >= 0 && E >= 1 && E <= B200MOE_MAX_EXPERTS, B200MOE_E_BAD_SHAPE, "ep_publish: M = %lld, E = %d", (long long)M, E);
+  B200_CHECK_ARG(slot_stride >= M && slot_stride % 4 == 0 && offs_stride >= E + 1 && offs_stride % 4 == 0, B200MOE_E_BAD_SHAPE,
+                 "ep_publish: strides %lld / %d must cover M = %lld / E + 1 = %d and be multiples of 4 elements",
+                 (long long)slot_stride, offs_stride, (long long)M, E + 1);
+  LOAD_PEERS(ti, tab_idx_peers, "ep_publish(idx tables)");
+  LOAD_PEERS(ts, tab_spos_peers, "ep_publish(slot_pos tables)");
+  LOAD_PEERS(tw, tab_w_peers, "ep_publish(weight tables)");
+  LOAD_PEERS(to, tab_offs_peers, "ep_publish(offs tables)");
+  long long bx = (M + 255) / 256;
+  if (bx > 64) bx = 64;
+  if (bx < 1) bx = 1;
+  ep_publish_kernel<<<dim3(static_cast<unsigned>(bx), static_cast<unsigned>(W)), 256, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const long long*>(idx), slot_pos, w, offs, M, E, rank, slot_stride, offs_stride, ti, ts, tw, to);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
 
 int b200moe_ep_gather_pull(const void* const* x_peers, const void* const* idx_peers, const void* const* spos_peers,
                            const void* const* offs_peers, const int32_t* counts_l, const int32_t* poffs_l,

@@ -31,6 +31,11 @@ def _plan(*a):
     L.check(L.lib().b200moe_ep_plan(*a))
 
 
+@ops._op("ep_publish", 1)
+def _publish(*a):
+    L.check(L.lib().b200moe_ep_publish(*a))
+
+
 @ops._op("ep_gather_pull", 1)
 def _gather_pull(*a):
     L.check(L.lib().b200moe_ep_gather_pull(*a))
@@ -94,7 +99,14 @@ class SymmetricWorkspace:
         self.T, self.H, self.k, self.E = T, H, k, E
         M = T * k
         self.cap_w = L.padded_rows_cap(self.W * M, E // self.W)
-        fields = [("flags", 16 * 4), ("x", T * H * 2), ("go", T * H * 2), ("w", M * 4), ("idx", M * 8), ("spos", M * 4), ("offs", (E + 1) * 4)]
+        W = self.W
+        # x / go: payload rows that peers pull.  tab_*: replicas of EVERY rank's routing tables ([W][M] idx, slot_pos,
+        # routing weight; [W][E+1] offs), written by the owners of the tables (b200moe_ep_publish) so that the pull
+        # kernels resolve rows from local memory
+        self.slot_stride, self.offs_stride = _align(M, 4), _align(E + 1, 4)     # elements: every replica 16-byte aligned
+        Ms, Es = self.slot_stride, self.offs_stride
+        fields = [("flags", 16 * 4), ("x", T * H * 2), ("go", T * H * 2), ("tab_idx", W * Ms * 8), ("tab_spos", W * Ms * 4),
+                  ("tab_w", W * Ms * 4), ("tab_offs", W * Es * 4)]
         if exchange == "pull":     # owners keep their result rows; sized for every routed row landing on one rank
             fields += [("eo", self.cap_w * H * 2), ("gxs", self.cap_w * H * 2), ("gw", self.cap_w * 4)]
         else:                      # home ranks receive the result rows of their own slots
@@ -110,10 +122,10 @@ class SymmetricWorkspace:
         v = lambda name, n, dt: self.buf[self.offsets[name]: self.offsets[name] + n * dt.itemsize].view(dt)
         self.x = v("x", T * H, torch.bfloat16).view(T, H)
         self.go = v("go", T * H, torch.bfloat16).view(T, H)
-        self.w = v("w", M, torch.float32).view(T, k)
-        self.idx = v("idx", M, torch.int64).view(T, k)
-        self.spos = v("spos", M, torch.int32)
-        self.offs = v("offs", E + 1, torch.int32)
+        # host arrays of W pointers into THIS rank's replicas: entry s = the table rank s published here
+        mine = base[self.rank]
+        self.tabs = {name: L.ptr_table([mine + self.offsets[name] + s * stride for s in range(W)])
+                     for name, stride in (("tab_idx", Ms * 8), ("tab_spos", Ms * 4), ("tab_w", Ms * 4), ("tab_offs", Es * 4))}
         if exchange == "pull":
             self.eo = v("eo", self.cap_w * H, torch.bfloat16).view(self.cap_w, H)
             self.gxs = v("gxs", self.cap_w * H, torch.bfloat16).view(self.cap_w, H)
@@ -153,7 +165,7 @@ def _backward_push(ctx, grad_out, grad_eo):
     # the expert outputs of this rank's tokens are still in its receive buffer: grad of the routing weights
     grad_w = torch.empty(T, k, dtype=torch.float32, device=dev)
     _slot_dots(L.ptr(ws.go), L.ptr(ws.recv), T, k, H, L.ptr(grad_w), st)
-    _combine_bwd_pull(ws.peers["go"], ws.peers["w"], ws.peers["idx"], ws.peers["spos"], ws.peers["offs"], None,
+    _combine_bwd_pull(ws.peers["go"], ws.tabs["tab_w"], ws.tabs["tab_idx"], ws.tabs["tab_spos"], ws.tabs["tab_offs"], None,
                       L.ptr(perm_l.counts), L.ptr(perm_l.poffs), L.ptr(src_base), W, ws.rank, E, T, k, H,
                       L.ptr(grad_eo), None, st)
     grad_gu = ops.expert_down_dgrad_glu(grad_eo, down_local, gate_up, perm_l)
@@ -189,11 +201,14 @@ class _ExpertParallelP2P(torch.autograd.Function):
 
         perm = ops.permute_build(idx, E, want_order=True)   # slot_pos comes with the order tables
         ws.x.copy_(hidden)
-        ws.idx.copy_(idx)
-        ws.spos.copy_(perm.slot_pos)
-        ws.offs.copy_(perm.offs)
+        # routing tables (and the routing weights the backward needs) go to every rank's replicas
+        _publish(L.ptr(idx), L.ptr(perm.slot_pos), L.ptr(w32), L.ptr(perm.offs), T * k, E, W, rank, ws.slot_stride,
+                 ws.offs_stride, ws.peers["tab_idx"],
+                 ws.peers["tab_spos"], ws.peers["tab_w"], ws.peers["tab_offs"], st)
         counts_all = torch.empty(W, E, **i32)
-        dist.all_gather_into_tensor(counts_all, perm.counts, group=ws.group)   # also: peers' x/idx/spos/offs are in place
+        # the count exchange is also the ordering point: behind it every rank's x is in place and every table replica
+        # has arrived (each rank's contribution is sent after its own copies and stores in stream order)
+        dist.all_gather_into_tensor(counts_all, perm.counts, group=ws.group)
         # the one host wait of the step: a kernel stores the row count into pinned host memory and the host waits
         # for an event behind it (a .item() would be a device-to-host copy, and that copy queues behind any large
         # transfer the caller's input pipeline has on the copy engines)
@@ -213,7 +228,7 @@ class _ExpertParallelP2P(torch.autograd.Function):
         push = ws.exchange == "push"
         row_rank = torch.empty(cap_l, **i32) if push else None
         row_slot = torch.empty(cap_l, **i32) if push else None
-        _gather_pull(ws.peers["x"], ws.peers["idx"], ws.peers["spos"], ws.peers["offs"], L.ptr(counts_l),
+        _gather_pull(ws.peers["x"], ws.tabs["tab_idx"], ws.tabs["tab_spos"], ws.tabs["tab_offs"], L.ptr(counts_l),
                      L.ptr(poffs_l), L.ptr(src_base), W, rank, E, T, k, H, L.ptr(x_s), L.ptr(row_rank),
                      L.ptr(row_slot), st)
         perm_l = ops.Permutation(R, 1, El, cap_l, counts_l, None, poffs_l, None, None, tile_expert_l, None, None)
@@ -253,12 +268,11 @@ class _ExpertParallelP2P(torch.autograd.Function):
         dev = x_s.device
         st = L.stream_of(x_s)
         ws.go.copy_(grad_out)
-        ws.w.copy_(w32)
-        ws.barrier()                                                # every home rank's grad_out / w are in place
+        ws.barrier()                                                # every home rank's grad_out is in place
         grad_eo = torch.empty(cap_l, H, dtype=torch.bfloat16, device=dev)
         if ws.exchange == "push":
             return _backward_push(ctx, grad_out, grad_eo)
-        _combine_bwd_pull(ws.peers["go"], ws.peers["w"], ws.peers["idx"], ws.peers["spos"], ws.peers["offs"],
+        _combine_bwd_pull(ws.peers["go"], ws.tabs["tab_w"], ws.tabs["tab_idx"], ws.tabs["tab_spos"], ws.tabs["tab_offs"],
                           L.ptr(ws.eo), L.ptr(perm_l.counts), L.ptr(perm_l.poffs), L.ptr(src_base), W, ws.rank, E, T, k,
                           H, L.ptr(grad_eo), L.ptr(ws.gw), st)
         grad_gu = ops.expert_down_dgrad_glu(grad_eo, down_local, gate_up, perm_l)
