@@ -57,8 +57,8 @@ METRIC = "moe_layer_fwd_bwd_tokens_per_s"
 # H=2048, I=1408, 1536 rows per expert; the capture is summarised under profiles/).  Traffic grows in
 # proportion to the routed rows when H, I and the rows per expert stay the same (the headline workload).
 NCU_TRAFFIC = {"rows": 24576, "H": 2048, "I": 1408, "rows_per_expert": 1536,
-               "bytes": {"expert_gate_up_swiglu": 479.2e6, "expert_down": 243.0e6, "expert_down_dgrad_glu": 482.0e6,
-                         "expert_gate_up_dgrad": 422.8e6, "expert_wgrad": (394.8e6 + 237.9e6) / 2}}
+               "bytes": {"expert_gate_up_swiglu": 482.7e6, "expert_down": 244.4e6, "expert_down_dgrad_glu": 487.1e6,
+                         "expert_gate_up_dgrad": 423.9e6, "expert_wgrad": (398.0e6 + 240.6e6) / 2}}
 
 
 def _peaks(precision="bf16"):
