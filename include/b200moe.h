@@ -146,6 +146,12 @@ int b200moe_expert_gate_up_swiglu(const void* x_s, const void* gate_up_proj,
                                   const int32_t* tile_expert, const int32_t* poffs,
                                   int64_t rows_cap, int E, int64_t H, int64_t I, void* gate_up,
                                   void* inter, int32_t* status, b200moe_stream_t stream);
+/* The same GEMM with a per-expert activation code (act_codes (E) int32: 0 SiLU, 1 ReLU^2, 5 SiTU = tanh(g)*sigmoid(g),
+ * the parameter-free codes of _act_eager, kernels/sm75/moe.py:859-881, that need no row reduction) applied in the
+ * epilogue in place of the separate _glu_fwd launch (kernels/sm75/moe.py:767); act_codes NULL = all SiLU. */
+int b200moe_expert_gate_up_act(const void* x_s, const void* gate_up_proj, const int32_t* act_codes,
+                               const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E, int64_t H,
+                               int64_t I, void* gate_up, void* inter, int32_t* status, b200moe_stream_t stream);
 /* Generic grouped products over the padded rows (the two entry points after them are special cases):
  * linear:   out (rows,N) = a (rows,K) * W[e]^T, W (E,N,K)   -- kernels/sm75/moe.py:765,770 (x @ W[e].t())
  * linear_t: out (rows,N) = a (rows,K) * W[e],   W (E,K,N)   -- kernels/sm75/moe.py:807,822 (g @ W[e]) */
@@ -174,6 +180,12 @@ int b200moe_expert_down_dgrad_glu(const void* grad_eo, const void* down_proj, co
                                   const int32_t* tile_expert, const int32_t* poffs,
                                   int64_t rows_cap, int E, int64_t H, int64_t I, void* grad_gate_up,
                                   int32_t* status, b200moe_stream_t stream);
+/* The same with per-expert activation codes (see b200moe_expert_gate_up_act): the backward of _glu_bwd
+ * (kernels/sm75/moe.py:187-232) for codes 0, 1 and 5 without parameters, fused in the epilogue. */
+int b200moe_expert_down_dgrad_act(const void* grad_eo, const void* down_proj, const void* gate_up,
+                                  const int32_t* act_codes, const int32_t* tile_expert, const int32_t* poffs,
+                                  int64_t rows_cap, int E, int64_t H, int64_t I, void* grad_gate_up, int32_t* status,
+                                  b200moe_stream_t stream);
 /* Replaces grad_x_s = grad_gate_up @ W_gu[e] (kernels/sm75/moe.py:612, :822). */
 int b200moe_expert_gate_up_dgrad(const void* grad_gate_up, const void* gate_up_proj,
                                  const int32_t* tile_expert, const int32_t* poffs,

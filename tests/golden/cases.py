@@ -42,6 +42,10 @@ POLY_CASES = {
     "normsitu_specials": ([7, 2, 7, 5, 3, 4], True, None, 96),
     "situ_specials": ([0, 5, 2, 5, 3, 4], True, None, 96),
     "empty_experts_poly": ([5, 5, 5, 5, 0, 2], True, 4, 96),
+    # stacks of the parameter-free codes 0 / 1 / 5 only: the CUDA path applies these inside the GEMM epilogues
+    "fused_codes_015": ([0, 1, 5, 1, 5, 0], False, None, 96),
+    "fused_codes_015_wide": ([5, 1, 0, 1, 5, 0], False, None, 1536),
+    "fused_codes_015_empty": ([1, 5, 0, 5, 1, 0], False, 4, 256),
     "mixed_wide": ([0, 1, 2, 5, 0, 5], True, None, 1536),
     "situ_specials_wide": ([0, 5, 2, 5, 3, 4], True, None, 1536),
 }

@@ -49,6 +49,8 @@ _SIGNATURES = {
     "b200moe_permute_build_static": (c_int, [c_void_p, c_int64, c_int, c_int] + [c_void_p] * 8 + [c_void_p, c_void_p]),
     "b200moe_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p]),
     "b200moe_expert_gate_up_swiglu": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 4),
+    "b200moe_expert_gate_up_act": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 4),
+    "b200moe_expert_down_dgrad_act": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
     "b200moe_expert_linear": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
     "b200moe_expert_linear_t": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
     "b200moe_glu_fwd_rows": (c_int, [c_void_p] * 5 + [c_int64, c_int64, c_void_p, c_void_p]),

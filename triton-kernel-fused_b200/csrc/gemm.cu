@@ -56,7 +56,8 @@ struct Cfg {
 };
 
 
-template <int BN, int EPI, int CTAS>
+// POLY (GLU epilogues only): per-expert activation codes 0 / 1 / 5 (p.act_codes); false = SiLU for every expert
+template <int BN, int EPI, int CTAS, bool POLY = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmD2,
@@ -259,6 +260,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     for (int tile = first_tile; tile < total; tile += tile_step, ++it) {
       const Tile t = get_tile(p, tile, TN, TM, 64, order);
       const int buf = it & 1;
+      int act_code = 0;   // activation of this tile's expert (uniform over the tile)
+      if constexpr (POLY) act_code = p.act_codes[t.g];
       const int row0 = t.m0 + BM * static_cast<int>(cta_rank) + q * 32;   // first row of this warp
       const long long row = static_cast<long long>(row0) + lane;
       // GLU backward works on four 32-column sub-chunks per warp with two sets of (gate, up) boxes of
@@ -399,11 +402,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 // activation kernel does (kernels/sm75/moe.py:163-184)
                 const float2 gf = unpack_bf16x2(pg);
                 const float2 uf = unpack_bf16x2(pu);
-                const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
-                const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
                 og[16 * sub + i] = pg;
                 ou[16 * sub + i] = pu;
-                oh[16 * sub + i] = pack_bf16x2(gf.x * s0 * uf.x, gf.y * s1 * uf.y);
+                oh[16 * sub + i] = pack_bf16x2(glu_fwd_val<POLY>(act_code, gf.x, uf.x), glu_fwd_val<POLY>(act_code, gf.y, uf.y));
               }
             }
             staging_free(lane);
@@ -438,7 +439,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
             tmem_ld_wait();
             uint32_t og[16], ou[16];
-            glu_bwd32(r, g4, u4, og, ou);
+            glu_bwd32<POLY>(r, g4, u4, og, ou, act_code);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {              // results replace the inputs in place
               const int off = lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4);
@@ -517,9 +518,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 // activation kernel does (kernels/sm75/moe.py:163-184)
                 const float2 gf = unpack_bf16x2(og[h]);
                 const float2 uf = unpack_bf16x2(ou[h]);
-                const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
-                const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
-                oh[h] = pack_bf16x2(gf.x * s0 * uf.x, gf.y * s1 * uf.y);
+                oh[h] = pack_bf16x2(glu_fwd_val<POLY>(act_code, gf.x, uf.x), glu_fwd_val<POLY>(act_code, gf.y, uf.y));
               }
               *reinterpret_cast<uint4*>(gu + col) = make_uint4(og[0], og[1], og[2], og[3]);
               *reinterpret_cast<uint4*>(gu + I + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
@@ -572,12 +571,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                   // grad_inter is rounded to bf16 first: the reference materialises it in bf16
                   const float go0 = bf16_round(__uint_as_float(r[v * 8 + 2 * h]));
                   const float go1 = bf16_round(__uint_as_float(r[v * 8 + 2 * h + 1]));
-                  const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
-                  const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
-                  const float d0 = s0 * (1.0f + gf.x * (1.0f - s0));
-                  const float d1 = s1 * (1.0f + gf.y * (1.0f - s1));
-                  og[h] = pack_bf16x2(go0 * uf.x * d0, go1 * uf.y * d1);
-                  ou[h] = pack_bf16x2(go0 * (gf.x * s0), go1 * (gf.y * s1));
+                  float gg0, gu0, gg1, gu1;
+                  glu_bwd_val<POLY>(act_code, gf.x, uf.x, go0, gg0, gu0);
+                  glu_bwd_val<POLY>(act_code, gf.y, uf.y, go1, gg1, gu1);
+                  og[h] = pack_bf16x2(gg0, gg1);
+                  ou[h] = pack_bf16x2(gu0, gu1);
                 }
                 *reinterpret_cast<uint4*>(ggu + col) = make_uint4(og[0], og[1], og[2], og[3]);
                 *reinterpret_cast<uint4*>(ggu + I + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
@@ -615,14 +613,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 }
 
 // ---------------------------------------------------------------------------- host side
-template <int BN, int EPI, int CTAS>
+template <int BN, int EPI, int CTAS, bool POLY = false>
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const CUtensorMap& tmD2,
                   const GemmParams& p, int max_tiles, cudaStream_t stream) {
   using C = Cfg<BN, CTAS, epi_warp_bytes<BN, EPI>()>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_kernel<BN, EPI, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_err = cudaFuncSetAttribute(gemm_kernel<BN, EPI, CTAS, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     C::SMEM_BYTES);
   });
   if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(max dynamic smem)");
@@ -641,7 +639,7 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = (CTAS > 1) ? 1 : 0;
-  B200_CUDA(cudaLaunchKernelEx(&cfg, gemm_kernel<BN, EPI, CTAS>, tmA, tmB, tmD, tmD2, p));
+  B200_CUDA(cudaLaunchKernelEx(&cfg, gemm_kernel<BN, EPI, CTAS, POLY>, tmA, tmB, tmD, tmD2, p));
   return 0;
 }
 
@@ -687,7 +685,7 @@ static int pick_bn(long long n) {
 
 // d1 / d2 describe the bf16 outputs as {columns, rows, groups} tensors for the TMA-store epilogue
 // (d2 = the SwiGLU `inter` output); they are ignored by the kernels that store directly.
-template <int EPI>
+template <int EPI, bool POLY = false>
 static int dispatch_bn(int bn, const Operand& A, const Operand& B, const Operand* d1, const Operand* d2,
                        GemmParams& p, int max_tiles, cudaStream_t stream) {
   const bool pair = (bn == 256) && (p.sched != SCHED_DENSE) && pairs_enabled();
@@ -726,15 +724,15 @@ static int dispatch_bn(int bn, const Operand& A, const Operand& B, const Operand
       }
     }
   }
-  if (pair) return launch<256, EPI, 2>(tmA, tmB, tmD, tmD2, p, max_tiles > 0 ? (max_tiles + 1) / 2 : 0, stream);
+  if (pair) return launch<256, EPI, 2, POLY>(tmA, tmB, tmD, tmD2, p, max_tiles > 0 ? (max_tiles + 1) / 2 : 0, stream);
   if constexpr (EPI == EPI_AXPBY || EPI == EPI_STORE_SYM) {   // built for the 256-wide TMA-store epilogue only
     if (bn == 256) return launch<256, EPI, 1>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
     set_error("tile width %d not built for this epilogue", bn);
     return B200MOE_E_UNSUPPORTED;
   } else
   switch (bn) {
-    case 256: return launch<256, EPI, 1>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
-    case 128: return launch<128, EPI, 1>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
+    case 256: return launch<256, EPI, 1, POLY>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
+    case 128: return launch<128, EPI, 1, POLY>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
     default:
       if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32)
         return launch<64, EPI, 1>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
@@ -818,6 +816,13 @@ static int check_grouped(const char* who, const void* a, const void* b, const vo
 int b200moe_expert_gate_up_swiglu(const void* x_s, const void* gate_up_proj, const int32_t* tile_expert,
                                   const int32_t* poffs, int64_t rows_cap, int E, int64_t H, int64_t I,
                                   void* gate_up, void* inter, int32_t* status, b200moe_stream_t stream) {
+  return b200moe_expert_gate_up_act(x_s, gate_up_proj, nullptr, tile_expert, poffs, rows_cap, E, H, I, gate_up, inter,
+                                    status, stream);
+}
+
+int b200moe_expert_gate_up_act(const void* x_s, const void* gate_up_proj, const int32_t* act_codes,
+                               const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E, int64_t H,
+                               int64_t I, void* gate_up, void* inter, int32_t* status, b200moe_stream_t stream) {
   int rc = check_grouped("expert_gate_up_swiglu", x_s, gate_up_proj, gate_up, tile_expert, poffs, rows_cap, E, H, I);
   if (rc) return rc;
   B200_CHECK_ARG(inter && tile_expert, B200MOE_E_NULL, "expert_gate_up_swiglu: null pointer");
@@ -831,6 +836,10 @@ int b200moe_expert_gate_up_swiglu(const void* x_s, const void* gate_up_proj, con
   const int bn = (I >= 128) ? 256 : 128;   // tile covers bn/2 intermediate columns
   Operand d1{gate_up, 0, rows_cap, I, 2 * I, 2, I};       // {I, rows, 2}: group 0 = gate half, 1 = up half
   Operand d2{inter, 0, rows_cap, I, I, 1, rows_cap * I};
+  if (act_codes != nullptr) {
+    p.act_codes = act_codes;
+    return dispatch_bn<EPI_SWIGLU, true>(bn, a, b, &d1, &d2, p, 0, (cudaStream_t)stream);
+  }
   return dispatch_bn<EPI_SWIGLU>(bn, a, b, &d1, &d2, p, 0, (cudaStream_t)stream);
 }
 
@@ -937,6 +946,14 @@ int b200moe_expert_down_dgrad_glu(const void* grad_eo, const void* down_proj, co
                                   const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E,
                                   int64_t H, int64_t I, void* grad_gate_up, int32_t* status,
                                   b200moe_stream_t stream) {
+  return b200moe_expert_down_dgrad_act(grad_eo, down_proj, gate_up, nullptr, tile_expert, poffs, rows_cap, E, H, I,
+                                       grad_gate_up, status, stream);
+}
+
+int b200moe_expert_down_dgrad_act(const void* grad_eo, const void* down_proj, const void* gate_up,
+                                  const int32_t* act_codes, const int32_t* tile_expert, const int32_t* poffs,
+                                  int64_t rows_cap, int E, int64_t H, int64_t I, void* grad_gate_up, int32_t* status,
+                                  b200moe_stream_t stream) {
   int rc = check_grouped("expert_down_dgrad_glu", grad_eo, down_proj, grad_gate_up, tile_expert, poffs, rows_cap, E, H, I);
   if (rc) return rc;
   B200_CHECK_ARG(gate_up && tile_expert, B200MOE_E_NULL, "expert_down_dgrad_glu: null pointer");
@@ -950,6 +967,10 @@ int b200moe_expert_down_dgrad_glu(const void* grad_eo, const void* down_proj, co
   const int bn = pick_bn(I) == 64 ? 128 : pick_bn(I);
   Operand d{grad_gate_up, 0, rows_cap, I, 2 * I, 2, I};   // {I, rows, 2}: grad_gate half, grad_up half
   Operand d2{gate_up, 0, rows_cap, I, 2 * I, 2, I};       // the saved forward gate_up, same view (input)
+  if (act_codes != nullptr) {
+    p.act_codes = act_codes;
+    return dispatch_bn<EPI_GLU_BWD, true>(bn, a, b, &d, &d2, p, 0, (cudaStream_t)stream);
+  }
   return dispatch_bn<EPI_GLU_BWD>(bn, a, b, &d, &d2, p, 0, (cudaStream_t)stream);
 }
 

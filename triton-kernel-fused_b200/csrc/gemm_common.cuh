@@ -48,6 +48,9 @@ struct GemmParams {
   const int* push_rank;
   const int* push_slot;
   const long long* push_base;
+  // optional, GLU epilogues of the POLY instantiations: activation code of each expert (0 SiLU, 1 ReLU^2,
+  // 5 SiTU = tanh(g) * sigmoid(g)); nullptr in the plain instantiations, which are SiLU only
+  const int* act_codes;
 };
 
 struct Tile {
@@ -145,10 +148,54 @@ __device__ __forceinline__ uint4 pack8(const uint32_t* r) {
   return o;
 }
 
+// GLU activations of the fused epilogues.  POLY = false: SiLU only (the expressions the SiLU-only kernels have always
+// used, so their results do not change); POLY = true adds the parameter-free codes that need no row reduction:
+// 1 ReLU^2 and 5 SiTU = tanh(g) * sigmoid(g) (kernels/sm75/moe.py:859-881 of the reference).  `code` is uniform over
+// a tile (one expert per row tile).
+template <bool POLY>
+__device__ __forceinline__ float glu_fwd_val(int code, float g, float u) {
+  const float s = __fdividef(1.0f, 1.0f + __expf(-g));
+  if constexpr (POLY) {
+    if (code == 1) {
+      const float r = fmaxf(g, 0.0f);
+      return r * r * u;
+    }
+    if (code == 5) {
+      const float t = __fdividef(2.0f, 1.0f + __expf(-2.0f * g)) - 1.0f;
+      return t * s * u;
+    }
+  }
+  return g * s * u;
+}
+// grad_gate = go * up * f'(g), grad_up = go * f(g)
+template <bool POLY>
+__device__ __forceinline__ void glu_bwd_val(int code, float g, float u, float go, float& grad_gate, float& grad_up) {
+  const float s = __fdividef(1.0f, 1.0f + __expf(-g));
+  if constexpr (POLY) {
+    if (code == 1) {
+      const float r = fmaxf(g, 0.0f);
+      grad_gate = go * u * (2.0f * r);
+      grad_up = go * (r * r);
+      return;
+    }
+    if (code == 5) {
+      const float t = __fdividef(2.0f, 1.0f + __expf(-2.0f * g)) - 1.0f;
+      const float d = (1.0f - t * t) * s + t * s * (1.0f - s);
+      grad_gate = go * u * d;
+      grad_up = go * (t * s);
+      return;
+    }
+  }
+  const float d = s * (1.0f + g * (1.0f - s));
+  grad_gate = go * u * d;
+  grad_up = go * (g * s);
+}
+
 // grad_gate = gi*up*sig(g)*(1+g*(1-sig(g))), grad_up = gi*g*sig(g) for 32 columns; gi (fp32 accumulator)
 // is rounded to bf16 first because the reference materialises grad_inter in bf16
+template <bool POLY = false>
 __device__ __forceinline__ void glu_bwd32(const uint32_t (&r)[32], const uint4 (&g)[4], const uint4 (&u)[4],
-                                          uint32_t* og, uint32_t* ou) {
+                                          uint32_t* og, uint32_t* ou, int code = 0) {
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
     const uint32_t gw[4] = {g[v].x, g[v].y, g[v].z, g[v].w};
@@ -159,12 +206,11 @@ __device__ __forceinline__ void glu_bwd32(const uint32_t (&r)[32], const uint4 (
       const float2 uf = unpack_bf16x2(uw[h]);
       const float go0 = bf16_round(__uint_as_float(r[v * 8 + 2 * h]));
       const float go1 = bf16_round(__uint_as_float(r[v * 8 + 2 * h + 1]));
-      const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x));
-      const float s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
-      const float d0 = s0 * (1.0f + gf.x * (1.0f - s0));
-      const float d1 = s1 * (1.0f + gf.y * (1.0f - s1));
-      og[4 * v + h] = pack_bf16x2(go0 * uf.x * d0, go1 * uf.y * d1);
-      ou[4 * v + h] = pack_bf16x2(go0 * (gf.x * s0), go1 * (gf.y * s1));
+      float gg0, gu0, gg1, gu1;
+      glu_bwd_val<POLY>(code, gf.x, uf.x, go0, gg0, gu0);
+      glu_bwd_val<POLY>(code, gf.y, uf.y, go1, gg1, gu1);
+      og[4 * v + h] = pack_bf16x2(gg0, gg1);
+      ou[4 * v + h] = pack_bf16x2(gu0, gu1);
     }
   }
 }

@@ -47,14 +47,22 @@ class _GroupedMoE(torch.autograd.Function):
         down_proj = down_proj.contiguous()
         w32 = wt.detach().float().contiguous()
 
+        # a stack that mixes the parameter-free codes 0 / 1 / 5 keeps the fused epilogues: the code of a tile's
+        # expert picks the activation there; an all-SiLU stack runs the SiLU-only instantiations
+        codes, _ = _code_info(act_codes)
+        codes_dev = None
+        if any(c != 0 for c in codes):
+            codes_dev = act_codes.to(device=hidden.device, dtype=torch.int32).contiguous()
+
         perm = ops.permute_build(idx, E)
         x_s = ops.gather_rows(hidden, perm)
-        gate_up, inter = ops.expert_gate_up_swiglu(x_s, gate_up_proj, perm)
+        gate_up, inter = ops.expert_gate_up_swiglu(x_s, gate_up_proj, perm, codes_dev)
         eo = ops.expert_down(inter, down_proj, perm)
         out = ops.combine(eo, w32, perm)
 
         ctx.perm = perm
         ctx.wt_dtype = wt.dtype
+        ctx.codes_dev = codes_dev
         ctx.save_for_backward(x_s, gate_up, inter, eo, w32, gate_up_proj, down_proj)
         return out
 
@@ -69,7 +77,7 @@ class _GroupedMoE(torch.autograd.Function):
         grad_eo, grad_w = ops.combine_bwd(grad_out, eo, w32, perm)
         grad_hidden = grad_gate_up_proj = grad_down_proj = None
         if need_x or need_gu:
-            grad_gu = ops.expert_down_dgrad_glu(grad_eo, down_proj, gate_up, perm)
+            grad_gu = ops.expert_down_dgrad_glu(grad_eo, down_proj, gate_up, perm, ctx.codes_dev)
             if need_gu:
                 grad_gate_up_proj = ops.expert_wgrad(grad_gu, x_s, perm)
             if need_x:
@@ -82,6 +90,7 @@ class _GroupedMoE(torch.autograd.Function):
 
 
 GLU_CODES = (0, 1, 2, 5, 6, 7)     # weight-carrying experts (kernels/sm75/moe.py:1-31)
+FUSED_CODES = (0, 1, 5)            # applied inside the GEMM epilogues (no row reduction, no parameters)
 SPECIAL_CODES = (3, 4)             # Identity, Zero: expert kinds without weights, listed after the GLU experts
 
 
@@ -212,8 +221,9 @@ def moe(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes
     """hidden (N,H) bf16 (fp16 / fp32: computed in bf16), indices (N,k) int64, weights (N,k) float, gate_up_proj (E_glu,2I,H),
     down_proj (E_glu,H,I), act_codes (E,) int32, act_params (E,2) fp32 [alpha,gamma] for code 5 or None
     -> (N,H).  Same contract as the reference's `moe` (kernels/sm75/moe.py:838-855); differentiable
-    w.r.t. hidden, weights, both projections and act_params.  A pure SiLU-GLU stack runs with the
-    activation fused into the GEMM epilogues; any other stack runs the PolyGLU row kernels."""
+    w.r.t. hidden, weights, both projections and act_params.  A stack of SiLU / ReLU^2 / parameter-free SiTU experts
+    (codes 0, 1, 5, no act_params, no Identity / Zero experts) runs with the activation fused into the GEMM epilogues;
+    any other stack (Norm codes, learnable SiTU, special experts) runs the PolyGLU row kernels."""
     codes, n_glu = _code_info(act_codes)
     if hidden.shape[0] == 0:
         return _empty_result(hidden, top_k_weights, gate_up_proj, down_proj, act_params)
@@ -225,7 +235,7 @@ def moe(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes
         out = moe(hidden.to(bf), top_k_indices, top_k_weights, _bf16_copy(gate_up_proj), _bf16_copy(down_proj),
                   act_codes, act_params)
         return out.to(hidden.dtype)
-    if act_params is None and n_glu == len(codes) and all(c == 0 for c in codes):
+    if act_params is None and n_glu == len(codes) and all(c in FUSED_CODES for c in codes):
         return _GroupedMoE.apply(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes)
     return _PolyGLUMoE.apply(hidden, top_k_indices, top_k_weights, gate_up_proj, down_proj, act_codes, act_params)
 
