@@ -174,6 +174,8 @@ def _workload(n_gpus, which="headline"):
         w = dict(MXFP8 if which == "mxfp8" else MXFP8_PROFILE)
     elif which == "zipf":
         w = dict(ZIPF)
+    elif which == "polyglu":          # the headline layer with experts of activation codes 0 / 1 / 5 in turn
+        w = dict(HEADLINE)
     else:
         w = dict(HEADLINE if which == "headline" else PROFILE)
     w["which"] = which
@@ -189,7 +191,8 @@ def _make_layer(pkg, w, device, seed, world):
         if world > 1:
             layer = pkg.ExpertParallelMoELayer(w["H"], w["I"], w["E"], top_k=w["k"], **_ep_settings())
         else:
-            layer = pkg.MoELayer(w["H"], w["I"], w["E"], top_k=w["k"], precision=w["precision"])
+            codes = [(0, 1, 5)[e % 3] for e in range(w["E"])] if w["which"] == "polyglu" else None
+            layer = pkg.MoELayer(w["H"], w["I"], w["E"], top_k=w["k"], precision=w["precision"], act_codes=codes)
     layer = layer.to(torch.bfloat16)
     if w["which"] == "zipf":   # selection bias = 0.15 x log of Zipf(1.1) frequencies over a seeded expert order
         gz = torch.Generator().manual_seed(7)
@@ -542,6 +545,17 @@ def run_ours(args):
     ms_step = res["ms_step"]
 
     secondary = {}
+    if args.workload == "polyglu" and world == 1:
+        # the same stack through the generic path (plain GEMM -> row kernel -> GEMM): what the fused epilogues save
+        moe_mod = importlib.import_module(PKG + ".moe")
+        fused_codes, moe_mod.FUSED_CODES = moe_mod.FUSED_CODES, ()
+        try:
+            torch.cuda.empty_cache()
+            r2 = measure_layer(cx, w, max(3, min(args.steps, 10)), 3, e2e=False)
+            secondary["row_kernel_path"] = {"ms_per_step": round(r2["ms_step"], 4), "clocks": r2["clocks"],
+                                            "kernels": _kernel_table(r2, w, max(3, min(args.steps, 10)))}
+        finally:
+            moe_mod.FUSED_CODES = fused_codes
     if not args.no_secondary and args.workload == "headline":
         sec_steps, sec_warm = max(3, min(args.steps, 10)), 3
         names = ("zipf", "mxfp8") if world == 1 else ("ep5",)
@@ -868,7 +882,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary configurations after the headline")
     ap.add_argument("--no-parity", action="store_true", help="N > 1: skip the expert-parallel parity check")
-    ap.add_argument("--workload", default="headline", choices=["headline", "profile", "ep5", "mxfp8", "mxfp8_profile", "zipf", "muon", "muon_profile"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "profile", "ep5", "mxfp8", "mxfp8_profile", "zipf", "polyglu", "muon", "muon_profile"],
                     help="profile = small case for profiler captures (not a benchmark number)")
     args = ap.parse_args()
     if args.impl == "reference":

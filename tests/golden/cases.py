@@ -47,6 +47,8 @@ POLY_CASES = {
     "fused_codes_015_wide": ([5, 1, 0, 1, 5, 0], False, None, 1536),
     "fused_codes_015_empty": ([1, 5, 0, 5, 1, 0], False, 4, 256),
     "mixed_wide": ([0, 1, 2, 5, 0, 5], True, None, 1536),
+    "normrelu2_wide": ([1, 2, 6, 6, 0, 6], True, None, 1536),        # parity_situ.py:96
+    "normsitu_wide": ([2, 5, 7, 7, 0, 7], True, None, 1536),         # parity_situ.py:97
     "situ_specials_wide": ([0, 5, 2, 5, 3, 4], True, None, 1536),
 }
 

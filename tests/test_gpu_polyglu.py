@@ -92,3 +92,45 @@ def test_fused_activation_codes_equal_the_row_kernels(pkg, I):
     for a, b, c in zip(fused, rows, routed):
         assert torch.equal(a, c)
         assert O.rel_l2(a.float(), b.float()) < 2e-3
+
+
+@pytest.mark.parametrize("name", ["all_situ", "situ_specials", "normrelu2_wide", "fused_codes_015"])
+def test_moe_under_bf16_autocast_of_fp32_tensors(pkg, poly_golden, name):
+    """fp32 parameters and activations under torch.autocast(bf16), the reference's "bf16-ac" cases
+    (parity_situ.py:103-106): the Function casts at its boundary, gradients come back in fp32."""
+    c = poly_inputs(name)
+    f32 = lambda t: t.float().to(DEV).requires_grad_(True)
+    h, gu, dn, wt = f32(c["hidden"]), f32(c["gate_up"]), f32(c["down"]), f32(c["w"])
+    ap = f32(c["act_params"]) if c["act_params"] is not None else None
+    codes = torch.tensor(c["codes"], dtype=torch.int32, device=DEV)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = pkg.moe(h, c["idx"].to(DEV), wt, gu, dn, codes, ap)
+    assert out.dtype == torch.bfloat16
+    (out.float() * c["grad_out"].to(DEV)).sum().backward()
+    pkg.check_status()
+    g = lambda k: torch.from_numpy(poly_golden[f"{name}.{k}"]).float()
+    assert h.grad.dtype == torch.float32 and gu.grad.dtype == torch.float32 and dn.grad.dtype == torch.float32
+    assert O.rel_l2(out.float().cpu(), g("out")) < TOL
+    assert O.rel_l2(h.grad.cpu(), g("grad_hidden")) < TOL
+    assert O.rel_l2(wt.grad.cpu(), g("grad_w")) < TOL
+    assert O.rel_l2(gu.grad.cpu()[:, ::4, ::4], g("grad_gate_up_sub")) < TOL
+    assert O.rel_l2(dn.grad.cpu()[:, ::4, ::4], g("grad_down_sub")) < TOL
+
+
+def test_router_and_layer_under_bf16_autocast(pkg):
+    """The whole module with fp32 parameters under autocast equals the same module held in bf16, bit for bit: both
+    routes cast the same values at the same boundaries."""
+    T, H, E, I, k = 1024, 256, 8, 256, 2
+    torch.manual_seed(5)
+    layer32 = pkg.MoELayer(H, I, E, top_k=k).to(DEV)
+    layer16 = pkg.MoELayer(H, I, E, top_k=k).to(DEV)
+    layer16.load_state_dict(layer32.state_dict())
+    layer16 = layer16.to(torch.bfloat16)
+    x = torch.randn(T, H, device=DEV)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y32 = layer32(x)
+    y16 = layer16(x.to(torch.bfloat16))
+    pkg.check_status()
+    assert y32.dtype == torch.bfloat16 and torch.equal(y32, y16)
+    y32.float().sum().backward()
+    assert layer32.gate_up_proj.grad.dtype == torch.float32 and torch.isfinite(layer32.gate.weight.grad).all()

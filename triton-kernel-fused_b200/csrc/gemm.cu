@@ -20,6 +20,7 @@
 #include <stdlib.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "gemm_common.cuh"
 
@@ -396,16 +397,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               tmem_ld_wait();
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                const uint32_t pg = pack_bf16x2(__uint_as_float(g[2 * i]), __uint_as_float(g[2 * i + 1]));
-                const uint32_t pu = pack_bf16x2(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]));
-                // the activation reads the bf16-rounded gate/up, as the reference's separate
-                // activation kernel does (kernels/sm75/moe.py:163-184)
-                const float2 gf = unpack_bf16x2(pg);
-                const float2 uf = unpack_bf16x2(pu);
-                og[16 * sub + i] = pg;
-                ou[16 * sub + i] = pu;
-                oh[16 * sub + i] = pack_bf16x2(glu_fwd_val<POLY>(act_code, gf.x, uf.x), glu_fwd_val<POLY>(act_code, gf.y, uf.y));
+                og[16 * sub + i] = pack_bf16x2(__uint_as_float(g[2 * i]), __uint_as_float(g[2 * i + 1]));
+                ou[16 * sub + i] = pack_bf16x2(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]));
               }
+              glu_fwd_pairs_by_code<POLY>(act_code, og + 16 * sub, ou + 16 * sub, oh + 16 * sub, 16);
             }
             staging_free(lane);
             stage_row(sbuf, lane, og);
@@ -514,12 +509,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               for (int h = 0; h < 4; ++h) {
                 og[h] = pack_bf16x2(__uint_as_float(g[v * 8 + 2 * h]), __uint_as_float(g[v * 8 + 2 * h + 1]));
                 ou[h] = pack_bf16x2(__uint_as_float(u[v * 8 + 2 * h]), __uint_as_float(u[v * 8 + 2 * h + 1]));
-                // the activation reads the bf16-rounded gate/up, as the reference's separate
-                // activation kernel does (kernels/sm75/moe.py:163-184)
-                const float2 gf = unpack_bf16x2(og[h]);
-                const float2 uf = unpack_bf16x2(ou[h]);
-                oh[h] = pack_bf16x2(glu_fwd_val<POLY>(act_code, gf.x, uf.x), glu_fwd_val<POLY>(act_code, gf.y, uf.y));
               }
+              glu_fwd_pairs_by_code<POLY>(act_code, og, ou, oh, 4);
               *reinterpret_cast<uint4*>(gu + col) = make_uint4(og[0], og[1], og[2], og[3]);
               *reinterpret_cast<uint4*>(gu + I + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
               *reinterpret_cast<uint4*>(it_out + col) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
@@ -564,19 +555,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
                 const uint32_t uw[4] = {u4.x, u4.y, u4.z, u4.w};
                 uint32_t og[4], ou[4];
+                auto bwd8 = [&](auto code_tag) {
+                  constexpr int CODE = decltype(code_tag)::value;
 #pragma unroll
-                for (int h = 0; h < 4; ++h) {
-                  const float2 gf = unpack_bf16x2(gw[h]);
-                  const float2 uf = unpack_bf16x2(uw[h]);
-                  // grad_inter is rounded to bf16 first: the reference materialises it in bf16
-                  const float go0 = bf16_round(__uint_as_float(r[v * 8 + 2 * h]));
-                  const float go1 = bf16_round(__uint_as_float(r[v * 8 + 2 * h + 1]));
-                  float gg0, gu0, gg1, gu1;
-                  glu_bwd_val<POLY>(act_code, gf.x, uf.x, go0, gg0, gu0);
-                  glu_bwd_val<POLY>(act_code, gf.y, uf.y, go1, gg1, gu1);
-                  og[h] = pack_bf16x2(gg0, gg1);
-                  ou[h] = pack_bf16x2(gu0, gu1);
-                }
+                  for (int h = 0; h < 4; ++h) {
+                    const float2 gf = unpack_bf16x2(gw[h]);
+                    const float2 uf = unpack_bf16x2(uw[h]);
+                    // grad_inter is rounded to bf16 first: the reference materialises it in bf16
+                    const float go0 = bf16_round(__uint_as_float(r[v * 8 + 2 * h]));
+                    const float go1 = bf16_round(__uint_as_float(r[v * 8 + 2 * h + 1]));
+                    float gg0, gu0, gg1, gu1;
+                    glu_bwd_val<CODE>(gf.x, uf.x, go0, gg0, gu0);
+                    glu_bwd_val<CODE>(gf.y, uf.y, go1, gg1, gu1);
+                    og[h] = pack_bf16x2(gg0, gg1);
+                    ou[h] = pack_bf16x2(gu0, gu1);
+                  }
+                };
+                if (POLY && act_code == 1) bwd8(std::integral_constant<int, 1>{});
+                else if (POLY && act_code == 5) bwd8(std::integral_constant<int, 5>{});
+                else bwd8(std::integral_constant<int, 0>{});
                 *reinterpret_cast<uint4*>(ggu + col) = make_uint4(og[0], og[1], og[2], og[3]);
                 *reinterpret_cast<uint4*>(ggu + I + col) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
               }

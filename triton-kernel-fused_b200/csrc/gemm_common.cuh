@@ -148,54 +148,73 @@ __device__ __forceinline__ uint4 pack8(const uint32_t* r) {
   return o;
 }
 
-// GLU activations of the fused epilogues.  POLY = false: SiLU only (the expressions the SiLU-only kernels have always
-// used, so their results do not change); POLY = true adds the parameter-free codes that need no row reduction:
-// 1 ReLU^2 and 5 SiTU = tanh(g) * sigmoid(g) (kernels/sm75/moe.py:859-881 of the reference).  `code` is uniform over
-// a tile (one expert per row tile).
-template <bool POLY>
-__device__ __forceinline__ float glu_fwd_val(int code, float g, float u) {
-  const float s = __fdividef(1.0f, 1.0f + __expf(-g));
-  if constexpr (POLY) {
-    if (code == 1) {
-      const float r = fmaxf(g, 0.0f);
-      return r * r * u;
-    }
-    if (code == 5) {
+// GLU activations of the fused epilogues, by activation code: 0 SiLU, 1 ReLU^2, 5 SiTU = tanh(g) * sigmoid(g)
+// (the parameter-free codes of the reference that need no row reduction, kernels/sm75/moe.py:859-881).  The code is
+// uniform over a tile (one expert per row tile), so the epilogues branch once per 32-column chunk and run a loop
+// specialised for the code; code 0 uses the expressions the SiLU-only kernels have always used.
+template <int CODE>
+__device__ __forceinline__ float glu_fwd_val(float g, float u) {
+  if constexpr (CODE == 1) {
+    const float r = fmaxf(g, 0.0f);
+    return r * r * u;
+  } else {
+    const float s = __fdividef(1.0f, 1.0f + __expf(-g));
+    if constexpr (CODE == 5) {
       const float t = __fdividef(2.0f, 1.0f + __expf(-2.0f * g)) - 1.0f;
       return t * s * u;
+    } else {
+      return g * s * u;
     }
   }
-  return g * s * u;
 }
 // grad_gate = go * up * f'(g), grad_up = go * f(g)
-template <bool POLY>
-__device__ __forceinline__ void glu_bwd_val(int code, float g, float u, float go, float& grad_gate, float& grad_up) {
-  const float s = __fdividef(1.0f, 1.0f + __expf(-g));
-  if constexpr (POLY) {
-    if (code == 1) {
-      const float r = fmaxf(g, 0.0f);
-      grad_gate = go * u * (2.0f * r);
-      grad_up = go * (r * r);
-      return;
-    }
-    if (code == 5) {
+template <int CODE>
+__device__ __forceinline__ void glu_bwd_val(float g, float u, float go, float& grad_gate, float& grad_up) {
+  if constexpr (CODE == 1) {
+    const float r = fmaxf(g, 0.0f);
+    grad_gate = go * u * (2.0f * r);
+    grad_up = go * (r * r);
+  } else {
+    const float s = __fdividef(1.0f, 1.0f + __expf(-g));
+    if constexpr (CODE == 5) {
       const float t = __fdividef(2.0f, 1.0f + __expf(-2.0f * g)) - 1.0f;
       const float d = (1.0f - t * t) * s + t * s * (1.0f - s);
       grad_gate = go * u * d;
       grad_up = go * (t * s);
-      return;
+    } else {
+      const float d = s * (1.0f + g * (1.0f - s));
+      grad_gate = go * u * d;
+      grad_up = go * (g * s);
     }
   }
-  const float d = s * (1.0f + g * (1.0f - s));
-  grad_gate = go * u * d;
-  grad_up = go * (g * s);
 }
 
-// grad_gate = gi*up*sig(g)*(1+g*(1-sig(g))), grad_up = gi*g*sig(g) for 32 columns; gi (fp32 accumulator)
+// Forward GLU on n packed pairs: pg / pu = bf16-rounded gate / up (the activation reads the rounded values, as the
+// reference's separate activation kernel does, kernels/sm75/moe.py:163-184); oh = act(gate) * up
+template <int CODE>
+__device__ __forceinline__ void glu_fwd_pairs(const uint32_t* pg, const uint32_t* pu, uint32_t* oh, int n) {
+#pragma unroll
+  for (int i = 0; i < n; ++i) {
+    const float2 gf = unpack_bf16x2(pg[i]);
+    const float2 uf = unpack_bf16x2(pu[i]);
+    oh[i] = pack_bf16x2(glu_fwd_val<CODE>(gf.x, uf.x), glu_fwd_val<CODE>(gf.y, uf.y));
+  }
+}
+template <bool POLY>
+__device__ __forceinline__ void glu_fwd_pairs_by_code(int code, const uint32_t* pg, const uint32_t* pu, uint32_t* oh,
+                                                      int n) {
+  if constexpr (POLY) {
+    if (code == 1) return glu_fwd_pairs<1>(pg, pu, oh, n);
+    if (code == 5) return glu_fwd_pairs<5>(pg, pu, oh, n);
+  }
+  glu_fwd_pairs<0>(pg, pu, oh, n);
+}
+
+// grad_gate = gi*up*f'(g), grad_up = gi*f(g) for 32 columns; gi (fp32 accumulator)
 // is rounded to bf16 first because the reference materialises grad_inter in bf16
-template <bool POLY = false>
-__device__ __forceinline__ void glu_bwd32(const uint32_t (&r)[32], const uint4 (&g)[4], const uint4 (&u)[4],
-                                          uint32_t* og, uint32_t* ou, int code = 0) {
+template <int CODE>
+__device__ __forceinline__ void glu_bwd32_code(const uint32_t (&r)[32], const uint4 (&g)[4], const uint4 (&u)[4],
+                                               uint32_t* og, uint32_t* ou) {
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
     const uint32_t gw[4] = {g[v].x, g[v].y, g[v].z, g[v].w};
@@ -207,12 +226,21 @@ __device__ __forceinline__ void glu_bwd32(const uint32_t (&r)[32], const uint4 (
       const float go0 = bf16_round(__uint_as_float(r[v * 8 + 2 * h]));
       const float go1 = bf16_round(__uint_as_float(r[v * 8 + 2 * h + 1]));
       float gg0, gu0, gg1, gu1;
-      glu_bwd_val<POLY>(code, gf.x, uf.x, go0, gg0, gu0);
-      glu_bwd_val<POLY>(code, gf.y, uf.y, go1, gg1, gu1);
+      glu_bwd_val<CODE>(gf.x, uf.x, go0, gg0, gu0);
+      glu_bwd_val<CODE>(gf.y, uf.y, go1, gg1, gu1);
       og[4 * v + h] = pack_bf16x2(gg0, gg1);
       ou[4 * v + h] = pack_bf16x2(gu0, gu1);
     }
   }
+}
+template <bool POLY = false>
+__device__ __forceinline__ void glu_bwd32(const uint32_t (&r)[32], const uint4 (&g)[4], const uint4 (&u)[4],
+                                          uint32_t* og, uint32_t* ou, int code = 0) {
+  if constexpr (POLY) {
+    if (code == 1) return glu_bwd32_code<1>(r, g, u, og, ou);
+    if (code == 5) return glu_bwd32_code<5>(r, g, u, og, ou);
+  }
+  glu_bwd32_code<0>(r, g, u, og, ou);
 }
 
 // the same with grad_inter already rounded and packed: gi[i] = columns (2i, 2i+1)
