@@ -370,6 +370,16 @@ int b200moe_muon_row_sumsq(const void* x, int64_t rows, int64_t cols, float* row
  * row.  The row prescale of scale_mode "aurora" with K = 1, beta = 0 (kernels/muon/muon_scaling.py:107-111). */
 int b200moe_muon_prescale_rows(const void* x, const float* rowss, int64_t rows, int64_t cols, float tgt, float eps,
                                void* out, float* rowss_out, b200moe_stream_t stream);
+/* Row scaling with a given multiplier (the combined per-row multiplier of the reference's `aurora_ema` prescale,
+ * kernels/muon/muon_scaling.py:141-142): out[row,:] = bf16(x[row,:] * mult[row]), rowss_out[row] = sum of squares of
+ * the rounded row.  x, out (rows, cols) bf16; mult, rowss_out (rows) fp32. */
+int b200moe_muon_scale_rows(const void* x, const float* mult, int64_t rows, int64_t cols, void* out, float* rowss_out,
+                            b200moe_stream_t stream);
+/* Weight update of the per-row scale modes (`normuon`, `aurora_ema_v2`: kernels/muon/muon_scaling.py:166-195 and the
+ * scatter at kernels/sm75/muon.py:381,431-434): p[row,:] = decay * p[row,:] + alpha * bf16(x[row,:] * mult[row]);
+ * x (rows, cols) bf16 in the parameters' own layout, p bf16 or fp32 (p_f32). */
+int b200moe_muon_update_rows(const void* x, const float* mult, int64_t rows, int64_t cols, float decay, float alpha, void* p,
+                             int p_f32, b200moe_stream_t stream);
 
 /* Frobenius normalisation into the iteration's layout (kernels/sm75/muon.py:78-82): norms[e] =
  * bf16(max(sqrt(sum_i rowss[e*r+i]), eps)); transposed == 0: xp (E, Rp, c), xp[e,i,:] = x[e,i,:] / norms[e];

@@ -86,6 +86,16 @@ MUON_STEP_CASES = {
     "aurora_tall": ((4, 96, 64), 23, "aurora", True, 0.1, 3),
     "aurora_wide": ((4, 64, 96), 24, "aurora", True, 0.0, 3),
 }
+# the per-row scale modes and aurora with two passes: name -> (shape, seed, scale_mode, nesterov, weight_decay, steps, aurora_k)
+MUON_MODE_CASES = {
+    "normuon_tall": ((3, 96, 64), 31, "normuon", True, 0.1, 3, None),
+    "normuon_wide": ((3, 64, 96), 32, "normuon", True, 0.0, 3, None),
+    "aurora_ema_tall": ((3, 96, 64), 33, "aurora_ema", True, 0.1, 3, None),
+    "aurora_ema_wide": ((3, 64, 96), 34, "aurora_ema", False, 0.0, 3, None),
+    "aurora_ema_v2_tall": ((3, 96, 64), 35, "aurora_ema_v2", True, 0.1, 3, None),
+    "aurora_k2_tall": ((3, 96, 64), 36, "aurora", True, 0.0, 3, 2),
+    "aurora_k2_wide": ((3, 64, 96), 37, "aurora", True, 0.1, 3, 2),
+}
 MUON_LR, MUON_MOMENTUM = 0.02, 0.95
 
 
@@ -98,7 +108,7 @@ def muon_ns_input(name):
 def muon_step_inputs(name):
     """(initial parameters, list of per-step gradients), fp32, seeded."""
     import torch
-    shape, seed, _mode, _nest, _wd, steps = MUON_STEP_CASES[name]
+    shape, seed, _mode, _nest, _wd, steps = (MUON_STEP_CASES.get(name) or MUON_MODE_CASES[name])[:6]
     g = torch.Generator().manual_seed(seed)
     p0 = torch.randn(*shape, generator=g) * 0.02
     grads = [torch.randn(*shape, generator=g) for _ in range(steps)]

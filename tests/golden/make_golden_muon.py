@@ -6,7 +6,9 @@ It imports `newton_schulz` and `FusedMuon` from the reference's kernels/sm75/muo
 CPU), feeds them the seeded inputs of tests/golden/cases.py and stores
   * ns_<case>_f32 / ns_<case>_bf16 : newton_schulz(G, ns_dtype=float32 / bfloat16) of the reference;
   * step_<case>_p / step_<case>_mom: the parameters and the momentum buffer after the case's last step of
-                                     FusedMuon(ns_dtype=float32) in the case's scale mode.
+                                     FusedMuon(ns_dtype=float32) in the case's scale mode (polar, aurora with one
+                                     and two passes, normuon, aurora_ema, aurora_ema_v2), and step_<case>_v, the
+                                     per-row EMA state of the modes that keep one.
 Inputs are reproducible from their seeds, so only outputs are stored.
 """
 import os
@@ -25,8 +27,8 @@ sys.path.insert(0, REF)
 
 from kernels.sm75.muon import FusedMuon, newton_schulz   # noqa: E402  (the reference itself)
 
-from tests.golden.cases import (MUON_LR, MUON_MOMENTUM, MUON_NS_CASES, MUON_STEP_CASES, muon_ns_input,  # noqa: E402
-                                muon_step_inputs)
+from tests.golden.cases import (MUON_LR, MUON_MODE_CASES, MUON_MOMENTUM, MUON_NS_CASES, MUON_STEP_CASES,  # noqa: E402
+                                muon_ns_input, muon_step_inputs)
 
 
 def main():
@@ -45,6 +47,18 @@ def main():
             opt.step()
         out[f"step_{name}_p"] = p.detach().clone().numpy()
         out[f"step_{name}_mom"] = opt.state[p]["muon_mom"].float().numpy()
+    for name, (_shape, _seed, mode, nesterov, wd, steps, k) in MUON_MODE_CASES.items():
+        p0, grads = muon_step_inputs(name)
+        p = torch.nn.Parameter(p0.clone())
+        opt = FusedMuon([p], lr=MUON_LR, momentum=MUON_MOMENTUM, nesterov=nesterov, weight_decay=wd,
+                        ns_dtype=torch.float32, scale_mode=mode, aurora_k=k)
+        for i in range(steps):
+            p.grad = grads[i].clone()
+            opt.step()
+        out[f"step_{name}_p"] = p.detach().clone().numpy()
+        out[f"step_{name}_mom"] = opt.state[p]["muon_mom"].float().numpy()
+        if "scale_v" in opt.state[p]:
+            out[f"step_{name}_v"] = opt.state[p]["scale_v"].float().numpy()
     np.savez_compressed(os.path.join(HERE, "muon.npz"), **out)
     print("wrote muon.npz:", {k: v.shape for k, v in out.items()})
 

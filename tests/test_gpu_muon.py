@@ -13,7 +13,7 @@ import pytest
 import torch
 
 from oracle import muon_oracle as MO
-from tests.golden.cases import (MUON_LR, MUON_MOMENTUM, MUON_NS_CASES, MUON_STEP_CASES, muon_ns_input,
+from tests.golden.cases import (MUON_LR, MUON_MODE_CASES, MUON_MOMENTUM, MUON_NS_CASES, MUON_STEP_CASES, muon_ns_input,
                                 muon_step_inputs)
 
 pytestmark = pytest.mark.gpu
@@ -110,7 +110,7 @@ def test_layer_sized_stack_step_and_padding(pkg):
 
 def test_rejected_options(pkg):
     p = torch.nn.Parameter(torch.zeros(2, 64, 64, device=DEV))
-    for kw in (dict(scale_mode="normuon"), dict(aurora_k=2), dict(ns_dtype=torch.float16), dict(use_graph=True),
+    for kw in (dict(scale_mode="no_such_mode"), dict(aurora_k=0), dict(ns_dtype=torch.float16),
                dict(xorth_post=0.1), dict(spectral_wd=0.1)):
         with pytest.raises(ValueError):
             pkg.FusedMuon([p], **kw)
@@ -203,3 +203,94 @@ def test_state_dict_round_trip_with_fp32_master_weights(pkg):
     p_c.grad = grads[0].to(DEV)
     with pytest.raises(ValueError):
         opt_c.step()
+
+
+@pytest.mark.parametrize("name", list(MUON_MODE_CASES))
+@pytest.mark.parametrize("pdtype", [torch.float32, torch.bfloat16])
+def test_per_row_modes_and_two_pass_aurora_against_reference_golden(pkg, gold, name, pdtype):
+    """normuon, aurora_ema, aurora_ema_v2 and aurora with two passes: three steps against the reference's own
+    FusedMuon (fp32 iteration) and against the oracle with a bf16 iteration; the per-row EMA state against both."""
+    shape, _seed, mode, nesterov, wd, steps, k = MUON_MODE_CASES[name]
+    p0, grads = muon_step_inputs(name)
+    p = torch.nn.Parameter(p0.to(DEV).to(pdtype))
+    opt = pkg.FusedMuon([p], lr=MUON_LR, momentum=MUON_MOMENTUM, nesterov=nesterov, weight_decay=wd, scale_mode=mode,
+                        aurora_k=k)
+    po, mo, vo = p0.to(pdtype).clone(), torch.zeros_like(p0, dtype=torch.bfloat16), torch.zeros(shape[0], shape[1])
+    for i in range(steps):
+        p.grad = grads[i].to(DEV).to(pdtype)
+        opt.step()
+        MO.muon_step(po, grads[i].to(pdtype), mo, MUON_LR, MUON_MOMENTUM, nesterov, wd, ns_dtype=torch.bfloat16,
+                     scale_mode=mode, aurora_k=k or 1, scale_v=vo)
+    torch.cuda.synchronize(); pkg.check_status()
+    start = p0.to(pdtype).float()
+    moved = p.detach().float().cpu() - start
+    ref_moved = torch.from_numpy(gold[f"step_{name}_p"]) - p0
+    tol = STEP_TOL if pdtype == torch.float32 else 2 * STEP_TOL
+    assert MO.rel_l2(moved, ref_moved) < tol
+    assert MO.rel_l2(moved, po.float() - start) < tol
+    if f"step_{name}_v" in gold.files:
+        v = opt.state[p]["scale_v"].cpu()
+        assert v.dtype == torch.float32 and v.shape == (shape[0], shape[1])
+        assert MO.rel_l2(v, torch.from_numpy(gold[f"step_{name}_v"])) < 5e-2
+        assert MO.rel_l2(v, vo) < 5e-2
+
+
+@pytest.mark.parametrize("mode", ["polar", "aurora", "normuon", "aurora_ema"])
+def test_graph_mode_replays_the_eager_step_bit_for_bit(pkg, mode):
+    """use_graph: gradients are staged eagerly, the rest of the step is captured after the warm-up steps and replayed;
+    parameters and state end exactly where the eager optimizer puts them, also when the gradient tensors are new
+    objects every step."""
+    g = torch.Generator().manual_seed(29)
+    shapes = [(3, 128, 192), (192, 128), (3, 128, 192)]
+    init = [torch.randn(*s, generator=g) * 0.02 for s in shapes]
+    grads = [[torch.randn(*s, generator=g) for s in shapes] for _ in range(6)]
+
+    def run(use_graph):
+        ps = [torch.nn.Parameter(t.clone().to(DEV)) for t in init]
+        opt = pkg.FusedMuon(ps, lr=0.01, weight_decay=0.1, scale_mode=mode, use_graph=use_graph, graph_warmup=2)
+        for step_grads in grads:
+            for p, gr in zip(ps, step_grads):
+                p.grad = gr.to(DEV)                 # a new tensor every step, as after zero_grad(set_to_none=True)
+            opt.step()
+        torch.cuda.synchronize(); pkg.check_status()
+        return opt, [p.detach().clone() for p in ps], [opt.state[p]["muon_mom"].clone() for p in ps]
+
+    opt_g, pg, mg = run(True)
+    _, pe, me = run(False)
+    assert opt_g._graph is not None and not opt_g._graph_failed          # it did capture
+    for a, b in zip(pg + mg, pe + me):
+        assert torch.equal(a, b)
+
+
+def test_distributed_muon_on_one_rank_equals_fused_muon(pkg):
+    """With a process group of one rank DistributedMuon owns every parameter: momentum, update and apply go through
+    its own code path (update materialised, broadcast, row-update kernel) and must land where FusedMuon lands."""
+    import torch.distributed as dist
+    import socket
+    if not dist.is_initialized():
+        s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+        dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1,
+                                device_id=torch.device("cuda", 0))
+    try:
+        g = torch.Generator().manual_seed(31)
+        shapes = [(2, 128, 192), (192, 128), (64, 64)]
+        init = [torch.randn(*s, generator=g) * 0.02 for s in shapes]
+        grads = [[torch.randn(*s, generator=g) for s in shapes] for _ in range(3)]
+        for mode in ("polar", "aurora", "normuon"):
+            outs = []
+            for cls in (pkg.FusedMuon, pkg.DistributedMuon):
+                ps = [torch.nn.Parameter(t.clone().to(DEV)) for t in init]
+                opt = cls(ps, lr=0.01, weight_decay=0.1, scale_mode=mode)
+                for step_grads in grads:
+                    for p, gr in zip(ps, step_grads):
+                        p.grad = gr.to(DEV)
+                    opt.step()
+                torch.cuda.synchronize(); pkg.check_status()
+                outs.append([p.detach().clone() for p in ps])
+            for a, b, t0 in zip(outs[0], outs[1], init):
+                # same kernels, same roundings; the decay-and-add is one fused expression in both paths
+                assert MO.rel_l2((b.cpu() - t0), (a.cpu() - t0)) < 1e-3, mode
+        with pytest.raises(NotImplementedError):
+            pkg.DistributedMuon([torch.nn.Parameter(init[0].to(DEV))], scale_mode="aurora_ema")
+    finally:
+        dist.destroy_process_group()

@@ -50,10 +50,12 @@ def test_muon_rejects_what_is_not_built_and_cpu_tensors():
     import pytest
     pkg = importlib.import_module(PKG)
     p = torch.nn.Parameter(torch.zeros(2, 64, 64))
-    for kw in (dict(scale_mode="normuon"), dict(scale_mode="aurora_ema"), dict(aurora_k=2), dict(ns_dtype=torch.float32),
-               dict(use_graph=True), dict(xorth_post=0.1), dict(spectral_wd=0.1)):
+    for kw in (dict(scale_mode="no_such_mode"), dict(aurora_k=0), dict(ns_dtype=torch.float32),
+               dict(xorth_post=0.1), dict(spectral_wd=0.1)):
         with pytest.raises(ValueError):
             pkg.FusedMuon([p], **kw)
+    for mode in ("polar", "aurora", "normuon", "aurora_ema", "aurora_ema_v2"):     # every mode of the reference
+        assert pkg.FusedMuon([p], scale_mode=mode, aurora_k=2, use_graph=True).scale_mode == mode
     opt = pkg.FusedMuon([p], lr=0.1, scale_mode="polar")
     opt.step()                                   # no gradient: nothing is stepped, nothing is launched
     assert float(p.detach().abs().sum()) == 0.0 and not opt.state[p]

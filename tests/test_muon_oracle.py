@@ -53,4 +53,23 @@ def test_step_matches_reference(name):
 def test_unknown_scale_mode_is_rejected():
     p = torch.zeros(1, 8, 8)
     with pytest.raises(ValueError):
-        MO.muon_step(p, p.clone(), p.clone(), 0.1, scale_mode="normuon")
+        MO.muon_step(p, p.clone(), p.clone(), 0.1, scale_mode="no_such_mode")
+
+
+from tests.golden.cases import MUON_MODE_CASES   # noqa: E402
+
+
+@pytest.mark.parametrize("name", list(MUON_MODE_CASES))
+def test_per_row_modes_and_two_pass_aurora_match_reference(name):
+    """normuon, aurora_ema, aurora_ema_v2 and aurora with two passes against the reference's FusedMuon (fp32)."""
+    shape, _seed, mode, nesterov, wd, steps, k = MUON_MODE_CASES[name]
+    p0, grads = muon_step_inputs(name)
+    p, mom = p0.clone(), torch.zeros_like(p0)
+    v = torch.zeros(shape[0], shape[1])
+    for i in range(steps):
+        MO.muon_step(p, grads[i], mom, MUON_LR, MUON_MOMENTUM, nesterov, wd, ns_dtype=torch.float32, scale_mode=mode,
+                     aurora_k=k or 1, scale_v=v)
+    assert (p - torch.from_numpy(GOLD[f"step_{name}_p"])).abs().max().item() < 1e-5
+    assert MO.rel_l2(mom, torch.from_numpy(GOLD[f"step_{name}_mom"])) < 1e-6
+    if f"step_{name}_v" in GOLD.files:
+        assert MO.rel_l2(v, torch.from_numpy(GOLD[f"step_{name}_v"])) < 1e-5

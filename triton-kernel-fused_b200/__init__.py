@@ -11,7 +11,7 @@ from . import ops
 from .ops import TILE_M
 from .ep import ExpertParallelMoELayer, ep_moe
 from . import muon
-from .muon import FusedMuon, newton_schulz
+from .muon import DistributedMuon, FusedMuon, newton_schulz
 
 __all__ = ["moe", "moe_grouped", "moe_per_expert", "GROUPED_MIN_TOKENS", "fused_mlp_router", "fused_router", "FusedConvRouter",
-           "FusedMLPRouter", "router_bias_update", "MoELayer", "moe_mxfp8", "ExpertParallelMoELayer", "ep_moe", "FusedMuon", "newton_schulz", "muon", "ops", "build", "lib", "check_status"]
+           "FusedMLPRouter", "router_bias_update", "MoELayer", "moe_mxfp8", "ExpertParallelMoELayer", "ep_moe", "FusedMuon", "DistributedMuon", "newton_schulz", "muon", "ops", "build", "lib", "check_status"]

@@ -87,6 +87,8 @@ _SIGNATURES = {
     "b200moe_muon_row_sumsq": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "b200moe_muon_prescale_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_float, c_float, c_void_p, c_void_p,
                                            c_void_p]),
+    "b200moe_muon_scale_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "b200moe_muon_update_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_float, c_float, c_void_p, c_int, c_void_p]),
     "b200moe_muon_normalise_pack": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_float,
                                             c_void_p, c_void_p, c_void_p]),
     "b200moe_expert_linear_axpby": (c_int, [c_void_p] * 3 + [c_float] * 3 + [c_int] + [c_void_p] * 2 +

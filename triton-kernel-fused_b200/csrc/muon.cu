@@ -103,6 +103,67 @@ __global__ void __launch_bounds__(256) muon_prescale_rows_kernel(const uint4* __
   }
 }
 
+// out[row, :] = bf16(x[row, :] * mult[row]) and the sum of squares of the rounded row: the row prescale of the
+// reference's `aurora_ema` mode (one combined multiplier per row, kernels/muon/muon_scaling.py:141-142).
+__global__ void __launch_bounds__(256) muon_scale_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ mult,
+                                                              long long rows, int vec_per_row, uint4* __restrict__ out,
+                                                              float* __restrict__ rowss_out) {
+  const int lane = threadIdx.x & 31;
+  for (long long row = blockIdx.x * 8LL + (threadIdx.x >> 5); row < rows; row += gridDim.x * 8LL) {
+    const float s = mult[row];
+    const uint4* src = x + row * vec_per_row;
+    uint4* dst = out + row * vec_per_row;
+    float ss = 0.0f;
+    for (int c = lane; c < vec_per_row; c += 32) {
+      float f[8];
+      unpack8(src[c], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        f[j] = round_bf16(f[j] * s);
+        ss += f[j] * f[j];
+      }
+      dst[c] = pack8(f);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if (lane == 0) rowss_out[row] = ss;
+  }
+}
+
+// p[row, :] = decay * p[row, :] + alpha * bf16(x[row, :] * mult[row]): the weight update of the per-row scale modes
+// (`normuon`, `aurora_ema_v2`: kernels/muon/muon_scaling.py:166-195, kernels/sm75/muon.py:381,431-434), x in the
+// parameters' own (rows, cols) layout.  One warp per row.
+template <bool kPF32>
+__global__ void __launch_bounds__(256) muon_update_rows_kernel(const uint4* __restrict__ x, const float* __restrict__ mult,
+                                                               long long rows, int vec_per_row, float decay, float alpha,
+                                                               void* p) {
+  const int lane = threadIdx.x & 31;
+  for (long long row = blockIdx.x * 8LL + (threadIdx.x >> 5); row < rows; row += gridDim.x * 8LL) {
+    const float s = mult[row];
+    const uint4* src = x + row * vec_per_row;
+    for (int c = lane; c < vec_per_row; c += 32) {
+      float o[8], w[8];
+      unpack8(src[c], o);
+      const long long pi = (row * vec_per_row + c) * 8;
+      if (kPF32) {
+        float4* pp = reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + pi);
+        const float4 a = pp[0], b = pp[1];
+        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+#pragma unroll
+        for (int t = 0; t < 8; ++t) w[t] = w[t] * decay + alpha * round_bf16(o[t] * s);
+        pp[0] = make_float4(w[0], w[1], w[2], w[3]);
+        pp[1] = make_float4(w[4], w[5], w[6], w[7]);
+      } else {
+        uint4* pp = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p) + pi);
+        unpack8(*pp, w);
+#pragma unroll
+        for (int t = 0; t < 8; ++t) w[t] = round_bf16(w[t] * decay) + alpha * round_bf16(o[t] * s);
+        *pp = pack8(w);
+      }
+    }
+  }
+}
+
 // norms[e] = bf16(max(sqrt(sum_i rowss[e, i]), eps)) as a float: the per-matrix Frobenius norm the iteration divides
 // by (kernels/sm75/muon.py:78,82).  One CTA per matrix, fixed summation order (reruns are bit-identical).
 __global__ void __launch_bounds__(256) muon_stack_norms_kernel(const float* __restrict__ rowss, int r, float eps,
@@ -379,6 +440,35 @@ int b200moe_muon_prescale_rows(const void* x, const float* rowss, int64_t rows, 
   if (rows == 0) return 0;
   muon_prescale_rows_kernel<<<stream_grid(rows, 8), 256, 0, (cudaStream_t)stream>>>(
       (const uint4*)x, rowss, rows, (int)(cols / 8), tgt, eps, (uint4*)out, rowss_out);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_muon_scale_rows(const void* x, const float* mult, int64_t rows, int64_t cols, void* out, float* rowss_out,
+                            b200moe_stream_t stream) {
+  B200_CHECK_ARG(x && mult && out && rowss_out, B200MOE_E_NULL, "muon_scale_rows: null pointer");
+  B200_CHECK_ARG(rows >= 0 && cols > 0 && cols % 8 == 0 && cols < (1LL << 24), B200MOE_E_BAD_SHAPE,
+                 "muon_scale_rows: cols = %lld must be a multiple of 8", (long long)cols);
+  B200_CHECK_ARG(aligned16(x) && aligned16(out), B200MOE_E_ALIGN, "muon_scale_rows: pointers must be 16-byte aligned");
+  if (rows == 0) return 0;
+  muon_scale_rows_kernel<<<stream_grid(rows, 8), 256, 0, (cudaStream_t)stream>>>((const uint4*)x, mult, rows, (int)(cols / 8),
+                                                                                 (uint4*)out, rowss_out);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int b200moe_muon_update_rows(const void* x, const float* mult, int64_t rows, int64_t cols, float decay, float alpha, void* p,
+                             int p_f32, b200moe_stream_t stream) {
+  B200_CHECK_ARG(x && mult && p, B200MOE_E_NULL, "muon_update_rows: null pointer");
+  B200_CHECK_ARG(rows >= 0 && cols > 0 && cols % 8 == 0 && cols < (1LL << 24), B200MOE_E_BAD_SHAPE,
+                 "muon_update_rows: cols = %lld must be a multiple of 8", (long long)cols);
+  B200_CHECK_ARG(aligned16(x) && aligned16(p), B200MOE_E_ALIGN, "muon_update_rows: pointers must be 16-byte aligned");
+  if (rows == 0) return 0;
+  const int grid = stream_grid(rows, 8);
+  if (p_f32)
+    muon_update_rows_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)x, mult, rows, (int)(cols / 8), decay, alpha, p);
+  else
+    muon_update_rows_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)x, mult, rows, (int)(cols / 8), decay, alpha, p);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
