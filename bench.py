@@ -146,7 +146,8 @@ def _ep_settings():
     """Transport and exchange of the expert-parallel layer in this run (environment overrides for A/B runs)."""
     return dict(transport=os.environ.get("B200MOE_EP_TRANSPORT", "p2p"), exchange=os.environ.get("B200MOE_EP_EXCHANGE", "push"),
                 overlap_chunks=int(os.environ.get("B200MOE_EP_CHUNKS", "1")),
-                reserved_sms=int(os.environ.get("B200MOE_EP_RESERVED_SMS", "12")))
+                reserved_sms=int(os.environ.get("B200MOE_EP_RESERVED_SMS", "16")),
+                expert_groups=int(os.environ.get("B200MOE_EP_GROUPS", "1")))
 
 
 def _parallelism_label(n_gpus):

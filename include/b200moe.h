@@ -148,10 +148,14 @@ int b200moe_expert_gate_up_swiglu(const void* x_s, const void* gate_up_proj,
                                   void* inter, int32_t* status, b200moe_stream_t stream);
 /* The same GEMM with a per-expert activation code (act_codes (E) int32: 0 SiLU, 1 ReLU^2, 5 SiTU = tanh(g)*sigmoid(g),
  * the parameter-free codes of _act_eager, kernels/sm75/moe.py:859-881, that need no row reduction) applied in the
- * epilogue in place of the separate _glu_fwd launch (kernels/sm75/moe.py:767); act_codes NULL = all SiLU. */
+ * epilogue in place of the separate _glu_fwd launch (kernels/sm75/moe.py:767); act_codes NULL = all SiLU.
+ * [row_lo, row_hi): only the row tiles of these rows are computed (multiples of B200MOE_TILE_M inside rows_cap;
+ * 0, 0 = every row): the expert-parallel layer runs the rows of one group of experts while the rows of the next
+ * group are still arriving.  No reference counterpart for the window. */
 int b200moe_expert_gate_up_act(const void* x_s, const void* gate_up_proj, const int32_t* act_codes,
-                               const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E, int64_t H,
-                               int64_t I, void* gate_up, void* inter, int32_t* status, b200moe_stream_t stream);
+                               const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int64_t row_lo,
+                               int64_t row_hi, int E, int64_t H, int64_t I, void* gate_up, void* inter,
+                               int32_t* status, b200moe_stream_t stream);
 /* Generic grouped products over the padded rows (the two entry points after them are special cases):
  * linear:   out (rows,N) = a (rows,K) * W[e]^T, W (E,N,K)   -- kernels/sm75/moe.py:765,770 (x @ W[e].t())
  * linear_t: out (rows,N) = a (rows,K) * W[e],   W (E,K,N)   -- kernels/sm75/moe.py:807,822 (g @ W[e]) */
@@ -181,11 +185,12 @@ int b200moe_expert_down_dgrad_glu(const void* grad_eo, const void* down_proj, co
                                   int64_t rows_cap, int E, int64_t H, int64_t I, void* grad_gate_up,
                                   int32_t* status, b200moe_stream_t stream);
 /* The same with per-expert activation codes (see b200moe_expert_gate_up_act): the backward of _glu_bwd
- * (kernels/sm75/moe.py:187-232) for codes 0, 1 and 5 without parameters, fused in the epilogue. */
+ * (kernels/sm75/moe.py:187-232) for codes 0, 1 and 5 without parameters, fused in the epilogue; row window as for
+ * b200moe_expert_gate_up_act. */
 int b200moe_expert_down_dgrad_act(const void* grad_eo, const void* down_proj, const void* gate_up,
                                   const int32_t* act_codes, const int32_t* tile_expert, const int32_t* poffs,
-                                  int64_t rows_cap, int E, int64_t H, int64_t I, void* grad_gate_up, int32_t* status,
-                                  b200moe_stream_t stream);
+                                  int64_t rows_cap, int64_t row_lo, int64_t row_hi, int E, int64_t H, int64_t I,
+                                  void* grad_gate_up, int32_t* status, b200moe_stream_t stream);
 /* Replaces grad_x_s = grad_gate_up @ W_gu[e] (kernels/sm75/moe.py:612, :822). */
 int b200moe_expert_gate_up_dgrad(const void* grad_gate_up, const void* gate_up_proj,
                                  const int32_t* tile_expert, const int32_t* poffs,
@@ -290,12 +295,14 @@ int b200moe_combine_bwd(const void* grad_out, const void* eo, const float* w,
  * THIS rank's block of expert e inside e's owner. */
 int b200moe_ep_plan(const int32_t* counts_all, int W, int rank, int E, int32_t* poffs_l, int32_t* counts_l,
                     int32_t* tile_expert_l, int32_t* src_base, int32_t* dest_base, b200moe_stream_t stream);
-/* ep_local_rows: the number of routed rows that arrive on this rank (sum over the sources of counts_all (W,E) for
- * the local experts), written to `host_word`, a word of PINNED HOST memory (cudaHostAlloc / cudaHostRegister; the
- * call fails with B200MOE_E_CUDA and launches nothing otherwise).  The host sizes its buffers from it after waiting
- * for an event recorded behind this call; no device-to-host copy is involved, so the read does not queue behind
- * transfers that occupy the copy engines.  No reference counterpart. */
-int b200moe_ep_local_rows(const int32_t* counts_all, int W, int rank, int E, int32_t* host_word,
+/* ep_local_rows: host_words[0] = the number of routed rows that arrive on this rank (sum over the sources of
+ * counts_all (W,E) for the local experts); host_words[1 + j], j < E/W = the row at which local expert j ends in the
+ * padded layout (poffs_l[j + 1] of b200moe_ep_plan).  `host_words`: 1 + E/W words of PINNED HOST memory
+ * (cudaHostAlloc / cudaHostRegister; the call fails with B200MOE_E_CUDA and launches nothing otherwise).  The host
+ * sizes its buffers, and splits the local experts into groups of about equal rows, after waiting for an event
+ * recorded behind this call; no device-to-host copy is involved, so the read does not queue behind transfers that
+ * occupy the copy engines.  No reference counterpart. */
+int b200moe_ep_local_rows(const int32_t* counts_all, int W, int rank, int E, int32_t* host_words,
                           b200moe_stream_t stream);
 /* ep_publish: this rank's routing tables -- idx (M) int64, slot_pos (M) int32, w (M) fp32 routing weights, offs
  * (E+1) int32 -- stored into slot `rank` of the replica arrays of EVERY rank (tab_*_peers[r] = base of rank r's
@@ -323,11 +330,14 @@ int b200moe_ep_barrier(const void* const* flags_peers, int W, int rank, uint32_t
  * src_base[s][e_local] + slot_pos - offs[e]; the token row is read from the peer ONCE however many of its
  * experts live here.  Pad rows are zeroed.  T is the token count of every rank.  row_rank / row_slot (nullable,
  * both or none): for every row the home rank and the slot t*k+j it came from (-1 / 0 for pad rows), i.e. where
- * b200moe_expert_linear_push sends that row's result. */
+ * b200moe_expert_linear_push sends that row's result.  [e_lo, e_hi): the local experts whose rows this launch fills
+ * (0, E/W = all), so that the rows of one group of experts can arrive while the GEMMs of another group run;
+ * max_sms > 0 limits the launch to that many SMs' worth of CTAs (a launch beside a persistent GEMM that leaves
+ * them free, see b200moe_set_reserved_sms), 0 = all SMs. */
 int b200moe_ep_gather_pull(const void* const* x_peers, const void* const* idx_peers, const void* const* spos_peers,
                            const void* const* offs_peers, const int32_t* counts_l, const int32_t* poffs_l,
-                           const int32_t* src_base, int W, int rank, int E, int64_t T, int k, int64_t H, void* x_s,
-                           int32_t* row_rank, int32_t* row_slot, b200moe_stream_t stream);
+                           const int32_t* src_base, int W, int rank, int E, int e_lo, int e_hi, int max_sms, int64_t T,
+                           int k, int64_t H, void* x_s, int32_t* row_rank, int32_t* row_slot, b200moe_stream_t stream);
 /* home side: out[t] = sum_j w[t,j] * rows_peers[owner][dest_base[e] + slot_pos[s] - offs[e]] (w NULL = 1),
  * summed in slot order; the rows arrive by bulk copies into a shared-memory ring (one CTA per SM, on at most
  * the SMs b200moe_set_exchange_sms allows).  When gw_peers / grad_w are given, grad_w[s] is fetched from the
@@ -337,12 +347,14 @@ int b200moe_ep_combine_pull(const void* const* rows_peers, const float* w, const
                             int64_t T, int k, int64_t H, void* out, const void* const* gw_peers, float* grad_w,
                             int32_t* status, b200moe_stream_t stream);
 /* owner side, backward, same traversal: grad_eo[row] = w_peers[s][t,j] * go_peers[s][t] (grad_out read once per
- * token and owner); gw_rows[row] = <go, eo[row]> (eo and gw_rows both NULL: no dot products); pad rows zero. */
+ * token and owner); gw_rows[row] = <go, eo[row]> (eo and gw_rows both NULL: no dot products); pad rows zero.
+ * e_lo, e_hi, max_sms as for b200moe_ep_gather_pull. */
 int b200moe_ep_combine_bwd_pull(const void* const* go_peers, const void* const* w_peers,
                                 const void* const* idx_peers, const void* const* spos_peers,
                                 const void* const* offs_peers, const void* eo, const int32_t* counts_l,
-                                const int32_t* poffs_l, const int32_t* src_base, int W, int rank, int E, int64_t T,
-                                int k, int64_t H, void* grad_eo, float* gw_rows, b200moe_stream_t stream);
+                                const int32_t* poffs_l, const int32_t* src_base, int W, int rank, int E, int e_lo,
+                                int e_hi, int max_sms, int64_t T, int k, int64_t H, void* grad_eo, float* gw_rows,
+                                b200moe_stream_t stream);
 
 /* out[t*k+j] = <grad_out[t], rows[t*k+j]> (fp32): the gradient of the routing weights at the home rank when the
  * expert outputs of its tokens were pushed to it in slot order.  No reference counterpart as a kernel (the

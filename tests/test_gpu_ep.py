@@ -33,10 +33,12 @@ def _worker(rank, world, port, cfg, transport, q):
         sl = slice(rank * Tl, (rank + 1) * Tl)
         # "p2p" = push exchange, "p2p-pull" = pull exchange, "p2p-pull+24" = pull with the last backward pull
         # overlapped on 24 SMs
+        # "p2p/3" = push exchange with the local experts pipelined in 3 groups
+        transport, _, groups = transport.partition("/")
         transport, _, sms = transport.partition("+")
         transport, _, exch = transport.partition("-")
         layer = pkg.ExpertParallelMoELayer(H, I, E, top_k=k, transport=transport, reserved_sms=int(sms or 0),
-                                           exchange=exch or "push").to(dev).to(torch.bfloat16)
+                                           exchange=exch or "push", expert_groups=int(groups or 1)).to(dev).to(torch.bfloat16)
         with torch.no_grad():
             layer.gate.weight.copy_(inp["gate_weight"])
             layer.gate_up_proj.copy_(inp["gate_up"][rank * El:(rank + 1) * El])
@@ -59,7 +61,7 @@ def _worker(rank, world, port, cfg, transport, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport", ["nccl", "p2p", "p2p-pull", "p2p-pull+24"])
+@pytest.mark.parametrize("transport", ["nccl", "p2p", "p2p-pull", "p2p-pull+24", "p2p/2", "p2p+24/3"])
 @pytest.mark.parametrize("cfg", [(2048, 512, 16, 256, 4), (1024, 256, 64, 128, 8)])
 def test_expert_parallel_equals_single_gpu(pkg, cfg, transport):
     if torch.cuda.device_count() < 2:

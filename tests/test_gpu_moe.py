@@ -60,6 +60,36 @@ def test_forward_stages(pkg, T, H, E, I, k):
     assert (gu_d[:total].cpu()[pad] == 0).all() and (eo_d[:total].cpu()[pad] == 0).all()
 
 
+def test_row_windows_compose_to_the_whole_launch(pkg):
+    """gate/up + SwiGLU and dgrad(down) + GLU backward over two windows of rows (the expert-parallel layer runs groups
+    of experts this way) write exactly what one launch over all rows writes; a misaligned window is refused."""
+    T, H, E, I, k = 2048, 256, 8, 192, 2
+    inp = O.make_inputs(T, H, E, I, k, seed=23, bias_std=0.01, dtype=torch.bfloat16)
+    idx, w, _ = O.router_epilogue_fwd(inp["x"].float() @ inp["gate_weight"].float().t(), inp["bias"], k)
+    ops = pkg.ops
+    perm = ops.permute_build(idx.to(DEV), E)
+    xs = ops.gather_rows(inp["x"].to(DEV), perm)
+    gu_w, dn_w = inp["gate_up"].to(DEV), inp["down"].to(DEV)
+    gu_full, it_full = ops.expert_gate_up_swiglu(xs, gu_w, perm)
+    cut = int(perm.poffs[E // 2])                       # a tile-aligned expert boundary
+    total = int(perm.poffs[E])
+    gu_two, it_two = torch.zeros_like(gu_full), torch.zeros_like(it_full)
+    ops.expert_gate_up_swiglu(xs, gu_w, perm, out=(gu_two, it_two), rows=(0, cut))
+    assert (gu_two[cut:total] == 0).all()                # the first window leaves the other rows alone
+    ops.expert_gate_up_swiglu(xs, gu_w, perm, out=(gu_two, it_two), rows=(cut, perm.cap))
+    pkg.check_status()
+    assert torch.equal(gu_two[:total], gu_full[:total]) and torch.equal(it_two[:total], it_full[:total])
+    geo = torch.randn(perm.cap, H, device=DEV).to(torch.bfloat16)
+    gg_full = ops.expert_down_dgrad_glu(geo, dn_w, gu_full, perm)
+    gg_two = torch.zeros_like(gg_full)
+    ops.expert_down_dgrad_glu(geo, dn_w, gu_full, perm, out=gg_two, rows=(cut, perm.cap))
+    ops.expert_down_dgrad_glu(geo, dn_w, gu_full, perm, out=gg_two, rows=(0, cut))
+    pkg.check_status()
+    assert torch.equal(gg_two[:total], gg_full[:total])
+    with pytest.raises(ValueError):
+        ops.expert_gate_up_swiglu(xs, gu_w, perm, out=(gu_two, it_two), rows=(100, cut))
+
+
 @pytest.mark.parametrize("T,H,E,I,k", [(1024, 256, 8, 192, 2), (2048, 512, 16, 320, 4)])
 def test_backward_stages(pkg, T, H, E, I, k):
     inp = O.make_inputs(T, H, E, I, k, seed=22, bias_std=0.01, dtype=torch.bfloat16)

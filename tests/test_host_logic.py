@@ -146,3 +146,24 @@ def test_bf16_copies_of_frozen_stacks_are_reused_until_the_stack_changes():
     import gc
     gc.collect()
     assert len(moe_mod._BF16_COPIES) == n - 1             # freed with its tensor
+
+
+def test_expert_groups_split_local_experts_by_rows():
+    """The expert-parallel pipeline's grouping: consecutive experts, about equal padded rows, empty groups dropped,
+    every row in exactly one group."""
+    ep = importlib.import_module("triton-kernel-fused_b200.ep_p2p")
+    ends = [256, 512, 768, 1024, 1280, 1536, 1792, 2048]
+    assert ep.expert_groups(ends, 2) == [(0, 4, 0, 1024), (4, 8, 1024, 2048)]
+    assert ep.expert_groups(ends, 4) == [(0, 2, 0, 512), (2, 4, 512, 1024), (4, 6, 1024, 1536), (6, 8, 1536, 2048)]
+    assert ep.expert_groups(ends, 1) == [(0, 8, 0, 2048)]
+    # one expert holds nearly everything: the cut falls behind it, nothing is lost, nothing is empty
+    skew = [256, 256, 5120, 5376]
+    for n in (2, 3, 4, 7):
+        g = ep.expert_groups(skew, n)
+        assert g[0][0] == 0 and g[-1][1] == 4 and g[0][2] == 0 and g[-1][3] == 5376
+        assert all(a[1] == b[0] and a[3] == b[2] for a, b in zip(g, g[1:]))
+        assert all(r_hi > r_lo for _, _, r_lo, r_hi in g)
+    # experts without rows (ends repeat) and a rank without any row
+    assert ep.expert_groups([0, 0, 256, 256], 2) == [(0, 3, 0, 256)] or ep.expert_groups([0, 0, 256, 256], 2) == [(0, 4, 0, 256)]
+    assert ep.expert_groups([0, 0, 0, 0], 2) == []
+    assert ep.expert_groups([], 2) == []

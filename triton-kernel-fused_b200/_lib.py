@@ -49,8 +49,8 @@ _SIGNATURES = {
     "b200moe_permute_build_static": (c_int, [c_void_p, c_int64, c_int, c_int] + [c_void_p] * 8 + [c_void_p, c_void_p]),
     "b200moe_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p]),
     "b200moe_expert_gate_up_swiglu": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 4),
-    "b200moe_expert_gate_up_act": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 4),
-    "b200moe_expert_down_dgrad_act": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
+    "b200moe_expert_gate_up_act": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_int, c_int64, c_int64] + [c_void_p] * 4),
+    "b200moe_expert_down_dgrad_act": (c_int, [c_void_p] * 6 + [c_int64] * 3 + [c_int, c_int64, c_int64] + [c_void_p] * 3),
     "b200moe_expert_linear": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
     "b200moe_expert_linear_t": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
     "b200moe_glu_fwd_rows": (c_int, [c_void_p] * 5 + [c_int64, c_int64, c_void_p, c_void_p]),
@@ -75,12 +75,12 @@ _SIGNATURES = {
     "b200moe_ep_local_rows": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "b200moe_ep_publish": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int, c_int, c_int64, c_int] + [c_void_p] * 5),
     "b200moe_ep_barrier": (c_int, [c_void_p, c_int, c_int, ctypes.c_uint32, c_int64, c_void_p, c_void_p]),
-    "b200moe_ep_gather_pull": (c_int, [c_void_p] * 7 + [c_int, c_int, c_int, c_int64, c_int, c_int64] + [c_void_p] * 4),
+    "b200moe_ep_gather_pull": (c_int, [c_void_p] * 7 + [c_int] * 6 + [c_int64, c_int, c_int64] + [c_void_p] * 4),
     "b200moe_slot_dots": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_void_p, c_void_p]),
     "b200moe_expert_linear_push": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64] +
                                    [c_void_p] * 5),
     "b200moe_ep_combine_pull": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int64, c_int, c_int64] + [c_void_p] * 5),
-    "b200moe_ep_combine_bwd_pull": (c_int, [c_void_p] * 9 + [c_int, c_int, c_int, c_int64, c_int, c_int64] + [c_void_p] * 3),
+    "b200moe_ep_combine_bwd_pull": (c_int, [c_void_p] * 9 + [c_int] * 6 + [c_int64, c_int, c_int64] + [c_void_p] * 3),
     "b200moe_combine": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64, c_void_p, c_void_p]),
     "b200moe_combine_bwd": (c_int, [c_void_p] * 5 + [c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "b200moe_muon_momentum": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_float, c_int, c_void_p]),

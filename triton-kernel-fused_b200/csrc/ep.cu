@@ -77,26 +77,32 @@ ep_plan_kernel(const int* __restrict__ counts_all, int W, int rank, int E, int* 
   }
 }
 
-// Rows that arrive on this rank (the sum of every source's counts for the local experts), stored straight into a
-// word of pinned host memory: the host learns how large its buffers must be by waiting for this kernel, without a
-// device-to-host copy that would queue behind whatever transfer the copy engines are busy with.
+// Rows that arrive on this rank, stored straight into pinned host memory: host_words[0] = the sum of every source's
+// counts for the local experts, host_words[1 + j] = the padded row at which local expert j ENDS (the padded offsets
+// b200moe_ep_plan computes on the device).  The host learns how large its buffers must be, and where a group of
+// experts starts, by waiting for this kernel, without a device-to-host copy that would queue behind whatever
+// transfer the copy engines are busy with.
 __global__ void __launch_bounds__(B200MOE_MAX_EXPERTS)
-ep_local_rows_kernel(const int* __restrict__ counts_all, int W, int rank, int E, volatile int* __restrict__ host_word) {
-  __shared__ int s_sum[B200MOE_MAX_EXPERTS / 32];
+ep_local_rows_kernel(const int* __restrict__ counts_all, int W, int rank, int E, volatile int* __restrict__ host_words) {
+  __shared__ int s_cnt[B200MOE_MAX_EXPERTS];
   const int El = E / W;
+  const int j = threadIdx.x;
   int v = 0;
-  if (static_cast<int>(threadIdx.x) < El)
-    for (int s = 0; s < W; ++s) v += counts_all[s * E + rank * El + threadIdx.x];
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-  if ((threadIdx.x & 31) == 0) s_sum[threadIdx.x >> 5] = v;
+  if (j < El)
+    for (int s = 0; s < W; ++s) v += counts_all[s * E + rank * El + j];
+  s_cnt[j] = v;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int tot = 0;
-    for (int i = 0; i < B200MOE_MAX_EXPERTS / 32; ++i) tot += s_sum[i];
-    *host_word = tot;
-    __threadfence_system();
+  if (j < El) {   // El <= 256 terms per thread: not worth a scan
+    int end = 0;
+    for (int i = 0; i <= j; ++i) end += ((s_cnt[i] + B200MOE_TILE_M - 1) / B200MOE_TILE_M) * B200MOE_TILE_M;
+    host_words[1 + j] = end;
   }
+  if (j == 0) {
+    int tot = 0;
+    for (int i = 0; i < El; ++i) tot += s_cnt[i];
+    host_words[0] = tot;
+  }
+  __threadfence_system();
 }
 
 // Every rank sends its routing tables (expert index, position inside the expert segment and routing weight of each
@@ -132,12 +138,14 @@ __device__ __forceinline__ unsigned local_rows_of_token(const long long* __restr
                                                         const int* __restrict__ spos_s,
                                                         const int* __restrict__ offs_s,
                                                         const int* __restrict__ src_base, int s, long long t, int k,
-                                                        int rank, int El, int lane, int& row) {
+                                                        int rank, int El, int e_lo, int e_hi, int lane, int& row) {
   bool local = false;
   row = 0;
   if (lane < k) {
     const long long ev = idx_s[t * k + lane];
-    if (ev >= 0 && ev / El == rank) {   // an index below 0 or past the last expert belongs to no rank
+    // an index below 0 or past the last expert belongs to no rank; [e_lo, e_hi) = the local experts this launch serves
+    if (ev >= 0 && ev / El == rank && ev - static_cast<long long>(rank) * El >= e_lo &&
+        ev - static_cast<long long>(rank) * El < e_hi) {
       const int e = static_cast<int>(ev);
       const int sp = spos_s[t * k + lane];
       if (sp >= 0) {                    // -1: the source's permutation gave the slot no row
@@ -152,8 +160,8 @@ __device__ __forceinline__ unsigned local_rows_of_token(const long long* __restr
 // pad rows [poffs[j] + counts[j], poffs[j+1]) of every local expert, one warp per row
 template <typename F>
 __device__ __forceinline__ void for_each_pad_row(const int* __restrict__ counts_l, const int* __restrict__ poffs_l,
-                                                 int El, long long warp0, long long nwarps, F f) {
-  for (int j = 0; j < El; ++j) {
+                                                 int e_lo, int e_hi, long long warp0, long long nwarps, F f) {
+  for (int j = e_lo; j < e_hi; ++j) {
     const int p0 = poffs_l[j] + counts_l[j], p1 = poffs_l[j + 1];
     for (long long r = p0 + warp0; r < p1; r += nwarps) f(r);
   }
@@ -161,12 +169,16 @@ __device__ __forceinline__ void for_each_pad_row(const int* __restrict__ counts_
 
 // One warp per (source rank, token): the token row is loaded once (from the peer's x) and stored to each of
 // its rows here.  Tasks are numbered token-major so that neighbouring warps read from different peers.
-__global__ void __launch_bounds__(256)
+// THREADS = 256 for a launch over the whole GPU; 1024 when the launch is confined to a few SMs beside a persistent
+// GEMM (one CTA per SM: a GEMM CTA takes a whole SM's shared memory, so the two never share an SM, and a pull of
+// `n` CTAs takes at most `n` SMs away from the GEMM whichever of the two is placed first)
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
 ep_gather_pull_kernel(const __grid_constant__ PeerPtrs x_peers, const __grid_constant__ PeerPtrs idx_peers,
                       const __grid_constant__ PeerPtrs spos_peers, const __grid_constant__ PeerPtrs offs_peers,
                       const int* __restrict__ counts_l, const int* __restrict__ poffs_l,
-                      const int* __restrict__ src_base, int W, int rank, int El, long long T, int k, int vec_per_row,
-                      uint4* __restrict__ x_s, int* __restrict__ row_rank, int* __restrict__ row_slot) {
+                      const int* __restrict__ src_base, int W, int rank, int El, int e_lo, int e_hi, long long T, int k,
+                      int vec_per_row, uint4* __restrict__ x_s, int* __restrict__ row_rank, int* __restrict__ row_slot) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
@@ -177,7 +189,7 @@ ep_gather_pull_kernel(const __grid_constant__ PeerPtrs x_peers, const __grid_con
     const unsigned mask = local_rows_of_token(reinterpret_cast<const long long*>(idx_peers.p[s]),
                                               reinterpret_cast<const int*>(spos_peers.p[s]),
                                               reinterpret_cast<const int*>(offs_peers.p[s]), src_base, s, t, k, rank,
-                                              El, lane, row);
+                                              El, e_lo, e_hi, lane, row);
     if (mask == 0u) continue;
     if (row_rank != nullptr && ((mask >> lane) & 1u)) {   // where the result rows of this row go back to
       row_rank[row] = s;
@@ -199,7 +211,7 @@ ep_gather_pull_kernel(const __grid_constant__ PeerPtrs x_peers, const __grid_con
       }
     }
   }
-  for_each_pad_row(counts_l, poffs_l, El, warp0, nwarps, [&](long long r) {
+  for_each_pad_row(counts_l, poffs_l, e_lo, e_hi, warp0, nwarps, [&](long long r) {
     uint4* dst = x_s + r * vec_per_row;
     for (int c = lane; c < vec_per_row; c += 32) dst[c] = make_uint4(0u, 0u, 0u, 0u);
     if (row_rank != nullptr && lane == 0) {
@@ -382,12 +394,15 @@ ep_pull_row_scalars_kernel(const __grid_constant__ PeerPtrs gw_peers, const long
 
 // One warp per (source rank, token): grad_out of the token is loaded once from the peer; for each of its
 // rows r here grad_eo[r] = grad_out * w_peer[slot] and gw_rows[r] = <grad_out, eo[r]> (fp32); pad rows zero.
-__global__ void __launch_bounds__(256, 3)
+// DOTS = false: no row dot products (eo ignored), twice the loads in flight per lane (KB = 8); THREADS as for
+// ep_gather_pull_kernel.
+template <int THREADS, int MINB, bool DOTS, int KB>
+__global__ void __launch_bounds__(THREADS, MINB)
 ep_combine_bwd_pull_kernel(const __grid_constant__ PeerPtrs go_peers, const __grid_constant__ PeerPtrs w_peers,
                            const __grid_constant__ PeerPtrs idx_peers, const __grid_constant__ PeerPtrs spos_peers,
                            const __grid_constant__ PeerPtrs offs_peers, const uint4* __restrict__ eo, const int* __restrict__ counts_l,
                            const int* __restrict__ poffs_l, const int* __restrict__ src_base, int W, int rank, int El,
-                           long long T, int k, int vec_per_row, uint4* __restrict__ grad_eo,
+                           int e_lo, int e_hi, long long T, int k, int vec_per_row, uint4* __restrict__ grad_eo,
                            float* __restrict__ gw_rows) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -399,13 +414,14 @@ ep_combine_bwd_pull_kernel(const __grid_constant__ PeerPtrs go_peers, const __gr
     const unsigned mask = local_rows_of_token(reinterpret_cast<const long long*>(idx_peers.p[s]),
                                               reinterpret_cast<const int*>(spos_peers.p[s]),
                                               reinterpret_cast<const int*>(offs_peers.p[s]), src_base, s, t, k, rank,
-                                              El, lane, row);
+                                              El, e_lo, e_hi, lane, row);
     if (mask == 0u) continue;
     float wt_lane = 0.0f;
     if ((mask >> lane) & 1u) wt_lane = reinterpret_cast<const float*>(w_peers.p[s])[t * k + lane];
     const uint4* g = reinterpret_cast<const uint4*>(go_peers.p[s]) + t * vec_per_row;
     float dot_lane = 0.0f;   // lane j keeps the row dot of slot j
-    constexpr int kB = 4;   // 16-byte vectors per lane and row in flight
+    constexpr int kB = KB;   // 16-byte vectors per lane and row in flight
+    const bool dots = DOTS && eo != nullptr;
     for (int c0 = lane; c0 < vec_per_row; c0 += 32 * kB) {
       uint4 gv[kB], ev[kB], ev_next[kB];
 #pragma unroll
@@ -414,7 +430,7 @@ ep_combine_bwd_pull_kernel(const __grid_constant__ PeerPtrs go_peers, const __gr
       unsigned m = mask;
       int j = __ffs(m) - 1;
       int r = __shfl_sync(0xffffffffu, row, j);
-      if (eo != nullptr) {
+      if (dots) {
         const uint4* e = eo + static_cast<long long>(r) * vec_per_row;
 #pragma unroll
         for (int i = 0; i < kB; ++i)
@@ -425,7 +441,7 @@ ep_combine_bwd_pull_kernel(const __grid_constant__ PeerPtrs go_peers, const __gr
         // the next slot's eo row is requested before this slot's arithmetic
         const int jn = m != 0u ? __ffs(m) - 1 : j;
         const int rn = __shfl_sync(0xffffffffu, row, jn);
-        if (m != 0u && eo != nullptr) {
+        if (m != 0u && dots) {
           const uint4* e = eo + static_cast<long long>(rn) * vec_per_row;
 #pragma unroll
           for (int i = 0; i < kB; ++i)
@@ -438,7 +454,7 @@ ep_combine_bwd_pull_kernel(const __grid_constant__ PeerPtrs go_peers, const __gr
         for (int i = 0; i < kB; ++i)
           if (c0 + 32 * i < vec_per_row) {
             const float2 g0 = unpack_bf16x2(gv[i].x), g1 = unpack_bf16x2(gv[i].y), g2 = unpack_bf16x2(gv[i].z), g3 = unpack_bf16x2(gv[i].w);
-            if (eo != nullptr) {
+            if (dots) {
               const float2 e0 = unpack_bf16x2(ev[i].x), e1 = unpack_bf16x2(ev[i].y), e2 = unpack_bf16x2(ev[i].z), e3 = unpack_bf16x2(ev[i].w);
               dot += g0.x * e0.x + g0.y * e0.y + g1.x * e1.x + g1.y * e1.y + g2.x * e2.x + g2.y * e2.y + g3.x * e3.x + g3.y * e3.y;
             }
@@ -458,9 +474,9 @@ ep_combine_bwd_pull_kernel(const __grid_constant__ PeerPtrs go_peers, const __gr
         r = rn;
       }
     }
-    if (gw_rows != nullptr && ((mask >> lane) & 1u)) gw_rows[row] = dot_lane;
+    if (DOTS && gw_rows != nullptr && ((mask >> lane) & 1u)) gw_rows[row] = dot_lane;
   }
-  for_each_pad_row(counts_l, poffs_l, El, warp0, nwarps, [&](long long r) {
+  for_each_pad_row(counts_l, poffs_l, e_lo, e_hi, warp0, nwarps, [&](long long r) {
     uint4* dst = grad_eo + r * vec_per_row;
     for (int c = lane; c < vec_per_row; c += 32) dst[c] = make_uint4(0u, 0u, 0u, 0u);
     if (gw_rows != nullptr && lane == 0) gw_rows[r] = 0.0f;
@@ -569,14 +585,14 @@ int b200moe_ep_plan(const int32_t* counts_all, int W, int rank, int E, int32_t* 
   return 0;
 }
 
-int b200moe_ep_local_rows(const int32_t* counts_all, int W, int rank, int E, int32_t* host_word,
+int b200moe_ep_local_rows(const int32_t* counts_all, int W, int rank, int E, int32_t* host_words,
                           b200moe_stream_t stream) {
-  B200_CHECK_ARG(counts_all && host_word, B200MOE_E_NULL, "ep_local_rows: null pointer");
+  B200_CHECK_ARG(counts_all && host_words, B200MOE_E_NULL, "ep_local_rows: null pointer");
   CHECK_WORLD("ep_local_rows");
   B200_CHECK_ARG(E >= W && E <= B200MOE_MAX_EXPERTS && E % W == 0, B200MOE_E_BAD_SHAPE,
                  "ep_local_rows: E = %d must be a multiple of W = %d and at most %d", E, W, B200MOE_MAX_EXPERTS);
-  void* dev_view = nullptr;   // the device's address of the pinned host word; fails (nothing launched) if it is not pinned
-  B200_CUDA(cudaHostGetDevicePointer(&dev_view, host_word, 0));
+  void* dev_view = nullptr;   // the device's address of the pinned host words; fails (nothing launched) if not pinned
+  B200_CUDA(cudaHostGetDevicePointer(&dev_view, host_words, 0));
   ep_local_rows_kernel<<<1, B200MOE_MAX_EXPERTS, 0, (cudaStream_t)stream>>>(counts_all, W, rank, E,
                                                                              reinterpret_cast<volatile int*>(dev_view));
   B200_CUDA(cudaGetLastError());
@@ -614,8 +630,8 @@ int b200moe_ep_publish(const int64_t* idx, const int32_t* slot_pos, const float*
 
 int b200moe_ep_gather_pull(const void* const* x_peers, const void* const* idx_peers, const void* const* spos_peers,
                            const void* const* offs_peers, const int32_t* counts_l, const int32_t* poffs_l,
-                           const int32_t* src_base, int W, int rank, int E, int64_t T, int k, int64_t H, void* x_s,
-                           int32_t* row_rank, int32_t* row_slot, b200moe_stream_t stream) {
+                           const int32_t* src_base, int W, int rank, int E, int e_lo, int e_hi, int max_sms, int64_t T,
+                           int k, int64_t H, void* x_s, int32_t* row_rank, int32_t* row_slot, b200moe_stream_t stream) {
   B200_CHECK_ARG(counts_l && poffs_l && src_base && x_s, B200MOE_E_NULL, "ep_gather_pull: null pointer");
   B200_CHECK_ARG((row_rank == nullptr) == (row_slot == nullptr), B200MOE_E_NULL,
                  "ep_gather_pull: row_rank and row_slot go together");
@@ -626,9 +642,16 @@ int b200moe_ep_gather_pull(const void* const* x_peers, const void* const* idx_pe
   LOAD_PEERS(ip, idx_peers, "ep_gather_pull(idx)");
   LOAD_PEERS(sp, spos_peers, "ep_gather_pull(slot_pos)");
   LOAD_PEERS(fp, offs_peers, "ep_gather_pull(offs)");
-  ep_gather_pull_kernel<<<grid_rows((T * W + 7) / 8, 8), 256, 0, (cudaStream_t)stream>>>(
-      xp, ip, sp, fp, counts_l, poffs_l, src_base, W, rank, E / W, T, k, static_cast<int>(H / 8),
-      reinterpret_cast<uint4*>(x_s), row_rank, row_slot);
+  B200_CHECK_ARG(0 <= e_lo && e_lo <= e_hi && e_hi <= E / W && max_sms >= 0, B200MOE_E_BAD_SHAPE,
+                 "ep_gather_pull: local expert range [%d, %d) of %d, max_sms = %d", e_lo, e_hi, E / W, max_sms);
+  if (max_sms > 0 && max_sms < num_sms())
+    ep_gather_pull_kernel<1024><<<max_sms, 1024, 0, (cudaStream_t)stream>>>(
+        xp, ip, sp, fp, counts_l, poffs_l, src_base, W, rank, E / W, e_lo, e_hi, T, k, static_cast<int>(H / 8),
+        reinterpret_cast<uint4*>(x_s), row_rank, row_slot);
+  else
+    ep_gather_pull_kernel<256><<<grid_rows((T * W + 7) / 8, 8), 256, 0, (cudaStream_t)stream>>>(
+        xp, ip, sp, fp, counts_l, poffs_l, src_base, W, rank, E / W, e_lo, e_hi, T, k, static_cast<int>(H / 8),
+        reinterpret_cast<uint4*>(x_s), row_rank, row_slot);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -679,8 +702,9 @@ int b200moe_ep_combine_pull(const void* const* rows_peers, const float* w, const
 int b200moe_ep_combine_bwd_pull(const void* const* go_peers, const void* const* w_peers,
                                 const void* const* idx_peers, const void* const* spos_peers,
                                 const void* const* offs_peers, const void* eo, const int32_t* counts_l,
-                                const int32_t* poffs_l, const int32_t* src_base, int W, int rank, int E, int64_t T,
-                                int k, int64_t H, void* grad_eo, float* gw_rows, b200moe_stream_t stream) {
+                                const int32_t* poffs_l, const int32_t* src_base, int W, int rank, int E, int e_lo,
+                                int e_hi, int max_sms, int64_t T, int k, int64_t H, void* grad_eo, float* gw_rows,
+                                b200moe_stream_t stream) {
   B200_CHECK_ARG(counts_l && poffs_l && src_base && grad_eo, B200MOE_E_NULL, "ep_combine_bwd_pull: null pointer");
   B200_CHECK_ARG((eo == nullptr) == (gw_rows == nullptr), B200MOE_E_NULL,
                  "ep_combine_bwd_pull: eo and gw_rows go together (both NULL: no row dot products)");
@@ -692,9 +716,17 @@ int b200moe_ep_combine_bwd_pull(const void* const* go_peers, const void* const* 
   LOAD_PEERS(ip, idx_peers, "ep_combine_bwd_pull(idx)");
   LOAD_PEERS(sp, spos_peers, "ep_combine_bwd_pull(slot_pos)");
   LOAD_PEERS(fp, offs_peers, "ep_combine_bwd_pull(offs)");
-  ep_combine_bwd_pull_kernel<<<grid_rows((T * W + 7) / 8, 8), 256, 0, (cudaStream_t)stream>>>(
-      gp, wp, ip, sp, fp, reinterpret_cast<const uint4*>(eo), counts_l, poffs_l, src_base, W, rank, E / W, T, k,
-      static_cast<int>(H / 8), reinterpret_cast<uint4*>(grad_eo), gw_rows);
+  B200_CHECK_ARG(0 <= e_lo && e_lo <= e_hi && e_hi <= E / W && max_sms >= 0, B200MOE_E_BAD_SHAPE,
+                 "ep_combine_bwd_pull: local expert range [%d, %d) of %d, max_sms = %d", e_lo, e_hi, E / W, max_sms);
+  const bool few_sms = max_sms > 0 && max_sms < num_sms();
+#define B200_BWD_PULL(THREADS, MINB, DOTS, KB, GRID)                                                               \
+  ep_combine_bwd_pull_kernel<THREADS, MINB, DOTS, KB><<<(GRID), THREADS, 0, (cudaStream_t)stream>>>(               \
+      gp, wp, ip, sp, fp, reinterpret_cast<const uint4*>(eo), counts_l, poffs_l, src_base, W, rank, E / W, e_lo,   \
+      e_hi, T, k, static_cast<int>(H / 8), reinterpret_cast<uint4*>(grad_eo), gw_rows)
+  if (few_sms && eo == nullptr) B200_BWD_PULL(1024, 1, false, 8, max_sms);
+  else if (few_sms) B200_BWD_PULL(768, 1, true, 4, max_sms);
+  else B200_BWD_PULL(256, 3, true, 4, grid_rows((T * W + 7) / 8, 8));
+#undef B200_BWD_PULL
   B200_CUDA(cudaGetLastError());
   return 0;
 }

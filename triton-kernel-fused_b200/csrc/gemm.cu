@@ -797,6 +797,16 @@ int b200moe_gemm_tn_splitk(const void* A, const void* B, float* P, int64_t M, in
                                     (cudaStream_t)stream);
 }
 
+// row window of a grouped-M launch: (0, 0) = every row, else tile-aligned 0 <= row_lo < row_hi <= rows_cap
+static int check_row_window(const char* who, int64_t rows_cap, int64_t row_lo, int64_t row_hi) {
+  if (row_lo == 0 && row_hi == 0) return 0;
+  B200_CHECK_ARG(row_lo >= 0 && row_lo < row_hi && row_hi <= rows_cap && row_lo % B200MOE_TILE_M == 0 &&
+                     row_hi % B200MOE_TILE_M == 0,
+                 B200MOE_E_BAD_SHAPE, "%s: row window [%lld, %lld) must be tile-aligned and inside %lld rows", who,
+                 (long long)row_lo, (long long)row_hi, (long long)rows_cap);
+  return 0;
+}
+
 static int check_grouped(const char* who, const void* a, const void* b, const void* c, const int32_t* tile_expert,
                          const int32_t* poffs, int64_t rows_cap, int E, int64_t H, int64_t I) {
   B200_CHECK_ARG(a && b && c && poffs, B200MOE_E_NULL, "%s: null pointer", who);
@@ -813,14 +823,17 @@ static int check_grouped(const char* who, const void* a, const void* b, const vo
 int b200moe_expert_gate_up_swiglu(const void* x_s, const void* gate_up_proj, const int32_t* tile_expert,
                                   const int32_t* poffs, int64_t rows_cap, int E, int64_t H, int64_t I,
                                   void* gate_up, void* inter, int32_t* status, b200moe_stream_t stream) {
-  return b200moe_expert_gate_up_act(x_s, gate_up_proj, nullptr, tile_expert, poffs, rows_cap, E, H, I, gate_up, inter,
-                                    status, stream);
+  return b200moe_expert_gate_up_act(x_s, gate_up_proj, nullptr, tile_expert, poffs, rows_cap, 0, 0, E, H, I, gate_up,
+                                    inter, status, stream);
 }
 
 int b200moe_expert_gate_up_act(const void* x_s, const void* gate_up_proj, const int32_t* act_codes,
-                               const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E, int64_t H,
-                               int64_t I, void* gate_up, void* inter, int32_t* status, b200moe_stream_t stream) {
+                               const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int64_t row_lo,
+                               int64_t row_hi, int E, int64_t H, int64_t I, void* gate_up, void* inter,
+                               int32_t* status, b200moe_stream_t stream) {
   int rc = check_grouped("expert_gate_up_swiglu", x_s, gate_up_proj, gate_up, tile_expert, poffs, rows_cap, E, H, I);
+  if (rc) return rc;
+  rc = check_row_window("expert_gate_up_swiglu", rows_cap, row_lo, row_hi);
   if (rc) return rc;
   B200_CHECK_ARG(inter && tile_expert, B200MOE_E_NULL, "expert_gate_up_swiglu: null pointer");
   B200_CHECK_ARG(aligned16(gate_up) && aligned16(inter), B200MOE_E_ALIGN, "expert_gate_up_swiglu: outputs not aligned");
@@ -830,6 +843,7 @@ int b200moe_expert_gate_up_act(const void* x_s, const void* gate_up_proj, const 
   GemmParams p{};
   p.sched = SCHED_GROUPED_M; p.N = (int)I; p.K = (int)H; p.num_groups = E;
   p.tile_expert = tile_expert; p.poffs = poffs; p.D = gate_up; p.aux = inter; p.I = (int)I; p.status = status;
+  p.row_lo = (int)row_lo; p.row_hi = (int)row_hi;
   const int bn = (I >= 128) ? 256 : 128;   // tile covers bn/2 intermediate columns
   Operand d1{gate_up, 0, rows_cap, I, 2 * I, 2, I};       // {I, rows, 2}: group 0 = gate half, 1 = up half
   Operand d2{inter, 0, rows_cap, I, I, 1, rows_cap * I};
@@ -943,15 +957,17 @@ int b200moe_expert_down_dgrad_glu(const void* grad_eo, const void* down_proj, co
                                   const int32_t* tile_expert, const int32_t* poffs, int64_t rows_cap, int E,
                                   int64_t H, int64_t I, void* grad_gate_up, int32_t* status,
                                   b200moe_stream_t stream) {
-  return b200moe_expert_down_dgrad_act(grad_eo, down_proj, gate_up, nullptr, tile_expert, poffs, rows_cap, E, H, I,
+  return b200moe_expert_down_dgrad_act(grad_eo, down_proj, gate_up, nullptr, tile_expert, poffs, rows_cap, 0, 0, E, H, I,
                                        grad_gate_up, status, stream);
 }
 
 int b200moe_expert_down_dgrad_act(const void* grad_eo, const void* down_proj, const void* gate_up,
                                   const int32_t* act_codes, const int32_t* tile_expert, const int32_t* poffs,
-                                  int64_t rows_cap, int E, int64_t H, int64_t I, void* grad_gate_up, int32_t* status,
-                                  b200moe_stream_t stream) {
+                                  int64_t rows_cap, int64_t row_lo, int64_t row_hi, int E, int64_t H, int64_t I,
+                                  void* grad_gate_up, int32_t* status, b200moe_stream_t stream) {
   int rc = check_grouped("expert_down_dgrad_glu", grad_eo, down_proj, grad_gate_up, tile_expert, poffs, rows_cap, E, H, I);
+  if (rc) return rc;
+  rc = check_row_window("expert_down_dgrad_glu", rows_cap, row_lo, row_hi);
   if (rc) return rc;
   B200_CHECK_ARG(gate_up && tile_expert, B200MOE_E_NULL, "expert_down_dgrad_glu: null pointer");
   B200_CHECK_ARG(aligned16(grad_gate_up) && aligned16(gate_up), B200MOE_E_ALIGN, "expert_down_dgrad_glu: not aligned");
@@ -961,6 +977,7 @@ int b200moe_expert_down_dgrad_act(const void* grad_eo, const void* down_proj, co
   p.sched = SCHED_GROUPED_M; p.b_mn = 1; p.N = (int)I; p.K = (int)H; p.num_groups = E;
   p.tile_expert = tile_expert; p.poffs = poffs; p.D = grad_gate_up; p.aux = const_cast<void*>(gate_up);
   p.I = (int)I; p.status = status;
+  p.row_lo = (int)row_lo; p.row_hi = (int)row_hi;
   const int bn = pick_bn(I) == 64 ? 128 : pick_bn(I);
   Operand d{grad_gate_up, 0, rows_cap, I, 2 * I, 2, I};   // {I, rows, 2}: grad_gate half, grad_up half
   Operand d2{gate_up, 0, rows_cap, I, 2 * I, 2, I};       // the saved forward gate_up, same view (input)

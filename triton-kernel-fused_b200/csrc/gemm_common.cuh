@@ -51,6 +51,10 @@ struct GemmParams {
   // optional, GLU epilogues of the POLY instantiations: activation code of each expert (0 SiLU, 1 ReLU^2,
   // 5 SiTU = tanh(g) * sigmoid(g)); nullptr in the plain instantiations, which are SiLU only
   const int* act_codes;
+  // optional, GROUPED_M: only the row tiles of rows [row_lo, row_hi) are computed (multiples of B200MOE_TILE_M;
+  // row_hi <= 0: every row).  Lets a caller run the rows of one group of experts while the rows of the next
+  // group are still arriving.
+  int row_lo, row_hi;
 };
 
 struct Tile {
@@ -69,7 +73,10 @@ __device__ __forceinline__ int total_tiles(const GemmParams& p, int TN, int TM) 
   const int nt = (p.N + TN - 1) / TN;
   if (p.sched == SCHED_GROUPED_M && p.sym_rows > 0) return p.num_groups * sym_tiles_per_group(p, TN, TM);
   if (p.sched == SCHED_DENSE) return ((p.M + TM - 1) / TM) * nt;
-  if (p.sched == SCHED_GROUPED_M) return (p.poffs[p.num_groups] / TM) * nt;
+  if (p.sched == SCHED_GROUPED_M) {
+    const int rows = p.poffs[p.num_groups];
+    return ((p.row_hi > 0 ? max(min(rows, p.row_hi) - p.row_lo, 0) : rows) / TM) * nt;
+  }
   return ((p.M + TM - 1) / TM) * nt * p.num_groups;
 }
 
@@ -130,7 +137,7 @@ __device__ __forceinline__ Tile get_tile(const GemmParams& p, int tile, int TN, 
     t.nkb = (p.K + BK - 1) / BK;
   } else {
     const int mi = tile / nt;
-    t.m0 = mi * TM;
+    t.m0 = mi * TM + (p.row_hi > 0 ? p.row_lo : 0);
     t.n0 = (tile - mi * nt) * TN;
     t.g = (p.sched == SCHED_GROUPED_M) ? p.tile_expert[t.m0 / B200MOE_TILE_M] : 0;
     t.k0 = 0;

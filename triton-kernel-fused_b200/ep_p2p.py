@@ -9,6 +9,13 @@ epilogue of the down projection (forward) and of the gate/up dgrad (backward) se
 slot of the home rank's receive buffer, tile by tile while the GEMM runs, and the home rank combines locally;
 `exchange="pull"` keeps the rows on the owner and lets the home ranks pull them while combining.
 
+`expert_groups` > 1 (push exchange) splits the rank's local experts into that many groups of about equal rows and
+pipelines them: the rows of group g+1 are pulled on a few SMs (`overlap_sms`, one 1024-thread CTA each, on a
+stream of its own) while the gate/up GEMM of group g runs on the others, and likewise the grad_out rows of group
+g+1 beside the GLU-backward GEMM of group g; only the pull of the first group is exposed.  Off by default: on
+8 GPUs at the benchmark's layer the two extra GEMM launches and the SMs the GEMMs give up cost more than the hidden
+half of the pulls saves (a pull confined to 16-24 SMs keeps too few loads in flight to fill NVLink).
+
 Per step and direction there is one tiny NCCL all-gather (the (W,E) count matrix, which also orders
 the phases), one host read of that matrix (to size the local buffers) and two device-side barriers
 (`b200moe_ep_barrier`: flag words in the symmetric buffer, plain peer stores and bounded local waits).
@@ -80,19 +87,65 @@ def _align(n, a=256):
     return (n + a - 1) // a * a
 
 
+def expert_groups(ends, n):
+    """Split local experts 0..len(ends)-1 into at most `n` runs of consecutive experts with about equal padded rows.
+    ends[j] = padded row at which expert j ends.  Returns [(e_lo, e_hi, row_lo, row_hi)], empty runs left out."""
+    import bisect
+    El, total = len(ends), (ends[-1] if ends else 0)
+    cuts = [0]
+    for g in range(1, max(1, int(n))):
+        j = bisect.bisect_left(ends, total * g / n) + 1      # first cut at or behind the g-th share of the rows
+        cuts.append(min(max(j, cuts[-1]), El))
+    cuts.append(El)
+    starts = [0] + list(ends)
+    return [(lo, hi, starts[lo], starts[hi]) for lo, hi in zip(cuts, cuts[1:]) if starts[hi] > starts[lo]]
+
+
+def _pipelined(ws, groups, pull, gemm):
+    """pull(e_lo, e_hi, max_sms, stream) / gemm(g, grp): group 0 is pulled by the whole GPU on the current stream,
+    the others on `ws.overlap_sms` SMs on the side stream, each beside the GEMMs of the groups before it, which
+    leave those SMs free."""
+    dev = ws.buf.device
+    main, side = torch.cuda.current_stream(dev), ws.side_stream
+    pull(groups[0][0], groups[0][1], 0, main.cuda_stream)
+    start, arrived = ws.pipe_events[0], ws.pipe_events[1:]
+    start.record(main)
+    side.wait_event(start)
+    for g, (e_lo, e_hi, _, _) in enumerate(groups[1:]):
+        pull(e_lo, e_hi, ws.overlap_sms, side.cuda_stream)
+        arrived[g].record(side)
+    try:
+        for g, grp in enumerate(groups):
+            if g > 0:
+                main.wait_event(arrived[g - 1])
+            # the last GEMM starts when the last pull is over and takes every SM
+            L.check(L.lib().b200moe_set_reserved_sms(ws.overlap_sms if g + 1 < len(groups) else 0))
+            gemm(g, grp)
+    finally:
+        L.check(L.lib().b200moe_set_reserved_sms(0))
+
+
 class SymmetricWorkspace:
     """One symmetric allocation carved into the buffers peers read.  Sized for the worst case
     (every routed row of every rank lands on one rank), so it is allocated once."""
 
-    def __init__(self, T, H, k, E, group, device, overlap_sms=0, exchange="push"):
-        """overlap_sms > 0: in the backward pass the last pull (grad_hidden) runs on that many SMs beside the
-        weight-gradient GEMMs, which leave them free and run on a high-priority stream of their own."""
+    def __init__(self, T, H, k, E, group, device, overlap_sms=0, exchange="push", expert_groups=1):
+        """exchange="pull", overlap_sms > 0: in the backward pass the last pull (grad_hidden) runs on that many SMs
+        beside the weight-gradient GEMMs, which leave them free and run on a high-priority stream of their own.
+        exchange="push", expert_groups > 1: the dispatch-side pulls are pipelined against the GEMMs by groups of
+        local experts, on overlap_sms SMs (default 16)."""
         import torch.distributed._symmetric_memory as symm
         if exchange not in ("push", "pull"):
             raise ValueError("exchange must be 'push' or 'pull'")
         self.exchange = exchange
-        self.overlap_sms = int(overlap_sms) if exchange == "pull" else 0
-        self.gemm_stream = torch.cuda.Stream(device=device, priority=-1) if self.overlap_sms > 0 else None
+        self.expert_groups = max(1, int(expert_groups)) if exchange == "push" else 1
+        if exchange == "pull":
+            self.overlap_sms = int(overlap_sms)
+        else:
+            self.overlap_sms = (int(overlap_sms) or 16) if self.expert_groups > 1 else 0
+        self.gemm_stream = torch.cuda.Stream(device=device, priority=-1) if exchange == "pull" and self.overlap_sms > 0 else None
+        self.side_stream = torch.cuda.Stream(device=device) if self.expert_groups > 1 else None
+        self.pipe_events = [torch.cuda.Event() for _ in range(self.expert_groups)] if self.expert_groups > 1 else []
         self.group = group
         self.W = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -138,7 +191,7 @@ class SymmetricWorkspace:
             self.recvg_base = torch.tensor([b + self.offsets["recvg"] for b in base], dtype=torch.int64, device=device)
             self.ident = torch.arange(M, dtype=torch.int32, device=device)   # slot -> row of the receive buffers
         self.generation = 0
-        self.rows_host = torch.zeros(1, dtype=torch.int32).pin_memory()   # written by ep_local_rows_kernel
+        self.rows_host = torch.zeros(1 + E // W, dtype=torch.int32).pin_memory()   # written by ep_local_rows_kernel
         self.rows_event = torch.cuda.Event()
         # barrier flags: one word per peer, zero before the first barrier on every rank (the rendezvous below is the
         # one library barrier of the workspace's life: nobody announces itself into an array that is still being zeroed)
@@ -165,10 +218,19 @@ def _backward_push(ctx, grad_out, grad_eo):
     # the expert outputs of this rank's tokens are still in its receive buffer: grad of the routing weights
     grad_w = torch.empty(T, k, dtype=torch.float32, device=dev)
     _slot_dots(L.ptr(ws.go), L.ptr(ws.recv), T, k, H, L.ptr(grad_w), st)
-    _combine_bwd_pull(ws.peers["go"], ws.tabs["tab_w"], ws.tabs["tab_idx"], ws.tabs["tab_spos"], ws.tabs["tab_offs"], None,
-                      L.ptr(perm_l.counts), L.ptr(perm_l.poffs), L.ptr(src_base), W, ws.rank, E, T, k, H,
-                      L.ptr(grad_eo), None, st)
-    grad_gu = ops.expert_down_dgrad_glu(grad_eo, down_local, gate_up, perm_l)
+
+    def pull(e_lo, e_hi, max_sms, stream):
+        _combine_bwd_pull(ws.peers["go"], ws.tabs["tab_w"], ws.tabs["tab_idx"], ws.tabs["tab_spos"], ws.tabs["tab_offs"],
+                          None, L.ptr(perm_l.counts), L.ptr(perm_l.poffs), L.ptr(src_base), W, ws.rank, E, e_lo, e_hi,
+                          max_sms, T, k, H, L.ptr(grad_eo), None, stream)
+
+    if len(ctx.groups) > 1:
+        grad_gu = torch.empty(cap_l, gate_up.shape[1], dtype=torch.bfloat16, device=dev)
+        _pipelined(ws, ctx.groups, pull, lambda g, grp: ops.expert_down_dgrad_glu(
+            grad_eo, down_local, gate_up, perm_l, out=grad_gu, rows=grp[2:]))
+    else:
+        pull(0, El, 0, st)
+        grad_gu = ops.expert_down_dgrad_glu(grad_eo, down_local, gate_up, perm_l)
     # gate/up dgrad whose epilogue sends each grad_x row to its slot at the token's home rank
     twoI = gate_up_local.shape[1]
     _linear_push(L.ptr(grad_gu), L.ptr(gate_up_local), 1, L.ptr(perm_l.tile_expert), L.ptr(perm_l.poffs), cap_l, El, H,
@@ -215,7 +277,9 @@ class _ExpertParallelP2P(torch.autograd.Function):
         L.check(L.lib().b200moe_ep_local_rows(L.ptr(counts_all), W, rank, E, ws.rows_host.data_ptr(), st))
         ws.rows_event.record(torch.cuda.current_stream(dev))
         ws.rows_event.synchronize()
-        R = int(ws.rows_host[0])
+        words = ws.rows_host.tolist()
+        R = words[0]
+        groups = expert_groups(words[1:], ws.expert_groups) if ws.expert_groups > 1 else []
         cap_l = L.padded_rows_cap(R, El)
         poffs_l = torch.empty(El + 1, **i32)
         counts_l = torch.empty(El, **i32)
@@ -228,11 +292,23 @@ class _ExpertParallelP2P(torch.autograd.Function):
         push = ws.exchange == "push"
         row_rank = torch.empty(cap_l, **i32) if push else None
         row_slot = torch.empty(cap_l, **i32) if push else None
-        _gather_pull(ws.peers["x"], ws.tabs["tab_idx"], ws.tabs["tab_spos"], ws.tabs["tab_offs"], L.ptr(counts_l),
-                     L.ptr(poffs_l), L.ptr(src_base), W, rank, E, T, k, H, L.ptr(x_s), L.ptr(row_rank),
-                     L.ptr(row_slot), st)
+
+        def pull(e_lo, e_hi, max_sms, stream):
+            _gather_pull(ws.peers["x"], ws.tabs["tab_idx"], ws.tabs["tab_spos"], ws.tabs["tab_offs"], L.ptr(counts_l),
+                         L.ptr(poffs_l), L.ptr(src_base), W, rank, E, e_lo, e_hi, max_sms, T, k, H, L.ptr(x_s),
+                         L.ptr(row_rank), L.ptr(row_slot), stream)
+
         perm_l = ops.Permutation(R, 1, El, cap_l, counts_l, None, poffs_l, None, None, tile_expert_l, None, None)
-        gate_up, inter = ops.expert_gate_up_swiglu(x_s, gate_up_local, perm_l)
+        if len(groups) > 1:
+            twoI = gate_up_local.shape[1]
+            gate_up = torch.empty(cap_l, twoI, dtype=torch.bfloat16, device=dev)
+            inter = torch.empty(cap_l, twoI // 2, dtype=torch.bfloat16, device=dev)
+            _pipelined(ws, groups, pull, lambda g, grp: ops.expert_gate_up_swiglu(
+                x_s, gate_up_local, perm_l, out=(gate_up, inter), rows=grp[2:]))
+        else:
+            groups = []
+            pull(0, El, 0, st)
+            gate_up, inter = ops.expert_gate_up_swiglu(x_s, gate_up_local, perm_l)
         status = L.ptr(L.status_word(dev))
         if push:
             # down projection whose epilogue sends each output row to its slot at the token's home rank
@@ -250,6 +326,7 @@ class _ExpertParallelP2P(torch.autograd.Function):
         ws.generation += 1
         ctx.ws, ctx.perm, ctx.perm_l, ctx.gen = ws, perm, perm_l, ws.generation
         ctx.tables = (dest_base, src_base, row_rank, row_slot)
+        ctx.groups = groups
         ctx.wt_dtype = wt.dtype
         ctx.save_for_backward(idx, x_s, gate_up, inter, w32, gate_up_local, down_local)
         return out
@@ -273,8 +350,8 @@ class _ExpertParallelP2P(torch.autograd.Function):
         if ws.exchange == "push":
             return _backward_push(ctx, grad_out, grad_eo)
         _combine_bwd_pull(ws.peers["go"], ws.tabs["tab_w"], ws.tabs["tab_idx"], ws.tabs["tab_spos"], ws.tabs["tab_offs"],
-                          L.ptr(ws.eo), L.ptr(perm_l.counts), L.ptr(perm_l.poffs), L.ptr(src_base), W, ws.rank, E, T, k,
-                          H, L.ptr(grad_eo), L.ptr(ws.gw), st)
+                          L.ptr(ws.eo), L.ptr(perm_l.counts), L.ptr(perm_l.poffs), L.ptr(src_base), W, ws.rank, E, 0,
+                          E // W, 0, T, k, H, L.ptr(grad_eo), L.ptr(ws.gw), st)
         grad_gu = ops.expert_down_dgrad_glu(grad_eo, down_local, gate_up, perm_l)
         grad_hidden = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
         grad_w = torch.empty(T, k, dtype=torch.float32, device=dev)

@@ -196,14 +196,19 @@ def gather_compact(x, perm: Permutation):
 
 
 @_op("expert_gate_up_swiglu", 1)
-def expert_gate_up_swiglu(x_s, gate_up_proj, perm: Permutation, act_codes=None):
-    """act_codes: (E,) int32 device tensor of per-expert codes 0 / 1 / 5 applied in the epilogue (None = all SiLU)."""
+def expert_gate_up_swiglu(x_s, gate_up_proj, perm: Permutation, act_codes=None, out=None, rows=(0, 0)):
+    """act_codes: (E,) int32 device tensor of per-expert codes 0 / 1 / 5 applied in the epilogue (None = all SiLU).
+    out: (gate_up, inter) buffers of perm.cap rows to write into; rows = (lo, hi): only these rows (tile-aligned)."""
     E, twoI, H = gate_up_proj.shape
     I = twoI // 2
-    gate_up = torch.empty(perm.cap, twoI, dtype=torch.bfloat16, device=x_s.device)
-    inter = torch.empty(perm.cap, I, dtype=torch.bfloat16, device=x_s.device)
+    if out is None:
+        gate_up = torch.empty(perm.cap, twoI, dtype=torch.bfloat16, device=x_s.device)
+        inter = torch.empty(perm.cap, I, dtype=torch.bfloat16, device=x_s.device)
+    else:
+        gate_up, inter = out
     L.check(L.lib().b200moe_expert_gate_up_act(L.ptr(x_s), L.ptr(gate_up_proj), L.ptr(act_codes), L.ptr(perm.tile_expert),
-                                               L.ptr(perm.poffs), perm.cap, E, H, I, L.ptr(gate_up), L.ptr(inter),
+                                               L.ptr(perm.poffs), perm.cap, rows[0], rows[1], E, H, I, L.ptr(gate_up),
+                                               L.ptr(inter),
                                                L.ptr(L.status_word(x_s.device)), L.stream_of(x_s)))
     return gate_up, inter
 
@@ -219,11 +224,12 @@ def expert_down(inter, down_proj, perm: Permutation, out=None):
 
 
 @_op("expert_down_dgrad_glu", 1)
-def expert_down_dgrad_glu(grad_eo, down_proj, gate_up, perm: Permutation, act_codes=None):
+def expert_down_dgrad_glu(grad_eo, down_proj, gate_up, perm: Permutation, act_codes=None, out=None, rows=(0, 0)):
     E, H, I = down_proj.shape
-    ggu = torch.empty(perm.cap, 2 * I, dtype=torch.bfloat16, device=grad_eo.device)
+    ggu = torch.empty(perm.cap, 2 * I, dtype=torch.bfloat16, device=grad_eo.device) if out is None else out
     L.check(L.lib().b200moe_expert_down_dgrad_act(L.ptr(grad_eo), L.ptr(down_proj), L.ptr(gate_up), L.ptr(act_codes),
-                                                  L.ptr(perm.tile_expert), L.ptr(perm.poffs), perm.cap, E, H, I,
+                                                  L.ptr(perm.tile_expert), L.ptr(perm.poffs), perm.cap, rows[0], rows[1],
+                                                  E, H, I,
                                                   L.ptr(ggu), L.ptr(L.status_word(grad_eo.device)),
                                                   L.stream_of(grad_eo)))
     return ggu
