@@ -769,6 +769,85 @@ def run_muon(args):
     print(json.dumps(line), flush=True)
 
 
+def run_conv_router(args):
+    """--workload conv_router: forward + backward of `fused_router` (causal K-tap conv router) on the token count and
+    width of the headline layer, once with the GEMMs that read x in place through shifted TMA boxes and once over
+    the unfolded (B*S, K*H) copy.  A line of its own for the conv-router row, not the headline metric."""
+    if int(os.environ.get("WORLD_SIZE", 1)) > 1:
+        if int(os.environ.get("RANK", 0)) == 0:
+            print(json.dumps({"workload": "conv_router", "unavailable": "single-GPU workload"}), flush=True)
+        return
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    pkg = importlib.import_module(PKG)
+    pkg.lib()
+    ops = pkg.ops
+    B, S, H, E, K, k = 16, 1024, HEADLINE["H"], HEADLINE["E"], 4, HEADLINE["k"]
+    g = torch.Generator(device=dev).manual_seed(7)
+    x = torch.randn(B, S, H, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(E, H, K, device=dev, generator=g) * 0.02).to(torch.bfloat16).requires_grad_(True)
+    bias = torch.randn(E, device=dev, generator=g) * 0.01
+    G = torch.randn(B, S, k, device=dev, generator=g)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)     # larger than the 126 MB L2
+
+    def step():
+        x.grad = w.grad = None
+        _, wt = pkg.fused_router(x, w, bias, k, E)
+        (wt * G).sum().backward()
+
+    def measure(steps, warm):
+        for _ in range(warm):
+            step()
+        pkg.check_status()
+        records = []
+        ops.set_hook(lambda name, launches, a, b: records.append((name, launches, a, b)))
+        total = 0.0
+        sampler = ClockSampler(0)
+        sampler.start()
+        for _ in range(steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        clocks = sampler.stop()
+        ops.set_hook(None)
+        pkg.check_status()
+        per_op, launches = {}, 0
+        for name, n, a, b in records:
+            d = per_op.setdefault(name, [0.0, 0])
+            d[0] += a.elapsed_time(b)
+            d[1] += 1
+            launches += n
+        kernels = {name: dict(launches_per_step=n / steps, avg_ms=round(ms / n, 4))
+                   for name, (ms, n) in sorted(per_op.items(), key=lambda kv: -kv[1][0])}
+        return total / steps, kernels, launches, clocks
+
+    n_warm = max(args.warmup, 3)
+    steps = max(3, min(args.steps, 50))
+    ms, kernels, launches, clocks = measure(steps, n_warm)
+    direct_ok = ops.conv_direct_ok
+    ops.conv_direct_ok = lambda S_, H_: False
+    try:
+        ms_u, kernels_u, _, clocks_u = measure(steps, n_warm)
+    finally:
+        ops.conv_direct_ok = direct_ok
+    flops = 6.0 * B * S * K * H * E          # logits, dX and dW GEMMs
+    line = {
+        "metric": "conv_router_fwd_bwd_ms", "value": round(ms, 4), "unit": "ms", "n_gpus": 1, "steps": steps, "warmup": n_warm,
+        "ms_per_step": round(ms, 4), "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"fused_router fwd+bwd, x ({B},{S},{H}) bf16, conv weight ({E},{H},{K}), top-{k}",
+                   "l2": "flushed between steps (256 MB write)"},
+        "gemm_tflops": round(flops / (ms * 1e-3) / 1e12, 1),
+        "kernels": kernels, "gpu_launches": launches, "clocks": clocks,
+        "unfolded_copy_path": {"ms_per_step": round(ms_u, 4), "kernels": kernels_u, "clocks": clocks_u},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def cpu_baseline(w, steps, warmup, sample_tokens=512):
     """The oracle port (plain PyTorch fp32 on the host cores) on a bounded sample: `sample_tokens`
     tokens through the full-size layer (all E experts, full d_model and d_ff), forward + backward."""
@@ -883,7 +962,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary configurations after the headline")
     ap.add_argument("--no-parity", action="store_true", help="N > 1: skip the expert-parallel parity check")
-    ap.add_argument("--workload", default="headline", choices=["headline", "profile", "ep5", "mxfp8", "mxfp8_profile", "zipf", "polyglu", "muon", "muon_profile"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "profile", "ep5", "mxfp8", "mxfp8_profile", "zipf", "polyglu", "muon", "muon_profile",
+                             "conv_router"],
                     help="profile = small case for profiler captures (not a benchmark number)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -892,6 +972,8 @@ def main():
         run_torch_grouped(args)
     elif args.workload.startswith("muon"):
         run_muon(args)
+    elif args.workload == "conv_router":
+        run_conv_router(args)
     else:
         run_ours(args)
 

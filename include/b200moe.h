@@ -91,6 +91,23 @@ int b200moe_conv_unfold(const void* x, int64_t B, int64_t S, int64_t H, int K, v
 int b200moe_conv_fold(const void* grad_xu, int64_t B, int64_t S, int64_t H, int K, void* grad_x,
                       b200moe_stream_t stream);
 
+/* The same convolution WITHOUT the unfolded copy (what the reference's one-launch conv router does,
+ * kernels/sm120/router.py:34-85): the GEMM's TMA producer reads x through a {H, S, B} tensor map, one 64-channel box
+ * per (tap, channel block), `tap - (K-1)` positions away from the tile's rows; positions before the sequence start
+ * are out of the map's bounds and arrive as zeros (the causal padding).
+ * fwd: logits (B*S, E) = conv(x (B,S,H), Wf (E, K*H));  needs S % 128 == 0 (a row tile stays inside one sequence)
+ *      and H % 64 == 0.
+ * dx:  grad_x (B*S, H) from grad_logits (B,S,E) and Wb (K*E, H), Wb[j*E+e, h] = W[e,h,j]; S % 128 == 0, E % 64 == 0.
+ * dw_splitk: fp32 slices P[s] (E, K*H) of grad_Wf = grad_logits^T * unfold(x) over chunks of k_chunk rows (multiple
+ *      of 64), to be summed by b200moe_splitk_reduce; S % 64 == 0, H % 64 == 0.
+ * Other shapes take b200moe_conv_unfold / conv_fold with the plain GEMMs. */
+int b200moe_conv_gemm_fwd(const void* x, const void* wf, void* logits, int64_t B, int64_t S, int64_t H, int64_t E,
+                          int taps, int32_t* status, b200moe_stream_t stream);
+int b200moe_conv_gemm_dx(const void* grad_logits, const void* wb, void* grad_x, int64_t B, int64_t S, int64_t H,
+                         int64_t E, int taps, int32_t* status, b200moe_stream_t stream);
+int b200moe_conv_gemm_dw_splitk(const void* grad_logits, const void* x, float* P, int64_t B, int64_t S, int64_t H,
+                                int64_t E, int taps, int64_t k_chunk, int32_t* status, b200moe_stream_t stream);
+
 /* ---- dense bf16 GEMMs on tcgen05 (router projections) ----------------------------------------
  * Replace the cuBLAS calls at kernels/sm75/router.py:235 (logits), :258 (dX), :259 (dW).
  * nt: D(M,N) = A(M,K) * B(N,K)^T      nn: D(M,N) = A(M,K) * B(K,N)

@@ -28,7 +28,41 @@ def test_conv_logits_equal_unfolded_gemm():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("B,S,H,E,K,k", [(4, 512, 256, 16, 4, 2), (2, 300, 512, 64, 3, 6)])
+@pytest.mark.parametrize("B,S,H,E,K", [(2, 256, 128, 64, 4), (3, 384, 320, 128, 2), (1, 128, 64, 64, 1),
+                                       (5, 128, 512, 256, 3)])
+def test_conv_gemms_without_the_unfolded_copy(pkg, B, S, H, E, K):
+    """The GEMMs that read x in place through shifted TMA boxes against the same GEMMs over the unfolded copy:
+    the forward runs the identical MMA sequence (bit-equal logits); dX and dW differ only in summation grouping."""
+    ops = pkg.ops
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(B, S, H, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(E, H, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    gl = torch.randn(B * S, E, generator=g).to(torch.bfloat16).to(DEV)
+    assert ops.conv_direct_ok(S, H)
+    wf = w.permute(0, 2, 1).reshape(E, K * H).contiguous()
+    wb = w.permute(2, 0, 1).reshape(K * E, H).contiguous()
+    xu = ops.conv_unfold(x, K)
+    assert torch.equal(ops.conv_gemm_fwd(x, wf, K), ops.gemm_nt(xu, wf))
+    gx_ref = ops.conv_fold(ops.gemm_nn(gl, wf), B, S, H, K)
+    gx = ops.conv_gemm_dx(gl, wb, B, S, K)
+    assert O.rel_l2(gx.float().cpu(), gx_ref.float().cpu()) < 6e-3
+    # fp32 reference of dX: the fold of the fp32 product
+    gxu32 = (gl.float() @ wf.float()).view(B, S, K, H)
+    gx32 = torch.zeros(B, S, H, device=DEV)
+    for j in range(K):
+        sh = K - 1 - j
+        gx32[:, :S - sh] += gxu32[:, sh:, j]
+    assert O.rel_l2(gx.float().cpu(), gx32.cpu()) < 4e-3
+    gw = ops.conv_gemm_dw(gl, x, K)
+    gw32 = gl.float().t() @ xu.float()
+    assert O.rel_l2(gw.float().cpu(), gw32.cpu()) < 4e-3
+    assert O.rel_l2(ops.gemm_tn(gl, xu).float().cpu(), gw32.cpu()) < 4e-3
+    pkg.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,S,H,E,K,k", [(4, 512, 256, 16, 4, 2), (2, 300, 512, 64, 3, 6), (2, 256, 128, 64, 4, 2),
+                                         (3, 384, 320, 128, 2, 4)])
 def test_fused_conv_router_forward_backward(pkg, B, S, H, E, K, k):
     g = torch.Generator().manual_seed(5)
     x = torch.randn(B, S, H, generator=g).to(torch.bfloat16)

@@ -38,6 +38,9 @@ _SIGNATURES = {
     "b200moe_router_bias_update": (c_int, [c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "b200moe_conv_unfold": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "b200moe_conv_fold": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "b200moe_conv_gemm_fwd": (c_int, [c_void_p] * 3 + [c_int64] * 4 + [c_int, c_void_p, c_void_p]),
+    "b200moe_conv_gemm_dx": (c_int, [c_void_p] * 3 + [c_int64] * 4 + [c_int, c_void_p, c_void_p]),
+    "b200moe_conv_gemm_dw_splitk": (c_int, [c_void_p] * 3 + [c_int64] * 4 + [c_int, c_int64, c_void_p, c_void_p]),
     "b200moe_gemm_nt": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "b200moe_gemm_nn": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "b200moe_gemm_tn_splitk": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,

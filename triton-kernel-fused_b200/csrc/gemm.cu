@@ -146,11 +146,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const uint32_t sa = smem_u32(smem + s * C::STAGE_BYTES);
           const uint32_t sb = sa + C::A_BYTES;
           const int kk = t.k0 + kb * BK;
+          // coordinates of the B boxes (MN-major case) and of the A box (K-major case); a convolution operand
+          // (see GemmParams::conv_taps) replaces the flat row by (position + shift, batch)
+          int a_c0 = kk, a_c1 = m0, a_c2 = 0, b_n0 = t.n0, b_k = kk, b_g = gB;
+          if (p.conv_taps > 0) {
+            if (p.sched == SCHED_DENSE) {
+              const int per_tap = p.conv_C / BK, tap = kb / per_tap;
+              a_c2 = m0 / p.conv_S;
+              a_c1 = m0 - a_c2 * p.conv_S + p.conv_sign * (tap - (p.conv_taps - 1));
+              a_c0 = (kb - tap * per_tap) * BK;
+            } else {
+              const int tap = t.n0 / p.conv_C;
+              b_n0 = t.n0 - tap * p.conv_C;
+              b_g = kk / p.conv_S;
+              b_k = kk - b_g * p.conv_S + tap - (p.conv_taps - 1);
+            }
+          }
           if constexpr (CTAS == 1) {
             const uint32_t full = bar_full + 8 * s;
             mbar_arrive_expect_tx(full, C::STAGE_BYTES);
             if (!p.a_mn) {
-              tma_load_3d(sa, &tmA, full, kk, m0, 0);  // box {64 k, 128 rows}
+              tma_load_3d(sa, &tmA, full, a_c0, a_c1, a_c2);  // box {64 k, 128 rows}
             } else {
 #pragma unroll
               for (int j = 0; j < BM / 64; ++j)  // boxes {64 mn, 64 k-rows}
@@ -165,14 +181,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             } else {
 #pragma unroll
               for (int j = 0; j < BN / 64; ++j)
-                tma_load_3d(sb + j * (64 * BK * 2), &tmB, full, t.n0 + 64 * j, kk, gB);
+                tma_load_3d(sb + j * (64 * BK * 2), &tmB, full, b_n0 + 64 * j, b_k, b_g);
             }
           } else {
             // the leader's barrier counts the bytes of both CTAs
             const uint32_t full = mapa_shared(bar_full + 8 * s, 0);
             if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, 2 * C::STAGE_BYTES);
             if (!p.a_mn) {
-              tma_load_3d_pair(sa, &tmA, full, kk, m0, 0);
+              tma_load_3d_pair(sa, &tmA, full, a_c0, a_c1, a_c2);
             } else {
 #pragma unroll
               for (int j = 0; j < BM / 64; ++j)
@@ -187,7 +203,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
               for (int j = 0; j < BNC / 64; ++j)
                 tma_load_3d_pair(sb + j * (64 * BK * 2), &tmB, full,
-                                 t.n0 + bstep * static_cast<int>(cta_rank) + 64 * j, kk, gB);
+                                 b_n0 + bstep * static_cast<int>(cta_rank) + 64 * j, b_k, b_g);
             }
           }
           if (++s == NSTAGE) {
@@ -794,6 +810,79 @@ int b200moe_gemm_tn_splitk(const void* A, const void* B, float* P, int64_t M, in
   p.D = P; p.ldd = N; p.d_group_stride = M * N; p.status = status;
   const int bn = pick_bn(N);
   return dispatch_bn<EPI_STORE_F32>(bn, a, b, nullptr, nullptr, p, (int)(slices * ceil_div(M, BM) * ceil_div(N, bn)),
+                                    (cudaStream_t)stream);
+}
+
+static int check_conv(const char* who, int64_t B, int64_t S, int64_t H, int64_t E, int taps, int64_t s_mult,
+                      int64_t c_mult64) {
+  B200_CHECK_ARG(B > 0 && S > 0 && taps >= 1 && taps <= 64, B200MOE_E_BAD_SHAPE, "%s: B = %lld, S = %lld, taps = %d", who,
+                 (long long)B, (long long)S, taps);
+  B200_CHECK_ARG(S % s_mult == 0, B200MOE_E_BAD_SHAPE, "%s: S = %lld must be a multiple of %lld", who, (long long)S,
+                 (long long)s_mult);
+  B200_CHECK_ARG(c_mult64 % 64 == 0, B200MOE_E_BAD_SHAPE, "%s: the convolved channel count %lld must be a multiple of 64",
+                 who, (long long)c_mult64);
+  B200_CHECK_ARG(H % 8 == 0 && E % 8 == 0 && H > 0 && E > 0, B200MOE_E_BAD_SHAPE, "%s: H = %lld, E = %lld", who,
+                 (long long)H, (long long)E);
+  B200_CHECK_ARG(B * S < (1LL << 31) && taps * H < (1LL << 31) && taps * E < (1LL << 31), B200MOE_E_BAD_SHAPE,
+                 "%s: extent beyond 2^31", who);
+  return 0;
+}
+
+int b200moe_conv_gemm_fwd(const void* x, const void* wf, void* logits, int64_t B, int64_t S, int64_t H, int64_t E, int taps,
+                          int32_t* status, b200moe_stream_t stream) {
+  B200_CHECK_ARG(x && wf && logits, B200MOE_E_NULL, "conv_gemm_fwd: null pointer");
+  int rc = check_conv("conv_gemm_fwd", B, S, H, E, taps, BM, H);
+  if (rc) return rc;
+  B200_CHECK_ARG(aligned16(logits), B200MOE_E_ALIGN, "conv_gemm_fwd: logits not 16-byte aligned");
+  const int64_t M = B * S, K = taps * H;
+  Operand a{x, 0, S, H, H, B, S * H};       // {H, S, B}: positions outside [0, S) read as zero
+  Operand b{wf, 0, E, K, K, 1, E * K};
+  GemmParams p{};
+  p.sched = SCHED_DENSE; p.M = (int)M; p.N = (int)E; p.K = (int)K; p.num_groups = 1;
+  p.D = logits; p.ldd = E; p.status = status;
+  p.conv_taps = taps; p.conv_S = (int)S; p.conv_C = (int)H; p.conv_sign = 1;
+  const int bn = pick_bn(E);
+  Operand d{logits, 0, M, E, E, 1, M * E};
+  return dispatch_bn<EPI_STORE>(bn, a, b, &d, nullptr, p, (int)(ceil_div(M, BM) * ceil_div(E, bn)), (cudaStream_t)stream);
+}
+
+int b200moe_conv_gemm_dx(const void* grad_logits, const void* wb, void* grad_x, int64_t B, int64_t S, int64_t H, int64_t E,
+                         int taps, int32_t* status, b200moe_stream_t stream) {
+  B200_CHECK_ARG(grad_logits && wb && grad_x, B200MOE_E_NULL, "conv_gemm_dx: null pointer");
+  int rc = check_conv("conv_gemm_dx", B, S, H, E, taps, BM, E);
+  if (rc) return rc;
+  B200_CHECK_ARG(aligned16(grad_x), B200MOE_E_ALIGN, "conv_gemm_dx: grad_x not 16-byte aligned");
+  const int64_t M = B * S, K = taps * E;
+  Operand a{grad_logits, 0, S, E, E, B, S * E};   // {E, S, B}, read (taps - 1) - tap positions ahead
+  Operand b{wb, 1, H, K, H, 1, H * K};            // stored (taps * E, H): MN-major
+  GemmParams p{};
+  p.sched = SCHED_DENSE; p.b_mn = 1; p.M = (int)M; p.N = (int)H; p.K = (int)K; p.num_groups = 1;
+  p.D = grad_x; p.ldd = H; p.status = status;
+  p.conv_taps = taps; p.conv_S = (int)S; p.conv_C = (int)E; p.conv_sign = -1;
+  const int bn = pick_bn(H);
+  Operand d{grad_x, 0, M, H, H, 1, M * H};
+  return dispatch_bn<EPI_STORE>(bn, a, b, &d, nullptr, p, (int)(ceil_div(M, BM) * ceil_div(H, bn)), (cudaStream_t)stream);
+}
+
+int b200moe_conv_gemm_dw_splitk(const void* grad_logits, const void* x, float* P, int64_t B, int64_t S, int64_t H,
+                                int64_t E, int taps, int64_t k_chunk, int32_t* status, b200moe_stream_t stream) {
+  B200_CHECK_ARG(grad_logits && x && P, B200MOE_E_NULL, "conv_gemm_dw_splitk: null pointer");
+  int rc = check_conv("conv_gemm_dw_splitk", B, S, H, E, taps, 64, H);
+  if (rc) return rc;
+  B200_CHECK_ARG(k_chunk > 0 && k_chunk % 64 == 0, B200MOE_E_BAD_SHAPE,
+                 "conv_gemm_dw_splitk: k_chunk = %lld must be a positive multiple of 64", (long long)k_chunk);
+  B200_CHECK_ARG(aligned16(P), B200MOE_E_ALIGN, "conv_gemm_dw_splitk: P not 16-byte aligned");
+  const int64_t K = B * S, N = taps * H;
+  const long long slices = ceil_div(K, k_chunk);
+  Operand a{grad_logits, 1, E, K, E, 1, E * K};   // stored (B*S, E)
+  Operand b{x, 1, H, S, H, B, S * H};             // {H, S, B}: the k rows of tap j are read j - (taps - 1) positions away
+  GemmParams p{};
+  p.sched = SCHED_GROUPED_K; p.a_mn = 1; p.b_mn = 1; p.M = (int)E; p.N = (int)N; p.K = (int)K;
+  p.num_groups = (int)slices; p.k_chunk = (int)k_chunk; p.poffs = nullptr;
+  p.D = P; p.ldd = N; p.d_group_stride = E * N; p.status = status;
+  p.conv_taps = taps; p.conv_S = (int)S; p.conv_C = (int)H; p.conv_sign = 1;
+  const int bn = H % 256 == 0 ? 256 : (H % 128 == 0 ? 128 : 64);   // a tile's columns belong to one tap
+  return dispatch_bn<EPI_STORE_F32>(bn, a, b, nullptr, nullptr, p, (int)(slices * ceil_div(E, BM) * ceil_div(N, bn)),
                                     (cudaStream_t)stream);
 }
 

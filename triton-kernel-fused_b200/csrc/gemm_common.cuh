@@ -55,6 +55,13 @@ struct GemmParams {
   // row_hi <= 0: every row).  Lets a caller run the rows of one group of experts while the rows of the next
   // group are still arriving.
   int row_lo, row_hi;
+  // optional (conv_taps > 0): causal-convolution operand.  The operand's tensor map is {conv_C channels, conv_S
+  // positions, batches} and every 64-wide k-block is loaded `shift` positions away from the tile's own, positions
+  // outside [0, conv_S) reading as zero (the convolution's padding), so the unfolded (rows, taps * C) copy of the
+  // input is never written.  DENSE: operand A, k-block kb = (tap, channel block), shift = conv_sign * (tap -
+  // (conv_taps - 1)); row tiles must not straddle batches (conv_S % 128 == 0).  GROUPED_K by chunks (split-K
+  // weight gradient): operand B, tap = tile column / conv_C, shift = tap - (conv_taps - 1); conv_S % 64 == 0.
+  int conv_taps, conv_S, conv_C, conv_sign;
 };
 
 struct Tile {

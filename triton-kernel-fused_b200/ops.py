@@ -518,3 +518,50 @@ def conv_fold(grad_xu, B, S, H, K):
     gx = torch.empty(B, S, H, dtype=torch.bfloat16, device=grad_xu.device)
     L.check(L.lib().b200moe_conv_fold(L.ptr(grad_xu), B, S, H, int(K), L.ptr(gx), L.stream_of(grad_xu)))
     return gx
+
+
+def conv_direct_ok(S, H):
+    """Shapes the no-copy convolution GEMMs take (forward and weight gradient): row tiles inside one sequence,
+    64-channel k-blocks inside one tap."""
+    return S % 128 == 0 and H % 64 == 0
+
+
+@_op("conv_gemm_fwd", 1)
+def conv_gemm_fwd(x, wf, K):
+    """logits (B*S, E) of the causal K-tap convolution of x (B,S,H) with Wf (E, K*H), x read in place."""
+    L.require_cuda_bf16("x", x); L.require_cuda_bf16("wf", wf)
+    B, S, H = x.shape
+    E = wf.shape[0]
+    logits = torch.empty(B * S, E, dtype=torch.bfloat16, device=x.device)
+    L.check(L.lib().b200moe_conv_gemm_fwd(L.ptr(x), L.ptr(wf), L.ptr(logits), B, S, H, E, int(K),
+                                          L.ptr(L.status_word(x.device)), L.stream_of(x)))
+    return logits
+
+
+@_op("conv_gemm_dx", 1)
+def conv_gemm_dx(grad_logits, wb, B, S, K):
+    """grad_x (B,S,H) from grad_logits (B*S, E) and Wb (K*E, H), Wb[j*E+e, h] = W[e,h,j]."""
+    E, H = grad_logits.shape[1], wb.shape[1]
+    gx = torch.empty(B, S, H, dtype=torch.bfloat16, device=grad_logits.device)
+    L.check(L.lib().b200moe_conv_gemm_dx(L.ptr(grad_logits), L.ptr(wb), L.ptr(gx), B, S, H, E, int(K),
+                                         L.ptr(L.status_word(gx.device)), L.stream_of(gx)))
+    return gx
+
+
+@_op("conv_gemm_dw", 2)
+def conv_gemm_dw(grad_logits, x, K, target_ctas=296):
+    """grad_Wf (E, K*H) = grad_logits (B*S, E)^T @ unfold(x), through fp32 split-K slices, x read in place."""
+    B, S, H = x.shape
+    E = grad_logits.shape[1]
+    rows, N = B * S, K * H
+    bn = 256 if H % 256 == 0 else (128 if H % 128 == 0 else 64)
+    tiles = ((E + 127) // 128) * (N // bn)
+    slices = max(1, min(target_ctas // max(tiles, 1), (rows + 63) // 64))
+    k_chunk = (((rows + slices - 1) // slices) + 63) // 64 * 64
+    slices = (rows + k_chunk - 1) // k_chunk
+    part = torch.empty(slices, E, N, dtype=torch.float32, device=x.device)
+    d = torch.empty(E, N, dtype=torch.bfloat16, device=x.device)
+    L.check(L.lib().b200moe_conv_gemm_dw_splitk(L.ptr(grad_logits), L.ptr(x), L.ptr(part), B, S, H, E, int(K), k_chunk,
+                                                L.ptr(L.status_word(x.device)), L.stream_of(x)))
+    L.check(L.lib().b200moe_splitk_reduce(L.ptr(part), slices, E * N, L.ptr(d), L.stream_of(x)))
+    return d

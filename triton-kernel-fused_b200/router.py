@@ -78,7 +78,10 @@ def fused_mlp_router(x, gate_weight, bias, top_k, num_experts, norm_topk_prob=Tr
 class FusedConvRouter(torch.autograd.Function):
     """Causal-conv router (kernels/sm75/router.py:172-218, FusedConvRouterCuDNN): logits[b,s,e] =
     sum_{j,h} x[b, s-(K-1)+j, h] * W[e,h,j], then the same sigmoid / bias / top-k epilogue.  The conv is one
-    tcgen05 GEMM over the unfolded input; backward = epilogue Jacobian, dX GEMM + fold, split-K dW GEMM."""
+    tcgen05 GEMM whose TMA producer reads x in place, tap by tap, through a (H, S, B) tensor map (S a multiple of
+    128, H of 64; as kernels/sm120/router.py:34-85 does in one launch), or over an unfolded copy of x for other
+    shapes; backward = epilogue Jacobian, dX GEMM (the same way over grad_logits when E is a multiple of 64, else
+    plain GEMM + fold), split-K dW GEMM."""
 
     @staticmethod
     def forward(ctx, x, weight, bias, top_k, num_experts, norm_topk=True, scale=1.0):
@@ -91,26 +94,39 @@ class FusedConvRouter(torch.autograd.Function):
         B, S, H = x.shape
         E, _, K = weight.shape
         L.require(num_experts is None or int(num_experts) == E, "num_experts must equal conv_weight.shape[0]")
-        xu = ops.conv_unfold(x.contiguous(), K)
+        x = x.contiguous()
         wf = weight.permute(0, 2, 1).reshape(E, K * H).contiguous()      # Wf[e, j*H+h] = W[e,h,j]
-        logits = ops.gemm_nt(xu, wf)
+        ctx.direct = ops.conv_direct_ok(S, H)
+        if ctx.direct:
+            xu = x                                                        # read in place by the GEMMs
+            logits = ops.conv_gemm_fwd(x, wf, K)
+        else:
+            xu = ops.conv_unfold(x, K)
+            logits = ops.gemm_nt(xu, wf)
         bias32 = bias.detach().float().contiguous() if bias is not None else None
         idx, w, counts = ops.router_topk_fwd(logits, bias32, top_k, norm_topk and top_k > 1, scale)
         ctx.shape = (B, S, H, E, K)
-        ctx.save_for_backward(xu, wf, logits, idx)
+        ctx.save_for_backward(xu, wf, weight, logits, idx)
         ctx.norm, ctx.scale = bool(norm_topk and top_k > 1), float(scale)
         ctx.mark_non_differentiable(idx, counts)
         return idx, w, counts
 
     @staticmethod
     def backward(ctx, grad_idx, grad_weights, grad_counts):
-        xu, wf, logits, idx = ctx.saved_tensors
+        xu, wf, weight, logits, idx = ctx.saved_tensors
         B, S, H, E, K = ctx.shape
         gl = ops.router_topk_bwd(logits, idx, grad_weights, ctx.norm, ctx.scale)
-        grad_x = ops.conv_fold(ops.gemm_nn(gl, wf), B, S, H, K) if ctx.needs_input_grad[0] else None
+        grad_x = None
+        if ctx.needs_input_grad[0]:
+            if ctx.direct and E % 64 == 0:
+                wb = weight.permute(2, 0, 1).reshape(K * E, H).contiguous()   # Wb[j*E+e, h] = W[e,h,j]
+                grad_x = ops.conv_gemm_dx(gl, wb, B, S, K)
+            else:
+                grad_x = ops.conv_fold(ops.gemm_nn(gl, wf), B, S, H, K)
         grad_w = None
         if ctx.needs_input_grad[1]:
-            grad_w = ops.gemm_tn(gl, xu).view(E, K, H).permute(0, 2, 1).contiguous()
+            gwf = ops.conv_gemm_dw(gl, xu, K) if ctx.direct else ops.gemm_tn(gl, xu)
+            grad_w = gwf.view(E, K, H).permute(0, 2, 1).contiguous()
         return grad_x, grad_w, None, None, None, None, None
 
 
