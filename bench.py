@@ -267,6 +267,10 @@ def measure_layer(cx, w, steps, n_warm, e2e=True):
     ops = pkg.ops
     T, H = w["T"], w["H"]
     layer = _make_layer(pkg, w, dev, seed=0, world=world)
+    if w["precision"] == "mxfp8":
+        # no optimizer step runs between the timed steps, so the stacks never change: with the cache of quantised
+        # weights on, every step after the first would skip the weight quantisation that a training step pays
+        importlib.import_module(PKG + ".mxfp8").WEIGHT_CACHE = False
     params = [layer.gate.weight, layer.gate_up_proj, layer.down_proj]
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     x_dev = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)

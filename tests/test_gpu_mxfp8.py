@@ -135,6 +135,72 @@ def test_moe_mxfp8_forward_backward(pkg, T, H, E, I, k):
     assert O.rel_l2(out.float().cpu(), full) < 0.1
 
 
+def test_quantised_weights_are_reused_until_the_stack_changes(pkg):
+    """The cache of quantised expert stacks: a second call on unchanged weights launches no weight quantiser and
+    returns the same bits; an in-place update (what an optimizer step does) invalidates it; a forward-only call
+    that cached the row-wise copy alone is followed correctly by a call that needs the transposed copy too."""
+    import importlib
+    mx = importlib.import_module("triton-kernel-fused_b200.mxfp8")
+    T, H, E, I, k = 512, 256, 4, 128, 2
+    inp = O.make_inputs(T, H, E, I, k, seed=52, bias_std=0.01, dtype=torch.bfloat16)
+    idx, w, _, _ = O.mlp_router_fwd(inp["x"], inp["gate_weight"], inp["bias"], k)
+    x, idx_d, w_d = inp["x"].to(DEV), idx.to(DEV), w.to(DEV)
+    gu = inp["gate_up"].to(DEV).requires_grad_(True)
+    dn = inp["down"].to(DEV).requires_grad_(True)
+    codes = torch.zeros(E, dtype=torch.int32, device=DEV)
+    seen = []
+    mx._QUANTISED.clear()
+    assert mx.WEIGHT_CACHE
+    weights = {gu.data_ptr(): "gate_up", dn.data_ptr(): "down"}
+    real_rows, real_both = pkg.ops.mxfp8_quant_rows, pkg.ops.mxfp8_quant_both
+
+    def spy(fn):
+        def wrapped(t, *a, **kw):
+            if t.data_ptr() in weights:
+                seen.append(weights[t.data_ptr()])
+            return fn(t, *a, **kw)
+        return wrapped
+
+    def run(grad):
+        seen.clear()
+        pkg.ops.mxfp8_quant_rows, pkg.ops.mxfp8_quant_both = spy(real_rows), spy(real_both)
+        try:
+            if grad:
+                gu.grad = dn.grad = None
+                out = pkg.moe_mxfp8(x, idx_d, w_d, gu, dn, codes)
+                out.float().sum().backward()
+                return out.detach().clone(), gu.grad.clone(), dn.grad.clone()
+            with torch.no_grad():
+                return pkg.moe_mxfp8(x, idx_d, w_d, gu, dn, codes).clone(), None, None
+        finally:
+            pkg.ops.mxfp8_quant_rows, pkg.ops.mxfp8_quant_both = real_rows, real_both
+
+    o_inf, _, _ = run(False)
+    assert sorted(seen) == ["down", "gate_up"]    # first call: both stacks quantised (row-wise only)
+    o_inf2, _, _ = run(False)
+    assert seen == [] and torch.equal(o_inf, o_inf2)
+    o0, _, _ = run(True)                          # weight gradients only: the copies kept so far still serve
+    assert seen == [] and torch.equal(o0, o_inf)
+    x.requires_grad_(True)                        # grad_x needs gate_up quantised along 2I too: the row-only entry does not serve
+    o1, g1, d1 = run(True)
+    assert seen == ["gate_up"]
+    o2, g2, d2 = run(True)
+    assert seen == []
+    assert torch.equal(o1, o2) and torch.equal(g1, g2) and torch.equal(d1, d2) and torch.equal(o1, o_inf)
+    with torch.no_grad():
+        gu.mul_(0.5)                              # version moves: the stale copy must not be used
+    o3, _, _ = run(True)
+    assert seen == ["gate_up"]                    # gate_up re-quantised, down still cached
+    mx.WEIGHT_CACHE = False
+    try:
+        o4, _, _ = run(True)
+        assert sorted(seen) == ["down", "gate_up"] and torch.equal(o3, o4)
+    finally:
+        mx.WEIGHT_CACHE = True
+    assert not torch.equal(o3, o1)
+    pkg.check_status()
+
+
 def test_mxfp8_rejects_unaligned_width(pkg):
     x = torch.zeros(8, 192, dtype=torch.bfloat16, device=DEV)
     idx = torch.zeros(8, 1, dtype=torch.int64, device=DEV)

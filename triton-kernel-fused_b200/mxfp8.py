@@ -2,8 +2,10 @@
 run on tcgen05 block-scaled MMAs over e4m3 operands with E8M0 block-32 scales.
 
 The reference has no MXFP8 path; the signature mirrors `moe` (kernels/sm75/moe.py:838) and the
-numerics follow the OCP MX convention (see include/b200moe.h).  Master weights stay bf16 and are
-quantised on every call; each GEMM quantises its operands along its own reduction dimension
+numerics follow the OCP MX convention (see include/b200moe.h).  Master weights stay bf16; their quantised
+copies are kept until the weights change (autograd version counter: an optimizer step invalidates them, the
+micro-batches of a gradient-accumulation step and inference calls reuse them; `WEIGHT_CACHE = False` turns it
+off); each GEMM quantises its operands along its own reduction dimension
 (row-wise for forward/dgrad activations, transposed copies for weights in dgrad and for both
 operands of the wgrads).  Needs d_model % 128 == 0 and d_ff % 128 == 0.
 """
@@ -24,6 +26,27 @@ __all__ = ["moe_mxfp8", "FUSE_QUANT_EPILOGUE"]
 # row quantiser) instead of a separate pass.  Off by default: it measured 2 % slower on the full step,
 # because the pair kernel's single-buffered accumulator exposes every cycle added to the epilogue.
 FUSE_QUANT_EPILOGUE = os.environ.get("B200MOE_MXFP8_FUSE_QUANT", "0") == "1"
+
+# Quantised copies of the expert stacks are reused while the stacks are unchanged (B200MOE_MXFP8_WEIGHT_CACHE=0: off).
+# They cost one byte per weight and direction: 2 x the bf16 stack's bytes when both directions are kept.
+WEIGHT_CACHE = os.environ.get("B200MOE_MXFP8_WEIGHT_CACHE", "1") == "1"
+_QUANTISED = {}      # id(stack) -> (weak reference, version, data pointer, has the transposed copy, tensors)
+
+
+def _quantised_weights(stack, rows_fn, both_fn, both):
+    """(q, sf) or (q, sf, qt, sft) of an expert stack, from the cache when the stack is the same tensor, at the same
+    address, with the same autograd version as when the copies were made (every in-place update moves the version)."""
+    if not WEIGHT_CACHE:
+        return both_fn() if both else rows_fn()
+    import weakref
+    key = id(stack)
+    hit = _QUANTISED.get(key)
+    if hit is not None and hit[0]() is stack and hit[1] == stack._version and hit[2] == stack.data_ptr() and (hit[3] or not both):
+        return hit[4] if both or not hit[3] else hit[4][:2]
+    res = both_fn() if both else rows_fn()
+    _QUANTISED[key] = (weakref.ref(stack, lambda _r, k=key: _QUANTISED.pop(k, None)), stack._version, stack.data_ptr(),
+                       both, res)
+    return res
 
 
 class _MoEMxfp8(torch.autograd.Function):
@@ -55,10 +78,12 @@ class _MoEMxfp8(torch.autograd.Function):
         # tensors that the backward needs quantised along their other dimension are quantised both ways in
         # one pass over DRAM, and the transposed copy is what the backward keeps
         wgt = wgtsf = wtq = wtsf = it = itsf = None
+        res = _quantised_weights(gate_up_proj, lambda: ops.mxfp8_quant_rows(gate_up_proj.view(E * twoI, H), interleave_I=I),
+                                 lambda: ops.mxfp8_quant_both(gate_up_proj, interleave_I=I), need_x)   # + (E, H, 2I)
         if need_x:
-            wq, wsf, wgt, wgtsf = ops.mxfp8_quant_both(gate_up_proj, interleave_I=I)       # + (E, H, 2I)
+            wq, wsf, wgt, wgtsf = res
         else:
-            wq, wsf = ops.mxfp8_quant_rows(gate_up_proj.view(E * twoI, H), interleave_I=I)
+            wq, wsf = res
         gate_up = torch.empty(perm.cap, twoI, dtype=torch.bfloat16, device=dev)
         inter = torch.empty(perm.cap, I, dtype=torch.bfloat16, device=dev)
         fuse = FUSE_QUANT_EPILOGUE and not need_dn
@@ -70,10 +95,12 @@ class _MoEMxfp8(torch.autograd.Function):
             iq, isf, it, itsf = ops.mxfp8_quant_both(inter)                                 # + (I, rows)
         else:
             iq, isf = ops.mxfp8_quant_rows(inter)
+        res = _quantised_weights(down_proj, lambda: ops.mxfp8_quant_rows(down_proj.view(E * H, I)),
+                                 lambda: ops.mxfp8_quant_both(down_proj), need_x or need_gu)           # + (E, I, H)
         if need_x or need_gu:
-            dq, dsf, wtq, wtsf = ops.mxfp8_quant_both(down_proj)                            # + (E, I, H)
+            dq, dsf, wtq, wtsf = res
         else:
-            dq, dsf = ops.mxfp8_quant_rows(down_proj.view(E * H, I))
+            dq, dsf = res
         eo = torch.empty(perm.cap, H, dtype=torch.bfloat16, device=dev)
         ops.mxfp8_expert_gemm(ops.EPI_STORE, iq, isf, dq, dsf, perm, H, I, I, eo)
         out = ops.combine(eo, w32, perm)
