@@ -123,7 +123,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int total = total_tiles(p, TN, TM);
+  constexpr bool WINDOW = (EPI == EPI_SWIGLU || EPI == EPI_GLU_BWD);   // entry points with a row window
+  constexpr bool CONV = (EPI == EPI_STORE || EPI == EPI_STORE_F32);     // entry points with a convolution operand
+  const int total = total_tiles(p, TN, TM, WINDOW);
+  const int row_base = (WINDOW && p.row_hi > 0) ? p.row_lo : 0;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (each CTA)
@@ -132,7 +135,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t ph = 0;
       bool ok = true;
       for (int tile = first_tile; tile < total && ok; tile += tile_step) {
-        const Tile t = get_tile(p, tile, TN, TM, 64, order);
+        const Tile t = get_tile(p, tile, TN, TM, 64, order, row_base);
         const int gB = (p.sched == SCHED_GROUPED_M) ? t.g : 0;
         const int m0 = t.m0 + BM * static_cast<int>(cta_rank);
         // a last pair tile with at most BN/2 live columns runs as a 256 x BN/2 MMA: each CTA then
@@ -149,7 +152,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           // coordinates of the B boxes (MN-major case) and of the A box (K-major case); a convolution operand
           // (see GemmParams::conv_taps) replaces the flat row by (position + shift, batch)
           int a_c0 = kk, a_c1 = m0, a_c2 = 0, b_n0 = t.n0, b_k = kk, b_g = gB;
-          if (p.conv_taps > 0) {
+          if (CONV && p.conv_taps > 0) {
             if (p.sched == SCHED_DENSE) {
               const int per_tap = p.conv_C / BK, tap = kb / per_tap;
               a_c2 = m0 / p.conv_S;
@@ -227,7 +230,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t ph = 0;
       bool ok = true;
       for (int tile = first_tile; tile < total && ok; tile += tile_step, ++it) {
-        const Tile t = get_tile(p, tile, TN, TM, 64, order);
+        const Tile t = get_tile(p, tile, TN, TM, 64, order, row_base);
         const int buf = it & 1;
         if (!mbar_wait(bar_tempty + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag, ST_WAIT_MMA_TMEM)) break;
         tc_fence_after();
@@ -275,7 +278,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     uint32_t epi_phase = 0;   // parity of this warp's GLU-backward load barrier
     int it = 0;
     for (int tile = first_tile; tile < total; tile += tile_step, ++it) {
-      const Tile t = get_tile(p, tile, TN, TM, 64, order);
+      const Tile t = get_tile(p, tile, TN, TM, 64, order, row_base);
       const int buf = it & 1;
       int act_code = 0;   // activation of this tile's expert (uniform over the tile)
       if constexpr (POLY) act_code = p.act_codes[t.g];

@@ -76,13 +76,15 @@ __device__ __forceinline__ int sym_tiles_per_group(const GemmParams& p, int TN, 
   return n;
 }
 
-__device__ __forceinline__ int total_tiles(const GemmParams& p, int TN, int TM) {
+// `window`: the launch honours GemmParams::row_lo / row_hi (only the kernels whose entry points take a row window
+// are compiled with it, so that the others carry no code or registers for it)
+__device__ __forceinline__ int total_tiles(const GemmParams& p, int TN, int TM, bool window = false) {
   const int nt = (p.N + TN - 1) / TN;
   if (p.sched == SCHED_GROUPED_M && p.sym_rows > 0) return p.num_groups * sym_tiles_per_group(p, TN, TM);
   if (p.sched == SCHED_DENSE) return ((p.M + TM - 1) / TM) * nt;
   if (p.sched == SCHED_GROUPED_M) {
     const int rows = p.poffs[p.num_groups];
-    return ((p.row_hi > 0 ? max(min(rows, p.row_hi) - p.row_lo, 0) : rows) / TM) * nt;
+    return ((window && p.row_hi > 0 ? max(min(rows, p.row_hi) - p.row_lo, 0) : rows) / TM) * nt;
   }
   return ((p.M + TM - 1) / TM) * nt * p.num_groups;
 }
@@ -107,7 +109,7 @@ __device__ __forceinline__ const int* build_group_order(const GemmParams& p, int
 }
 
 __device__ __forceinline__ Tile get_tile(const GemmParams& p, int tile, int TN, int TM, int BK = 64,
-                                         const int* order = nullptr) {
+                                         const int* order = nullptr, int row_base = 0) {
   Tile t;
   const int nt = (p.N + TN - 1) / TN;
   if (p.sched == SCHED_GROUPED_K) {
@@ -144,7 +146,7 @@ __device__ __forceinline__ Tile get_tile(const GemmParams& p, int tile, int TN, 
     t.nkb = (p.K + BK - 1) / BK;
   } else {
     const int mi = tile / nt;
-    t.m0 = mi * TM + (p.row_hi > 0 ? p.row_lo : 0);
+    t.m0 = mi * TM + row_base;   // first row of the launch's row window (0: every row)
     t.n0 = (tile - mi * nt) * TN;
     t.g = (p.sched == SCHED_GROUPED_M) ? p.tile_expert[t.m0 / B200MOE_TILE_M] : 0;
     t.k0 = 0;
