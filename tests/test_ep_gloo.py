@@ -44,6 +44,28 @@ def _worker(rank, world, port, cfg, skew, q):
         local_counts = torch.bincount(idx[sl].flatten(), minlength=E).to(torch.int32)
         dist.all_reduce(local_counts)
         assert torch.equal(local_counts, counts)
+        # the layers' load-balance loop: per-rank counts accumulated over two forwards, summed over the ranks
+        layer_mod = importlib.import_module("triton-kernel-fused_b200.layer")
+
+        class Loop(layer_mod.LoadBalanceMixin, torch.nn.Module):
+            def __init__(self):
+                super().__init__()
+                self._init_load(E)
+
+            def _load_group(self):
+                return (None,)
+
+        loop = Loop()
+        mine = torch.bincount(idx[sl].flatten(), minlength=E).to(torch.int32)
+        loop._record_counts(mine)
+        loop._record_counts(mine)
+        assert torch.equal(loop._global_load(), 2 * counts.long())
+        stats = loop.load_stats()
+        assert stats["load"] == (2 * counts.long()).tolist() and stats["tokens_routed"] == 2 * T * k
+        assert stats["idle_experts"] == int((counts == 0).sum())
+        loop.eval()
+        loop._record_counts(mine)                                    # evaluation forwards do not count as load
+        assert torch.equal(loop.load, 2 * mine.long())
         q.put((rank, out.detach(), x.grad, wt.grad, gu.grad, dn.grad))
     finally:
         dist.destroy_process_group()

@@ -265,6 +265,35 @@ def test_layer_module_vs_oracle(pkg):
     assert (layer.bias != inp["bias"].to(DEV)).any()
 
 
+def test_load_balance_loop_accumulates_between_bias_updates(pkg):
+    """The reference's training loop (.autoresearch/train_grok_moe.py:79-80, 86-90): the load of every training
+    forward since the last update is summed, the update uses the sum and clears it; evaluation forwards do not
+    count; a second update without a forward changes nothing."""
+    T, H, E, I, k = 1024, 256, 8, 128, 2
+    inp = O.make_inputs(T, H, E, I, k, seed=13, bias_std=0.05, dtype=torch.bfloat16)
+    layer = pkg.MoELayer(H, I, E, top_k=k).to(DEV).to(torch.bfloat16)
+    with torch.no_grad():
+        layer.gate.weight.copy_(inp["gate_weight"])
+        layer.bias.copy_(inp["bias"])
+    x1, x2 = inp["x"][:T // 2].to(DEV), inp["x"][T // 2:].to(DEV)
+    with torch.no_grad():
+        layer(x1)
+        c1 = layer.last_counts.clone().long()
+        layer(x2)
+        c2 = layer.last_counts.clone().long()
+        layer.eval()
+        layer(x1)                                     # not counted
+        layer.train()
+    assert torch.equal(layer.load, c1 + c2) and layer.load.dtype == torch.int64
+    st = layer.load_stats()
+    assert st["load"] == (c1 + c2).tolist() and st["tokens_routed"] == T * k
+    ref = O.router_bias_update(inp["bias"].clone(), (c1 + c2).cpu(), 0.01)
+    layer.update_bias(0.01)
+    assert torch.equal(layer.bias.cpu(), ref) and int(layer.load.sum()) == 0
+    layer.update_bias(0.01)                           # nothing routed since: no change
+    assert torch.equal(layer.bias.cpu(), ref)
+
+
 def test_skewed_routing_with_empty_experts(pkg):
     """Zipf-skewed logit bias (reduced size of the many-expert skewed config): some experts get no
     tokens; their weight gradients are exactly zero and nothing is NaN."""

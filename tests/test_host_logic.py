@@ -167,3 +167,23 @@ def test_expert_groups_split_local_experts_by_rows():
     assert ep.expert_groups([0, 0, 256, 256], 2) == [(0, 3, 0, 256)] or ep.expert_groups([0, 0, 256, 256], 2) == [(0, 4, 0, 256)]
     assert ep.expert_groups([0, 0, 0, 0], 2) == []
     assert ep.expert_groups([], 2) == []
+
+
+def test_load_telemetry_figures():
+    """`load_stats` of the layers' load-balance mixin: the figures follow from the accumulated counts."""
+    layer_mod = importlib.import_module("triton-kernel-fused_b200.layer")
+
+    class Loop(layer_mod.LoadBalanceMixin, torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self._init_load(4)
+
+    loop = Loop()
+    assert loop.load_stats() == {"load": [0, 0, 0, 0], "tokens_routed": 0, "max_over_mean": 0.0, "min_over_mean": 0.0,
+                                 "cv": 0.0, "idle_experts": 4}
+    loop._record_counts(torch.tensor([6, 2, 0, 0], dtype=torch.int32))
+    loop._record_counts(torch.tensor([2, 2, 4, 0], dtype=torch.int32))
+    st = loop.load_stats()
+    assert st["load"] == [8, 4, 4, 0] and st["tokens_routed"] == 16 and st["idle_experts"] == 1
+    assert st["max_over_mean"] == 2.0 and st["min_over_mean"] == 0.0
+    assert abs(st["cv"] - (8.0 ** 0.5) / 4.0) < 1e-12          # std of (8,4,4,0) = sqrt(8), mean 4

@@ -25,7 +25,8 @@ import torch.nn as nn
 from . import _lib as L
 from . import ops as _cuda_ops
 from .moe import _amp_cast
-from .router import fused_mlp_router, router_bias_update
+from .layer import LoadBalanceMixin
+from .router import fused_mlp_router
 
 __all__ = ["ExpertParallelMoELayer", "ep_moe", "exchange_plan"]
 
@@ -114,7 +115,7 @@ def ep_moe(hidden, top_k_indices, top_k_weights, gate_up_proj_local, down_proj_l
                                     group, num_experts, _cuda_ops if _kernels is None else _kernels)
 
 
-class ExpertParallelMoELayer(nn.Module):
+class ExpertParallelMoELayer(LoadBalanceMixin, nn.Module):
     """Router replicated on every rank, E/W experts per rank.  transport = "nccl" moves rows with
     all_to_all_single; "p2p" uses the peer-memory kernels of csrc/ep.cu (rows are pulled over NVLink
     inside the gather and combine kernels; needs torch symmetric memory and a fixed token count).  Gradients of the replicated router
@@ -164,12 +165,17 @@ class ExpertParallelMoELayer(nn.Module):
         self.down_proj = nn.Parameter(torch.randn(self.local_experts, H, I) * init_std)
         self.register_buffer("bias", torch.zeros(E, dtype=torch.float32))
         self.norm_topk_prob, self.routed_scaling_factor = norm_topk_prob, routed_scaling_factor
-        self.last_counts = None
+        self._init_load(E)
 
     def _apply(self, fn, *a, **kw):
         super()._apply(fn, *a, **kw)
         self.bias.data = self.bias.data.float()
         return self
+
+    def _load_group(self):
+        # counts are those of this rank's tokens: the load-balance step and the telemetry sum them over the ranks
+        # (the reference leaves that all-reduce to the caller, kernels/sm75/router.py:293-297)
+        return (self.group,)
 
     def _pipeline(self, flat):
         idx, w, counts = fused_mlp_router(flat, self.gate.weight, self.bias, self.top_k, self.num_experts,
@@ -190,7 +196,8 @@ class ExpertParallelMoELayer(nn.Module):
         flat = x.reshape(-1, shape[-1])
         n = self.overlap_chunks
         if n == 1 or flat.shape[0] < n:
-            out, self.last_counts = self._pipeline(flat)
+            out, counts = self._pipeline(flat)
+            self._record_counts(counts)
             return out.reshape(shape)
         if self._streams is None:
             self._streams = [torch.cuda.Stream(device=flat.device) for _ in range(n)]
@@ -207,15 +214,5 @@ class ExpertParallelMoELayer(nn.Module):
             outs.append(o)
         for st in self._streams:
             cur.wait_stream(st)
-        self.last_counts = counts
+        self._record_counts(counts)
         return torch.cat(outs).reshape(shape)
-
-    @torch.no_grad()
-    def update_bias(self, u):
-        """All-reduce the per-rank counts (the reference leaves this to the caller,
-        kernels/sm75/router.py:293-297), then apply the sign update identically on every rank."""
-        if self.last_counts is None:
-            return
-        c = self.last_counts.clone()
-        dist.all_reduce(c, group=self.group)
-        router_bias_update(self.bias, c, u)

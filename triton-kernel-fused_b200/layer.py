@@ -10,10 +10,63 @@ from .moe import moe
 from .mxfp8 import moe_mxfp8
 from .router import fused_mlp_router, router_bias_update
 
-__all__ = ["MoELayer"]
+__all__ = ["MoELayer", "LoadBalanceMixin"]
 
 
-class MoELayer(nn.Module):
+class LoadBalanceMixin:
+    """The load-balance loop around the layer, as the reference's training module keeps it
+    (.autoresearch/train_grok_moe.py:70,79-80,86-90): `load` accumulates the per-expert counts of every training
+    forward since the last bias update; `update_bias(u)` applies b += u * sign(mean(load) - load) on the accumulated
+    load and clears it; `load_stats()` is the per-expert telemetry.  With several ranks (`_load_group()` not None)
+    the load is summed over the ranks first, so every rank applies the same update."""
+
+    def _init_load(self, E):
+        self.register_buffer("load", torch.zeros(E, dtype=torch.int64))
+        self.last_counts = None
+
+    def _load_group(self):
+        return None            # (group,) for layers whose counts are per rank; None = this process sees every token
+
+    def _record_counts(self, counts):
+        self.last_counts = counts
+        if self.training and counts is not None:
+            self.load += counts
+
+    def _global_load(self, counts=None):
+        if counts is not None:
+            return counts
+        c = self.load.clone()
+        g = self._load_group()
+        if g is not None:
+            import torch.distributed as dist
+            dist.all_reduce(c, group=g[0])
+        return c
+
+    @torch.no_grad()
+    def update_bias(self, u, counts=None):
+        """Load-balance step on the load accumulated since the last call (or on `counts`, already global, when
+        given).  No forward since the last call: nothing happens."""
+        if counts is None and self.last_counts is None:
+            return
+        router_bias_update(self.bias, self._global_load(counts), u)
+        self.load.zero_()
+        self.last_counts = None if counts is None else self.last_counts
+
+    @torch.no_grad()
+    def load_stats(self):
+        """Per-expert load since the last bias update (global over the ranks): the counts and the figures a training
+        loop logs.  Reads the device (one synchronising copy)."""
+        c = self._global_load().double().cpu()
+        total, E = float(c.sum()), c.numel()
+        mean = total / E if E else 0.0
+        return {"load": c.long().tolist(), "tokens_routed": int(total),
+                "max_over_mean": float(c.max() / mean) if mean > 0 else 0.0,
+                "min_over_mean": float(c.min() / mean) if mean > 0 else 0.0,
+                "cv": float(c.std(unbiased=False) / mean) if mean > 0 else 0.0,
+                "idle_experts": int((c == 0).sum())}
+
+
+class MoELayer(LoadBalanceMixin, nn.Module):
     def __init__(self, H, I, E, top_k=2, norm_topk_prob=True, routed_scaling_factor=1.0, init_std=0.02,
                  precision="bf16", act_codes=None, learnable_situ=False):
         """act_codes: one activation code per expert (default all 0 = SiLU-GLU); Identity (3) / Zero (4)
@@ -39,11 +92,12 @@ class MoELayer(nn.Module):
         self.num_experts = E
         self.norm_topk_prob = norm_topk_prob
         self.routed_scaling_factor = routed_scaling_factor
-        self.last_counts = None
+        self._init_load(E)
 
     def _apply(self, fn, *a, **kw):
         super()._apply(fn, *a, **kw)
         self.bias.data = self.bias.data.float()        # the selection bias stays fp32
+        self.load.data = self.load.data.long()
         if self.act_params is not None:
             self.act_params.data = self.act_params.data.float()
         return self
@@ -53,14 +107,7 @@ class MoELayer(nn.Module):
         flat = x.reshape(-1, shape[-1])
         idx, w, counts = fused_mlp_router(flat, self.gate.weight, self.bias, self.top_k, self.num_experts,
                                           self.norm_topk_prob, self.routed_scaling_factor, return_counts=True)
-        self.last_counts = counts
+        self._record_counts(counts)
         fn = moe_mxfp8 if self.precision == "mxfp8" else moe
         out = fn(flat, idx, w, self.gate_up_proj, self.down_proj, self.act_codes, self.act_params)
         return out.reshape(shape)
-
-    @torch.no_grad()
-    def update_bias(self, u, counts=None):
-        """Load-balance step: pass the all-reduced counts when running on several ranks."""
-        c = self.last_counts if counts is None else counts
-        if c is not None:
-            router_bias_update(self.bias, c, u)
