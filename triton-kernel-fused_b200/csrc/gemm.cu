@@ -57,7 +57,9 @@ struct Cfg {
 };
 
 
-// POLY (GLU epilogues only): per-expert activation codes 0 / 1 / 5 (p.act_codes); false = SiLU for every expert
+// POLY: the variant of the kernel.  GLU epilogues: per-expert activation codes 0 / 1 / 5 (p.act_codes); false =
+// SiLU for every expert.  Store epilogues (EPI_STORE, EPI_STORE_F32): a convolution operand (p.conv_taps), compiled
+// only into the instantiations the conv-router entry points launch, so that the expert GEMMs carry no code for it.
 template <int BN, int EPI, int CTAS, bool POLY = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -124,13 +126,66 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   constexpr bool WINDOW = (EPI == EPI_SWIGLU || EPI == EPI_GLU_BWD);   // entry points with a row window
-  constexpr bool CONV = (EPI == EPI_STORE || EPI == EPI_STORE_F32);     // entry points with a convolution operand
+  constexpr bool CONV = POLY && (EPI == EPI_STORE || EPI == EPI_STORE_F32);   // launched by the conv-router entry points
   const int total = total_tiles(p, TN, TM, WINDOW);
   const int row_base = (WINDOW && p.row_hi > 0) ? p.row_lo : 0;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (each CTA)
-    if (lane == 0) {
+    if constexpr (CTAS == 2 && !CONV) {
+      // Pair tiles: the up to four boxes of a stage (one or two of A, one or two of B) are issued by four lanes in
+      // ONE instruction, each lane with its own tensor map, destination and coordinates, instead of by one lane
+      // in up to four instructions.  The producer's time between "stage free" and "loads issued" is what an empty
+      // ring waits for: with both operands MN-major (the weight-gradient GEMMs, four boxes per stage) the
+      // one-lane producer could not keep up with the MMAs, and this form made those launches 12-13 % faster.
+      if (lane < 4) {
+        const bool isA = lane < 2;
+        const int j = lane & 1;
+        const bool mn = isA ? (p.a_mn != 0) : (EPI != EPI_SWIGLU && p.b_mn != 0);
+        const int nbox = !mn ? 1 : (isA ? BM / 64 : BNC / 64);
+        const bool active = j < nbox;
+        const CUtensorMap* tm = isA ? &tmA : &tmB;
+        const uint32_t dst_off = (isA ? 0u : static_cast<uint32_t>(C::A_BYTES)) + static_cast<uint32_t>(j) * (64 * BK * 2);
+        const uint32_t full0 = mapa_shared(bar_full, 0);
+        const bool expects = (lane == 0 && cta_rank == 0);
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int tile = first_tile; tile < total && ok; tile += tile_step) {
+          const Tile t = get_tile(p, tile, TN, TM, 64, order, row_base);
+          const int gB = (p.sched == SCHED_GROUPED_M) ? t.g : 0;
+          const int m0 = t.m0 + BM * static_cast<int>(cta_rank);
+          const int bstep = (EPI != EPI_SWIGLU && p.N - t.n0 <= BN / 2) ? BNC / 2 : BNC;
+          // this lane's box: the coordinate that does not move with k, and the group
+          int fixed, grp;
+          if (isA) {
+            fixed = m0 + (mn ? 64 * j : 0);
+            grp = 0;
+          } else if constexpr (EPI == EPI_SWIGLU) {
+            fixed = t.n0;
+            grp = 2 * gB + static_cast<int>(cta_rank);
+          } else {
+            fixed = t.n0 + bstep * static_cast<int>(cta_rank) + (mn ? 64 * j : 0);
+            grp = gB;
+          }
+          int kk = t.k0;
+          for (int kb = 0; kb < t.nkb; ++kb, kk += BK) {
+            if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, ST_WAIT_PRODUCER)) {
+              ok = false;
+              break;
+            }
+            if (expects) mbar_arrive_expect_tx(bar_full + 8 * s, 2 * C::STAGE_BYTES);
+            if (active)
+              tma_load_3d_pair(smem_u32(smem + s * C::STAGE_BYTES) + dst_off, tm, full0 + 8 * s, mn ? fixed : kk,
+                               mn ? kk : fixed, grp);
+            if (++s == NSTAGE) {
+              s = 0;
+              ph ^= 1;
+            }
+          }
+        }
+      }
+    } else if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -281,7 +336,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const Tile t = get_tile(p, tile, TN, TM, 64, order, row_base);
       const int buf = it & 1;
       int act_code = 0;   // activation of this tile's expert (uniform over the tile)
-      if constexpr (POLY) act_code = p.act_codes[t.g];
+      if constexpr (POLY && (EPI == EPI_SWIGLU || EPI == EPI_GLU_BWD)) act_code = p.act_codes[t.g];
       const int row0 = t.m0 + BM * static_cast<int>(cta_rank) + q * 32;   // first row of this warp
       const long long row = static_cast<long long>(row0) + lane;
       // GLU backward works on four 32-column sub-chunks per warp with two sets of (gate, up) boxes of
@@ -751,7 +806,7 @@ static int dispatch_bn(int bn, const Operand& A, const Operand& B, const Operand
     case 128: return launch<128, EPI, 1, POLY>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
     default:
       if constexpr (EPI == EPI_STORE || EPI == EPI_STORE_F32)
-        return launch<64, EPI, 1>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
+        return launch<64, EPI, 1, POLY>(tmA, tmB, tmD, tmD2, p, max_tiles, stream);
       set_error("tile width %d not built for this epilogue", bn);
       return B200MOE_E_UNSUPPORTED;
   }
@@ -846,7 +901,7 @@ int b200moe_conv_gemm_fwd(const void* x, const void* wf, void* logits, int64_t B
   p.conv_taps = taps; p.conv_S = (int)S; p.conv_C = (int)H; p.conv_sign = 1;
   const int bn = pick_bn(E);
   Operand d{logits, 0, M, E, E, 1, M * E};
-  return dispatch_bn<EPI_STORE>(bn, a, b, &d, nullptr, p, (int)(ceil_div(M, BM) * ceil_div(E, bn)), (cudaStream_t)stream);
+  return dispatch_bn<EPI_STORE, true>(bn, a, b, &d, nullptr, p, (int)(ceil_div(M, BM) * ceil_div(E, bn)), (cudaStream_t)stream);
 }
 
 int b200moe_conv_gemm_dx(const void* grad_logits, const void* wb, void* grad_x, int64_t B, int64_t S, int64_t H, int64_t E,
@@ -864,7 +919,7 @@ int b200moe_conv_gemm_dx(const void* grad_logits, const void* wb, void* grad_x, 
   p.conv_taps = taps; p.conv_S = (int)S; p.conv_C = (int)E; p.conv_sign = -1;
   const int bn = pick_bn(H);
   Operand d{grad_x, 0, M, H, H, 1, M * H};
-  return dispatch_bn<EPI_STORE>(bn, a, b, &d, nullptr, p, (int)(ceil_div(M, BM) * ceil_div(H, bn)), (cudaStream_t)stream);
+  return dispatch_bn<EPI_STORE, true>(bn, a, b, &d, nullptr, p, (int)(ceil_div(M, BM) * ceil_div(H, bn)), (cudaStream_t)stream);
 }
 
 int b200moe_conv_gemm_dw_splitk(const void* grad_logits, const void* x, float* P, int64_t B, int64_t S, int64_t H,
@@ -885,7 +940,7 @@ int b200moe_conv_gemm_dw_splitk(const void* grad_logits, const void* x, float* P
   p.D = P; p.ldd = N; p.d_group_stride = E * N; p.status = status;
   p.conv_taps = taps; p.conv_S = (int)S; p.conv_C = (int)H; p.conv_sign = 1;
   const int bn = H % 256 == 0 ? 256 : (H % 128 == 0 ? 128 : 64);   // a tile's columns belong to one tap
-  return dispatch_bn<EPI_STORE_F32>(bn, a, b, nullptr, nullptr, p, (int)(slices * ceil_div(E, BM) * ceil_div(N, bn)),
+  return dispatch_bn<EPI_STORE_F32, true>(bn, a, b, nullptr, nullptr, p, (int)(slices * ceil_div(E, BM) * ceil_div(N, bn)),
                                     (cudaStream_t)stream);
 }
 

@@ -401,7 +401,15 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const int total = total_tiles(p, TN, TM);
 
   if (warp == 0) {
-    if (lane == 0) {   // ---------------------------------------------------------- producer (each CTA)
+    // ------------------------------------------------------------------------------ producer (each CTA)
+    // The four boxes of a stage (A, B, the A scale atom, the two B scale atoms) are issued by four lanes in ONE
+    // instruction, each lane with its own tensor map, destination and coordinates: four instructions from one lane
+    // took longer than the MMAs of a stage, and the ring ran dry.
+    if (lane < 4) {
+      const CUtensorMap* tm = lane == 0 ? &tmA : lane == 1 ? &tmB : lane == 2 ? &tmSFA : &tmSFB;
+      const uint32_t dst_off = lane == 0 ? 0u : lane == 1 ? kATile : lane == 2 ? kATile + kBTile : kATile + kBTile + kSfAtom;
+      const uint32_t full0 = mapa_shared(bar_full, 0);              // the leader's barrier counts both CTAs
+      const bool expects = (lane == 0 && cta_rank == 0);
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -411,20 +419,18 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const int m0 = t.m0 + BM * cta_rank;
         const int rb_a = m0 >> 7;
         const int rb_b = static_cast<int>((static_cast<long long>(gB) * fp.b_rows_per_group + t.n0) >> 7);
+        // data boxes: (k, row, group); scale atoms: (0, k chunk of 128, 128-row block)
+        const int c1_fixed = lane == 0 ? m0 : t.n0 + 128 * cta_rank;
+        const int c2 = lane == 0 ? 0 : lane == 1 ? gB : lane == 2 ? rb_a : rb_b;
         for (int kb = 0; kb < t.nkb; ++kb) {
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, ST_WAIT_PRODUCER)) {
             ok = false;
             break;
           }
-          const uint32_t full = mapa_shared(bar_full + 8 * s, 0);   // the leader's barrier counts both CTAs
-          if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, 2 * (kATile + kBTile + 3 * kSfAtom));
-          const uint32_t sa = smem_u32(smem + s * kPStage);
+          if (expects) mbar_arrive_expect_tx(bar_full + 8 * s, 2 * (kATile + kBTile + 3 * kSfAtom));
           const int kk = t.k0 + kb * FBK;
-          const int kc = kk >> 7;
-          tma_load_3d_pair(sa, &tmA, full, kk, m0, 0);
-          tma_load_3d_pair(sa + kATile, &tmB, full, kk, t.n0 + 128 * cta_rank, gB);
-          tma_load_3d_pair(sa + kATile + kBTile, &tmSFA, full, 0, kc, rb_a);              // 1 atom
-          tma_load_3d_pair(sa + kATile + kBTile + kSfAtom, &tmSFB, full, 0, kc, rb_b);    // 2 atoms
+          tma_load_3d_pair(smem_u32(smem + s * kPStage) + dst_off, tm, full0 + 8 * s, lane < 2 ? kk : 0,
+                           lane < 2 ? c1_fixed : (kk >> 7), c2);
           if (++s == kPStages) {
             s = 0;
             ph ^= 1;
