@@ -21,8 +21,21 @@ class LoadBalanceMixin:
     the load is summed over the ranks first, so every rank applies the same update."""
 
     def _init_load(self, E):
-        self.register_buffer("load", torch.zeros(E, dtype=torch.int64))
+        # `load` is a plain attribute, not a registered buffer: it is per-rank bookkeeping between two bias updates,
+        # so it stays out of the state dict and a DistributedDataParallel wrapper does not overwrite it with rank 0's
+        self._load_experts = int(E)
+        self.load = None
         self.last_counts = None
+
+    def _load_tensor(self, device=None):
+        if device is None:      # wherever it already lives, else beside the selection bias
+            device = self.load.device if self.load is not None else getattr(getattr(self, "bias", None), "device", "cpu")
+        if self.load is None or self.load.device != torch.device(device):
+            old = self.load
+            self.load = torch.zeros(self._load_experts, dtype=torch.int64, device=device)
+            if old is not None:
+                self.load += old.to(device)
+        return self.load
 
     def _load_group(self):
         return None            # (group,) for layers whose counts are per rank; None = this process sees every token
@@ -30,12 +43,12 @@ class LoadBalanceMixin:
     def _record_counts(self, counts):
         self.last_counts = counts
         if self.training and counts is not None:
-            self.load += counts
+            self._load_tensor(counts.device).add_(counts)
 
     def _global_load(self, counts=None):
         if counts is not None:
             return counts
-        c = self.load.clone()
+        c = self._load_tensor().clone()
         g = self._load_group()
         if g is not None:
             import torch.distributed as dist
@@ -49,7 +62,7 @@ class LoadBalanceMixin:
         if counts is None and self.last_counts is None:
             return
         router_bias_update(self.bias, self._global_load(counts), u)
-        self.load.zero_()
+        self._load_tensor().zero_()
         self.last_counts = None if counts is None else self.last_counts
 
     @torch.no_grad()
@@ -97,7 +110,6 @@ class MoELayer(LoadBalanceMixin, nn.Module):
     def _apply(self, fn, *a, **kw):
         super()._apply(fn, *a, **kw)
         self.bias.data = self.bias.data.float()        # the selection bias stays fp32
-        self.load.data = self.load.data.long()
         if self.act_params is not None:
             self.act_params.data = self.act_params.data.float()
         return self
