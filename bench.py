@@ -147,7 +147,8 @@ def _ep_settings():
     return dict(transport=os.environ.get("B200MOE_EP_TRANSPORT", "p2p"), exchange=os.environ.get("B200MOE_EP_EXCHANGE", "push"),
                 overlap_chunks=int(os.environ.get("B200MOE_EP_CHUNKS", "1")),
                 reserved_sms=int(os.environ.get("B200MOE_EP_RESERVED_SMS", "16")),
-                expert_groups=int(os.environ.get("B200MOE_EP_GROUPS", "1")))
+                expert_groups=int(os.environ.get("B200MOE_EP_GROUPS", "1")),
+                capacity_factor=float(os.environ.get("B200MOE_EP_CAPACITY", "1.5")) or None)
 
 
 def _parallelism_label(n_gpus):
@@ -161,7 +162,11 @@ def _parallelism_label(n_gpus):
                  "GEMM epilogues; NCCL carries only the count all-gather")
     else:
         plane = "peer memory over NVLink: rows pulled in both directions; NCCL carries only the count all-gather"
-    return f"expert parallel ep{n_gpus} (E/{n_gpus} experts per GPU; transport={ep['transport']}, exchange={ep['exchange']}: {plane})"
+    cap = ""
+    if ep["transport"] == "p2p" and ep["exchange"] == "push" and ep.get("capacity_factor"):
+        cap = (f"; local buffers of a fixed capacity, {ep['capacity_factor']} x a rank's own routed rows, no host wait "
+               "(a step that does not fit raises an error, nothing is dropped)")
+    return f"expert parallel ep{n_gpus} (E/{n_gpus} experts per GPU; transport={ep['transport']}, exchange={ep['exchange']}: {plane}{cap})"
 
 
 def _workload(n_gpus, which="headline"):

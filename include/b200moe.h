@@ -309,9 +309,14 @@ int b200moe_combine_bwd(const void* grad_out, const void* eo, const float* w,
  * a peer; the caller separates the phases with cross-rank barriers.  W <= 16, E % W == 0.
  * ep_plan: counts_all (W,E) -> this rank's padded segments poffs_l (E/W+1), counts_l (E/W) live rows,
  * tile_expert_l, src_base (W,E/W) first row of each source rank's block, dest_base (E) first row of
- * THIS rank's block of expert e inside e's owner. */
+ * THIS rank's block of expert e inside e's owner.  rows_cap > 0 (with a status word): the caller's buffers hold
+ * rows_cap padded rows and were sized without reading the row count back to the host; if ANY rank's padded rows
+ * exceed it (every rank evaluates the same count matrix and decides alike) the status word gets 8 and the tables are
+ * written so that the step computes nothing: empty segments, source blocks at a negative row (which the pull kernels
+ * skip).  rows_cap = 0: no check. */
 int b200moe_ep_plan(const int32_t* counts_all, int W, int rank, int E, int32_t* poffs_l, int32_t* counts_l,
-                    int32_t* tile_expert_l, int32_t* src_base, int32_t* dest_base, b200moe_stream_t stream);
+                    int32_t* tile_expert_l, int32_t* src_base, int32_t* dest_base, int64_t rows_cap, int32_t* status,
+                    b200moe_stream_t stream);
 /* ep_local_rows: host_words[0] = the number of routed rows that arrive on this rank (sum over the sources of
  * counts_all (W,E) for the local experts); host_words[1 + j], j < E/W = the row at which local expert j ends in the
  * padded layout (poffs_l[j + 1] of b200moe_ep_plan).  `host_words`: 1 + E/W words of PINNED HOST memory

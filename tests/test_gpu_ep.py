@@ -33,12 +33,15 @@ def _worker(rank, world, port, cfg, transport, q):
         sl = slice(rank * Tl, (rank + 1) * Tl)
         # "p2p" = push exchange, "p2p-pull" = pull exchange, "p2p-pull+24" = pull with the last backward pull
         # overlapped on 24 SMs
-        # "p2p/3" = push exchange with the local experts pipelined in 3 groups
+        # "p2p/3" = push exchange with the local experts pipelined in 3 groups; "p2p@1.5" = buffers of a fixed
+        # capacity (1.5 x a rank's own routed rows), no host wait in the forward
+        transport, _, cap = transport.partition("@")
         transport, _, groups = transport.partition("/")
         transport, _, sms = transport.partition("+")
         transport, _, exch = transport.partition("-")
         layer = pkg.ExpertParallelMoELayer(H, I, E, top_k=k, transport=transport, reserved_sms=int(sms or 0),
-                                           exchange=exch or "push", expert_groups=int(groups or 1)).to(dev).to(torch.bfloat16)
+                                           exchange=exch or "push", expert_groups=int(groups or 1),
+                                           capacity_factor=float(cap) if cap else None).to(dev).to(torch.bfloat16)
         with torch.no_grad():
             layer.gate.weight.copy_(inp["gate_weight"])
             layer.gate_up_proj.copy_(inp["gate_up"][rank * El:(rank + 1) * El])
@@ -61,7 +64,7 @@ def _worker(rank, world, port, cfg, transport, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport", ["nccl", "p2p", "p2p-pull", "p2p-pull+24", "p2p/2", "p2p+24/3"])
+@pytest.mark.parametrize("transport", ["nccl", "p2p", "p2p-pull", "p2p-pull+24", "p2p/2", "p2p+24/3", "p2p@1.5"])
 @pytest.mark.parametrize("cfg", [(2048, 512, 16, 256, 4), (1024, 256, 64, 128, 8)])
 def test_expert_parallel_equals_single_gpu(pkg, cfg, transport):
     if torch.cuda.device_count() < 2:
@@ -111,3 +114,60 @@ def test_expert_parallel_equals_single_gpu(pkg, cfg, transport):
     assert O.rel_l2(cat(3), layer.down_proj.grad.cpu()) < tol
     assert O.rel_l2(res[0][4], layer.gate.weight.grad.cpu()) < 2e-2
     assert torch.equal(res[0][5], layer.bias.cpu()) and torch.equal(res[1][5], layer.bias.cpu())
+
+
+def _overflow_worker(rank, world, port, q):
+    import importlib
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        pkg = importlib.import_module("triton-kernel-fused_b200")
+        T, H, E, I, k = 512, 256, 8, 128, 2
+        torch.manual_seed(3)
+        layer = pkg.ExpertParallelMoELayer(H, I, E, top_k=k, transport="p2p", capacity_factor=0.25).to(dev).to(torch.bfloat16)
+        x = torch.randn(T, H, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        out = layer(x)
+        out.float().sum().backward()
+        torch.cuda.synchronize()
+        try:
+            pkg.check_status()
+            q.put((rank, "no error raised"))
+        except RuntimeError as exc:
+            q.put((rank, "raised" if "fixed-capacity" in str(exc) else f"other: {exc}"))
+        # the status word was cleared by the read: the context and the layer's workspace stay usable
+        torch.cuda.synchronize()
+        pkg.check_status()
+    except BaseException as exc:
+        q.put((rank, "error: " + repr(exc)[:300]))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def test_fixed_capacity_overflow_is_reported_not_truncated(pkg):
+    """Buffers sized for a quarter of the rows that will arrive: every rank's plan kernel refuses the step (status 8),
+    nothing is computed or written out of bounds, and the error reaches the caller as a RuntimeError."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_overflow_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {}
+    try:
+        for _ in range(world):
+            r = q.get(timeout=300)
+            got[r[0]] = r[1]
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
+    assert got == {0: "raised", 1: "raised"}, got

@@ -74,7 +74,7 @@ _SIGNATURES = {
     "b200moe_mxfp8_gather_quant_both": (c_int, [c_void_p] * 3 + [c_int, c_int64, c_int64] + [c_void_p] * 5),
     "b200moe_mxfp8_gather_quant": (c_int, [c_void_p] * 3 + [c_int, c_int64, c_int64] + [c_void_p] * 4),
     "b200moe_mxfp8_expert_wgrad": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int64, c_int64] + [c_void_p] * 3),
-    "b200moe_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 5 + [c_void_p]),
+    "b200moe_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 5 + [c_int64, c_void_p, c_void_p]),
     "b200moe_ep_local_rows": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "b200moe_ep_publish": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int, c_int, c_int64, c_int] + [c_void_p] * 5),
     "b200moe_ep_barrier": (c_int, [c_void_p, c_int, c_int, ctypes.c_uint32, c_int64, c_void_p, c_void_p]),

@@ -113,6 +113,7 @@ const char* b200moe_status_string(int s) {
     case b200moe::ST_BAD_EXPERT_INDEX: return "permute: expert index outside [0, E)";
     case b200moe::ST_SELFTEST_TIMEOUT: return "self-test: the bounded wait ran out (expected)";
     case b200moe::ST_WAIT_PEER: return "expert-parallel barrier: a peer rank did not arrive within the limit";
+    case b200moe::ST_EP_CAPACITY: return "expert parallel: more rows routed to one rank than the fixed-capacity buffers hold; nothing was computed";
     default: return "unknown status";
   }
 }

@@ -17,7 +17,8 @@ enum : int {
   ST_WAIT_EPILOGUE = 4,   // epilogue: the accumulator never completed
   ST_BAD_EXPERT_INDEX = 5,// permute: an expert index outside [0, E)
   ST_SELFTEST_TIMEOUT = 6,// self-test: a wait that nothing completes ran out, as intended
-  ST_WAIT_PEER = 7        // cross-rank barrier: a peer's arrival never showed up within the limit
+  ST_WAIT_PEER = 7,       // cross-rank barrier: a peer's arrival never showed up within the limit
+  ST_EP_CAPACITY = 8      // expert parallel with fixed buffers: a rank would receive more rows than its buffers hold
 };
 
 void set_error(const char* fmt, ...);

@@ -33,9 +33,11 @@ struct PeerPtrs {
 __global__ void __launch_bounds__(B200MOE_MAX_EXPERTS)
 ep_plan_kernel(const int* __restrict__ counts_all, int W, int rank, int E, int* __restrict__ poffs_l,
                int* __restrict__ counts_l, int* __restrict__ tile_expert_l, int* __restrict__ src_base,
-               int* __restrict__ dest_base) {
+               int* __restrict__ dest_base, long long rows_cap, int* __restrict__ status) {
   __shared__ int s_tot[B200MOE_MAX_EXPERTS];
   __shared__ int s_start[B200MOE_MAX_EXPERTS + 1];   // padded start of expert e inside its owner
+  __shared__ int s_over;                             // some owner's padded rows exceed rows_cap (same answer on every rank)
+  if (threadIdx.x == 0) s_over = 0;
   const int e = threadIdx.x;
   const int El = E / W;
   int before_me = 0;
@@ -57,8 +59,20 @@ ep_plan_kernel(const int* __restrict__ counts_all, int W, int rank, int E, int* 
       run += ((s_tot[g] + B200MOE_TILE_M - 1) / B200MOE_TILE_M) * B200MOE_TILE_M;
     }
     if (e == rank) poffs_l[El] = run;
+    if (rows_cap > 0 && run > rows_cap) s_over = 1;
   }
   __syncthreads();
+  if (s_over != 0) {
+    // Fixed-capacity buffers (no host read of the row count) and a routing decision that does not fit on some rank.
+    // Every rank sees the same count matrix and takes this branch together: the step computes nothing (no segment has
+    // rows, no source has a block: the pull kernels skip negative rows) and the status word reports it.
+    if (e <= El) poffs_l[e] = 0;
+    if (e < El) counts_l[e] = 0;
+    if (e < W * El) src_base[e] = -(1 << 30);
+    if (e < E) dest_base[e] = 0;
+    if (e == 0 && status != nullptr) atomicCAS(status, 0, ST_EP_CAPACITY);
+    return;
+  }
   if (e < E) {
     dest_base[e] = s_start[e] + before_me;
     if (e / El == rank) {
@@ -149,8 +163,8 @@ __device__ __forceinline__ unsigned local_rows_of_token(const long long* __restr
       const int e = static_cast<int>(ev);
       const int sp = spos_s[t * k + lane];
       if (sp >= 0) {                    // -1: the source's permutation gave the slot no row
-        local = true;
         row = src_base[s * El + (e - rank * El)] + sp - offs_s[e];
+        local = row >= 0;               // negative: the plan refused the step (fixed capacity exceeded)
       }
     }
   }
@@ -573,14 +587,19 @@ using namespace b200moe;
 extern "C" {
 
 int b200moe_ep_plan(const int32_t* counts_all, int W, int rank, int E, int32_t* poffs_l, int32_t* counts_l,
-                    int32_t* tile_expert_l, int32_t* src_base, int32_t* dest_base, b200moe_stream_t stream) {
+                    int32_t* tile_expert_l, int32_t* src_base, int32_t* dest_base, int64_t rows_cap, int32_t* status,
+                    b200moe_stream_t stream) {
   B200_CHECK_ARG(counts_all && poffs_l && counts_l && tile_expert_l && src_base && dest_base, B200MOE_E_NULL,
                  "ep_plan: null pointer");
   CHECK_WORLD("ep_plan");
   B200_CHECK_ARG(E >= W && E <= B200MOE_MAX_EXPERTS && E % W == 0, B200MOE_E_BAD_SHAPE,
                  "ep_plan: E = %d must be a multiple of W = %d and at most %d", E, W, B200MOE_MAX_EXPERTS);
+  B200_CHECK_ARG(rows_cap <= 0 || (status != nullptr && rows_cap % B200MOE_TILE_M == 0), B200MOE_E_BAD_SHAPE,
+                 "ep_plan: a row capacity (%lld) needs a status word and must be a multiple of %d", (long long)rows_cap,
+                 B200MOE_TILE_M);
   ep_plan_kernel<<<1, B200MOE_MAX_EXPERTS, 0, (cudaStream_t)stream>>>(counts_all, W, rank, E, poffs_l, counts_l,
-                                                                       tile_expert_l, src_base, dest_base);
+                                                                       tile_expert_l, src_base, dest_base, rows_cap,
+                                                                       status);
   B200_CUDA(cudaGetLastError());
   return 0;
 }

@@ -123,7 +123,8 @@ class ExpertParallelMoELayer(LoadBalanceMixin, nn.Module):
     parameter; expert gradients are complete on the owning rank."""
 
     def __init__(self, H, I, E, top_k=2, group=None, norm_topk_prob=True, routed_scaling_factor=1.0, init_std=0.02,
-                 overlap_chunks=1, reserved_sms=0, transport="nccl", exchange="push", expert_groups=1):
+                 overlap_chunks=1, reserved_sms=0, transport="nccl", exchange="push", expert_groups=1,
+                 capacity_factor=None):
         """overlap_chunks > 1 splits the local tokens into that many independent pipelines on their own
         CUDA streams, so the all-to-alls of one chunk run while the expert GEMMs of another do;
         reserved_sms keeps that many SMs free of the persistent GEMM kernels for the communication
@@ -132,7 +133,10 @@ class ExpertParallelMoELayer(LoadBalanceMixin, nn.Module):
         exchange (transport="p2p" only): "push" = result rows are sent to the home ranks by the epilogues of the
         GEMMs that produce them, "pull" = home ranks fetch them while combining.
         expert_groups (transport="p2p", exchange="push"): > 1 pipelines the dispatch-side pulls against the expert
-        GEMMs by that many groups of local experts; the pulls behind the first run on reserved_sms SMs (default 16)."""
+        GEMMs by that many groups of local experts; the pulls behind the first run on reserved_sms SMs (default 16).
+        capacity_factor (same transport and exchange): the local buffers hold that multiple of a rank's own routed
+        rows (T * top_k) and the forward no longer waits on the host for the row count; a step that routes more rows
+        to a rank computes nothing and raises status 8 (RuntimeError at the next check_status), it is never truncated."""
         super().__init__()
         if transport not in ("nccl", "p2p"):
             raise ValueError("transport must be 'nccl' (all_to_all_single) or 'p2p' (peer-memory kernels)")
@@ -152,6 +156,9 @@ class ExpertParallelMoELayer(LoadBalanceMixin, nn.Module):
         if int(expert_groups) > 1 and not (transport == "p2p" and exchange == "push"):
             raise ValueError("expert_groups > 1 needs transport='p2p' with exchange='push'")
         self.expert_groups = max(1, int(expert_groups))
+        if capacity_factor is not None and not (transport == "p2p" and exchange == "push" and self.expert_groups == 1):
+            raise ValueError("capacity_factor needs transport='p2p' with exchange='push' and expert_groups=1")
+        self.capacity_factor = capacity_factor
         self._streams = None
         world = dist.get_world_size(group)
         if E % world != 0:
@@ -187,7 +194,8 @@ class ExpertParallelMoELayer(LoadBalanceMixin, nn.Module):
             if ws is None or (ws.T, ws.H, ws.k) != (T, H, self.top_k):
                 ws = self._workspace = SymmetricWorkspace(T, H, self.top_k, self.num_experts, self.group, flat.device,
                                                           overlap_sms=self.reserved_sms, exchange=self.exchange,
-                                                          expert_groups=self.expert_groups)
+                                                          expert_groups=self.expert_groups,
+                                                          capacity_factor=self.capacity_factor)
             return ep_moe_p2p(flat, idx, w, self.gate_up_proj, self.down_proj, ws), counts
         return ep_moe(flat, idx, w, self.gate_up_proj, self.down_proj, self.num_experts, self.group), counts
 

@@ -16,6 +16,11 @@ g+1 beside the GLU-backward GEMM of group g; only the pull of the first group is
 8 GPUs at the benchmark's layer the two extra GEMM launches and the SMs the GEMMs give up cost more than the hidden
 half of the pulls saves (a pull confined to 16-24 SMs keeps too few loads in flight to fill NVLink).
 
+`capacity_factor` (push exchange) sizes the local buffers once, for that multiple of a rank's own routed rows, and
+drops the forward's host wait: nothing is read back, the host runs ahead of the GPU for the whole step.  A routing
+decision that sends more rows to some rank than that is not truncated: `b200moe_ep_plan` raises status 8 on every
+rank, the step computes nothing, and `check_status` reports it.
+
 Per step and direction there is one tiny NCCL all-gather (the (W,E) count matrix, which also orders
 the phases), one host read of that matrix (to size the local buffers) and two device-side barriers
 (`b200moe_ep_barrier`: flag words in the symmetric buffer, plain peer stores and bounded local waits).
@@ -129,7 +134,8 @@ class SymmetricWorkspace:
     """One symmetric allocation carved into the buffers peers read.  Sized for the worst case
     (every routed row of every rank lands on one rank), so it is allocated once."""
 
-    def __init__(self, T, H, k, E, group, device, overlap_sms=0, exchange="push", expert_groups=1):
+    def __init__(self, T, H, k, E, group, device, overlap_sms=0, exchange="push", expert_groups=1,
+                 capacity_factor=None):
         """exchange="pull", overlap_sms > 0: in the backward pass the last pull (grad_hidden) runs on that many SMs
         beside the weight-gradient GEMMs, which leave them free and run on a high-priority stream of their own.
         exchange="push", expert_groups > 1: the dispatch-side pulls are pipelined against the GEMMs by groups of
@@ -144,6 +150,16 @@ class SymmetricWorkspace:
         else:
             self.overlap_sms = (int(overlap_sms) or 16) if self.expert_groups > 1 else 0
         self.gemm_stream = torch.cuda.Stream(device=device, priority=-1) if exchange == "pull" and self.overlap_sms > 0 else None
+        # fixed-capacity buffers: rows (a multiple of the tile) every step's local buffers have; None = sized per step
+        self.rows_fixed = None
+        if capacity_factor is not None:
+            if exchange != "push" or self.expert_groups > 1:
+                raise ValueError("capacity_factor needs exchange='push' and expert_groups=1")
+            if not float(capacity_factor) > 0:
+                raise ValueError("capacity_factor must be positive")
+            W_ = dist.get_world_size(group)
+            rows = min(W_ * T * k, int(-(-float(capacity_factor) * T * k // 1)))
+            self.rows_fixed = L.padded_rows_cap(rows, E // W_)
         self.side_stream = torch.cuda.Stream(device=device) if self.expert_groups > 1 else None
         self.pipe_events = [torch.cuda.Event() for _ in range(self.expert_groups)] if self.expert_groups > 1 else []
         self.group = group
@@ -274,20 +290,23 @@ class _ExpertParallelP2P(torch.autograd.Function):
         # the one host wait of the step: a kernel stores the row count into pinned host memory and the host waits
         # for an event behind it (a .item() would be a device-to-host copy, and that copy queues behind any large
         # transfer the caller's input pipeline has on the copy engines)
-        L.check(L.lib().b200moe_ep_local_rows(L.ptr(counts_all), W, rank, E, ws.rows_host.data_ptr(), st))
-        ws.rows_event.record(torch.cuda.current_stream(dev))
-        ws.rows_event.synchronize()
-        words = ws.rows_host.tolist()
-        R = words[0]
-        groups = expert_groups(words[1:], ws.expert_groups) if ws.expert_groups > 1 else []
-        cap_l = L.padded_rows_cap(R, El)
+        if ws.rows_fixed is None:
+            L.check(L.lib().b200moe_ep_local_rows(L.ptr(counts_all), W, rank, E, ws.rows_host.data_ptr(), st))
+            ws.rows_event.record(torch.cuda.current_stream(dev))
+            ws.rows_event.synchronize()
+            words = ws.rows_host.tolist()
+            R = words[0]
+            groups = expert_groups(words[1:], ws.expert_groups) if ws.expert_groups > 1 else []
+            cap_l = L.padded_rows_cap(R, El)
+        else:               # buffers of a fixed size: no host wait; the plan kernel checks that the rows fit
+            R, groups, cap_l = 0, [], ws.rows_fixed
         poffs_l = torch.empty(El + 1, **i32)
         counts_l = torch.empty(El, **i32)
         tile_expert_l = torch.empty(cap_l // ops.TILE_M, **i32)
         src_base = torch.empty(W * El, **i32)
         dest_base = torch.empty(E, **i32)
-        _plan(L.ptr(counts_all), W, rank, E, L.ptr(poffs_l), L.ptr(counts_l),
-                                    L.ptr(tile_expert_l), L.ptr(src_base), L.ptr(dest_base), st)
+        _plan(L.ptr(counts_all), W, rank, E, L.ptr(poffs_l), L.ptr(counts_l), L.ptr(tile_expert_l), L.ptr(src_base),
+              L.ptr(dest_base), cap_l if ws.rows_fixed is not None else 0, L.ptr(L.status_word(dev)), st)
         x_s = torch.empty(cap_l, H, dtype=torch.bfloat16, device=dev)
         push = ws.exchange == "push"
         row_rank = torch.empty(cap_l, **i32) if push else None
