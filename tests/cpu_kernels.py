@@ -121,3 +121,30 @@ class CpuKernels:
         grad_eo[:total][live] = go * w.flatten()[rs[live]][:, None].to(go.dtype)
         grad_w.view(-1)[rs[live]] = (go.float() * eo[:total][live].float()).sum(1)
         return grad_eo, grad_w
+
+    @staticmethod
+    def ep_plan(counts_all, W, rank, E, rows_cap=0, tile=256):
+        """CPU model of the expert-parallel plan (csrc/ep.cu ep_plan_kernel): from the (W, E) count matrix, this rank's
+        padded segments, the first row of every source's block in them, and the first row of this rank's block inside
+        every expert's owner.  rows_cap > 0: if any owner's padded rows exceed it, every rank returns the tables of a
+        step that computes nothing."""
+        El = E // W
+        tot = counts_all.sum(0)
+        pad = lambda c: (int(c) + tile - 1) // tile * tile
+        start = torch.zeros(E, dtype=torch.int64)
+        owner_rows = []
+        for d in range(W):
+            run = 0
+            for j in range(El):
+                start[d * El + j] = run
+                run += pad(tot[d * El + j])
+            owner_rows.append(run)
+        if rows_cap > 0 and any(r > rows_cap for r in owner_rows):
+            return dict(overflow=True, poffs_l=torch.zeros(El + 1, dtype=torch.int64), counts_l=torch.zeros(El, dtype=torch.int64),
+                        src_base=torch.full((W * El,), -(1 << 30), dtype=torch.int64), dest_base=torch.zeros(E, dtype=torch.int64))
+        dest_base = start + counts_all[:rank].sum(0)
+        mine = slice(rank * El, (rank + 1) * El)
+        poffs_l = torch.cat([start[mine], torch.tensor([owner_rows[rank]])])
+        src_base = torch.stack([start[mine] + counts_all[:s, mine].sum(0) for s in range(W)]).reshape(-1)
+        return dict(overflow=False, poffs_l=poffs_l, counts_l=tot[mine].clone(), src_base=src_base, dest_base=dest_base)
+

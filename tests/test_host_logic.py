@@ -187,3 +187,17 @@ def test_load_telemetry_figures():
     assert st["load"] == [8, 4, 4, 0] and st["tokens_routed"] == 16 and st["idle_experts"] == 1
     assert st["max_over_mean"] == 2.0 and st["min_over_mean"] == 0.0
     assert abs(st["cv"] - (8.0 ** 0.5) / 4.0) < 1e-12          # std of (8,4,4,0) = sqrt(8), mean 4
+
+
+def test_fixed_capacity_rows():
+    """Sizing of the expert-parallel layer's fixed-capacity buffers: factor x own routed rows, rounded up, clamped to
+    the rows that exist; nonsense factors are refused before anything is allocated."""
+    import pytest
+    ep = importlib.import_module("triton-kernel-fused_b200.ep_p2p")
+    assert ep.fixed_capacity_rows(8, 16384, 6, 1.5) == 147456
+    assert ep.fixed_capacity_rows(8, 1000, 3, 1.0001) == 3001          # rounded up
+    assert ep.fixed_capacity_rows(2, 1024, 4, 5.0) == 2 * 4096          # never more rows than exist
+    assert ep.fixed_capacity_rows(4, 10, 2, 0.25) == 5
+    for bad in (0, -1.0, float("nan")):
+        with pytest.raises(ValueError):
+            ep.fixed_capacity_rows(2, 8, 2, bad)

@@ -78,3 +78,36 @@ def test_slots_without_a_row_are_skipped_by_the_combine_model():
     assert torch.equal(out[0], 0.5 * rows[0])
     assert torch.equal(out[1], rows[5] + 2.0 * rows[2])
     assert torch.equal(CpuKernels.combine_raw(rows, None, table, 2, 2)[0], rows[0])
+
+
+def test_expert_parallel_plan_blocks_tile_every_segment_and_overflow_is_decided_alike():
+    """The plan of the expert-parallel exchange (model of csrc/ep.cu ep_plan_kernel): the blocks of the W sources
+    tile each expert's live rows without gap or overlap, the home rank's idea of where its rows go (dest_base) is the
+    owner's idea of where that source's block starts (src_base), and a count matrix that does not fit a fixed
+    capacity is refused by every rank together."""
+    import torch
+    from tests.cpu_kernels import CpuKernels
+    g = torch.Generator().manual_seed(0)
+    W, E = 4, 16
+    El = E // W
+    counts = torch.randint(0, 700, (W, E), generator=g)
+    counts[:, 5] = 0                                              # an expert nobody routes to
+    plans = [CpuKernels.ep_plan(counts, W, r, E) for r in range(W)]
+    for owner in range(W):
+        p = plans[owner]
+        for j in range(El):
+            e = owner * El + j
+            lo = int(p["poffs_l"][j])
+            assert lo % 256 == 0 and int(p["poffs_l"][j + 1]) - lo == (int(p["counts_l"][j]) + 255) // 256 * 256
+            at = lo
+            for s in range(W):
+                assert int(p["src_base"][s * El + j]) == at == int(plans[s]["dest_base"][e])
+                at += int(counts[s, e])
+            assert at == lo + int(p["counts_l"][j])
+    rows = [int(p["poffs_l"][El]) for p in plans]
+    cap = max(rows) - 256                                         # one owner does not fit
+    refused = [CpuKernels.ep_plan(counts, W, r, E, rows_cap=cap) for r in range(W)]
+    assert all(p["overflow"] for p in refused)
+    assert all(int(p["poffs_l"].sum()) == 0 and int(p["counts_l"].sum()) == 0 and (p["src_base"] < 0).all() for p in refused)
+    assert not any(CpuKernels.ep_plan(counts, W, r, E, rows_cap=max(rows))["overflow"] for r in range(W))
+

@@ -92,6 +92,16 @@ def _align(n, a=256):
     return (n + a - 1) // a * a
 
 
+def fixed_capacity_rows(W, T, k, capacity_factor):
+    """Routed rows the fixed-capacity buffers of one rank are sized for: capacity_factor times the rank's own routed
+    rows (T * k), rounded up, never more than the W * T * k rows that exist."""
+    cf = float(capacity_factor)
+    if not cf > 0:
+        raise ValueError("capacity_factor must be positive")
+    M = int(T) * int(k)
+    return min(int(W) * M, int(-(-cf * M // 1)))
+
+
 def expert_groups(ends, n):
     """Split local experts 0..len(ends)-1 into at most `n` runs of consecutive experts with about equal padded rows.
     ends[j] = padded row at which expert j ends.  Returns [(e_lo, e_hi, row_lo, row_hi)], empty runs left out."""
@@ -155,11 +165,8 @@ class SymmetricWorkspace:
         if capacity_factor is not None:
             if exchange != "push" or self.expert_groups > 1:
                 raise ValueError("capacity_factor needs exchange='push' and expert_groups=1")
-            if not float(capacity_factor) > 0:
-                raise ValueError("capacity_factor must be positive")
             W_ = dist.get_world_size(group)
-            rows = min(W_ * T * k, int(-(-float(capacity_factor) * T * k // 1)))
-            self.rows_fixed = L.padded_rows_cap(rows, E // W_)
+            self.rows_fixed = L.padded_rows_cap(fixed_capacity_rows(W_, T, k, capacity_factor), E // W_)
         self.side_stream = torch.cuda.Stream(device=device) if self.expert_groups > 1 else None
         self.pipe_events = [torch.cuda.Event() for _ in range(self.expert_groups)] if self.expert_groups > 1 else []
         self.group = group
